@@ -1,0 +1,75 @@
+"""libstrix_b200: sm_100a (B200) kernels behind libstrix's op surface.
+
+Usable as a drop-in for the reference's `strix` package on its quantized
+inference path (`import libstrix_b200 as strix`): the same `select / explain /
+geometries / kernels / ops / selections / Range` table API
+(python/strix/registry.py of the reference), the same wrappers (`attn_decode`,
+python/strix/__init__.py:343-381) and the same `torch.ops.strix.*` schemas.
+
+Importing loads libstrix_b200.so (the C-ABI of include/strix_b200.h) and fails
+if it has not been built; nothing here computes on the CPU.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from .registry import Range, explain, geometries, kernels, ops, select, selections
+
+_lib.load()
+from . import torch_ops  # noqa: E402  (registers torch.ops.strix.*)
+
+StrixError = _lib.StrixError
+
+
+def is_supported_device() -> bool:
+    """True on a CUDA device of compute capability 10.x (B200). The reference
+    gates on HIP + gfx1151 instead (python/strix/__init__.py:510-513)."""
+    if not torch.cuda.is_available() or torch.version.cuda is None:
+        return False
+    return torch.cuda.get_device_capability(0)[0] == 10
+
+
+def attn_decode(
+    out: torch.Tensor,
+    q: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    seq_lens: torch.Tensor,
+    block_table: torch.Tensor,
+    scale: float,
+    num_splits: int = 1,
+    window_left: int = -1,
+    k_scale: torch.Tensor | None = None,
+    v_scale: torch.Tensor | None = None,
+    sinks: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """Paged attention for one query token per sequence (decode), split-KV.
+
+    q, out: [N, Hq, D] bf16; caches: [blocks, block_size, Hkv, D] views; the
+    query is position seq_lens[n] - 1. The caches are int8 with k_scale /
+    v_scale ([blocks, block_size, Hkv] fp32) as dequant scales, one per (key,
+    head). sinks: optional fp32 [Hq] attention-sink logits. num_splits in
+    1..64 divides each sequence's keys as the reference does; num_splits = 0
+    uses fixed 1024-key segments, which balances ragged batches. No host sync.
+    """
+    torch.ops.strix.attn_decode_bf16(
+        out, q, key_cache, value_cache, seq_lens.to(torch.int32),
+        block_table.to(torch.int32), scale, num_splits, window_left, k_scale, v_scale, sinks,
+    )
+    return out
+
+
+__all__ = [
+    "Range",
+    "StrixError",
+    "attn_decode",
+    "explain",
+    "geometries",
+    "is_supported_device",
+    "kernels",
+    "ops",
+    "select",
+    "selections",
+]

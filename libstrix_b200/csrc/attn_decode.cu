@@ -1,0 +1,548 @@
+// Paged decode attention (one query token per sequence) over an int8 or bf16
+// KV cache, for sm_100a.
+//
+// Semantics follow strix::attn_decode_bf16 (csrc/attn/attn_decode_bf16.hip:28-300
+// of the reference): exp2-domain online softmax, K scale multiplies the score,
+// V scale multiplies P, l is the unweighted sum of p, split-KV partials
+// (m, l, un-normalised O) combined by a second kernel, sinks folded after the
+// combine, window_left keys to the left of the query.
+//
+// Design (HBM-bound: 1,056 bytes per key per sequence at 4 KV heads, D = 128):
+//   * one CTA per (segment, sequence, group of KV heads); its 8 warps are split
+//     over the KV heads of the group, so the warps of one CTA walk the same
+//     pages at the same time and each page is fetched from DRAM once;
+//   * a warp owns whole 16-key tiles: K and V bytes go global -> registers with
+//     128-bit loads (a row of one head is read by 4 or 8 adjacent lanes as one
+//     contiguous run), double-buffered one tile ahead, block-table entries 32
+//     tiles ahead;
+//   * int8 -> fp16 is exact and done with byte permutes (0x6400 | (b ^ 0x80) is
+//     1024 + b + 128), which also performs the V transposition for free;
+//   * scores are S^T = K Q^T with the 16 keys as the MMA M dimension and the
+//     (up to) 8 query heads of the KV head as N, so no tensor-core work is
+//     wasted on padding; P^T comes from the score fragment with two
+//     movmatrix transposes; O^T = V^T P^T accumulates in fp32 registers;
+//   * each warp keeps its own (m, l, O); warps of a head merge through shared
+//     memory once, at the end.
+#include <cstdlib>
+
+#include "common.cuh"
+
+namespace strix {
+namespace {
+
+constexpr uint32_t kMagic = 0x64646464u;   // high byte of fp16 1024 + x
+constexpr uint32_t kBias = 0x64806480u;    // f16x2 (1152, 1152)
+
+struct DecodeArgs {
+  __nv_bfloat16* out;
+  const __nv_bfloat16* q;
+  const void* kc;
+  const void* vc;
+  const float* ksc;
+  const float* vsc;
+  const int32_t* seq_lens;
+  const int32_t* bt;
+  const float* sinks;
+  float* o_part;
+  float* ml_part;
+  int64_t bt_stride, q_st, q_sh, o_st, o_sh;
+  int64_t k_sb, k_ss, k_sh, v_sb, v_ss, v_sh;
+  int64_t ks_sb, ks_ss, ks_sh, vs_sb, vs_ss, vs_sh;
+  int block_size, hq, hkv, g, hpc;  // hpc: KV heads per CTA
+  int nseg, seg_keys, win_left;
+  float scale_log2;
+};
+
+template <int NW, bool ALIGNED>
+__device__ __forceinline__ void load_words(uint32_t (&dst)[NW], const uint8_t* p) {
+  if constexpr (ALIGNED) {
+    static_assert(NW % 4 == 0, "vector path needs whole uint4s");
+#pragma unroll
+    for (int i = 0; i < NW / 4; ++i) {
+      const uint4 x = ldg_stream(p + 16 * i);
+      dst[4 * i] = x.x;
+      dst[4 * i + 1] = x.y;
+      dst[4 * i + 2] = x.z;
+      dst[4 * i + 3] = x.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < NW; ++i)
+      dst[i] = __ldg(reinterpret_cast<const uint32_t*>(p + 4 * i));
+  }
+}
+
+// One 16-key tile of one KV head as this lane sees it. With g = lane / 4 and
+// c = lane % 4: K rows g and g + 8, bytes [c * D/4, (c + 1) * D/4) of each;
+// V rows 2c, 2c + 1, 2c + 8, 2c + 9, bytes [g * D/8, (g + 1) * D/8) of each.
+template <int D>
+struct TileQ8 {
+  uint32_t k[2][D / 16];
+  uint32_t v[4][D / 32];
+  float ks[2], vs[2];
+};
+
+template <int D, bool ALIGNED>
+__device__ __forceinline__ void load_tile(TileQ8<D>& t, const DecodeArgs& a, int blk,
+                                          int off, int kvh, int g, int c) {
+  const uint8_t* kb = static_cast<const uint8_t*>(a.kc) + int64_t(blk) * a.k_sb +
+                      int64_t(off) * a.k_ss + int64_t(kvh) * a.k_sh + c * (D / 4);
+  load_words<D / 16, ALIGNED>(t.k[0], kb + int64_t(g) * a.k_ss);
+  load_words<D / 16, ALIGNED>(t.k[1], kb + int64_t(g + 8) * a.k_ss);
+  const uint8_t* vb = static_cast<const uint8_t*>(a.vc) + int64_t(blk) * a.v_sb +
+                      int64_t(off) * a.v_ss + int64_t(kvh) * a.v_sh + g * (D / 8);
+  load_words<D / 32, ALIGNED>(t.v[0], vb + int64_t(2 * c) * a.v_ss);
+  load_words<D / 32, ALIGNED>(t.v[1], vb + int64_t(2 * c + 1) * a.v_ss);
+  load_words<D / 32, ALIGNED>(t.v[2], vb + int64_t(2 * c + 8) * a.v_ss);
+  load_words<D / 32, ALIGNED>(t.v[3], vb + int64_t(2 * c + 9) * a.v_ss);
+  const float* ksp = a.ksc + int64_t(blk) * a.ks_sb + int64_t(off) * a.ks_ss +
+                     int64_t(kvh) * a.ks_sh;
+  const float* vsp = a.vsc + int64_t(blk) * a.vs_sb + int64_t(off) * a.vs_ss +
+                     int64_t(kvh) * a.vs_sh;
+  t.ks[0] = __ldg(ksp + int64_t(g) * a.ks_ss);
+  t.ks[1] = __ldg(ksp + int64_t(g + 8) * a.ks_ss);
+  t.vs[0] = __ldg(vsp + int64_t(g) * a.vs_ss);
+  t.vs[1] = __ldg(vsp + int64_t(g + 8) * a.vs_ss);
+}
+
+// Per-warp running softmax state for the two query heads 2c and 2c + 1 this
+// lane holds scores for, and the O^T accumulator: acc[t] covers head dims
+// g * D/8 + 2t (c0, c1) and + 2t + 1 (c2, c3) for heads 2c (c0, c2), 2c + 1.
+template <int D>
+struct WarpState {
+  float m[2], l[2];
+  float acc[D / 16][4];
+};
+
+template <int D>
+__device__ __forceinline__ void compute_tile(const TileQ8<D>& t, WarpState<D>& st,
+                                             const uint32_t (&qf)[D / 8], int key0,
+                                             int k_begin, int k_end, float scale_log2,
+                                             int g) {
+  // S^T[16 keys, 8 heads] = K Q^T
+  float s[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int i = 0; i < D / 16; ++i) {
+    const uint32_t w0 = t.k[0][i] ^ 0x80808080u, w1 = t.k[1][i] ^ 0x80808080u;
+    uint32_t a[4];
+    a[0] = sub_f16x2(prmt(w0, kMagic, 0x4140), kBias);
+    a[1] = sub_f16x2(prmt(w1, kMagic, 0x4140), kBias);
+    a[2] = sub_f16x2(prmt(w0, kMagic, 0x4342), kBias);
+    a[3] = sub_f16x2(prmt(w1, kMagic, 0x4342), kBias);
+    mma_f16_16816(s, a, qf[2 * i], qf[2 * i + 1]);
+  }
+  const int ka = key0 + g, kb = ka + 8;
+  const bool va = ka >= k_begin && ka < k_end, vb = kb >= k_begin && kb < k_end;
+  const float ksa = t.ks[0] * scale_log2, ksb = t.ks[1] * scale_log2;
+  const float x0 = va ? s[0] * ksa : -INFINITY, x1 = va ? s[1] * ksa : -INFINITY;
+  const float x2 = vb ? s[2] * ksb : -INFINITY, x3 = vb ? s[3] * ksb : -INFINITY;
+  float mx0 = fmaxf(x0, x2), mx1 = fmaxf(x1, x3);
+#pragma unroll
+  for (int o = 4; o < 32; o <<= 1) {
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+  }
+  const float mn0 = fmaxf(st.m[0], mx0), mn1 = fmaxf(st.m[1], mx1);
+  const float r0 = mn0 == -INFINITY ? 0.f : mn0, r1 = mn1 == -INFINITY ? 0.f : mn1;
+  const float al0 = fast_exp2(st.m[0] - r0), al1 = fast_exp2(st.m[1] - r1);
+  st.m[0] = mn0;
+  st.m[1] = mn1;
+  const float p0 = fast_exp2(x0 - r0), p1 = fast_exp2(x1 - r1);
+  const float p2 = fast_exp2(x2 - r0), p3 = fast_exp2(x3 - r1);
+  st.l[0] = st.l[0] * al0 + (p0 + p2);
+  st.l[1] = st.l[1] * al1 + (p1 + p3);
+  // A stale scale of a masked key may be anything (NaN included): p is 0 there,
+  // so force the product to 0 as well.
+  const float vsa = va ? t.vs[0] : 0.f, vsb = vb ? t.vs[1] : 0.f;
+  const uint32_t b0 = movmatrix_trans(pack_f16x2(p0 * vsa, p1 * vsa));
+  const uint32_t b1 = movmatrix_trans(pack_f16x2(p2 * vsb, p3 * vsb));
+  // O^T[D, 8 heads] = alpha O^T + V^T P^T
+#pragma unroll
+  for (int i = 0; i < D / 16; ++i) {
+    st.acc[i][0] *= al0;
+    st.acc[i][1] *= al1;
+    st.acc[i][2] *= al0;
+    st.acc[i][3] *= al1;
+    const int w = i / 2;
+    const uint32_t sel = (i & 1) ? 0x7362u : 0x5140u;
+    const uint32_t x01 = prmt(t.v[0][w] ^ 0x80808080u, t.v[1][w] ^ 0x80808080u, sel);
+    const uint32_t x23 = prmt(t.v[2][w] ^ 0x80808080u, t.v[3][w] ^ 0x80808080u, sel);
+    uint32_t a[4];
+    a[0] = sub_f16x2(prmt(x01, kMagic, 0x4140), kBias);
+    a[1] = sub_f16x2(prmt(x01, kMagic, 0x4342), kBias);
+    a[2] = sub_f16x2(prmt(x23, kMagic, 0x4140), kBias);
+    a[3] = sub_f16x2(prmt(x23, kMagic, 0x4342), kBias);
+    mma_f16_16816(st.acc[i], a, b0, b1);
+  }
+}
+
+template <int D, bool ALIGNED, int kWarps, int kMinCtas>
+__global__ void __launch_bounds__(kWarps * 32, kMinCtas)
+attn_decode_q8_kernel(const DecodeArgs a) {
+  constexpr int kThreads = kWarps * 32;
+  const int seg = blockIdx.x, hgrp = blockIdx.y, n = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, c = lane & 3;
+  const int hslot = warp % a.hpc;           // KV head within the CTA's group
+  const int sub = warp / a.hpc;             // this warp's rank among the head's warps
+  const int wph = kWarps / a.hpc;           // warps per KV head
+  const int kvh = hgrp * a.hpc + hslot;
+  const int G = a.g;
+  const int h0 = kvh * G;
+
+  const int kv_len = a.seq_lens[n];
+  const int pos = kv_len - 1;
+  const int k_lo = a.win_left >= 0 ? max(0, pos - a.win_left) : 0;
+  const int seg_len = a.seg_keys > 0
+                          ? a.seg_keys
+                          : ((kv_len - k_lo + a.nseg - 1) / a.nseg + 15) / 16 * 16;
+  const int k_begin = k_lo + seg * seg_len;
+  const int k_end = min(kv_len, k_begin + seg_len);
+  const bool single = a.nseg == 1;
+
+  __shared__ float s_m[kWarps][8], s_l[kWarps][8];
+  __shared__ __align__(16) float s_o[4][8][D];   // hpc <= 4 slots
+
+  if (k_begin >= k_end) {  // empty segment (block-uniform)
+    const int heads = a.hpc * G;
+    if (single) {
+      for (int i = threadIdx.x; i < heads * D; i += kThreads) {
+        const int h = hgrp * heads + i / D;
+        a.out[int64_t(n) * a.o_st + int64_t(h) * a.o_sh + i % D] = __float2bfloat16(0.f);
+      }
+    } else if (threadIdx.x < heads) {
+      const int h = hgrp * heads + threadIdx.x;
+      float* ml = a.ml_part + ((int64_t(n) * a.hq + h) * a.nseg + seg) * 2;
+      ml[0] = -INFINITY;
+      ml[1] = 0.f;
+    }
+    return;
+  }
+
+  // Q^T fragments: head g of this KV head, dims c * D/4 + 4i .. + 3 for k-step i.
+  uint32_t qf[D / 8];
+  if (g < G) {
+    const __nv_bfloat16* qp =
+        a.q + int64_t(n) * a.q_st + int64_t(h0 + g) * a.q_sh + c * (D / 4);
+#pragma unroll
+    for (int i = 0; i < D / 16; ++i) {
+      const uint2 w = *reinterpret_cast<const uint2*>(qp + 4 * i);
+      qf[2 * i] = pack_f16x2(bf16_lo(w.x), bf16_hi(w.x));
+      qf[2 * i + 1] = pack_f16x2(bf16_lo(w.y), bf16_hi(w.y));
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) qf[i] = 0u;
+  }
+
+  WarpState<D> st;
+  st.m[0] = st.m[1] = -INFINITY;
+  st.l[0] = st.l[1] = 0.f;
+#pragma unroll
+  for (int i = 0; i < D / 16; ++i)
+    st.acc[i][0] = st.acc[i][1] = st.acc[i][2] = st.acc[i][3] = 0.f;
+
+  // Tiles are aligned to 16 keys from position 0, so a tile never straddles a
+  // page (block_size is a multiple of 16).
+  const int t_begin = k_begin >> 4, t_end = (k_end + 15) >> 4;
+  const int32_t* bt = a.bt + int64_t(n) * a.bt_stride;
+  const int bs = a.block_size;
+
+  int my_blk = 0, nload = 0;
+  // Returns the block id of this warp's nload-th tile; every 32 tiles each lane
+  // fetches one entry ahead of use.
+  auto next_block = [&](int tile) {
+    if ((nload & 31) == 0) {
+      const int tl = tile + lane * wph;
+      my_blk = tl < t_end ? bt[(tl * 16) / bs] : 0;
+    }
+    const int blk = __shfl_sync(0xffffffffu, my_blk, nload & 31);
+    ++nload;
+    return blk;
+  };
+
+  TileQ8<D> ta, tb;
+  int t = t_begin + sub;
+  if (t < t_end) {
+    const int blk = next_block(t);
+    load_tile<D, ALIGNED>(ta, a, blk, (t * 16) % bs, kvh, g, c);
+  }
+  while (t < t_end) {
+    if (t + wph < t_end) {
+      const int blk = next_block(t + wph);
+      load_tile<D, ALIGNED>(tb, a, blk, ((t + wph) * 16) % bs, kvh, g, c);
+    }
+    compute_tile<D>(ta, st, qf, t * 16, k_begin, k_end, a.scale_log2, g);
+    t += wph;
+    if (t >= t_end) break;
+    if (t + wph < t_end) {
+      const int blk = next_block(t + wph);
+      load_tile<D, ALIGNED>(ta, a, blk, ((t + wph) * 16) % bs, kvh, g, c);
+    }
+    compute_tile<D>(tb, st, qf, t * 16, k_begin, k_end, a.scale_log2, g);
+    t += wph;
+  }
+
+  // ---- merge the warps of each KV head ------------------------------------
+#pragma unroll
+  for (int o = 4; o < 32; o <<= 1) {
+    st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], o);
+    st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], o);
+  }
+  if (g == 0) {
+    s_m[warp][2 * c] = st.m[0];
+    s_m[warp][2 * c + 1] = st.m[1];
+    s_l[warp][2 * c] = st.l[0];
+    s_l[warp][2 * c + 1] = st.l[1];
+  }
+  __syncthreads();
+  float M[2] = {-INFINITY, -INFINITY}, L[2] = {0.f, 0.f};
+  for (int w = hslot; w < kWarps; w += a.hpc) {
+    M[0] = fmaxf(M[0], s_m[w][2 * c]);
+    M[1] = fmaxf(M[1], s_m[w][2 * c + 1]);
+  }
+  for (int w = hslot; w < kWarps; w += a.hpc) {
+    const float m0 = s_m[w][2 * c], m1 = s_m[w][2 * c + 1];
+    L[0] += m0 == -INFINITY ? 0.f : s_l[w][2 * c] * fast_exp2(m0 - M[0]);
+    L[1] += m1 == -INFINITY ? 0.f : s_l[w][2 * c + 1] * fast_exp2(m1 - M[1]);
+  }
+  {
+    const float f0 = st.m[0] == -INFINITY ? 0.f : fast_exp2(st.m[0] - M[0]);
+    const float f1 = st.m[1] == -INFINITY ? 0.f : fast_exp2(st.m[1] - M[1]);
+#pragma unroll
+    for (int i = 0; i < D / 16; ++i) {
+      st.acc[i][0] *= f0;
+      st.acc[i][1] *= f1;
+      st.acc[i][2] *= f0;
+      st.acc[i][3] *= f1;
+    }
+  }
+  // s_o[slot][head][d]: lane owns dims g * D/8 + 2i, + 2i + 1 of heads 2c, 2c + 1.
+  float* so0 = &s_o[hslot][2 * c][g * (D / 8)];
+  float* so1 = &s_o[hslot][2 * c + 1][g * (D / 8)];
+  for (int r = wph - 1; r >= 1; --r) {
+    if (sub == r) {
+#pragma unroll
+      for (int i = 0; i < D / 16; ++i) {
+        *reinterpret_cast<float2*>(so0 + 2 * i) = make_float2(st.acc[i][0], st.acc[i][2]);
+        *reinterpret_cast<float2*>(so1 + 2 * i) = make_float2(st.acc[i][1], st.acc[i][3]);
+      }
+    }
+    __syncthreads();
+    if (sub == 0) {
+#pragma unroll
+      for (int i = 0; i < D / 16; ++i) {
+        const float2 x = *reinterpret_cast<const float2*>(so0 + 2 * i);
+        const float2 y = *reinterpret_cast<const float2*>(so1 + 2 * i);
+        st.acc[i][0] += x.x;
+        st.acc[i][2] += x.y;
+        st.acc[i][1] += y.x;
+        st.acc[i][3] += y.y;
+      }
+    }
+    __syncthreads();
+  }
+  if (sub != 0) return;
+
+  // ---- write: final rows (single segment) or partials ----------------------
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int hl = 2 * c + j;
+    if (hl >= G) continue;
+    const int h = h0 + hl;
+    if (single) {
+      float inv = L[j] > 0.f ? 1.f / L[j] : 0.f;
+      if (a.sinks != nullptr) {
+        const float s2 = a.sinks[h] * kLog2e;
+        const float mf = fmaxf(M[j], s2);
+        const float al = M[j] == -INFINITY ? 0.f : fast_exp2(M[j] - mf);
+        inv = al / (L[j] * al + fast_exp2(s2 - mf));
+      }
+      __nv_bfloat16* op = a.out + int64_t(n) * a.o_st + int64_t(h) * a.o_sh + g * (D / 8);
+#pragma unroll
+      for (int i = 0; i < D / 16; ++i)
+        *reinterpret_cast<uint32_t*>(op + 2 * i) =
+            pack_bf16x2(st.acc[i][j] * inv, st.acc[i][2 + j] * inv);
+    } else {
+      const int64_t row = (int64_t(n) * a.hq + h) * a.nseg + seg;
+      float* op = a.o_part + row * D + g * (D / 8);
+#pragma unroll
+      for (int i = 0; i < D / 16; ++i)
+        *reinterpret_cast<float2*>(op + 2 * i) = make_float2(st.acc[i][j], st.acc[i][2 + j]);
+      if (g == 0) {
+        a.ml_part[2 * row] = M[j];
+        a.ml_part[2 * row + 1] = L[j];
+      }
+    }
+  }
+}
+
+// Combines the segments of one (sequence, head): w_s = 2^(m_s - m),
+// O = sum w_s O_s / sum w_s l_s; empty segments (m = -inf) weigh nothing.
+// Follows attn_decode_reduce_kernel (csrc/attn/attn_decode_bf16.hip:276-300).
+template <int D>
+__global__ void __launch_bounds__(D / 2) attn_decode_reduce_kernel(
+    __nv_bfloat16* __restrict__ out, const float* __restrict__ o_part,
+    const float* __restrict__ ml_part, int nseg, int hq, int64_t o_st, int64_t o_sh,
+    const float* __restrict__ sinks) {
+  const int64_t row = int64_t(blockIdx.y) * hq + blockIdx.x;
+  const float* ml = ml_part + row * nseg * 2;
+  float m = -INFINITY;
+  for (int s = 0; s < nseg; ++s) m = fmaxf(m, ml[2 * s]);
+  float l = 0.f;
+  float2 acc = make_float2(0.f, 0.f);
+  for (int s = 0; s < nseg; ++s) {
+    const float ms = ml[2 * s];
+    if (ms == -INFINITY) continue;
+    const float w = exp2f(ms - m);
+    l += w * ml[2 * s + 1];
+    const float2 o =
+        *reinterpret_cast<const float2*>(o_part + (row * nseg + s) * D + 2 * threadIdx.x);
+    acc.x += w * o.x;
+    acc.y += w * o.y;
+  }
+  if (sinks != nullptr) {
+    const float s2 = sinks[blockIdx.x] * kLog2e;
+    const float mf = fmaxf(m, s2);
+    const float al = m == -INFINITY ? 0.f : exp2f(m - mf);
+    acc.x *= al;
+    acc.y *= al;
+    l = l * al + exp2f(s2 - mf);
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  *reinterpret_cast<uint32_t*>(out + int64_t(blockIdx.y) * o_st + int64_t(blockIdx.x) * o_sh +
+                               2 * threadIdx.x) = pack_bf16x2(acc.x * inv, acc.y * inv);
+}
+
+}  // namespace
+}  // namespace strix
+
+using namespace strix;
+
+extern "C" int64_t strix_attn_decode_segments(int64_t num_splits, int64_t max_blocks,
+                                              int64_t block_size) {
+  if (num_splits < 0 || num_splits > 64) return -1;
+  if (num_splits > 0) return num_splits;
+  if (max_blocks < 0 || block_size <= 0) return -1;
+  const int64_t keys = max_blocks * block_size;
+  const int64_t n = (keys + STRIX_DECODE_AUTO_KEYS - 1) / STRIX_DECODE_AUTO_KEYS;
+  return n < 1 ? 1 : n;
+}
+
+extern "C" int64_t strix_attn_decode_workspace(int64_t nseq, int64_t hq, int64_t head_dim,
+                                               int64_t num_splits, int64_t max_blocks,
+                                               int64_t block_size) {
+  const int64_t nseg = strix_attn_decode_segments(num_splits, max_blocks, block_size);
+  if (nseg < 0) return -1;
+  if (nseg == 1) return 0;
+  return nseq * hq * nseg * (head_dim + 2) * int64_t(sizeof(float));
+}
+
+extern "C" int strix_attn_decode_bf16(
+    void* out, const void* q, const void* key_cache, const void* value_cache,
+    const float* k_scale, const float* v_scale, const int32_t* seq_lens,
+    const int32_t* block_table, const float* sinks, void* workspace, int64_t nseq,
+    int64_t hq, int64_t hkv, int64_t head_dim, int64_t block_size, int64_t max_blocks,
+    int64_t bt_stride, int64_t q_st, int64_t q_sh, int64_t o_st, int64_t o_sh, int64_t k_sb,
+    int64_t k_ss, int64_t k_sh, int64_t v_sb, int64_t v_ss, int64_t v_sh, int64_t ks_sb,
+    int64_t ks_ss, int64_t ks_sh, int64_t vs_sb, int64_t vs_ss, int64_t vs_sh, double scale,
+    int64_t num_splits, int64_t window_left, int kv_int8, strix_stream_t stream) {
+  STRIX_CHECK(nseq >= 0 && hq > 0 && hkv > 0, "q [N, H, D], caches [blocks, block_size, Hkv, D]");
+  STRIX_CHECK(hq % hkv == 0, "Hq %% Hkv");
+  const int64_t g = hq / hkv;
+  STRIX_CHECK(kv_int8 != 0, "attn_decode_bf16: bf16 KV cache not built (int8 only)");
+  STRIX_CHECK((head_dim == 128 || head_dim == 256) && g <= 8,
+              "attn_decode_bf16 int8: head_dim %lld GQA %lld not built (128, 256: GQA 1-8)",
+              (long long)head_dim, (long long)g);
+  STRIX_CHECK(k_scale != nullptr && v_scale != nullptr, "int8 KV needs k_scale and v_scale");
+  STRIX_CHECK(block_size > 0 && block_size % 16 == 0, "block_size must be a multiple of 16");
+  STRIX_CHECK(k_sb % 4 == 0 && k_ss % 4 == 0 && k_sh % 4 == 0 && v_sb % 4 == 0 &&
+                  v_ss % 4 == 0 && v_sh % 4 == 0,
+              "aligned cache rows");
+  STRIX_CHECK((reinterpret_cast<uintptr_t>(key_cache) | reinterpret_cast<uintptr_t>(value_cache)) % 4 == 0,
+              "aligned cache rows");
+  STRIX_CHECK(q_st % 4 == 0 && q_sh % 4 == 0 && reinterpret_cast<uintptr_t>(q) % 8 == 0,
+              "q must be bf16 with a contiguous head_dim");
+  STRIX_CHECK(o_st % 2 == 0 && o_sh % 2 == 0 && reinterpret_cast<uintptr_t>(out) % 4 == 0,
+              "out must match q");
+  STRIX_CHECK(num_splits >= 0 && num_splits <= 64, "num_splits in [1, 64]");
+  STRIX_CHECK(window_left >= -1, "window_left >= -1");
+  const int64_t nseg = strix_attn_decode_segments(num_splits, max_blocks, block_size);
+  STRIX_CHECK(nseg >= 1 && nseg <= 65535, "segment count out of range");
+  STRIX_CHECK(nseg == 1 || workspace != nullptr, "split-KV needs a workspace");
+  STRIX_CHECK(nseq <= 65535, "at most 65535 sequences per call");
+  if (nseq == 0) return STRIX_OK;
+
+  DecodeArgs a;
+  a.out = static_cast<__nv_bfloat16*>(out);
+  a.q = static_cast<const __nv_bfloat16*>(q);
+  a.kc = key_cache;
+  a.vc = value_cache;
+  a.ksc = k_scale;
+  a.vsc = v_scale;
+  a.seq_lens = seq_lens;
+  a.bt = block_table;
+  a.sinks = sinks;
+  a.o_part = static_cast<float*>(workspace);
+  a.ml_part = a.o_part ? a.o_part + nseq * hq * nseg * head_dim : nullptr;
+  a.bt_stride = bt_stride;
+  a.q_st = q_st, a.q_sh = q_sh, a.o_st = o_st, a.o_sh = o_sh;
+  a.k_sb = k_sb, a.k_ss = k_ss, a.k_sh = k_sh;
+  a.v_sb = v_sb, a.v_ss = v_ss, a.v_sh = v_sh;
+  a.ks_sb = ks_sb, a.ks_ss = ks_ss, a.ks_sh = ks_sh;
+  a.vs_sb = vs_sb, a.vs_ss = vs_ss, a.vs_sh = vs_sh;
+  a.block_size = int(block_size);
+  a.hq = int(hq), a.hkv = int(hkv), a.g = int(g);
+  a.hpc = hkv % 4 == 0 ? 4 : (hkv % 2 == 0 ? 2 : 1);
+  a.nseg = int(nseg);
+  a.seg_keys = num_splits == 0 ? STRIX_DECODE_AUTO_KEYS : 0;
+  a.win_left = int(window_left);
+  a.scale_log2 = float(scale) * kLog2e;
+
+  const bool aligned = (k_sb | k_ss | k_sh | v_sb | v_ss | v_sh) % 16 == 0 &&
+                       (reinterpret_cast<uintptr_t>(key_cache) |
+                        reinterpret_cast<uintptr_t>(value_cache)) % 16 == 0;
+  const dim3 grid{unsigned(nseg), unsigned(hkv / a.hpc), unsigned(nseq)};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // Warps per CTA: 8 (two per KV head at 4 heads per CTA, 128 registers) or 4
+  // (one per KV head, 168 registers, three CTAs per SM). STRIX_DECODE_WARPS
+  // overrides the default for tuning runs.
+  static const int warps_env = [] {
+    const char* e = getenv("STRIX_DECODE_WARPS");
+    return e ? atoi(e) : 0;
+  }();
+  const int warps = (warps_env == 4 || warps_env == 8) ? warps_env : (head_dim == 128 ? 8 : 4);
+#define STRIX_LAUNCH_DECODE(D, AL, W, MINB) \
+  attn_decode_q8_kernel<D, AL, W, MINB><<<grid, W * 32, 0, st>>>(a)
+  if (head_dim == 128) {
+    if (warps == 8) {
+      if (aligned) STRIX_LAUNCH_DECODE(128, true, 8, 2);
+      else STRIX_LAUNCH_DECODE(128, false, 8, 2);
+    } else {
+      if (aligned) STRIX_LAUNCH_DECODE(128, true, 4, 3);
+      else STRIX_LAUNCH_DECODE(128, false, 4, 3);
+    }
+  } else {
+    if (warps == 8) {
+      if (aligned) STRIX_LAUNCH_DECODE(256, true, 8, 1);
+      else STRIX_LAUNCH_DECODE(256, false, 8, 1);
+    } else {
+      if (aligned) STRIX_LAUNCH_DECODE(256, true, 4, 2);
+      else STRIX_LAUNCH_DECODE(256, false, 4, 2);
+    }
+  }
+#undef STRIX_LAUNCH_DECODE
+  int rc = launch_status("attn_decode");
+  if (rc != STRIX_OK) return rc;
+  if (nseg > 1) {
+    const dim3 rgrid{unsigned(hq), unsigned(nseq), 1u};
+    if (head_dim == 128)
+      attn_decode_reduce_kernel<128><<<rgrid, 64, 0, st>>>(a.out, a.o_part, a.ml_part, a.nseg,
+                                                           a.hq, o_st, o_sh, sinks);
+    else
+      attn_decode_reduce_kernel<256><<<rgrid, 128, 0, st>>>(a.out, a.o_part, a.ml_part, a.nseg,
+                                                            a.hq, o_st, o_sh, sinks);
+    rc = launch_status("attn_decode_reduce");
+  }
+  return rc;
+}

@@ -1,0 +1,208 @@
+"""Kernel table of libstrix_b200: which entry point serves which op at which geometry.
+
+Same contract as the reference's python/strix/registry.py (Kernel :87, select
+:930, explain :918, geometries :895, kernels, ops, selections, Range :65):
+
+  * `select(op, **geometry)` returns the NAME of the first row of `op` whose
+    every constraint key was passed and is satisfied, else `None` - the caller
+    then keeps its default path. Every query is recorded for `selections()`.
+  * a constraint is a single required value (also a *geometry point*), a tuple
+    of allowed values, or a `Range` bound;
+  * `geometries(op, *keys, **where)` collects the points of the rows that accept
+    `where`, so a plugin can derive its shape gate from the table.
+
+The rows below describe the sm_100a kernels actually built in csrc/; shapes the
+reference built for gfx1151 but that have no kernel here are absent, so
+`select` answers `None` for them.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+
+_SHORT = {
+    torch.bfloat16: "bf16",
+    torch.float16: "fp16",
+    torch.float32: "fp32",
+    torch.float8_e4m3fn: "fp8_e4m3",
+    torch.int8: "int8",
+}
+
+
+def _norm(value: Any) -> Any:
+    """torch dtypes (or their 'torch.xxx' spelling) become the table's short names."""
+    if isinstance(value, torch.dtype):
+        return _SHORT.get(value, str(value))
+    if isinstance(value, str) and value.startswith("torch."):
+        return _SHORT.get(getattr(torch, value[len("torch."):], None), value)
+    return value
+
+
+@dataclass(frozen=True)
+class Range:
+    """Inclusive integer bound; `Range(lo=6)` reads "6 or more"."""
+
+    lo: int | None = None
+    hi: int | None = None
+
+    def covers(self, got: Any) -> bool:
+        if isinstance(got, bool) or not isinstance(got, int):
+            return False
+        return (self.lo is None or got >= self.lo) and (self.hi is None or got <= self.hi)
+
+    def __str__(self) -> str:
+        if self.lo is not None and self.hi is not None:
+            return f"in {self.lo}..{self.hi}"
+        return f">= {self.lo}" if self.lo is not None else f"<= {self.hi}"
+
+
+def _satisfies(want: Any, got: Any) -> bool:
+    if isinstance(want, Range):
+        return want.covers(got)
+    if isinstance(want, tuple):
+        return got in want
+    return got == want
+
+
+def _describe(want: Any) -> str:
+    if isinstance(want, Range):
+        return str(want)
+    return f"in {want}" if isinstance(want, tuple) else f"== {want}"
+
+
+@dataclass(frozen=True)
+class Kernel:
+    name: str
+    op: str
+    doc: str
+    constraints: dict[str, Any] = field(default_factory=dict)
+    spec: dict[str, Any] = field(default_factory=dict)  # informational only
+
+    def check(self, geometry: dict[str, Any]) -> str | None:
+        """None when the row takes the geometry, else the first failed key."""
+        for key, want in self.constraints.items():
+            if key not in geometry:
+                return f"{key} not given"
+            got = _norm(geometry[key])
+            if not _satisfies(want, got):
+                return f"{key}={got}, needs {_describe(want)}"
+        return None
+
+    def accepts(self, partial: dict[str, Any]) -> bool:
+        """Whether a partial geometry lies inside this row."""
+        for key, value in partial.items():
+            if key not in self.constraints:
+                return False
+            if not _satisfies(self.constraints[key], _norm(value)):
+                return False
+        return True
+
+
+def _decode_row(head_dim: int, gqa: int, doc: str) -> Kernel:
+    return Kernel(
+        "attn_decode_bf16",
+        "attn_decode",
+        doc,
+        {
+            "head_dim": head_dim,
+            "gqa": gqa,
+            "queries": 1,
+            "dtype": "bf16",
+            "kv_dtype": ("int8",),
+            "window": (True, False),
+            "sinks": (True, False),
+        },
+        {"tile_keys": 16, "mma": "m16n8k16 f16, keys as M", "bound": "hbm"},
+    )
+
+
+KERNELS: list[Kernel] = [
+    # ------------------------------------------------------------ attention
+    _decode_row(
+        128, 8,
+        "one query per sequence over an int8_per_token_head paged cache: 16-key "
+        "tiles streamed global->registers, exact int8->fp16 widening by byte "
+        "permutes, K scale on the score, V scale on P, split-KV partials merged "
+        "by a reduce kernel, sinks after the merge",
+    ),
+    _decode_row(128, 4, "as (128, 8); the unused query-head columns of the MMA are zero"),
+    _decode_row(128, 2, "as (128, 8); the unused query-head columns of the MMA are zero"),
+    _decode_row(128, 1, "as (128, 8); the unused query-head columns of the MMA are zero"),
+    _decode_row(256, 8, "head 256 GQA 8, four warps per CTA (255 registers)"),
+    _decode_row(256, 6, "head 256 GQA 6 (two MMA columns idle)"),
+    _decode_row(256, 2, "head 256 GQA 2 (sliding layers)"),
+]
+
+_POINT_TYPES = (int, bool, str)
+_selections: dict[tuple, dict[str, Any]] = {}
+
+
+def ops() -> dict[str, list[str]]:
+    """op -> kernel names implementing it, in priority order, without repeats."""
+    table: dict[str, list[str]] = {}
+    for row in KERNELS:
+        names = table.setdefault(row.op, [])
+        if row.name not in names:
+            names.append(row.name)
+    return table
+
+
+def geometries(op: str, *keys: str, **where: Any) -> set[tuple]:
+    """Shape points `op` covers as tuples of `keys`; `where` narrows the rows first.
+
+    A row whose value for one of `keys` is a set or a Range is not a point and
+    contributes nothing.
+    """
+    points: set[tuple] = set()
+    for row in KERNELS:
+        if row.op != op or not row.accepts(where):
+            continue
+        values = [row.constraints.get(k) for k in keys]
+        if all(isinstance(v, _POINT_TYPES) for v in values):
+            points.add(tuple(_norm(v) for v in values))
+    return points
+
+
+def explain(op: str, **geometry: Any) -> list[dict[str, Any]]:
+    """One entry per row of `op`: its name, whether it matches, and why not."""
+    report = []
+    for row in KERNELS:
+        if row.op != op:
+            continue
+        reason = row.check(geometry)
+        report.append({"name": row.name, "ok": reason is None, "reason": reason})
+    return report
+
+
+def select(op: str, **geometry: Any) -> str | None:
+    report = explain(op, **geometry)
+    hit = next((r["name"] for r in report if r["ok"]), None)
+    query = tuple(sorted((k, _norm(v)) for k, v in geometry.items()))
+    record = _selections.get((op, query))
+    if record is None:
+        why = None if hit else ("; ".join(r["reason"] for r in report) or "no kernel")
+        record = {"op": op, "query": dict(query), "kernel": hit, "reason": why, "count": 0}
+        _selections[(op, query)] = record
+    record["count"] += 1
+    return hit
+
+
+def selections() -> list[dict[str, Any]]:
+    """Every distinct `select` query so far with its answer and hit count."""
+    return list(_selections.values())
+
+
+def kernels() -> list[dict[str, Any]]:
+    return [
+        {
+            "name": row.name,
+            "op": row.op,
+            "doc": row.doc,
+            "constraints": dict(row.constraints),
+            "spec": dict(row.spec),
+        }
+        for row in KERNELS
+    ]

@@ -1,0 +1,61 @@
+"""The C-ABI library loads without a GPU, exports every symbol the header
+declares, and rejects bad geometry before touching the device."""
+
+import ctypes
+
+import pytest
+
+from libstrix_b200 import _lib
+
+
+def test_library_exports_every_declared_symbol():
+    protos = _lib.parse_header()
+    assert "strix_attn_decode_bf16" in protos and len(protos) >= 5
+    lib = ctypes.CDLL(str(_lib.LIB_PATH))
+    for name in protos:
+        assert hasattr(lib, name), name
+
+
+def test_version_and_error_string():
+    lib = _lib.load()
+    assert lib.strix_version() >= 1000
+    assert isinstance(lib.strix_last_error(), bytes)
+
+
+def test_decode_segments_and_workspace():
+    lib = _lib.load()
+    assert lib.strix_attn_decode_segments(4, 10, 16) == 4
+    assert lib.strix_attn_decode_segments(0, 4096, 16) == 64
+    assert lib.strix_attn_decode_segments(0, 0, 16) == 1
+    assert lib.strix_attn_decode_segments(65, 1, 16) == -1
+    assert lib.strix_attn_decode_workspace(3, 32, 128, 1, 10, 16) == 0
+    assert lib.strix_attn_decode_workspace(3, 32, 128, 4, 10, 16) == 3 * 32 * 4 * 130 * 4
+
+
+def _decode_args(**over):
+    a = dict(out=8, q=8, kc=16, vc=16, ks=4, vs=4, sl=4, bt=4, sinks=None, ws=None,
+             nseq=1, hq=32, hkv=4, d=128, bs=16, max_blocks=4, bt_stride=4,
+             q_st=4096, q_sh=128, o_st=4096, o_sh=128,
+             k_sb=8192, k_ss=512, k_sh=128, v_sb=8192, v_ss=512, v_sh=128,
+             ks_sb=64, ks_ss=4, ks_sh=1, vs_sb=64, vs_ss=4, vs_sh=1,
+             scale=0.1, splits=1, win=-1, q8=1, stream=None)
+    a.update(over)
+    return list(a.values())
+
+
+@pytest.mark.parametrize(
+    "over,fragment",
+    [
+        (dict(d=64), "not built"),
+        (dict(hq=30), "Hq % Hkv"),
+        (dict(bs=24), "multiple of 16"),
+        (dict(splits=65), "num_splits in [1, 64]"),
+        (dict(q8=0), "bf16 KV cache not built"),
+        (dict(ks=None), "int8 KV needs k_scale and v_scale"),
+        (dict(splits=4), "workspace"),
+        (dict(k_ss=510), "aligned cache rows"),
+    ],
+)
+def test_decode_rejects_bad_arguments_without_a_gpu(over, fragment):
+    with pytest.raises(_lib.StrixError, match=fragment.replace("[", r"\[").replace("]", r"\]")):
+        _lib.call("strix_attn_decode_bf16", *_decode_args(**over))
