@@ -32,6 +32,11 @@ namespace {
 
 constexpr uint32_t kMagic = 0x64646464u;   // high byte of fp16 1024 + x
 constexpr uint32_t kBias = 0x64806480u;    // f16x2 (1152, 1152)
+constexpr float kPScale = 32768.f;         // fp16 headroom for the V-scaled weights
+constexpr float kPScaleInv = 1.f / 32768.f;
+
+// Bytes of one ring stage: 16 K rows, 16 V rows, 16 + 16 fp32 scales.
+constexpr int stage_bytes(int d) { return 2 * 16 * d + 128; }
 
 struct DecodeArgs {
   __nv_bfloat16* out;
@@ -114,29 +119,50 @@ struct WarpState {
   float acc[D / 16][4];
 };
 
+// Query fragments for the score MMAs. The bf16 query of a head is turned into
+// 16-bit fixed point against the head's absmax, q = s * (256 * hi + lo) with
+// hi a signed and lo an unsigned byte (error <= absmax * 2^-16, far below
+// bf16's own resolution), so that S^T = K Q^T runs as two exact int8 MMAs on
+// the raw cache bytes with no widening of K at all.
+template <int D>
+struct QFrag {
+  uint32_t hi[D / 16], lo[D / 16];
+  float qs[2];  // s * softmax_scale * log2(e) for heads 2c and 2c + 1
+};
+
 template <int D>
 __device__ __forceinline__ void compute_tile(const TileQ8<D>& t, WarpState<D>& st,
-                                             const uint32_t (&qf)[D / 8], int key0,
-                                             int k_begin, int k_end, float scale_log2,
-                                             int g) {
-  // S^T[16 keys, 8 heads] = K Q^T
-  float s[4] = {0.f, 0.f, 0.f, 0.f};
+                                             const QFrag<D>& qf, int key0, int k_begin,
+                                             int k_end, int g) {
+  // S^T[16 keys, 8 heads] = K Q^T, int32-exact
+  int sh[4] = {0, 0, 0, 0}, sl[4] = {0, 0, 0, 0};
 #pragma unroll
-  for (int i = 0; i < D / 16; ++i) {
-    const uint32_t w0 = t.k[0][i] ^ 0x80808080u, w1 = t.k[1][i] ^ 0x80808080u;
-    uint32_t a[4];
-    a[0] = sub_f16x2(prmt(w0, kMagic, 0x4140), kBias);
-    a[1] = sub_f16x2(prmt(w1, kMagic, 0x4140), kBias);
-    a[2] = sub_f16x2(prmt(w0, kMagic, 0x4342), kBias);
-    a[3] = sub_f16x2(prmt(w1, kMagic, 0x4342), kBias);
-    mma_f16_16816(s, a, qf[2 * i], qf[2 * i + 1]);
+  for (int i = 0; i < D / 32; ++i) {
+    const uint32_t a[4] = {t.k[0][2 * i], t.k[1][2 * i], t.k[0][2 * i + 1], t.k[1][2 * i + 1]};
+    mma_s8s8_16832(sh, a, qf.hi[2 * i], qf.hi[2 * i + 1]);
+    mma_s8u8_16832(sl, a, qf.lo[2 * i], qf.lo[2 * i + 1]);
   }
+  float s[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) s[i] = float(sh[i] * 256 + sl[i]);
+  s[0] *= qf.qs[0];
+  s[1] *= qf.qs[1];
+  s[2] *= qf.qs[0];
+  s[3] *= qf.qs[1];
   const int ka = key0 + g, kb = ka + 8;
   const bool va = ka >= k_begin && ka < k_end, vb = kb >= k_begin && kb < k_end;
-  const float ksa = t.ks[0] * scale_log2, ksb = t.ks[1] * scale_log2;
+  const float ksa = t.ks[0], ksb = t.ks[1];
   const float x0 = va ? s[0] * ksa : -INFINITY, x1 = va ? s[1] * ksa : -INFINITY;
   const float x2 = vb ? s[2] * ksb : -INFINITY, x3 = vb ? s[3] * ksb : -INFINITY;
-  float mx0 = fmaxf(x0, x2), mx1 = fmaxf(x1, x3);
+  // The running reference is max(x + log2|v_scale|), not max(x): then the
+  // V-scaled weights p * |v_scale| are <= 1 whatever the scale's magnitude, and
+  // kPScale lifts them into fp16's normal range (tiny weights of a 65k-key
+  // softmax would otherwise land in fp16 subnormals). m, l and O all use the
+  // same reference, so the split-KV merge formulas are unchanged. A stale scale
+  // of a masked key may be anything (NaN included): it is replaced.
+  const float lva = va ? fmaxf(fast_log2(fabsf(t.vs[0])), -100.f) : 0.f;
+  const float lvb = vb ? fmaxf(fast_log2(fabsf(t.vs[1])), -100.f) : 0.f;
+  float mx0 = fmaxf(x0 + lva, x2 + lvb), mx1 = fmaxf(x1 + lva, x3 + lvb);
 #pragma unroll
   for (int o = 4; o < 32; o <<= 1) {
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
@@ -151,18 +177,22 @@ __device__ __forceinline__ void compute_tile(const TileQ8<D>& t, WarpState<D>& s
   const float p2 = fast_exp2(x2 - r0), p3 = fast_exp2(x3 - r1);
   st.l[0] = st.l[0] * al0 + (p0 + p2);
   st.l[1] = st.l[1] * al1 + (p1 + p3);
-  // A stale scale of a masked key may be anything (NaN included): p is 0 there,
-  // so force the product to 0 as well.
-  const float vsa = va ? t.vs[0] : 0.f, vsb = vb ? t.vs[1] : 0.f;
+  const float vsa = va ? t.vs[0] * kPScale : 0.f, vsb = vb ? t.vs[1] * kPScale : 0.f;
   const uint32_t b0 = movmatrix_trans(pack_f16x2(p0 * vsa, p1 * vsa));
   const uint32_t b1 = movmatrix_trans(pack_f16x2(p2 * vsb, p3 * vsb));
-  // O^T[D, 8 heads] = alpha O^T + V^T P^T
+  // O^T[D, 8 heads] = alpha O^T + V^T P^T; the rescale is skipped while no lane's
+  // running reference moved (the common case after the first tiles).
+  if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {
+#pragma unroll
+    for (int i = 0; i < D / 16; ++i) {
+      st.acc[i][0] *= al0;
+      st.acc[i][1] *= al1;
+      st.acc[i][2] *= al0;
+      st.acc[i][3] *= al1;
+    }
+  }
 #pragma unroll
   for (int i = 0; i < D / 16; ++i) {
-    st.acc[i][0] *= al0;
-    st.acc[i][1] *= al1;
-    st.acc[i][2] *= al0;
-    st.acc[i][3] *= al1;
     const int w = i / 2;
     const uint32_t sel = (i & 1) ? 0x7362u : 0x5140u;
     const uint32_t x01 = prmt(t.v[0][w] ^ 0x80808080u, t.v[1][w] ^ 0x80808080u, sel);
@@ -176,10 +206,17 @@ __device__ __forceinline__ void compute_tile(const TileQ8<D>& t, WarpState<D>& s
   }
 }
 
-template <int D, bool ALIGNED, int kWarps, int kMinCtas>
+// STAGES == 0: tiles go global -> registers, double-buffered (any 4-byte-aligned
+// layout). STAGES >= 2: each warp owns a ring of STAGES tiles in shared memory
+// filled with 16-byte cp.async copies STAGES - 1 tiles ahead (rows 16-byte
+// aligned); 16-byte chunks are XOR-swizzled by row so that both the K and the V
+// fragment reads are bank-conflict free. No barrier or flag is shared between
+// warps in the main loop.
+template <int D, bool ALIGNED, int kWarps, int kMinCtas, int STAGES>
 __global__ void __launch_bounds__(kWarps * 32, kMinCtas)
 attn_decode_q8_kernel(const DecodeArgs a) {
   constexpr int kThreads = kWarps * 32;
+  extern __shared__ __align__(16) uint8_t dyn_smem[];
   const int seg = blockIdx.x, hgrp = blockIdx.y, n = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
@@ -201,7 +238,7 @@ attn_decode_q8_kernel(const DecodeArgs a) {
   const bool single = a.nseg == 1;
 
   __shared__ float s_m[kWarps][8], s_l[kWarps][8];
-  __shared__ __align__(16) float s_o[4][8][D];   // hpc <= 4 slots
+  float* const s_o = reinterpret_cast<float*>(dyn_smem);  // [hpc][8][D], after the main loop
 
   if (k_begin >= k_end) {  // empty segment (block-uniform)
     const int heads = a.hpc * G;
@@ -219,20 +256,48 @@ attn_decode_q8_kernel(const DecodeArgs a) {
     return;
   }
 
-  // Q^T fragments: head g of this KV head, dims c * D/4 + 4i .. + 3 for k-step i.
-  uint32_t qf[D / 8];
-  if (g < G) {
-    const __nv_bfloat16* qp =
-        a.q + int64_t(n) * a.q_st + int64_t(h0 + g) * a.q_sh + c * (D / 4);
+  // Q^T fragments: head g of this KV head, dims c * D/4 + 8i .. + 7 for k-step i
+  // (the same permutation of head dims that the K loads use).
+  QFrag<D> qf;
+  {
+    float qv[D / 4];
+    float amax = 0.f;
+    if (g < G) {
+      const __nv_bfloat16* qp =
+          a.q + int64_t(n) * a.q_st + int64_t(h0 + g) * a.q_sh + c * (D / 4);
+#pragma unroll
+      for (int i = 0; i < D / 16; ++i) {
+        const uint2 w = *reinterpret_cast<const uint2*>(qp + 4 * i);
+        qv[4 * i] = bf16_lo(w.x);
+        qv[4 * i + 1] = bf16_hi(w.x);
+        qv[4 * i + 2] = bf16_lo(w.y);
+        qv[4 * i + 3] = bf16_hi(w.y);
+      }
+#pragma unroll
+      for (int i = 0; i < D / 4; ++i) amax = fmaxf(amax, fabsf(qv[i]));
+    } else {
+#pragma unroll
+      for (int i = 0; i < D / 4; ++i) qv[i] = 0.f;
+    }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const float step = amax > 0.f ? amax * (1.f / 32767.f) : 1.f;
+    const float inv = 1.f / step;
 #pragma unroll
     for (int i = 0; i < D / 16; ++i) {
-      const uint2 w = *reinterpret_cast<const uint2*>(qp + 4 * i);
-      qf[2 * i] = pack_f16x2(bf16_lo(w.x), bf16_hi(w.x));
-      qf[2 * i + 1] = pack_f16x2(bf16_lo(w.y), bf16_hi(w.y));
-    }
-  } else {
+      uint32_t hi = 0, lo = 0;
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i) qf[i] = 0u;
+      for (int j = 0; j < 4; ++j) {
+        const int f = __float2int_rn(qv[4 * i + j] * inv);
+        hi |= (uint32_t(f >> 8) & 0xffu) << (8 * j);
+        lo |= (uint32_t(f) & 0xffu) << (8 * j);
+      }
+      qf.hi[i] = hi;
+      qf.lo[i] = lo;
+    }
+    const float qs = step * a.scale_log2;
+    qf.qs[0] = __shfl_sync(0xffffffffu, qs, 8 * c);
+    qf.qs[1] = __shfl_sync(0xffffffffu, qs, 8 * c + 4);
   }
 
   WarpState<D> st;
@@ -261,26 +326,104 @@ attn_decode_q8_kernel(const DecodeArgs a) {
     return blk;
   };
 
-  TileQ8<D> ta, tb;
-  int t = t_begin + sub;
-  if (t < t_end) {
-    const int blk = next_block(t);
-    load_tile<D, ALIGNED>(ta, a, blk, (t * 16) % bs, kvh, g, c);
-  }
-  while (t < t_end) {
-    if (t + wph < t_end) {
-      const int blk = next_block(t + wph);
-      load_tile<D, ALIGNED>(tb, a, blk, ((t + wph) * 16) % bs, kvh, g, c);
+  if constexpr (STAGES == 0) {
+    TileQ8<D> ta, tb;
+    int t = t_begin + sub;
+    if (t < t_end) {
+      const int blk = next_block(t);
+      load_tile<D, ALIGNED>(ta, a, blk, (t * 16) % bs, kvh, g, c);
     }
-    compute_tile<D>(ta, st, qf, t * 16, k_begin, k_end, a.scale_log2, g);
-    t += wph;
-    if (t >= t_end) break;
-    if (t + wph < t_end) {
-      const int blk = next_block(t + wph);
-      load_tile<D, ALIGNED>(ta, a, blk, ((t + wph) * 16) % bs, kvh, g, c);
+    while (t < t_end) {
+      if (t + wph < t_end) {
+        const int blk = next_block(t + wph);
+        load_tile<D, ALIGNED>(tb, a, blk, ((t + wph) * 16) % bs, kvh, g, c);
+      }
+      compute_tile<D>(ta, st, qf, t * 16, k_begin, k_end, g);
+      t += wph;
+      if (t >= t_end) break;
+      if (t + wph < t_end) {
+        const int blk = next_block(t + wph);
+        load_tile<D, ALIGNED>(ta, a, blk, ((t + wph) * 16) % bs, kvh, g, c);
+      }
+      compute_tile<D>(tb, st, qf, t * 16, k_begin, k_end, g);
+      t += wph;
     }
-    compute_tile<D>(tb, st, qf, t * 16, k_begin, k_end, a.scale_log2, g);
-    t += wph;
+  } else {
+    constexpr int kStage = stage_bytes(D);
+    constexpr int CPR = D / 16;       // 16-byte chunks per row
+    constexpr int RPI = 32 / CPR;     // rows one warp-wide copy instruction covers
+    uint8_t* const ring = dyn_smem + warp * (STAGES * kStage);
+    const uint32_t ring_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring));
+    const int crow = lane / CPR, cch = lane % CPR;
+    const int64_t k_lane = int64_t(crow) * a.k_ss + cch * 16 + int64_t(kvh) * a.k_sh;
+    const int64_t v_lane = int64_t(crow) * a.v_ss + cch * 16 + int64_t(kvh) * a.v_sh;
+    const bool is_k = lane < 16;
+    const float* sc_base = is_k ? a.ksc + int64_t(kvh) * a.ks_sh + int64_t(lane) * a.ks_ss
+                                : a.vsc + int64_t(kvh) * a.vs_sh + int64_t(lane - 16) * a.vs_ss;
+    const int64_t sc_sb = is_k ? a.ks_sb : a.vs_sb, sc_ss = is_k ? a.ks_ss : a.vs_ss;
+
+    int t_issue = t_begin + sub, stage_issue = 0;
+    auto issue_next = [&]() {
+      if (t_issue < t_end) {
+        const int blk = next_block(t_issue);
+        const int off = (t_issue * 16) % bs;
+        const uint8_t* kp = static_cast<const uint8_t*>(a.kc) + int64_t(blk) * a.k_sb +
+                            int64_t(off) * a.k_ss + k_lane;
+        const uint8_t* vp = static_cast<const uint8_t*>(a.vc) + int64_t(blk) * a.v_sb +
+                            int64_t(off) * a.v_ss + v_lane;
+        const uint32_t dst = ring_s + stage_issue * kStage;
+#pragma unroll
+        for (int j = 0; j < 16 / RPI; ++j) {
+          const int row = j * RPI + crow;
+          const uint32_t d = dst + row * D + ((cch ^ (row & 7)) << 4);
+          cp_async_16(d, kp + int64_t(j * RPI) * a.k_ss);
+          cp_async_16(d + 16 * D, vp + int64_t(j * RPI) * a.v_ss);
+        }
+        cp_async_4(dst + 32 * D + lane * 4, sc_base + int64_t(blk) * sc_sb + int64_t(off) * sc_ss);
+      }
+      cp_async_commit();
+      t_issue += wph;
+      stage_issue = stage_issue + 1 == STAGES ? 0 : stage_issue + 1;
+    };
+#pragma unroll
+    for (int i = 0; i < STAGES - 1; ++i) issue_next();
+    int stage = 0;
+    for (int t = t_begin + sub; t < t_end; t += wph) {
+      issue_next();
+      cp_async_wait<STAGES - 1>();
+      __syncwarp();
+      TileQ8<D> tile;
+      const uint8_t* sp = ring + stage * kStage;
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const uint8_t* rowp = sp + (g + 8 * r) * D;
+#pragma unroll
+        for (int i = 0; i < D / 64; ++i) {
+          const uint4 x = *reinterpret_cast<const uint4*>(rowp + (((c * (D / 64) + i) ^ g) << 4));
+          tile.k[r][4 * i] = x.x, tile.k[r][4 * i + 1] = x.y;
+          tile.k[r][4 * i + 2] = x.z, tile.k[r][4 * i + 3] = x.w;
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int row = 2 * c + (r & 1) + 8 * (r >> 1);
+        const uint8_t* rowp = sp + 16 * D + row * D;
+#pragma unroll
+        for (int i = 0; i < D / 128; ++i) {
+          const uint4 x =
+              *reinterpret_cast<const uint4*>(rowp + (((g * (D / 128) + i) ^ (row & 7)) << 4));
+          tile.v[r][4 * i] = x.x, tile.v[r][4 * i + 1] = x.y;
+          tile.v[r][4 * i + 2] = x.z, tile.v[r][4 * i + 3] = x.w;
+        }
+      }
+      const float* scp = reinterpret_cast<const float*>(sp + 32 * D);
+      tile.ks[0] = scp[g], tile.ks[1] = scp[g + 8];
+      tile.vs[0] = scp[16 + g], tile.vs[1] = scp[24 + g];
+      compute_tile<D>(tile, st, qf, t * 16, k_begin, k_end, g);
+      __syncwarp();
+      stage = stage + 1 == STAGES ? 0 : stage + 1;
+    }
+    cp_async_wait<0>();
   }
 
   // ---- merge the warps of each KV head ------------------------------------
@@ -307,8 +450,8 @@ attn_decode_q8_kernel(const DecodeArgs a) {
     L[1] += m1 == -INFINITY ? 0.f : s_l[w][2 * c + 1] * fast_exp2(m1 - M[1]);
   }
   {
-    const float f0 = st.m[0] == -INFINITY ? 0.f : fast_exp2(st.m[0] - M[0]);
-    const float f1 = st.m[1] == -INFINITY ? 0.f : fast_exp2(st.m[1] - M[1]);
+    const float f0 = st.m[0] == -INFINITY ? 0.f : fast_exp2(st.m[0] - M[0]) * kPScaleInv;
+    const float f1 = st.m[1] == -INFINITY ? 0.f : fast_exp2(st.m[1] - M[1]) * kPScaleInv;
 #pragma unroll
     for (int i = 0; i < D / 16; ++i) {
       st.acc[i][0] *= f0;
@@ -318,8 +461,8 @@ attn_decode_q8_kernel(const DecodeArgs a) {
     }
   }
   // s_o[slot][head][d]: lane owns dims g * D/8 + 2i, + 2i + 1 of heads 2c, 2c + 1.
-  float* so0 = &s_o[hslot][2 * c][g * (D / 8)];
-  float* so1 = &s_o[hslot][2 * c + 1][g * (D / 8)];
+  float* so0 = s_o + (hslot * 8 + 2 * c) * D + g * (D / 8);
+  float* so1 = so0 + D;
   for (int r = wph - 1; r >= 1; --r) {
     if (sub == r) {
 #pragma unroll
@@ -414,10 +557,39 @@ __global__ void __launch_bounds__(D / 2) attn_decode_reduce_kernel(
                                2 * threadIdx.x) = pack_bf16x2(acc.x * inv, acc.y * inv);
 }
 
+template <int D, bool AL, int W, int MINB, int S>
+int launch_decode(dim3 grid, cudaStream_t st, const DecodeArgs& a, size_t smem) {
+  auto kernel = attn_decode_q8_kernel<D, AL, W, MINB, S>;
+  if (smem > 48 * 1024) {
+    // per device, once: opt in to more than 48 KB of dynamic shared memory
+    static bool done[64] = {};
+    int dev = 0;
+    STRIX_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !done[dev]) {
+      STRIX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      int(smem)));
+      if (dev >= 0 && dev < 64) done[dev] = true;
+    }
+  }
+  kernel<<<grid, W * 32, smem, st>>>(a);
+  return launch_status("attn_decode");
+}
+
 }  // namespace
 }  // namespace strix
 
 using namespace strix;
+
+// Keys per segment in automatic mode; STRIX_DECODE_SEG_KEYS (a multiple of 16)
+// overrides the default for tuning runs.
+static int auto_seg_keys() {
+  static const int keys = [] {
+    const char* e = getenv("STRIX_DECODE_SEG_KEYS");
+    const int v = e ? atoi(e) : 0;
+    return (v >= 64 && v % 16 == 0) ? v : STRIX_DECODE_AUTO_KEYS;
+  }();
+  return keys;
+}
 
 extern "C" int64_t strix_attn_decode_segments(int64_t num_splits, int64_t max_blocks,
                                               int64_t block_size) {
@@ -425,7 +597,7 @@ extern "C" int64_t strix_attn_decode_segments(int64_t num_splits, int64_t max_bl
   if (num_splits > 0) return num_splits;
   if (max_blocks < 0 || block_size <= 0) return -1;
   const int64_t keys = max_blocks * block_size;
-  const int64_t n = (keys + STRIX_DECODE_AUTO_KEYS - 1) / STRIX_DECODE_AUTO_KEYS;
+  const int64_t n = (keys + auto_seg_keys() - 1) / auto_seg_keys();
   return n < 1 ? 1 : n;
 }
 
@@ -469,7 +641,7 @@ extern "C" int strix_attn_decode_bf16(
   STRIX_CHECK(window_left >= -1, "window_left >= -1");
   const int64_t nseg = strix_attn_decode_segments(num_splits, max_blocks, block_size);
   STRIX_CHECK(nseg >= 1 && nseg <= 65535, "segment count out of range");
-  STRIX_CHECK(nseg == 1 || workspace != nullptr, "split-KV needs a workspace");
+  STRIX_CHECK(nseg == 1 || nseq == 0 || workspace != nullptr, "split-KV needs a workspace");
   STRIX_CHECK(nseq <= 65535, "at most 65535 sequences per call");
   if (nseq == 0) return STRIX_OK;
 
@@ -495,7 +667,7 @@ extern "C" int strix_attn_decode_bf16(
   a.hq = int(hq), a.hkv = int(hkv), a.g = int(g);
   a.hpc = hkv % 4 == 0 ? 4 : (hkv % 2 == 0 ? 2 : 1);
   a.nseg = int(nseg);
-  a.seg_keys = num_splits == 0 ? STRIX_DECODE_AUTO_KEYS : 0;
+  a.seg_keys = num_splits == 0 ? auto_seg_keys() : 0;
   a.win_left = int(window_left);
   a.scale_log2 = float(scale) * kLog2e;
 
@@ -504,35 +676,43 @@ extern "C" int strix_attn_decode_bf16(
                         reinterpret_cast<uintptr_t>(value_cache)) % 16 == 0;
   const dim3 grid{unsigned(nseg), unsigned(hkv / a.hpc), unsigned(nseq)};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // Warps per CTA: 8 (two per KV head at 4 heads per CTA, 128 registers) or 4
-  // (one per KV head, 168 registers, three CTAs per SM). STRIX_DECODE_WARPS
-  // overrides the default for tuning runs.
+  // Path and shape of the main kernel. Rows that are 16-byte aligned take the
+  // shared-memory ring (4 warps, 3 stages, 4 CTAs per SM at head_dim 128);
+  // anything else takes the register-buffered loop. STRIX_DECODE_STAGES
+  // (0, 3, 4) and STRIX_DECODE_WARPS (4, 8) override the choice for tuning runs.
+  static const int stages_env = [] {
+    const char* e = getenv("STRIX_DECODE_STAGES");
+    return e ? atoi(e) : -1;
+  }();
   static const int warps_env = [] {
     const char* e = getenv("STRIX_DECODE_WARPS");
     return e ? atoi(e) : 0;
   }();
-  const int warps = (warps_env == 4 || warps_env == 8) ? warps_env : (head_dim == 128 ? 8 : 4);
-#define STRIX_LAUNCH_DECODE(D, AL, W, MINB) \
-  attn_decode_q8_kernel<D, AL, W, MINB><<<grid, W * 32, 0, st>>>(a)
+  int stages = aligned ? 3 : 0;
+  if (aligned && (stages_env == 0 || stages_env == 3 || stages_env == 4)) stages = stages_env;
+  const int warps = (warps_env == 4 || warps_env == 8) ? warps_env : 4;
+  const size_t merge_bytes = size_t(a.hpc) * 8 * head_dim * sizeof(float);
+  int rc = STRIX_OK;
+#define STRIX_DECODE_CASE(D, AL, W, MINB, S)                                              \
+  rc = launch_decode<D, AL, W, MINB, S>(                                                  \
+      grid, st, a, S == 0 ? merge_bytes : size_t(W) * S * stage_bytes(D))
   if (head_dim == 128) {
-    if (warps == 8) {
-      if (aligned) STRIX_LAUNCH_DECODE(128, true, 8, 2);
-      else STRIX_LAUNCH_DECODE(128, false, 8, 2);
+    if (stages == 0) {
+      if (warps == 8) { if (aligned) STRIX_DECODE_CASE(128, true, 8, 2, 0); else STRIX_DECODE_CASE(128, false, 8, 2, 0); }
+      else { if (aligned) STRIX_DECODE_CASE(128, true, 4, 3, 0); else STRIX_DECODE_CASE(128, false, 4, 3, 0); }
+    } else if (stages == 4) {
+      if (warps == 8) STRIX_DECODE_CASE(128, true, 8, 1, 4); else STRIX_DECODE_CASE(128, true, 4, 3, 4);
     } else {
-      if (aligned) STRIX_LAUNCH_DECODE(128, true, 4, 3);
-      else STRIX_LAUNCH_DECODE(128, false, 4, 3);
+      if (warps == 8) STRIX_DECODE_CASE(128, true, 8, 2, 3); else STRIX_DECODE_CASE(128, true, 4, 4, 3);
     }
   } else {
-    if (warps == 8) {
-      if (aligned) STRIX_LAUNCH_DECODE(256, true, 8, 1);
-      else STRIX_LAUNCH_DECODE(256, false, 8, 1);
+    if (stages == 0) {
+      if (aligned) STRIX_DECODE_CASE(256, true, 4, 2, 0); else STRIX_DECODE_CASE(256, false, 4, 2, 0);
     } else {
-      if (aligned) STRIX_LAUNCH_DECODE(256, true, 4, 2);
-      else STRIX_LAUNCH_DECODE(256, false, 4, 2);
+      STRIX_DECODE_CASE(256, true, 4, 2, 3);
     }
   }
-#undef STRIX_LAUNCH_DECODE
-  int rc = launch_status("attn_decode");
+#undef STRIX_DECODE_CASE
   if (rc != STRIX_OK) return rc;
   if (nseg > 1) {
     const dim3 rgrid{unsigned(hq), unsigned(nseq), 1u};
