@@ -75,7 +75,7 @@ def load() -> ctypes.CDLL:
         return _lib
     if not LIB_PATH.exists():
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m libstrix_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python libstrix_b200/build.py` "
             "(needs nvcc; there is no CPU or PyTorch fallback)"
         )
     lib = ctypes.CDLL(str(LIB_PATH))
@@ -84,7 +84,9 @@ def load() -> ctypes.CDLL:
         try:
             fn = getattr(lib, name)
         except AttributeError as e:
-            raise ImportError(f"{LIB_PATH} does not export {name}; rebuild it") from e
+            raise ImportError(
+                f"{LIB_PATH} does not export {name}; rebuild it with "
+                "`python libstrix_b200/build.py`") from e
         fn.restype = ret
         fn.argtypes = argtypes
     _lib = lib

@@ -1,6 +1,8 @@
 """Builds libstrix_b200.so from csrc/*.cu with nvcc for sm_100a, in-tree.
 
-    python -m libstrix_b200.build [--force] [--verbose]
+    python libstrix_b200/build.py [--force] [--verbose]
+
+(run as a script: importing the package needs the library to exist already)
 
 One object per .cu (compiled in parallel, rebuilt only when the source or a
 header is newer), linked into libstrix_b200/libstrix_b200.so. The library has
