@@ -89,6 +89,35 @@ int strix_attn_decode_bf16(
     double scale, int64_t num_splits, int64_t window_left, int kv_int8,
     strix_stream_t stream);
 
+/* strix_attn_decode_bf16 without a workspace argument, for callers that cannot
+ * allocate device memory: a host loop that owns nothing but the input and
+ * output buffers it was given, or a process whose device memory was budgeted
+ * at start-up so that a late cudaMalloc may fail or stall the GPU. It has no
+ * counterpart in the reference (whose launcher allocates with torch). The
+ * split-KV partials go to an array of STRIX_DECODE_STATIC_SCRATCH_BYTES built
+ * into the library (held on every GPU that loads it, until exit); a launch that
+ * needs more (see strix_attn_decode_workspace) is rejected with
+ * STRIX_ERR_INVALID and a message that states both sizes. The call allocates and
+ * frees nothing. The first call on each device looks the array's address up
+ * (cudaGetSymbolAddress) - make it before any stream capture. All calls share
+ * the array: calls that overlap on the GPU race on it. Arguments otherwise as
+ * strix_attn_decode_bf16. */
+#define STRIX_DECODE_STATIC_SCRATCH_BYTES (16 * 1024 * 1024)
+
+int strix_attn_decode_bf16_static(
+    void* out, const void* q, const void* key_cache, const void* value_cache,
+    const float* k_scale, const float* v_scale, const int32_t* seq_lens,
+    const int32_t* block_table, const float* sinks,
+    int64_t nseq, int64_t hq, int64_t hkv, int64_t head_dim, int64_t block_size,
+    int64_t max_blocks, int64_t bt_stride,
+    int64_t q_st, int64_t q_sh, int64_t o_st, int64_t o_sh,
+    int64_t k_sb, int64_t k_ss, int64_t k_sh,
+    int64_t v_sb, int64_t v_ss, int64_t v_sh,
+    int64_t ks_sb, int64_t ks_ss, int64_t ks_sh,
+    int64_t vs_sb, int64_t vs_ss, int64_t vs_sh,
+    double scale, int64_t num_splits, int64_t window_left, int kv_int8,
+    strix_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -726,3 +726,65 @@ extern "C" int strix_attn_decode_bf16(
   }
   return rc;
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant of strix_attn_decode_bf16.
+//
+// Some hosts of this library cannot hand it scratch memory: a C or C++ serving
+// loop that only owns the input and output buffers its framework gave it, or a
+// process whose device memory was budgeted at start-up, where a late cudaMalloc
+// may fail or stall the device. For them the split-KV partials live in the
+// fixed array below instead of a caller-provided workspace. Every GPU that
+// loads the library holds these STRIX_DECODE_STATIC_SCRATCH_BYTES until exit.
+//
+// g_decode_scratch is a device symbol: in host code its name is only a
+// stand-in, never a device address, so the address handed to the kernels is
+// obtained with cudaGetSymbolAddress - once per device, with that device
+// current, on the first call made on it (make that first call before any
+// stream capture begins). No call here allocates or frees memory.
+//
+// All calls share the array and it keeps the previous call's contents. Nothing
+// in it has to start at zero: every (sequence, head, segment) slot's (m, l)
+// pair is rewritten by each call, and a partial O row is read only when its m
+// is finite, i.e. when this call wrote it. Two calls that overlap on the GPU
+// (different streams, or one device used from several threads) race on it.
+static __device__ __align__(256) float
+    g_decode_scratch[STRIX_DECODE_STATIC_SCRATCH_BYTES / sizeof(float)];
+
+extern "C" int strix_attn_decode_bf16_static(
+    void* out, const void* q, const void* key_cache, const void* value_cache,
+    const float* k_scale, const float* v_scale, const int32_t* seq_lens,
+    const int32_t* block_table, const float* sinks, int64_t nseq, int64_t hq, int64_t hkv,
+    int64_t head_dim, int64_t block_size, int64_t max_blocks, int64_t bt_stride, int64_t q_st,
+    int64_t q_sh, int64_t o_st, int64_t o_sh, int64_t k_sb, int64_t k_ss, int64_t k_sh,
+    int64_t v_sb, int64_t v_ss, int64_t v_sh, int64_t ks_sb, int64_t ks_ss, int64_t ks_sh,
+    int64_t vs_sb, int64_t vs_ss, int64_t vs_sh, double scale, int64_t num_splits,
+    int64_t window_left, int kv_int8, strix_stream_t stream) {
+  STRIX_CHECK(nseq >= 0 && hq > 0 && head_dim > 0, "q [N, H, D], caches [blocks, block_size, Hkv, D]");
+  const int64_t bytes =
+      strix_attn_decode_workspace(nseq, hq, head_dim, num_splits, max_blocks, block_size);
+  STRIX_CHECK(bytes >= 0, "num_splits in [1, 64]");
+  STRIX_CHECK(bytes <= int64_t(STRIX_DECODE_STATIC_SCRATCH_BYTES),
+              "attn_decode_bf16_static: this launch needs %lld bytes of split-KV scratch but the "
+              "built-in array holds %lld; lower num_splits or the batch, or use "
+              "strix_attn_decode_bf16 with a caller workspace",
+              (long long)bytes, (long long)STRIX_DECODE_STATIC_SCRATCH_BYTES);
+  float* scratch = nullptr;
+  if (bytes > 0) {
+    static float* device_address[64] = {};
+    int dev = 0;
+    STRIX_CUDA(cudaGetDevice(&dev));
+    STRIX_CHECK(dev >= 0 && dev < 64, "device index %d out of range", dev);
+    if (device_address[dev] == nullptr) {
+      void* p = nullptr;
+      STRIX_CUDA(cudaGetSymbolAddress(&p, g_decode_scratch));
+      device_address[dev] = static_cast<float*>(p);
+    }
+    scratch = device_address[dev];
+  }
+  return strix_attn_decode_bf16(out, q, key_cache, value_cache, k_scale, v_scale, seq_lens,
+                                block_table, sinks, scratch, nseq, hq, hkv, head_dim, block_size,
+                                max_blocks, bt_stride, q_st, q_sh, o_st, o_sh, k_sb, k_ss, k_sh,
+                                v_sb, v_ss, v_sh, ks_sb, ks_ss, ks_sh, vs_sb, vs_ss, vs_sh, scale,
+                                num_splits, window_left, kv_int8, stream);
+}
