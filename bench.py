@@ -182,6 +182,7 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--ctx-hi", type=int, default=65536)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-moe", action="store_true", help="skip the MoE FP8 layer runs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -322,9 +323,76 @@ def main() -> None:
             line["parity"] = {"max_abs_err": diff.max().item(), "ref_rms": rms,
                               "ref_at_max_err": ref.view(-1)[worst].item(),
                               "max_abs_ref": ref.abs().max().item(), "ok": ok}
+        if world == 1 and not args.no_moe:
+            del batch
+            torch.cuda.empty_cache()
+            line["moe_fp8"] = bench_moe_fp8(args, dev, not args.no_cpu_baseline)
+            line["gpu_launches"] += line["moe_fp8"]["gpu_launches"]
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def bench_moe_fp8(args, dev, with_cpu: bool) -> dict:
+    """The MoE half of the compound metric: one FP8 W8A8 block-scaled layer at
+    256 tokens (config 1: hidden 2048, 128 experts, top-8, intermediate 768) and,
+    for the tensor-bound regime, at 4096 tokens. At 256 tokens every expert is
+    hit with ~16 rows, so the layer is bound by streaming the 604 MB of expert
+    weights once: GB/s of weight bytes against the HBM roofline is reported
+    beside TFLOP/s. Weights (604 MB) exceed the 126 MB L2."""
+    import libstrix_b200 as strix
+    from libstrix_b200.moe import Fp8MoeWorkspace, pick_block_m
+    from libstrix_b200.workloads import moe_fp8_layer
+
+    peak, peak_kind = measured_peaks()
+    out = {"config": "MoE FP8 W8A8 block-scaled, H=2048 E=128 top-8 I=768", "gpu_launches": 0,
+           "runs": []}
+    for tokens in (256, 4096):
+        layer = moe_fp8_layer(tokens=tokens, seed=0, device=dev)
+        ws = Fp8MoeWorkspace(tokens, layer.top_k, 2048, 768, dev)
+
+        def step():
+            return strix.moe.fused_moe_fp8_w8a8(layer.x, layer.logits, layer.w13, layer.w13_scale,
+                                                layer.w2, layer.w2_scale, layer.top_k, ws=ws)
+
+        for _ in range(args.warmup):
+            step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            res = step()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        gbs = layer.weight_bytes / (ms * 1e-3) / 1e9
+        run = {"tokens": tokens, "ms_per_layer": ms, "tflops": layer.flops / (ms * 1e-3) / 1e12,
+               "weight_gbs": gbs, "weight_bytes": layer.weight_bytes,
+               "block_m": pick_block_m(tokens, layer.top_k, 128),
+               "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s",
+                            "frac": gbs / peak, "peak_kind": peak_kind}}
+        out["gpu_launches"] += 7 * args.steps
+        if with_cpu and tokens == 256:
+            from oracle import moe as M
+
+            cpu = layer.to("cpu")
+            threads = len(os.sched_getaffinity(0))
+            torch.set_num_threads(threads)
+            t0 = time.perf_counter()
+            ref, _, _ = M.moe_fp8_layer(cpu.x, cpu.logits, cpu.w13, cpu.w13_scale, cpu.w2,
+                                        cpu.w2_scale, cpu.top_k)
+            sec = time.perf_counter() - t0
+            diff = (res.float().cpu() - ref.float()).abs()
+            rms = ref.float().pow(2).mean().sqrt().item()
+            run["cpu_baseline"] = {"value": layer.flops / sec / 1e12, "unit": "TFLOP/s",
+                                   "cores": threads, "kind": "port", "seconds": sec,
+                                   "sample": "the whole 256-token layer, torch fp32 incl. dequantisation"}
+            run["parity"] = {"max_abs_err": diff.max().item(), "ref_rms": rms,
+                             "ok": bool((diff <= 2e-2 * rms + ref.float().abs() * 2.0 ** -8).all())}
+        out["runs"].append(run)
+        del layer, ws
+        torch.cuda.empty_cache()
+    return out
 
 
 if __name__ == "__main__":

@@ -89,6 +89,79 @@ int strix_attn_decode_bf16(
     double scale, int64_t num_splits, int64_t window_left, int kv_int8,
     strix_stream_t stream);
 
+/* ------------------------------------------------------------------------
+ * MoE layer: router, permutation, activation quantisers, expert GEMMs, combine.
+ * ---------------------------------------------------------------------- */
+
+/* Router: fp32 softmax over `experts` -> top_k (ties: lower expert index) ->
+ * weights p_i / sum of selected p (renormalize != 0) or p_i. Not in the
+ * reference (vLLM's fused_topk on its call path, python/strix_vllm/moe.py);
+ * defined by the benchmark configuration's "softmax then top-k then
+ * renormalise". logits fp32 [tokens, experts] (row stride logits_stride),
+ * topk_ids int32 [tokens, top_k], topk_weights fp32 [tokens, top_k]. */
+int strix_moe_topk_softmax(const float* logits, int32_t* topk_ids, float* topk_weights,
+                           int64_t tokens, int64_t experts, int64_t top_k,
+                           int64_t logits_stride, int renormalize, strix_stream_t stream);
+
+/* Entries sorted_ids must hold for strix_moe_align (a multiple of block_m). */
+int64_t strix_moe_align_capacity(int64_t numel, int64_t experts, int64_t block_m);
+
+/* Permutation with the moe_align_block_size contract that the reference's
+ * kernels consume (csrc/moe/moe_gemm_w8a16.hip:110-123) and its tests restate
+ * (tests/test_moe_gemm.py:9-31): slot ids (0 .. numel-1) grouped by expert in
+ * ascending expert and ascending slot order, each expert's run padded to
+ * block_m with the invalid id `numel`; experts without tokens get no block;
+ * *num_post_padded = total padded length. Everything after it is filled:
+ * sorted_ids with `numel`, expert_ids with -1 (a block the GEMMs skip). Ids
+ * outside [0, experts) are ignored (not routed here). */
+int strix_moe_align(const int32_t* topk_ids, int32_t* sorted_ids, int32_t* expert_ids,
+                    int32_t* num_post_padded, int64_t numel, int64_t experts, int64_t block_m,
+                    int64_t sorted_capacity, int64_t expert_capacity, strix_stream_t stream);
+
+/* Per (row, 128-element group) symmetric int8 quantiser: s = amax / 127 (1 for
+ * an all-zero group), q = clamp(rint(x * (1 / s)), +-127). Replaces
+ * strix::moe_act_quant_i8 (csrc/moe/moe_gemm_w4a8.hip:283-348). x bf16 (or fp16
+ * when x_is_f16) [rows, k], q int8 [rows, k], sa fp32 [rows, k / 128]. */
+int strix_moe_act_quant_i8(const void* x, void* q, float* sa, int64_t rows, int64_t k,
+                           int64_t x_stride, int64_t q_stride, int64_t sa_stride, int x_is_f16,
+                           strix_stream_t stream);
+
+/* As above to float8_e4m3fn: s = amax / 448 (1 for an all-zero group), q =
+ * e4m3(x / s), round to nearest even. No counterpart in the reference (its FP8
+ * experts take 16-bit activations); this is the activation form of the
+ * benchmark's W8A8 configuration. */
+int strix_moe_act_quant_fp8(const void* x, void* q, float* sa, int64_t rows, int64_t k,
+                            int64_t x_stride, int64_t q_stride, int64_t sa_stride, int x_is_f16,
+                            strix_stream_t stream);
+
+/* Grouped expert GEMM over the moe_align layout. Replaces moe_gemm_bf16
+ * (csrc/moe/moe_gemm_bf16.hip:298), moe_gemm_w8a16 / moe_gemm_fp8 /
+ * moe_gemm_fp8_raw (csrc/moe/moe_gemm_w8a16.hip:581-623) and adds the W8A8 FP8
+ * form. c[sid, :] is written only for valid sorted ids (sid < num_valid).
+ *   weight_format  0 float8_e4m3fn, 1 int8, 2 bf16        w [experts, n, k]
+ *   act_format     0 bf16, 1 fp16, 2 float8_e4m3fn (+ act_scales fp32 [a_rows, k/128])
+ *   scale_kind     0 none, 1 per output channel [E, N], 2 block fp32 [E, N/128, K/128]
+ *   scale_dtype    0 fp32, 1 bf16, 2 fp16
+ *   gate_act       0: c[sid, n] = (a W^T)[n] * topk_weights[sid] (1 if NULL), c is [*, n]
+ *                  1 silu / 2 gelu_tanh: W rows are [gate; up], c[sid, j] =
+ *                  act(gate_j) * up_j, c is [*, n / 2]
+ * Strides are in elements. k must be a multiple of 128, n of 16. */
+int strix_moe_gemm(
+    void* c, const void* a, const void* w, const void* scales, const float* act_scales,
+    const int32_t* sorted_ids, const int32_t* expert_ids, const int32_t* num_post_padded,
+    const float* topk_weights, int64_t num_valid, int64_t a_rows, int64_t experts, int64_t n,
+    int64_t k, int64_t a_stride, int64_t c_stride, int64_t w_stride_e, int64_t w_stride_n,
+    int64_t s_stride_e, int64_t s_stride_n, int64_t sa_stride, int64_t sorted_len,
+    int64_t expert_len, int64_t top_k, int64_t block_m, int weight_format, int act_format,
+    int scale_kind, int scale_dtype, int gate_act, int c_is_f16, strix_stream_t stream);
+
+/* Combine: out[t, :] = sum over j of in[t, j, :] in fp32, one bf16 rounding
+ * (vLLM's moe_sum on the reference's call path, python/strix_vllm/moe.py:1012-1014;
+ * routing weights were already applied by the down GEMM). bf16 in [tokens,
+ * top_k, hidden] (strides in_st, in_sj), bf16 out [tokens, hidden]. */
+int strix_moe_sum(const void* in, void* out, int64_t tokens, int64_t top_k, int64_t hidden,
+                  int64_t in_st, int64_t in_sj, int64_t out_st, strix_stream_t stream);
+
 /* strix_attn_decode_bf16 without a workspace argument, for callers that cannot
  * allocate device memory: a host loop that owns nothing but the input and
  * output buffers it was given, or a process whose device memory was budgeted

@@ -19,6 +19,7 @@ from .registry import Range, explain, geometries, kernels, ops, select, selectio
 
 _lib.load()
 from . import torch_ops  # noqa: E402  (registers torch.ops.strix.*)
+from . import moe  # noqa: E402
 
 StrixError = _lib.StrixError
 
@@ -69,6 +70,7 @@ __all__ = [
     "geometries",
     "is_supported_device",
     "kernels",
+    "moe",
     "ops",
     "select",
     "selections",

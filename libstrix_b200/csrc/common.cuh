@@ -102,6 +102,16 @@ __device__ __forceinline__ void cp_async_16(uint32_t smem_addr, const void* gptr
 __device__ __forceinline__ void cp_async_4(uint32_t smem_addr, const void* gptr) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_addr), "l"(gptr));
 }
+// As above, but the destination is filled with zeros when `valid` is false
+// (src-size 0); the source address must still be a mapped one.
+__device__ __forceinline__ void cp_async_16_zfill(uint32_t smem_addr, const void* gptr, bool valid) {
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr), "l"(gptr), "r"(n));
+}
+__device__ __forceinline__ void cp_async_4_zfill(uint32_t smem_addr, const void* gptr, bool valid) {
+  const int n = valid ? 4 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_addr), "l"(gptr), "r"(n));
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {

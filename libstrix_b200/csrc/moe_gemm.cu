@@ -1,0 +1,463 @@
+// Grouped expert GEMM over the moe_align_block_size layout, for sm_100a: the
+// weight-streaming kernel family (small and medium token counts per expert,
+// where the layer is bound by reading each routed expert's weights once).
+//
+// Contract (all moe_gemm_* ops of the reference, csrc/moe/moe_gemm_w8a16.hip:76-404):
+//   * m-block mb owns sorted ids [mb * block_m, (mb + 1) * block_m); it is
+//     skipped when mb * block_m >= *num_post_padded or expert_ids[mb] < 0;
+//   * a sorted id sid >= num_valid is padding: it contributes zeros and writes
+//     nothing; the A row of slot sid is sid / top_k, the C row is sid;
+//   * gate_mul: W rows are [gate (N/2); up (N/2)], output column j < N/2 is
+//     act(sum_k A W[j]) * (sum_k A W[N/2 + j]) computed in fp32 and rounded once;
+//     otherwise C[sid, n] = (sum_k ...) * topk_w[sid];
+//   * block scales index [expert, global W row / 128, k / 128].
+//
+// Shape of the kernel: a CTA = (m-block, 4 warps); each warp owns 16 weight rows
+// (8 gate rows + the 8 matching up rows under gate_mul, so the fused epilogue
+// needs no exchange) and keeps them as the MMA M dimension, while the tokens of
+// the m-block are the N dimension in tiles of 8 (fully padded tiles are skipped,
+// so ragged experts waste no tensor work). Per 128-wide K block every thread
+// copies its share of the weight rows and of the token rows into a shared-memory
+// ring with 16-byte cp.async (3 blocks ahead); operands are read back as MMA
+// fragments with bank-conflict-free swizzles. 8-bit x 8-bit forms run the MMA on
+// the raw bytes (e4m3 x e4m3 -> f32, s8 x s8 -> s32); forms with 16-bit
+// activations widen the weights exactly in registers and apply block scales to
+// the fp32 partial sums of each K block.
+#include "common.cuh"
+
+namespace strix {
+namespace {
+
+constexpr int kWarps = 4;
+constexpr int kThreads = kWarps * 32;
+constexpr int kStages = 4;
+constexpr int kKB = 128;  // K elements per pipeline step (= the scale block)
+
+enum WFmt { W_E4M3 = 0, W_INT8 = 1, W_BF16 = 2 };
+enum AFmt { A_BF16 = 0, A_F16 = 1, A_E4M3 = 2 };
+enum ScaleKind { S_NONE = 0, S_CHANNEL = 1, S_BLOCK = 2 };
+enum Act { ACT_NONE = 0, ACT_SILU = 1, ACT_GELU_TANH = 2 };
+
+struct MoeArgs {
+  void* c;
+  const void* a;
+  const void* w;
+  const void* scales;
+  const float* sa;  // activation scales [rows, K / 128] (A_E4M3 only)
+  const int32_t* sorted_ids;
+  const int32_t* expert_ids;
+  const int32_t* num_post;
+  const float* topk_w;
+  int64_t num_valid;
+  int64_t a_stride, c_stride, w_se, w_sn, s_se, s_sn, sa_stride;  // elements
+  int top_k, K, N, block_m;
+  int scale_kind, scale_dtype;  // dtype: 0 fp32, 1 bf16, 2 fp16
+  int c_f16;
+};
+
+__device__ __forceinline__ float load_scale(const void* p, int64_t idx, int dtype) {
+  if (dtype == 0) return static_cast<const float*>(p)[idx];
+  const uint16_t h = static_cast<const uint16_t*>(p)[idx];
+  if (dtype == 1) return __uint_as_float(uint32_t(h) << 16);
+  return __half2float(__ushort_as_half(h));
+}
+
+__device__ __forceinline__ float apply_act(float g, int act) {
+  if (act == ACT_SILU) return g / (1.f + __expf(-g));
+  // GELU-tanh: 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))
+  const float u = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+  return 0.5f * g * (1.f + tanhf(u));
+}
+
+__device__ __forceinline__ void mma_e4m3_16832(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                               uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 "
+      "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Four 8-bit weights (one 32-bit word) -> two registers of 16-bit pairs in the
+// activation's format: (w0, w1) and (w2, w3). The fp16 form is exact and the
+// scale goes onto the fp32 sums (the reference's "raw" kernels and their
+// oracle, tests/test_moe_fp8_raw.py:17-28). The bf16 form multiplies by the
+// scale first and rounds the product to bf16, which is what the reference's
+// bf16 kernels stage (csrc/moe/moe_gemm_w8a16.hip:218-243) and what their
+// oracle dequantises to (tests/test_moe_fp8.py:29): at these magnitudes the
+// fused gate amplifies the 2^-9 rounding beyond the test tolerance otherwise.
+template <int WF, int AF>
+__device__ __forceinline__ void widen(uint32_t w, float scale, uint32_t& lo, uint32_t& hi) {
+  uint32_t f_lo, f_hi;  // exact f16x2
+  if constexpr (WF == W_E4M3) {
+    asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\t"
+        "cvt.rn.f16x2.e4m3x2 %0, l;\n\tcvt.rn.f16x2.e4m3x2 %1, h;\n\t}"
+        : "=r"(f_lo), "=r"(f_hi)
+        : "r"(w));
+  } else {  // W_INT8: 0x6400 | (b ^ 0x80) is fp16 1024 + b + 128
+    const uint32_t x = w ^ 0x80808080u;
+    f_lo = sub_f16x2(prmt(x, 0x64646464u, 0x4140), 0x64806480u);
+    f_hi = sub_f16x2(prmt(x, 0x64646464u, 0x4342), 0x64806480u);
+  }
+  if constexpr (AF == A_F16) {
+    lo = f_lo, hi = f_hi;
+  } else {
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&f_lo));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&f_hi));
+    lo = pack_bf16x2(a.x * scale, a.y * scale), hi = pack_bf16x2(b.x * scale, b.y * scale);
+  }
+}
+
+// Shared-memory row layouts of one K block. A row of 8-bit elements is 128
+// bytes = 8 chunks of 16; a row of 16-bit elements is 256 bytes = 16 chunks.
+// Lane c of a fragment owns elements [32c, 32c + 32) of a row: chunks 2c, 2c+1
+// (8-bit) or 4c .. 4c+3 (16-bit). The physical chunk is permuted so that the 8
+// lanes of each shared-memory phase (2 rows x 4 lanes) cover 8 distinct chunks
+// of one 128-byte bank window.
+__device__ __forceinline__ int swz8(int row, int chunk) { return chunk ^ (row & 7); }
+__device__ __forceinline__ int swz16(int row, int chunk) {
+  // chunk = 4c + j  ->  4j + c, then the two rows of a phase take the two halves
+  return ((((chunk & 3) << 2) | (chunk >> 2)) ^ ((row & 1) << 2));
+}
+
+template <int BYTES>  // bytes per element: 1 or 2
+__device__ __forceinline__ uint32_t row_chunk_offset(int row, int chunk) {
+  if constexpr (BYTES == 1) return uint32_t(row * 128 + (swz8(row, chunk) << 4));
+  return uint32_t(row * 256 + (swz16(row, chunk) << 4));
+}
+
+template <int WF, int AF, int BMC>
+struct Layout {
+  static constexpr int WB = WF == W_BF16 ? 2 : 1;    // weight bytes / element
+  static constexpr int AB = AF == A_E4M3 ? 1 : 2;    // activation bytes / element
+  static constexpr int kWRow = kKB * WB, kARow = kKB * AB;
+  static constexpr int kWBytes = kWarps * 16 * kWRow;  // all warps' weight rows
+  static constexpr int kABytes = BMC * kARow;
+  static constexpr int kSaBytes = AF == A_E4M3 ? BMC * 4 : 0;
+  static constexpr int kStage = kWBytes + kABytes + kSaBytes;
+  static constexpr int kSmem = kStages * kStage + BMC * 8 + 16;
+};
+
+template <int WF, int AF, int BMC, int ACT>
+__global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs p) {
+  using L = Layout<WF, AF, BMC>;
+  constexpr int NT = BMC / 8;  // token tiles of 8
+  extern __shared__ __align__(16) uint8_t smem[];
+  int64_t* s_arow = reinterpret_cast<int64_t*>(smem + kStages * L::kStage);  // [BMC] A row or -1
+
+  const int mb = blockIdx.y;
+  if (mb * p.block_m >= *p.num_post) return;
+  const int expert = p.expert_ids[mb];
+  if (expert < 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, c = lane & 3;
+  constexpr bool kGate = ACT != ACT_NONE;
+  const int half_n = p.N / 2;
+  // weight rows of this warp: local row r < 8 -> row_lo + r, r >= 8 -> row_hi + r - 8
+  const int nb = (blockIdx.x * kWarps + warp) * (kGate ? 8 : 16);
+  const bool warp_live = nb < (kGate ? half_n : p.N);
+  const int row_lo = nb, row_hi = kGate ? half_n + nb : nb + 8;
+  const int nkb = p.K / kKB;
+
+  const uint8_t* wbase = static_cast<const uint8_t*>(p.w) + int64_t(expert) * p.w_se * L::WB;
+  const uint32_t smem_s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+
+  for (int tc = 0; tc < p.block_m; tc += BMC) {  // token chunks of the m-block
+    __syncthreads();  // previous chunk's readers are done with s_arow and the ring
+    int valid = 0;
+    for (int i = threadIdx.x; i < BMC; i += kThreads) {
+      const int64_t sid = tc + i < p.block_m ? p.sorted_ids[mb * p.block_m + tc + i] : p.num_valid;
+      const bool ok = sid >= 0 && sid < p.num_valid;
+      s_arow[i] = ok ? sid / p.top_k : -1;
+      valid |= ok;
+    }
+    if (!__syncthreads_or(valid)) continue;  // a chunk of padding only
+
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+
+    // token tiles that hold at least one real token (padding sits at the end of
+    // an expert's run, but a ragged middle is handled too: rows are zero-filled)
+    int nt_live = 0;
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      bool any = false;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) any |= s_arow[8 * j + i] >= 0;
+      if (any) nt_live = j + 1;
+    }
+
+    // weights widened to bf16 carry their scale (see widen); other forms scale sums
+    constexpr bool kPrescale = AF == A_BF16 && WF != W_BF16;
+    float ch0 = 1.f, ch1 = 1.f;
+    if (p.scale_kind == S_CHANNEL && warp_live) {
+      ch0 = load_scale(p.scales, int64_t(expert) * p.s_se + row_lo + g, p.scale_dtype);
+      ch1 = load_scale(p.scales, int64_t(expert) * p.s_se + row_hi + g, p.scale_dtype);
+    }
+
+    auto issue = [&](int kb) {
+      if (kb < nkb) {
+        const uint32_t st = smem_s + (kb % kStages) * L::kStage;
+        // weights: each warp copies its own 16 rows (CPW chunks per row)
+        if (warp_live) {
+          constexpr int CPW = L::kWRow / 16;
+#pragma unroll
+          for (int i = 0; i < 16 * CPW / 32; ++i) {
+            const int id = i * 32 + lane, r = id / CPW, ch = id % CPW;
+            const int grow = r < 8 ? row_lo + r : row_hi + r - 8;
+            const uint8_t* src = wbase + (int64_t(grow) * p.w_sn + int64_t(kb) * kKB) * L::WB + ch * 16;
+            cp_async_16(st + warp * 16 * L::kWRow + row_chunk_offset<L::WB>(r, ch), src);
+          }
+        }
+        // activations: all threads share the BMC token rows (zero-filled padding)
+        constexpr int CPA = L::kARow / 16;
+        for (int id = threadIdx.x; id < nt_live * 8 * CPA; id += kThreads) {
+          const int r = id / CPA, ch = id % CPA;
+          const int64_t arow = s_arow[r];
+          const uint8_t* src = static_cast<const uint8_t*>(p.a) +
+                               ((arow < 0 ? 0 : arow) * p.a_stride + int64_t(kb) * kKB) * L::AB + ch * 16;
+          cp_async_16_zfill(st + L::kWBytes + row_chunk_offset<L::AB>(r, ch), src, arow >= 0);
+        }
+        if constexpr (AF == A_E4M3) {
+          for (int r = threadIdx.x; r < nt_live * 8; r += kThreads) {
+            const int64_t arow = s_arow[r];
+            cp_async_4_zfill(st + L::kWBytes + L::kABytes + r * 4,
+                             p.sa + (arow < 0 ? 0 : arow) * p.sa_stride + kb, arow >= 0);
+          }
+        }
+      }
+      cp_async_commit();
+    };
+
+#pragma unroll
+    for (int i = 0; i < kStages - 1; ++i) issue(i);
+
+    for (int kb = 0; kb < nkb; ++kb) {
+      cp_async_wait<kStages - 2>();
+      __syncthreads();          // block kb landed for everyone; stage kb-1 is free
+      issue(kb + kStages - 1);
+      if (!warp_live) continue;
+      const uint8_t* st = smem + (kb % kStages) * L::kStage;
+      const uint8_t* wst = st + warp * 16 * L::kWRow;
+      const uint8_t* ast = st + L::kWBytes;
+
+      // block scales of this warp's two row groups
+      float sw0 = 1.f, sw1 = 1.f;
+      if (p.scale_kind == S_BLOCK) {
+        const int64_t sb = int64_t(expert) * p.s_se + kb;
+        sw0 = load_scale(p.scales, sb + int64_t((row_lo + g) / 128) * p.s_sn, p.scale_dtype);
+        sw1 = load_scale(p.scales, sb + int64_t((row_hi + g) / 128) * p.s_sn, p.scale_dtype);
+      }
+
+      if constexpr (AF == A_E4M3) {
+        // raw e4m3 x e4m3: lane's 32 bytes of rows g, g + 8
+        uint32_t wr[2][8];
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            const uint4 x = *reinterpret_cast<const uint4*>(
+                wst + row_chunk_offset<1>(g + 8 * r, 2 * c + i));
+            wr[r][4 * i] = x.x, wr[r][4 * i + 1] = x.y, wr[r][4 * i + 2] = x.z, wr[r][4 * i + 3] = x.w;
+          }
+        const float* sap = reinterpret_cast<const float*>(ast + L::kABytes);
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          if (j >= nt_live) break;
+          uint32_t xr[8];
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            const uint4 x = *reinterpret_cast<const uint4*>(
+                ast + row_chunk_offset<1>(8 * j + g, 2 * c + i));
+            xr[4 * i] = x.x, xr[4 * i + 1] = x.y, xr[4 * i + 2] = x.z, xr[4 * i + 3] = x.w;
+          }
+          float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int s = 0; s < 4; ++s) {
+            const uint32_t a[4] = {wr[0][2 * s], wr[1][2 * s], wr[0][2 * s + 1], wr[1][2 * s + 1]};
+            mma_e4m3_16832(part, a, xr[2 * s], xr[2 * s + 1]);
+          }
+          const float sa0 = sap[8 * j + 2 * c], sa1 = sap[8 * j + 2 * c + 1];
+          acc[j][0] += part[0] * (sw0 * sa0);
+          acc[j][1] += part[1] * (sw0 * sa1);
+          acc[j][2] += part[2] * (sw1 * sa0);
+          acc[j][3] += part[3] * (sw1 * sa1);
+        }
+      } else {
+        // 16-bit activations: weights widened to the activation's format
+        uint32_t wf[2][16];  // per row: 8 k-steps x (lo, hi)
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          if constexpr (WF == W_BF16) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint4 x = *reinterpret_cast<const uint4*>(
+                  wst + row_chunk_offset<2>(g + 8 * r, 4 * c + i));
+              wf[r][4 * i] = x.x, wf[r][4 * i + 1] = x.y, wf[r][4 * i + 2] = x.z, wf[r][4 * i + 3] = x.w;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              const uint4 x = *reinterpret_cast<const uint4*>(
+                  wst + row_chunk_offset<1>(g + 8 * r, 2 * c + i));
+              const float ws = r == 0 ? sw0 * ch0 : sw1 * ch1;
+              widen<WF, AF>(x.x, ws, wf[r][8 * i], wf[r][8 * i + 1]);
+              widen<WF, AF>(x.y, ws, wf[r][8 * i + 2], wf[r][8 * i + 3]);
+              widen<WF, AF>(x.z, ws, wf[r][8 * i + 4], wf[r][8 * i + 5]);
+              widen<WF, AF>(x.w, ws, wf[r][8 * i + 6], wf[r][8 * i + 7]);
+            }
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          if (j >= nt_live) break;
+          uint32_t xr[16];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint4 x = *reinterpret_cast<const uint4*>(
+                ast + row_chunk_offset<2>(8 * j + g, 4 * c + i));
+            xr[4 * i] = x.x, xr[4 * i + 1] = x.y, xr[4 * i + 2] = x.z, xr[4 * i + 3] = x.w;
+          }
+          float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int s = 0; s < 8; ++s) {
+            const uint32_t a[4] = {wf[0][2 * s], wf[1][2 * s], wf[0][2 * s + 1], wf[1][2 * s + 1]};
+            if constexpr (AF == A_F16) mma_f16_16816(part, a, xr[2 * s], xr[2 * s + 1]);
+            else mma_bf16_16816(part, a, xr[2 * s], xr[2 * s + 1]);
+          }
+          const float f0 = kPrescale ? 1.f : sw0, f1 = kPrescale ? 1.f : sw1;
+          acc[j][0] += part[0] * f0;
+          acc[j][1] += part[1] * f0;
+          acc[j][2] += part[2] * f1;
+          acc[j][3] += part[3] * f1;
+        }
+      }
+    }
+    cp_async_wait<0>();
+    if (!warp_live) continue;
+
+    // ---- epilogue: lane holds (row g | g + 8) x (tokens 2c, 2c + 1) of each tile
+    if (kPrescale) ch0 = ch1 = 1.f;  // already inside the widened weights
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      if (j >= nt_live) break;
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        const int slot = tc + 8 * j + 2 * c + t;
+        if (slot >= p.block_m) continue;
+        const int64_t sid = p.sorted_ids[mb * p.block_m + slot];
+        if (sid < 0 || sid >= p.num_valid) continue;
+        const float v0 = acc[j][t] * ch0, v1 = acc[j][2 + t] * ch1;
+        if constexpr (kGate) {
+          const float o = apply_act(v0, ACT) * v1;
+          const int64_t at = sid * p.c_stride + nb + g;
+          if (p.c_f16) static_cast<__half*>(p.c)[at] = __float2half_rn(o);
+          else static_cast<__nv_bfloat16*>(p.c)[at] = __float2bfloat16_rn(o);
+        } else {
+          const float tw = p.topk_w ? p.topk_w[sid] : 1.f;
+          __nv_bfloat16* crow = static_cast<__nv_bfloat16*>(p.c) + sid * p.c_stride;
+          crow[row_lo + g] = __float2bfloat16_rn(v0 * tw);
+          crow[row_hi + g] = __float2bfloat16_rn(v1 * tw);
+        }
+      }
+    }
+  }
+}
+
+template <int WF, int AF, int BMC, int ACT>
+int launch_stream(const MoeArgs& p, dim3 grid, cudaStream_t st) {
+  using L = Layout<WF, AF, BMC>;
+  auto kernel = moe_gemm_stream_kernel<WF, AF, BMC, ACT>;
+  if (L::kSmem > 48 * 1024) {
+    static bool done[64] = {};
+    int dev = 0;
+    STRIX_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !done[dev]) {
+      STRIX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmem));
+      if (dev >= 0 && dev < 64) done[dev] = true;
+    }
+  }
+  kernel<<<grid, kThreads, L::kSmem, st>>>(p);
+  return launch_status("moe_gemm");
+}
+
+template <int WF, int AF, int BMC>
+int launch_act(const MoeArgs& p, int act, dim3 grid, cudaStream_t st) {
+  if (act == ACT_NONE) return launch_stream<WF, AF, BMC, ACT_NONE>(p, grid, st);
+  if (act == ACT_SILU) return launch_stream<WF, AF, BMC, ACT_SILU>(p, grid, st);
+  return launch_stream<WF, AF, BMC, ACT_GELU_TANH>(p, grid, st);
+}
+
+template <int WF, int AF>
+int launch_bm(const MoeArgs& p, int act, dim3 grid, cudaStream_t st) {
+  if (p.block_m <= 16) return launch_act<WF, AF, 16>(p, act, grid, st);
+  if (p.block_m <= 32) return launch_act<WF, AF, 32>(p, act, grid, st);
+  return launch_act<WF, AF, 64>(p, act, grid, st);
+}
+
+}  // namespace
+}  // namespace strix
+
+using namespace strix;
+
+extern "C" int strix_moe_gemm(
+    void* c, const void* a, const void* w, const void* scales, const float* act_scales,
+    const int32_t* sorted_ids, const int32_t* expert_ids, const int32_t* num_post_padded,
+    const float* topk_weights, int64_t num_valid, int64_t a_rows, int64_t experts, int64_t n,
+    int64_t k, int64_t a_stride, int64_t c_stride, int64_t w_stride_e, int64_t w_stride_n,
+    int64_t s_stride_e, int64_t s_stride_n, int64_t sa_stride, int64_t sorted_len,
+    int64_t expert_len, int64_t top_k, int64_t block_m, int weight_format, int act_format,
+    int scale_kind, int scale_dtype, int gate_act, int c_is_f16, strix_stream_t stream) {
+  STRIX_CHECK(weight_format >= W_E4M3 && weight_format <= W_BF16, "unknown weight format");
+  STRIX_CHECK(act_format >= A_BF16 && act_format <= A_E4M3, "unknown activation format");
+  STRIX_CHECK(gate_act >= ACT_NONE && gate_act <= ACT_GELU_TANH,
+              "activation must be silu or gelu_tanh");
+  STRIX_CHECK(scale_kind >= S_NONE && scale_kind <= S_BLOCK && scale_dtype >= 0 && scale_dtype <= 2,
+              "scales bf16, fp16 or fp32");
+  STRIX_CHECK(experts > 0 && n > 0 && k > 0 && num_valid >= 0 && a_rows >= 0, "bad ranks");
+  STRIX_CHECK(k % kKB == 0, "K %% 128");
+  STRIX_CHECK(gate_act == ACT_NONE || (n % 16 == 0 && topk_weights == nullptr),
+              "silu_mul needs even N and no topk weights");
+  STRIX_CHECK(gate_act != ACT_NONE || n % 16 == 0, "N %% 16");
+  STRIX_CHECK(top_k >= 1 && block_m >= 1 && block_m <= 1024, "bad top_k / block_m");
+  STRIX_CHECK(expert_len * block_m >= sorted_len, "expert_ids too short for block_m %lld",
+              (long long)block_m);
+  STRIX_CHECK(act_format != A_E4M3 || (weight_format == W_E4M3 && act_scales != nullptr),
+              "e4m3 activations need e4m3 weights and activation scales");
+  STRIX_CHECK(weight_format != W_BF16 || (act_format == A_BF16 && scale_kind == S_NONE),
+              "bf16 weights take bf16 activations and no scales");
+  STRIX_CHECK(weight_format == W_BF16 || scale_kind != S_NONE, "quantized weights need scales");
+  STRIX_CHECK(scale_kind != S_BLOCK || (weight_format == W_E4M3 && n % 128 == 0),
+              "block scales must be fp32 [E, N/128, K/128]");
+  STRIX_CHECK(!c_is_f16 || (gate_act != ACT_NONE && act_format == A_F16),
+              "fp16 output only for the fused activation of the fp16 form");
+  const int wb = weight_format == W_BF16 ? 2 : 1, ab = act_format == A_E4M3 ? 1 : 2;
+  STRIX_CHECK((a_stride * ab) % 16 == 0 && (w_stride_n * wb) % 16 == 0 && (w_stride_e * wb) % 16 == 0 &&
+                  reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0,
+              "16-byte aligned rows required");
+  if (sorted_len == 0 || num_valid == 0) return STRIX_OK;
+
+  MoeArgs p;
+  p.c = c, p.a = a, p.w = w, p.scales = scales, p.sa = act_scales;
+  p.sorted_ids = sorted_ids, p.expert_ids = expert_ids, p.num_post = num_post_padded;
+  p.topk_w = topk_weights;
+  p.num_valid = num_valid;
+  p.a_stride = a_stride, p.c_stride = c_stride, p.w_se = w_stride_e, p.w_sn = w_stride_n;
+  p.s_se = s_stride_e, p.s_sn = s_stride_n, p.sa_stride = sa_stride;
+  p.top_k = int(top_k), p.K = int(k), p.N = int(n), p.block_m = int(block_m);
+  p.scale_kind = scale_kind, p.scale_dtype = scale_dtype, p.c_f16 = c_is_f16;
+
+  const int rows_per_cta = kWarps * (gate_act != ACT_NONE ? 8 : 16);
+  const int64_t out_rows = gate_act != ACT_NONE ? n / 2 : n;
+  const int64_t m_blocks = (sorted_len + block_m - 1) / block_m;
+  STRIX_CHECK(m_blocks <= 65535, "too many m-blocks");
+  const dim3 grid{unsigned((out_rows + rows_per_cta - 1) / rows_per_cta), unsigned(m_blocks), 1u};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (weight_format == W_E4M3 && act_format == A_E4M3) return launch_bm<W_E4M3, A_E4M3>(p, gate_act, grid, st);
+  if (weight_format == W_E4M3 && act_format == A_BF16) return launch_bm<W_E4M3, A_BF16>(p, gate_act, grid, st);
+  if (weight_format == W_E4M3 && act_format == A_F16) return launch_bm<W_E4M3, A_F16>(p, gate_act, grid, st);
+  if (weight_format == W_INT8 && act_format == A_BF16) return launch_bm<W_INT8, A_BF16>(p, gate_act, grid, st);
+  if (weight_format == W_BF16) return launch_bm<W_BF16, A_BF16>(p, gate_act, grid, st);
+  return fail(STRIX_ERR_INVALID, "moe_gemm: weight/activation format pair not built");
+}

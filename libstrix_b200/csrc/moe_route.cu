@@ -1,0 +1,356 @@
+// The small kernels around the expert GEMMs of a MoE layer, for sm_100a:
+// router (softmax -> top-k -> renormalise), token permutation
+// (moe_align_block_size contract), per-(row, 128-group) activation quantisers
+// (e4m3 and int8) and the top-k combine.
+//
+// The reference takes the router, the permutation and the combine from vLLM
+// (python/strix_vllm/moe.py:959-961, 1012-1014 call moe_align_block_size and
+// moe_sum); the permutation contract is the one its tests restate
+// (tests/test_moe_gemm.py:9-31). moe_act_quant_i8 follows
+// csrc/moe/moe_gemm_w4a8.hip:283-316.
+#include "common.cuh"
+
+namespace strix {
+namespace {
+
+// ------------------------------------------------------------------ router
+// One warp per token. Selection is on the logits (softmax is monotonic), ties
+// go to the lower expert index; weights are p_i / sum of the selected p.
+template <int VPL>  // values per lane: experts <= 32 * VPL
+__global__ void __launch_bounds__(128) topk_softmax_kernel(
+    const float* __restrict__ logits, int64_t l_stride, int32_t* __restrict__ ids,
+    float* __restrict__ weights, int tokens, int experts, int top_k, int renorm) {
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= tokens) return;
+  const float* row = logits + int64_t(t) * l_stride;
+  float v[VPL];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int e = lane + 32 * i;
+    v[i] = e < experts ? row[e] : -INFINITY;
+    mx = fmaxf(mx, v[i]);
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) sum += v[i] == -INFINITY ? 0.f : expf(v[i] - mx);
+#pragma unroll
+  for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  float my_w = 0.f, wsum = 0.f;   // lane j keeps the j-th selection
+  int my_id = 0;
+  for (int j = 0; j < top_k; ++j) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int e = lane + 32 * i;
+      if (e < experts && (v[i] > best || (v[i] == best && e < bi)) && v[i] != -INFINITY) {
+        best = v[i];
+        bi = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) {
+        best = ob;
+        bi = oi;
+      }
+    }
+    // every lane now agrees on (best, bi); its owner retires the value
+    if (bi != 0x7fffffff && (bi & 31) == lane) {
+#pragma unroll
+      for (int i = 0; i < VPL; ++i)
+        if (i == (bi >> 5)) v[i] = -INFINITY;
+    }
+    const float p = bi == 0x7fffffff ? 0.f : __fdiv_rn(expf(best - mx), sum);
+    wsum += p;
+    if (lane == j) {
+      my_w = p;
+      my_id = bi == 0x7fffffff ? 0 : bi;
+    }
+  }
+  if (lane < top_k) {
+    ids[int64_t(t) * top_k + lane] = my_id;
+    weights[int64_t(t) * top_k + lane] = renorm ? __fdiv_rn(my_w, wsum) : my_w;
+  }
+}
+
+// ------------------------------------------------------------------- align
+// CTA e < experts places the slots routed to expert e; CTA `experts` writes
+// num_post_padded and fills everything past it. Each CTA histograms all slots
+// itself (one pass over the ids, served by L2), so there is no inter-CTA
+// dependency and a single launch suffices. Order inside an expert is ascending
+// slot id (a stable partition), which makes the result unique and comparable
+// bit for bit.
+constexpr int kAlignThreads = 256;
+
+__global__ void __launch_bounds__(kAlignThreads) moe_align_kernel(
+    const int32_t* __restrict__ topk_ids, int32_t* __restrict__ sorted_ids,
+    int32_t* __restrict__ expert_ids, int32_t* __restrict__ num_post, int numel, int experts,
+    int block_m, int cap, int cap_blocks) {
+  extern __shared__ int s_count[];            // [experts]
+  __shared__ int s_warp[kAlignThreads / 32];
+  __shared__ int s_base;
+  const int e = blockIdx.x, tid = threadIdx.x;
+  for (int i = tid; i < experts; i += kAlignThreads) s_count[i] = 0;
+  __syncthreads();
+  for (int i = tid; i < numel; i += kAlignThreads) {
+    const int id = topk_ids[i];
+    if (id >= 0 && id < experts) atomicAdd(&s_count[id], 1);
+  }
+  __syncthreads();
+  // padded slots before expert e (or the grand total for the last CTA)
+  int part = 0;
+  const int upto = e < experts ? e : experts;
+  for (int i = tid; i < upto; i += kAlignThreads)
+    part += (s_count[i] + block_m - 1) / block_m * block_m;
+#pragma unroll
+  for (int o = 16; o; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+  if ((tid & 31) == 0) s_warp[tid >> 5] = part;
+  __syncthreads();
+  if (tid == 0) {
+    int s = 0;
+    for (int i = 0; i < kAlignThreads / 32; ++i) s += s_warp[i];
+    s_base = s;
+  }
+  __syncthreads();
+  const int base = s_base;
+  if (e == experts) {
+    if (tid == 0) num_post[0] = base;
+    for (int i = base + tid; i < cap; i += kAlignThreads) sorted_ids[i] = numel;
+    for (int i = base / block_m + tid; i < cap_blocks; i += kAlignThreads) expert_ids[i] = -1;
+    return;
+  }
+  const int count = s_count[e];
+  const int padded = (count + block_m - 1) / block_m * block_m;
+  for (int i = tid; i < padded / block_m; i += kAlignThreads)
+    if (base / block_m + i < cap_blocks) expert_ids[base / block_m + i] = e;
+  for (int i = count + tid; i < padded; i += kAlignThreads)
+    if (base + i < cap) sorted_ids[base + i] = numel;
+  if (count == 0) return;
+  // ordered compaction of the slots whose id == e
+  int placed = 0;
+  for (int start = 0; start < numel; start += kAlignThreads) {
+    const int i = start + tid;
+    const bool hit = i < numel && topk_ids[i] == e;
+    const unsigned bal = __ballot_sync(0xffffffffu, hit);
+    __syncthreads();  // s_warp reuse
+    if ((tid & 31) == 0) s_warp[tid >> 5] = __popc(bal);
+    __syncthreads();
+    int before = 0, total = 0;
+#pragma unroll
+    for (int w = 0; w < kAlignThreads / 32; ++w) {
+      const int c = s_warp[w];
+      before += w < (tid >> 5) ? c : 0;
+      total += c;
+    }
+    if (hit) {
+      const int pos = base + placed + before + __popc(bal & ((1u << (tid & 31)) - 1u));
+      if (pos < cap) sorted_ids[pos] = i;
+    }
+    placed += total;
+  }
+}
+
+// ------------------------------------------------------- activation quantisers
+// 16 lanes share one 128-element group (8 elements = 16 bytes each).
+template <bool FP8, bool IN_F16>
+__global__ void __launch_bounds__(256) act_quant_kernel(
+    const uint16_t* __restrict__ x, int64_t x_stride, uint8_t* __restrict__ q, int64_t q_stride,
+    float* __restrict__ sa, int64_t sa_stride, int64_t rows, int groups) {
+  int64_t team = (int64_t(blockIdx.x) * 256 + threadIdx.x) >> 4;
+  const int sub = threadIdx.x & 15;
+  // out-of-range teams redo the last group and skip the stores, so every lane
+  // of the warp stays in the shuffles below
+  const bool live = team < rows * groups;
+  if (!live) team = rows * groups - 1;
+  const int64_t r = team / groups;
+  const int gi = int(team % groups);
+  const uint4 w = *reinterpret_cast<const uint4*>(x + r * x_stride + gi * 128 + sub * 8);
+  const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+  float v[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (IN_F16) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&ws[i]));
+      v[2 * i] = f.x, v[2 * i + 1] = f.y;
+    } else {
+      v[2 * i] = bf16_lo(ws[i]), v[2 * i + 1] = bf16_hi(ws[i]);
+    }
+  }
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+  for (int o = 8; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o, 16));
+  uint2 packed;
+  float s;
+  if (FP8) {
+    s = amax > 0.f ? __fdiv_rn(amax, 448.f) : 1.f;
+    uint32_t h[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float a = __fdiv_rn(v[2 * i], s), b = __fdiv_rn(v[2 * i + 1], s);
+      uint16_t o;
+      asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(o) : "f"(b), "f"(a));
+      h[i] = o;
+    }
+    packed.x = h[0] | (h[1] << 16);
+    packed.y = h[2] | (h[3] << 16);
+  } else {
+    // s = amax / 127 (1 for an all-zero group), q = clamp(rint(x * (1 / s)), +-127):
+    // csrc/moe/moe_gemm_w4a8.hip:305-312
+    s = amax > 0.f ? __fdiv_rn(amax, 127.f) : 1.f;
+    const float inv = __fdiv_rn(1.f, s);
+    uint32_t b[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int qi = max(-127, min(127, __float2int_rn(v[i] * inv)));
+      b[i] = uint32_t(qi) & 0xffu;
+    }
+    packed.x = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+    packed.y = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
+  }
+  if (!live) return;
+  *reinterpret_cast<uint2*>(q + r * q_stride + gi * 128 + sub * 8) = packed;
+  if (sub == 0) sa[r * sa_stride + gi] = s;
+}
+
+// -------------------------------------------------------------------- combine
+// out[t, h] = sum_j in[t, j, h] in fp32 (j ascending), one bf16 rounding.
+__global__ void __launch_bounds__(256) moe_sum_kernel(
+    const uint16_t* __restrict__ in, int64_t in_st, int64_t in_sj, uint16_t* __restrict__ out,
+    int64_t out_st, int tokens, int top_k, int hidden8) {
+  const int64_t idx = int64_t(blockIdx.x) * 256 + threadIdx.x;
+  if (idx >= int64_t(tokens) * hidden8) return;
+  const int64_t t = idx / hidden8;
+  const int h = int(idx % hidden8) * 8;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int j = 0; j < top_k; ++j) {
+    const uint4 w = *reinterpret_cast<const uint4*>(in + t * in_st + j * in_sj + h);
+    const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      acc[2 * i] += bf16_lo(ws[i]);
+      acc[2 * i + 1] += bf16_hi(ws[i]);
+    }
+  }
+  uint4 o;
+  o.x = pack_bf16x2(acc[0], acc[1]);
+  o.y = pack_bf16x2(acc[2], acc[3]);
+  o.z = pack_bf16x2(acc[4], acc[5]);
+  o.w = pack_bf16x2(acc[6], acc[7]);
+  *reinterpret_cast<uint4*>(out + t * out_st + h) = o;
+}
+
+}  // namespace
+}  // namespace strix
+
+using namespace strix;
+
+extern "C" int strix_moe_topk_softmax(const float* logits, int32_t* topk_ids, float* topk_weights,
+                                      int64_t tokens, int64_t experts, int64_t top_k,
+                                      int64_t logits_stride, int renormalize,
+                                      strix_stream_t stream) {
+  STRIX_CHECK(tokens >= 0 && experts >= 1 && experts <= 1024, "experts must be in 1..1024");
+  STRIX_CHECK(top_k >= 1 && top_k <= 32 && top_k <= experts, "top_k must be in 1..min(32, experts)");
+  STRIX_CHECK(logits_stride >= experts, "logits rows must not overlap");
+  if (tokens == 0) return STRIX_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = unsigned((tokens + 3) / 4);
+#define STRIX_TOPK(V)                                                                        \
+  topk_softmax_kernel<V><<<grid, 128, 0, st>>>(logits, logits_stride, topk_ids, topk_weights, \
+                                               int(tokens), int(experts), int(top_k), renormalize)
+  if (experts <= 32) STRIX_TOPK(1);
+  else if (experts <= 64) STRIX_TOPK(2);
+  else if (experts <= 128) STRIX_TOPK(4);
+  else if (experts <= 256) STRIX_TOPK(8);
+  else if (experts <= 512) STRIX_TOPK(16);
+  else STRIX_TOPK(32);
+#undef STRIX_TOPK
+  return launch_status("moe_topk_softmax");
+}
+
+extern "C" int64_t strix_moe_align_capacity(int64_t numel, int64_t experts, int64_t block_m) {
+  if (numel < 0 || experts < 1 || block_m < 1) return -1;
+  // every routed expert wastes at most block_m - 1 slots; at most min(numel, experts) are routed
+  const int64_t routed = numel < experts ? numel : experts;
+  const int64_t cap = numel + routed * (block_m - 1);
+  return (cap + block_m - 1) / block_m * block_m;
+}
+
+extern "C" int strix_moe_align(const int32_t* topk_ids, int32_t* sorted_ids, int32_t* expert_ids,
+                               int32_t* num_post_padded, int64_t numel, int64_t experts,
+                               int64_t block_m, int64_t sorted_capacity, int64_t expert_capacity,
+                               strix_stream_t stream) {
+  STRIX_CHECK(numel >= 0 && numel < (int64_t(1) << 30), "too many routed slots");
+  STRIX_CHECK(experts >= 1 && experts <= 8192, "experts must be in 1..8192");
+  STRIX_CHECK(block_m >= 1 && block_m <= 1024, "block_m must be in 1..1024");
+  STRIX_CHECK(sorted_capacity >= strix_moe_align_capacity(numel, experts, block_m),
+              "sorted_ids too short: needs strix_moe_align_capacity() entries");
+  STRIX_CHECK(expert_capacity * block_m >= sorted_capacity,
+              "expert_ids too short for block_m %lld", (long long)block_m);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  moe_align_kernel<<<unsigned(experts + 1), kAlignThreads, size_t(experts) * sizeof(int), st>>>(
+      topk_ids, sorted_ids, expert_ids, num_post_padded, int(numel), int(experts), int(block_m),
+      int(sorted_capacity), int(expert_capacity));
+  return launch_status("moe_align");
+}
+
+static int act_quant_common(const void* x, void* q, float* sa, int64_t rows, int64_t k,
+                            int64_t x_stride, int64_t q_stride, int64_t sa_stride, int x_is_f16,
+                            bool fp8, strix_stream_t stream) {
+  STRIX_CHECK(rows >= 0 && k > 0 && k % 128 == 0, "K must be a multiple of 128");
+  STRIX_CHECK(x_stride % 8 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 &&
+                  q_stride % 8 == 0 && reinterpret_cast<uintptr_t>(q) % 8 == 0,
+              "16-byte aligned rows required");
+  STRIX_CHECK(sa_stride >= k / 128, "sa must be [rows, K / 128]");
+  if (rows == 0) return STRIX_OK;
+  const int groups = int(k / 128);
+  const int64_t teams = rows * groups;
+  const unsigned grid = unsigned((teams * 16 + 255) / 256);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  auto xp = static_cast<const uint16_t*>(x);
+  auto qp = static_cast<uint8_t*>(q);
+  if (fp8) {
+    if (x_is_f16) act_quant_kernel<true, true><<<grid, 256, 0, st>>>(xp, x_stride, qp, q_stride, sa, sa_stride, rows, groups);
+    else act_quant_kernel<true, false><<<grid, 256, 0, st>>>(xp, x_stride, qp, q_stride, sa, sa_stride, rows, groups);
+  } else {
+    if (x_is_f16) act_quant_kernel<false, true><<<grid, 256, 0, st>>>(xp, x_stride, qp, q_stride, sa, sa_stride, rows, groups);
+    else act_quant_kernel<false, false><<<grid, 256, 0, st>>>(xp, x_stride, qp, q_stride, sa, sa_stride, rows, groups);
+  }
+  return launch_status("moe_act_quant");
+}
+
+extern "C" int strix_moe_act_quant_i8(const void* x, void* q, float* sa, int64_t rows, int64_t k,
+                                      int64_t x_stride, int64_t q_stride, int64_t sa_stride,
+                                      int x_is_f16, strix_stream_t stream) {
+  return act_quant_common(x, q, sa, rows, k, x_stride, q_stride, sa_stride, x_is_f16, false, stream);
+}
+
+extern "C" int strix_moe_act_quant_fp8(const void* x, void* q, float* sa, int64_t rows, int64_t k,
+                                       int64_t x_stride, int64_t q_stride, int64_t sa_stride,
+                                       int x_is_f16, strix_stream_t stream) {
+  return act_quant_common(x, q, sa, rows, k, x_stride, q_stride, sa_stride, x_is_f16, true, stream);
+}
+
+extern "C" int strix_moe_sum(const void* in, void* out, int64_t tokens, int64_t top_k,
+                             int64_t hidden, int64_t in_st, int64_t in_sj, int64_t out_st,
+                             strix_stream_t stream) {
+  STRIX_CHECK(tokens >= 0 && top_k >= 1 && hidden > 0 && hidden % 8 == 0,
+              "hidden must be a multiple of 8");
+  STRIX_CHECK(in_st % 8 == 0 && in_sj % 8 == 0 && out_st % 8 == 0 &&
+                  reinterpret_cast<uintptr_t>(in) % 16 == 0 &&
+                  reinterpret_cast<uintptr_t>(out) % 16 == 0,
+              "16-byte aligned rows required");
+  if (tokens == 0) return STRIX_OK;
+  const int64_t work = tokens * (hidden / 8);
+  moe_sum_kernel<<<unsigned((work + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint16_t*>(in), in_st, in_sj, static_cast<uint16_t*>(out), out_st,
+      int(tokens), int(top_k), int(hidden / 8));
+  return launch_status("moe_sum");
+}

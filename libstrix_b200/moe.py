@@ -1,0 +1,90 @@
+"""MoE layer built from the strix ops: route -> permute -> quantise -> gate-up
+GEMM with the fused gate -> quantise -> down GEMM x routing weight -> combine.
+
+The sequence is the reference's StrixFp8Experts.apply
+(python/strix_vllm/moe.py:905-1014) with vLLM's router, moe_align_block_size
+and moe_sum replaced by this library's kernels, and with the W8A8 activation
+form of the benchmark configuration (e4m3 per token per 128).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+
+def pick_block_m(tokens: int, top_k: int, experts: int) -> int:
+    """Rows per m-block: the smallest of 16/32/64 that holds an average expert's
+    share twice over, so most experts stream their weights exactly once."""
+    per_expert = tokens * top_k / max(experts, 1)
+    for bm in (16, 32):
+        if per_expert * 2 <= bm:
+            return bm
+    return 64
+
+
+def route(logits: torch.Tensor, top_k: int, renormalize: bool = True):
+    """(topk_weights fp32 [T, k], topk_ids int32 [T, k]) by softmax -> top-k -> renormalise."""
+    t = logits.size(0)
+    weights = torch.empty(t, top_k, dtype=torch.float32, device=logits.device)
+    ids = torch.empty(t, top_k, dtype=torch.int32, device=logits.device)
+    torch.ops.strix.moe_topk_softmax(weights, ids, logits, renormalize)
+    return weights, ids
+
+
+def align(topk_ids: torch.Tensor, block_m: int, num_experts: int):
+    """(sorted_ids, expert_ids, num_post_padded) with the moe_align_block_size contract."""
+    lib = _lib.load()
+    cap = lib.strix_moe_align_capacity(topk_ids.numel(), num_experts, block_m)
+    sorted_ids = torch.empty(cap, dtype=torch.int32, device=topk_ids.device)
+    expert_ids = torch.empty(cap // block_m, dtype=torch.int32, device=topk_ids.device)
+    num_post = torch.empty(1, dtype=torch.int32, device=topk_ids.device)
+    torch.ops.strix.moe_align_block_size(topk_ids, num_experts, block_m, sorted_ids, expert_ids,
+                                         num_post)
+    return sorted_ids, expert_ids, num_post
+
+
+def act_quant_fp8(x: torch.Tensor):
+    q = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
+    sa = torch.empty(x.size(0), x.size(1) // 128, dtype=torch.float32, device=x.device)
+    torch.ops.strix.moe_act_quant_fp8(x, q, sa)
+    return q, sa
+
+
+class Fp8MoeWorkspace:
+    """Intermediate buffers of one layer call, reusable across calls of one shape."""
+
+    def __init__(self, tokens, top_k, hidden, inter, device):
+        slots = tokens * top_k
+        bf16, f32, f8 = torch.bfloat16, torch.float32, torch.float8_e4m3fn
+        self.xq = torch.empty(tokens, hidden, dtype=f8, device=device)
+        self.xs = torch.empty(tokens, hidden // 128, dtype=f32, device=device)
+        self.act = torch.empty(slots, inter, dtype=bf16, device=device)
+        self.aq = torch.empty(slots, inter, dtype=f8, device=device)
+        self.as_ = torch.empty(slots, inter // 128, dtype=f32, device=device)
+        self.y = torch.empty(slots, hidden, dtype=bf16, device=device)
+        self.out = torch.empty(tokens, hidden, dtype=bf16, device=device)
+
+
+def fused_moe_fp8_w8a8(x, logits, w13, w13_scale, w2, w2_scale, top_k, block_m=None, ws=None):
+    """One MoE layer, FP8 W8A8 block-scaled. x bf16 [T, H]; logits fp32 [T, E];
+    w13 e4m3 [E, 2I, H] + fp32 scales [E, 2I/128, H/128]; w2 e4m3 [E, H, I] +
+    scales [E, H/128, I/128]. Returns bf16 [T, H]. Seven kernel launches, no
+    host synchronisation."""
+    t, h = x.shape
+    e, n13, _ = w13.shape
+    inter = n13 // 2
+    bm = block_m or pick_block_m(t, top_k, e)
+    ws = ws or Fp8MoeWorkspace(t, top_k, h, inter, x.device)
+    weights, ids = route(logits, top_k)
+    sorted_ids, expert_ids, num_post = align(ids, bm, e)
+    ops = torch.ops.strix
+    ops.moe_act_quant_fp8(x, ws.xq, ws.xs)
+    ops.moe_gemm_fp8_w8a8(ws.act, ws.xq, ws.xs, w13, w13_scale, sorted_ids, expert_ids, num_post,
+                          None, top_k, bm, 64, True, "silu")
+    ops.moe_act_quant_fp8(ws.act, ws.aq, ws.as_)
+    ops.moe_gemm_fp8_w8a8(ws.y, ws.aq, ws.as_, w2, w2_scale, sorted_ids, expert_ids, num_post,
+                          weights.view(-1), 1, bm, 64, False, "silu")
+    ops.moe_sum(ws.y.view(t, top_k, h), ws.out)
+    return ws.out

@@ -119,7 +119,67 @@ def _decode_row(head_dim: int, gqa: int, doc: str) -> Kernel:
     )
 
 
+_GATES = ("silu", "gelu_tanh")
+_STREAM_SPEC = {
+    "tile": "16 weight rows per warp x 8-token tiles, K blocks of 128",
+    "staging": "cp.async ring, 4 stages",
+    "bound": "hbm (weight stream) at small token counts",
+}
+
+
+def _moe_row(name: str, op: str, doc: str, **constraints: Any) -> Kernel:
+    base = {"silu_mul": (True, False), "activation": _GATES}
+    return Kernel(name, op, doc, {**base, **constraints}, dict(_STREAM_SPEC))
+
+
+_MOE_ROWS = [
+    _moe_row(
+        "moe_gemm_fp8_w8a8", "moe_gemm_fp8",
+        "e4m3 experts x e4m3 activations (one fp32 scale per token and 128-wide K "
+        "group): the MMA runs on the raw bytes, block or channel weight scales and "
+        "the activation scale fold into the fp32 partial sums per K block",
+        dtype="bf16", activation_dtype="fp8_e4m3", weight_dtype="fp8_e4m3", weight_bits=8,
+        quant="fp8", group_size=(0, 128),
+    ),
+    _moe_row(
+        "moe_gemm_fp8", "moe_gemm_fp8",
+        "e4m3 experts x bf16 activations; weights widened exactly in registers, "
+        "scales applied to fp32 sums",
+        dtype="bf16", weight_dtype="fp8_e4m3", weight_bits=8, quant="fp8", group_size=(0, 128),
+    ),
+    _moe_row(
+        "moe_gemm_fp8_raw", "moe_gemm_fp8",
+        "e4m3 experts x fp16 activations (fp16 out under the fused gate, bf16 otherwise)",
+        dtype="fp16", weight_dtype="fp8_e4m3", weight_bits=8, quant="fp8", group_size=(0, 128),
+    ),
+    _moe_row(
+        "moe_gemm_w8a16", "moe_gemm_w8a16",
+        "int8 experts with one scale per output channel x bf16 activations",
+        dtype="bf16", weight_dtype="int8", weight_bits=8, quant="int8", group_size=(0,),
+    ),
+    _moe_row(
+        "moe_gemm_bf16", "moe_gemm",
+        "bf16 experts x bf16 activations, fused gate epilogue",
+        dtype="bf16", weight_dtype="bf16", quant=None,
+    ),
+    Kernel("moe_act_quant_i8", "moe_act_quant_i8",
+           "int8 activations per (row, 128 group): s = amax / 127, q = rint(x / s)",
+           {"dtype": ("bf16", "fp16"), "activation_dtype": "int8", "group_size": 128}),
+    Kernel("moe_act_quant_fp8", "moe_act_quant_fp8",
+           "e4m3 activations per (row, 128 group): s = amax / 448",
+           {"dtype": ("bf16", "fp16"), "activation_dtype": "fp8_e4m3", "group_size": 128}),
+    Kernel("moe_topk_softmax", "moe_router",
+           "fp32 softmax -> top-k (ties to the lower index) -> renormalise, one warp per token",
+           {"experts": Range(1, 1024), "top_k": Range(1, 32), "dtype": "fp32"}),
+    Kernel("moe_align_block_size", "moe_align",
+           "stable per-expert permutation padded to block_m; one CTA per expert, single launch",
+           {"experts": Range(1, 8192), "block_m": Range(1, 1024)}),
+    Kernel("moe_sum", "moe_sum", "fp32 sum of the top-k expert rows, one bf16 rounding",
+           {"dtype": "bf16"}),
+]
+
 KERNELS: list[Kernel] = [
+    *_MOE_ROWS,
     # ------------------------------------------------------------ attention
     _decode_row(
         128, 8,

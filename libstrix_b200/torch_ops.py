@@ -115,3 +115,191 @@ def attn_decode_bf16(
             *(ks.stride() if q8 else (0, 0, 0)), *(vs.stride() if q8 else (0, 0, 0)),
             float(scale), num_splits, window_left, int(q8), _stream(),
         )
+
+
+# ----------------------------------------------------------------------- MoE
+
+_W_E4M3, _W_INT8, _W_BF16 = 0, 1, 2
+_A_BF16, _A_F16, _A_E4M3 = 0, 1, 2
+_S_NONE, _S_CHANNEL, _S_BLOCK = 0, 1, 2
+_SCALE_DTYPES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+_ACTS = {"silu": 1, "gelu_tanh": 2}
+
+
+def _moe_gemm(c, a, w, scales, act_scales, sorted_ids, expert_ids, num_post_padded, topk_weights,
+              top_k, block_m, block_n, silu_mul, activation, *, wfmt, afmt, name):
+    """Shared host side of the moe_gemm_* ops; the checks (and their messages)
+    follow moe_gemm_impl, csrc/moe/moe_gemm_w8a16.hip:444-514 of the reference.
+    block_n is the caller's tile hint and is only validated."""
+    a_dtype = {_A_BF16: torch.bfloat16, _A_F16: torch.float16, _A_E4M3: torch.float8_e4m3fn}[afmt]
+    w_dtype = {_W_E4M3: torch.float8_e4m3fn, _W_INT8: torch.int8, _W_BF16: torch.bfloat16}[wfmt]
+    c_f16 = afmt == _A_F16 and silu_mul and c.dtype != torch.bfloat16
+    c_dtype = torch.float16 if c_f16 else torch.bfloat16
+    _check(a.dtype == a_dtype and w.dtype == w_dtype and c.dtype == c_dtype
+           and (scales is None or scales.dtype in _SCALE_DTYPES),
+           f"{name}: a {a_dtype}, c {c_dtype}; scales bf16, fp16 or fp32; w {w_dtype}")
+    _check(a.dim() == 2 and w.dim() == 3 and c.dim() == 2, "bad ranks")
+    e, n, k = w.shape
+    _check(a.size(1) == k and c.size(1) == (n // 2 if silu_mul else n), "shape mismatch")
+    scale_kind, s_se, s_sn, s_dtype = _S_NONE, 0, 0, 0
+    if wfmt != _W_BF16:
+        _check(scales is not None and scales.dim() in (2, 3), "scales must be [E, N]")
+        block = wfmt == _W_E4M3 and scales.dim() == 3 and scales.size(1) != n
+        if block:
+            _check(scales.dtype == torch.float32 and n % 128 == 0 and k % 128 == 0
+                   and tuple(scales.shape) == (e, n // 128, k // 128),
+                   "block scales must be fp32 [E, N/128, K/128]")
+            scale_kind, s_sn = _S_BLOCK, scales.stride(1)
+        else:
+            _check(scales.size(0) == e and scales.size(1) == n
+                   and (scales.dim() == 2 or scales.size(2) == 1),
+                   "scales must be [E, N] or [E, N, 1]")
+            scale_kind = _S_CHANNEL
+            _check(scales.stride(1) == 1 or scales.dim() == 3, "last dims must be contiguous")
+        _check(scales.stride(-1) == 1, "last dims must be contiguous")
+        s_se, s_dtype = scales.stride(0), _SCALE_DTYPES[scales.dtype]
+    _check(a.stride(1) == 1 and w.stride(2) == 1 and c.stride(1) == 1,
+           "last dims must be contiguous")
+    _check(not silu_mul or (n % 2 == 0 and topk_weights is None),
+           "silu_mul needs even N and no topk weights")
+    _check(activation in _ACTS, f"activation must be silu or gelu_tanh, got {activation}")
+    _check(k % 64 == 0 and n % block_n == 0, "K % 64 and N % block_n")
+    _check(sorted_ids.dtype == torch.int32 and expert_ids.dtype == torch.int32
+           and num_post_padded.dtype == torch.int32, "routing tensors must be int32")
+    _check(expert_ids.numel() * block_m >= sorted_ids.numel(),
+           f"expert_ids too short for block_m {block_m}")
+    if topk_weights is not None:
+        _check(topk_weights.dtype == torch.float32 and topk_weights.is_contiguous()
+               and topk_weights.numel() == c.size(0),
+               "topk_weights must be contiguous fp32 [num_valid]")
+    sa_stride = 0
+    if afmt == _A_E4M3:
+        _check(act_scales is not None and act_scales.dtype == torch.float32
+               and act_scales.dim() == 2 and act_scales.size(0) == a.size(0)
+               and act_scales.size(1) == k // 128 and act_scales.stride(1) == 1,
+               "activation scales must be fp32 [rows, K/128]")
+        sa_stride = act_scales.stride(0)
+    with torch.cuda.device(c.device):
+        _lib.call(
+            "strix_moe_gemm",
+            c.data_ptr(), a.data_ptr(), w.data_ptr(), _ptr(scales), _ptr(act_scales),
+            sorted_ids.data_ptr(), expert_ids.data_ptr(), num_post_padded.data_ptr(),
+            _ptr(topk_weights), c.size(0), a.size(0), e, n, k, a.stride(0), c.stride(0),
+            w.stride(0), w.stride(1), s_se, s_sn, sa_stride, sorted_ids.numel(),
+            expert_ids.numel(), top_k, block_m, wfmt, afmt, scale_kind, s_dtype,
+            _ACTS[activation] if silu_mul else 0, int(c_f16), _stream(),
+        )
+
+
+_MOE_TAIL = ("Tensor sorted_ids, Tensor expert_ids, Tensor num_post_padded, "
+             "Tensor? topk_weights, int top_k, int block_m, int block_n, "
+             "bool silu_mul=False, str activation='silu') -> ()")
+
+
+@_define("moe_gemm_bf16(Tensor(a!) c, Tensor a, Tensor b, " + _MOE_TAIL)
+def moe_gemm_bf16(c, a, b, sorted_ids, expert_ids, num_post_padded, topk_weights, top_k,
+                  block_m, block_n, silu_mul=False, activation="silu"):
+    _moe_gemm(c, a, b, None, None, sorted_ids, expert_ids, num_post_padded, topk_weights, top_k,
+              block_m, block_n, silu_mul, activation, wfmt=_W_BF16, afmt=_A_BF16,
+              name="moe_gemm_bf16")
+
+
+@_define("moe_gemm_w8a16(Tensor(a!) c, Tensor a, Tensor b, Tensor scales, " + _MOE_TAIL)
+def moe_gemm_w8a16(c, a, b, scales, sorted_ids, expert_ids, num_post_padded, topk_weights, top_k,
+                   block_m, block_n, silu_mul=False, activation="silu"):
+    _moe_gemm(c, a, b, scales, None, sorted_ids, expert_ids, num_post_padded, topk_weights, top_k,
+              block_m, block_n, silu_mul, activation, wfmt=_W_INT8, afmt=_A_BF16,
+              name="moe_gemm_w8a16/fp8")
+
+
+@_define("moe_gemm_fp8(Tensor(a!) c, Tensor a, Tensor b, Tensor scales, " + _MOE_TAIL)
+def moe_gemm_fp8(c, a, b, scales, sorted_ids, expert_ids, num_post_padded, topk_weights, top_k,
+                 block_m, block_n, silu_mul=False, activation="silu"):
+    _moe_gemm(c, a, b, scales, None, sorted_ids, expert_ids, num_post_padded, topk_weights, top_k,
+              block_m, block_n, silu_mul, activation, wfmt=_W_E4M3, afmt=_A_BF16,
+              name="moe_gemm_w8a16/fp8")
+
+
+@_define("moe_gemm_fp8_raw(Tensor(a!) c, Tensor a, Tensor b, Tensor scales, " + _MOE_TAIL)
+def moe_gemm_fp8_raw(c, a, b, scales, sorted_ids, expert_ids, num_post_padded, topk_weights,
+                     top_k, block_m, block_n, silu_mul=False, activation="silu"):
+    _moe_gemm(c, a, b, scales, None, sorted_ids, expert_ids, num_post_padded, topk_weights, top_k,
+              block_m, block_n, silu_mul, activation, wfmt=_W_E4M3, afmt=_A_F16,
+              name="moe_gemm_w8a16/fp8")
+
+
+# Not in the reference: the W8A8 form of the FP8 experts (e4m3 activations with
+# one fp32 scale per token and 128-wide K group), modelled on moe_gemm_w4a8's
+# argument order (csrc/torch_ops.cpp:214-217).
+@_define("moe_gemm_fp8_w8a8(Tensor(a!) c, Tensor qa, Tensor sa, Tensor b, Tensor scales, "
+         + _MOE_TAIL)
+def moe_gemm_fp8_w8a8(c, qa, sa, b, scales, sorted_ids, expert_ids, num_post_padded, topk_weights,
+                      top_k, block_m, block_n, silu_mul=False, activation="silu"):
+    _moe_gemm(c, qa, b, scales, sa, sorted_ids, expert_ids, num_post_padded, topk_weights, top_k,
+              block_m, block_n, silu_mul, activation, wfmt=_W_E4M3, afmt=_A_E4M3,
+              name="moe_gemm_fp8_w8a8")
+
+
+def _act_quant(entry, x, q, sa, q_dtype):
+    _check(x.dim() == 2 and x.dtype in (torch.bfloat16, torch.float16) and x.stride(1) == 1,
+           "x must be bf16 or fp16 [rows, K]")
+    _check(q.dtype == q_dtype and q.shape == x.shape and q.stride(1) == 1,
+           f"q must be {q_dtype} [rows, K]")
+    _check(x.size(1) % 128 == 0, "K must be a multiple of 128")
+    _check(sa.dtype == torch.float32 and tuple(sa.shape) == (x.size(0), x.size(1) // 128)
+           and sa.stride(1) == 1, "sa must be fp32 [rows, K / 128]")
+    with torch.cuda.device(x.device):
+        _lib.call(entry, x.data_ptr(), q.data_ptr(), sa.data_ptr(), x.size(0), x.size(1),
+                  x.stride(0), q.stride(0), sa.stride(0), int(x.dtype == torch.float16), _stream())
+
+
+@_define("moe_act_quant_i8(Tensor x, Tensor(a!) q, Tensor(b!) sa) -> ()")
+def moe_act_quant_i8(x, q, sa):
+    _act_quant("strix_moe_act_quant_i8", x, q, sa, torch.int8)
+
+
+@_define("moe_act_quant_fp8(Tensor x, Tensor(a!) q, Tensor(b!) sa) -> ()")
+def moe_act_quant_fp8(x, q, sa):
+    _act_quant("strix_moe_act_quant_fp8", x, q, sa, torch.float8_e4m3fn)
+
+
+@_define("moe_topk_softmax(Tensor(a!) topk_weights, Tensor(b!) topk_ids, Tensor gating_output, "
+         "bool renormalize=True) -> ()")
+def moe_topk_softmax(topk_weights, topk_ids, gating_output, renormalize=True):
+    _check(gating_output.dim() == 2 and gating_output.dtype == torch.float32
+           and gating_output.stride(1) == 1, "gating_output must be fp32 [tokens, experts]")
+    t, k = topk_ids.shape
+    _check(topk_ids.dtype == torch.int32 and topk_ids.is_contiguous()
+           and topk_weights.dtype == torch.float32 and topk_weights.is_contiguous()
+           and topk_weights.shape == topk_ids.shape and t == gating_output.size(0),
+           "topk_ids int32 and topk_weights fp32, contiguous [tokens, top_k]")
+    with torch.cuda.device(gating_output.device):
+        _lib.call("strix_moe_topk_softmax", gating_output.data_ptr(), topk_ids.data_ptr(),
+                  topk_weights.data_ptr(), t, gating_output.size(1), k, gating_output.stride(0),
+                  int(renormalize), _stream())
+
+
+@_define("moe_align_block_size(Tensor topk_ids, int num_experts, int block_size, "
+         "Tensor(a!) sorted_token_ids, Tensor(b!) experts_ids, Tensor(c!) num_tokens_post_pad) -> ()")
+def moe_align_block_size(topk_ids, num_experts, block_size, sorted_token_ids, experts_ids,
+                         num_tokens_post_pad):
+    _check(topk_ids.dtype == torch.int32 and topk_ids.is_contiguous()
+           and sorted_token_ids.dtype == torch.int32 and sorted_token_ids.is_contiguous()
+           and experts_ids.dtype == torch.int32 and experts_ids.is_contiguous()
+           and num_tokens_post_pad.dtype == torch.int32, "routing tensors must be int32")
+    with torch.cuda.device(topk_ids.device):
+        _lib.call("strix_moe_align", topk_ids.data_ptr(), sorted_token_ids.data_ptr(),
+                  experts_ids.data_ptr(), num_tokens_post_pad.data_ptr(), topk_ids.numel(),
+                  num_experts, block_size, sorted_token_ids.numel(), experts_ids.numel(), _stream())
+
+
+@_define("moe_sum(Tensor input, Tensor(a!) output) -> ()")
+def moe_sum(input, output):
+    _check(input.dim() == 3 and input.dtype == torch.bfloat16 and input.stride(2) == 1
+           and output.dtype == torch.bfloat16 and output.stride(1) == 1
+           and tuple(output.shape) == (input.size(0), input.size(2)),
+           "input bf16 [tokens, top_k, hidden], output bf16 [tokens, hidden]")
+    with torch.cuda.device(input.device):
+        _lib.call("strix_moe_sum", input.data_ptr(), output.data_ptr(), input.size(0),
+                  input.size(1), input.size(2), input.stride(0), input.stride(1),
+                  output.stride(0), _stream())

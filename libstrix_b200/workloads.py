@@ -92,3 +92,67 @@ def decode_batch(
     q = torch.randn(batch, hq, head_dim, generator=gen, device=device).bfloat16()
     return DecodeBatch(q, key_cache, value_cache, k_scale, v_scale,
                        lens.to(torch.int32).to(device), table.to(device), head_dim ** -0.5)
+
+
+@dataclass
+class MoeFp8Layer:
+    """One MoE layer in the FP8 W8A8 block-scaled form (benchmark config 1)."""
+
+    x: torch.Tensor          # bf16 [T, H]
+    logits: torch.Tensor     # fp32 [T, E]
+    w13: torch.Tensor        # e4m3 [E, 2I, H]   rows [gate; up]
+    w13_scale: torch.Tensor  # fp32 [E, 2I/128, H/128]
+    w2: torch.Tensor         # e4m3 [E, H, I]
+    w2_scale: torch.Tensor   # fp32 [E, H/128, I/128]
+    top_k: int
+
+    def to(self, device) -> "MoeFp8Layer":
+        return MoeFp8Layer(*[
+            v.to(device) if isinstance(v, torch.Tensor) else v for v in self.__dict__.values()
+        ])
+
+    @property
+    def flops(self) -> int:
+        t, h = self.x.shape
+        n13 = self.w13.size(1)
+        return 2 * t * self.top_k * (n13 * h + h * (n13 // 2))
+
+    @property
+    def weight_bytes(self) -> int:
+        return self.w13.numel() + self.w2.numel() + 4 * (self.w13_scale.numel() + self.w2_scale.numel())
+
+
+def quantize_fp8_block(w: torch.Tensor):
+    """fp32 [E, N, K] -> (e4m3, fp32 scales [E, N/128, K/128]) with s = amax / 448 per block."""
+    e, n, k = w.shape
+    blocks = w.view(e, n // 128, 128, k // 128, 128)
+    s = blocks.abs().amax(dim=(2, 4)).clamp_min(1e-12) / 448.0
+    q = (blocks / s[:, :, None, :, None]).reshape(e, n, k).to(torch.float8_e4m3fn)
+    return q, s.contiguous()
+
+
+def moe_fp8_layer(tokens=256, hidden=2048, experts=128, top_k=8, inter=768, seed=0,
+                  device="cpu", zipf_bias: float | None = None) -> MoeFp8Layer:
+    """Activations bf16 ~ N(0,1); router logits fp32 ~ N(0,1) (plus a Zipf(1.1)
+    per-expert log-bias when `zipf_bias` is given); weights ~ N(0, 0.02)
+    quantised to e4m3 with fp32 128x128 block scales."""
+    gen = torch.Generator(device=device).manual_seed(seed)
+    x = torch.randn(tokens, hidden, generator=gen, device=device).bfloat16()
+    logits = torch.randn(tokens, experts, generator=gen, device=device)
+    if zipf_bias is not None:
+        ranks = torch.arange(1, experts + 1, device=device, dtype=torch.float32)
+        bias = torch.log(ranks.pow(-zipf_bias) / ranks.pow(-zipf_bias).sum())
+        perm = torch.randperm(experts, generator=torch.Generator().manual_seed(seed)).to(device)
+        logits = logits + bias[perm]
+
+    def weights(n, k):
+        q = torch.empty(experts, n, k, dtype=torch.float8_e4m3fn, device=device)
+        s = torch.empty(experts, n // 128, k // 128, dtype=torch.float32, device=device)
+        for e0 in range(0, experts, 16):  # bounded fp32 temporaries
+            w = torch.randn(min(16, experts - e0), n, k, generator=gen, device=device) * 0.02
+            q[e0:e0 + 16], s[e0:e0 + 16] = quantize_fp8_block(w)
+        return q, s
+
+    w13, s13 = weights(2 * inter, hidden)
+    w2, s2 = weights(hidden, inter)
+    return MoeFp8Layer(x, logits, w13, s13, w2, s2, top_k)

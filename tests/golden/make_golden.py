@@ -73,7 +73,50 @@ def golden_attn_decode() -> None:
     torch.save(cases, OUT / "attn_decode.pt")
 
 
-GENERATORS = {"attn_decode": golden_attn_decode}
+def golden_moe() -> None:
+    """align() and reference() of tests/test_moe_gemm.py:9-42, make_weights() of
+    tests/test_moe_fp8.py:17-29 and tests/test_moe_fp8_raw.py:17-28 (with the
+    module constant E shrunk so the fixture stays small), and a full
+    w13 -> gate -> w2 chain evaluated by the reference's functions."""
+    import torch.nn.functional as F
+
+    ref = load_reference_test("test_moe_gemm")
+    sys.modules["test_moe_w8a16"] = load_reference_test("test_moe_w8a16")
+    fp8 = load_reference_test("test_moe_fp8")
+    raw = load_reference_test("test_moe_fp8_raw")
+    out = {"align": [], "grouped": [], "fp8": []}
+    g = torch.Generator().manual_seed(0)
+    for tokens, top_k, e, block_m in [(1, 2, 4, 16), (5, 3, 8, 4), (37, 4, 16, 16), (64, 8, 128, 64)]:
+        ids = torch.stack([torch.randperm(e, generator=g)[:top_k] for _ in range(tokens)])
+        s, x, n = ref.align(ids, block_m, e)
+        out["align"].append({"topk_ids": ids, "block_m": block_m, "experts": e,
+                             "sorted_ids": s, "expert_ids": x, "num_post": n})
+    for tokens, top_k, e, n, k in [(5, 2, 4, 64, 128), (9, 1, 3, 32, 64)]:
+        ids = torch.stack([torch.randperm(e, generator=g)[:top_k] for _ in range(tokens)])
+        a = torch.randn(tokens * (1 if top_k > 1 else 1), k, generator=g).bfloat16()
+        b = (torch.randn(e, n, k, generator=g) / k ** 0.5).bfloat16()
+        wts = torch.rand(tokens, top_k, generator=g)
+        a_in = a if top_k > 1 else torch.randn(tokens, k, generator=g).bfloat16()
+        out["grouped"].append({"a": a_in, "b": b, "topk_ids": ids, "top_k": top_k, "weights": wts,
+                               "out": ref.reference(a_in, b, ids, top_k, wts),
+                               "out_unweighted": ref.reference(a_in, b, ids, top_k, None)})
+    for mod, name in ((fp8, "plain"), (raw, "raw")):
+        mod.E = 2
+        for scheme in ("block", "channel"):
+            w, scales, deq = mod.make_weights(256, 128, scheme)
+            ids = torch.stack([torch.randperm(2, generator=g)[:2] for _ in range(6)])
+            a = torch.randn(6, 128, generator=g).to(torch.bfloat16 if name == "plain" else torch.float16)
+            h = (fp8 if name == "plain" else raw).reference(a, deq, ids, 2, None) \
+                if name == "raw" else ref.reference(a, deq, ids, 2, None)
+            gate, up = h[:, :128], h[:, 128:]
+            out["fp8"].append({"kind": name, "scheme": scheme, "w": w.view(torch.uint8),
+                               "scales": scales, "deq": deq, "a": a, "topk_ids": ids,
+                               "h": h, "silu": F.silu(gate) * up,
+                               "gelu": F.gelu(gate, approximate="tanh") * up})
+    torch.save(out, OUT / "moe.pt")
+
+
+GENERATORS = {"attn_decode": golden_attn_decode, "moe": golden_moe}
 
 if __name__ == "__main__":
     wanted = sys.argv[1:] or list(GENERATORS)

@@ -36,3 +36,56 @@ def test_build_paged_kv_tables_are_a_permutation():
     used = torch.cat([table[0, :3], table[1, :1]]).tolist()
     assert len(set(used)) == len(used) and max(used) < kc.size(0)
     assert kc.shape == (kc.size(0), 16, 2, 64) and kc.stride(-1) == 1
+
+
+def test_moe_oracle_matches_reference_outputs():
+    from oracle import moe as M
+
+    gold = torch.load(GOLDEN / "moe.pt")
+    for c in gold["align"]:
+        s, x, n = M.align(c["topk_ids"], c["block_m"], c["experts"])
+        assert torch.equal(s, c["sorted_ids"]) and torch.equal(x, c["expert_ids"])
+        assert torch.equal(n, c["num_post"])
+    for c in gold["grouped"]:
+        out = M.grouped_reference(c["a"], c["b"], c["topk_ids"], c["top_k"], c["weights"])
+        torch.testing.assert_close(out, c["out"], rtol=0, atol=0)
+        out = M.grouped_reference(c["a"], c["b"], c["topk_ids"], c["top_k"])
+        torch.testing.assert_close(out, c["out_unweighted"], rtol=0, atol=0)
+    for c in gold["fp8"]:
+        w, scales, deq = M.make_fp8_weights(2, 256, 128, c["scheme"], keep_fp32=c["kind"] == "raw")
+        assert torch.equal(w.view(torch.uint8), c["w"]) and torch.equal(scales, c["scales"])
+        assert torch.equal(deq, c["deq"])
+        h = M.grouped_reference(c["a"], deq, c["topk_ids"], 2)
+        torch.testing.assert_close(h, c["h"], rtol=0, atol=0)
+        torch.testing.assert_close(M.gate_mul(h, "silu"), c["silu"], rtol=0, atol=0)
+        torch.testing.assert_close(M.gate_mul(h, "gelu_tanh"), c["gelu"], rtol=0, atol=0)
+
+
+def test_act_quant_oracles():
+    from oracle import moe as M
+
+    torch.manual_seed(0)
+    x = (torch.randn(37, 640) * 3).bfloat16()
+    x[5, 128:256] = 0
+    q, s = M.act_quant_i8(x)
+    assert float(s[5, 1]) == 1.0 and int(q[5, 128:256].abs().max()) == 0
+    assert int(q.abs().max()) == 127
+    assert bool(((M.dequant_act(q, s) - x.float()).abs() <= s.repeat_interleave(128, -1) * 0.5 + 1e-6).all())
+    q8, s8 = M.act_quant_fp8(x)
+    assert q8.dtype == torch.float8_e4m3fn and float(s8[5, 1]) == 1.0
+    assert float(q8.float().abs().max()) == 448.0
+    rel = (M.dequant_act(q8, s8) - x.float()).abs() / x.float().abs().clamp_min(1e-3)
+    assert float(rel.max()) <= 2 ** -4 + 1e-6      # e4m3: 3 mantissa bits
+
+
+def test_router_oracle_properties():
+    from oracle import moe as M
+
+    torch.manual_seed(0)
+    logits = torch.randn(64, 128)
+    ids, w = M.router(logits, 8)
+    assert ids.dtype == torch.int32 and ids.shape == (64, 8)
+    torch.testing.assert_close(w.sum(-1), torch.ones(64))
+    # the chosen experts are the 8 largest logits of each row, in descending order
+    want = torch.sort(logits, dim=-1, descending=True).indices[:, :8]
+    assert torch.equal(ids.long(), want)
