@@ -162,6 +162,15 @@ int strix_moe_gemm(
 int strix_moe_sum(const void* in, void* out, int64_t tokens, int64_t top_k, int64_t hidden,
                   int64_t in_st, int64_t in_sj, int64_t out_st, strix_stream_t stream);
 
+/* Layout probe of the tcgen05 path: one CTA computes D[128, n] = A[128, k] *
+ * B[n, k]^T from row-major 8-bit operands (kind 0: int8 -> int32 D, bit-exact;
+ * kind 1: float8_e4m3fn -> fp32 D). Plays the role of the reference's
+ * _wmma_bf16_tile (csrc/testing/wmma_layout_test.hip:27, schema
+ * csrc/torch_ops.cpp:183). *status (device int32, zeroed by the caller) is set
+ * to 1 if a bounded wait inside the kernel ran out. */
+int strix_umma_tile(void* d, const void* a, const void* b, int32_t* status, int64_t n, int64_t k,
+                    int kind, strix_stream_t stream);
+
 /* strix_attn_decode_bf16 without a workspace argument, for callers that cannot
  * allocate device memory: a host loop that owns nothing but the input and
  * output buffers it was given, or a process whose device memory was budgeted

@@ -23,6 +23,8 @@
 // the raw bytes (e4m3 x e4m3 -> f32, s8 x s8 -> s32); forms with 16-bit
 // activations widen the weights exactly in registers and apply block scales to
 // the fp32 partial sums of each K block.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace strix {
@@ -53,6 +55,7 @@ struct MoeArgs {
   int top_k, K, N, block_m;
   int scale_kind, scale_dtype;  // dtype: 0 fp32, 1 bf16, 2 fp16
   int c_f16;
+  int tiles_per_cta;  // consecutive n-tiles one CTA streams
 };
 
 __device__ __forceinline__ float load_scale(const void* p, int64_t idx, int dtype) {
@@ -153,14 +156,47 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs
   const int g = lane >> 2, c = lane & 3;
   constexpr bool kGate = ACT != ACT_NONE;
   const int half_n = p.N / 2;
-  // weight rows of this warp: local row r < 8 -> row_lo + r, r >= 8 -> row_hi + r - 8
-  const int nb = (blockIdx.x * kWarps + warp) * (kGate ? 8 : 16);
-  const bool warp_live = nb < (kGate ? half_n : p.N);
-  const int row_lo = nb, row_hi = kGate ? half_n + nb : nb + 8;
+  // A CTA walks `tiles_per_cta` consecutive n-tiles of its m-block as ONE flat
+  // pipeline over (tile, K block). Weight rows of a warp in a tile: local row
+  // r < 8 -> row_lo + r, else row_hi + r - 8.
+  constexpr int kRowsPerWarp = kGate ? 8 : 16;
+  const int out_rows = kGate ? half_n : p.N;
+  const int n_tiles = (out_rows + kWarps * kRowsPerWarp - 1) / (kWarps * kRowsPerWarp);
+  const int tile0 = blockIdx.x * p.tiles_per_cta;
+  const int ntile = min(p.tiles_per_cta, n_tiles - tile0);
   const int nkb = p.K / kKB;
+  const int total_it = ntile * nkb;
 
   const uint8_t* wbase = static_cast<const uint8_t*>(p.w) + int64_t(expert) * p.w_se * L::WB;
   const uint32_t smem_s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+
+  // ---- per-thread copy plan (everything that does not depend on the K block)
+  // weights: copy i of a warp covers local rows i * RPI + lane / CPW, chunk lane % CPW
+  constexpr int CPW = L::kWRow / 16, RPI = 32 / CPW, NCW = 16 / RPI;
+  const int w_r0 = lane / CPW, w_ch = lane % CPW;
+  uint32_t w_dst[NCW];
+#pragma unroll
+  for (int i = 0; i < NCW; ++i)
+    w_dst[i] = warp * 16 * L::kWRow + row_chunk_offset<L::WB>(i * RPI + w_r0, w_ch);
+  // activations: copy i of a thread is chunk id = i * kThreads + tid of the BMC x CPA tile
+  constexpr int CPA = L::kARow / 16, NCA = BMC * CPA / kThreads;
+  static_assert(BMC * CPA % kThreads == 0, "activation tile must split evenly over the threads");
+  uint32_t a_dst[NCA];
+#pragma unroll
+  for (int i = 0; i < NCA; ++i) {
+    const int id = i * kThreads + threadIdx.x;
+    a_dst[i] = L::kWBytes + row_chunk_offset<L::AB>(id / CPA, id % CPA);
+  }
+  // fragment read offsets inside a stage: weights rows g, g + 8; token row 8j + g
+  constexpr int WCH = 2 * L::WB, ACH = 2 * L::AB;  // 16-byte chunks a lane owns per row
+  uint32_t w_off[2][WCH], a_off[ACH];
+#pragma unroll
+  for (int r = 0; r < 2; ++r)
+#pragma unroll
+    for (int i = 0; i < WCH; ++i)
+      w_off[r][i] = warp * 16 * L::kWRow + row_chunk_offset<L::WB>(g + 8 * r, WCH * c + i);
+#pragma unroll
+  for (int i = 0; i < ACH; ++i) a_off[i] = L::kWBytes + row_chunk_offset<L::AB>(g, ACH * c + i);
 
   for (int tc = 0; tc < p.block_m; tc += BMC) {  // token chunks of the m-block
     __syncthreads();  // previous chunk's readers are done with s_arow and the ring
@@ -173,10 +209,6 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs
     }
     if (!__syncthreads_or(valid)) continue;  // a chunk of padding only
 
-    float acc[NT][4];
-#pragma unroll
-    for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-
     // token tiles that hold at least one real token (padding sits at the end of
     // an expert's run, but a ragged middle is handled too: rows are zero-filled)
     int nt_live = 0;
@@ -188,66 +220,118 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs
       if (any) nt_live = j + 1;
     }
 
+    // activation sources of this thread (fixed for the whole chunk)
+    const uint8_t* a_src[NCA];
+    bool a_ok[NCA], a_use[NCA];
+#pragma unroll
+    for (int i = 0; i < NCA; ++i) {
+      const int id = i * kThreads + threadIdx.x, r = id / CPA;
+      const int64_t arow = s_arow[r];
+      a_ok[i] = arow >= 0;
+      a_use[i] = r < nt_live * 8;
+      a_src[i] = static_cast<const uint8_t*>(p.a) + (arow < 0 ? 0 : arow) * p.a_stride * L::AB +
+                 (id % CPA) * 16;
+    }
+    const float* sa_src = nullptr;
+    bool sa_ok = false;
+    if constexpr (AF == A_E4M3) {
+      if (threadIdx.x < BMC) {
+        const int64_t arow = s_arow[threadIdx.x];
+        sa_ok = arow >= 0;
+        sa_src = p.sa + (arow < 0 ? 0 : arow) * p.sa_stride;
+      }
+    }
+    // the two token slots whose results this lane holds in tile j: 8j + 2c, + 1
+    int out_sid[NT][2];
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        const int slot = tc + 8 * j + 2 * c + t;
+        const int sid = slot < p.block_m ? p.sorted_ids[mb * p.block_m + slot] : -1;
+        out_sid[j][t] = (sid >= 0 && sid < p.num_valid) ? sid : -1;
+      }
     // weights widened to bf16 carry their scale (see widen); other forms scale sums
     constexpr bool kPrescale = AF == A_BF16 && WF != W_BF16;
-    float ch0 = 1.f, ch1 = 1.f;
-    if (p.scale_kind == S_CHANNEL && warp_live) {
-      ch0 = load_scale(p.scales, int64_t(expert) * p.s_se + row_lo + g, p.scale_dtype);
-      ch1 = load_scale(p.scales, int64_t(expert) * p.s_se + row_hi + g, p.scale_dtype);
-    }
 
-    auto issue = [&](int kb) {
-      if (kb < nkb) {
-        const uint32_t st = smem_s + (kb % kStages) * L::kStage;
-        // weights: each warp copies its own 16 rows (CPW chunks per row)
-        if (warp_live) {
-          constexpr int CPW = L::kWRow / 16;
+    // ---- producer side: next (tile, K block) to copy
+    int it_issue = 0, ti_issue = 0, kb_issue = 0, stage_issue = 0;
+    bool w_live_issue = false;
+    const uint8_t* w_src[NCW];
+    auto issue = [&]() {
+      if (it_issue < total_it) {
+        if (kb_issue == 0) {  // a new n-tile: this lane's weight row pointers
+          const int nb_i = ((tile0 + ti_issue) * kWarps + warp) * kRowsPerWarp;
+          w_live_issue = nb_i < out_rows;
+          const int hi_i = kGate ? half_n + nb_i : nb_i + 8;
 #pragma unroll
-          for (int i = 0; i < 16 * CPW / 32; ++i) {
-            const int id = i * 32 + lane, r = id / CPW, ch = id % CPW;
-            const int grow = r < 8 ? row_lo + r : row_hi + r - 8;
-            const uint8_t* src = wbase + (int64_t(grow) * p.w_sn + int64_t(kb) * kKB) * L::WB + ch * 16;
-            cp_async_16(st + warp * 16 * L::kWRow + row_chunk_offset<L::WB>(r, ch), src);
+          for (int i = 0; i < NCW; ++i) {
+            const int r = i * RPI + w_r0;
+            const int grow = r < 8 ? nb_i + r : hi_i + r - 8;
+            w_src[i] = wbase + int64_t(grow) * p.w_sn * L::WB + w_ch * 16;
           }
         }
-        // activations: all threads share the BMC token rows (zero-filled padding)
-        constexpr int CPA = L::kARow / 16;
-        for (int id = threadIdx.x; id < nt_live * 8 * CPA; id += kThreads) {
-          const int r = id / CPA, ch = id % CPA;
-          const int64_t arow = s_arow[r];
-          const uint8_t* src = static_cast<const uint8_t*>(p.a) +
-                               ((arow < 0 ? 0 : arow) * p.a_stride + int64_t(kb) * kKB) * L::AB + ch * 16;
-          cp_async_16_zfill(st + L::kWBytes + row_chunk_offset<L::AB>(r, ch), src, arow >= 0);
+        const uint32_t st = smem_s + stage_issue * L::kStage;
+        if (w_live_issue) {
+#pragma unroll
+          for (int i = 0; i < NCW; ++i) {
+            cp_async_16(st + w_dst[i], w_src[i]);
+            w_src[i] += kKB * L::WB;
+          }
         }
+        const int koff = kb_issue * kKB * L::AB;
+#pragma unroll
+        for (int i = 0; i < NCA; ++i)
+          if (a_use[i]) cp_async_16_zfill(st + a_dst[i], a_src[i] + koff, a_ok[i]);
         if constexpr (AF == A_E4M3) {
-          for (int r = threadIdx.x; r < nt_live * 8; r += kThreads) {
-            const int64_t arow = s_arow[r];
-            cp_async_4_zfill(st + L::kWBytes + L::kABytes + r * 4,
-                             p.sa + (arow < 0 ? 0 : arow) * p.sa_stride + kb, arow >= 0);
-          }
+          if (sa_src != nullptr && int(threadIdx.x) < nt_live * 8)
+            cp_async_4_zfill(st + L::kWBytes + L::kABytes + threadIdx.x * 4, sa_src + kb_issue, sa_ok);
         }
+        ++it_issue;
+        stage_issue = stage_issue + 1 == kStages ? 0 : stage_issue + 1;
+        if (++kb_issue == nkb) kb_issue = 0, ++ti_issue;
       }
       cp_async_commit();
     };
 
 #pragma unroll
-    for (int i = 0; i < kStages - 1; ++i) issue(i);
+    for (int i = 0; i < kStages - 1; ++i) issue();
 
-    for (int kb = 0; kb < nkb; ++kb) {
+    // ---- consumer side
+    float acc[NT][4];
+    float ch0 = 1.f, ch1 = 1.f;
+    int kb = 0, nb = 0, row_lo = 0, row_hi = 0, stage = 0, ti = 0;
+    int64_t sc0 = 0, sc1 = 0;  // block-scale indices of the two row groups at K block 0
+    bool warp_live = false;
+    for (int it = 0; it < total_it; ++it) {
       cp_async_wait<kStages - 2>();
-      __syncthreads();          // block kb landed for everyone; stage kb-1 is free
-      issue(kb + kStages - 1);
+      __syncthreads();          // step `it` landed for everyone; the stage of it-1 is free
+      issue();
+      if (kb == 0) {            // a new n-tile starts
+        nb = ((tile0 + ti) * kWarps + warp) * kRowsPerWarp;
+        warp_live = nb < out_rows;
+        row_lo = nb, row_hi = kGate ? half_n + nb : nb + 8;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+        ch0 = ch1 = 1.f;
+        if (warp_live && p.scale_kind == S_CHANNEL) {
+          ch0 = load_scale(p.scales, int64_t(expert) * p.s_se + row_lo + g, p.scale_dtype);
+          ch1 = load_scale(p.scales, int64_t(expert) * p.s_se + row_hi + g, p.scale_dtype);
+        }
+        sc0 = int64_t(expert) * p.s_se + int64_t((row_lo + g) / 128) * p.s_sn;
+        sc1 = int64_t(expert) * p.s_se + int64_t((row_hi + g) / 128) * p.s_sn;
+      }
+      const uint8_t* st = smem + stage * L::kStage;
+      const bool last_kb = kb == nkb - 1;
+      const int kb_now = kb;
+      stage = stage + 1 == kStages ? 0 : stage + 1;
+      if (last_kb) kb = 0, ++ti; else ++kb;
       if (!warp_live) continue;
-      const uint8_t* st = smem + (kb % kStages) * L::kStage;
-      const uint8_t* wst = st + warp * 16 * L::kWRow;
-      const uint8_t* ast = st + L::kWBytes;
 
-      // block scales of this warp's two row groups
       float sw0 = 1.f, sw1 = 1.f;
       if (p.scale_kind == S_BLOCK) {
-        const int64_t sb = int64_t(expert) * p.s_se + kb;
-        sw0 = load_scale(p.scales, sb + int64_t((row_lo + g) / 128) * p.s_sn, p.scale_dtype);
-        sw1 = load_scale(p.scales, sb + int64_t((row_hi + g) / 128) * p.s_sn, p.scale_dtype);
+        sw0 = load_scale(p.scales, sc0 + kb_now, p.scale_dtype);
+        sw1 = load_scale(p.scales, sc1 + kb_now, p.scale_dtype);
       }
 
       if constexpr (AF == A_E4M3) {
@@ -257,19 +341,17 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs
         for (int r = 0; r < 2; ++r)
 #pragma unroll
           for (int i = 0; i < 2; ++i) {
-            const uint4 x = *reinterpret_cast<const uint4*>(
-                wst + row_chunk_offset<1>(g + 8 * r, 2 * c + i));
+            const uint4 x = *reinterpret_cast<const uint4*>(st + w_off[r][i]);
             wr[r][4 * i] = x.x, wr[r][4 * i + 1] = x.y, wr[r][4 * i + 2] = x.z, wr[r][4 * i + 3] = x.w;
           }
-        const float* sap = reinterpret_cast<const float*>(ast + L::kABytes);
+        const float2* sap = reinterpret_cast<const float2*>(st + L::kWBytes + L::kABytes) + c;
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
           if (j >= nt_live) break;
           uint32_t xr[8];
 #pragma unroll
           for (int i = 0; i < 2; ++i) {
-            const uint4 x = *reinterpret_cast<const uint4*>(
-                ast + row_chunk_offset<1>(8 * j + g, 2 * c + i));
+            const uint4 x = *reinterpret_cast<const uint4*>(st + a_off[i] + j * 8 * L::kARow);
             xr[4 * i] = x.x, xr[4 * i + 1] = x.y, xr[4 * i + 2] = x.z, xr[4 * i + 3] = x.w;
           }
           float part[4] = {0.f, 0.f, 0.f, 0.f};
@@ -278,11 +360,11 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs
             const uint32_t a[4] = {wr[0][2 * s], wr[1][2 * s], wr[0][2 * s + 1], wr[1][2 * s + 1]};
             mma_e4m3_16832(part, a, xr[2 * s], xr[2 * s + 1]);
           }
-          const float sa0 = sap[8 * j + 2 * c], sa1 = sap[8 * j + 2 * c + 1];
-          acc[j][0] += part[0] * (sw0 * sa0);
-          acc[j][1] += part[1] * (sw0 * sa1);
-          acc[j][2] += part[2] * (sw1 * sa0);
-          acc[j][3] += part[3] * (sw1 * sa1);
+          const float2 sa = sap[4 * j];  // scales of tokens 8j + 2c, 8j + 2c + 1
+          acc[j][0] += part[0] * (sw0 * sa.x);
+          acc[j][1] += part[1] * (sw0 * sa.y);
+          acc[j][2] += part[2] * (sw1 * sa.x);
+          acc[j][3] += part[3] * (sw1 * sa.y);
         }
       } else {
         // 16-bit activations: weights widened to the activation's format
@@ -292,15 +374,13 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs
           if constexpr (WF == W_BF16) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              const uint4 x = *reinterpret_cast<const uint4*>(
-                  wst + row_chunk_offset<2>(g + 8 * r, 4 * c + i));
+              const uint4 x = *reinterpret_cast<const uint4*>(st + w_off[r][i]);
               wf[r][4 * i] = x.x, wf[r][4 * i + 1] = x.y, wf[r][4 * i + 2] = x.z, wf[r][4 * i + 3] = x.w;
             }
           } else {
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
-              const uint4 x = *reinterpret_cast<const uint4*>(
-                  wst + row_chunk_offset<1>(g + 8 * r, 2 * c + i));
+              const uint4 x = *reinterpret_cast<const uint4*>(st + w_off[r][i]);
               const float ws = r == 0 ? sw0 * ch0 : sw1 * ch1;
               widen<WF, AF>(x.x, ws, wf[r][8 * i], wf[r][8 * i + 1]);
               widen<WF, AF>(x.y, ws, wf[r][8 * i + 2], wf[r][8 * i + 3]);
@@ -315,8 +395,7 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs
           uint32_t xr[16];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            const uint4 x = *reinterpret_cast<const uint4*>(
-                ast + row_chunk_offset<2>(8 * j + g, 4 * c + i));
+            const uint4 x = *reinterpret_cast<const uint4*>(st + a_off[i] + j * 8 * L::kARow);
             xr[4 * i] = x.x, xr[4 * i + 1] = x.y, xr[4 * i + 2] = x.z, xr[4 * i + 3] = x.w;
           }
           float part[4] = {0.f, 0.f, 0.f, 0.f};
@@ -333,35 +412,33 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs
           acc[j][3] += part[3] * f1;
         }
       }
-    }
-    cp_async_wait<0>();
-    if (!warp_live) continue;
+      if (!last_kb) continue;
 
-    // ---- epilogue: lane holds (row g | g + 8) x (tokens 2c, 2c + 1) of each tile
-    if (kPrescale) ch0 = ch1 = 1.f;  // already inside the widened weights
+      // ---- epilogue of this n-tile: lane holds (row g | g + 8) x (tokens 2c, 2c + 1)
+      const float e0 = kPrescale ? 1.f : ch0, e1 = kPrescale ? 1.f : ch1;
 #pragma unroll
-    for (int j = 0; j < NT; ++j) {
-      if (j >= nt_live) break;
+      for (int j = 0; j < NT; ++j) {
+        if (j >= nt_live) break;
 #pragma unroll
-      for (int t = 0; t < 2; ++t) {
-        const int slot = tc + 8 * j + 2 * c + t;
-        if (slot >= p.block_m) continue;
-        const int64_t sid = p.sorted_ids[mb * p.block_m + slot];
-        if (sid < 0 || sid >= p.num_valid) continue;
-        const float v0 = acc[j][t] * ch0, v1 = acc[j][2 + t] * ch1;
-        if constexpr (kGate) {
-          const float o = apply_act(v0, ACT) * v1;
-          const int64_t at = sid * p.c_stride + nb + g;
-          if (p.c_f16) static_cast<__half*>(p.c)[at] = __float2half_rn(o);
-          else static_cast<__nv_bfloat16*>(p.c)[at] = __float2bfloat16_rn(o);
-        } else {
-          const float tw = p.topk_w ? p.topk_w[sid] : 1.f;
-          __nv_bfloat16* crow = static_cast<__nv_bfloat16*>(p.c) + sid * p.c_stride;
-          crow[row_lo + g] = __float2bfloat16_rn(v0 * tw);
-          crow[row_hi + g] = __float2bfloat16_rn(v1 * tw);
+        for (int t = 0; t < 2; ++t) {
+          const int64_t sid = out_sid[j][t];
+          if (sid < 0) continue;
+          const float v0 = acc[j][t] * e0, v1 = acc[j][2 + t] * e1;
+          if constexpr (kGate) {
+            const float o = apply_act(v0, ACT) * v1;
+            const int64_t at = sid * p.c_stride + nb + g;
+            if (p.c_f16) static_cast<__half*>(p.c)[at] = __float2half_rn(o);
+            else static_cast<__nv_bfloat16*>(p.c)[at] = __float2bfloat16_rn(o);
+          } else {
+            const float tw = p.topk_w ? p.topk_w[sid] : 1.f;
+            __nv_bfloat16* crow = static_cast<__nv_bfloat16*>(p.c) + sid * p.c_stride;
+            crow[row_lo + g] = __float2bfloat16_rn(v0 * tw);
+            crow[row_hi + g] = __float2bfloat16_rn(v1 * tw);
+          }
         }
       }
     }
+    cp_async_wait<0>();
   }
 }
 
@@ -452,7 +529,18 @@ extern "C" int strix_moe_gemm(
   const int64_t out_rows = gate_act != ACT_NONE ? n / 2 : n;
   const int64_t m_blocks = (sorted_len + block_m - 1) / block_m;
   STRIX_CHECK(m_blocks <= 65535, "too many m-blocks");
-  const dim3 grid{unsigned((out_rows + rows_per_cta - 1) / rows_per_cta), unsigned(m_blocks), 1u};
+  const int64_t n_tiles = (out_rows + rows_per_cta - 1) / rows_per_cta;
+  // n-tiles per CTA: enough K blocks per CTA (>= 48, i.e. 6 KB x 4 warps x 48 of
+  // weights) to amortise the pipeline fill, while keeping several CTAs per
+  // m-block. STRIX_MOE_TILES_PER_CTA overrides it for tuning runs.
+  static const int tpc_env = [] {
+    const char* e = getenv("STRIX_MOE_TILES_PER_CTA");
+    return e ? atoi(e) : 0;
+  }();
+  int64_t tpc = tpc_env > 0 ? tpc_env : (48 + k / kKB - 1) / (k / kKB);
+  if (tpc > n_tiles) tpc = n_tiles;
+  p.tiles_per_cta = int(tpc);
+  const dim3 grid{unsigned((n_tiles + tpc - 1) / tpc), unsigned(m_blocks), 1u};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (weight_format == W_E4M3 && act_format == A_E4M3) return launch_bm<W_E4M3, A_E4M3>(p, gate_act, grid, st);
   if (weight_format == W_E4M3 && act_format == A_BF16) return launch_bm<W_E4M3, A_BF16>(p, gate_act, grid, st);

@@ -179,6 +179,9 @@ _MOE_ROWS = [
 ]
 
 KERNELS: list[Kernel] = [
+    Kernel("_umma_tile", "umma_tile",
+           "one-CTA tcgen05 tile product, the layout probe of the sm_100a kernels",
+           {"weight_dtype": ("int8", "fp8_e4m3"), "m": 128}),
     *_MOE_ROWS,
     # ------------------------------------------------------------ attention
     _decode_row(

@@ -303,3 +303,28 @@ def moe_sum(input, output):
         _lib.call("strix_moe_sum", input.data_ptr(), output.data_ptr(), input.size(0),
                   input.size(1), input.size(2), input.stride(0), input.stride(1),
                   output.stride(0), _stream())
+
+
+# ----------------------------------------------------------- tcgen05 layout probe
+
+def _umma_tile_fake(a, b):
+    return a.new_empty((128, b.size(0)), dtype=torch.int32 if a.dtype == torch.int8 else torch.float32)
+
+
+@_define("_umma_tile(Tensor a, Tensor b) -> Tensor", fake=_umma_tile_fake)
+def _umma_tile(a, b):
+    """D[128, N] = A[128, K] @ B[N, K]^T on one CTA through tcgen05 / TMEM: int8
+    operands give an exact int32 result, float8_e4m3fn operands an fp32 one."""
+    _check(a.dim() == 2 and b.dim() == 2 and a.size(0) == 128 and a.size(1) == b.size(1)
+           and a.is_contiguous() and b.is_contiguous() and a.dtype == b.dtype
+           and a.dtype in (torch.int8, torch.float8_e4m3fn),
+           "a [128, K], b [N, K]: contiguous int8 or float8_e4m3fn")
+    kind = 0 if a.dtype == torch.int8 else 1
+    d = torch.empty(128, b.size(0), dtype=torch.int32 if kind == 0 else torch.float32,
+                    device=a.device)
+    status = torch.zeros(1, dtype=torch.int32, device=a.device)
+    with torch.cuda.device(a.device):
+        _lib.call("strix_umma_tile", d.data_ptr(), a.data_ptr(), b.data_ptr(), status.data_ptr(),
+                  b.size(0), a.size(1), kind, _stream())
+    _check(int(status.item()) == 0, "_umma_tile: a bounded wait ran out inside the kernel")
+    return d
