@@ -171,6 +171,25 @@ int strix_moe_sum(const void* in, void* out, int64_t tokens, int64_t top_k, int6
 int strix_umma_tile(void* d, const void* a, const void* b, int32_t* status, int64_t n, int64_t k,
                     int kind, strix_stream_t stream);
 
+/* Health of the tcgen05 kernels: *host_out = 0 while every launch so far met its
+ * bounded waits, 1 after one of them gave up (its output is then incomplete).
+ * Synchronises the device; for tests and debugging. No reference counterpart. */
+int strix_umma_status(int32_t* host_out);
+
+/* Tuning hook: widest m-block (block_m) of an FP8 W8A8 strix_moe_gemm call that
+ * is served by the tcgen05 kernel; wider ones take the mma.sync streaming kernel.
+ * Default 32 (or STRIX_MOE_UMMA_MAX_BLOCK_M); 0 turns the tcgen05 kernel off,
+ * 128 sends everything it covers to it. No reference counterpart. */
+int strix_moe_set_umma_max_block_m(int block_m);
+
+/* Tuning aid: cycle counters of CTA 0 of the tcgen05 MoE kernel, accumulated only
+ * while the environment variable STRIX_UMMA_PROF is set: [0] issuer waiting for
+ * data, [1] issuer waiting for an accumulator, [2] steps, [3] consumer waiting
+ * for MMAs, [4] consumer waiting for TMEM loads, [5] consumer epilogues, [6]
+ * consumer waiting for metadata, [7] kernel cycles. Synchronises the device;
+ * reset != 0 zeroes the counters afterwards. No reference counterpart. */
+int strix_umma_prof(int64_t* host_out8, int reset);
+
 /* strix_attn_decode_bf16 without a workspace argument, for callers that cannot
  * allocate device memory: a host loop that owns nothing but the input and
  * output buffers it was given, or a process whose device memory was budgeted

@@ -16,7 +16,8 @@ from . import _lib
 
 def pick_block_m(tokens: int, top_k: int, experts: int) -> int:
     """Rows per m-block: the smallest of 16/32/64 that holds an average expert's
-    share twice over, so most experts stream their weights exactly once."""
+    share twice over, so most experts stream their weights exactly once; 64
+    (the widest token chunk of the streaming kernel) beyond that."""
     per_expert = tokens * top_k / max(experts, 1)
     for bm in (16, 32):
         if per_expert * 2 <= bm:

@@ -19,6 +19,19 @@ DEV = "cuda"
 E, TOP_K = 32, 8
 
 
+@pytest.fixture(autouse=True)
+def tcgen05_kernels_met_their_waits():
+    """Every bounded wait inside the tcgen05 kernels must have been met: a
+    timed-out wait makes a kernel give up (wrong output, but no hang)."""
+    import ctypes
+
+    from libstrix_b200 import _lib
+
+    yield
+    flag = ctypes.c_int32(-1)
+    assert _lib.load().strix_umma_status(ctypes.byref(flag)) == 0 and flag.value == 0
+
+
 def rms_check(out, ref, tol):
     """|err| <= tol x RMS(ref), widened per element by the bf16 output quantum."""
     out, ref = out.float().cpu(), ref.float()
@@ -241,9 +254,22 @@ def test_moe_gemm_w8a16(tokens, block_m, gemm, activation, scale_dtype):
 @pytest.mark.parametrize("tokens", [1, 5, 40, 300])
 @pytest.mark.parametrize("block_m", [16, 32, 64, 128])
 @pytest.mark.parametrize("gemm,activation", [("w13", "silu"), ("w13", "gelu_tanh"), ("w2", "silu")])
-def test_moe_gemm_fp8_w8a8(tokens, block_m, gemm, activation, scheme):
+@pytest.mark.parametrize("kernel", ["tcgen05", "stream"])
+def test_moe_gemm_fp8_w8a8(tokens, block_m, gemm, activation, scheme, kernel):
     """The oracle consumes the kernel path's own quantised activations
-    (dequantised), the convention of tests/test_moe_w4a8.py:78-80."""
+    (dequantised), the convention of tests/test_moe_w4a8.py:78-80. Both
+    implementations are run: the tcgen05 kernel (every block_m up to 128) and
+    the mma.sync weight-streaming kernel."""
+    from libstrix_b200 import _lib
+
+    _lib.load().strix_moe_set_umma_max_block_m(128 if kernel == "tcgen05" else 0)
+    try:
+        _w8a8_case(tokens, block_m, gemm, activation, scheme)
+    finally:
+        _lib.load().strix_moe_set_umma_max_block_m(32)
+
+
+def _w8a8_case(tokens, block_m, gemm, activation, scheme):
     n, k = shapes(gemm)
     w, scales, _ = M.make_fp8_weights(E, n, k, scheme)
     full = scales.repeat_interleave(128, 1).repeat_interleave(128, 2) if scheme == "block" \
