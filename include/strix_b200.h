@@ -171,6 +171,24 @@ int strix_moe_sum(const void* in, void* out, int64_t tokens, int64_t top_k, int6
 int strix_umma_tile(void* d, const void* a, const void* b, int32_t* status, int64_t n, int64_t k,
                     int kind, strix_stream_t stream);
 
+/* ------------------------------------------------------------------------
+ * Dense quantized GEMMs.
+ * ---------------------------------------------------------------------- */
+
+/* W8A8 INT8 GEMM with per-token and per-channel scales:
+ *   out[m, n] = bf16((sum_k a_q[m, k] * w[n, k]) * a_scale[m] * w_scale[n])
+ * a_q int8 [m, k] (row stride a_stride), w int8 [n, k] (row stride w_stride),
+ * scales fp32, out bf16 [m, n] (row stride out_stride). The sum is exact in
+ * int32; acc_out, when not NULL, receives it ([m, n] int32, row stride
+ * out_stride). k must be a multiple of 128. This is the per-token form of the
+ * reference's w8a8_wmma_gemm (csrc/gemm/w8a8_wmma_gemm.hip:15-22, :799-918,
+ * which quantises the activations per 128-wide group inside the op); runs on
+ * tcgen05 kind::i8. */
+int strix_w8a8_int8_gemm(void* out, int32_t* acc_out, const void* a_q, const float* a_scale,
+                         const void* w, const float* w_scale, int64_t m, int64_t n, int64_t k,
+                         int64_t a_stride, int64_t w_stride, int64_t out_stride,
+                         strix_stream_t stream);
+
 /* Health of the tcgen05 kernels: *host_out = 0 while every launch so far met its
  * bounded waits, 1 after one of them gave up (its output is then incomplete).
  * Synchronises the device; for tests and debugging. No reference counterpart. */

@@ -1,0 +1,347 @@
+// Dense W8A8 INT8 GEMM on the Blackwell tensor cores (tcgen05.mma kind::i8,
+// int32 accumulators in TMEM), for sm_100a:
+//
+//     out[m, n] = bf16( (sum_k a[m, k] * w[n, k]) * a_scale[m] * w_scale[n] )
+//
+// with int8 activations a [M, K] (one fp32 scale per token), int8 weights
+// w [N, K] (one fp32 scale per output channel) and an int32-exact sum. This is
+// the per-token form of the reference's w8a8_wmma_gemm
+// (csrc/gemm/w8a8_wmma_gemm.hip:15-22, which quantises per 128-wide group
+// inside the op); the int32 accumulators can be written out as well, so tests
+// can compare them bit for bit.
+//
+// Both operands are K-major row matrices, so one kernel serves two
+// orientations of the 128 x NB accumulator tile:
+//   * M >= 128: A = 128 tokens, B = 256 weight rows; a thread of the epilogue
+//     owns one token and writes 256 consecutive outputs;
+//   * small M (decode): the operands swap - A = 128 weight rows (they fill the
+//     MMA's M dimension whatever the batch), B = the tokens padded to 16/32/64;
+//     the kernel is then a pure weight stream (HBM-bound).
+// One persistent CTA per SM; producers (4 warps, cp.async into a swizzled
+// ring), one issuing thread, 4 epilogue warps; two TMEM accumulators so a tile's
+// epilogue overlaps the next tile's MMAs. Every mbarrier wait is bounded.
+#include <cstdlib>
+
+#include "umma.cuh"
+
+namespace strix {
+namespace {
+
+using namespace umma;
+
+constexpr int kGProducerWarps = 4, kGEpilogueWarps = 4;
+constexpr int kGThreads = (kGProducerWarps + kGEpilogueWarps + 1) * 32;
+constexpr int kGKBlock = 128;
+
+struct GemmArgs {
+  __nv_bfloat16* out;      // [M, N]
+  int32_t* acc_out;        // optional [M, N] int32 accumulators, or NULL
+  const uint8_t* a_mat;    // MMA A operand rows (tokens, or weights when swapped)
+  const uint8_t* b_mat;    // MMA B operand rows
+  const float* a_scale;    // per A row
+  const float* b_scale;    // per B row
+  int32_t* status;
+  int64_t a_stride, b_stride, out_stride;
+  int a_rows, b_rows, K;
+  int a_tiles, b_tiles;
+  int swap;                // 1: A rows are output columns (weights), B rows are tokens
+};
+
+template <int NB>
+struct GemmLayout {
+  static constexpr int kABytes = 128 * kGKBlock;
+  static constexpr int kBBytes = NB * kGKBlock;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = (200 * 1024) / kStageBytes > 8 ? 8 : (200 * 1024) / kStageBytes;
+  static constexpr int kTmemCols = 2 * NB < 32 ? 32 : 2 * NB;
+  static constexpr int kSmem = 1024 + kStages * kStageBytes + 256;
+};
+
+template <int NB>
+__global__ void __launch_bounds__(kGThreads, 1) gemm_w8a8_umma_kernel(const GemmArgs p) {
+  using L = GemmLayout<NB>;
+  constexpr int S = L::kStages;
+  extern __shared__ uint8_t raw_smem[];
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
+                                             ~uintptr_t(1023));
+  __shared__ __align__(8) uint64_t full_bar[S], empty_bar[S], landed_bar[S], tfull_bar[2], tempty_bar[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ volatile int s_abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nkb = p.K / kGKBlock;
+  const int total_items = p.a_tiles * p.b_tiles;
+
+  if (tid == 0) {
+    for (int i = 0; i < S; ++i) {
+      mbar_init(&full_bar[i], kGProducerWarps);
+      mbar_init(&empty_bar[i], 1);
+      mbar_init(&landed_bar[i], kGProducerWarps * 32);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull_bar[i], 1);
+      mbar_init(&tempty_bar[i], kGEpilogueWarps);
+    }
+    s_abort = 0;
+    fence_mbar_init();
+  }
+  if (warp == kGProducerWarps + kGEpilogueWarps) tmem_alloc(&tmem_slot, L::kTmemCols);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t ring_s = smem_u32(ring);
+
+  if (warp < kGProducerWarps) {
+    // ------------------------------------------------------------ producers
+    // Non-blocking loop: issue the next K block when its ring stage is free,
+    // publish the oldest stage once all 128 threads' copies have landed.
+    const int ch = tid & 7, r0 = tid >> 3;
+    const uint32_t dst0 = uint32_t(r0 * 128 + ((ch ^ (r0 & 7)) << 4));
+    constexpr int NBI = NB / 16;  // B rows per thread
+    int item = blockIdx.x, kb = 0, issued = 0, pub = 0;
+    const uint8_t* asrc[8];
+    const uint8_t* bsrc[NBI];
+    bool aok[8], bok[NBI];
+    auto open_item = [&](int it) {
+      const int bt = it / p.a_tiles, at = it - bt * p.a_tiles;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int row = at * 128 + r0 + 16 * i;
+        aok[i] = row < p.a_rows;
+        asrc[i] = p.a_mat + int64_t(aok[i] ? row : 0) * p.a_stride + ch * 16;
+      }
+#pragma unroll
+      for (int i = 0; i < NBI; ++i) {
+        const int row = bt * NB + r0 + 16 * i;
+        bok[i] = row < p.b_rows;
+        bsrc[i] = p.b_mat + int64_t(bok[i] ? row : 0) * p.b_stride + ch * 16;
+      }
+    };
+    if (item < total_items) open_item(item);
+    bool dead = false;
+    uint32_t idle = 0;
+    while (!dead && (item < total_items || pub < issued)) {
+      bool progressed = false;
+      if (item < total_items) {
+        const int s = issued % S;
+        if (__all_sync(0xffffffffu, mbar_test(&empty_bar[s], ((issued / S) & 1) ^ 1))) {
+          const uint32_t st = ring_s + s * L::kStageBytes;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            cp_async_16_zfill(st + dst0 + 2048 * i, asrc[i], aok[i]);
+            asrc[i] += kGKBlock;
+          }
+#pragma unroll
+          for (int i = 0; i < NBI; ++i) {
+            cp_async_16_zfill(st + L::kABytes + dst0 + 2048 * i, bsrc[i], bok[i]);
+            bsrc[i] += kGKBlock;
+          }
+          mbar_arrive_cp_async(&landed_bar[s]);
+          ++issued;
+          if (++kb == nkb) {
+            kb = 0;
+            item += gridDim.x;
+            if (item < total_items) open_item(item);
+          }
+          progressed = true;
+        }
+      }
+      if (pub < issued) {
+        const int s = pub % S;
+        if (__all_sync(0xffffffffu, mbar_test(&landed_bar[s], (pub / S) & 1))) {
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&full_bar[s]);
+          ++pub;
+          progressed = true;
+        }
+      }
+      if (progressed) {
+        idle = 0;
+      } else {
+        __nanosleep(100);
+        if (__any_sync(0xffffffffu, ++idle > (kSpinLimit >> 4) || s_abort != 0)) dead = true;
+      }
+    }
+    cp_async_wait<0>();
+    if (dead) atomicExch(p.status, 1), s_abort = 1;
+  } else if (warp == kGProducerWarps + kGEpilogueWarps) {
+    // --------------------------------------------------------------- issuer
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc(D_S32, 1, 1, 128, NB);
+      int t = 0, li = 0;
+      bool dead = false;
+      for (int item = blockIdx.x; item < total_items && !dead; item += gridDim.x, ++li) {
+        const int buf = li & 1;
+        if (!mbar_wait(&tempty_bar[buf], ((li >> 1) & 1) ^ 1)) {  // epilogue drained it
+          dead = true;
+          break;
+        }
+        for (int kb = 0; kb < nkb; ++kb, ++t) {
+          const int s = t % S;
+          if (!mbar_wait(&full_bar[s], (t / S) & 1) || s_abort) {
+            dead = true;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa_addr = ring_s + s * L::kStageBytes, sb_addr = sa_addr + L::kABytes;
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4)
+            mma_ss<KIND_I8>(tmem + buf * NB, smem_desc_sw128(sa_addr, 32 * k4),
+                            smem_desc_sw128(sb_addr, 32 * k4), idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+          mma_commit(&empty_bar[s]);
+        }
+        if (!dead) mma_commit(&tfull_bar[buf]);   // the tile's sums are complete
+      }
+      if (dead) atomicExch(p.status, 1), s_abort = 1;
+    }
+  } else {
+    // ------------------------------------------------------------- epilogue
+    const int ctid = tid - kGProducerWarps * 32;          // TMEM lane = A row of the tile
+    const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
+    constexpr int CH = NB < 32 ? NB : 32;
+    int li = 0;
+    bool dead = false;
+    for (int item = blockIdx.x; item < total_items && !dead; item += gridDim.x, ++li) {
+      const int bt = item / p.a_tiles, at = item - bt * p.a_tiles;
+      const int buf = li & 1;
+      const int row_a = at * 128 + ctid;
+      const bool row_ok = row_a < p.a_rows;
+      const float sa = row_ok ? __ldg(p.a_scale + row_a) : 0.f;
+      const bool ok = mbar_wait(&tfull_bar[buf], (li >> 1) & 1);
+      if (__any_sync(0xffffffffu, !ok) || s_abort) {
+        dead = true;
+        break;
+      }
+      tc_fence_after_sync();
+#pragma unroll 1
+      for (int c0 = 0; c0 < NB; c0 += CH) {
+        __syncwarp();
+        uint32_t r[CH];
+        if constexpr (CH == 32) tmem_ld_32x32(tmem + lane_base + buf * NB + c0, r);
+        else tmem_ld_32x16(tmem + lane_base + buf * NB + c0, r);
+        tmem_ld_wait();
+        if (c0 + CH >= NB) {   // everything read: the issuer may reuse this accumulator
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+        }
+        const int col0 = bt * NB + c0;
+        if (!row_ok) {
+          // a padding row of the tile: nothing to write (the warp stays together
+          // for the next chunk's collective TMEM load)
+        } else if (p.swap) {
+          // A rows are output columns: out[token = col0 + j][n = row_a]
+#pragma unroll
+          for (int j = 0; j < CH; ++j) {
+            const int tok = col0 + j;
+            if (tok >= p.b_rows) continue;
+            // (sum * token scale) * channel scale, the order of the other orientation
+            const float v = float(int(r[j])) * __ldg(p.b_scale + tok) * sa;
+            p.out[int64_t(tok) * p.out_stride + row_a] = __float2bfloat16_rn(v);
+            if (p.acc_out) p.acc_out[int64_t(tok) * p.out_stride + row_a] = int(r[j]);
+          }
+        } else {
+          // A rows are tokens: this thread writes CH consecutive outputs of its row
+          __nv_bfloat16* orow = p.out + int64_t(row_a) * p.out_stride + col0;
+          if (col0 + CH <= p.b_rows) {
+#pragma unroll
+            for (int j = 0; j < CH; j += 8) {
+              const float4 s0 = __ldg(reinterpret_cast<const float4*>(p.b_scale + col0 + j));
+              const float4 s1 = __ldg(reinterpret_cast<const float4*>(p.b_scale + col0 + j + 4));
+              uint4 o;
+              o.x = pack_bf16x2(float(int(r[j])) * sa * s0.x, float(int(r[j + 1])) * sa * s0.y);
+              o.y = pack_bf16x2(float(int(r[j + 2])) * sa * s0.z, float(int(r[j + 3])) * sa * s0.w);
+              o.z = pack_bf16x2(float(int(r[j + 4])) * sa * s1.x, float(int(r[j + 5])) * sa * s1.y);
+              o.w = pack_bf16x2(float(int(r[j + 6])) * sa * s1.z, float(int(r[j + 7])) * sa * s1.w);
+              *reinterpret_cast<uint4*>(orow + j) = o;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < CH; ++j)
+              if (col0 + j < p.b_rows)
+                orow[j] = __float2bfloat16_rn(float(int(r[j])) * sa * __ldg(p.b_scale + col0 + j));
+          }
+          if (p.acc_out) {
+            int32_t* arow = p.acc_out + int64_t(row_a) * p.out_stride + col0;
+#pragma unroll
+            for (int j = 0; j < CH; ++j)
+              if (col0 + j < p.b_rows) arow[j] = int(r[j]);
+          }
+        }
+      }
+    }
+    if (dead) atomicExch(p.status, 1), s_abort = 1;
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == kGProducerWarps + kGEpilogueWarps) tmem_dealloc(tmem, L::kTmemCols);
+}
+
+template <int NB>
+int launch_gemm(const GemmArgs& p, cudaStream_t st) {
+  using L = GemmLayout<NB>;
+  auto kernel = gemm_w8a8_umma_kernel<NB>;
+  static bool done[64] = {};
+  static int sms[64] = {};
+  int dev = 0;
+  STRIX_CUDA(cudaGetDevice(&dev));
+  STRIX_CHECK(dev >= 0 && dev < 64, "device index %d out of range", dev);
+  if (!done[dev]) {
+    STRIX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmem));
+    STRIX_CUDA(cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev));
+    done[dev] = true;
+  }
+  const int items = p.a_tiles * p.b_tiles;
+  kernel<<<items < sms[dev] ? items : sms[dev], kGThreads, L::kSmem, st>>>(p);
+  return launch_status("w8a8_int8_gemm");
+}
+
+}  // namespace
+
+int32_t* umma_status_ptr();  // moe_gemm_umma.cu: device address of the shared status word
+
+}  // namespace strix
+
+using namespace strix;
+
+extern "C" int strix_w8a8_int8_gemm(void* out, int32_t* acc_out, const void* a_q,
+                                    const float* a_scale, const void* w, const float* w_scale,
+                                    int64_t m, int64_t n, int64_t k, int64_t a_stride,
+                                    int64_t w_stride, int64_t out_stride, strix_stream_t stream) {
+  STRIX_CHECK(m >= 0 && n > 0 && k > 0, "bad shapes");
+  STRIX_CHECK(k % 128 == 0, "K must be a multiple of 128");
+  STRIX_CHECK(a_stride % 16 == 0 && w_stride % 16 == 0 && out_stride % 8 == 0 &&
+                  reinterpret_cast<uintptr_t>(a_q) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0 &&
+                  reinterpret_cast<uintptr_t>(out) % 16 == 0 && reinterpret_cast<uintptr_t>(w_scale) % 16 == 0,
+              "16-byte aligned rows required");
+  STRIX_CHECK(n < (int64_t(1) << 31) && m < (int64_t(1) << 31), "matrix too large");
+  if (m == 0) return STRIX_OK;
+  GemmArgs p;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.acc_out = acc_out;
+  p.status = umma_status_ptr();
+  STRIX_CHECK(p.status != nullptr, "status word unavailable");
+  p.out_stride = out_stride;
+  p.K = int(k);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (m <= 64) {
+    // decode: weights fill the MMA's M dimension, the tokens are the N dimension
+    p.swap = 1;
+    p.a_mat = static_cast<const uint8_t*>(w), p.a_stride = w_stride, p.a_scale = w_scale;
+    p.b_mat = static_cast<const uint8_t*>(a_q), p.b_stride = a_stride, p.b_scale = a_scale;
+    p.a_rows = int(n), p.b_rows = int(m);
+    p.a_tiles = int((n + 127) / 128), p.b_tiles = 1;
+    if (m <= 16) return launch_gemm<16>(p, st);
+    if (m <= 32) return launch_gemm<32>(p, st);
+    return launch_gemm<64>(p, st);
+  }
+  p.swap = 0;
+  p.a_mat = static_cast<const uint8_t*>(a_q), p.a_stride = a_stride, p.a_scale = a_scale;
+  p.b_mat = static_cast<const uint8_t*>(w), p.b_stride = w_stride, p.b_scale = w_scale;
+  p.a_rows = int(m), p.b_rows = int(n);
+  p.a_tiles = int((m + 127) / 128), p.b_tiles = int((n + 255) / 256);
+  return launch_gemm<256>(p, st);
+}

@@ -480,6 +480,13 @@ int launch_umma(const UmmaMoeArgs& p, cudaStream_t st) {
 
 }  // namespace
 
+// Device address of the status word shared by every tcgen05 kernel of the library.
+int32_t* umma_status_ptr() {
+  void* addr = nullptr;
+  return cudaGetSymbolAddress(&addr, g_umma_status) == cudaSuccess ? static_cast<int32_t*>(addr)
+                                                                    : nullptr;
+}
+
 // Widest m-block the tcgen05 kernel takes (wider ones go to the streaming kernel).
 int g_umma_max_block_m = [] {
   const char* e = getenv("STRIX_MOE_UMMA_MAX_BLOCK_M");

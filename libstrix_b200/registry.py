@@ -183,6 +183,17 @@ KERNELS: list[Kernel] = [
            "one-CTA tcgen05 tile product, the layout probe of the sm_100a kernels",
            {"weight_dtype": ("int8", "fp8_e4m3"), "m": 128}),
     *_MOE_ROWS,
+    # ---------------------------------------------------------- dense GEMMs
+    Kernel("w8a8_int8_gemm", "w8a8",
+           "dense W8A8 INT8 GEMM on tcgen05 kind::i8 (int32 sums in TMEM, exact): int8 "
+           "activations with one fp32 scale per token, int8 weights with one per output "
+           "channel. K % 128 == 0. Up to 64 rows the weights are the MMA's M dimension "
+           "and the kernel is a weight stream; beyond that 128 x 256 tiles",
+           {"weight_bits": 8, "weight_dtype": "int8", "act_dtype": "int8", "group_size": 0,
+            "dtype": "bf16"},
+           {"tile": "128 weights x 16/32/64 tokens (rows <= 64), 128 tokens x 256 weights",
+            "pipeline": "4 producer warps (cp.async ring, 128B swizzle), 1 issuing thread, "
+                        "4 epilogue warps, 2 TMEM accumulators, persistent grid"}),
     # ------------------------------------------------------------ attention
     _decode_row(
         128, 8,

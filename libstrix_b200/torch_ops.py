@@ -305,6 +305,38 @@ def moe_sum(input, output):
                   output.stride(0), _stream())
 
 
+# ------------------------------------------------------------ dense quantized GEMMs
+
+def _w8a8_int8_fake(a_q, a_scale, w, w_scale, acc_out=None):
+    return a_q.new_empty((a_q.size(0), w.size(0)), dtype=torch.bfloat16)
+
+
+# Not in the reference: the per-token form of its w8a8_wmma_gemm
+# (csrc/torch_ops.cpp:277, which takes bf16 activations and quantises per
+# 128-group inside). acc_out, if given, receives the exact int32 sums.
+@_define("w8a8_int8_gemm(Tensor a_q, Tensor a_scale, Tensor w, Tensor w_scale, "
+         "Tensor(a!)? acc_out=None) -> Tensor", fake=_w8a8_int8_fake)
+def w8a8_int8_gemm(a_q, a_scale, w, w_scale, acc_out=None):
+    _check(a_q.dim() == 2 and w.dim() == 2 and a_q.dtype == torch.int8 and w.dtype == torch.int8
+           and a_q.size(1) == w.size(1) and a_q.stride(1) == 1 and w.stride(1) == 1,
+           "a_q int8 [M, K], w int8 [N, K]")
+    m, k = a_q.shape
+    n = w.size(0)
+    _check(k % 128 == 0, "K must be a multiple of 128")
+    _check(a_scale.dtype == torch.float32 and a_scale.numel() == m and a_scale.is_contiguous()
+           and w_scale.dtype == torch.float32 and w_scale.numel() == n and w_scale.is_contiguous(),
+           "scales must be contiguous fp32 [M] and [N]")
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=a_q.device)
+    if acc_out is not None:
+        _check(acc_out.dtype == torch.int32 and tuple(acc_out.shape) == (m, n)
+               and acc_out.is_contiguous(), "acc_out must be contiguous int32 [M, N]")
+    with torch.cuda.device(a_q.device):
+        _lib.call("strix_w8a8_int8_gemm", out.data_ptr(), _ptr(acc_out), a_q.data_ptr(),
+                  a_scale.data_ptr(), w.data_ptr(), w_scale.data_ptr(), m, n, k, a_q.stride(0),
+                  w.stride(0), out.stride(0), _stream())
+    return out
+
+
 # ----------------------------------------------------------- tcgen05 layout probe
 
 def _umma_tile_fake(a, b):
