@@ -17,31 +17,30 @@
 //   * small M (decode): the operands swap - A = 128 weight rows (they fill the
 //     MMA's M dimension whatever the batch), B = the tokens padded to 16/32/64;
 //     the kernel is then a pure weight stream (HBM-bound).
-// One persistent CTA per SM; producers (4 warps, cp.async into a swizzled
-// ring), one issuing thread, 4 epilogue warps; two TMEM accumulators so a tile's
-// epilogue overlaps the next tile's MMAs. Every mbarrier wait is bounded.
+// One persistent CTA per SM: one producing thread (TMA boxes of 128 bytes x
+// rows with the 128-byte swizzle into a ring of stages), one issuing thread,
+// 4 epilogue warps; two TMEM accumulators so a tile's epilogue overlaps the
+// next tile's MMAs. Every mbarrier wait is bounded.
 #include <cstdlib>
 
-#include "umma.cuh"
+#include "tma.cuh"
 
 namespace strix {
 namespace {
 
 using namespace umma;
 
-constexpr int kGProducerWarps = 4, kGEpilogueWarps = 4;
-constexpr int kGThreads = (kGProducerWarps + kGEpilogueWarps + 1) * 32;
+constexpr int kGEpilogueWarps = 4;             // warps 2..5; warp 0 produces, warp 1 issues
+constexpr int kGThreads = (kGEpilogueWarps + 2) * 32;
 constexpr int kGKBlock = 128;
 
 struct GemmArgs {
   __nv_bfloat16* out;      // [M, N]
   int32_t* acc_out;        // optional [M, N] int32 accumulators, or NULL
-  const uint8_t* a_mat;    // MMA A operand rows (tokens, or weights when swapped)
-  const uint8_t* b_mat;    // MMA B operand rows
   const float* a_scale;    // per A row
   const float* b_scale;    // per B row
   int32_t* status;
-  int64_t a_stride, b_stride, out_stride;
+  int64_t out_stride;
   int a_rows, b_rows, K;
   int a_tiles, b_tiles;
   int swap;                // 1: A rows are output columns (weights), B rows are tokens
@@ -52,19 +51,21 @@ struct GemmLayout {
   static constexpr int kABytes = 128 * kGKBlock;
   static constexpr int kBBytes = NB * kGKBlock;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = (200 * 1024) / kStageBytes > 8 ? 8 : (200 * 1024) / kStageBytes;
+  static constexpr int kStages = (208 * 1024) / kStageBytes > 12 ? 12 : (208 * 1024) / kStageBytes;
   static constexpr int kTmemCols = 2 * NB < 32 ? 32 : 2 * NB;
   static constexpr int kSmem = 1024 + kStages * kStageBytes + 256;
 };
 
 template <int NB>
-__global__ void __launch_bounds__(kGThreads, 1) gemm_w8a8_umma_kernel(const GemmArgs p) {
+__global__ void __launch_bounds__(kGThreads, 1) gemm_w8a8_umma_kernel(const GemmArgs p,
+                                                                     const __grid_constant__ CUtensorMap map_a,
+                                                                     const __grid_constant__ CUtensorMap map_b) {
   using L = GemmLayout<NB>;
   constexpr int S = L::kStages;
   extern __shared__ uint8_t raw_smem[];
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
                                              ~uintptr_t(1023));
-  __shared__ __align__(8) uint64_t full_bar[S], empty_bar[S], landed_bar[S], tfull_bar[2], tempty_bar[2];
+  __shared__ __align__(8) uint64_t full_bar[S], empty_bar[S], tfull_bar[2], tempty_bar[2];
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int s_abort;
 
@@ -74,9 +75,8 @@ __global__ void __launch_bounds__(kGThreads, 1) gemm_w8a8_umma_kernel(const Gemm
 
   if (tid == 0) {
     for (int i = 0; i < S; ++i) {
-      mbar_init(&full_bar[i], kGProducerWarps);
+      mbar_init(&full_bar[i], 1);
       mbar_init(&empty_bar[i], 1);
-      mbar_init(&landed_bar[i], kGProducerWarps * 32);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&tfull_bar[i], 1);
@@ -85,88 +85,37 @@ __global__ void __launch_bounds__(kGThreads, 1) gemm_w8a8_umma_kernel(const Gemm
     s_abort = 0;
     fence_mbar_init();
   }
-  if (warp == kGProducerWarps + kGEpilogueWarps) tmem_alloc(&tmem_slot, L::kTmemCols);
+  if (warp == 1) tmem_alloc(&tmem_slot, L::kTmemCols);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = tmem_slot;
   const uint32_t ring_s = smem_u32(ring);
 
-  if (warp < kGProducerWarps) {
-    // ------------------------------------------------------------ producers
-    // Non-blocking loop: issue the next K block when its ring stage is free,
-    // publish the oldest stage once all 128 threads' copies have landed.
-    const int ch = tid & 7, r0 = tid >> 3;
-    const uint32_t dst0 = uint32_t(r0 * 128 + ((ch ^ (r0 & 7)) << 4));
-    constexpr int NBI = NB / 16;  // B rows per thread
-    int item = blockIdx.x, kb = 0, issued = 0, pub = 0;
-    const uint8_t* asrc[8];
-    const uint8_t* bsrc[NBI];
-    bool aok[8], bok[NBI];
-    auto open_item = [&](int it) {
-      const int bt = it / p.a_tiles, at = it - bt * p.a_tiles;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int row = at * 128 + r0 + 16 * i;
-        aok[i] = row < p.a_rows;
-        asrc[i] = p.a_mat + int64_t(aok[i] ? row : 0) * p.a_stride + ch * 16;
-      }
-#pragma unroll
-      for (int i = 0; i < NBI; ++i) {
-        const int row = bt * NB + r0 + 16 * i;
-        bok[i] = row < p.b_rows;
-        bsrc[i] = p.b_mat + int64_t(bok[i] ? row : 0) * p.b_stride + ch * 16;
-      }
-    };
-    if (item < total_items) open_item(item);
-    bool dead = false;
-    uint32_t idle = 0;
-    while (!dead && (item < total_items || pub < issued)) {
-      bool progressed = false;
-      if (item < total_items) {
-        const int s = issued % S;
-        if (__all_sync(0xffffffffu, mbar_test(&empty_bar[s], ((issued / S) & 1) ^ 1))) {
+  if (warp == 0) {
+    // ------------------------------------------------------------- producer
+    if (lane == 0) {
+      tma::prefetch_map(&map_a);
+      tma::prefetch_map(&map_b);
+      bool dead = false;
+      int t = 0;
+      for (int item = blockIdx.x; item < total_items && !dead; item += gridDim.x) {
+        const int bt = item / p.a_tiles, at = item - bt * p.a_tiles;
+        for (int kb = 0; kb < nkb; ++kb, ++t) {
+          const int s = t % S;
+          if (!mbar_wait(&empty_bar[s], ((t / S) & 1) ^ 1) || s_abort) {   // the MMAs have read it
+            dead = true;
+            break;
+          }
           const uint32_t st = ring_s + s * L::kStageBytes;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            cp_async_16_zfill(st + dst0 + 2048 * i, asrc[i], aok[i]);
-            asrc[i] += kGKBlock;
-          }
-#pragma unroll
-          for (int i = 0; i < NBI; ++i) {
-            cp_async_16_zfill(st + L::kABytes + dst0 + 2048 * i, bsrc[i], bok[i]);
-            bsrc[i] += kGKBlock;
-          }
-          mbar_arrive_cp_async(&landed_bar[s]);
-          ++issued;
-          if (++kb == nkb) {
-            kb = 0;
-            item += gridDim.x;
-            if (item < total_items) open_item(item);
-          }
-          progressed = true;
+          tma::mbar_expect_tx(&full_bar[s], L::kStageBytes);
+          tma::load_2d(st, &map_a, kb * kGKBlock, at * 128, &full_bar[s]);
+          tma::load_2d(st + L::kABytes, &map_b, kb * kGKBlock, bt * NB, &full_bar[s]);
         }
       }
-      if (pub < issued) {
-        const int s = pub % S;
-        if (__all_sync(0xffffffffu, mbar_test(&landed_bar[s], (pub / S) & 1))) {
-          fence_proxy_async();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&full_bar[s]);
-          ++pub;
-          progressed = true;
-        }
-      }
-      if (progressed) {
-        idle = 0;
-      } else {
-        __nanosleep(100);
-        if (__any_sync(0xffffffffu, ++idle > (kSpinLimit >> 4) || s_abort != 0)) dead = true;
-      }
+      if (dead) atomicExch(p.status, 1), s_abort = 1;
     }
-    cp_async_wait<0>();
-    if (dead) atomicExch(p.status, 1), s_abort = 1;
-  } else if (warp == kGProducerWarps + kGEpilogueWarps) {
+  } else if (warp == 1) {
     // --------------------------------------------------------------- issuer
     if (lane == 0) {
       const uint32_t idesc = instr_desc(D_S32, 1, 1, 128, NB);
@@ -198,7 +147,7 @@ __global__ void __launch_bounds__(kGThreads, 1) gemm_w8a8_umma_kernel(const Gemm
     }
   } else {
     // ------------------------------------------------------------- epilogue
-    const int ctid = tid - kGProducerWarps * 32;          // TMEM lane = A row of the tile
+    const int ctid = (warp & 3) * 32 + lane;              // TMEM lane = A row of the tile
     const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
     constexpr int CH = NB < 32 ? NB : 32;
     int li = 0;
@@ -277,11 +226,12 @@ __global__ void __launch_bounds__(kGThreads, 1) gemm_w8a8_umma_kernel(const Gemm
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == kGProducerWarps + kGEpilogueWarps) tmem_dealloc(tmem, L::kTmemCols);
+  if (warp == 1) tmem_dealloc(tmem, L::kTmemCols);
 }
 
 template <int NB>
-int launch_gemm(const GemmArgs& p, cudaStream_t st) {
+int launch_gemm(const GemmArgs& p, const void* a_mat, int64_t a_stride, const void* b_mat,
+                int64_t b_stride, cudaStream_t st) {
   using L = GemmLayout<NB>;
   auto kernel = gemm_w8a8_umma_kernel<NB>;
   static bool done[64] = {};
@@ -294,8 +244,12 @@ int launch_gemm(const GemmArgs& p, cudaStream_t st) {
     STRIX_CUDA(cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev));
     done[dev] = true;
   }
+  CUtensorMap map_a, map_b;
+  STRIX_CHECK(tma::make_map_u8(&map_a, a_mat, uint64_t(p.a_rows), uint64_t(p.K), uint64_t(a_stride), 128) &&
+                  tma::make_map_u8(&map_b, b_mat, uint64_t(p.b_rows), uint64_t(p.K), uint64_t(b_stride), NB),
+              "tensor map encoding failed");
   const int items = p.a_tiles * p.b_tiles;
-  kernel<<<items < sms[dev] ? items : sms[dev], kGThreads, L::kSmem, st>>>(p);
+  kernel<<<items < sms[dev] ? items : sms[dev], kGThreads, L::kSmem, st>>>(p, map_a, map_b);
   return launch_status("w8a8_int8_gemm");
 }
 
@@ -330,18 +284,16 @@ extern "C" int strix_w8a8_int8_gemm(void* out, int32_t* acc_out, const void* a_q
   if (m <= 64) {
     // decode: weights fill the MMA's M dimension, the tokens are the N dimension
     p.swap = 1;
-    p.a_mat = static_cast<const uint8_t*>(w), p.a_stride = w_stride, p.a_scale = w_scale;
-    p.b_mat = static_cast<const uint8_t*>(a_q), p.b_stride = a_stride, p.b_scale = a_scale;
+    p.a_scale = w_scale, p.b_scale = a_scale;
     p.a_rows = int(n), p.b_rows = int(m);
     p.a_tiles = int((n + 127) / 128), p.b_tiles = 1;
-    if (m <= 16) return launch_gemm<16>(p, st);
-    if (m <= 32) return launch_gemm<32>(p, st);
-    return launch_gemm<64>(p, st);
+    if (m <= 16) return launch_gemm<16>(p, w, w_stride, a_q, a_stride, st);
+    if (m <= 32) return launch_gemm<32>(p, w, w_stride, a_q, a_stride, st);
+    return launch_gemm<64>(p, w, w_stride, a_q, a_stride, st);
   }
   p.swap = 0;
-  p.a_mat = static_cast<const uint8_t*>(a_q), p.a_stride = a_stride, p.a_scale = a_scale;
-  p.b_mat = static_cast<const uint8_t*>(w), p.b_stride = w_stride, p.b_scale = w_scale;
+  p.a_scale = a_scale, p.b_scale = w_scale;
   p.a_rows = int(m), p.b_rows = int(n);
   p.a_tiles = int((m + 127) / 128), p.b_tiles = int((n + 255) / 256);
-  return launch_gemm<256>(p, st);
+  return launch_gemm<256>(p, a_q, a_stride, w, w_stride, st);
 }
