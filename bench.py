@@ -341,7 +341,7 @@ def bench_moe_fp8(args, dev, with_cpu: bool) -> dict:
     weights once: GB/s of weight bytes against the HBM roofline is reported
     beside TFLOP/s. Weights (604 MB) exceed the 126 MB L2."""
     import libstrix_b200 as strix
-    from libstrix_b200.moe import Fp8MoeWorkspace, pick_block_m
+    from libstrix_b200.moe import pick_block_m, workspace_for
     from libstrix_b200.workloads import moe_fp8_layer
 
     peak, peak_kind = measured_peaks()
@@ -349,7 +349,7 @@ def bench_moe_fp8(args, dev, with_cpu: bool) -> dict:
            "runs": []}
     for tokens in (256, 4096):
         layer = moe_fp8_layer(tokens=tokens, seed=0, device=dev)
-        ws = Fp8MoeWorkspace(tokens, layer.top_k, 2048, 768, dev)
+        ws = workspace_for(tokens, layer.top_k, 2048, 768, 128, pick_block_m(tokens, layer.top_k, 128), dev)
 
         def step():
             return strix.moe.fused_moe_fp8_w8a8(layer.x, layer.logits, layer.w13, layer.w13_scale,

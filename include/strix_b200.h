@@ -194,11 +194,41 @@ int strix_w8a8_int8_gemm(void* out, int32_t* acc_out, const void* a_q, const flo
  * Synchronises the device; for tests and debugging. No reference counterpart. */
 int strix_umma_status(int32_t* host_out);
 
-/* Tuning hook: widest m-block (block_m) of an FP8 W8A8 strix_moe_gemm call that
- * is served by the tcgen05 kernel; wider ones take the mma.sync streaming kernel.
- * Default 32 (or STRIX_MOE_UMMA_MAX_BLOCK_M); 0 turns the tcgen05 kernel off,
- * 128 sends everything it covers to it. No reference counterpart. */
-int strix_moe_set_umma_max_block_m(int block_m);
+/* The FP8 activation quantiser writing the SORTED layout the tcgen05 grouped
+ * GEMM reads: output row p (p < *num_post_padded, p < rows) holds the quantised
+ * input row sorted_ids[p] / top_k, or zeros with scale 1 for a padding slot
+ * (sorted_ids[p] >= num_valid). With sorted_ids == NULL the rows are quantised
+ * in place order (row p from row p) and only the bound by *num_post_padded
+ * applies - the form used between the two GEMMs. q e4m3 [rows, k], sa fp32
+ * [rows, k / 128]. No counterpart in the reference, whose kernels gather token
+ * rows inside the GEMM (csrc/moe/moe_gemm_w8a16.hip:128-160). */
+int strix_moe_act_quant_fp8_sorted(const void* x, void* q, float* sa, const int32_t* sorted_ids,
+                                   const int32_t* num_post_padded, int64_t rows, int64_t k,
+                                   int64_t top_k, int64_t num_valid, int64_t x_stride,
+                                   int64_t q_stride, int64_t sa_stride, int x_is_f16,
+                                   strix_stream_t stream);
+
+/* FP8 W8A8 grouped expert GEMM on tcgen05 over activations in sorted order
+ * (row p of a / act_scales = sorted position p; see above). Arithmetic and
+ * epilogues are those of strix_moe_gemm with weight_format 0, act_format 2,
+ * fp32 scales (scale_kind 1 channel [E, N] or 2 block [E, N/128, K/128]);
+ * gate_act 0 none (c[row, n] times topk_weights[sid] if given), 1 silu, 2
+ * gelu_tanh (c is [*, n / 2]). c_sorted != 0 writes output row p for every
+ * sorted position of the processed m-blocks (padding rows included), else row
+ * sorted_ids[p] for valid slots only - the contract of the reference's
+ * moe_gemm_fp8 (csrc/moe/moe_gemm_w8a16.hip:581-623). sorted_len counts whole
+ * m-blocks. strix_moe_gemm_fp8_sorted_covers() tells (1/0) whether a geometry
+ * is covered; uncovered ones are rejected. */
+int strix_moe_gemm_fp8_sorted(void* c, const void* a, const float* act_scales, const void* w,
+                              const float* scales, const int32_t* sorted_ids,
+                              const int32_t* expert_ids, const int32_t* num_post_padded,
+                              const float* topk_weights, int64_t num_valid, int64_t n, int64_t k,
+                              int64_t a_stride, int64_t c_stride, int64_t w_stride_e,
+                              int64_t w_stride_n, int64_t s_stride_e, int64_t s_stride_n,
+                              int64_t sa_stride, int64_t sorted_len, int64_t block_m,
+                              int scale_kind, int gate_act, int c_sorted, strix_stream_t stream);
+int strix_moe_gemm_fp8_sorted_covers(int64_t n, int64_t k, int64_t block_m, int gate_act,
+                                     int scale_kind);
 
 /* Tuning aid: cycle counters of CTA 0 of the tcgen05 MoE kernel, accumulated only
  * while the environment variable STRIX_UMMA_PROF is set: [0] issuer waiting for

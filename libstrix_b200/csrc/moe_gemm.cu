@@ -475,14 +475,6 @@ int launch_bm(const MoeArgs& p, int act, dim3 grid, cudaStream_t st) {
 
 }  // namespace
 
-// moe_gemm_umma.cu: the tcgen05 form of the FP8 W8A8 GEMM; -1 = geometry not covered
-int moe_gemm_fp8_umma(void* c, const void* a, const void* w, const float* scales,
-                      const float* act_scales, const int32_t* sorted_ids,
-                      const int32_t* expert_ids, const int32_t* num_post, const float* topk_w,
-                      int64_t num_valid, int64_t n, int64_t k, int64_t a_stride, int64_t c_stride,
-                      int64_t w_se, int64_t w_sn, int64_t s_se, int64_t s_sn, int64_t sa_stride,
-                      int64_t sorted_len, int64_t top_k, int64_t block_m, int scale_kind,
-                      int scale_is_f32, int gate_act, cudaStream_t st);
 }  // namespace strix
 
 using namespace strix;
@@ -523,15 +515,6 @@ extern "C" int strix_moe_gemm(
                   reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0,
               "16-byte aligned rows required");
   if (sorted_len == 0 || num_valid == 0) return STRIX_OK;
-  if (weight_format == W_E4M3 && act_format == A_E4M3) {
-    const int rc = moe_gemm_fp8_umma(
-        c, a, w, static_cast<const float*>(scales), act_scales, sorted_ids, expert_ids,
-        num_post_padded, topk_weights, num_valid, n, k, a_stride, c_stride, w_stride_e, w_stride_n,
-        s_stride_e, s_stride_n, sa_stride, sorted_len, top_k, block_m, scale_kind,
-        scale_dtype == 0, gate_act, static_cast<cudaStream_t>(stream));
-    if (rc != -1) return rc;
-  }
-
   MoeArgs p;
   p.c = c, p.a = a, p.w = w, p.scales = scales, p.sa = act_scales;
   p.sorted_ids = sorted_ids, p.expert_ids = expert_ids, p.num_post = num_post_padded;

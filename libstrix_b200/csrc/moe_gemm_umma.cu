@@ -1,9 +1,15 @@
 // Grouped expert GEMM for FP8 W8A8 experts on the Blackwell tensor cores
 // (tcgen05.mma kind::f8f6f4, accumulators in TMEM), for sm_100a.
 //
-// Same contract as moe_gemm.cu (moe_align_block_size layout, fused gate
-// epilogue, routing weight on the down GEMM; csrc/moe/moe_gemm_w8a16.hip:76-404
-// of the reference). What differs is the machine mapping:
+// Same arithmetic as the FP8 W8A8 form of moe_gemm.cu (moe_align_block_size
+// layout, fused gate epilogue, routing weight on the down GEMM;
+// csrc/moe/moe_gemm_w8a16.hip:76-404 of the reference), but over activations
+// that are already laid out in sorted order: row p of `a` (and of its scales)
+// belongs to sorted position p, so an m-block's tokens are block_m consecutive
+// rows and one TMA box fetches them. The quantiser writes that layout
+// (strix_moe_act_quant_fp8_sorted), the gate-up GEMM can write its output in it
+// too, and the down GEMM scatters to slot order for the combine. What differs
+// from moe_gemm.cu is the machine mapping:
 //
 //   * operands swap roles: a tile of 128 expert-weight rows is the MMA's A (M =
 //     128) and the m-block's tokens are B (N = block_m, 16..128), so a ragged
@@ -12,9 +18,15 @@
 //     exactly once per m-block, straight from shared memory, with no widening;
 //   * one persistent CTA per SM walks work items (m-block, 128-row weight tile)
 //     in a fixed stride; three roles run decoupled through mbarriers:
-//       producers (4 warps)  cp.async weight rows and gathered token rows into an
-//                            8..5-stage ring, in the 128-byte-swizzled K-major
-//                            layout the MMA descriptors expect;
+//       producer (1 thread)  two TMA boxes per K block - 128 weight rows (a 4-d
+//                            box, which also interleaves the gate and up rows)
+//                            and the m-block's token rows - into an 8..5-stage
+//                            ring in the 128-byte-swizzled K-major layout the
+//                            MMA descriptors expect; they complete the stage's
+//                            barrier by byte count;
+//       metadata (1 warp)    a few items ahead: the tokens' slot ids, routing
+//                            weights and activation scales and the tile's weight
+//                            block scales, into shared memory;
 //       issuer (1 thread)    four K=32 MMAs per 128-wide K block into one of the
 //                            TMEM accumulator buffers, then tcgen05.commit to
 //                            free the ring stage and to publish the buffer;
@@ -29,25 +41,24 @@
 #include <cstdlib>
 #include <type_traits>
 
-#include "umma.cuh"
+#include "tma.cuh"
 
 namespace strix {
 namespace {
 
 using namespace umma;
 
-constexpr int kProducerWarps = 4, kConsumerWarps = 4;
-constexpr int kThreadsU = (kProducerWarps + kConsumerWarps + 1) * 32;  // + issuer warp
+constexpr int kProducerWarps = 4, kConsumerWarps = 4;   // warps 0..3: producer, metadata, issuer, spare
+constexpr int kThreadsU = (kProducerWarps + kConsumerWarps) * 32;
+constexpr int kIssuerWarp = 2;
 constexpr int kTileM = 128;   // weight rows per tile (TMEM lanes)
 constexpr int kKBlock = 128;  // K bytes per pipeline step = the scale block
 constexpr int kMaxMBlocks = 2048;  // m-blocks whose expert ids are cached in shared memory
 
 struct UmmaMoeArgs {
   void* c;
-  const uint8_t* a;        // e4m3 [rows, K]
-  const uint8_t* w;        // e4m3 [E, N, K]
   const float* scales;     // block [E, N/128, K/128] or channel [E, N] fp32
-  const float* sa;         // [rows, K/128]
+  const float* sa;         // [sorted rows, K/128]
   const int32_t* sorted_ids;
   const int32_t* expert_ids;
   const int32_t* num_post;
@@ -55,11 +66,13 @@ struct UmmaMoeArgs {
   int32_t* status;
   long long* prof;         // optional cycle counters of CTA 0 (tuning aid), or NULL
   int64_t num_valid;
-  int64_t a_stride, c_stride, w_se, w_sn, s_se, s_sn, sa_stride;
-  int top_k, K, N, block_m;
+  int64_t c_stride, s_se, s_sn, sa_stride;
+  int K, N, block_m;
   int scale_kind;  // 1 channel, 2 block
   int gate_act;    // 0 none, 1 silu, 2 gelu_tanh
   int n_tiles;     // weight tiles per m-block
+  int c_sorted;    // 1: c rows are sorted positions, 0: slot ids (padding skipped)
+  int debug;       // measurement switches (STRIX_UMMA_DEBUG): 1 skip the folds, 2 skip the epilogue
 };
 
 template <int NTOK>
@@ -74,7 +87,10 @@ struct UmmaLayout {
   static constexpr int kTmemCols = NTOK * kAccBufs < 32 ? 32 : NTOK * kAccBufs;
   static constexpr int kMaxKBlocks = NTOK <= 64 ? 64 : 32;  // K <= 8192 (4096 at 128 tokens)
   static constexpr int kSaFloats = kMaxKBlocks * NTOK;      // one item's activation scales
-  static constexpr int kMetaBytes = 2 * (kSaFloats * 4 + NTOK * 4);  // double-buffered per item
+  static constexpr int kSwFloats = kMaxKBlocks * 2;         // weight block scales (gate / up row block)
+  // per item, kMetaBufs deep: activation scales, block scales, slot ids, routing weights
+  static constexpr int kMetaBufs = NTOK <= 32 ? 4 : 2;
+  static constexpr int kMetaBytes = kMetaBufs * (kSaFloats * 4 + kSwFloats * 4 + NTOK * 4 + NTOK * 4);
   static constexpr int kSmem = 1024 + kStages * kStageBytes + kMetaBytes + 1024;
 };
 
@@ -92,18 +108,24 @@ __device__ __forceinline__ int tile_row(int nt, int lane, bool gate, int half_n)
 }
 
 template <int NTOK>
-__global__ void __launch_bounds__(kThreadsU, 1) moe_gemm_umma_kernel(const UmmaMoeArgs p) {
+__global__ void __launch_bounds__(kThreadsU, 1) moe_gemm_umma_kernel(const UmmaMoeArgs p,
+                                                                    const __grid_constant__ CUtensorMap map_w,
+                                                                    const __grid_constant__ CUtensorMap map_a) {
   using L = UmmaLayout<NTOK>;
   constexpr int S = L::kStages, NB = L::kAccBufs;
   extern __shared__ uint8_t raw_smem[];
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
                                              ~uintptr_t(1023));
-  // per-item metadata, double-buffered: activation scales [kb][NTOK] and the
-  // tokens' slot ids (-1 = padding); written by the producers one item ahead
-  float* s_sa = reinterpret_cast<float*>(ring + S * L::kStageBytes);      // [2][kSaFloats]
-  int* s_sid = reinterpret_cast<int*>(s_sa + 2 * L::kSaFloats);           // [2][NTOK]
+  // per-item metadata, MB buffers deep: activation scales [kb][NTOK], weight
+  // block scales, routing weights and the tokens' slot ids (-1 = padding);
+  // written by the metadata warp ahead of the consumers
+  constexpr int MB = L::kMetaBufs;
+  float* s_sa = reinterpret_cast<float*>(ring + S * L::kStageBytes);      // [MB][kSaFloats]
+  float* s_sw = s_sa + MB * L::kSaFloats;                                 // [MB][kb][gate|up]
+  float* s_tw = s_sw + MB * L::kSwFloats;                                 // [MB][NTOK] routing weights
+  int* s_sid = reinterpret_cast<int*>(s_tw + MB * NTOK);                  // [MB][NTOK]
   __shared__ __align__(8) uint64_t full_bar[S], empty_bar[S], tfull_bar[NB], tempty_bar[NB];
-  __shared__ __align__(8) uint64_t meta_empty_bar[2], meta_full_bar[2], landed_bar[S];
+  __shared__ __align__(8) uint64_t meta_empty_bar[MB], meta_full_bar[MB];
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int s_abort;
 
@@ -121,150 +143,119 @@ __global__ void __launch_bounds__(kThreadsU, 1) moe_gemm_umma_kernel(const UmmaM
 
   if (tid == 0) {
     for (int i = 0; i < S; ++i) {
-      mbar_init(&full_bar[i], kProducerWarps);       // one arrive per producer warp
+      mbar_init(&full_bar[i], 1);    // the producer's arrive, which announces the stage's bytes
       mbar_init(&empty_bar[i], 1);
-      mbar_init(&landed_bar[i], kProducerWarps * 32);
     }
     for (int i = 0; i < NB; ++i) {
       mbar_init(&tfull_bar[i], 1);
       mbar_init(&tempty_bar[i], kConsumerWarps);
     }
-    mbar_init(&meta_empty_bar[0], kConsumerWarps);
-    mbar_init(&meta_empty_bar[1], kConsumerWarps);
-    mbar_init(&meta_full_bar[0], kProducerWarps);
-    mbar_init(&meta_full_bar[1], kProducerWarps);
+    for (int i = 0; i < MB; ++i) {
+      mbar_init(&meta_empty_bar[i], kConsumerWarps);
+      mbar_init(&meta_full_bar[i], 1);
+    }
     s_abort = 0;
     fence_mbar_init();
   }
-  if (warp == kProducerWarps + kConsumerWarps) tmem_alloc(&tmem_slot, L::kTmemCols);
+  if (warp == kIssuerWarp) tmem_alloc(&tmem_slot, L::kTmemCols);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = tmem_slot;
   const uint32_t ring_s = smem_u32(ring);
 
-  if (warp < kProducerWarps) {
-    // ------------------------------------------------------------ producers
-    // A non-blocking loop with two duties, so that neither can starve the other:
-    //   issue    when the next ring stage is free (its MMAs retired), copy the next
-    //            K block into it; the copies report to the stage's `landed`
-    //            barrier by themselves (cp.async.mbarrier.arrive);
-    //   publish  when the oldest unpublished stage has landed, make its bytes
-    //            visible to the tensor core's async proxy and arrive on `full`.
-    const int ch = tid & 7, r0 = tid >> 3;                    // chunk, first row (0..15)
-    const uint32_t dst0 = uint32_t(r0 * 128 + ((ch ^ (r0 & 7)) << 4));  // rows r0 + 16 i: + 2048 i
-    constexpr int NCB = NTOK * 8 / 128 > 0 ? NTOK * 8 / 128 : 1;
-    // Slot ids of the rows this thread copies (and of token tid % NTOK for the
-    // metadata) are fetched one item ahead: a global-memory round trip per item
-    // on the producers' critical path would drain the ring between items.
-    int pre_rows[NCB], pre_tok = -1;
-    auto prefetch_ids = [&](int item) {
+  // next valid item at or after `item` (items of skipped m-blocks are passed over)
+  auto next_valid = [&](int item) {
+    while (item < total_items && s_expert[item / p.n_tiles] < 0) item += gridDim.x;
+    return item;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- producer
+    if (lane == 0) {
+      tma::prefetch_map(&map_w);
+      tma::prefetch_map(&map_a);
+      int t = 0;
+      bool dead = false;
+      for (int item = next_valid(blockIdx.x); item < total_items && !dead;
+           item = next_valid(item + gridDim.x)) {
+        const int mb = item / p.n_tiles, nt = item - mb * p.n_tiles;
+        const int expert = s_expert[mb];
+        const int w_row = nt * (gate ? kTileM / 2 : kTileM);
+        for (int kb = 0; kb < nkb; ++kb, ++t) {
+          const int s = t % S;
+          if (!mbar_wait(&empty_bar[s], ((t / S) & 1) ^ 1) || s_abort) {   // its MMAs retired
+            dead = true;
+            break;
+          }
+          const uint32_t st = ring_s + s * L::kStageBytes;
+          tma::mbar_expect_tx(&full_bar[s], L::kStageBytes);
+          tma::load_4d(st, &map_w, kb * kKBlock, 0, w_row, expert, &full_bar[s]);
+          tma::load_2d(st + L::kABytes, &map_a, kb * kKBlock, mb * NTOK, &full_bar[s]);
+        }
+      }
+      if (dead) atomicExch(p.status, 1), s_abort = 1;
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- metadata
+    int pre_sid[NTOK / 32 > 0 ? NTOK / 32 : 1];
+    constexpr int NR = NTOK / 32 > 0 ? NTOK / 32 : 1;
+    auto fetch_ids = [&](int item) {
       const int mb = item / p.n_tiles;
 #pragma unroll
-      for (int i = 0; i < NCB; ++i) {
-        const int r = r0 + 16 * i;
-        pre_rows[i] = (item < total_items && r < NTOK && r < p.block_m)
-                          ? p.sorted_ids[mb * p.block_m + r] : -1;
+      for (int i = 0; i < NR; ++i) {
+        const int r = lane + 32 * i;
+        pre_sid[i] = (item < total_items && r < NTOK && r < p.block_m)
+                         ? p.sorted_ids[mb * p.block_m + r] : -1;
       }
-      const int j = tid % NTOK;
-      pre_tok = (item < total_items && j < p.block_m) ? p.sorted_ids[mb * p.block_m + j] : -1;
     };
-    // next valid item at or after `item` (items of skipped m-blocks are passed over)
-    auto next_valid = [&](int item) {
-      while (item < total_items && s_expert[item / p.n_tiles] < 0) item += gridDim.x;
-      return item;
-    };
-
-    int item = next_valid(blockIdx.x);   // item being issued
-    prefetch_ids(item);
-    int kb = nkb;                        // K block to issue next; nkb = "open the item first"
-    int issued = 0, pub = 0, li = 0;     // steps issued / published, items opened
-    const uint8_t* wsrc[8];
-    const uint8_t* asrc[NCB];
-    bool aok[NCB];
+    int item = next_valid(blockIdx.x), li = 0;
+    fetch_ids(item);
     bool dead = false;
-    uint32_t idle = 0;
-    while (!dead && (item < total_items || pub < issued)) {
-      bool progressed = false;
-      // ---- open the next item: pointers + metadata (needs a free metadata buffer)
-      if (item < total_items && kb == nkb) {
-        const int buf = li & 1;
-        if (__all_sync(0xffffffffu, mbar_test(&meta_empty_bar[buf], ((li >> 1) & 1) ^ 1))) {
-          const int mb = item / p.n_tiles, nt = item - mb * p.n_tiles;
-          const int expert = s_expert[mb];
+    while (item < total_items && !dead) {
+      const int buf = li % MB;
+      const bool free_ok = mbar_wait(&meta_empty_bar[buf], ((li / MB) & 1) ^ 1);
+      if (__any_sync(0xffffffffu, !free_ok || s_abort != 0)) {
+        dead = true;
+        break;
+      }
+      const int mb = item / p.n_tiles, nt = item - mb * p.n_tiles;
+      const int expert = s_expert[mb];
+      const uint32_t sa_dst = smem_u32(s_sa + buf * L::kSaFloats);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int row = tile_row(nt, r0 + 16 * i, gate, half_n);
-            wsrc[i] = p.w + int64_t(expert) * p.w_se + int64_t(row) * p.w_sn + ch * 16;
-          }
-#pragma unroll
-          for (int i = 0; i < NCB; ++i) {
-            const int64_t sid = pre_rows[i];
-            aok[i] = sid >= 0 && sid < p.num_valid;
-            asrc[i] = p.a + (aok[i] ? sid / p.top_k : 0) * p.a_stride + ch * 16;
-          }
-          // metadata for the consumers; it rides the item's first copy group
-          const int j = tid % NTOK;
-          const int64_t sid = pre_tok;
-          const bool ok = sid >= 0 && sid < p.num_valid;
-          if (tid < NTOK) s_sid[buf * NTOK + j] = ok ? int(sid) : -1;
-          const float* sap = p.sa + (ok ? sid / p.top_k : 0) * p.sa_stride;
-          const uint32_t sa_dst = smem_u32(s_sa + buf * L::kSaFloats);
-          for (int k2 = tid / NTOK; k2 < nkb; k2 += 128 / NTOK)
-            cp_async_4_zfill(sa_dst + (k2 * NTOK + j) * 4, sap + k2, ok);
-          prefetch_ids(next_valid(item + gridDim.x));
-          kb = 0;
-          ++li;
-          progressed = true;
+      for (int i = 0; i < NR; ++i) {
+        const int j = lane + 32 * i;
+        if (j >= NTOK) continue;
+        const int64_t sid = pre_sid[i];
+        const bool ok = sid >= 0 && sid < p.num_valid;
+        s_sid[buf * NTOK + j] = ok ? int(sid) : -1;
+        if (p.topk_w != nullptr)
+          cp_async_4_zfill(smem_u32(s_tw + buf * NTOK + j), p.topk_w + (ok ? sid : 0), ok);
+        else
+          s_tw[buf * NTOK + j] = 1.f;
+        const float* sap = p.sa + (int64_t(mb) * NTOK + j) * p.sa_stride;
+        for (int k2 = 0; k2 < nkb; ++k2) cp_async_4(sa_dst + (k2 * NTOK + j) * 4, sap + k2);
+      }
+      // the tile's weight block scales, one per K block and per row block (the
+      // gate rows and the up rows of a tile lie in two different 128-row blocks)
+      if (p.scale_kind == 2) {
+        for (int i = lane; i < 2 * nkb; i += 32) {
+          const int k2 = i >> 1, par = i & 1;
+          const int blk = gate ? ((par ? half_n : 0) + nt * (kTileM / 2)) / 128 : nt;
+          cp_async_4(smem_u32(s_sw + buf * L::kSwFloats + i),
+                     p.scales + int64_t(expert) * p.s_se + int64_t(blk) * p.s_sn + k2);
         }
       }
-      // ---- issue one K block
-      if (item < total_items && kb < nkb) {
-        const int s = issued % S;
-        if (__all_sync(0xffffffffu, mbar_test(&empty_bar[s], ((issued / S) & 1) ^ 1))) {
-          const uint32_t st = ring_s + s * L::kStageBytes;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            cp_async_16(st + dst0 + 2048 * i, wsrc[i]);
-            wsrc[i] += kKBlock;
-          }
-#pragma unroll
-          for (int i = 0; i < NCB; ++i) {
-            if (r0 + 16 * i < NTOK)
-              cp_async_16_zfill(st + L::kABytes + dst0 + 2048 * i, asrc[i] + kb * kKBlock, aok[i]);
-          }
-          mbar_arrive_cp_async(&landed_bar[s]);   // fires when this thread's copies land
-          ++issued;
-          if (++kb == nkb) item = next_valid(item + gridDim.x);
-          progressed = true;
-        }
-      }
-      // ---- publish the oldest stage whose copies (all 128 threads') have landed
-      if (pub < issued) {
-        const int s = pub % S;
-        if (__all_sync(0xffffffffu, mbar_test(&landed_bar[s], (pub / S) & 1))) {
-          fence_proxy_async();     // each thread fences its own copies ...
-          __syncwarp();            // ... then one lane arrives for the warp: 128
-          if (lane == 0) {         // arrives on one shared word would serialise
-            mbar_arrive(&full_bar[s]);
-            // every item has nkb steps, so step u opens item u / nkb: its metadata landed too
-            if (pub % nkb == 0) mbar_arrive(&meta_full_bar[(pub / nkb) & 1]);
-          }
-          ++pub;
-          progressed = true;
-        }
-      }
-      if (progressed) {
-        idle = 0;
-      } else {
-        __nanosleep(200);   // leave the issue slots to the consumer warps
-        // warp-uniform, like every other decision in this loop (it holds warp votes)
-        if (__any_sync(0xffffffffu, ++idle > (kSpinLimit >> 4) || s_abort != 0)) dead = true;
-      }
+      item = next_valid(item + gridDim.x);
+      fetch_ids(item);            // in flight while this item's copies land
+      cp_async_commit();
+      cp_async_wait<0>();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&meta_full_bar[buf]);
+      ++li;
     }
-    cp_async_wait<0>();
-    if (dead) atomicExch(p.status, 1), s_abort = 1;
-  } else if (warp == kProducerWarps + kConsumerWarps) {
+    if (dead && lane == 0) atomicExch(p.status, 1), s_abort = 1;
+  } else if (warp == kIssuerWarp) {
     // --------------------------------------------------------------- issuer
     if (lane == 0) {
       const uint32_t idesc = instr_desc(D_F32, 0, 0, kTileM, NTOK);
@@ -292,7 +283,7 @@ __global__ void __launch_bounds__(kThreadsU, 1) moe_gemm_umma_kernel(const UmmaM
           tc_fence_after_sync();
           const uint32_t sa_addr = ring_s + s * L::kStageBytes, sb_addr = sa_addr + L::kABytes;
 #pragma unroll
-          for (int k4 = 0; k4 < 4; ++k4)
+          for (int k4 = 0; k4 < 4 && !(p.debug & 8); ++k4)
             mma_ss<KIND_F8F6F4>(tmem + b * NTOK, smem_desc_sw128(sa_addr, 32 * k4),
                                 smem_desc_sw128(sb_addr, 32 * k4), idesc, k4 > 0 ? 1u : 0u);
           mma_commit(&empty_bar[s]);   // the stage may be refilled
@@ -301,7 +292,7 @@ __global__ void __launch_bounds__(kThreadsU, 1) moe_gemm_umma_kernel(const UmmaM
       }
       if (dead) atomicExch(p.status, 1), s_abort = 1;
     }
-  } else {
+  } else if (warp >= kProducerWarps) {
     // ------------------------------------------------------------ consumers
     const int ctid = tid - kProducerWarps * 32;      // 0..127 = TMEM lane = tile row
     const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
@@ -314,13 +305,11 @@ __global__ void __launch_bounds__(kThreadsU, 1) moe_gemm_umma_kernel(const UmmaM
       if (expert < 0) continue;
       // this row's scales: the loads are in flight while the item's data arrives
       const int row = tile_row(nt, ctid, gate, half_n);
-      const float* swp = p.scales + int64_t(expert) * p.s_se + int64_t(row / 128) * p.s_sn;
-      float sw_next = p.scale_kind == 2 ? swp[0] : 1.f;
       const float chs = p.scale_kind == 1 ? p.scales[int64_t(expert) * p.s_se + row] : 1.f;
       // the producers wrote this item's token ids and activation scales
-      const int buf = li & 1;
+      const int buf = li % MB;
       const long long m0 = clock64();
-      const bool meta_ok = mbar_wait(&meta_full_bar[buf], (li >> 1) & 1);
+      const bool meta_ok = mbar_wait(&meta_full_bar[buf], (li / MB) & 1);
       if (p.prof != nullptr && blockIdx.x == 0 && ctid == 0) p.prof[6] += clock64() - m0;
       if (__any_sync(0xffffffffu, !meta_ok) || s_abort) {
         dead = true;
@@ -328,6 +317,8 @@ __global__ void __launch_bounds__(kThreadsU, 1) moe_gemm_umma_kernel(const UmmaM
       }
       const float* sa_item = s_sa + buf * L::kSaFloats;
       const int* sid_item = s_sid + buf * NTOK;
+      const float* sw_item = s_sw + buf * L::kSwFloats + (gate ? (ctid & 1) : 0);
+      const float* tw_item = s_tw + buf * NTOK;
       float acc[NTOK];
 #pragma unroll
       for (int j = 0; j < NTOK; ++j) acc[j] = 0.f;
@@ -351,6 +342,7 @@ __global__ void __launch_bounds__(kThreadsU, 1) moe_gemm_umma_kernel(const UmmaM
           }
           tc_fence_after_sync();
         }
+        if (p.debug & 16) return;
         if constexpr (CH == 32) tmem_ld_32x32(tmem + lane_base + b * NTOK + c * CH, r);
         else tmem_ld_32x16(tmem + lane_base + b * NTOK + c * CH, r);
       };
@@ -371,8 +363,7 @@ __global__ void __launch_bounds__(kThreadsU, 1) moe_gemm_umma_kernel(const UmmaM
           constexpr int PAR = decltype(par)::value;
           const int kb = kb2 + PAR;
           if (kb >= nkb || dead) return;
-          const float sw = sw_next;
-          if (p.scale_kind == 2 && kb + 1 < nkb) sw_next = swp[kb + 1];
+          const float sw = p.scale_kind == 2 ? sw_item[2 * kb] : 1.f;
           const float* sak = sa_item + kb * NTOK;
           auto chunk = [&](auto cc) {
             constexpr int C = decltype(cc)::value;
@@ -383,7 +374,7 @@ __global__ void __launch_bounds__(kThreadsU, 1) moe_gemm_umma_kernel(const UmmaM
             const bool more = nkb_ < nkb;
             if (more) issue_ld(nkb_, nc, R[BUF ^ 1]);
 #pragma unroll
-            for (int j = 0; j < CH; j += 4) {
+            for (int j = 0; j < CH && !(p.debug & 1); j += 4) {
               const float4 s4 = *reinterpret_cast<const float4*>(sak + C * CH + j);
               acc[C * CH + j] = fmaf(__uint_as_float(R[BUF][j]), sw * s4.x, acc[C * CH + j]);
               acc[C * CH + j + 1] = fmaf(__uint_as_float(R[BUF][j + 1]), sw * s4.y, acc[C * CH + j + 1]);
@@ -412,29 +403,23 @@ __global__ void __launch_bounds__(kThreadsU, 1) moe_gemm_umma_kernel(const UmmaM
 
       // ---- epilogue of the item: this thread owns weight row `row`, all tokens
       const long long ep0 = clock64();
-      if (gate) {
+      if (p.debug & 2) {
+      } else if (gate) {
         __nv_bfloat16* cbase = static_cast<__nv_bfloat16*>(p.c) + nt * (kTileM / 2) + (ctid >> 1);
 #pragma unroll
         for (int j = 0; j < NTOK; ++j) {
           const float v = acc[j] * chs;
           const float other = __shfl_xor_sync(0xffffffffu, v, 1);  // even lane: gate, odd: up
-          const int sid = sid_item[j];
-          if (sid >= 0 && (ctid & 1) == 0)
-            cbase[int64_t(sid) * p.c_stride] = __float2bfloat16_rn(gate_fn(v, p.gate_act) * other);
+          const int crow = p.c_sorted ? mb * NTOK + j : sid_item[j];
+          if (crow >= 0 && (ctid & 1) == 0)
+            cbase[int64_t(crow) * p.c_stride] = __float2bfloat16_rn(gate_fn(v, p.gate_act) * other);
         }
       } else {
         __nv_bfloat16* cbase = static_cast<__nv_bfloat16*>(p.c) + row;
-        // routing weights first (independent loads in flight together), stores after
 #pragma unroll
         for (int j = 0; j < NTOK; ++j) {
-          const int sid = sid_item[j];
-          const float tw = (sid >= 0 && p.topk_w) ? __ldg(p.topk_w + sid) : 1.f;
-          acc[j] *= chs * tw;
-        }
-#pragma unroll
-        for (int j = 0; j < NTOK; ++j) {
-          const int sid = sid_item[j];
-          if (sid >= 0) cbase[int64_t(sid) * p.c_stride] = __float2bfloat16_rn(acc[j]);
+          const int crow = p.c_sorted ? mb * NTOK + j : sid_item[j];
+          if (crow >= 0) cbase[int64_t(crow) * p.c_stride] = __float2bfloat16_rn(acc[j] * chs * tw_item[j]);
         }
       }
       __syncwarp();
@@ -449,7 +434,7 @@ __global__ void __launch_bounds__(kThreadsU, 1) moe_gemm_umma_kernel(const UmmaM
   // ---- teardown: all roles meet, then the allocating warp frees TMEM
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == kProducerWarps + kConsumerWarps) tmem_dealloc(tmem, L::kTmemCols);
+  if (warp == kIssuerWarp) tmem_dealloc(tmem, L::kTmemCols);
 }
 
 // Status word the kernels raise when a bounded wait runs out (0 = healthy).
@@ -461,7 +446,8 @@ __device__ int32_t g_umma_status = 0;
 __device__ long long g_umma_prof[8] = {};
 
 template <int NTOK>
-int launch_umma(const UmmaMoeArgs& p, cudaStream_t st) {
+int launch_umma(const UmmaMoeArgs& p, const CUtensorMap& map_w, const CUtensorMap& map_a,
+                cudaStream_t st) {
   using L = UmmaLayout<NTOK>;
   auto kernel = moe_gemm_umma_kernel<NTOK>;
   static bool done[64] = {};
@@ -474,7 +460,7 @@ int launch_umma(const UmmaMoeArgs& p, cudaStream_t st) {
     STRIX_CUDA(cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev));
     done[dev] = true;
   }
-  kernel<<<sms[dev], kThreadsU, L::kSmem, st>>>(p);
+  kernel<<<sms[dev], kThreadsU, L::kSmem, st>>>(p, map_w, map_a);
   return launch_status("moe_gemm_umma");
 }
 
@@ -487,42 +473,52 @@ int32_t* umma_status_ptr() {
                                                                     : nullptr;
 }
 
-// Widest m-block the tcgen05 kernel takes (wider ones go to the streaming kernel).
-int g_umma_max_block_m = [] {
-  const char* e = getenv("STRIX_MOE_UMMA_MAX_BLOCK_M");
-  return e ? atoi(e) : 32;
-}();
-
-// FP8 W8A8 grouped GEMM on tcgen05. Returns -1 when the geometry is not covered
-// (the caller then takes the mma.sync weight-streaming kernel), else a status.
-int moe_gemm_fp8_umma(void* c, const void* a, const void* w, const float* scales,
-                      const float* act_scales, const int32_t* sorted_ids,
-                      const int32_t* expert_ids, const int32_t* num_post, const float* topk_w,
-                      int64_t num_valid, int64_t n, int64_t k, int64_t a_stride, int64_t c_stride,
-                      int64_t w_se, int64_t w_sn, int64_t s_se, int64_t s_sn, int64_t sa_stride,
-                      int64_t sorted_len, int64_t top_k, int64_t block_m, int scale_kind,
-                      int scale_is_f32, int gate_act, cudaStream_t st) {
-  static const bool disabled = getenv("STRIX_MOE_NO_UMMA") != nullptr;
-  // Measured on B200 (256 and 4,096 tokens, 128 experts, top-8): with the fp32
-  // promotion of every K block the consumer warps, not the tensor core, set the
-  // pace; up to 32 tokens per m-block this kernel matches the mma.sync streaming
-  // kernel, beyond that the streaming kernel is ahead, so wider blocks go there
-  // unless STRIX_MOE_UMMA_MAX_BLOCK_M raises the limit.
-  if (block_m > g_umma_max_block_m) return -1;
+// Whether the tcgen05 kernel covers a geometry (the entry point below rejects the rest).
+static bool sorted_covers(int64_t n, int64_t k, int64_t block_m, int gate_act, int scale_kind) {
   const int64_t out_rows = gate_act ? n / 2 : n;
   const int tile_out = gate_act ? kTileM / 2 : kTileM;
-  if (disabled || !scale_is_f32 || block_m < 16 || block_m > 128 || block_m % 16 != 0 ||
-      out_rows % tile_out != 0 || k % kKBlock != 0 || k > (block_m > 64 ? 32 : 64) * kKBlock ||
-      (scale_kind == 2 && gate_act && (n / 2) % 128 != 0) || sorted_len < block_m ||
-      sorted_len / block_m > kMaxMBlocks)
-    return -1;
+  return (block_m == 16 || block_m == 32 || block_m == 64 || block_m == 128) && n > 0 && k > 0 &&
+         n % 2 == 0 && out_rows % tile_out == 0 && k % kKBlock == 0 &&
+         k <= (block_m > 64 ? 32 : 64) * kKBlock && (scale_kind == 1 || scale_kind == 2) &&
+         !(scale_kind == 2 && gate_act && (n / 2) % 128 != 0);
+}
+
+}  // namespace strix
+
+using namespace strix;
+
+extern "C" int strix_moe_gemm_fp8_sorted_covers(int64_t n, int64_t k, int64_t block_m, int gate_act,
+                                                int scale_kind) {
+  return sorted_covers(n, k, block_m, gate_act, scale_kind) ? 1 : 0;
+}
+
+extern "C" int strix_moe_gemm_fp8_sorted(
+    void* c, const void* a, const float* act_scales, const void* w, const float* scales,
+    const int32_t* sorted_ids, const int32_t* expert_ids, const int32_t* num_post_padded,
+    const float* topk_weights, int64_t num_valid, int64_t n, int64_t k, int64_t a_stride,
+    int64_t c_stride, int64_t w_stride_e, int64_t w_stride_n, int64_t s_stride_e,
+    int64_t s_stride_n, int64_t sa_stride, int64_t sorted_len, int64_t block_m, int scale_kind,
+    int gate_act, int c_sorted, strix_stream_t stream) {
+  STRIX_CHECK(gate_act >= 0 && gate_act <= 2, "activation must be none, silu or gelu_tanh");
+  STRIX_CHECK(sorted_covers(n, k, block_m, gate_act, scale_kind),
+              "geometry not covered: block_m in 16/32/64/128, K %% 128, K <= 8192 (4096 at 128 "
+              "tokens), whole 128-row weight tiles, channel or 128x128 block scales");
+  STRIX_CHECK(sorted_len % block_m == 0 && sorted_len / block_m <= kMaxMBlocks,
+              "sorted_len must be whole m-blocks, at most %d of them", kMaxMBlocks);
+  STRIX_CHECK(gate_act == 0 || topk_weights == nullptr, "the fused gate takes no routing weights");
+  STRIX_CHECK(w_stride_n % 16 == 0 && w_stride_e % 16 == 0 && a_stride % 16 == 0 &&
+                  reinterpret_cast<uintptr_t>(w) % 16 == 0 && reinterpret_cast<uintptr_t>(a) % 16 == 0,
+              "16-byte aligned rows required");
+  STRIX_CHECK(sa_stride >= k / kKBlock, "act_scales must be [sorted_len, K / 128]");
+  if (sorted_len == 0 || num_valid == 0) return STRIX_OK;
+  const int64_t out_rows = gate_act ? n / 2 : n;
+  const int tile_out = gate_act ? kTileM / 2 : kTileM;
   UmmaMoeArgs p;
-  p.c = c, p.a = static_cast<const uint8_t*>(a), p.w = static_cast<const uint8_t*>(w);
-  p.scales = scales, p.sa = act_scales;
-  p.sorted_ids = sorted_ids, p.expert_ids = expert_ids, p.num_post = num_post, p.topk_w = topk_w;
-  void* status_addr = nullptr;
-  STRIX_CUDA(cudaGetSymbolAddress(&status_addr, g_umma_status));
-  p.status = static_cast<int32_t*>(status_addr);
+  p.c = c, p.scales = scales, p.sa = act_scales;
+  p.sorted_ids = sorted_ids, p.expert_ids = expert_ids, p.num_post = num_post_padded;
+  p.topk_w = topk_weights;
+  p.status = umma_status_ptr();
+  STRIX_CHECK(p.status != nullptr, "status word unavailable");
   static const bool profiling = getenv("STRIX_UMMA_PROF") != nullptr;
   p.prof = nullptr;
   if (profiling) {
@@ -531,26 +527,30 @@ int moe_gemm_fp8_umma(void* c, const void* a, const void* w, const float* scales
     p.prof = static_cast<long long*>(prof_addr);
   }
   p.num_valid = num_valid;
-  p.a_stride = a_stride, p.c_stride = c_stride, p.w_se = w_se, p.w_sn = w_sn;
-  p.s_se = s_se, p.s_sn = s_sn, p.sa_stride = sa_stride;
-  p.top_k = int(top_k), p.K = int(k), p.N = int(n), p.block_m = int(block_m);
-  p.scale_kind = scale_kind, p.gate_act = gate_act;
+  p.c_stride = c_stride, p.s_se = s_stride_e, p.s_sn = s_stride_n, p.sa_stride = sa_stride;
+  p.K = int(k), p.N = int(n), p.block_m = int(block_m);
+  p.scale_kind = scale_kind, p.gate_act = gate_act, p.c_sorted = c_sorted;
   p.n_tiles = int(out_rows / tile_out);
-  if (block_m <= 16) return launch_umma<16>(p, st);
-  if (block_m <= 32) return launch_umma<32>(p, st);
-  if (block_m <= 64) return launch_umma<64>(p, st);
-  return launch_umma<128>(p, st);
-}
-
-}  // namespace strix
-
-// 0 while every tcgen05 kernel launched so far met its waits; 1 after one of
-// them gave up on a bounded wait (its output is then incomplete). Synchronises
-// the device; meant for tests and debugging.
-extern "C" int strix_moe_set_umma_max_block_m(int block_m) {
-  STRIX_CHECK(block_m >= 0 && block_m <= 128, "block_m limit must be in 0..128");
-  strix::g_umma_max_block_m = block_m;
-  return STRIX_OK;
+  static const int debug = [] { const char* e = getenv("STRIX_UMMA_DEBUG"); return e ? atoi(e) : 0; }();
+  p.debug = debug;
+  // Weights as a 4-d byte tensor (k, half, row, expert): under the fused gate
+  // `half` steps from the gate rows to the up rows, so a box of 2 x 64 rows lands
+  // as gate row i / up row i alternating; otherwise it has extent 1. The expert
+  // extent is an upper bound (expert ids index it).
+  const uint64_t halves = gate_act ? 2 : 1, rows = uint64_t(out_rows);
+  const uint64_t dims[4] = {uint64_t(k), halves, rows, uint64_t(1) << 16};
+  const uint64_t strides[3] = {uint64_t(w_stride_n) * rows, uint64_t(w_stride_n), uint64_t(w_stride_e)};
+  const uint32_t box[4] = {128, uint32_t(halves), uint32_t(tile_out), 1};
+  CUtensorMap map_w, map_a;
+  STRIX_CHECK(tma::make_map_u8_nd(&map_w, w, 4, dims, strides, box) &&
+                  tma::make_map_u8(&map_a, a, uint64_t(sorted_len), uint64_t(k), uint64_t(a_stride),
+                                   uint32_t(block_m)),
+              "tensor map encoding failed");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (block_m == 16) return launch_umma<16>(p, map_w, map_a, st);
+  if (block_m == 32) return launch_umma<32>(p, map_w, map_a, st);
+  if (block_m == 64) return launch_umma<64>(p, map_w, map_a, st);
+  return launch_umma<128>(p, map_w, map_a, st);
 }
 
 extern "C" int strix_umma_prof(int64_t* host_out8, int reset) {

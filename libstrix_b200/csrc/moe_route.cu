@@ -158,19 +158,36 @@ __global__ void __launch_bounds__(kAlignThreads) moe_align_kernel(
 
 // ------------------------------------------------------- activation quantisers
 // 16 lanes share one 128-element group (8 elements = 16 bytes each).
+// With `row_map` (the sorted ids of moe_align_block_size) output row r is the
+// quantised input row row_map[r] / top_k - the activations in sorted order, a
+// row of zeros (scale 1) for a padding slot; `row_limit` (the padded slot count,
+// on the device) bounds the rows that are written at all.
 template <bool FP8, bool IN_F16>
 __global__ void __launch_bounds__(256) act_quant_kernel(
     const uint16_t* __restrict__ x, int64_t x_stride, uint8_t* __restrict__ q, int64_t q_stride,
-    float* __restrict__ sa, int64_t sa_stride, int64_t rows, int groups) {
+    float* __restrict__ sa, int64_t sa_stride, int64_t rows, int groups,
+    const int32_t* __restrict__ row_map, const int32_t* __restrict__ row_limit, int top_k,
+    int64_t num_valid) {
   int64_t team = (int64_t(blockIdx.x) * 256 + threadIdx.x) >> 4;
   const int sub = threadIdx.x & 15;
   // out-of-range teams redo the last group and skip the stores, so every lane
   // of the warp stays in the shuffles below
-  const bool live = team < rows * groups;
+  bool live = team < rows * groups;
   if (!live) team = rows * groups - 1;
   const int64_t r = team / groups;
   const int gi = int(team % groups);
-  const uint4 w = *reinterpret_cast<const uint4*>(x + r * x_stride + gi * 128 + sub * 8);
+  if (row_limit != nullptr && r >= *row_limit) live = false;
+  int64_t src = r;
+  bool filled = true;
+  if (row_map != nullptr) {
+    const int64_t sid = live ? row_map[r] : -1;
+    filled = sid >= 0 && sid < num_valid;
+    src = filled ? sid / top_k : 0;
+  } else if (!live) {
+    src = 0;
+  }
+  uint4 w = make_uint4(0u, 0u, 0u, 0u);
+  if (filled) w = *reinterpret_cast<const uint4*>(x + src * x_stride + gi * 128 + sub * 8);
   const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
   float v[8];
 #pragma unroll
@@ -303,7 +320,9 @@ extern "C" int strix_moe_align(const int32_t* topk_ids, int32_t* sorted_ids, int
 
 static int act_quant_common(const void* x, void* q, float* sa, int64_t rows, int64_t k,
                             int64_t x_stride, int64_t q_stride, int64_t sa_stride, int x_is_f16,
-                            bool fp8, strix_stream_t stream) {
+                            bool fp8, strix_stream_t stream, const int32_t* row_map = nullptr,
+                            const int32_t* row_limit = nullptr, int top_k = 1,
+                            int64_t num_valid = 0) {
   STRIX_CHECK(rows >= 0 && k > 0 && k % 128 == 0, "K must be a multiple of 128");
   STRIX_CHECK(x_stride % 8 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 &&
                   q_stride % 8 == 0 && reinterpret_cast<uintptr_t>(q) % 8 == 0,
@@ -317,11 +336,11 @@ static int act_quant_common(const void* x, void* q, float* sa, int64_t rows, int
   auto xp = static_cast<const uint16_t*>(x);
   auto qp = static_cast<uint8_t*>(q);
   if (fp8) {
-    if (x_is_f16) act_quant_kernel<true, true><<<grid, 256, 0, st>>>(xp, x_stride, qp, q_stride, sa, sa_stride, rows, groups);
-    else act_quant_kernel<true, false><<<grid, 256, 0, st>>>(xp, x_stride, qp, q_stride, sa, sa_stride, rows, groups);
+    if (x_is_f16) act_quant_kernel<true, true><<<grid, 256, 0, st>>>(xp, x_stride, qp, q_stride, sa, sa_stride, rows, groups, row_map, row_limit, top_k, num_valid);
+    else act_quant_kernel<true, false><<<grid, 256, 0, st>>>(xp, x_stride, qp, q_stride, sa, sa_stride, rows, groups, row_map, row_limit, top_k, num_valid);
   } else {
-    if (x_is_f16) act_quant_kernel<false, true><<<grid, 256, 0, st>>>(xp, x_stride, qp, q_stride, sa, sa_stride, rows, groups);
-    else act_quant_kernel<false, false><<<grid, 256, 0, st>>>(xp, x_stride, qp, q_stride, sa, sa_stride, rows, groups);
+    if (x_is_f16) act_quant_kernel<false, true><<<grid, 256, 0, st>>>(xp, x_stride, qp, q_stride, sa, sa_stride, rows, groups, row_map, row_limit, top_k, num_valid);
+    else act_quant_kernel<false, false><<<grid, 256, 0, st>>>(xp, x_stride, qp, q_stride, sa, sa_stride, rows, groups, row_map, row_limit, top_k, num_valid);
   }
   return launch_status("moe_act_quant");
 }
@@ -336,6 +355,19 @@ extern "C" int strix_moe_act_quant_fp8(const void* x, void* q, float* sa, int64_
                                        int64_t x_stride, int64_t q_stride, int64_t sa_stride,
                                        int x_is_f16, strix_stream_t stream) {
   return act_quant_common(x, q, sa, rows, k, x_stride, q_stride, sa_stride, x_is_f16, true, stream);
+}
+
+extern "C" int strix_moe_act_quant_fp8_sorted(const void* x, void* q, float* sa,
+                                              const int32_t* sorted_ids,
+                                              const int32_t* num_post_padded, int64_t rows,
+                                              int64_t k, int64_t top_k, int64_t num_valid,
+                                              int64_t x_stride, int64_t q_stride,
+                                              int64_t sa_stride, int x_is_f16,
+                                              strix_stream_t stream) {
+  STRIX_CHECK(num_post_padded != nullptr, "num_post_padded must not be NULL");
+  STRIX_CHECK(top_k >= 1 && num_valid >= 0, "bad top_k / num_valid");
+  return act_quant_common(x, q, sa, rows, k, x_stride, q_stride, sa_stride, x_is_f16, true, stream,
+                          sorted_ids, num_post_padded, int(top_k), num_valid);
 }
 
 extern "C" int strix_moe_sum(const void* in, void* out, int64_t tokens, int64_t top_k,

@@ -50,6 +50,22 @@ inline bool make_map_u8(CUtensorMap* map, const void* base, uint64_t rows, uint6
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Map over bytes with up to 4 dimensions: dims[0] = bytes per row (stride 1),
+// dims[i] with byte strides[i - 1] for i >= 1 (multiples of 16, in any order of
+// magnitude, which lets a box interleave rows of two regions), box[0] = 128.
+inline bool make_map_u8_nd(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
+                           const uint64_t* strides, const uint32_t* box) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn || rank < 2 || rank > 4) return false;
+  cuuint64_t d[4], st[3];
+  cuuint32_t b[4], estr[4];
+  for (int i = 0; i < rank; ++i) d[i] = dims[i], b[i] = box[i], estr[i] = 1;
+  for (int i = 0; i + 1 < rank; ++i) st[i] = strides[i];
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, cuuint32_t(rank), const_cast<void*>(base), d, st, b,
+            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 __device__ __forceinline__ void prefetch_map(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
@@ -69,6 +85,16 @@ __device__ __forceinline__ void load_2d(uint32_t smem_dst, const CUtensorMap* ma
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
           smem_dst),
       "l"(reinterpret_cast<uint64_t>(map)), "r"(umma::smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void load_4d(uint32_t smem_dst, const CUtensorMap* map, int c0, int c1,
+                                        int c2, int c3, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(
+          smem_dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(umma::smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2),
+      "r"(c3)
       : "memory");
 }
 

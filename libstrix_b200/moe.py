@@ -54,38 +54,87 @@ def act_quant_fp8(x: torch.Tensor):
 
 
 class Fp8MoeWorkspace:
-    """Intermediate buffers of one layer call, reusable across calls of one shape."""
+    """Intermediate buffers of one layer call, reusable across calls of one shape.
+    With `sorted_rows` (the capacity of the sorted id list) the activation
+    buffers are laid out by sorted position, the layout of the tcgen05 path."""
 
-    def __init__(self, tokens, top_k, hidden, inter, device):
+    def __init__(self, tokens, top_k, hidden, inter, device, sorted_rows=None):
         slots = tokens * top_k
         bf16, f32, f8 = torch.bfloat16, torch.float32, torch.float8_e4m3fn
-        self.xq = torch.empty(tokens, hidden, dtype=f8, device=device)
-        self.xs = torch.empty(tokens, hidden // 128, dtype=f32, device=device)
-        self.act = torch.empty(slots, inter, dtype=bf16, device=device)
-        self.aq = torch.empty(slots, inter, dtype=f8, device=device)
-        self.as_ = torch.empty(slots, inter // 128, dtype=f32, device=device)
+        self.sorted_rows = sorted_rows
+        in_rows = sorted_rows if sorted_rows is not None else tokens
+        mid_rows = sorted_rows if sorted_rows is not None else slots
+        self.xq = torch.empty(in_rows, hidden, dtype=f8, device=device)
+        self.xs = torch.empty(in_rows, hidden // 128, dtype=f32, device=device)
+        self.act = torch.empty(mid_rows, inter, dtype=bf16, device=device)
+        self.aq = torch.empty(mid_rows, inter, dtype=f8, device=device)
+        self.as_ = torch.empty(mid_rows, inter // 128, dtype=f32, device=device)
         self.y = torch.empty(slots, hidden, dtype=bf16, device=device)
         self.out = torch.empty(tokens, hidden, dtype=bf16, device=device)
 
 
-def fused_moe_fp8_w8a8(x, logits, w13, w13_scale, w2, w2_scale, top_k, block_m=None, ws=None):
+def workspace_for(tokens, top_k, hidden, inter, experts, block_m, device, layout="sorted"):
+    """The workspace fused_moe_fp8_w8a8 wants for this shape, so that a caller
+    can allocate it once."""
+    if layout != "sorted":
+        return Fp8MoeWorkspace(tokens, top_k, hidden, inter, device)
+    cap = _lib.load().strix_moe_align_capacity(tokens * top_k, experts, block_m)
+    return Fp8MoeWorkspace(tokens, top_k, hidden, inter, device, sorted_rows=cap)
+
+
+def sorted_path_covers(w13, w13_scale, w2, w2_scale, block_m: int) -> bool:
+    """Whether both GEMMs of the layer run on the tcgen05 sorted-layout kernel."""
+    lib = _lib.load()
+
+    def kind(w, s):
+        return 2 if s.dim() == 3 and s.size(1) != w.size(1) else 1
+
+    return bool(lib.strix_moe_gemm_fp8_sorted_covers(w13.size(1), w13.size(2), block_m, 1,
+                                                     kind(w13, w13_scale))
+                and lib.strix_moe_gemm_fp8_sorted_covers(w2.size(1), w2.size(2), block_m, 0,
+                                                         kind(w2, w2_scale)))
+
+
+def fused_moe_fp8_w8a8(x, logits, w13, w13_scale, w2, w2_scale, top_k, block_m=None, ws=None,
+                       layout="auto"):
     """One MoE layer, FP8 W8A8 block-scaled. x bf16 [T, H]; logits fp32 [T, E];
     w13 e4m3 [E, 2I, H] + fp32 scales [E, 2I/128, H/128]; w2 e4m3 [E, H, I] +
     scales [E, H/128, I/128]. Returns bf16 [T, H]. Seven kernel launches, no
-    host synchronisation."""
+    host synchronisation.
+
+    layout "sorted" (the default where covered): the quantiser permutes the
+    tokens into sorted order, both GEMMs run on tcgen05 with TMA-fed operands,
+    the intermediate stays in sorted order and the down GEMM scatters to slot
+    order for the combine. layout "gather": the GEMMs gather token rows by slot
+    id themselves (the reference's op contract, mma.sync streaming kernels)."""
     t, h = x.shape
     e, n13, _ = w13.shape
     inter = n13 // 2
     bm = block_m or pick_block_m(t, top_k, e)
-    ws = ws or Fp8MoeWorkspace(t, top_k, h, inter, x.device)
+    if layout == "auto":
+        layout = "sorted" if sorted_path_covers(w13, w13_scale, w2, w2_scale, bm) else "gather"
     weights, ids = route(logits, top_k)
     sorted_ids, expert_ids, num_post = align(ids, bm, e)
     ops = torch.ops.strix
-    ops.moe_act_quant_fp8(x, ws.xq, ws.xs)
-    ops.moe_gemm_fp8_w8a8(ws.act, ws.xq, ws.xs, w13, w13_scale, sorted_ids, expert_ids, num_post,
-                          None, top_k, bm, 64, True, "silu")
-    ops.moe_act_quant_fp8(ws.act, ws.aq, ws.as_)
-    ops.moe_gemm_fp8_w8a8(ws.y, ws.aq, ws.as_, w2, w2_scale, sorted_ids, expert_ids, num_post,
-                          weights.view(-1), 1, bm, 64, False, "silu")
+    if layout == "sorted":
+        cap = sorted_ids.numel()
+        if ws is None or ws.sorted_rows != cap:
+            ws = Fp8MoeWorkspace(t, top_k, h, inter, x.device, sorted_rows=cap)
+        slots = t * top_k
+        ops.moe_act_quant_fp8_sorted(x, ws.xq, ws.xs, sorted_ids, num_post, top_k, slots)
+        ops.moe_gemm_fp8_sorted(ws.act, ws.xq, ws.xs, w13, w13_scale, sorted_ids, expert_ids,
+                                num_post, None, slots, bm, True, "silu", True)
+        ops.moe_act_quant_fp8_sorted(ws.act, ws.aq, ws.as_, None, num_post, 1, slots)
+        ops.moe_gemm_fp8_sorted(ws.y, ws.aq, ws.as_, w2, w2_scale, sorted_ids, expert_ids,
+                                num_post, weights.view(-1), slots, bm, False, "silu", False)
+    else:
+        if ws is None or ws.sorted_rows is not None:
+            ws = Fp8MoeWorkspace(t, top_k, h, inter, x.device)
+        ops.moe_act_quant_fp8(x, ws.xq, ws.xs)
+        ops.moe_gemm_fp8_w8a8(ws.act, ws.xq, ws.xs, w13, w13_scale, sorted_ids, expert_ids,
+                              num_post, None, top_k, bm, 64, True, "silu")
+        ops.moe_act_quant_fp8(ws.act, ws.aq, ws.as_)
+        ops.moe_gemm_fp8_w8a8(ws.y, ws.aq, ws.as_, w2, w2_scale, sorted_ids, expert_ids, num_post,
+                              weights.view(-1), 1, bm, 64, False, "silu")
     ops.moe_sum(ws.y.view(t, top_k, h), ws.out)
     return ws.out

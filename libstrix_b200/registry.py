@@ -133,6 +133,25 @@ def _moe_row(name: str, op: str, doc: str, **constraints: Any) -> Kernel:
 
 
 _MOE_ROWS = [
+    Kernel(
+        "moe_gemm_fp8_sorted", "moe_gemm_fp8",
+        "e4m3 experts x e4m3 activations laid out by sorted position, on tcgen05 "
+        "(kind::f8f6f4, fp32 partial sums in TMEM folded per 128-wide K block with "
+        "the block scale x the token's scale): 128 weight rows are the MMA's M, the "
+        "m-block's tokens its N; both operands arrive by TMA",
+        {"dtype": "bf16", "activation_dtype": "fp8_e4m3", "weight_dtype": "fp8_e4m3",
+         "weight_bits": 8, "quant": "fp8", "group_size": (0, 128), "layout": "sorted",
+         "block_m": (16, 32, 64, 128), "silu_mul": (True, False), "activation": _GATES},
+        {"tile": "128 weight rows x block_m tokens, K blocks of 128",
+         "pipeline": "TMA producer thread, issuing thread, metadata warp, 4 folding warps; "
+                     "8..5-stage ring, up to 8 TMEM accumulators, persistent grid",
+         "bound": "hbm (weight stream) at small token counts"},
+    ),
+    Kernel("moe_act_quant_fp8_sorted", "moe_act_quant_fp8",
+           "e4m3 activations per (row, 128 group) written in sorted order (row p = token "
+           "sorted_ids[p] / top_k, zeros for padding), the input layout of moe_gemm_fp8_sorted",
+           {"dtype": ("bf16", "fp16"), "activation_dtype": "fp8_e4m3", "group_size": 128,
+            "layout": "sorted"}),
     _moe_row(
         "moe_gemm_fp8_w8a8", "moe_gemm_fp8",
         "e4m3 experts x e4m3 activations (one fp32 scale per token and 128-wide K "

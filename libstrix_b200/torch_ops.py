@@ -263,6 +263,80 @@ def moe_act_quant_fp8(x, q, sa):
     _act_quant("strix_moe_act_quant_fp8", x, q, sa, torch.float8_e4m3fn)
 
 
+# ---- sorted-layout forms (not in the reference): the activations are laid out
+# by sorted position, so an m-block's tokens are consecutive rows and the
+# tcgen05 grouped GEMM fetches them with one TMA box.
+
+@_define("moe_act_quant_fp8_sorted(Tensor x, Tensor(a!) q, Tensor(b!) sa, Tensor? sorted_ids, "
+         "Tensor num_post_padded, int top_k, int num_valid) -> ()")
+def moe_act_quant_fp8_sorted(x, q, sa, sorted_ids, num_post_padded, top_k, num_valid):
+    """q[p], sa[p] = quantised x[sorted_ids[p] // top_k] for p < num_post_padded
+    (zeros for padding slots); with sorted_ids None, row p from row p."""
+    _check(x.dim() == 2 and x.dtype in (torch.bfloat16, torch.float16) and x.stride(1) == 1,
+           "x must be bf16 or fp16 [rows, K]")
+    k = x.size(1)
+    _check(k % 128 == 0, "K must be a multiple of 128")
+    rows = q.size(0)
+    _check(q.dtype == torch.float8_e4m3fn and q.dim() == 2 and q.size(1) == k and q.stride(1) == 1,
+           "q must be float8_e4m3fn [sorted rows, K]")
+    _check(sa.dtype == torch.float32 and tuple(sa.shape) == (rows, k // 128) and sa.stride(1) == 1,
+           "sa must be fp32 [sorted rows, K / 128]")
+    _check(num_post_padded.dtype == torch.int32, "num_post_padded must be int32")
+    if sorted_ids is None:
+        _check(x.size(0) >= rows, "x has fewer rows than q")
+    else:
+        _check(sorted_ids.dtype == torch.int32 and sorted_ids.numel() >= rows
+               and sorted_ids.is_contiguous(), "sorted_ids must be int32 with an entry per row of q")
+        _check(num_valid <= x.size(0) * top_k, "num_valid exceeds rows(x) * top_k")
+    with torch.cuda.device(x.device):
+        _lib.call("strix_moe_act_quant_fp8_sorted", x.data_ptr(), q.data_ptr(), sa.data_ptr(),
+                  _ptr(sorted_ids), num_post_padded.data_ptr(), rows, k, top_k, num_valid,
+                  x.stride(0), q.stride(0), sa.stride(0), int(x.dtype == torch.float16), _stream())
+
+
+@_define("moe_gemm_fp8_sorted(Tensor(a!) c, Tensor qa, Tensor sa, Tensor b, Tensor scales, "
+         "Tensor sorted_ids, Tensor expert_ids, Tensor num_post_padded, Tensor? topk_weights, "
+         "int num_valid, int block_m, bool silu_mul=False, str activation='silu', "
+         "bool c_sorted=False) -> ()")
+def moe_gemm_fp8_sorted(c, qa, sa, b, scales, sorted_ids, expert_ids, num_post_padded,
+                        topk_weights, num_valid, block_m, silu_mul=False, activation="silu",
+                        c_sorted=False):
+    f8 = torch.float8_e4m3fn
+    _check(qa.dtype == f8 and b.dtype == f8 and c.dtype == torch.bfloat16
+           and scales.dtype == torch.float32, "qa, b float8_e4m3fn; c bf16; scales fp32")
+    _check(qa.dim() == 2 and b.dim() == 3 and c.dim() == 2, "bad ranks")
+    e, n, k = b.shape
+    _check(qa.size(1) == k and c.size(1) == (n // 2 if silu_mul else n), "shape mismatch")
+    _check(qa.stride(1) == 1 and b.stride(2) == 1 and c.stride(1) == 1 and scales.stride(-1) == 1,
+           "last dims must be contiguous")
+    if scales.dim() == 3 and scales.size(1) != n:
+        _check(tuple(scales.shape) == (e, n // 128, k // 128),
+               "block scales must be fp32 [E, N/128, K/128]")
+        scale_kind, s_sn = _S_BLOCK, scales.stride(1)
+    else:
+        _check(scales.size(0) == e and scales.size(1) == n, "scales must be [E, N] or [E, N, 1]")
+        scale_kind, s_sn = _S_CHANNEL, 0
+    _check(activation in _ACTS, f"activation must be silu or gelu_tanh, got {activation}")
+    _check(sorted_ids.dtype == torch.int32 and expert_ids.dtype == torch.int32
+           and num_post_padded.dtype == torch.int32, "routing tensors must be int32")
+    sorted_len = sorted_ids.numel() // block_m * block_m
+    _check(qa.size(0) >= sorted_len and sa.size(0) >= sorted_len
+           and tuple(sa.shape[1:]) == (k // 128,) and sa.stride(1) == 1 and sa.dtype == torch.float32,
+           "qa / sa must cover every sorted position: [sorted_len, K] and fp32 [sorted_len, K/128]")
+    _check(expert_ids.numel() * block_m >= sorted_len, f"expert_ids too short for block_m {block_m}")
+    _check(c.size(0) >= (sorted_len if c_sorted else num_valid), "c has too few rows")
+    if topk_weights is not None:
+        _check(topk_weights.dtype == torch.float32 and topk_weights.is_contiguous()
+               and topk_weights.numel() >= num_valid, "topk_weights must be contiguous fp32 [num_valid]")
+    with torch.cuda.device(c.device):
+        _lib.call("strix_moe_gemm_fp8_sorted", c.data_ptr(), qa.data_ptr(), sa.data_ptr(),
+                  b.data_ptr(), scales.data_ptr(), sorted_ids.data_ptr(), expert_ids.data_ptr(),
+                  num_post_padded.data_ptr(), _ptr(topk_weights), num_valid, n, k, qa.stride(0),
+                  c.stride(0), b.stride(0), b.stride(1), scales.stride(0), s_sn, sa.stride(0),
+                  sorted_len, block_m, scale_kind, _ACTS[activation] if silu_mul else 0,
+                  int(c_sorted), _stream())
+
+
 @_define("moe_topk_softmax(Tensor(a!) topk_weights, Tensor(b!) topk_ids, Tensor gating_output, "
          "bool renormalize=True) -> ()")
 def moe_topk_softmax(topk_weights, topk_ids, gating_output, renormalize=True):

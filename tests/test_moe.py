@@ -254,22 +254,10 @@ def test_moe_gemm_w8a16(tokens, block_m, gemm, activation, scale_dtype):
 @pytest.mark.parametrize("tokens", [1, 5, 40, 300])
 @pytest.mark.parametrize("block_m", [16, 32, 64, 128])
 @pytest.mark.parametrize("gemm,activation", [("w13", "silu"), ("w13", "gelu_tanh"), ("w2", "silu")])
-@pytest.mark.parametrize("kernel", ["tcgen05", "stream"])
-def test_moe_gemm_fp8_w8a8(tokens, block_m, gemm, activation, scheme, kernel):
+def test_moe_gemm_fp8_w8a8(tokens, block_m, gemm, activation, scheme):
     """The oracle consumes the kernel path's own quantised activations
-    (dequantised), the convention of tests/test_moe_w4a8.py:78-80. Both
-    implementations are run: the tcgen05 kernel (every block_m up to 128) and
-    the mma.sync weight-streaming kernel."""
-    from libstrix_b200 import _lib
-
-    _lib.load().strix_moe_set_umma_max_block_m(128 if kernel == "tcgen05" else 0)
-    try:
-        _w8a8_case(tokens, block_m, gemm, activation, scheme)
-    finally:
-        _lib.load().strix_moe_set_umma_max_block_m(32)
-
-
-def _w8a8_case(tokens, block_m, gemm, activation, scheme):
+    (dequantised), the convention of tests/test_moe_w4a8.py:78-80. Gathered
+    form (token rows fetched by slot id inside the GEMM)."""
     n, k = shapes(gemm)
     w, scales, _ = M.make_fp8_weights(E, n, k, scheme)
     full = scales.repeat_interleave(128, 1).repeat_interleave(128, 2) if scheme == "block" \
@@ -282,6 +270,79 @@ def _w8a8_case(tokens, block_m, gemm, activation, scheme):
                         routing(tokens), gemm, activation, block_m, sa=sa,
                         a_deq=M.dequant_act(qa, sa))
     rms_check(out, ref, 2e-2)
+
+
+@pytest.mark.parametrize("scheme", ["block", "channel"])
+@pytest.mark.parametrize("tokens", [1, 5, 40, 300])
+@pytest.mark.parametrize("block_m", [16, 32, 64, 128])
+@pytest.mark.parametrize("gemm,activation", [("w13", "silu"), ("w13", "gelu_tanh"), ("w2", "silu")])
+def test_moe_gemm_fp8_sorted(tokens, block_m, gemm, activation, scheme):
+    """The tcgen05 kernel over activations in sorted order: the quantiser
+    permutes (w13) or keeps (w2) the rows, the GEMM writes sorted rows under the
+    gate and slot rows otherwise; both against the gathered oracle."""
+    n, k = shapes(gemm)
+    w, scales, _ = M.make_fp8_weights(E, n, k, scheme)
+    full = scales.repeat_interleave(128, 1).repeat_interleave(128, 2) if scheme == "block" \
+        else scales[..., None]
+    b = w.float() * full
+    g = torch.Generator().manual_seed(0)
+    ids = routing(tokens)
+    slots = tokens * TOP_K
+    sorted_ids, expert_ids, num_post = (t.to(DEV) for t in M.align(ids, block_m, E))
+    cap = sorted_ids.numel()
+    qs = torch.empty(cap, k, dtype=torch.float8_e4m3fn, device=DEV)
+    ss = torch.empty(cap, k // 128, dtype=torch.float32, device=DEV)
+    pos = sorted_ids.cpu().long()
+    live = pos < slots
+    if gemm == "w13":
+        a = torch.randn(tokens, k, generator=g).bfloat16()
+        torch.ops.strix.moe_act_quant_fp8_sorted(a.to(DEV), qs, ss, sorted_ids, num_post, TOP_K, slots)
+        a_topk, weights = TOP_K, None
+    else:
+        # the intermediate arrives in sorted order: row p belongs to slot sorted_ids[p]
+        a = torch.randn(slots, k, generator=g).bfloat16()
+        a_sorted = torch.zeros(cap, k, dtype=torch.bfloat16)
+        a_sorted[live] = a[pos[live]]
+        torch.ops.strix.moe_act_quant_fp8_sorted(a_sorted.to(DEV), qs, ss, None, num_post, 1, slots)
+        a_topk, weights = 1, torch.rand(tokens, TOP_K, generator=g)
+    # the quantiser itself: bit-exact against the oracle's, row by row
+    qa_ref, sa_ref = M.act_quant_fp8(a)
+    src = pos[live] // a_topk if gemm == "w13" else pos[live]
+    assert torch.equal(qs.cpu()[live].view(torch.uint8), qa_ref[src].view(torch.uint8))
+    assert torch.equal(ss.cpu()[live], sa_ref[src])
+    n_post = int(num_post.item())
+    pad = (~live) & (torch.arange(cap) < n_post)
+    assert not qs.cpu()[pad].view(torch.uint8).any()
+
+    c_sorted = gemm == "w13"
+    out_cols = n // 2 if gemm == "w13" else n
+    c = torch.full((cap if c_sorted else slots, out_cols), float("nan"), dtype=torch.bfloat16,
+                   device=DEV)
+    torch.ops.strix.moe_gemm_fp8_sorted(c, qs, ss, w.to(DEV), scales.to(DEV), sorted_ids, expert_ids,
+                                        num_post, None if weights is None else weights.flatten().to(DEV),
+                                        slots, block_m, gemm == "w13", activation, c_sorted)
+    ref = M.grouped_reference(M.dequant_act(qa_ref, sa_ref), b, ids, a_topk, weights)
+    if gemm == "w13":
+        ref = M.gate_mul(ref, activation)
+    out = c.float().cpu()
+    if c_sorted:
+        assert not out[pad].any(), "padding rows of a processed m-block must come out as zeros"
+        by_slot = torch.full((slots, out_cols), float("nan"))
+        by_slot[pos[live]] = out[live]
+        out = by_slot
+    rms_check(out, ref, 2e-2)
+
+
+def test_moe_gemm_fp8_sorted_rejects_uncovered_geometry():
+    w = torch.zeros(2, 256, 128, dtype=torch.float8_e4m3fn, device=DEV)
+    s = torch.ones(2, 256, device=DEV)
+    ids = torch.zeros(24, dtype=torch.int32, device=DEV)
+    q = torch.zeros(24, 128, dtype=torch.float8_e4m3fn, device=DEV)
+    sa = torch.ones(24, 1, device=DEV)
+    c = torch.zeros(24, 256, dtype=torch.bfloat16, device=DEV)
+    one = torch.ones(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(RuntimeError, match="geometry not covered"):
+        torch.ops.strix.moe_gemm_fp8_sorted(c, q, sa, w, s, ids, one, one, None, 24, 24)
 
 
 def test_moe_gemm_golden_fixtures():
@@ -340,14 +401,15 @@ def test_gemm_errors():
 
 # ---------------------------------------------------------------- the layer
 
-@pytest.mark.parametrize("tokens", [256, 37])
-def test_fp8_layer_benchmark_geometry(tokens):
+@pytest.mark.parametrize("layout", ["sorted", "gather"])
+@pytest.mark.parametrize("tokens", [256, 37, 1])
+def test_fp8_layer_benchmark_geometry(tokens, layout):
     """Config 1: hidden 2048, 128 experts, top-8, intermediate 768, FP8 W8A8
     block-scaled. Indices (routing, permutation) bit-exact, output within 2e-2 x
-    RMS of the oracle layer."""
+    RMS of the oracle layer, in both layouts of the intermediate buffers."""
     layer = moe_fp8_layer(tokens=tokens, seed=3, device=DEV)
     out = strix.moe.fused_moe_fp8_w8a8(layer.x, layer.logits, layer.w13, layer.w13_scale,
-                                       layer.w2, layer.w2_scale, layer.top_k)
+                                       layer.w2, layer.w2_scale, layer.top_k, layout=layout)
     cpu = layer.to("cpu")
     ref, ids_ref, w_ref = M.moe_fp8_layer(cpu.x, cpu.logits, cpu.w13, cpu.w13_scale, cpu.w2,
                                           cpu.w2_scale, cpu.top_k)
