@@ -328,6 +328,8 @@ def main() -> None:
             torch.cuda.empty_cache()
             line["moe_fp8"] = bench_moe_fp8(args, dev, not args.no_cpu_baseline)
             line["gpu_launches"] += line["moe_fp8"]["gpu_launches"]
+            line["gemm_w8a8_int8"] = bench_gemm_w8a8(args, dev, not args.no_cpu_baseline)
+            line["gpu_launches"] += line["gemm_w8a8_int8"]["gpu_launches"]
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -392,6 +394,64 @@ def bench_moe_fp8(args, dev, with_cpu: bool) -> dict:
         out["runs"].append(run)
         del layer, ws
         torch.cuda.empty_cache()
+    return out
+
+
+def bench_gemm_w8a8(args, dev, with_cpu: bool) -> dict:
+    """Dense W8A8 INT8 GEMM of config 2: K=5120, N=34816 (a 27B-like MLP gate-up),
+    M in {1, 16, 4096}. The decode rows (M <= 16) stream the 178 MB of weights
+    once per launch - HBM roofline; every launch reads another of six weight
+    copies (1.07 GB in rotation, far beyond the 126 MB L2). M = 4096 is tensor
+    bound: TOPS against twice the measured bf16 peak (the int8 rate is nominally
+    twice the bf16 rate; no int8 library GEMM was measured on this pool)."""
+    from oracle import gemm as G
+
+    hbm, peak_kind = measured_peaks()
+    f = ROOT / "MEASURED_PEAKS.json"
+    bf16 = float(json.loads(f.read_text())["bf16_tflops"]) if f.exists() else 1590.0
+    n, k, copies = 34816, 5120, 6
+    g = torch.Generator(device=dev).manual_seed(0)
+    ws = [torch.randint(-127, 128, (n, k), generator=g, dtype=torch.int8, device=dev)
+          for _ in range(copies)]
+    sw = torch.rand(n, generator=g, device=dev) * 9e-3 + 1e-3
+    out = {"config": "dense W8A8 INT8 GEMM K=5120 N=34816, int32-exact sums, bf16 out",
+           "gpu_launches": 0, "runs": []}
+    op = torch.ops.strix.w8a8_int8_gemm
+    for m in (1, 16, 4096):
+        a = torch.randint(-127, 128, (m, k), generator=g, dtype=torch.int8, device=dev)
+        sa = torch.rand(m, generator=g, device=dev) * 4e-2 + 1e-2
+        for i in range(max(args.warmup, 3)):
+            res = op(a, sa, ws[i % copies], sw)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            res = op(a, sa, ws[i % copies], sw)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        byts = n * k + m * k + 2 * m * n
+        tops = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+        gbs = byts / (ms * 1e-3) / 1e9
+        roof = ({"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm,
+                 "peak_kind": peak_kind} if m <= 64 else
+                {"bound": "tensor", "achieved": tops, "peak": 2 * bf16, "unit": "TOP/s",
+                 "frac": tops / (2 * bf16), "peak_kind": "2 x measured bf16 (derived)"})
+        run = {"m": m, "ms_per_launch": ms, "tops": tops, "gbs": gbs, "bytes": byts,
+               "roofline": roof}
+        out["gpu_launches"] += args.steps
+        if with_cpu and m == 16:
+            last = ws[(args.steps - 1) % copies]
+            rows = torch.arange(0, n, 17, device=dev)
+            t0 = time.perf_counter()
+            ref, acc = G.w8a8_int8_gemm(a.cpu(), sa.cpu(), last[rows].cpu(), sw[rows].cpu())
+            sec = time.perf_counter() - t0
+            run["cpu_baseline"] = {"value": 2.0 * m * rows.numel() * k / sec / 1e12, "unit": "TOP/s",
+                                   "cores": torch.get_num_threads(), "kind": "port",
+                                   "seconds": sec, "sample": f"M=16, every 17th output channel ({rows.numel()})"}
+            run["parity"] = {"bit_exact_bf16": bool(torch.equal(res[:, rows].cpu().view(torch.int16),
+                                                                ref.view(torch.int16)))}
+        out["runs"].append(run)
     return out
 
 

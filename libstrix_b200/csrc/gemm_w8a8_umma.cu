@@ -119,6 +119,7 @@ __global__ void __launch_bounds__(kGThreads, 1) gemm_w8a8_umma_kernel(const Gemm
     // --------------------------------------------------------------- issuer
     if (lane == 0) {
       const uint32_t idesc = instr_desc(D_S32, 1, 1, 128, NB);
+      const uint32_t a_lo0 = smem_desc_lo(ring_s);
       int t = 0, li = 0;
       bool dead = false;
       for (int item = blockIdx.x; item < total_items && !dead; item += gridDim.x, ++li) {
@@ -134,11 +135,13 @@ __global__ void __launch_bounds__(kGThreads, 1) gemm_w8a8_umma_kernel(const Gemm
             break;
           }
           tc_fence_after_sync();
-          const uint32_t sa_addr = ring_s + s * L::kStageBytes, sb_addr = sa_addr + L::kABytes;
-#pragma unroll
-          for (int k4 = 0; k4 < 4; ++k4)
-            mma_ss<KIND_I8>(tmem + buf * NB, smem_desc_sw128(sa_addr, 32 * k4),
-                            smem_desc_sw128(sb_addr, 32 * k4), idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+          const uint32_t a_lo = a_lo0 + s * (L::kStageBytes >> 4), b_lo = a_lo + (L::kABytes >> 4);
+          const uint32_t d = tmem + buf * NB;
+          if (kb == 0) mma_ss_lo<KIND_I8, false>(d, a_lo, b_lo, idesc);
+          else mma_ss_lo<KIND_I8, true>(d, a_lo, b_lo, idesc);
+          mma_ss_lo<KIND_I8, true>(d, a_lo + 2, b_lo + 2, idesc);
+          mma_ss_lo<KIND_I8, true>(d, a_lo + 4, b_lo + 4, idesc);
+          mma_ss_lo<KIND_I8, true>(d, a_lo + 6, b_lo + 6, idesc);
           mma_commit(&empty_bar[s]);
         }
         if (!dead) mma_commit(&tfull_bar[buf]);   // the tile's sums are complete

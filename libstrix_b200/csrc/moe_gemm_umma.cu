@@ -48,8 +48,13 @@ namespace {
 
 using namespace umma;
 
-constexpr int kProducerWarps = 4, kConsumerWarps = 4;   // warps 0..3: producer, metadata, issuer, spare
-constexpr int kThreadsU = (kProducerWarps + kConsumerWarps) * 32;
+// warps 0..3: producer, metadata, issuer, spare; then G consumer warps per TMEM
+// lane quadrant, each folding 1/G of the m-block's tokens (8 at least)
+constexpr int kProducerWarps = 4;
+// (measured: 4 groups pay at 64 tokens; at 32 the extra warps only add barrier traffic,
+// at 128 they push the kernel into register spills)
+constexpr int column_groups(int ntok) { return ntok == 64 ? 4 : 2; }
+constexpr int umma_threads(int ntok) { return (kProducerWarps + 4 * column_groups(ntok)) * 32; }
 constexpr int kIssuerWarp = 2;
 constexpr int kTileM = 128;   // weight rows per tile (TMEM lanes)
 constexpr int kKBlock = 128;  // K bytes per pipeline step = the scale block
@@ -72,25 +77,36 @@ struct UmmaMoeArgs {
   int gate_act;    // 0 none, 1 silu, 2 gelu_tanh
   int n_tiles;     // weight tiles per m-block
   int c_sorted;    // 1: c rows are sorted positions, 0: slot ids (padding skipped)
+  int prefetch;    // K blocks of weights requested into L2 ahead of the ring
   int debug;       // measurement switches (STRIX_UMMA_DEBUG): 1 skip the folds, 2 skip the epilogue
 };
 
-template <int NTOK>
+// KBMAX bounds the K blocks of an item (16: K <= 2048, 64: K <= 8192); it sizes
+// the per-item scale buffers, and what they leave goes to the ring.
+template <int NTOK, int KBMAX>
 struct UmmaLayout {
   static constexpr int kABytes = kTileM * kKBlock;      // 16 KB of weights
   static constexpr int kBBytes = NTOK * kKBlock;        // token rows
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = NTOK <= 32 ? 8 : NTOK <= 64 ? 7 : 5;
-  // TMEM accumulator buffers: as many as fit (the issuer then runs that many K
-  // blocks ahead of the consumers, which covers their per-item epilogue)
-  static constexpr int kAccBufs = 512 / NTOK < 8 ? 512 / NTOK : 8;
-  static constexpr int kTmemCols = NTOK * kAccBufs < 32 ? 32 : NTOK * kAccBufs;
-  static constexpr int kMaxKBlocks = NTOK <= 64 ? 64 : 32;  // K <= 8192 (4096 at 128 tokens)
+  static constexpr int kMaxKBlocks = KBMAX;
   static constexpr int kSaFloats = kMaxKBlocks * NTOK;      // one item's activation scales
   static constexpr int kSwFloats = kMaxKBlocks * 2;         // weight block scales (gate / up row block)
   // per item, kMetaBufs deep: activation scales, block scales, slot ids, routing weights
   static constexpr int kMetaBufs = NTOK <= 32 ? 4 : 2;
   static constexpr int kMetaBytes = kMetaBufs * (kSaFloats * 4 + kSwFloats * 4 + NTOK * 4 + NTOK * 4);
+  // One ring position = a stage of operands + a TMEM accumulator: the MMAs of a
+  // K block then finish with ONE tcgen05.commit, which both frees the stage for
+  // the producer and publishes the partial sums to the consumers (a commit costs
+  // the issuing thread about as much as three MMAs). The ring takes the shared
+  // memory the metadata leaves (bytes in flight are what covers the memory
+  // latency), up to the 512 TMEM columns.
+  static constexpr int kBudget = 227 * 1024 - 10 * 1024 - 2048;   // static arrays, alignment slack
+  static constexpr int kFit = (kBudget - kMetaBytes) / kStageBytes;
+  static constexpr int kTmemFit = 512 / NTOK;
+  static constexpr int kStages = kFit < kTmemFit ? (kFit < 12 ? kFit : 12) : (kTmemFit < 12 ? kTmemFit : 12);
+  static constexpr int kAccBufs = kStages;
+  static constexpr int kTmemUsed = NTOK * kAccBufs;   // the allocation is a power of two >= 32
+  static constexpr int kTmemCols = kTmemUsed <= 32 ? 32 : kTmemUsed <= 64 ? 64 : kTmemUsed <= 128 ? 128 : kTmemUsed <= 256 ? 256 : 512;
   static constexpr int kSmem = 1024 + kStages * kStageBytes + kMetaBytes + 1024;
 };
 
@@ -107,12 +123,14 @@ __device__ __forceinline__ int tile_row(int nt, int lane, bool gate, int half_n)
   return (lane & 1) ? half_n + i : i;
 }
 
-template <int NTOK>
-__global__ void __launch_bounds__(kThreadsU, 1) moe_gemm_umma_kernel(const UmmaMoeArgs p,
+template <int NTOK, int KBMAX>
+__global__ void __launch_bounds__(umma_threads(NTOK), 1) moe_gemm_umma_kernel(const UmmaMoeArgs p,
                                                                     const __grid_constant__ CUtensorMap map_w,
                                                                     const __grid_constant__ CUtensorMap map_a) {
-  using L = UmmaLayout<NTOK>;
+  using L = UmmaLayout<NTOK, KBMAX>;
   constexpr int S = L::kStages, NB = L::kAccBufs;
+  constexpr int kColumnGroups = column_groups(NTOK), kConsumerWarps = 4 * kColumnGroups;
+  constexpr int kThreadsU = umma_threads(NTOK);
   extern __shared__ uint8_t raw_smem[];
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
                                              ~uintptr_t(1023));
@@ -124,7 +142,7 @@ __global__ void __launch_bounds__(kThreadsU, 1) moe_gemm_umma_kernel(const UmmaM
   float* s_sw = s_sa + MB * L::kSaFloats;                                 // [MB][kb][gate|up]
   float* s_tw = s_sw + MB * L::kSwFloats;                                 // [MB][NTOK] routing weights
   int* s_sid = reinterpret_cast<int*>(s_tw + MB * NTOK);                  // [MB][NTOK]
-  __shared__ __align__(8) uint64_t full_bar[S], empty_bar[S], tfull_bar[NB], tempty_bar[NB];
+  __shared__ __align__(8) uint64_t full_bar[S], empty_bar[S], tempty_bar[NB];
   __shared__ __align__(8) uint64_t meta_empty_bar[MB], meta_full_bar[MB];
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int s_abort;
@@ -147,7 +165,6 @@ __global__ void __launch_bounds__(kThreadsU, 1) moe_gemm_umma_kernel(const UmmaM
       mbar_init(&empty_bar[i], 1);
     }
     for (int i = 0; i < NB; ++i) {
-      mbar_init(&tfull_bar[i], 1);
       mbar_init(&tempty_bar[i], kConsumerWarps);
     }
     for (int i = 0; i < MB; ++i) {
@@ -177,12 +194,25 @@ __global__ void __launch_bounds__(kThreadsU, 1) moe_gemm_umma_kernel(const UmmaM
       tma::prefetch_map(&map_a);
       int t = 0;
       bool dead = false;
+      // A second cursor runs p.prefetch K blocks ahead of the loads and asks for
+      // the weights in L2 only: the ring holds too few bytes to cover the memory
+      // latency at full bandwidth, L2 has room for the rest.
+      int pf_item = next_valid(blockIdx.x), pf_kb = 0;
+      auto prefetch_one = [&]() {
+        if (pf_item >= total_items) return;
+        const int mb = pf_item / p.n_tiles, nt = pf_item - mb * p.n_tiles;
+        tma::prefetch_l2_4d(&map_w, pf_kb * kKBlock, 0, nt * (gate ? kTileM / 2 : kTileM),
+                            s_expert[mb]);
+        if (++pf_kb == nkb) pf_kb = 0, pf_item = next_valid(pf_item + gridDim.x);
+      };
+      for (int i = 0; i < p.prefetch; ++i) prefetch_one();
       for (int item = next_valid(blockIdx.x); item < total_items && !dead;
            item = next_valid(item + gridDim.x)) {
         const int mb = item / p.n_tiles, nt = item - mb * p.n_tiles;
         const int expert = s_expert[mb];
         const int w_row = nt * (gate ? kTileM / 2 : kTileM);
         for (int kb = 0; kb < nkb; ++kb, ++t) {
+          if (p.prefetch > 0) prefetch_one();
           const int s = t % S;
           if (!mbar_wait(&empty_bar[s], ((t / S) & 1) ^ 1) || s_abort) {   // its MMAs retired
             dead = true;
@@ -259,6 +289,7 @@ __global__ void __launch_bounds__(kThreadsU, 1) moe_gemm_umma_kernel(const UmmaM
     // --------------------------------------------------------------- issuer
     if (lane == 0) {
       const uint32_t idesc = instr_desc(D_F32, 0, 0, kTileM, NTOK);
+      const uint32_t a_lo0 = smem_desc_lo(ring_s);
       int t = 0;
       bool dead = false;
       for (int item = blockIdx.x; item < total_items && !dead; item += gridDim.x) {
@@ -266,12 +297,13 @@ __global__ void __launch_bounds__(kThreadsU, 1) moe_gemm_umma_kernel(const UmmaM
         if (s_expert[mb] < 0) continue;
         for (int kb = 0; kb < nkb; ++kb, ++t) {
           const int s = t % S, b = t % NB;
-          const long long c0 = clock64();
+          const bool prof = p.prof != nullptr && blockIdx.x == 0;
+          const long long c0 = prof ? clock64() : 0;
           const bool ok_full = mbar_wait(&full_bar[s], (t / S) & 1);
-          const long long c1 = clock64();
+          const long long c1 = prof ? clock64() : 0;
           const bool ok_acc = mbar_wait(&tempty_bar[b], ((t / NB) & 1) ^ 1);
-          const long long c2 = clock64();
-          if (p.prof != nullptr && blockIdx.x == 0) {
+          if (prof) {
+            const long long c2 = clock64();
             p.prof[0] += c1 - c0;   // cycles waiting for data
             p.prof[1] += c2 - c1;   // cycles waiting for a free accumulator
             p.prof[2] += 1;         // steps
@@ -281,22 +313,27 @@ __global__ void __launch_bounds__(kThreadsU, 1) moe_gemm_umma_kernel(const UmmaM
             break;
           }
           tc_fence_after_sync();
-          const uint32_t sa_addr = ring_s + s * L::kStageBytes, sb_addr = sa_addr + L::kABytes;
-#pragma unroll
-          for (int k4 = 0; k4 < 4 && !(p.debug & 8); ++k4)
-            mma_ss<KIND_F8F6F4>(tmem + b * NTOK, smem_desc_sw128(sa_addr, 32 * k4),
-                                smem_desc_sw128(sb_addr, 32 * k4), idesc, k4 > 0 ? 1u : 0u);
-          mma_commit(&empty_bar[s]);   // the stage may be refilled
-          mma_commit(&tfull_bar[b]);   // the partial sums are ready
+          // one add per operand and MMA: the issuing thread runs in order
+          const uint32_t a_lo = a_lo0 + s * (L::kStageBytes >> 4), b_lo = a_lo + (L::kABytes >> 4);
+          const uint32_t d = tmem + b * NTOK;
+          if (!(p.debug & 8)) {
+            mma_ss_lo<KIND_F8F6F4, false>(d, a_lo, b_lo, idesc);
+            mma_ss_lo<KIND_F8F6F4, true>(d, a_lo + 2, b_lo + 2, idesc);
+            mma_ss_lo<KIND_F8F6F4, true>(d, a_lo + 4, b_lo + 4, idesc);
+            mma_ss_lo<KIND_F8F6F4, true>(d, a_lo + 6, b_lo + 6, idesc);
+          }
+          mma_commit(&empty_bar[s]);   // the stage may be refilled, the partial sums are ready
         }
       }
       if (dead) atomicExch(p.status, 1), s_abort = 1;
     }
   } else if (warp >= kProducerWarps) {
     // ------------------------------------------------------------ consumers
-    const int ctid = tid - kProducerWarps * 32;      // 0..127 = TMEM lane = tile row
+    const int ctid = (warp & 3) * 32 + lane;         // 0..127 = TMEM lane = tile row
+    const int cg = (warp - kProducerWarps) >> 2;     // which half of the tokens
+    constexpr int NT2 = NTOK / kColumnGroups;        // tokens per consumer thread
     const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
-    constexpr int CH = NTOK < 32 ? NTOK : 32;        // columns per tcgen05.ld
+    constexpr int CH = NT2 < 32 ? NT2 : 32;          // columns per tcgen05.ld
     int t = 0, li = 0;
     bool dead = false;
     for (int item = blockIdx.x; item < total_items && !dead; item += gridDim.x) {
@@ -308,9 +345,10 @@ __global__ void __launch_bounds__(kThreadsU, 1) moe_gemm_umma_kernel(const UmmaM
       const float chs = p.scale_kind == 1 ? p.scales[int64_t(expert) * p.s_se + row] : 1.f;
       // the producers wrote this item's token ids and activation scales
       const int buf = li % MB;
-      const long long m0 = clock64();
+      const bool cprof = p.prof != nullptr && blockIdx.x == 0 && ctid == 0;
+      const long long m0 = cprof ? clock64() : 0;
       const bool meta_ok = mbar_wait(&meta_full_bar[buf], (li / MB) & 1);
-      if (p.prof != nullptr && blockIdx.x == 0 && ctid == 0) p.prof[6] += clock64() - m0;
+      if (cprof) p.prof[6] += clock64() - m0;
       if (__any_sync(0xffffffffu, !meta_ok) || s_abort) {
         dead = true;
         break;
@@ -319,23 +357,23 @@ __global__ void __launch_bounds__(kThreadsU, 1) moe_gemm_umma_kernel(const UmmaM
       const int* sid_item = s_sid + buf * NTOK;
       const float* sw_item = s_sw + buf * L::kSwFloats + (gate ? (ctid & 1) : 0);
       const float* tw_item = s_tw + buf * NTOK;
-      float acc[NTOK];
+      float acc[NT2];
 #pragma unroll
-      for (int j = 0; j < NTOK; ++j) acc[j] = 0.f;
+      for (int j = 0; j < NT2; ++j) acc[j] = 0.f;
       // The K blocks' partial sums are read as a stream of (step, chunk of CH
       // columns) units through two register buffers: the TMEM load (and, at a
       // step's first chunk, the wait for its MMAs) of the next unit is issued
       // before the multiply-adds of the current one, so neither latency sits
       // on this warp's critical path.
-      constexpr int NCH = NTOK / CH;
+      constexpr int NCH = NT2 / CH;
       uint32_t R[2][CH];
       const int t0 = t;
       auto issue_ld = [&](int kb, int c, uint32_t (&r)[CH]) {
         const int ts = t0 + kb, b = ts % NB;
         if (c == 0) {
-          const long long w0 = clock64();
-          const bool ok = mbar_wait(&tfull_bar[b], (ts / NB) & 1);
-          if (p.prof != nullptr && blockIdx.x == 0 && ctid == 0) p.prof[3] += clock64() - w0;
+          const long long w0 = cprof ? clock64() : 0;
+          const bool ok = mbar_wait(&empty_bar[b], (ts / NB) & 1);
+          if (cprof) p.prof[3] += clock64() - w0;
           if (__any_sync(0xffffffffu, !ok)) {   // warp-uniform: the epilogue shuffles
             dead = true;
             return;
@@ -343,8 +381,10 @@ __global__ void __launch_bounds__(kThreadsU, 1) moe_gemm_umma_kernel(const UmmaM
           tc_fence_after_sync();
         }
         if (p.debug & 16) return;
-        if constexpr (CH == 32) tmem_ld_32x32(tmem + lane_base + b * NTOK + c * CH, r);
-        else tmem_ld_32x16(tmem + lane_base + b * NTOK + c * CH, r);
+        const uint32_t src = tmem + lane_base + b * NTOK + cg * NT2 + c * CH;
+        if constexpr (CH == 32) tmem_ld_32x32(src, r);
+        else if constexpr (CH == 16) tmem_ld_32x16(src, r);
+        else tmem_ld_32x8(src, r);
       };
       auto landed = [&](int kb, int c) {   // after the wait for unit (kb, c)
         if (c == NCH - 1) {                // the step's last chunk: hand the buffer back
@@ -364,7 +404,7 @@ __global__ void __launch_bounds__(kThreadsU, 1) moe_gemm_umma_kernel(const UmmaM
           const int kb = kb2 + PAR;
           if (kb >= nkb || dead) return;
           const float sw = p.scale_kind == 2 ? sw_item[2 * kb] : 1.f;
-          const float* sak = sa_item + kb * NTOK;
+          const float* sak = sa_item + kb * NTOK + cg * NT2;
           auto chunk = [&](auto cc) {
             constexpr int C = decltype(cc)::value;
             constexpr int BUF = NCH == 1 ? PAR : (C & 1);
@@ -382,9 +422,9 @@ __global__ void __launch_bounds__(kThreadsU, 1) moe_gemm_umma_kernel(const UmmaM
               acc[C * CH + j + 3] = fmaf(__uint_as_float(R[BUF][j + 3]), sw * s4.w, acc[C * CH + j + 3]);
             }
             if (more && !dead) {
-              const long long w0 = clock64();
+              const long long w0 = cprof ? clock64() : 0;
               tmem_ld_wait();
-              if (p.prof != nullptr && blockIdx.x == 0 && ctid == 0) p.prof[4] += clock64() - w0;
+              if (cprof) p.prof[4] += clock64() - w0;
               landed(nkb_, nc);
             }
           };
@@ -402,29 +442,30 @@ __global__ void __launch_bounds__(kThreadsU, 1) moe_gemm_umma_kernel(const UmmaM
       if (dead) break;
 
       // ---- epilogue of the item: this thread owns weight row `row`, all tokens
-      const long long ep0 = clock64();
+      const long long ep0 = cprof ? clock64() : 0;
       if (p.debug & 2) {
       } else if (gate) {
         __nv_bfloat16* cbase = static_cast<__nv_bfloat16*>(p.c) + nt * (kTileM / 2) + (ctid >> 1);
 #pragma unroll
-        for (int j = 0; j < NTOK; ++j) {
+        for (int j = 0; j < NT2; ++j) {
           const float v = acc[j] * chs;
           const float other = __shfl_xor_sync(0xffffffffu, v, 1);  // even lane: gate, odd: up
-          const int crow = p.c_sorted ? mb * NTOK + j : sid_item[j];
+          const int crow = p.c_sorted ? mb * NTOK + cg * NT2 + j : sid_item[cg * NT2 + j];
           if (crow >= 0 && (ctid & 1) == 0)
             cbase[int64_t(crow) * p.c_stride] = __float2bfloat16_rn(gate_fn(v, p.gate_act) * other);
         }
       } else {
         __nv_bfloat16* cbase = static_cast<__nv_bfloat16*>(p.c) + row;
 #pragma unroll
-        for (int j = 0; j < NTOK; ++j) {
-          const int crow = p.c_sorted ? mb * NTOK + j : sid_item[j];
-          if (crow >= 0) cbase[int64_t(crow) * p.c_stride] = __float2bfloat16_rn(acc[j] * chs * tw_item[j]);
+        for (int j = 0; j < NT2; ++j) {
+          const int crow = p.c_sorted ? mb * NTOK + cg * NT2 + j : sid_item[cg * NT2 + j];
+          if (crow >= 0)
+            cbase[int64_t(crow) * p.c_stride] = __float2bfloat16_rn(acc[j] * chs * tw_item[cg * NT2 + j]);
         }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&meta_empty_bar[buf]);   // the producers may reuse this buffer
-      if (p.prof != nullptr && blockIdx.x == 0 && ctid == 0) p.prof[5] += clock64() - ep0;
+      if (cprof) p.prof[5] += clock64() - ep0;
       ++li;
     }
     if (dead) atomicExch(p.status, 1), s_abort = 1;
@@ -445,11 +486,11 @@ __device__ int32_t g_umma_status = 0;
 // epilogues, [6] consumer waiting for metadata, [7] kernel cycles.
 __device__ long long g_umma_prof[8] = {};
 
-template <int NTOK>
+template <int NTOK, int KBMAX>
 int launch_umma(const UmmaMoeArgs& p, const CUtensorMap& map_w, const CUtensorMap& map_a,
                 cudaStream_t st) {
-  using L = UmmaLayout<NTOK>;
-  auto kernel = moe_gemm_umma_kernel<NTOK>;
+  using L = UmmaLayout<NTOK, KBMAX>;
+  auto kernel = moe_gemm_umma_kernel<NTOK, KBMAX>;
   static bool done[64] = {};
   static int sms[64] = {};
   int dev = 0;
@@ -460,7 +501,7 @@ int launch_umma(const UmmaMoeArgs& p, const CUtensorMap& map_w, const CUtensorMa
     STRIX_CUDA(cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev));
     done[dev] = true;
   }
-  kernel<<<sms[dev], kThreadsU, L::kSmem, st>>>(p, map_w, map_a);
+  kernel<<<sms[dev], umma_threads(NTOK), L::kSmem, st>>>(p, map_w, map_a);
   return launch_status("moe_gemm_umma");
 }
 
@@ -533,6 +574,8 @@ extern "C" int strix_moe_gemm_fp8_sorted(
   p.n_tiles = int(out_rows / tile_out);
   static const int debug = [] { const char* e = getenv("STRIX_UMMA_DEBUG"); return e ? atoi(e) : 0; }();
   p.debug = debug;
+  static const int prefetch = [] { const char* e = getenv("STRIX_UMMA_PREFETCH"); return e ? atoi(e) : 16; }();
+  p.prefetch = prefetch < 0 ? 0 : prefetch > 256 ? 256 : prefetch;
   // Weights as a 4-d byte tensor (k, half, row, expert): under the fused gate
   // `half` steps from the gate rows to the up rows, so a box of 2 x 64 rows lands
   // as gate row i / up row i alternating; otherwise it has extent 1. The expert
@@ -547,10 +590,11 @@ extern "C" int strix_moe_gemm_fp8_sorted(
                                    uint32_t(block_m)),
               "tensor map encoding failed");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (block_m == 16) return launch_umma<16>(p, map_w, map_a, st);
-  if (block_m == 32) return launch_umma<32>(p, map_w, map_a, st);
-  if (block_m == 64) return launch_umma<64>(p, map_w, map_a, st);
-  return launch_umma<128>(p, map_w, map_a, st);
+  const bool short_k = k <= 16 * kKBlock;
+  if (block_m == 16) return short_k ? launch_umma<16, 16>(p, map_w, map_a, st) : launch_umma<16, 64>(p, map_w, map_a, st);
+  if (block_m == 32) return short_k ? launch_umma<32, 16>(p, map_w, map_a, st) : launch_umma<32, 64>(p, map_w, map_a, st);
+  if (block_m == 64) return short_k ? launch_umma<64, 16>(p, map_w, map_a, st) : launch_umma<64, 64>(p, map_w, map_a, st);
+  return short_k ? launch_umma<128, 16>(p, map_w, map_a, st) : launch_umma<128, 32>(p, map_w, map_a, st);
 }
 
 extern "C" int strix_umma_prof(int64_t* host_out8, int reset) {

@@ -98,5 +98,21 @@ __device__ __forceinline__ void load_4d(uint32_t smem_dst, const CUtensorMap* ma
       : "memory");
 }
 
+// Asks the TMA to bring a box into L2 only: no shared memory, no barrier. Bytes
+// a CTA will need later than its ring of stages can hold are put in flight this
+// way, so that the load proper finds them at L2 latency.
+__device__ __forceinline__ void prefetch_l2_4d(const CUtensorMap* map, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+__device__ __forceinline__ void prefetch_l2_2d(const CUtensorMap* map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(x), "r"(y)
+               : "memory");
+}
+
 }  // namespace tma
 }  // namespace strix

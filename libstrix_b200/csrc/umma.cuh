@@ -136,6 +136,15 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
       : "memory");
 }
 
+__device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7])
+      : "r"(taddr)
+      : "memory");
+}
+
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -155,6 +164,19 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t tile_smem_addr, uin
   d |= uint64_t(1024 >> 4) << 32;         // SBO = 1,024 bytes
   d |= uint64_t(1) << 46;                 // version
   d |= uint64_t(2) << 61;                 // SWIZZLE_128B
+  return d;
+}
+
+// The same descriptor as two 32-bit words, for issue loops: the high word is a
+// constant, and advancing the tile address by `bytes` (a multiple of 16) adds
+// bytes >> 4 to the low word, so the issuing thread spends one add per operand.
+constexpr uint32_t kDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t tile_smem_addr) {
+  return ((tile_smem_addr & 0x3ffffu) >> 4) | (1u << 16);
+}
+__device__ __forceinline__ uint64_t desc_pack(uint32_t lo, uint32_t hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
   return d;
 }
 
@@ -191,6 +213,33 @@ __device__ __forceinline__ void mma_ss(uint32_t tmem_d, uint64_t adesc, uint64_t
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+
+// As mma_ss with the operands' low descriptor words and a compile-time
+// accumulate flag: the shortest issue sequence (the issuing thread runs in
+// order, so every instruction around the MMA adds to the time between MMAs).
+template <int KIND, bool ACC>
+__device__ __forceinline__ void mma_ss_lo(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
+  const uint64_t adesc = desc_pack(a_lo, kDescHiSw128), bdesc = desc_pack(b_lo, kDescHiSw128);
+  if constexpr (KIND == KIND_F8F6F4) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "n"(ACC ? 1 : 0)
+        : "memory");
+  } else if constexpr (KIND == KIND_I8) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "n"(ACC ? 1 : 0)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "n"(ACC ? 1 : 0)
         : "memory");
   }
 }
