@@ -183,6 +183,10 @@ def main() -> None:
     ap.add_argument("--ctx-hi", type=int, default=65536)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-moe", action="store_true", help="skip the MoE FP8 layer runs")
+    ap.add_argument("--only", choices=["moe", "gemm"], default=None,
+                    help="run one secondary section alone (for profiling) and print its JSON")
+    ap.add_argument("--moe-tokens", type=int, nargs="*", default=[256, 4096])
+    ap.add_argument("--gemm-m", type=int, nargs="*", default=[1, 16, 4096])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -205,6 +209,13 @@ def main() -> None:
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    if args.only is not None:
+        if rank == 0:
+            section = bench_moe_fp8 if args.only == "moe" else bench_gemm_w8a8
+            print(json.dumps({args.only: section(args, dev, not args.no_cpu_baseline)}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     batch = decode_batch(batch=args.batch, ctx_hi=args.ctx_hi, seed=rank, device=dev)
     kv_bytes = batch.kv_bytes
@@ -349,7 +360,7 @@ def bench_moe_fp8(args, dev, with_cpu: bool) -> dict:
     peak, peak_kind = measured_peaks()
     out = {"config": "MoE FP8 W8A8 block-scaled, H=2048 E=128 top-8 I=768", "gpu_launches": 0,
            "runs": []}
-    for tokens in (256, 4096):
+    for tokens in args.moe_tokens:
         layer = moe_fp8_layer(tokens=tokens, seed=0, device=dev)
         ws = workspace_for(tokens, layer.top_k, 2048, 768, 128, pick_block_m(tokens, layer.top_k, 128), dev)
 
@@ -417,7 +428,7 @@ def bench_gemm_w8a8(args, dev, with_cpu: bool) -> dict:
     out = {"config": "dense W8A8 INT8 GEMM K=5120 N=34816, int32-exact sums, bf16 out",
            "gpu_launches": 0, "runs": []}
     op = torch.ops.strix.w8a8_int8_gemm
-    for m in (1, 16, 4096):
+    for m in args.gemm_m:
         a = torch.randint(-127, 128, (m, k), generator=g, dtype=torch.int8, device=dev)
         sa = torch.rand(m, generator=g, device=dev) * 4e-2 + 1e-2
         for i in range(max(args.warmup, 3)):

@@ -574,7 +574,7 @@ extern "C" int strix_moe_gemm_fp8_sorted(
   p.n_tiles = int(out_rows / tile_out);
   static const int debug = [] { const char* e = getenv("STRIX_UMMA_DEBUG"); return e ? atoi(e) : 0; }();
   p.debug = debug;
-  static const int prefetch = [] { const char* e = getenv("STRIX_UMMA_PREFETCH"); return e ? atoi(e) : 16; }();
+  static const int prefetch = [] { const char* e = getenv("STRIX_UMMA_PREFETCH"); return e ? atoi(e) : 0; }();
   p.prefetch = prefetch < 0 ? 0 : prefetch > 256 ? 256 : prefetch;
   // Weights as a 4-d byte tensor (k, half, row, expert): under the fused gate
   // `half` steps from the gate rows to the up rows, so a box of 2 x 64 rows lands
