@@ -189,6 +189,56 @@ int strix_w8a8_int8_gemm(void* out, int32_t* acc_out, const void* a_q, const flo
                          int64_t a_stride, int64_t w_stride, int64_t out_stride,
                          strix_stream_t stream);
 
+/* Grouped or dense GEMM with 4-bit weights and bf16 activations, on the
+ * weight-streaming kernel. Replaces moe_gemm_w4a16 (csrc/moe/moe_gemm_w4a16.hip:374),
+ * w4a16_wmma_gemm, mxfp4_wmma_gemm / mxfp4_gemv (csrc/gemm/mxfp4_wmma_gemm.hip:355-372,
+ * csrc/gemm/mxfp4_gemv.hip:111) and adds the grouped MXFP4 form.
+ *   weight_format 3: MXFP4 - w uint8 [E, N, K/2] (byte j: k = 2j in the low
+ *     nibble), scales uint8 e8m0 [E, N, K/32] (byte 0 = zero block), group 32
+ *   weight_format 4: INT4 - value = nibble - 8, scales bf16 (scale_dtype 1) or
+ *     fp16 (2) [E, N, K/group], group 32, 64 or 128
+ * K must be a multiple of 32 (a partial last 128-block is zero-filled).
+ * Routing as in strix_moe_gemm; with sorted_ids, expert_ids and
+ * num_post_padded all NULL the call is a dense GEMM: slot i is row i of a (a_rows
+ * = num_valid = M, experts = 1, sorted_len = M rounded up to block_m). bias (bf16,
+ * bias[row * bias_stride + n], stride 0 for a per-channel bias) is added to plain
+ * outputs. Strides are in elements of the tensors as stored. */
+int strix_gemm_w4a16(void* c, const void* a, const void* w, const void* scales, const void* bias,
+                     const int32_t* sorted_ids, const int32_t* expert_ids,
+                     const int32_t* num_post_padded, const float* topk_weights, int64_t num_valid,
+                     int64_t a_rows, int64_t experts, int64_t n, int64_t k, int64_t a_stride,
+                     int64_t c_stride, int64_t w_stride_e, int64_t w_stride_n, int64_t s_stride_e,
+                     int64_t s_stride_n, int64_t bias_stride, int64_t sorted_len,
+                     int64_t expert_len, int64_t top_k, int64_t block_m, int weight_format,
+                     int group, int scale_dtype, int gate_act, strix_stream_t stream);
+
+/* Dense GEMM c = x W^T (+ bias) with 8-bit weights and 16-bit activations on the
+ * weight-streaming kernel. Replaces w8a16_skinny_gemm / fp8_skinny_gemm
+ * (csrc/gemm/w8a16_skinny_gemm.hip:761,768) and fp8_wmma_gemm[_raw]
+ * (csrc/gemm/fp8_wmma_gemm.hip:324-344).
+ *   weight_format 0 e4m3, 1 int8, 5 excess-128 bytes (value = byte - 128)
+ *   act_format    0 bf16, 1 fp16 (e4m3 weights only; exact weights, scaled sums)
+ *   scale_kind    1 per channel [N]; 2 fp32 blocks [ceil(N/128), K/128] (e4m3);
+ *                 3 per row and 128-wide K group [N, K/128]; s_stride_n = row stride
+ * c bf16 [m, n]; K a multiple of 128, N of 16. */
+int strix_dense_gemm_w8a16(void* c, const void* x, const void* w, const void* scales,
+                           const void* bias, int64_t m, int64_t n, int64_t k, int64_t x_stride,
+                           int64_t c_stride, int64_t w_stride, int64_t s_stride_n,
+                           int64_t bias_stride, int64_t block_m, int weight_format,
+                           int act_format, int scale_kind, int scale_dtype, strix_stream_t stream);
+
+/* Whole-matrix decode to bf16 [n, k], byte-exact. Replaces mxfp4_dequant
+ * (csrc/gemm/mxfp4_wmma_gemm.hip), w4a16_dequant and fp8_dequant
+ * (csrc/gemm/fp8_dequant.hip:63). format 0 mxfp4 (w [n, k/2], scales e8m0
+ * [n, k/32]), 1 int4 (scales bf16/fp16 [n, k/group]), 2 e4m3 (w [n, k], scales
+ * fp32 per channel [n] = scale_kind 1, or [ceil(n/128), k/128] = scale_kind 2).
+ * s_stride_n / s_stride_g: element strides of the scale tensor over rows (row
+ * blocks for scale_kind 2) and K groups. */
+int strix_dequant_bf16(void* out, const void* w, const void* scales, int64_t n, int64_t k,
+                       int64_t w_stride, int64_t out_stride, int64_t s_stride_n, int64_t s_stride_g,
+                       int format, int group, int scale_kind, int scale_dtype,
+                       strix_stream_t stream);
+
 /* Health of the tcgen05 kernels: *host_out = 0 while every launch so far met its
  * bounded waits, 1 after one of them gave up (its output is then incomplete).
  * Synchronises the device; for tests and debugging. No reference counterpart. */

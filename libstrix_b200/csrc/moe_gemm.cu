@@ -35,9 +35,11 @@ constexpr int kThreads = kWarps * 32;
 constexpr int kStages = 4;
 constexpr int kKB = 128;  // K elements per pipeline step (= the scale block)
 
-enum WFmt { W_E4M3 = 0, W_INT8 = 1, W_BF16 = 2 };
+enum WFmt { W_E4M3 = 0, W_INT8 = 1, W_BF16 = 2, W_MXFP4 = 3, W_INT4 = 4, W_U8B128 = 5 };
+constexpr bool is_w4(int wf) { return wf == W_MXFP4 || wf == W_INT4; }
 enum AFmt { A_BF16 = 0, A_F16 = 1, A_E4M3 = 2 };
-enum ScaleKind { S_NONE = 0, S_CHANNEL = 1, S_BLOCK = 2 };
+// S_GROUP: one scale per output row and 128-wide K group, [E, N, K/128]
+enum ScaleKind { S_NONE = 0, S_CHANNEL = 1, S_BLOCK = 2, S_GROUP = 3 };
 enum Act { ACT_NONE = 0, ACT_SILU = 1, ACT_GELU_TANH = 2 };
 
 struct MoeArgs {
@@ -50,12 +52,15 @@ struct MoeArgs {
   const int32_t* expert_ids;
   const int32_t* num_post;
   const float* topk_w;
+  const void* bias;  // optional bf16 added to plain outputs: bias[sid * bias_stride + n]
+  int64_t bias_stride;
   int64_t num_valid;
   int64_t a_stride, c_stride, w_se, w_sn, s_se, s_sn, sa_stride;  // elements
   int top_k, K, N, block_m;
   int scale_kind, scale_dtype;  // dtype: 0 fp32, 1 bf16, 2 fp16
   int c_f16;
   int tiles_per_cta;  // consecutive n-tiles one CTA streams
+  int group;          // K elements per weight scale (4-bit formats: 32, 64 or 128)
 };
 
 __device__ __forceinline__ float load_scale(const void* p, int64_t idx, int dtype) {
@@ -97,8 +102,8 @@ __device__ __forceinline__ void widen(uint32_t w, float scale, uint32_t& lo, uin
         "cvt.rn.f16x2.e4m3x2 %0, l;\n\tcvt.rn.f16x2.e4m3x2 %1, h;\n\t}"
         : "=r"(f_lo), "=r"(f_hi)
         : "r"(w));
-  } else {  // W_INT8: 0x6400 | (b ^ 0x80) is fp16 1024 + b + 128
-    const uint32_t x = w ^ 0x80808080u;
+  } else {  // W_INT8: 0x6400 | (b ^ 0x80) is fp16 1024 + b + 128; excess-128 bytes are already b + 128
+    const uint32_t x = WF == W_U8B128 ? w : w ^ 0x80808080u;
     f_lo = sub_f16x2(prmt(x, 0x64646464u, 0x4140), 0x64806480u);
     f_hi = sub_f16x2(prmt(x, 0x64646464u, 0x4342), 0x64806480u);
   }
@@ -109,6 +114,29 @@ __device__ __forceinline__ void widen(uint32_t w, float scale, uint32_t& lo, uin
     const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&f_hi));
     lo = pack_bf16x2(a.x * scale, a.y * scale), hi = pack_bf16x2(b.x * scale, b.y * scale);
   }
+}
+
+// Eight 4-bit weights (one 32-bit word, element i in bits [4i, 4i + 4): byte j
+// holds k = 2j in its low nibble, csrc/gemm/mxfp4_wmma_gemm.hip and
+// tests/test_mxfp4.py:29-47) -> four registers of bf16 pairs, each value times
+// `scale` and rounded to bf16 (exact for e2m1 x 2^e). MXFP4: sign, 2-bit
+// exponent, 1-bit mantissa (0, .5, 1, 1.5, 2, 3, 4, 6); INT4: nibble - 8.
+template <int WF>
+__device__ __forceinline__ void widen4(uint32_t w, float scale, uint32_t* out) {
+  float v[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t n = (w >> (4 * i)) & 15u;
+    if constexpr (WF == W_MXFP4) {
+      const uint32_t e = (n >> 1) & 3u, m = n & 1u;
+      const uint32_t bits = e ? (((e + 126u) << 23) | (m << 22)) : (m ? 0x3F000000u : 0u);
+      v[i] = __uint_as_float(bits | ((n & 8u) << 28)) * scale;
+    } else {
+      v[i] = float(int(n) - 8) * scale;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) out[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
 }
 
 // Shared-memory row layouts of one K block. A row of 8-bit elements is 128
@@ -123,17 +151,20 @@ __device__ __forceinline__ int swz16(int row, int chunk) {
   return ((((chunk & 3) << 2) | (chunk >> 2)) ^ ((row & 1) << 2));
 }
 
-template <int BYTES>  // bytes per element: 1 or 2
+template <int ROWBYTES>  // bytes of a row of one K block: 64 (4-bit), 128 or 256
 __device__ __forceinline__ uint32_t row_chunk_offset(int row, int chunk) {
-  if constexpr (BYTES == 1) return uint32_t(row * 128 + (swz8(row, chunk) << 4));
+  // 64-byte rows: a quarter-warp reads 2 rows x 4 chunks = 128 consecutive bytes as they lie
+  if constexpr (ROWBYTES == 64) return uint32_t(row * 64 + (chunk << 4));
+  if constexpr (ROWBYTES == 128) return uint32_t(row * 128 + (swz8(row, chunk) << 4));
   return uint32_t(row * 256 + (swz16(row, chunk) << 4));
 }
 
 template <int WF, int AF, int BMC>
 struct Layout {
-  static constexpr int WB = WF == W_BF16 ? 2 : 1;    // weight bytes / element
+  static constexpr int WB = WF == W_BF16 ? 2 : 1;    // bytes per unit of the weight strides
   static constexpr int AB = AF == A_E4M3 ? 1 : 2;    // activation bytes / element
-  static constexpr int kWRow = kKB * WB, kARow = kKB * AB;
+  static constexpr int kWRow = is_w4(WF) ? kKB / 2 : kKB * WB, kARow = kKB * AB;
+  static constexpr int kWElems = kKB * 16 / kWRow;   // K elements per 16-byte weight chunk
   static constexpr int kWBytes = kWarps * 16 * kWRow;  // all warps' weight rows
   static constexpr int kABytes = BMC * kARow;
   static constexpr int kSaBytes = AF == A_E4M3 ? BMC * 4 : 0;
@@ -148,10 +179,14 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs
   extern __shared__ __align__(16) uint8_t smem[];
   int64_t* s_arow = reinterpret_cast<int64_t*>(smem + kStages * L::kStage);  // [BMC] A row or -1
 
+  // Without routing tensors (a dense GEMM) slot i is row i of one expert.
   const int mb = blockIdx.y;
-  if (mb * p.block_m >= *p.num_post) return;
-  const int expert = p.expert_ids[mb];
+  if (p.num_post != nullptr && mb * p.block_m >= *p.num_post) return;
+  const int expert = p.expert_ids != nullptr ? p.expert_ids[mb] : 0;
   if (expert < 0) return;
+  auto slot_id = [&](int pos) -> int64_t {
+    return p.sorted_ids != nullptr ? int64_t(p.sorted_ids[pos]) : int64_t(pos);
+  };
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
   constexpr bool kGate = ACT != ACT_NONE;
@@ -164,7 +199,7 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs
   const int n_tiles = (out_rows + kWarps * kRowsPerWarp - 1) / (kWarps * kRowsPerWarp);
   const int tile0 = blockIdx.x * p.tiles_per_cta;
   const int ntile = min(p.tiles_per_cta, n_tiles - tile0);
-  const int nkb = p.K / kKB;
+  const int nkb = (p.K + kKB - 1) / kKB;   // the last block may be partial: its tail is zero-filled
   const int total_it = ntile * nkb;
 
   const uint8_t* wbase = static_cast<const uint8_t*>(p.w) + int64_t(expert) * p.w_se * L::WB;
@@ -177,7 +212,7 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs
   uint32_t w_dst[NCW];
 #pragma unroll
   for (int i = 0; i < NCW; ++i)
-    w_dst[i] = warp * 16 * L::kWRow + row_chunk_offset<L::WB>(i * RPI + w_r0, w_ch);
+    w_dst[i] = warp * 16 * L::kWRow + row_chunk_offset<L::kWRow>(i * RPI + w_r0, w_ch);
   // activations: copy i of a thread is chunk id = i * kThreads + tid of the BMC x CPA tile
   constexpr int CPA = L::kARow / 16, NCA = BMC * CPA / kThreads;
   static_assert(BMC * CPA % kThreads == 0, "activation tile must split evenly over the threads");
@@ -185,24 +220,24 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs
 #pragma unroll
   for (int i = 0; i < NCA; ++i) {
     const int id = i * kThreads + threadIdx.x;
-    a_dst[i] = L::kWBytes + row_chunk_offset<L::AB>(id / CPA, id % CPA);
+    a_dst[i] = L::kWBytes + row_chunk_offset<L::kARow>(id / CPA, id % CPA);
   }
   // fragment read offsets inside a stage: weights rows g, g + 8; token row 8j + g
-  constexpr int WCH = 2 * L::WB, ACH = 2 * L::AB;  // 16-byte chunks a lane owns per row
+  constexpr int WCH = L::kWRow / 64, ACH = 2 * L::AB;  // 16-byte chunks a lane owns per row
   uint32_t w_off[2][WCH], a_off[ACH];
 #pragma unroll
   for (int r = 0; r < 2; ++r)
 #pragma unroll
     for (int i = 0; i < WCH; ++i)
-      w_off[r][i] = warp * 16 * L::kWRow + row_chunk_offset<L::WB>(g + 8 * r, WCH * c + i);
+      w_off[r][i] = warp * 16 * L::kWRow + row_chunk_offset<L::kWRow>(g + 8 * r, WCH * c + i);
 #pragma unroll
-  for (int i = 0; i < ACH; ++i) a_off[i] = L::kWBytes + row_chunk_offset<L::AB>(g, ACH * c + i);
+  for (int i = 0; i < ACH; ++i) a_off[i] = L::kWBytes + row_chunk_offset<L::kARow>(g, ACH * c + i);
 
   for (int tc = 0; tc < p.block_m; tc += BMC) {  // token chunks of the m-block
     __syncthreads();  // previous chunk's readers are done with s_arow and the ring
     int valid = 0;
     for (int i = threadIdx.x; i < BMC; i += kThreads) {
-      const int64_t sid = tc + i < p.block_m ? p.sorted_ids[mb * p.block_m + tc + i] : p.num_valid;
+      const int64_t sid = tc + i < p.block_m ? slot_id(mb * p.block_m + tc + i) : p.num_valid;
       const bool ok = sid >= 0 && sid < p.num_valid;
       s_arow[i] = ok ? sid / p.top_k : -1;
       valid |= ok;
@@ -248,8 +283,8 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
         const int slot = tc + 8 * j + 2 * c + t;
-        const int sid = slot < p.block_m ? p.sorted_ids[mb * p.block_m + slot] : -1;
-        out_sid[j][t] = (sid >= 0 && sid < p.num_valid) ? sid : -1;
+        const int64_t sid = slot < p.block_m ? slot_id(mb * p.block_m + slot) : -1;
+        out_sid[j][t] = (sid >= 0 && sid < p.num_valid) ? int(sid) : -1;
       }
     // weights widened to bf16 carry their scale (see widen); other forms scale sums
     constexpr bool kPrescale = AF == A_BF16 && WF != W_BF16;
@@ -272,17 +307,23 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs
           }
         }
         const uint32_t st = smem_s + stage_issue * L::kStage;
+        const int k_left = p.K - kb_issue * kKB;   // elements of this K block that exist
         if (w_live_issue) {
+          const bool in_k = w_ch * L::kWElems < k_left;
 #pragma unroll
           for (int i = 0; i < NCW; ++i) {
-            cp_async_16(st + w_dst[i], w_src[i]);
-            w_src[i] += kKB * L::WB;
+            cp_async_16_zfill(st + w_dst[i], in_k ? w_src[i] : wbase, in_k);
+            w_src[i] += L::kWRow;
           }
         }
         const int koff = kb_issue * kKB * L::AB;
 #pragma unroll
-        for (int i = 0; i < NCA; ++i)
-          if (a_use[i]) cp_async_16_zfill(st + a_dst[i], a_src[i] + koff, a_ok[i]);
+        for (int i = 0; i < NCA; ++i) {
+          if (!a_use[i]) continue;
+          const int id = i * kThreads + threadIdx.x;
+          const bool in_k = (id % CPA) * (16 / L::AB) < k_left;
+          cp_async_16_zfill(st + a_dst[i], in_k ? a_src[i] + koff : a_src[i], a_ok[i] && in_k);
+        }
         if constexpr (AF == A_E4M3) {
           if (sa_src != nullptr && int(threadIdx.x) < nt_live * 8)
             cp_async_4_zfill(st + L::kWBytes + L::kABytes + threadIdx.x * 4, sa_src + kb_issue, sa_ok);
@@ -303,6 +344,21 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs
     int kb = 0, nb = 0, row_lo = 0, row_hi = 0, stage = 0, ti = 0;
     int64_t sc0 = 0, sc1 = 0;  // block-scale indices of the two row groups at K block 0
     bool warp_live = false;
+    // 4-bit formats: this lane's 32 elements of a K block are one scale group
+    // (or part of one); the scales of the next step are fetched a step ahead
+    auto w4_scale = [&](int ti_, int kb_, int r) -> float {
+      const int nb_ = ((tile0 + ti_) * kWarps + warp) * kRowsPerWarp;
+      const int k0 = kb_ * kKB + 32 * c;
+      if (ti_ >= ntile || nb_ >= out_rows || k0 >= p.K) return 0.f;
+      const int row = (r == 0 ? nb_ : (kGate ? half_n + nb_ : nb_ + 8)) + g;
+      const int64_t idx = int64_t(expert) * p.s_se + int64_t(row) * p.s_sn + k0 / p.group;
+      if constexpr (WF == W_MXFP4)   // e8m0: 2^(byte - 127), byte 0 = the zero block
+        return __uint_as_float(uint32_t(static_cast<const uint8_t*>(p.scales)[idx]) << 23);
+      else
+        return load_scale(p.scales, idx, p.scale_dtype);
+    };
+    float g4n0 = 0.f, g4n1 = 0.f;
+    if constexpr (is_w4(WF)) g4n0 = w4_scale(0, 0, 0), g4n1 = w4_scale(0, 0, 1);
     for (int it = 0; it < total_it; ++it) {
       cp_async_wait<kStages - 2>();
       __syncthreads();          // step `it` landed for everyone; the stage of it-1 is free
@@ -318,18 +374,22 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs
           ch0 = load_scale(p.scales, int64_t(expert) * p.s_se + row_lo + g, p.scale_dtype);
           ch1 = load_scale(p.scales, int64_t(expert) * p.s_se + row_hi + g, p.scale_dtype);
         }
-        sc0 = int64_t(expert) * p.s_se + int64_t((row_lo + g) / 128) * p.s_sn;
-        sc1 = int64_t(expert) * p.s_se + int64_t((row_hi + g) / 128) * p.s_sn;
+        const int rdiv = p.scale_kind == S_GROUP ? 1 : 128;
+        sc0 = int64_t(expert) * p.s_se + int64_t((row_lo + g) / rdiv) * p.s_sn;
+        sc1 = int64_t(expert) * p.s_se + int64_t((row_hi + g) / rdiv) * p.s_sn;
       }
       const uint8_t* st = smem + stage * L::kStage;
       const bool last_kb = kb == nkb - 1;
       const int kb_now = kb;
       stage = stage + 1 == kStages ? 0 : stage + 1;
       if (last_kb) kb = 0, ++ti; else ++kb;
+      const float g4_0 = g4n0, g4_1 = g4n1;
+      const bool defer4 = WF == W_INT4 && p.group == 128;
+      if constexpr (is_w4(WF)) g4n0 = w4_scale(ti, kb, 0), g4n1 = w4_scale(ti, kb, 1);
       if (!warp_live) continue;
 
       float sw0 = 1.f, sw1 = 1.f;
-      if (p.scale_kind == S_BLOCK) {
+      if (p.scale_kind >= S_BLOCK) {
         sw0 = load_scale(p.scales, sc0 + kb_now, p.scale_dtype);
         sw1 = load_scale(p.scales, sc1 + kb_now, p.scale_dtype);
       }
@@ -377,6 +437,16 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs
               const uint4 x = *reinterpret_cast<const uint4*>(st + w_off[r][i]);
               wf[r][4 * i] = x.x, wf[r][4 * i + 1] = x.y, wf[r][4 * i + 2] = x.z, wf[r][4 * i + 3] = x.w;
             }
+          } else if constexpr (is_w4(WF)) {
+            const uint4 x = *reinterpret_cast<const uint4*>(st + w_off[r][0]);
+            // a scale that covers the whole K block goes onto the fp32 sums and the
+            // weights stay exact (the reference's deferred-scale path and its oracle,
+            // tests/test_moe_wna16.py:50-62); finer groups scale the weights
+            const float ws = defer4 ? 1.f : (r == 0 ? g4_0 : g4_1);
+            widen4<WF>(x.x, ws, &wf[r][0]);
+            widen4<WF>(x.y, ws, &wf[r][4]);
+            widen4<WF>(x.z, ws, &wf[r][8]);
+            widen4<WF>(x.w, ws, &wf[r][12]);
           } else {
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
@@ -405,7 +475,7 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs
             if constexpr (AF == A_F16) mma_f16_16816(part, a, xr[2 * s], xr[2 * s + 1]);
             else mma_bf16_16816(part, a, xr[2 * s], xr[2 * s + 1]);
           }
-          const float f0 = kPrescale ? 1.f : sw0, f1 = kPrescale ? 1.f : sw1;
+          const float f0 = defer4 ? g4_0 : kPrescale ? 1.f : sw0, f1 = defer4 ? g4_1 : kPrescale ? 1.f : sw1;
           acc[j][0] += part[0] * f0;
           acc[j][1] += part[1] * f0;
           acc[j][2] += part[2] * f1;
@@ -432,8 +502,13 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs
           } else {
             const float tw = p.topk_w ? p.topk_w[sid] : 1.f;
             __nv_bfloat16* crow = static_cast<__nv_bfloat16*>(p.c) + sid * p.c_stride;
-            crow[row_lo + g] = __float2bfloat16_rn(v0 * tw);
-            crow[row_hi + g] = __float2bfloat16_rn(v1 * tw);
+            float b0 = 0.f, b1 = 0.f;
+            if (p.bias != nullptr) {
+              const __nv_bfloat16* brow = static_cast<const __nv_bfloat16*>(p.bias) + sid * p.bias_stride;
+              b0 = __bfloat162float(brow[row_lo + g]), b1 = __bfloat162float(brow[row_hi + g]);
+            }
+            crow[row_lo + g] = __float2bfloat16_rn(v0 * tw + b0);
+            crow[row_hi + g] = __float2bfloat16_rn(v1 * tw + b1);
           }
         }
       }
@@ -479,34 +554,43 @@ int launch_bm(const MoeArgs& p, int act, dim3 grid, cudaStream_t st) {
 
 using namespace strix;
 
-extern "C" int strix_moe_gemm(
+static int moe_gemm_impl(
     void* c, const void* a, const void* w, const void* scales, const float* act_scales,
     const int32_t* sorted_ids, const int32_t* expert_ids, const int32_t* num_post_padded,
     const float* topk_weights, int64_t num_valid, int64_t a_rows, int64_t experts, int64_t n,
     int64_t k, int64_t a_stride, int64_t c_stride, int64_t w_stride_e, int64_t w_stride_n,
     int64_t s_stride_e, int64_t s_stride_n, int64_t sa_stride, int64_t sorted_len,
     int64_t expert_len, int64_t top_k, int64_t block_m, int weight_format, int act_format,
-    int scale_kind, int scale_dtype, int gate_act, int c_is_f16, strix_stream_t stream) {
-  STRIX_CHECK(weight_format >= W_E4M3 && weight_format <= W_BF16, "unknown weight format");
+    int scale_kind, int scale_dtype, int gate_act, int c_is_f16, strix_stream_t stream,
+    const void* bias, int64_t bias_stride, int group) {
+  STRIX_CHECK(weight_format >= W_E4M3 && weight_format <= W_U8B128, "unknown weight format");
+  const bool w4 = is_w4(weight_format);
   STRIX_CHECK(act_format >= A_BF16 && act_format <= A_E4M3, "unknown activation format");
   STRIX_CHECK(gate_act >= ACT_NONE && gate_act <= ACT_GELU_TANH,
               "activation must be silu or gelu_tanh");
-  STRIX_CHECK(scale_kind >= S_NONE && scale_kind <= S_BLOCK && scale_dtype >= 0 && scale_dtype <= 2,
+  STRIX_CHECK(scale_kind >= S_NONE && scale_kind <= S_GROUP && scale_dtype >= 0 && scale_dtype <= 2,
               "scales bf16, fp16 or fp32");
   STRIX_CHECK(experts > 0 && n > 0 && k > 0 && num_valid >= 0 && a_rows >= 0, "bad ranks");
-  STRIX_CHECK(k % kKB == 0, "K %% 128");
+  STRIX_CHECK(w4 ? k % 32 == 0 : k % kKB == 0, "K %% 128 (K %% 32 for 4-bit weights)");
+  STRIX_CHECK(!w4 || (act_format == A_BF16 && (group == 32 || group == 64 || group == 128) &&
+                      scales != nullptr && (weight_format != W_MXFP4 || group == 32)),
+              "4-bit weights take bf16 activations and scales per 32, 64 or 128 elements (32 for MXFP4)");
+  STRIX_CHECK(bias == nullptr || gate_act == ACT_NONE, "bias only on plain outputs");
   STRIX_CHECK(gate_act == ACT_NONE || (n % 16 == 0 && topk_weights == nullptr),
               "silu_mul needs even N and no topk weights");
   STRIX_CHECK(gate_act != ACT_NONE || n % 16 == 0, "N %% 16");
   STRIX_CHECK(top_k >= 1 && block_m >= 1 && block_m <= 1024, "bad top_k / block_m");
-  STRIX_CHECK(expert_len * block_m >= sorted_len, "expert_ids too short for block_m %lld",
-              (long long)block_m);
+  STRIX_CHECK(expert_ids == nullptr || expert_len * block_m >= sorted_len,
+              "expert_ids too short for block_m %lld", (long long)block_m);
+  STRIX_CHECK((sorted_ids == nullptr) == (expert_ids == nullptr) &&
+                  (sorted_ids == nullptr) == (num_post_padded == nullptr),
+              "routing tensors come together or not at all");
   STRIX_CHECK(act_format != A_E4M3 || (weight_format == W_E4M3 && act_scales != nullptr),
               "e4m3 activations need e4m3 weights and activation scales");
   STRIX_CHECK(weight_format != W_BF16 || (act_format == A_BF16 && scale_kind == S_NONE),
               "bf16 weights take bf16 activations and no scales");
-  STRIX_CHECK(weight_format == W_BF16 || scale_kind != S_NONE, "quantized weights need scales");
-  STRIX_CHECK(scale_kind != S_BLOCK || (weight_format == W_E4M3 && n % 128 == 0),
+  STRIX_CHECK(weight_format == W_BF16 || w4 || scale_kind != S_NONE, "quantized weights need scales");
+  STRIX_CHECK(scale_kind != S_BLOCK || weight_format == W_E4M3,
               "block scales must be fp32 [E, N/128, K/128]");
   STRIX_CHECK(!c_is_f16 || (gate_act != ACT_NONE && act_format == A_F16),
               "fp16 output only for the fused activation of the fp16 form");
@@ -519,6 +603,7 @@ extern "C" int strix_moe_gemm(
   p.c = c, p.a = a, p.w = w, p.scales = scales, p.sa = act_scales;
   p.sorted_ids = sorted_ids, p.expert_ids = expert_ids, p.num_post = num_post_padded;
   p.topk_w = topk_weights;
+  p.bias = bias, p.bias_stride = bias_stride, p.group = group > 0 ? group : 128;
   p.num_valid = num_valid;
   p.a_stride = a_stride, p.c_stride = c_stride, p.w_se = w_stride_e, p.w_sn = w_stride_n;
   p.s_se = s_stride_e, p.s_sn = s_stride_n, p.sa_stride = sa_stride;
@@ -537,7 +622,8 @@ extern "C" int strix_moe_gemm(
     const char* e = getenv("STRIX_MOE_TILES_PER_CTA");
     return e ? atoi(e) : 0;
   }();
-  int64_t tpc = tpc_env > 0 ? tpc_env : (48 + k / kKB - 1) / (k / kKB);
+  const int64_t nkb = (k + kKB - 1) / kKB;
+  int64_t tpc = tpc_env > 0 ? tpc_env : (48 + nkb - 1) / nkb;
   if (tpc > n_tiles) tpc = n_tiles;
   p.tiles_per_cta = int(tpc);
   const dim3 grid{unsigned((n_tiles + tpc - 1) / tpc), unsigned(m_blocks), 1u};
@@ -546,6 +632,59 @@ extern "C" int strix_moe_gemm(
   if (weight_format == W_E4M3 && act_format == A_BF16) return launch_bm<W_E4M3, A_BF16>(p, gate_act, grid, st);
   if (weight_format == W_E4M3 && act_format == A_F16) return launch_bm<W_E4M3, A_F16>(p, gate_act, grid, st);
   if (weight_format == W_INT8 && act_format == A_BF16) return launch_bm<W_INT8, A_BF16>(p, gate_act, grid, st);
+  if (weight_format == W_U8B128 && act_format == A_BF16) return launch_bm<W_U8B128, A_BF16>(p, gate_act, grid, st);
   if (weight_format == W_BF16) return launch_bm<W_BF16, A_BF16>(p, gate_act, grid, st);
+  if (weight_format == W_MXFP4) return launch_bm<W_MXFP4, A_BF16>(p, gate_act, grid, st);
+  if (weight_format == W_INT4) return launch_bm<W_INT4, A_BF16>(p, gate_act, grid, st);
   return fail(STRIX_ERR_INVALID, "moe_gemm: weight/activation format pair not built");
+}
+
+extern "C" int strix_moe_gemm(
+    void* c, const void* a, const void* w, const void* scales, const float* act_scales,
+    const int32_t* sorted_ids, const int32_t* expert_ids, const int32_t* num_post_padded,
+    const float* topk_weights, int64_t num_valid, int64_t a_rows, int64_t experts, int64_t n,
+    int64_t k, int64_t a_stride, int64_t c_stride, int64_t w_stride_e, int64_t w_stride_n,
+    int64_t s_stride_e, int64_t s_stride_n, int64_t sa_stride, int64_t sorted_len,
+    int64_t expert_len, int64_t top_k, int64_t block_m, int weight_format, int act_format,
+    int scale_kind, int scale_dtype, int gate_act, int c_is_f16, strix_stream_t stream) {
+  STRIX_CHECK(weight_format <= W_BF16, "unknown weight format");
+  STRIX_CHECK(sorted_ids != nullptr, "routing tensors must not be NULL");
+  STRIX_CHECK(scale_kind != S_BLOCK || n % 128 == 0, "block scales must be fp32 [E, N/128, K/128]");
+  return moe_gemm_impl(c, a, w, scales, act_scales, sorted_ids, expert_ids, num_post_padded,
+                       topk_weights, num_valid, a_rows, experts, n, k, a_stride, c_stride,
+                       w_stride_e, w_stride_n, s_stride_e, s_stride_n, sa_stride, sorted_len,
+                       expert_len, top_k, block_m, weight_format, act_format, scale_kind,
+                       scale_dtype, gate_act, c_is_f16, stream, nullptr, 0, 0);
+}
+
+extern "C" int strix_gemm_w4a16(
+    void* c, const void* a, const void* w, const void* scales, const void* bias,
+    const int32_t* sorted_ids, const int32_t* expert_ids, const int32_t* num_post_padded,
+    const float* topk_weights, int64_t num_valid, int64_t a_rows, int64_t experts, int64_t n,
+    int64_t k, int64_t a_stride, int64_t c_stride, int64_t w_stride_e, int64_t w_stride_n,
+    int64_t s_stride_e, int64_t s_stride_n, int64_t bias_stride, int64_t sorted_len,
+    int64_t expert_len, int64_t top_k, int64_t block_m, int weight_format, int group,
+    int scale_dtype, int gate_act, strix_stream_t stream) {
+  STRIX_CHECK(weight_format == W_MXFP4 || weight_format == W_INT4, "weight_format 3 (mxfp4) or 4 (int4)");
+  return moe_gemm_impl(c, a, w, scales, nullptr, sorted_ids, expert_ids, num_post_padded,
+                       topk_weights, num_valid, a_rows, experts, n, k, a_stride, c_stride,
+                       w_stride_e, w_stride_n, s_stride_e, s_stride_n, 0, sorted_len, expert_len,
+                       top_k, block_m, weight_format, A_BF16, S_NONE, scale_dtype, gate_act, 0,
+                       stream, bias, bias_stride, group);
+}
+
+extern "C" int strix_dense_gemm_w8a16(void* c, const void* x, const void* w, const void* scales,
+                                      const void* bias, int64_t m, int64_t n, int64_t k,
+                                      int64_t x_stride, int64_t c_stride, int64_t w_stride,
+                                      int64_t s_stride_n, int64_t bias_stride, int64_t block_m,
+                                      int weight_format, int act_format, int scale_kind,
+                                      int scale_dtype, strix_stream_t stream) {
+  STRIX_CHECK(weight_format == W_E4M3 || weight_format == W_INT8 || weight_format == W_U8B128,
+              "weight_format 0 (e4m3), 1 (int8) or 5 (excess-128 bytes)");
+  STRIX_CHECK(m >= 0 && block_m >= 1, "bad M / block_m");
+  const int64_t sorted_len = (m + block_m - 1) / block_m * block_m;
+  return moe_gemm_impl(c, x, w, scales, nullptr, nullptr, nullptr, nullptr, nullptr, m, m, 1, n, k,
+                       x_stride, c_stride, 0, w_stride, 0, s_stride_n, 0, sorted_len, 0, 1, block_m,
+                       weight_format, act_format, scale_kind, scale_dtype, ACT_NONE, 0, stream, bias,
+                       bias_stride, 0);
 }

@@ -202,6 +202,47 @@ KERNELS: list[Kernel] = [
            "one-CTA tcgen05 tile product, the layout probe of the sm_100a kernels",
            {"weight_dtype": ("int8", "fp8_e4m3"), "m": 128}),
     *_MOE_ROWS,
+    # ------------------------------------------------- 4-bit experts, dense 4-/8-bit
+    Kernel("moe_gemm_w4a16", "moe_gemm_w4a16",
+           "int4 experts (nibble - 8, low nibble = even k) with 16-bit scales per 32/64/128 "
+           "elements x bf16 activations; weights widened in registers to scaled bf16",
+           {"silu_mul": (True, False), "dtype": "bf16", "weight_dtype": "uint8", "weight_bits": 4,
+            "quant": "wna16", "group_size": (32, 64, 128), "activation": _GATES},
+           dict(_STREAM_SPEC)),
+    Kernel("moe_gemm_mxfp4", "moe_gemm_mxfp4",
+           "MXFP4 experts (e2m1 nibbles, e8m0 scale per 32 elements, byte 0 = zero block) x bf16 "
+           "activations; the decode is exact in bf16. K % 32 == 0 (hidden 2880 is covered)",
+           {"silu_mul": (True, False), "dtype": "bf16", "weight_dtype": "uint8", "weight_bits": 4,
+            "quant": "mxfp4", "group_size": 32, "scale_dtype": "e8m0", "activation": _GATES},
+           dict(_STREAM_SPEC)),
+    Kernel("mxfp4_gemv", "mxfp4_gemv", "MXFP4 W4A16 at 1-8 rows (the dense form of moe_gemm_mxfp4)",
+           {"weight_bits": 4, "group_size": 32, "dtype": "bf16", "m_max": 8}, dict(_STREAM_SPEC)),
+    Kernel("mxfp4_wmma_gemm", "mxfp4", "MXFP4 W4A16 dense GEMM, optional bias [N] or [M, N]",
+           {"weight_bits": 4, "group_size": 32, "dtype": "bf16", "scale_dtype": "e8m0"},
+           dict(_STREAM_SPEC)),
+    Kernel("w4a16_wmma_gemm", "w4a16", "int4 W4A16 dense GEMM, optional bias",
+           {"weight_bits": 4, "group_size": (32, 64, 128), "dtype": "bf16",
+            "scale_dtype": ("bf16", "fp16")}, dict(_STREAM_SPEC)),
+    Kernel("mxfp4_dequant", "mxfp4_dequant", "MXFP4 -> bf16 [N, K], byte-exact",
+           {"weight_bits": 4, "group_size": 32, "dtype": "bf16"}),
+    Kernel("w4a16_dequant", "w4a16_dequant", "int4 -> bf16 [N, K]",
+           {"weight_bits": 4, "group_size": (32, 64, 128), "dtype": "bf16"}),
+    Kernel("fp8_dequant", "fp8_dequant", "e4m3 x fp32 block or channel scales -> bf16 [N, K]",
+           {"weight_bits": 8, "weight_dtype": "fp8_e4m3", "group_size": (0, 128), "dtype": "bf16"}),
+    Kernel("w8a16_skinny_gemm", "w8a16",
+           "excess-128 byte weights x bf16 activations at 1-8 rows, scales per channel or per "
+           "(row, 128 group)",
+           {"weight_bits": 8, "group_size": (0, 128), "rows": Range(hi=8), "dtype": "bf16"},
+           dict(_STREAM_SPEC)),
+    Kernel("fp8_skinny_gemm", "fp8", "e4m3 weights x bf16 activations at 1-8 rows",
+           {"weight_bits": 8, "weight_dtype": "fp8_e4m3", "group_size": (0, 128),
+            "rows": Range(hi=8), "dtype": "bf16"}, dict(_STREAM_SPEC)),
+    Kernel("fp8_wmma_gemm", "fp8", "e4m3 weights x bf16 activations, any row count",
+           {"weight_bits": 8, "weight_dtype": "fp8_e4m3", "group_size": (0, 128),
+            "rows": Range(lo=9), "dtype": "bf16"}, dict(_STREAM_SPEC)),
+    Kernel("fp8_wmma_gemm_raw", "fp8", "e4m3 weights (exact) x fp16 activations, scales on the sums",
+           {"weight_bits": 8, "weight_dtype": "fp8_e4m3", "group_size": (0, 128),
+            "rows": Range(lo=1), "dtype": "fp16"}, dict(_STREAM_SPEC)),
     # ---------------------------------------------------------- dense GEMMs
     Kernel("w8a8_int8_gemm", "w8a8",
            "dense W8A8 INT8 GEMM on tcgen05 kind::i8 (int32 sums in TMEM, exact): int8 "

@@ -379,6 +379,242 @@ def moe_sum(input, output):
                   output.stride(0), _stream())
 
 
+# ------------------------------------------------- 4-bit experts and dense 4-/8-bit GEMMs
+_W_MXFP4, _W_INT4, _W_U8B128 = 3, 4, 5
+_S_GROUP = 3
+
+
+def _dense_block_m(m: int) -> int:
+    return 16 if m <= 16 else 32 if m <= 32 else 64
+
+
+def _gemm_w4(c, a, w, scales, bias, routing, topk_weights, top_k, block_m, wfmt, group, gate):
+    """Host side of strix_gemm_w4a16; routing = (sorted_ids, expert_ids, num_post) or None."""
+    dense = routing is None
+    if dense:
+        e, (n, kh) = 1, w.shape
+        w_se, w_sn, s_se, s_sn = 0, w.stride(0), 0, scales.stride(0)
+    else:
+        e, n, kh = w.shape
+        w_se, w_sn, s_se, s_sn = w.stride(0), w.stride(1), scales.stride(0), scales.stride(1)
+    k = kh * 2
+    _check(a.dtype == torch.bfloat16 and c.dtype == torch.bfloat16 and w.dtype == torch.uint8,
+           "a, c bf16; w uint8 (two 4-bit values per byte)")
+    _check(a.dim() == 2 and a.size(1) == k and a.stride(1) == 1 and w.stride(-1) == 1
+           and c.stride(1) == 1 and scales.stride(-1) == 1, "shape mismatch / last dims must be contiguous")
+    if wfmt == _W_MXFP4:
+        _check(scales.dtype == torch.uint8, "scale must be uint8 (e8m0)")
+        sdt = 0
+    else:
+        _check(scales.dtype in (torch.bfloat16, torch.float16), "scales must be bf16 or fp16")
+        sdt = _SCALE_DTYPES[scales.dtype]
+    _check(k % group == 0 and tuple(scales.shape[-2:]) == (n, k // group),
+           f"scales must be [..., N, K / {group}]")
+    bias_stride = 0
+    if bias is not None:
+        _check(bias.dtype == torch.bfloat16 and bias.stride(-1) == 1
+               and (tuple(bias.shape) == (n,) or tuple(bias.shape) == (c.size(0), n)),
+               "bias must be bf16 [N] or [M, N]")
+        bias_stride = bias.stride(0) if bias.dim() == 2 else 0
+    if dense:
+        m = a.size(0)
+        sid = eid = npp = None
+        sorted_len, expert_len, num_valid = (m + block_m - 1) // block_m * block_m, 0, m
+    else:
+        sid, eid, npp = routing
+        _check(sid.dtype == torch.int32 and eid.dtype == torch.int32 and npp.dtype == torch.int32,
+               "routing tensors must be int32")
+        _check(eid.numel() * block_m >= sid.numel(), f"expert_ids too short for block_m {block_m}")
+        sorted_len, expert_len, num_valid = sid.numel(), eid.numel(), c.size(0)
+    with torch.cuda.device(c.device):
+        _lib.call("strix_gemm_w4a16", c.data_ptr(), a.data_ptr(), w.data_ptr(), scales.data_ptr(),
+                  _ptr(bias), _ptr(sid), _ptr(eid), _ptr(npp), _ptr(topk_weights), num_valid,
+                  a.size(0), e, n, k, a.stride(0), c.stride(0), w_se, w_sn, s_se, s_sn, bias_stride,
+                  sorted_len, expert_len, top_k, block_m, wfmt, group, sdt, gate, _stream())
+
+
+@_define("moe_gemm_w4a16(Tensor(a!) c, Tensor a, Tensor b, Tensor scales, Tensor sorted_ids, "
+         "Tensor expert_ids, Tensor num_post_padded, Tensor? topk_weights, int top_k, int block_m, "
+         "int block_n, bool silu_mul=False, str activation='silu', int group_size=32) -> ()")
+def moe_gemm_w4a16(c, a, b, scales, sorted_ids, expert_ids, num_post_padded, topk_weights, top_k,
+                   block_m, block_n, silu_mul=False, activation="silu", group_size=32):
+    _check(activation in _ACTS, f"activation must be silu or gelu_tanh, got {activation}")
+    _check(group_size in (32, 64, 128), "group_size must be 32, 64 or 128")
+    _check(c.size(1) == (b.size(1) // 2 if silu_mul else b.size(1)), "shape mismatch")
+    _check(not silu_mul or topk_weights is None, "silu_mul needs even N and no topk weights")
+    _gemm_w4(c, a, b, scales, None, (sorted_ids, expert_ids, num_post_padded), topk_weights, top_k,
+             block_m, _W_INT4, group_size, _ACTS[activation] if silu_mul else 0)
+
+
+# Not in the reference: MXFP4 experts (e2m1 + e8m0 per 32), the grouped form of
+# mxfp4_wmma_gemm with moe_gemm_w4a16's argument order.
+@_define("moe_gemm_mxfp4(Tensor(a!) c, Tensor a, Tensor b, Tensor scales, Tensor sorted_ids, "
+         "Tensor expert_ids, Tensor num_post_padded, Tensor? topk_weights, int top_k, int block_m, "
+         "int block_n, bool silu_mul=False, str activation='silu') -> ()")
+def moe_gemm_mxfp4(c, a, b, scales, sorted_ids, expert_ids, num_post_padded, topk_weights, top_k,
+                   block_m, block_n, silu_mul=False, activation="silu"):
+    _check(activation in _ACTS, f"activation must be silu or gelu_tanh, got {activation}")
+    _check(c.size(1) == (b.size(1) // 2 if silu_mul else b.size(1)), "shape mismatch")
+    _check(not silu_mul or topk_weights is None, "silu_mul needs even N and no topk weights")
+    _gemm_w4(c, a, b, scales, None, (sorted_ids, expert_ids, num_post_padded), topk_weights, top_k,
+             block_m, _W_MXFP4, 32, _ACTS[activation] if silu_mul else 0)
+
+
+def _dense_fake(rows_from, w_from):
+    def fake(*args, **kw):
+        x, w = args[rows_from], args[w_from]
+        return x.new_empty((x.size(0), w.size(0)), dtype=torch.bfloat16)
+    return fake
+
+
+@_define("mxfp4_wmma_gemm(Tensor w, Tensor x, Tensor scales, Tensor? bias) -> Tensor",
+         fake=_dense_fake(1, 0))
+def mxfp4_wmma_gemm(w, x, scales, bias=None):
+    _check(w.dim() == 2 and x.dim() == 2, "bad ranks")
+    _check(x.size(1) % 128 == 0, "K must be a multiple of 128")
+    out = torch.empty(x.size(0), w.size(0), dtype=torch.bfloat16, device=x.device)
+    if x.size(0):
+        _gemm_w4(out, x, w, scales, bias, None, None, 1, _dense_block_m(x.size(0)), _W_MXFP4, 32, 0)
+    return out
+
+
+@_define("mxfp4_gemv(Tensor x, Tensor w, Tensor scales) -> Tensor", fake=_dense_fake(0, 1))
+def mxfp4_gemv(x, w, scales):
+    _check(1 <= x.size(0) <= 8, "mxfp4_gemv takes 1-8 rows")
+    return mxfp4_wmma_gemm(w, x, scales, None)
+
+
+@_define("w4a16_wmma_gemm(Tensor x, Tensor w, Tensor scales, Tensor? bias, int group_size) -> Tensor",
+         fake=_dense_fake(0, 1))
+def w4a16_wmma_gemm(x, w, scales, bias, group_size):
+    _check(group_size in (32, 64, 128), "group_size must be 32, 64 or 128")
+    out = torch.empty(x.size(0), w.size(0), dtype=torch.bfloat16, device=x.device)
+    if x.size(0):
+        _gemm_w4(out, x, w, scales, bias, None, None, 1, _dense_block_m(x.size(0)), _W_INT4,
+                 group_size, 0)
+    return out
+
+
+def _dequant(w, scales, fmt, group, scale_kind, k):
+    n = w.size(0)
+    out = torch.empty(n, k, dtype=torch.bfloat16, device=w.device)
+    _check(w.dim() == 2 and w.stride(1) == 1, "w must be [N, bytes] with a contiguous last dim")
+    s_n = scales.stride(0)
+    s_g = scales.stride(1) if scales.dim() == 2 else 0
+    sdt = _SCALE_DTYPES.get(scales.dtype, 0)
+    with torch.cuda.device(w.device):
+        _lib.call("strix_dequant_bf16", out.data_ptr(), w.data_ptr(), scales.data_ptr(), n, k,
+                  w.stride(0), out.stride(0), s_n, s_g, fmt, group, scale_kind, sdt, _stream())
+    return out
+
+
+def _dq_fake(w, scales, *a):
+    return w.new_empty((w.size(0), w.size(1) * (1 if w.dtype == torch.float8_e4m3fn else 2)),
+                       dtype=torch.bfloat16)
+
+
+@_define("mxfp4_dequant(Tensor w, Tensor scales) -> Tensor", fake=_dq_fake)
+def mxfp4_dequant(w, scales):
+    k = w.size(1) * 2
+    _check(w.dtype == torch.uint8 and scales.dtype == torch.uint8, "scale must be uint8 (e8m0)")
+    _check(k % 32 == 0 and tuple(scales.shape) == (w.size(0), k // 32), "scales must be [N, K / 32]")
+    return _dequant(w, scales, 0, 32, 0, k)
+
+
+@_define("w4a16_dequant(Tensor w, Tensor scales, int group_size) -> Tensor", fake=_dq_fake)
+def w4a16_dequant(w, scales, group_size):
+    k = w.size(1) * 2
+    _check(w.dtype == torch.uint8 and scales.dtype in (torch.bfloat16, torch.float16),
+           "w uint8, scales bf16 or fp16")
+    _check(group_size in (32, 64, 128) and tuple(scales.shape) == (w.size(0), k // group_size),
+           "scales must be [N, K / group_size]")
+    return _dequant(w, scales, 1, group_size, 0, k)
+
+
+@_define("fp8_dequant(Tensor w, Tensor scales) -> Tensor", fake=_dq_fake)
+def fp8_dequant(w, scales):
+    n, k = w.shape
+    _check(w.dtype == torch.float8_e4m3fn and scales.dtype == torch.float32, "w e4m3, scales fp32")
+    if scales.dim() == 2 and scales.size(1) != 1:
+        _check(k % 128 == 0 and tuple(scales.shape) == ((n + 127) // 128, k // 128),
+               "block scales must be [ceil(N/128), K/128]")
+        return _dequant(w, scales, 2, 128, 2, k)
+    _check(scales.numel() == n, "channel scales must be [N]")
+    return _dequant(w, scales.reshape(n), 2, 128, 1, k)
+
+
+def _dense_w8(x, w, scales, bias, wfmt, afmt, scale_kind):
+    m, k = x.shape
+    n = w.size(0)
+    _check(w.dim() == 2 and w.size(1) == k and x.stride(1) == 1 and w.stride(1) == 1,
+           "shape mismatch / last dims must be contiguous")
+    _check(k % 128 == 0, "K must be a multiple of 128")
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
+    bias_stride = 0
+    if bias is not None:
+        _check(bias.dtype == torch.bfloat16 and bias.stride(-1) == 1
+               and (tuple(bias.shape) == (n,) or tuple(bias.shape) == (m, n)),
+               "bias must be bf16 [N] or [M, N]")
+        bias_stride = bias.stride(0) if bias.dim() == 2 else 0
+    if m:
+        with torch.cuda.device(x.device):
+            _lib.call("strix_dense_gemm_w8a16", out.data_ptr(), x.data_ptr(), w.data_ptr(),
+                      scales.data_ptr(), _ptr(bias), m, n, k, x.stride(0), out.stride(0), w.stride(0),
+                      scales.stride(0) if scale_kind != _S_CHANNEL else 0, bias_stride,
+                      _dense_block_m(m), wfmt, afmt, scale_kind, _SCALE_DTYPES[scales.dtype],
+                      _stream())
+    return out
+
+
+@_define("w8a16_skinny_gemm(Tensor in_a, Tensor in_b, Tensor in_scale, Tensor? in_bias, int CuCount, "
+         "int group_size) -> Tensor", fake=_dense_fake(1, 0))
+def w8a16_skinny_gemm(in_a, in_b, in_scale, in_bias, CuCount, group_size):
+    """in_a: excess-128 weights uint8 [N, K]; in_b: activations bf16 [M <= 8, K];
+    in_scale: 16-bit [N] (group_size 0) or [N, K / 128] (group_size 128)."""
+    _check(1 <= in_b.size(0) <= 8, "w8a16_skinny_gemm takes 1-8 rows")
+    _check(in_a.dtype == torch.uint8 and in_b.dtype == torch.bfloat16
+           and in_scale.dtype in _SCALE_DTYPES, "in_a uint8, in_b bf16")
+    _check(group_size in (0, 128), "group_size must be 0 or 128")
+    n, k = in_a.shape
+    if group_size:
+        _check(tuple(in_scale.shape) == (n, k // 128) and in_scale.stride(1) == 1,
+               "scales must be [N, K / 128]")
+        return _dense_w8(in_b, in_a, in_scale, in_bias, _W_U8B128, _A_BF16, _S_GROUP)
+    _check(in_scale.numel() == n, "scales must be [N]")
+    return _dense_w8(in_b, in_a, in_scale.reshape(n), in_bias, _W_U8B128, _A_BF16, _S_CHANNEL)
+
+
+def _fp8_dense(w, x, scales, bias, afmt):
+    _check(w.dtype == torch.float8_e4m3fn and scales.dtype == torch.float32, "w e4m3, scales fp32")
+    n, k = w.shape
+    if scales.dim() == 2 and scales.size(1) != 1:
+        _check(tuple(scales.shape) == ((n + 127) // 128, k // 128) and scales.stride(1) == 1,
+               "block scales must be [ceil(N/128), K/128]")
+        return _dense_w8(x, w, scales, bias, _W_E4M3, afmt, _S_BLOCK)
+    _check(scales.numel() == n, "channel scales must be [N]")
+    return _dense_w8(x, w, scales.reshape(n), bias, _W_E4M3, afmt, _S_CHANNEL)
+
+
+@_define("fp8_skinny_gemm(Tensor in_a, Tensor in_b, Tensor in_scale, Tensor? in_bias, int CuCount) "
+         "-> Tensor", fake=_dense_fake(1, 0))
+def fp8_skinny_gemm(in_a, in_b, in_scale, in_bias, CuCount):
+    _check(1 <= in_b.size(0) <= 8, "fp8_skinny_gemm takes 1-8 rows")
+    _check(in_b.dtype == torch.bfloat16, "in_b must be bf16")
+    return _fp8_dense(in_a, in_b, in_scale, in_bias, _A_BF16)
+
+
+@_define("fp8_wmma_gemm(Tensor w, Tensor x, Tensor scales) -> Tensor", fake=_dense_fake(1, 0))
+def fp8_wmma_gemm(w, x, scales):
+    _check(x.dtype == torch.bfloat16, "x must be bf16")
+    return _fp8_dense(w, x, scales, None, _A_BF16)
+
+
+@_define("fp8_wmma_gemm_raw(Tensor w, Tensor x, Tensor scales) -> Tensor", fake=_dense_fake(1, 0))
+def fp8_wmma_gemm_raw(w, x, scales):
+    _check(x.dtype == torch.float16, "x must be fp16")
+    return _fp8_dense(w, x, scales, None, _A_F16)
+
+
 # ------------------------------------------------------------ dense quantized GEMMs
 
 def _w8a8_int8_fake(a_q, a_scale, w, w_scale, acc_out=None):

@@ -54,3 +54,60 @@ def act_quant_group_i8(x: torch.Tensor):
     s = torch.where(amax > 0, amax / 127, torch.ones_like(amax))
     q = torch.clamp(torch.round(xg / s), -127, 127).to(torch.int8)
     return q.reshape(m, k), s.reshape(m, k // 128)
+
+
+# ------------------------------------------------------------------ 4-bit formats
+MX_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+
+
+def mxfp4_dequant(w_u8: torch.Tensor, s_u8: torch.Tensor) -> torch.Tensor:
+    """fp32 [..., N, K]: e2m1 nibbles (low nibble = even k) times 2^(scale - 127),
+    a scale byte of 0 being the zero block - tests/test_mxfp4.py:29-47 with the
+    kernel's zero-block rule of :65-70 and :118-127."""
+    lut = torch.tensor(MX_VALUES, dtype=torch.float32)
+    w = w_u8.to(torch.int32)
+
+    def value(nib):
+        v = lut[(nib & 7).long()]
+        return torch.where((nib & 8) != 0, -v, v)
+
+    out = torch.empty(*w_u8.shape[:-1], w_u8.size(-1) * 2, dtype=torch.float32)
+    out[..., 0::2] = value(w & 15)
+    out[..., 1::2] = value((w >> 4) & 15)
+    scale = torch.pow(2.0, s_u8.float() - 127.0) * (s_u8 != 0)
+    return out * scale.repeat_interleave(32, dim=-1)
+
+
+def int4_pack(q: torch.Tensor) -> torch.Tensor:
+    """[..., K] values 0..15 -> [..., K/2] bytes, low nibble = even k
+    (tests/test_moe_wna16.py:44-46)."""
+    return (q[..., 0::2] | (q[..., 1::2] << 4)).contiguous()
+
+
+def int4_dequant(w_u8: torch.Tensor, scales: torch.Tensor, group: int, exact: bool = False):
+    """(nibble - 8) * scale per group, rounded to bf16 unless `exact`
+    (tests/test_moe_wna16.py:48-62)."""
+    q = torch.stack([(w_u8 & 0xF).float() - 8.0, ((w_u8 >> 4) & 0xF).float() - 8.0],
+                    dim=-1).reshape(*w_u8.shape[:-1], -1)
+    w = q * scales.float().repeat_interleave(group, dim=-1)
+    return w if exact else w.to(torch.bfloat16)
+
+
+def w8a16_reference(x, w_u8, scales, group_size):
+    """fp32 [M, N] of excess-128 byte weights (tests/test_w8a16.py:9-17)."""
+    w = w_u8.float() - 128.0
+    k = w.size(1)
+    s = scales.float()
+    s = s.repeat_interleave(group_size, dim=1)[:, :k] if group_size else s.reshape(-1, 1)
+    return x.float() @ (w * s).t()
+
+
+def fp8_dequant(w: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    """fp32 [N, K]: e4m3 times fp32 scales per channel [N] or per 128 x 128 block
+    [ceil(N/128), K/128] (csrc/gemm/fp8_dequant.hip:63)."""
+    n, k = w.shape
+    if scales.dim() == 2 and scales.size(1) != 1:
+        full = scales.repeat_interleave(128, 0)[:n].repeat_interleave(128, 1)[:, :k]
+    else:
+        full = scales.reshape(n, 1)
+    return w.float() * full

@@ -1,0 +1,251 @@
+"""4-bit expert formats (MXFP4, int4) and the dense 4-/8-bit GEMMs and decoders
+against the CPU oracle. Cases follow the reference's tests/test_mxfp4.py,
+tests/test_moe_wna16.py, tests/test_w8a16.py and tests/test_fp8.py (same shapes
+where the CPU oracle stays fast, fewer experts)."""
+
+import pytest
+import torch
+
+import libstrix_b200 as strix  # noqa: F401  (registers torch.ops.strix)
+from oracle import gemm as G
+from oracle import moe as M
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+ops = torch.ops.strix
+
+
+def close_to_peak(out, ref, atol):
+    out, ref = out.float().cpu(), ref.float()
+    assert torch.isfinite(out).all()
+    peak = ref.abs().amax().clamp_min(1e-30)
+    torch.testing.assert_close(out / peak, ref / peak, rtol=0, atol=atol)
+
+
+def rms_check(out, ref, tol):
+    out, ref = out.float().cpu(), ref.float()
+    assert torch.isfinite(out).all()
+    rms = ref.pow(2).mean().sqrt().item()
+    err = (out - ref).abs()
+    assert bool((err <= tol * max(rms, 1e-6) + ref.abs() * 2.0 ** -8).all()), \
+        f"max err {err.max().item():.3g}, rms {rms:.3g}"
+
+
+# ------------------------------------------------------------------ MXFP4 dense
+
+def mx_case(n, k, seed=0, lo=118, hi=134):
+    g = torch.Generator().manual_seed(seed)
+    w = torch.randint(0, 256, (n, k // 2), generator=g, dtype=torch.uint8)
+    s = torch.randint(lo, hi, (n, k // 32), generator=g, dtype=torch.uint8)
+    return w, s
+
+
+@pytest.mark.parametrize("n,k", [(256, 1024), (2048, 2688), (96, 5376)])
+def test_mxfp4_dequant_is_byte_exact(n, k):
+    w, s = mx_case(n, k)
+    s[0, :3] = 0
+    out = ops.mxfp4_dequant(w.to(DEV), s.to(DEV))
+    assert out.dtype == torch.bfloat16 and out.shape == (n, k)
+    torch.testing.assert_close(out.float().cpu(), G.mxfp4_dequant(w, s), rtol=0, atol=0)
+
+
+def test_mxfp4_gemm_is_the_dequantiser_on_one_hot_rows():
+    n, k = 256, 128
+    w, s = mx_case(n, k, lo=120, hi=135)
+    x = torch.eye(k, dtype=torch.bfloat16)
+    out = ops.mxfp4_wmma_gemm(w.to(DEV), x.to(DEV), s.to(DEV), None)
+    torch.testing.assert_close(out.t().float().cpu(), G.mxfp4_dequant(w, s), rtol=0, atol=0)
+
+
+def test_mxfp4_zero_block_scale_is_zero():
+    n, k = 64, 128
+    w, _ = mx_case(n, k)
+    s = torch.zeros(n, k // 32, dtype=torch.uint8)
+    s[:, 1] = 127
+    x0 = torch.zeros(8, k, dtype=torch.bfloat16)
+    x0[:, :32] = 1.0
+    x1 = torch.zeros(8, k, dtype=torch.bfloat16)
+    x1[:, 32:] = 1.0
+    assert torch.count_nonzero(ops.mxfp4_wmma_gemm(w.to(DEV), x0.to(DEV), s.to(DEV), None)) == 0
+    assert torch.count_nonzero(ops.mxfp4_wmma_gemm(w.to(DEV), x1.to(DEV), s.to(DEV), None)) > 0
+
+
+@pytest.mark.parametrize("n,k", [(256, 1024), (2048, 2688), (5376, 2688)])
+@pytest.mark.parametrize("m", [1, 5, 32, 513])
+def test_mxfp4_gemm_matches_dequant(n, k, m):
+    w, s = mx_case(n, k)
+    x = torch.randn(m, k, generator=torch.Generator().manual_seed(1)).bfloat16()
+    out = ops.mxfp4_wmma_gemm(w.to(DEV), x.to(DEV), s.to(DEV), None)
+    close_to_peak(out, x.float() @ G.mxfp4_dequant(w, s).t(), 1e-2)
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 5, 8])
+def test_mxfp4_gemv(m):
+    n, k = 1024, 2688
+    w, s = mx_case(n, k)
+    x = torch.randn(m, k, generator=torch.Generator().manual_seed(1)).bfloat16()
+    out = ops.mxfp4_gemv(x.to(DEV), w.to(DEV), s.to(DEV))
+    close_to_peak(out, x.float() @ G.mxfp4_dequant(w, s).t(), 1e-2)
+
+
+@pytest.mark.parametrize("bias_dim", [1, 2])
+def test_mxfp4_bias(bias_dim):
+    n, k, m = 512, 1024, 33
+    w, s = mx_case(n, k)
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(m, k, generator=g).bfloat16()
+    bias = torch.randn((n,) if bias_dim == 1 else (m, n), generator=g).bfloat16()
+    out = ops.mxfp4_wmma_gemm(w.to(DEV), x.to(DEV), s.to(DEV), bias.to(DEV))
+    close_to_peak(out, x.float() @ G.mxfp4_dequant(w, s).t() + bias.float(), 1e-2)
+
+
+def test_mxfp4_rejects_unbuilt_shapes():
+    x = torch.zeros(4, 96, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(8, 48, dtype=torch.uint8, device=DEV)
+    s = torch.zeros(8, 3, dtype=torch.uint8, device=DEV)
+    with pytest.raises(RuntimeError, match="K must be a multiple of 128"):
+        ops.mxfp4_wmma_gemm(w, x, s, None)
+    x = torch.zeros(4, 128, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(8, 64, dtype=torch.uint8, device=DEV)
+    with pytest.raises(RuntimeError, match="scale must be uint8"):
+        ops.mxfp4_wmma_gemm(w, x, w.to(torch.bfloat16), None)
+
+
+# ------------------------------------------------------------- grouped 4-bit experts
+
+E, TOP_K = 16, 4
+
+
+def routing(tokens, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return torch.stack([torch.randperm(E, generator=g)[:TOP_K] for _ in range(tokens)]).int()
+
+
+def run_grouped(op, extra, a, w_dev, s_dev, b_deq, ids, gemm, activation, block_m):
+    tokens = ids.size(0)
+    n = b_deq.size(1)
+    if gemm == "w13":
+        a_topk, weights, out_cols = TOP_K, None, n // 2
+    else:
+        a_topk, out_cols = 1, n
+        weights = torch.rand(tokens, TOP_K, generator=torch.Generator().manual_seed(5))
+    sorted_ids, expert_ids, num_post = M.align(ids, block_m, E)
+    c = torch.full((tokens * TOP_K, out_cols), float("nan"), dtype=torch.bfloat16, device=DEV)
+    op(c, a.to(DEV), w_dev, s_dev, sorted_ids.to(DEV), expert_ids.to(DEV), num_post.to(DEV),
+       None if weights is None else weights.flatten().to(DEV), a_topk, block_m, 64, gemm == "w13",
+       activation, *extra)
+    ref = M.grouped_reference(a, b_deq, ids, a_topk, weights)
+    if gemm == "w13":
+        ref = M.gate_mul(ref, activation)
+    return c, ref
+
+
+# gemma-4-26B-like (group 32, K tail of 64 on the down GEMM) and a group-128 model
+W4_MODELS = {"gemma": (32, (1408, 2816), (2816, 704)), "qfn": (128, (1280, 2560), (2560, 640))}
+
+
+@pytest.mark.parametrize("scale_dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("tokens", [1, 5, 70])
+@pytest.mark.parametrize("block_m", [16, 64])
+@pytest.mark.parametrize("gemm,activation", [("w13", "silu"), ("w13", "gelu_tanh"), ("w2", "silu")])
+@pytest.mark.parametrize("model", ["gemma", "qfn"])
+def test_moe_gemm_w4a16(model, tokens, block_m, gemm, activation, scale_dtype):
+    group, w13, w2 = W4_MODELS[model]
+    n, k = w13 if gemm == "w13" else w2
+    g = torch.Generator().manual_seed(0)
+    w_u8 = G.int4_pack(torch.randint(0, 16, (E, n, k), generator=g, dtype=torch.uint8))
+    scales = (torch.rand(E, n, k // group, generator=g) * 0.02 + 0.001).to(scale_dtype)
+    b = G.int4_dequant(w_u8, scales, group, exact=group % 64 == 0)
+    a = torch.randn(tokens if gemm == "w13" else tokens * TOP_K, k, generator=g).bfloat16()
+    c, ref = run_grouped(ops.moe_gemm_w4a16, (group,), a, w_u8.to(DEV), scales.to(DEV), b,
+                         routing(tokens), gemm, activation, block_m)
+    torch.testing.assert_close(c.float().cpu(), ref, rtol=2e-2, atol=2e-2)
+
+
+# gpt-oss-120B-like: hidden 2880 = 22.5 x 128 (the last K block is half empty)
+@pytest.mark.parametrize("tokens", [1, 7, 70])
+@pytest.mark.parametrize("block_m", [16, 32, 64])
+@pytest.mark.parametrize("gemm,activation", [("w13", "silu"), ("w2", "silu")])
+def test_moe_gemm_mxfp4(tokens, block_m, gemm, activation):
+    n, k = (5760, 2880) if gemm == "w13" else (2880, 2880)
+    g = torch.Generator().manual_seed(0)
+    w = torch.randint(0, 256, (E, n, k // 2), generator=g, dtype=torch.uint8)
+    s = torch.randint(118, 126, (E, n, k // 32), generator=g, dtype=torch.uint8)
+    s[0, :4, :2] = 0
+    b = G.mxfp4_dequant(w, s)
+    a = torch.randn(tokens if gemm == "w13" else tokens * TOP_K, k, generator=g).bfloat16()
+    c, ref = run_grouped(ops.moe_gemm_mxfp4, (), a, w.to(DEV), s.to(DEV), b, routing(tokens), gemm,
+                         activation, block_m)
+    rms_check(c, ref, 2e-2)
+
+
+def test_w4a16_dense_and_dequant():
+    n, k, group = 512, 1024, 64
+    g = torch.Generator().manual_seed(0)
+    w_u8 = G.int4_pack(torch.randint(0, 16, (n, k), generator=g, dtype=torch.uint8))
+    scales = (torch.rand(n, k // group, generator=g) * 0.02 + 0.001).bfloat16()
+    x = torch.randn(40, k, generator=g).bfloat16()
+    dq = ops.w4a16_dequant(w_u8.to(DEV), scales.to(DEV), group)
+    assert torch.equal(dq.cpu(), G.int4_dequant(w_u8, scales, group))
+    out = ops.w4a16_wmma_gemm(x.to(DEV), w_u8.to(DEV), scales.to(DEV), None, group)
+    close_to_peak(out, x.float() @ G.int4_dequant(w_u8, scales, group).float().t(), 1e-2)
+
+
+# ------------------------------------------------------------------ dense 8-bit
+
+@pytest.mark.parametrize("n,k", [(16384, 5120), (5120, 17408), (256, 1024)])
+@pytest.mark.parametrize("m", [1, 3, 8])
+@pytest.mark.parametrize("group_size", [0, 128])
+def test_w8a16_skinny(n, k, m, group_size):
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(m, k, generator=g).bfloat16()
+    w_u8 = torch.randint(0, 256, (n, k), generator=g, dtype=torch.uint8)
+    s = (torch.rand(n, k // group_size if group_size else 1, generator=g) * 0.01).bfloat16()
+    if group_size == 0:
+        s = s.reshape(n)
+    out = ops.w8a16_skinny_gemm(w_u8.to(DEV), x.to(DEV), s.to(DEV), None, 40, group_size)
+    close_to_peak(out, G.w8a16_reference(x, w_u8, s, group_size), 3e-2)
+
+
+def test_w8a16_skinny_rejects_more_than_8_rows():
+    x = torch.randn(9, 256, device=DEV, dtype=torch.bfloat16)
+    w_u8 = torch.randint(0, 256, (128, 256), device=DEV, dtype=torch.uint8)
+    s = torch.full((128,), 0.01, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="1-8 rows"):
+        ops.w8a16_skinny_gemm(w_u8, x, s, None, 40, 0)
+
+
+def fp8_case(n, k, scheme, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    wf = torch.randn(n, k, generator=g) * 0.02
+    if scheme == "block":
+        nb, kb = (n + 127) // 128, k // 128
+        pad = torch.zeros(nb * 128, k)
+        pad[:n] = wf
+        amax = pad.view(nb, 128, kb, 128).abs().amax((1, 3)).clamp_min(1e-12)
+        scales = amax / 448.0
+        full = scales.repeat_interleave(128, 0)[:n].repeat_interleave(128, 1)
+    else:
+        scales = wf.abs().amax(1).clamp_min(1e-12) / 448.0
+        full = scales[:, None]
+    return (wf / full).to(torch.float8_e4m3fn), scales.float()
+
+
+@pytest.mark.parametrize("scheme", ["block", "channel"])
+@pytest.mark.parametrize("n,k", [(2048, 2048), (1024 + 64, 1024)])
+def test_fp8_dequant_and_gemms(scheme, n, k):
+    w, scales = fp8_case(n, k, scheme)
+    ref_w = G.fp8_dequant(w, scales)
+    dq = ops.fp8_dequant(w.to(DEV), scales.to(DEV))
+    assert torch.equal(dq.cpu(), ref_w.to(torch.bfloat16))
+    g = torch.Generator().manual_seed(3)
+    for m in (1, 8, 70):
+        x = torch.randn(m, k, generator=g).bfloat16()
+        ref = x.float() @ ref_w.to(torch.bfloat16).float().t()
+        if m <= 8:
+            out = ops.fp8_skinny_gemm(w.to(DEV), x.to(DEV), scales.to(DEV), None, 40)
+            close_to_peak(out, ref, 1e-2)
+        out = ops.fp8_wmma_gemm(w.to(DEV), x.to(DEV), scales.to(DEV))
+        close_to_peak(out, ref, 1e-2)
+        out = ops.fp8_wmma_gemm_raw(w.to(DEV), x.half().to(DEV), scales.to(DEV))
+        close_to_peak(out, x.half().float() @ ref_w.t(), 1e-2)
