@@ -227,6 +227,27 @@ int strix_dense_gemm_w8a16(void* c, const void* x, const void* w, const void* sc
                            int64_t bias_stride, int64_t block_m, int weight_format,
                            int act_format, int scale_kind, int scale_dtype, strix_stream_t stream);
 
+/* Grouped or dense GEMM with int8 activations (qa int8 [rows, k], sa fp32 [rows,
+ * k/128], the output of strix_moe_act_quant_i8): s8 x s8 MMAs, sums exact in
+ * int32 per 128-wide K group, folded in fp32 with sa * weight scale. Replaces
+ * moe_gemm_w4a8 (csrc/moe/moe_gemm_w4a8.hip:374, kernel :57-277) and the GEMM
+ * half of w8a8_wmma_gemm (csrc/gemm/w8a8_wmma_gemm.hip:799-918).
+ *   weight_format 4: int4 [E, N, K/2] (nibble - 8); 5: excess-128 bytes [E, N, K]
+ *   scale_kind 1: per channel [E, N]; 3: per (row, group), element strides
+ *   s_stride_n over rows and s_stride_g over groups (so [N, K/128] and
+ *   [K/128, N] are both taken in place); scale_dtype 0 fp32, 1 bf16, 2 fp16.
+ * Routing as in strix_moe_gemm, or all three routing pointers NULL for a dense
+ * GEMM (see strix_gemm_w4a16). c bf16. */
+int strix_gemm_w8a8_group(void* c, const void* qa, const float* sa, const void* w,
+                          const void* scales, const int32_t* sorted_ids, const int32_t* expert_ids,
+                          const int32_t* num_post_padded, const float* topk_weights,
+                          int64_t num_valid, int64_t a_rows, int64_t experts, int64_t n, int64_t k,
+                          int64_t a_stride, int64_t c_stride, int64_t w_stride_e, int64_t w_stride_n,
+                          int64_t s_stride_e, int64_t s_stride_n, int64_t s_stride_g,
+                          int64_t sa_stride, int64_t sorted_len, int64_t expert_len, int64_t top_k,
+                          int64_t block_m, int weight_format, int scale_kind, int scale_dtype,
+                          int gate_act, strix_stream_t stream);
+
 /* Whole-matrix decode to bf16 [n, k], byte-exact. Replaces mxfp4_dequant
  * (csrc/gemm/mxfp4_wmma_gemm.hip), w4a16_dequant and fp8_dequant
  * (csrc/gemm/fp8_dequant.hip:63). format 0 mxfp4 (w [n, k/2], scales e8m0

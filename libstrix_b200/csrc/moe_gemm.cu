@@ -37,7 +37,8 @@ constexpr int kKB = 128;  // K elements per pipeline step (= the scale block)
 
 enum WFmt { W_E4M3 = 0, W_INT8 = 1, W_BF16 = 2, W_MXFP4 = 3, W_INT4 = 4, W_U8B128 = 5 };
 constexpr bool is_w4(int wf) { return wf == W_MXFP4 || wf == W_INT4; }
-enum AFmt { A_BF16 = 0, A_F16 = 1, A_E4M3 = 2 };
+enum AFmt { A_BF16 = 0, A_F16 = 1, A_E4M3 = 2, A_INT8 = 3 };
+constexpr bool is_a8(int af) { return af == A_E4M3 || af == A_INT8; }
 // S_GROUP: one scale per output row and 128-wide K group, [E, N, K/128]
 enum ScaleKind { S_NONE = 0, S_CHANNEL = 1, S_BLOCK = 2, S_GROUP = 3 };
 enum Act { ACT_NONE = 0, ACT_SILU = 1, ACT_GELU_TANH = 2 };
@@ -56,6 +57,7 @@ struct MoeArgs {
   int64_t bias_stride;
   int64_t num_valid;
   int64_t a_stride, c_stride, w_se, w_sn, s_se, s_sn, sa_stride;  // elements
+  int64_t s_sg;       // stride of the scale tensor over 128-wide K groups (S_BLOCK, S_GROUP)
   int top_k, K, N, block_m;
   int scale_kind, scale_dtype;  // dtype: 0 fp32, 1 bf16, 2 fp16
   int c_f16;
@@ -162,12 +164,12 @@ __device__ __forceinline__ uint32_t row_chunk_offset(int row, int chunk) {
 template <int WF, int AF, int BMC>
 struct Layout {
   static constexpr int WB = WF == W_BF16 ? 2 : 1;    // bytes per unit of the weight strides
-  static constexpr int AB = AF == A_E4M3 ? 1 : 2;    // activation bytes / element
+  static constexpr int AB = is_a8(AF) ? 1 : 2;       // activation bytes / element
   static constexpr int kWRow = is_w4(WF) ? kKB / 2 : kKB * WB, kARow = kKB * AB;
   static constexpr int kWElems = kKB * 16 / kWRow;   // K elements per 16-byte weight chunk
   static constexpr int kWBytes = kWarps * 16 * kWRow;  // all warps' weight rows
   static constexpr int kABytes = BMC * kARow;
-  static constexpr int kSaBytes = AF == A_E4M3 ? BMC * 4 : 0;
+  static constexpr int kSaBytes = is_a8(AF) ? BMC * 4 : 0;
   static constexpr int kStage = kWBytes + kABytes + kSaBytes;
   static constexpr int kSmem = kStages * kStage + BMC * 8 + 16;
 };
@@ -269,7 +271,7 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs
     }
     const float* sa_src = nullptr;
     bool sa_ok = false;
-    if constexpr (AF == A_E4M3) {
+    if constexpr (is_a8(AF)) {
       if (threadIdx.x < BMC) {
         const int64_t arow = s_arow[threadIdx.x];
         sa_ok = arow >= 0;
@@ -324,7 +326,7 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs
           const bool in_k = (id % CPA) * (16 / L::AB) < k_left;
           cp_async_16_zfill(st + a_dst[i], in_k ? a_src[i] + koff : a_src[i], a_ok[i] && in_k);
         }
-        if constexpr (AF == A_E4M3) {
+        if constexpr (is_a8(AF)) {
           if (sa_src != nullptr && int(threadIdx.x) < nt_live * 8)
             cp_async_4_zfill(st + L::kWBytes + L::kABytes + threadIdx.x * 4, sa_src + kb_issue, sa_ok);
         }
@@ -358,7 +360,7 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs
         return load_scale(p.scales, idx, p.scale_dtype);
     };
     float g4n0 = 0.f, g4n1 = 0.f;
-    if constexpr (is_w4(WF)) g4n0 = w4_scale(0, 0, 0), g4n1 = w4_scale(0, 0, 1);
+    if constexpr (is_w4(WF) && !is_a8(AF)) g4n0 = w4_scale(0, 0, 0), g4n1 = w4_scale(0, 0, 1);
     for (int it = 0; it < total_it; ++it) {
       cp_async_wait<kStages - 2>();
       __syncthreads();          // step `it` landed for everyone; the stage of it-1 is free
@@ -385,25 +387,43 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs
       if (last_kb) kb = 0, ++ti; else ++kb;
       const float g4_0 = g4n0, g4_1 = g4n1;
       const bool defer4 = WF == W_INT4 && p.group == 128;
-      if constexpr (is_w4(WF)) g4n0 = w4_scale(ti, kb, 0), g4n1 = w4_scale(ti, kb, 1);
+      if constexpr (is_w4(WF) && !is_a8(AF)) g4n0 = w4_scale(ti, kb, 0), g4n1 = w4_scale(ti, kb, 1);
       if (!warp_live) continue;
 
       float sw0 = 1.f, sw1 = 1.f;
       if (p.scale_kind >= S_BLOCK) {
-        sw0 = load_scale(p.scales, sc0 + kb_now, p.scale_dtype);
-        sw1 = load_scale(p.scales, sc1 + kb_now, p.scale_dtype);
+        sw0 = load_scale(p.scales, sc0 + kb_now * p.s_sg, p.scale_dtype);
+        sw1 = load_scale(p.scales, sc1 + kb_now * p.s_sg, p.scale_dtype);
       }
 
-      if constexpr (AF == A_E4M3) {
-        // raw e4m3 x e4m3: lane's 32 bytes of rows g, g + 8
+      if constexpr (is_a8(AF)) {
+        // 8-bit x 8-bit on the raw bytes (e4m3 x e4m3 -> f32, s8 x s8 -> s32, exact
+        // per 128-wide group): lane's 32 weights of rows g, g + 8 as bytes
         uint32_t wr[2][8];
 #pragma unroll
-        for (int r = 0; r < 2; ++r)
+        for (int r = 0; r < 2; ++r) {
+          if constexpr (WF == W_INT4) {
+            // 8 nibbles -> 8 signed bytes (nibble - 8), in element order
+            const uint4 x = *reinterpret_cast<const uint4*>(st + w_off[r][0]);
+            const uint32_t ws[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
-          for (int i = 0; i < 2; ++i) {
-            const uint4 x = *reinterpret_cast<const uint4*>(st + w_off[r][i]);
-            wr[r][4 * i] = x.x, wr[r][4 * i + 1] = x.y, wr[r][4 * i + 2] = x.z, wr[r][4 * i + 3] = x.w;
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t lo = ws[i] & 0x0F0F0F0Fu, hi = (ws[i] >> 4) & 0x0F0F0F0Fu;
+              wr[r][2 * i] = __vsub4(prmt(lo, hi, 0x5140), 0x08080808u);
+              wr[r][2 * i + 1] = __vsub4(prmt(lo, hi, 0x7362), 0x08080808u);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              const uint4 x = *reinterpret_cast<const uint4*>(st + w_off[r][i]);
+              wr[r][4 * i] = x.x, wr[r][4 * i + 1] = x.y, wr[r][4 * i + 2] = x.z, wr[r][4 * i + 3] = x.w;
+            }
+            if constexpr (WF == W_U8B128) {   // excess-128 bytes -> two's complement
+#pragma unroll
+              for (int i = 0; i < 8; ++i) wr[r][i] ^= 0x80808080u;
+            }
           }
+        }
         const float2* sap = reinterpret_cast<const float2*>(st + L::kWBytes + L::kABytes) + c;
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
@@ -415,10 +435,21 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs
             xr[4 * i] = x.x, xr[4 * i + 1] = x.y, xr[4 * i + 2] = x.z, xr[4 * i + 3] = x.w;
           }
           float part[4] = {0.f, 0.f, 0.f, 0.f};
+          if constexpr (AF == A_INT8) {
+            int ipart[4] = {0, 0, 0, 0};
 #pragma unroll
-          for (int s = 0; s < 4; ++s) {
-            const uint32_t a[4] = {wr[0][2 * s], wr[1][2 * s], wr[0][2 * s + 1], wr[1][2 * s + 1]};
-            mma_e4m3_16832(part, a, xr[2 * s], xr[2 * s + 1]);
+            for (int s = 0; s < 4; ++s) {
+              const uint32_t a[4] = {wr[0][2 * s], wr[1][2 * s], wr[0][2 * s + 1], wr[1][2 * s + 1]};
+              mma_s8s8_16832(ipart, a, xr[2 * s], xr[2 * s + 1]);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) part[i] = float(ipart[i]);
+          } else {
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+              const uint32_t a[4] = {wr[0][2 * s], wr[1][2 * s], wr[0][2 * s + 1], wr[1][2 * s + 1]};
+              mma_e4m3_16832(part, a, xr[2 * s], xr[2 * s + 1]);
+            }
           }
           const float2 sa = sap[4 * j];  // scales of tokens 8j + 2c, 8j + 2c + 1
           acc[j][0] += part[0] * (sw0 * sa.x);
@@ -562,19 +593,26 @@ static int moe_gemm_impl(
     int64_t s_stride_e, int64_t s_stride_n, int64_t sa_stride, int64_t sorted_len,
     int64_t expert_len, int64_t top_k, int64_t block_m, int weight_format, int act_format,
     int scale_kind, int scale_dtype, int gate_act, int c_is_f16, strix_stream_t stream,
-    const void* bias, int64_t bias_stride, int group) {
+    const void* bias, int64_t bias_stride, int group, int64_t s_stride_g = 1) {
   STRIX_CHECK(weight_format >= W_E4M3 && weight_format <= W_U8B128, "unknown weight format");
   const bool w4 = is_w4(weight_format);
-  STRIX_CHECK(act_format >= A_BF16 && act_format <= A_E4M3, "unknown activation format");
+  STRIX_CHECK(act_format >= A_BF16 && act_format <= A_INT8, "unknown activation format");
   STRIX_CHECK(gate_act >= ACT_NONE && gate_act <= ACT_GELU_TANH,
               "activation must be silu or gelu_tanh");
   STRIX_CHECK(scale_kind >= S_NONE && scale_kind <= S_GROUP && scale_dtype >= 0 && scale_dtype <= 2,
               "scales bf16, fp16 or fp32");
   STRIX_CHECK(experts > 0 && n > 0 && k > 0 && num_valid >= 0 && a_rows >= 0, "bad ranks");
   STRIX_CHECK(w4 ? k % 32 == 0 : k % kKB == 0, "K %% 128 (K %% 32 for 4-bit weights)");
-  STRIX_CHECK(!w4 || (act_format == A_BF16 && (group == 32 || group == 64 || group == 128) &&
-                      scales != nullptr && (weight_format != W_MXFP4 || group == 32)),
+  STRIX_CHECK(!w4 || act_format == A_INT8 ||
+                  (act_format == A_BF16 && (group == 32 || group == 64 || group == 128) &&
+                   scales != nullptr && (weight_format != W_MXFP4 || group == 32)),
               "4-bit weights take bf16 activations and scales per 32, 64 or 128 elements (32 for MXFP4)");
+  STRIX_CHECK(act_format != A_INT8 ||
+                  ((weight_format == W_INT4 || weight_format == W_U8B128 || weight_format == W_INT8) &&
+                   act_scales != nullptr && k % kKB == 0 &&
+                   (scale_kind == S_GROUP || scale_kind == S_CHANNEL)),
+              "int8 activations need int4 / int8 weights, activation scales, K %% 128 and scales "
+              "per channel or per (row, 128 group)");
   STRIX_CHECK(bias == nullptr || gate_act == ACT_NONE, "bias only on plain outputs");
   STRIX_CHECK(gate_act == ACT_NONE || (n % 16 == 0 && topk_weights == nullptr),
               "silu_mul needs even N and no topk weights");
@@ -594,7 +632,7 @@ static int moe_gemm_impl(
               "block scales must be fp32 [E, N/128, K/128]");
   STRIX_CHECK(!c_is_f16 || (gate_act != ACT_NONE && act_format == A_F16),
               "fp16 output only for the fused activation of the fp16 form");
-  const int wb = weight_format == W_BF16 ? 2 : 1, ab = act_format == A_E4M3 ? 1 : 2;
+  const int wb = weight_format == W_BF16 ? 2 : 1, ab = is_a8(act_format) ? 1 : 2;
   STRIX_CHECK((a_stride * ab) % 16 == 0 && (w_stride_n * wb) % 16 == 0 && (w_stride_e * wb) % 16 == 0 &&
                   reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0,
               "16-byte aligned rows required");
@@ -607,6 +645,7 @@ static int moe_gemm_impl(
   p.num_valid = num_valid;
   p.a_stride = a_stride, p.c_stride = c_stride, p.w_se = w_stride_e, p.w_sn = w_stride_n;
   p.s_se = s_stride_e, p.s_sn = s_stride_n, p.sa_stride = sa_stride;
+  p.s_sg = s_stride_g > 0 ? s_stride_g : 1;
   p.top_k = int(top_k), p.K = int(k), p.N = int(n), p.block_m = int(block_m);
   p.scale_kind = scale_kind, p.scale_dtype = scale_dtype, p.c_f16 = c_is_f16;
 
@@ -633,6 +672,8 @@ static int moe_gemm_impl(
   if (weight_format == W_E4M3 && act_format == A_F16) return launch_bm<W_E4M3, A_F16>(p, gate_act, grid, st);
   if (weight_format == W_INT8 && act_format == A_BF16) return launch_bm<W_INT8, A_BF16>(p, gate_act, grid, st);
   if (weight_format == W_U8B128 && act_format == A_BF16) return launch_bm<W_U8B128, A_BF16>(p, gate_act, grid, st);
+  if (weight_format == W_U8B128 && act_format == A_INT8) return launch_bm<W_U8B128, A_INT8>(p, gate_act, grid, st);
+  if (weight_format == W_INT4 && act_format == A_INT8) return launch_bm<W_INT4, A_INT8>(p, gate_act, grid, st);
   if (weight_format == W_BF16) return launch_bm<W_BF16, A_BF16>(p, gate_act, grid, st);
   if (weight_format == W_MXFP4) return launch_bm<W_MXFP4, A_BF16>(p, gate_act, grid, st);
   if (weight_format == W_INT4) return launch_bm<W_INT4, A_BF16>(p, gate_act, grid, st);
@@ -687,4 +728,21 @@ extern "C" int strix_dense_gemm_w8a16(void* c, const void* x, const void* w, con
                        x_stride, c_stride, 0, w_stride, 0, s_stride_n, 0, sorted_len, 0, 1, block_m,
                        weight_format, act_format, scale_kind, scale_dtype, ACT_NONE, 0, stream, bias,
                        bias_stride, 0);
+}
+
+extern "C" int strix_gemm_w8a8_group(
+    void* c, const void* qa, const float* sa, const void* w, const void* scales,
+    const int32_t* sorted_ids, const int32_t* expert_ids, const int32_t* num_post_padded,
+    const float* topk_weights, int64_t num_valid, int64_t a_rows, int64_t experts, int64_t n,
+    int64_t k, int64_t a_stride, int64_t c_stride, int64_t w_stride_e, int64_t w_stride_n,
+    int64_t s_stride_e, int64_t s_stride_n, int64_t s_stride_g, int64_t sa_stride,
+    int64_t sorted_len, int64_t expert_len, int64_t top_k, int64_t block_m, int weight_format,
+    int scale_kind, int scale_dtype, int gate_act, strix_stream_t stream) {
+  STRIX_CHECK(weight_format == W_INT4 || weight_format == W_U8B128,
+              "weight_format 4 (int4) or 5 (excess-128 bytes)");
+  return moe_gemm_impl(c, qa, w, scales, sa, sorted_ids, expert_ids, num_post_padded, topk_weights,
+                       num_valid, a_rows, experts, n, k, a_stride, c_stride, w_stride_e, w_stride_n,
+                       s_stride_e, s_stride_n, sa_stride, sorted_len, expert_len, top_k, block_m,
+                       weight_format, A_INT8, scale_kind, scale_dtype, gate_act, 0, stream, nullptr, 0,
+                       128, s_stride_g);
 }

@@ -243,6 +243,17 @@ KERNELS: list[Kernel] = [
     Kernel("fp8_wmma_gemm_raw", "fp8", "e4m3 weights (exact) x fp16 activations, scales on the sums",
            {"weight_bits": 8, "weight_dtype": "fp8_e4m3", "group_size": (0, 128),
             "rows": Range(lo=1), "dtype": "fp16"}, dict(_STREAM_SPEC)),
+    Kernel("moe_gemm_w4a8", "moe_gemm_w4a8",
+           "int4 experts x int8 activations (one fp32 scale per row and 128 group): s8 x s8 "
+           "MMAs, int32-exact per group, fp32 fold with the two scales",
+           {"silu_mul": (True, False), "dtype": "bf16", "activation_dtype": "int8",
+            "weight_dtype": "uint8", "weight_bits": 4, "quant": "wna16", "group_size": (128,),
+            "activation": _GATES}, dict(_STREAM_SPEC)),
+    Kernel("w8a8_wmma_gemm", "w8a16",
+           "excess-128 byte weights x activations quantised to int8 per (row, 128 group) inside "
+           "the op, int32-exact per group, fp32 group-scale fold. K % 128 == 0",
+           {"weight_bits": 8, "group_size": (0, 128), "rows": Range(lo=9), "dtype": "bf16"},
+           dict(_STREAM_SPEC)),
     # ---------------------------------------------------------- dense GEMMs
     Kernel("w8a8_int8_gemm", "w8a8",
            "dense W8A8 INT8 GEMM on tcgen05 kind::i8 (int32 sums in TMEM, exact): int8 "

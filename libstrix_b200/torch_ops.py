@@ -615,6 +615,86 @@ def fp8_wmma_gemm_raw(w, x, scales):
     return _fp8_dense(w, x, scales, None, _A_F16)
 
 
+def _gemm_a8(c, qa, sa, w, scales, routing, topk_weights, top_k, block_m, wfmt, gate,
+             s_sn, s_sg, scale_kind):
+    """Host side of strix_gemm_w8a8_group (int8 activations, per-128-group fold)."""
+    dense = routing is None
+    n = w.size(-2)
+    k = qa.size(1)
+    _check(qa.dtype == torch.int8 and qa.stride(1) == 1 and sa.dtype == torch.float32
+           and tuple(sa.shape) == (qa.size(0), k // 128) and sa.stride(1) == 1,
+           "qa int8 [rows, K], sa fp32 [rows, K / 128]")
+    _check(k % 128 == 0, "K must be a multiple of 128")
+    if dense:
+        sid = eid = npp = None
+        m = qa.size(0)
+        e, w_se, w_sn, s_se = 1, 0, w.stride(0), 0
+        sorted_len, expert_len, num_valid = (m + block_m - 1) // block_m * block_m, 0, m
+    else:
+        sid, eid, npp = routing
+        _check(sid.dtype == torch.int32 and eid.dtype == torch.int32 and npp.dtype == torch.int32,
+               "routing tensors must be int32")
+        _check(eid.numel() * block_m >= sid.numel(), f"expert_ids too short for block_m {block_m}")
+        e, w_se, w_sn, s_se = w.size(0), w.stride(0), w.stride(1), scales.stride(0)
+        sorted_len, expert_len, num_valid = sid.numel(), eid.numel(), c.size(0)
+    with torch.cuda.device(c.device):
+        _lib.call("strix_gemm_w8a8_group", c.data_ptr(), qa.data_ptr(), sa.data_ptr(), w.data_ptr(),
+                  scales.data_ptr(), _ptr(sid), _ptr(eid), _ptr(npp), _ptr(topk_weights), num_valid,
+                  qa.size(0), e, n, k, qa.stride(0), c.stride(0), w_se, w_sn, s_se, s_sn, s_sg,
+                  sa.stride(0), sorted_len, expert_len, top_k, block_m, wfmt, scale_kind,
+                  _SCALE_DTYPES[scales.dtype], gate, _stream())
+
+
+@_define("moe_gemm_w4a8(Tensor(a!) c, Tensor qa, Tensor sa, Tensor b, Tensor scales, "
+         "Tensor sorted_ids, Tensor expert_ids, Tensor num_post_padded, Tensor? topk_weights, "
+         "int top_k, int block_m, int block_n, bool silu_mul=False, str activation='silu') -> ()")
+def moe_gemm_w4a8(c, qa, sa, b, scales, sorted_ids, expert_ids, num_post_padded, topk_weights,
+                  top_k, block_m, block_n, silu_mul=False, activation="silu"):
+    _check(activation in _ACTS, f"activation must be silu or gelu_tanh, got {activation}")
+    _check(b.dtype == torch.uint8 and b.dim() == 3 and b.size(2) * 2 == qa.size(1)
+           and b.stride(2) == 1 and c.dtype == torch.bfloat16, "b uint8 [E, N, K / 2], c bf16")
+    e, n, _ = b.shape
+    _check(scales.dtype in (torch.bfloat16, torch.float16)
+           and tuple(scales.shape) == (e, n, qa.size(1) // 128) and scales.stride(2) == 1,
+           "scales must be bf16 or fp16 [E, N, K / 128]")
+    _check(c.size(1) == (n // 2 if silu_mul else n), "shape mismatch")
+    _check(not silu_mul or topk_weights is None, "silu_mul needs even N and no topk weights")
+    _gemm_a8(c, qa, sa, b, scales, (sorted_ids, expert_ids, num_post_padded), topk_weights, top_k,
+             block_m, _W_INT4, _ACTS[activation] if silu_mul else 0, scales.stride(1), 1, _S_GROUP)
+
+
+@_define("w8a8_wmma_gemm(Tensor in_w8, Tensor in_act, Tensor in_scale) -> Tensor",
+         fake=_dense_fake(1, 0))
+def w8a8_wmma_gemm(in_w8, in_act, in_scale):
+    """Excess-128 byte weights [N, K] x bf16 activations quantised to int8 per (row,
+    128 group) inside the op; int32-exact sums per group, fp32 fold. in_scale fp32
+    [N], [K/128, N] (group-major) or [N, K/128]."""
+    n, k = in_w8.shape
+    m = in_act.size(0)
+    _check(in_w8.dtype == torch.uint8 and in_w8.stride(1) == 1, "in_w8 must be uint8 [N, K]")
+    _check(in_act.dtype == torch.bfloat16 and in_act.dim() == 2 and in_act.size(1) == k,
+           "in_act must be bf16 [M, K]")
+    _check(k % 128 == 0, "K must be a multiple of 128")
+    _check(in_scale.dtype == torch.float32, "in_scale must be fp32")
+    g = k // 128
+    if in_scale.dim() == 1 or in_scale.numel() == n:
+        _check(in_scale.numel() == n, "in_scale must be [N], [K/128, N] or [N, K/128]")
+        kind, s_sn, s_sg, sc = _S_CHANNEL, 0, 1, in_scale.reshape(n)
+    elif tuple(in_scale.shape) == (g, n):
+        kind, s_sn, s_sg, sc = _S_GROUP, in_scale.stride(1), in_scale.stride(0), in_scale
+    else:
+        _check(tuple(in_scale.shape) == (n, g), "in_scale must be [N], [K/128, N] or [N, K/128]")
+        kind, s_sn, s_sg, sc = _S_GROUP, in_scale.stride(0), in_scale.stride(1), in_scale
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=in_act.device)
+    if m == 0:
+        return out
+    qa = torch.empty(m, k, dtype=torch.int8, device=in_act.device)
+    sa = torch.empty(m, g, dtype=torch.float32, device=in_act.device)
+    moe_act_quant_i8(in_act, qa, sa)
+    _gemm_a8(out, qa, sa, in_w8, sc, None, None, 1, _dense_block_m(m), _W_U8B128, 0, s_sn, s_sg, kind)
+    return out
+
+
 # ------------------------------------------------------------ dense quantized GEMMs
 
 def _w8a8_int8_fake(a_q, a_scale, w, w_scale, acc_out=None):

@@ -249,3 +249,64 @@ def test_fp8_dequant_and_gemms(scheme, n, k):
         close_to_peak(out, ref, 1e-2)
         out = ops.fp8_wmma_gemm_raw(w.to(DEV), x.half().to(DEV), scales.to(DEV))
         close_to_peak(out, x.half().float() @ ref_w.t(), 1e-2)
+
+
+# ------------------------------------------------------------ int8 activations
+
+@pytest.mark.parametrize("scale_dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("tokens", [1, 37, 130])
+@pytest.mark.parametrize("block_m", [16, 64, 128])
+@pytest.mark.parametrize("gemm,activation", [("w13", "silu"), ("w13", "gelu_tanh"), ("w2", "silu")])
+def test_moe_gemm_w4a8(tokens, block_m, gemm, activation, scale_dtype):
+    """The oracle consumes the dequantised int8 activations and the exact weights
+    (tests/test_moe_w4a8.py:78-85)."""
+    n, k = (1280, 2560) if gemm == "w13" else (2560, 640)
+    g = torch.Generator().manual_seed(0)
+    q4 = torch.randint(0, 16, (E, n, k), generator=g, dtype=torch.uint8)
+    w_u8 = G.int4_pack(q4)
+    scales = (torch.rand(E, n, k // 128, generator=g) * 0.02 + 0.001).to(scale_dtype)
+    b = (q4.float() - 8) * scales.float().repeat_interleave(128, dim=-1)
+    a = torch.randn(tokens if gemm == "w13" else tokens * TOP_K, k, generator=g).bfloat16()
+    qa, sa = M.act_quant_i8(a)
+    a_deq = qa.float() * sa.repeat_interleave(128, dim=-1)
+    ids = routing(tokens)
+    if gemm == "w13":
+        a_topk, weights, out_cols = TOP_K, None, n // 2
+    else:
+        a_topk, weights, out_cols = 1, torch.rand(tokens, TOP_K, generator=g), n
+    sorted_ids, expert_ids, num_post = M.align(ids, block_m, E)
+    c = torch.full((tokens * TOP_K, out_cols), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.moe_gemm_w4a8(c, qa.to(DEV), sa.to(DEV), w_u8.to(DEV), scales.to(DEV), sorted_ids.to(DEV),
+                      expert_ids.to(DEV), num_post.to(DEV),
+                      None if weights is None else weights.flatten().to(DEV), a_topk, block_m, 64,
+                      gemm == "w13", activation)
+    ref = M.grouped_reference(a_deq, b, ids, a_topk, weights)
+    if gemm == "w13":
+        ref = M.gate_mul(ref, activation)
+    torch.testing.assert_close(c.float().cpu(), ref, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("n,k", [(2048, 2048), (1024, 2048), (256, 4096)])
+@pytest.mark.parametrize("m", [6, 64, 300])
+@pytest.mark.parametrize("scale_form", ["channel", "group_major", "row_major"])
+def test_w8a8_wmma_gemm_reference_schema(n, k, m, scale_form):
+    """tests/test_w8a8_int8.py:84-104 (per-channel) and tests/test_w8a16.py:34-42
+    (per-group scales, group-major)."""
+    g = torch.Generator().manual_seed(0)
+    w_i8 = torch.randint(-127, 128, (n, k), generator=g, dtype=torch.int8)
+    w_u8 = (w_i8.to(torch.int16) + 128).to(torch.uint8)
+    x = torch.randn(m, k, generator=g).bfloat16()
+    if scale_form == "channel":
+        s = torch.rand(n, generator=g) * 0.01 + 1e-4
+        full, arg = s.reshape(n, 1), s
+    else:
+        s = torch.rand(n, k // 128, generator=g) * 0.01 + 1e-4
+        full = s.repeat_interleave(128, 1)
+        arg = s.t().contiguous() if scale_form == "group_major" else s
+    out = ops.w8a8_wmma_gemm(w_u8.to(DEV), x.to(DEV), arg.to(DEV))
+    # the op's own arithmetic, exactly: quantise, int sums per group, fp32 fold
+    q, sg = G.act_quant_group_i8(x)
+    exact = (q.float() * sg.repeat_interleave(128, 1)) @ (w_i8.float() * full).t()
+    close_to_peak(out, exact, 1e-2)
+    # and the reference's looser statement against unquantised activations
+    close_to_peak(out, x.float() @ (w_i8.float() * full).t(), 6e-2)
