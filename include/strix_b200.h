@@ -189,6 +189,36 @@ int strix_w8a8_int8_gemm(void* out, int32_t* acc_out, const void* a_q, const flo
                          int64_t a_stride, int64_t w_stride, int64_t out_stride,
                          strix_stream_t stream);
 
+/* ------------------------------------------------------------------------
+ * Prefill attention: causal paged flash attention over ragged sequences.
+ * Replaces strix::attn_prefill_bf16 (csrc/attn/attn_prefill_bf16.hip:508-662;
+ * schema csrc/torch_ops.cpp:240-244; wrapper python/strix/__init__.py:214-268).
+ *   q, out        bf16 [total_q, hq, head_dim]; the queries of sequence n are
+ *                 rows cu_seqlens_q[n] .. cu_seqlens_q[n + 1] and hold the LAST
+ *                 q_len of its seq_lens[n] positions.
+ *   key_cache, value_cache, k_scale, v_scale, block_table, sinks, window_left:
+ *                 as strix_attn_decode_bf16 (int8 caches with fp32 scales per
+ *                 key and head, or bf16 caches).
+ *   num_splits    1..64, accepted for the reference's signature: the result
+ *                 does not depend on it and this kernel always runs one pass.
+ *                 sinks need num_splits == 1 (the reference's rule and message).
+ * The reference's tile_offsets / max_tiles arguments are not needed: the grid is
+ * sized from total_q and nseq. Built: head_dim 64 and 128, any hq / hkv ratio.
+ * ---------------------------------------------------------------------- */
+int strix_attn_prefill_bf16(void* out, const void* q, const void* key_cache,
+                            const void* value_cache, const float* k_scale, const float* v_scale,
+                            const int32_t* cu_seqlens_q, const int32_t* seq_lens,
+                            const int32_t* block_table, const float* sinks, int64_t total_q,
+                            int64_t nseq, int64_t hq, int64_t hkv, int64_t head_dim,
+                            int64_t block_size, int64_t bt_stride, int64_t q_stride_t,
+                            int64_t q_stride_h, int64_t out_stride_t, int64_t out_stride_h,
+                            int64_t k_stride_b, int64_t k_stride_s, int64_t k_stride_h,
+                            int64_t v_stride_b, int64_t v_stride_s, int64_t v_stride_h,
+                            int64_t ks_stride_b, int64_t ks_stride_s, int64_t ks_stride_h,
+                            int64_t vs_stride_b, int64_t vs_stride_s, int64_t vs_stride_h,
+                            double scale, int64_t num_splits, int64_t window_left, int kv_int8,
+                            strix_stream_t stream);
+
 /* Grouped or dense GEMM with 4-bit weights and bf16 activations, on the
  * weight-streaming kernel. Replaces moe_gemm_w4a16 (csrc/moe/moe_gemm_w4a16.hip:374),
  * w4a16_wmma_gemm, mxfp4_wmma_gemm / mxfp4_gemv (csrc/gemm/mxfp4_wmma_gemm.hip:355-372,

@@ -62,7 +62,40 @@ def attn_decode(
     return out
 
 
+def attn_prefill(
+    out: torch.Tensor,
+    q: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    cu_seqlens_q: torch.Tensor,
+    seq_lens: torch.Tensor,
+    block_table: torch.Tensor,
+    scale: float,
+    num_splits: int = 1,
+    window_left: int = -1,
+    k_scale: torch.Tensor | None = None,
+    v_scale: torch.Tensor | None = None,
+    sinks: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """Causal paged attention for prefill (no host sync); same arguments as the
+    reference's strix.attn_prefill (python/strix/__init__.py:214-268).
+
+    q, out: [T, Hq, D] bf16, D = 64 or 128; caches [blocks, block_size, Hkv, D]
+    views, bf16 or int8 with k_scale / v_scale fp32 [blocks, block_size, Hkv];
+    the queries of sequence n are the last q_len of its seq_lens[n] positions.
+    window_left >= 0: the query at position p sees keys p - window_left .. p.
+    sinks: optional fp32 [Hq]; num_splits must be 1 then. num_splits is a hint
+    the kernel does not need."""
+    cu = cu_seqlens_q.to(torch.int32)
+    torch.ops.strix.attn_prefill_bf16(
+        out, q, key_cache, value_cache, k_scale, v_scale, cu, seq_lens.to(torch.int32),
+        block_table.to(torch.int32), cu, 0, scale, num_splits, window_left, sinks,
+    )
+    return out
+
+
 __all__ = [
+    "attn_prefill",
     "Range",
     "StrixError",
     "attn_decode",

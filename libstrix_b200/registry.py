@@ -279,6 +279,16 @@ KERNELS: list[Kernel] = [
     _decode_row(256, 8, "head 256 GQA 8, four warps per CTA (255 registers)"),
     _decode_row(256, 6, "head 256 GQA 6 (two MMA columns idle)"),
     _decode_row(256, 2, "head 256 GQA 2 (sliding layers)"),
+    *[Kernel(
+        "attn_prefill_bf16", "attn_prefill",
+        "causal paged flash attention over ragged sequences: 64 queries x one head per CTA, "
+        "64-key tiles double-buffered with cp.async, int8 caches widened once per tile to fp16 "
+        "(K scale on the score, V scale on P), mma.sync m16n8k16 through ldmatrix",
+        {"head_dim": hd, "gqa": Range(1, 64), "dtype": "bf16", "kv_dtype": ("bf16", "int8"),
+         "split_kv": (True, False), "window": (True, False), "causal": True,
+         "sinks": (True, False)},
+        {"tile": "64 queries x 64 keys", "mma": "m16n8k16 f16 (int8 KV) / bf16", "bound": "tensor"},
+    ) for hd in (128, 64)],
 ]
 
 _POINT_TYPES = (int, bool, str)

@@ -117,6 +117,61 @@ def attn_decode_bf16(
         )
 
 
+@_define(
+    "attn_prefill_bf16(Tensor(a!) out, Tensor q, Tensor key_cache, "
+    "Tensor value_cache, Tensor? k_scale, Tensor? v_scale, "
+    "Tensor cu_seqlens_q, Tensor seq_lens, "
+    "Tensor block_table, Tensor tile_offsets, int max_tiles, float scale, "
+    "int num_splits, int window_left=-1, Tensor? sinks=None) -> ()"
+)
+def attn_prefill_bf16(out, q, key_cache, value_cache, k_scale, v_scale, cu_seqlens_q, seq_lens,
+                      block_table, tile_offsets, max_tiles, scale, num_splits, window_left=-1,
+                      sinks=None):
+    """Host side of strix_attn_prefill_bf16; checks follow
+    csrc/attn/attn_prefill_bf16.hip:516-580 of the reference. tile_offsets and
+    max_tiles (the reference's 16-query tiling) are accepted and not used."""
+    _check(q.dim() == 3 and key_cache.dim() == 4 and value_cache.dim() == 4,
+           "q [T, H, D], caches [blocks, block_size, Hkv, D]")
+    d = q.size(-1)
+    _check(q.dtype == torch.bfloat16 and q.stride(-1) == 1,
+           "q must be bf16 with a contiguous head_dim")
+    q8 = key_cache.dtype != torch.bfloat16
+    _check(key_cache.dtype == (torch.int8 if q8 else torch.bfloat16)
+           and value_cache.dtype == key_cache.dtype, "caches must both be bf16 or both int8")
+    for t in (key_cache, value_cache):
+        _check(t.size(-1) >= d and t.stride(-1) == 1, "cache head_dim must be at least q's, contiguous")
+    if q8:
+        _check(k_scale is not None and v_scale is not None, "int8 KV needs k_scale and v_scale")
+        for t in (k_scale, v_scale):
+            _check(t.dtype == torch.float32 and t.dim() == 3
+                   and tuple(t.shape) == tuple(key_cache.shape[:3]),
+                   "scales must be fp32 [blocks, block_size, Hkv]")
+    _check(out.dtype == torch.bfloat16 and out.shape == q.shape and out.stride(-1) == 1,
+           "out must match q")
+    _check(cu_seqlens_q.dtype == torch.int32 and seq_lens.dtype == torch.int32
+           and block_table.dtype == torch.int32 and block_table.stride(1) == 1
+           and cu_seqlens_q.is_contiguous() and seq_lens.is_contiguous()
+           and seq_lens.numel() >= cu_seqlens_q.numel() - 1, "int32 metadata")
+    if sinks is not None:
+        _check(num_splits == 1, "sinks need num_splits == 1")
+        _check(sinks.dtype == torch.float32 and sinks.dim() == 1 and sinks.size(0) == q.size(1)
+               and sinks.is_contiguous(), "sinks must be contiguous fp32 [Hq]")
+    ks = k_scale if q8 else None
+    vs = v_scale if q8 else None
+    with torch.cuda.device(q.device):
+        _lib.call(
+            "strix_attn_prefill_bf16",
+            out.data_ptr(), q.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(), _ptr(ks),
+            _ptr(vs), cu_seqlens_q.data_ptr(), seq_lens.data_ptr(), block_table.data_ptr(),
+            _ptr(sinks), q.size(0), cu_seqlens_q.numel() - 1, q.size(1), key_cache.size(2), d,
+            key_cache.size(1), block_table.stride(0), q.stride(0), q.stride(1), out.stride(0),
+            out.stride(1), key_cache.stride(0), key_cache.stride(1), key_cache.stride(2),
+            value_cache.stride(0), value_cache.stride(1), value_cache.stride(2),
+            *(ks.stride() if q8 else (0, 0, 0)), *(vs.stride() if q8 else (0, 0, 0)),
+            float(scale), num_splits, window_left, int(q8), _stream(),
+        )
+
+
 # ----------------------------------------------------------------------- MoE
 
 _W_E4M3, _W_INT8, _W_BF16 = 0, 1, 2
