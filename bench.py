@@ -183,10 +183,11 @@ def main() -> None:
     ap.add_argument("--ctx-hi", type=int, default=65536)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-moe", action="store_true", help="skip the MoE FP8 layer runs")
-    ap.add_argument("--only", choices=["moe", "gemm"], default=None,
+    ap.add_argument("--only", choices=["moe", "gemm", "prefill"], default=None,
                     help="run one secondary section alone (for profiling) and print its JSON")
     ap.add_argument("--moe-tokens", type=int, nargs="*", default=[256, 4096])
     ap.add_argument("--gemm-m", type=int, nargs="*", default=[1, 16, 4096])
+    ap.add_argument("--prefill-tokens", type=int, nargs="*", default=[2048, 65536])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -211,7 +212,8 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=dev)
     if args.only is not None:
         if rank == 0:
-            section = bench_moe_fp8 if args.only == "moe" else bench_gemm_w8a8
+            section = {"moe": bench_moe_fp8, "gemm": bench_gemm_w8a8,
+                       "prefill": bench_attn_prefill}[args.only]
             print(json.dumps({args.only: section(args, dev, not args.no_cpu_baseline)}), flush=True)
         if world > 1:
             dist.destroy_process_group()
@@ -341,6 +343,8 @@ def main() -> None:
             line["gpu_launches"] += line["moe_fp8"]["gpu_launches"]
             line["gemm_w8a8_int8"] = bench_gemm_w8a8(args, dev, not args.no_cpu_baseline)
             line["gpu_launches"] += line["gemm_w8a8_int8"]["gpu_launches"]
+            line["attn_prefill"] = bench_attn_prefill(args, dev, not args.no_cpu_baseline)
+            line["gpu_launches"] += line["attn_prefill"]["gpu_launches"]
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -463,6 +467,74 @@ def bench_gemm_w8a8(args, dev, with_cpu: bool) -> dict:
             run["parity"] = {"bit_exact_bf16": bool(torch.equal(res[:, rows].cpu().view(torch.int16),
                                                                 ref.view(torch.int16)))}
         out["runs"].append(run)
+    return out
+
+
+def bench_attn_prefill(args, dev, with_cpu: bool) -> dict:
+    """Causal GQA prefill of config 4: one sequence of 2048 and of 65536 tokens, 40
+    query / 8 KV heads, head 128, int8 paged cache (block 16, shuffled table)
+    written from bf16 N(0,1) values with per-token-per-head scales. Tensor bound:
+    FLOPs = 4 x Hq x D x T (T + 1) / 2 (QK^T and PV over the causal half) against
+    the measured bf16 peak. Q + out (1.3 GB at 65536 tokens) exceed the L2."""
+    import libstrix_b200 as strix
+    from oracle import attention as A
+
+    f = ROOT / "MEASURED_PEAKS.json"
+    bf16 = float(json.loads(f.read_text())["bf16_tflops"]) if f.exists() else 1590.0
+    hq, hkv, hd, bs = 40, 8, 128, 16
+    out = {"config": "causal GQA prefill, Hq=40 Hkv=8 D=128 block=16, int8 KV", "gpu_launches": 0,
+           "runs": []}
+    g = torch.Generator(device=dev).manual_seed(0)
+    for t in args.prefill_tokens:
+        nblk = (t + bs - 1) // bs
+        kv = torch.randn(nblk, bs, hkv, 2 * hd, generator=g, device=dev, dtype=torch.bfloat16)
+        kq, ks = A.quantize_kv(kv[..., :hd])
+        vq, vs = A.quantize_kv(kv[..., hd:])
+        del kv
+        table = torch.randperm(nblk, generator=g, device=dev).int().view(1, nblk)
+        q = torch.randn(t, hq, hd, generator=g, device=dev, dtype=torch.bfloat16)
+        o = torch.empty_like(q)
+        cu = torch.tensor([0, t], dtype=torch.int32, device=dev)
+        sl = torch.tensor([t], dtype=torch.int32, device=dev)
+        scale = hd ** -0.5
+
+        def step():
+            strix.attn_prefill(o, q, kq, vq, cu, sl, table, scale, 1, -1, ks, vs)
+
+        steps = max(2, min(args.steps, 5 if t > 8192 else args.steps))
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        flops = 4.0 * hq * hd * t * (t + 1) / 2
+        tf = flops / (ms * 1e-3) / 1e12
+        run = {"tokens": t, "ms": ms, "tflops": tf, "flops": flops,
+               "roofline": {"bound": "tensor", "achieved": tf, "peak": bf16, "unit": "TFLOP/s",
+                            "frac": tf / bf16, "peak_kind": "measured bf16 (cuBLAS burst)"}}
+        out["gpu_launches"] += steps
+        if with_cpu and t <= 2048:
+            n_q = 256   # the last 256 queries against the whole context
+            t0 = time.perf_counter()
+            kx, vx = (kq.float() * ks[..., None]).cpu(), (vq.float() * vs[..., None]).cpu()
+            ref = A.attention_reference(q[-n_q:].cpu(), kx, vx, torch.tensor([0, n_q], dtype=torch.int32),
+                                        sl.cpu(), table.cpu(), scale)
+            sec = time.perf_counter() - t0
+            diff = (o[-n_q:].float().cpu() - ref).abs()
+            rms = ref.pow(2).mean().sqrt().item()
+            run["cpu_baseline"] = {"value": 4.0 * hq * hd * n_q * (t - n_q / 2) / sec / 1e12,
+                                   "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                                   "seconds": sec, "sample": f"last {n_q} of {t} queries"}
+            run["parity"] = {"max_abs_err": diff.max().item(), "ref_rms": rms,
+                             "ok": bool((diff <= 2e-2 * rms + ref.abs() * 2.0 ** -8).all())}
+        out["runs"].append(run)
+        del q, o, kq, vq, ks, vs
+        torch.cuda.empty_cache()
     return out
 
 

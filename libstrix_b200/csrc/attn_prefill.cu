@@ -87,7 +87,10 @@ __global__ void __launch_bounds__(kPfThreads) attn_prefill_kernel(const PrefillA
     q_begin = p.cu[n];
     q_len = p.cu[n + 1] - q_begin;
     const int tiles = (q_len + kBM - 1) / kBM;
-    if (tile < tiles) break;
+    if (tile < tiles) {
+      tile = tiles - 1 - tile;   // the last tiles see the most keys: start them first
+      break;
+    }
     tile -= tiles;
   }
   const int kv_len = p.seq_lens[n];
@@ -210,22 +213,23 @@ __global__ void __launch_bounds__(kPfThreads) attn_prefill_kernel(const PrefillA
     const int k0 = k_begin + t * kBN;
 
     // ---- S = Q K^T: 8 key tiles of 8 x D / 16 steps
+    // (d steps outermost: consecutive MMAs then feed eight independent accumulators)
     float s[kBN / 8][4];
 #pragma unroll
-    for (int j = 0; j < kBN / 8; ++j) {
-      s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+    for (int j = 0; j < kBN / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
 #pragma unroll
-      for (int sp = 0; sp < D / 32; ++sp) {
-        uint32_t b[4];
-        ldmatrix_x4(b, kt + tile_off<D>(8 * j + (lane & 7), 4 * sp + (lane >> 3)));
-        if constexpr (Q8) {
-          mma_f16_16816(s[j], qf[2 * sp], b[0], b[1]);
-          mma_f16_16816(s[j], qf[2 * sp + 1], b[2], b[3]);
-        } else {
-          mma_bf16_16816(s[j], qf[2 * sp], b[0], b[1]);
-          mma_bf16_16816(s[j], qf[2 * sp + 1], b[2], b[3]);
+    for (int sp = 0; sp < D / 32; ++sp) {
+      uint32_t b[kBN / 8][4];
+#pragma unroll
+      for (int j = 0; j < kBN / 8; ++j)
+        ldmatrix_x4(b[j], kt + tile_off<D>(8 * j + (lane & 7), 4 * sp + (lane >> 3)));
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int j = 0; j < kBN / 8; ++j) {
+          if constexpr (Q8) mma_f16_16816(s[j], qf[2 * sp + h], b[j][2 * h], b[j][2 * h + 1]);
+          else mma_bf16_16816(s[j], qf[2 * sp + h], b[j][2 * h], b[j][2 * h + 1]);
         }
-      }
     }
 
     // ---- scale, mask, online softmax (rows g and g + 8; keys 8j + 2c, + 1)
