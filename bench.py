@@ -183,7 +183,7 @@ def main() -> None:
     ap.add_argument("--ctx-hi", type=int, default=65536)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-moe", action="store_true", help="skip the MoE FP8 layer runs")
-    ap.add_argument("--only", choices=["moe", "gemm", "prefill"], default=None,
+    ap.add_argument("--only", choices=["moe", "gemm", "prefill", "ep"], default=None,
                     help="run one secondary section alone (for profiling) and print its JSON")
     ap.add_argument("--moe-tokens", type=int, nargs="*", default=[256, 4096])
     ap.add_argument("--gemm-m", type=int, nargs="*", default=[1, 16, 4096])
@@ -210,6 +210,13 @@ def main() -> None:
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    if args.only == "ep":
+        res = bench_ep_moe(args, dev, rank, world)
+        if rank == 0:
+            print(json.dumps({"ep": res}), flush=True)
+        if dist.is_initialized():
+            dist.destroy_process_group()
+        return
     if args.only is not None:
         if rank == 0:
             section = {"moe": bench_moe_fp8, "gemm": bench_gemm_w8a8,
@@ -345,8 +352,14 @@ def main() -> None:
             line["gpu_launches"] += line["gemm_w8a8_int8"]["gpu_launches"]
             line["attn_prefill"] = bench_attn_prefill(args, dev, not args.no_cpu_baseline)
             line["gpu_launches"] += line["attn_prefill"]["gpu_launches"]
+    # the expert-parallel MXFP4 layer runs on every rank (it is a collective)
+    ep_res = None if args.no_moe else bench_ep_moe(args, dev, rank, world)
+    if rank == 0:
+        if ep_res is not None:
+            line["ep_moe_mxfp4"] = ep_res
+            line["gpu_launches"] += ep_res["gpu_launches"]
         print(json.dumps(line), flush=True)
-    if world > 1:
+    if dist.is_initialized():
         dist.destroy_process_group()
 
 
@@ -468,6 +481,61 @@ def bench_gemm_w8a8(args, dev, with_cpu: bool) -> dict:
                                                                 ref.view(torch.int16)))}
         out["runs"].append(run)
     return out
+
+
+def bench_ep_moe(args, dev, rank: int, world: int) -> dict:
+    """Config 5: MXFP4 MoE layer, gpt-oss-120B-like (hidden 2880, 128 experts, top-4,
+    intermediate 2880), 8192 tokens in total, expert-parallel over the ranks:
+    each rank holds 8192 / N tokens and 128 / N experts; tokens move by NCCL
+    all-to-all (dispatch and combine). Router logits N(0,1) plus a Zipf(1.1)
+    per-expert bias. Strong scaling: the total work is fixed. Time = max over
+    ranks of the CUDA-event time; TFLOP/s counts 2 x slots x (2I x H + H x I)."""
+    import torch.distributed as dist
+
+    from libstrix_b200 import ep
+
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29517")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    tokens_total, hid, inter, experts, top_k = 8192, 2880, 2880, 128, 4
+    t_local, e_local = tokens_total // world, experts // world
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    x = torch.randn(t_local, hid, generator=g, device=dev, dtype=torch.bfloat16)
+    zipf = torch.log(1.0 / torch.arange(1, experts + 1, device=dev, dtype=torch.float32) ** 1.1)
+    zipf = zipf[torch.randperm(experts, generator=torch.Generator(device=dev).manual_seed(7), device=dev)]
+    logits = torch.randn(t_local, experts, generator=g, device=dev) + zipf
+    w13 = torch.randint(0, 256, (e_local, 2 * inter, hid // 2), generator=g, device=dev, dtype=torch.uint8)
+    s13 = torch.randint(118, 124, (e_local, 2 * inter, hid // 32), generator=g, device=dev, dtype=torch.uint8)
+    w2 = torch.randint(0, 256, (e_local, hid, inter // 2), generator=g, device=dev, dtype=torch.uint8)
+    s2 = torch.randint(118, 124, (e_local, hid, inter // 32), generator=g, device=dev, dtype=torch.uint8)
+
+    def step():
+        return ep.ep_moe_mxfp4(x, logits, w13, s13, w2, s2, top_k)
+
+    steps = max(2, min(args.steps, 10))
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        out = step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ok = bool(torch.isfinite(out.float()).all())
+    flops = 2.0 * tokens_total * top_k * (2 * inter * hid + hid * inter)
+    ms = ms.item()
+    return {"config": "MXFP4 MoE, H=2880 E=128 top-4 I=2880, 8192 tokens, EP over ranks, Zipf(1.1) bias",
+            "n_gpus": world, "scaling": "strong", "ms_per_layer": ms,
+            "tflops": flops / (ms * 1e-3) / 1e12, "tokens_per_s": tokens_total / (ms * 1e-3),
+            "weight_bytes_per_rank": int(w13.numel() + s13.numel() + w2.numel() + s2.numel()),
+            "finite": ok, "gpu_launches": 5 * steps,
+            "exchange": "NCCL all_to_all_single x4 per layer (counts, rows, ids+weights, results)"}
 
 
 def bench_attn_prefill(args, dev, with_cpu: bool) -> dict:

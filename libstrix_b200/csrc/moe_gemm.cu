@@ -123,8 +123,39 @@ __device__ __forceinline__ void widen(uint32_t w, float scale, uint32_t& lo, uin
 // tests/test_mxfp4.py:29-47) -> four registers of bf16 pairs, each value times
 // `scale` and rounded to bf16 (exact for e2m1 x 2^e). MXFP4: sign, 2-bit
 // exponent, 1-bit mantissa (0, .5, 1, 1.5, 2, 3, 4, 6); INT4: nibble - 8.
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
+// MXFP4 by table: the low three bits of a nibble index an 8-entry table of bf16
+// bit patterns (0, .5, 1, 1.5, 2, 3, 4, 6), looked up four nibbles at a time with
+// byte permutes (high bytes and low bytes apart), the sign bit moves to bit 15,
+// and one bf16x2 multiply applies the power-of-two scale (exact; 2^(s - 127) has
+// the bf16 pattern s << 7, and s = 0 is the zero block).
+__device__ __forceinline__ void widen_mxfp4(uint32_t w, uint32_t scale2, uint32_t* out) {
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t x = h == 0 ? w : w >> 16;          // nibbles 4h .. 4h + 3 in the low 16 bits
+    const uint32_t sel = x & 0x7777u;
+    const uint32_t hi = prmt(0x3F3F3F00u, 0x40404040u, sel);
+    const uint32_t lo = prmt(0xC0800000u, 0xC0804000u, sel);
+    const uint32_t p01 = prmt(lo, hi, 0x5140) | ((x & 0x8u) << 12) | ((x & 0x80u) << 24);
+    const uint32_t p23 = prmt(lo, hi, 0x7362) | ((x & 0x800u) << 4) | ((x & 0x8000u) << 16);
+    out[2 * h] = mul_bf16x2(p01, scale2);
+    out[2 * h + 1] = mul_bf16x2(p23, scale2);
+  }
+}
+
 template <int WF>
 __device__ __forceinline__ void widen4(uint32_t w, float scale, uint32_t* out) {
+  if constexpr (WF == W_MXFP4) {
+    // `scale` is 2^(s - 127) (or 0): its upper 16 bits are the bf16 pattern
+    const uint32_t sb = __float_as_uint(scale) >> 16;
+    widen_mxfp4(w, sb | (sb << 16), out);
+    return;
+  }
   float v[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {

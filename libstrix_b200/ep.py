@@ -1,0 +1,125 @@
+"""Expert-parallel MoE: token dispatch -> local experts -> combine.
+
+Every rank holds `experts_per_rank` consecutive experts and its own tokens. A
+routed slot (token, k) travels to the rank that owns its expert, is computed
+there with the grouped GEMMs of this library, and its result row travels back;
+the source rank then sums a token's top-k rows. The exchange is two
+`all_to_all_single` calls over the process group (NCCL over NVLink on GPUs,
+gloo in the CPU tests): activation rows one way, result rows the other, plus one
+small call for (local expert id, routing weight) pairs and one for the counts.
+
+The reference has no expert parallelism (its experts refuse an `expert_map`,
+python/strix_vllm/moe.py:193-210); this is the path the 8-GPU configuration
+needs. The split sizes of an uneven all-to-all live on the host, so a layer call
+synchronises once (the counts); everything else stays on the stream.
+"""
+
+from __future__ import annotations
+
+from typing import Callable
+
+import torch
+import torch.distributed as dist
+
+
+def dispatch_plan(topk_ids: torch.Tensor, experts_per_rank: int, world: int):
+    """(order, send_counts): slots sorted by destination rank (stable, so a
+    rank's rows keep slot order) and the number of slots per destination."""
+    dest = (topk_ids.reshape(-1) // experts_per_rank).to(torch.int64)
+    order = torch.sort(dest, stable=True).indices
+    send_counts = torch.bincount(dest, minlength=world)[:world]
+    return order, send_counts
+
+
+def ep_dispatch_combine(
+    x: torch.Tensor,
+    topk_weights: torch.Tensor,
+    topk_ids: torch.Tensor,
+    experts_per_rank: int,
+    local_fn: Callable[[torch.Tensor, torch.Tensor, torch.Tensor], torch.Tensor],
+    group=None,
+    combine: Callable[[torch.Tensor], torch.Tensor] | None = None,
+) -> torch.Tensor:
+    """x [T, H]; topk_weights fp32 [T, k]; topk_ids int [T, k] (global expert
+    ids). local_fn(rows [R, H], local_ids int32 [R], weights fp32 [R]) -> [R, H]
+    computes `weights[r] * expert[local_ids[r]](rows[r])` for the rows this rank
+    received. Returns [T, H]: for each token the sum of its k result rows
+    (`combine`, default a float32 sum rounded to x's dtype)."""
+    world = dist.get_world_size(group)
+    t, k = topk_ids.shape
+    h = x.size(1)
+    order, send_counts = dispatch_plan(topk_ids, experts_per_rank, world)
+    recv_counts = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv_counts, send_counts, group=group)
+    send_splits, recv_splits = send_counts.tolist(), recv_counts.tolist()   # the one host sync
+    n_recv = sum(recv_splits)
+
+    # rows and (local expert id, weight) of every slot, in dispatch order
+    send_x = x.index_select(0, order // k)
+    meta = torch.empty(t * k, 2, dtype=torch.float32, device=x.device)
+    flat_ids = topk_ids.reshape(-1).index_select(0, order)
+    meta[:, 0] = (flat_ids % experts_per_rank).to(torch.float32)
+    meta[:, 1] = topk_weights.reshape(-1).to(torch.float32).index_select(0, order)
+    recv_x = torch.empty(n_recv, h, dtype=x.dtype, device=x.device)
+    recv_meta = torch.empty(n_recv, 2, dtype=torch.float32, device=x.device)
+    dist.all_to_all_single(recv_x, send_x, recv_splits, send_splits, group=group)
+    dist.all_to_all_single(recv_meta, meta, recv_splits, send_splits, group=group)
+
+    y = local_fn(recv_x, recv_meta[:, 0].to(torch.int32), recv_meta[:, 1].contiguous())
+
+    back = torch.empty(t * k, h, dtype=y.dtype, device=x.device)
+    dist.all_to_all_single(back, y.contiguous(), send_splits, recv_splits, group=group)
+    slots = torch.empty_like(back)
+    slots.index_copy_(0, order, back)          # undo the dispatch order
+    slots = slots.view(t, k, h)
+    if combine is not None:
+        return combine(slots)
+    return slots.float().sum(1).to(x.dtype)
+
+
+def local_experts_mxfp4(w13, w13_scale, w2, w2_scale, block_m: int = 64):
+    """local_fn over this rank's MXFP4 experts: w13 uint8 [E, 2I, H/2] with e8m0
+    scales [E, 2I, H/32], w2 uint8 [E, H, I/2] with scales [E, H, I/32]. Gate-up
+    GEMM with SiLU-mul, down GEMM times the routing weight, both on the grouped
+    MXFP4 kernel; the received rows are tokens with one expert each."""
+    from . import moe as _moe
+
+    e = w13.size(0)
+    inter = w13.size(1) // 2
+    hidden = w2.size(1)
+    ops = torch.ops.strix
+
+    def run(rows, local_ids, weights):
+        r = rows.size(0)
+        y = torch.empty(r, hidden, dtype=torch.bfloat16, device=rows.device)
+        if r == 0:
+            return y
+        sorted_ids, expert_ids, num_post = _moe.align(local_ids.view(r, 1), block_m, e)
+        act = torch.empty(r, inter, dtype=torch.bfloat16, device=rows.device)
+        ops.moe_gemm_mxfp4(act, rows, w13, w13_scale, sorted_ids, expert_ids, num_post, None, 1,
+                           block_m, 64, True, "silu")
+        ops.moe_gemm_mxfp4(y, act, w2, w2_scale, sorted_ids, expert_ids, num_post, weights, 1,
+                           block_m, 64, False, "silu")
+        return y
+
+    return run
+
+
+def ep_moe_mxfp4(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, block_m: int = 64):
+    """One expert-parallel MXFP4 MoE layer. x bf16 [T_local, H]; logits fp32
+    [T_local, E_global]; the weight tensors hold this rank's E_global / world
+    experts. Router and combine run on this rank's tokens, the experts where
+    they live. Returns bf16 [T_local, H]."""
+    from . import moe as _moe
+
+    weights, ids = _moe.route(logits, top_k)
+    t, h = x.shape
+
+    def combine(slots):
+        out = torch.empty(t, h, dtype=torch.bfloat16, device=x.device)
+        torch.ops.strix.moe_sum(slots, out)
+        return out
+
+    return ep_dispatch_combine(x, weights, ids, w13.size(0),
+                               local_experts_mxfp4(w13, w13_scale, w2, w2_scale, block_m),
+                               group, combine)
