@@ -478,6 +478,282 @@ __global__ void __launch_bounds__(umma_threads(NTOK), 1) moe_gemm_umma_kernel(co
   if (warp == kIssuerWarp) tmem_dealloc(tmem, L::kTmemCols);
 }
 
+// ===================================================================== wide tiles
+// The same GEMM for m-blocks of 128 tokens, where the tensor core, not the weight
+// stream, sets the pace: the operands keep their natural roles - the m-block's
+// 128 tokens are the MMA's A (M = 128, one TMEM lane per token) and 256 weight
+// rows its B (N = 256; under the fused gate 128 gate rows interleaved with the
+// 128 matching up rows) - so one MMA does 128 x 256 x 32 multiply-adds and a K
+// block of 128 costs four of them. A consumer thread owns one token and 128 of
+// the 256 columns: the fold needs one scalar per thread and K block (the
+// token's activation scale times one of two weight-block scales), the gate
+// pairs adjacent columns in the thread's own registers, and an output row is
+// written as 128 or 256 contiguous bytes. Two 256-column accumulators fill TMEM;
+// a ring position's single commit frees its operand stage and publishes the sums.
+constexpr int kWideTok = 128, kWideCols = 256, kWideKbMax = 16;
+constexpr int kWideConsumerWarps = 8;                       // 2 per TMEM lane quadrant
+constexpr int kWideThreads = (kProducerWarps + kWideConsumerWarps) * 32;
+struct WideLayout {
+  static constexpr int kABytes = kWideTok * kKBlock;        // 16 KB of token rows
+  static constexpr int kBBytes = kWideCols * kKBlock;       // 32 KB of weight rows
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = 4, kAccBufs = 2, kMetaBufs = 2;
+  static constexpr int kSaFloats = kWideKbMax * kWideTok, kSwFloats = kWideKbMax * 2;
+  static constexpr int kMetaBytes = kMetaBufs * (kSaFloats * 4 + kSwFloats * 4 + kWideTok * 8);
+  static constexpr int kSmem = 1024 + kStages * kStageBytes + kMetaBytes + 256;
+};
+
+__global__ void __launch_bounds__(kWideThreads, 1) moe_gemm_umma_wide_kernel(
+    const UmmaMoeArgs p, const __grid_constant__ CUtensorMap map_w,
+    const __grid_constant__ CUtensorMap map_a) {
+  using L = WideLayout;
+  constexpr int S = L::kStages, NB = L::kAccBufs, MB = L::kMetaBufs;
+  extern __shared__ uint8_t raw_smem[];
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
+                                             ~uintptr_t(1023));
+  float* s_sa = reinterpret_cast<float*>(ring + S * L::kStageBytes);      // [MB][kb][token]
+  float* s_sw = s_sa + MB * L::kSaFloats;                                 // [MB][kb][2]
+  float* s_tw = s_sw + MB * L::kSwFloats;                                 // [MB][token]
+  int* s_sid = reinterpret_cast<int*>(s_tw + MB * kWideTok);              // [MB][token]
+  __shared__ __align__(8) uint64_t full_bar[S], done_bar[S], tempty_bar[NB];
+  __shared__ __align__(8) uint64_t meta_empty_bar[MB], meta_full_bar[MB];
+  __shared__ uint32_t tmem_slot;
+  __shared__ volatile int s_abort;
+  __shared__ int s_expert[kMaxMBlocks];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool gate = p.gate_act != 0;
+  const int half_n = p.N / 2;
+  const int nkb = p.K / kKBlock;
+  const int m_blocks = *p.num_post / kWideTok;
+  const int total_items = m_blocks * p.n_tiles;
+  const int tile_rows = gate ? kWideCols / 2 : kWideCols;   // output rows (per half) of a tile
+  for (int i = tid; i < m_blocks && i < kMaxMBlocks; i += kWideThreads) s_expert[i] = p.expert_ids[i];
+  if (tid == 0) {
+    for (int i = 0; i < S; ++i) mbar_init(&full_bar[i], 1), mbar_init(&done_bar[i], 1);
+    for (int i = 0; i < NB; ++i) mbar_init(&tempty_bar[i], kWideConsumerWarps);
+    for (int i = 0; i < MB; ++i) mbar_init(&meta_empty_bar[i], kWideConsumerWarps), mbar_init(&meta_full_bar[i], 1);
+    s_abort = 0;
+    fence_mbar_init();
+  }
+  if (warp == kIssuerWarp) tmem_alloc(&tmem_slot, 512);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t ring_s = smem_u32(ring);
+  auto next_valid = [&](int item) {
+    while (item < total_items && s_expert[item / p.n_tiles] < 0) item += gridDim.x;
+    return item;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- producer
+    if (lane == 0) {
+      tma::prefetch_map(&map_w);
+      tma::prefetch_map(&map_a);
+      int t = 0;
+      bool dead = false;
+      for (int item = next_valid(blockIdx.x); item < total_items && !dead;
+           item = next_valid(item + gridDim.x)) {
+        const int mb = item / p.n_tiles, nt = item - mb * p.n_tiles;
+        const int expert = s_expert[mb];
+        for (int kb = 0; kb < nkb; ++kb, ++t) {
+          const int s = t % S;
+          if (!mbar_wait(&done_bar[s], ((t / S) & 1) ^ 1) || s_abort) {   // its MMAs retired
+            dead = true;
+            break;
+          }
+          const uint32_t st = ring_s + s * L::kStageBytes;
+          tma::mbar_expect_tx(&full_bar[s], L::kStageBytes);
+          tma::load_2d(st, &map_a, kb * kKBlock, mb * kWideTok, &full_bar[s]);
+          tma::load_4d(st + L::kABytes, &map_w, kb * kKBlock, 0, nt * tile_rows, expert, &full_bar[s]);
+        }
+      }
+      if (dead) atomicExch(p.status, 1), s_abort = 1;
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- metadata
+    int li = 0;
+    bool dead = false;
+    for (int item = next_valid(blockIdx.x); item < total_items && !dead;
+         item = next_valid(item + gridDim.x), ++li) {
+      const int buf = li % MB;
+      const bool free_ok = mbar_wait(&meta_empty_bar[buf], ((li / MB) & 1) ^ 1);
+      if (__any_sync(0xffffffffu, !free_ok || s_abort != 0)) {
+        dead = true;
+        break;
+      }
+      const int mb = item / p.n_tiles, nt = item - mb * p.n_tiles;
+      const int expert = s_expert[mb];
+      const uint32_t sa_dst = smem_u32(s_sa + buf * L::kSaFloats);
+#pragma unroll
+      for (int i = 0; i < kWideTok / 32; ++i) {
+        const int j = lane + 32 * i;
+        const int64_t sid = p.sorted_ids[mb * kWideTok + j];
+        const bool ok = sid >= 0 && sid < p.num_valid;
+        s_sid[buf * kWideTok + j] = ok ? int(sid) : -1;
+        if (p.topk_w != nullptr)
+          cp_async_4_zfill(smem_u32(s_tw + buf * kWideTok + j), p.topk_w + (ok ? sid : 0), ok);
+        else
+          s_tw[buf * kWideTok + j] = 1.f;
+        const float* sap = p.sa + (int64_t(mb) * kWideTok + j) * p.sa_stride;
+        for (int k2 = 0; k2 < nkb; ++k2) cp_async_4(sa_dst + (k2 * kWideTok + j) * 4, sap + k2);
+      }
+      if (p.scale_kind == 2) {
+        // the tile's two 128-row blocks: gate / up rows, or the lower / upper half
+        for (int i = lane; i < 2 * nkb; i += 32) {
+          const int k2 = i >> 1, par = i & 1;
+          const int blk = gate ? ((par ? half_n : 0) + nt * tile_rows) / 128 : nt * 2 + par;
+          cp_async_4(smem_u32(s_sw + buf * L::kSwFloats + i),
+                     p.scales + int64_t(expert) * p.s_se + int64_t(blk) * p.s_sn + k2);
+        }
+      }
+      cp_async_commit();
+      cp_async_wait<0>();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&meta_full_bar[buf]);
+    }
+    if (dead && lane == 0) atomicExch(p.status, 1), s_abort = 1;
+  } else if (warp == kIssuerWarp) {
+    // --------------------------------------------------------------- issuer
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc(D_F32, 0, 0, kWideTok, kWideCols);
+      const uint32_t a_lo0 = smem_desc_lo(ring_s);
+      int t = 0;
+      bool dead = false;
+      for (int item = next_valid(blockIdx.x); item < total_items && !dead;
+           item = next_valid(item + gridDim.x)) {
+        for (int kb = 0; kb < nkb; ++kb, ++t) {
+          const int s = t % S, b = t % NB;
+          const bool ok_full = mbar_wait(&full_bar[s], (t / S) & 1);
+          const bool ok_acc = mbar_wait(&tempty_bar[b], ((t / NB) & 1) ^ 1);
+          if (!ok_full || !ok_acc || s_abort) {
+            dead = true;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_lo = a_lo0 + s * (L::kStageBytes >> 4), b_lo = a_lo + (L::kABytes >> 4);
+          const uint32_t d = tmem + b * kWideCols;
+          mma_ss_lo<KIND_F8F6F4, false>(d, a_lo, b_lo, idesc);
+          mma_ss_lo<KIND_F8F6F4, true>(d, a_lo + 2, b_lo + 2, idesc);
+          mma_ss_lo<KIND_F8F6F4, true>(d, a_lo + 4, b_lo + 4, idesc);
+          mma_ss_lo<KIND_F8F6F4, true>(d, a_lo + 6, b_lo + 6, idesc);
+          mma_commit(&done_bar[s]);   // the stage may be refilled, the sums are ready
+        }
+      }
+      if (dead) atomicExch(p.status, 1), s_abort = 1;
+    }
+  } else if (warp >= kProducerWarps) {
+    // ------------------------------------------------------------ consumers
+    const int tok = (warp & 3) * 32 + lane;           // TMEM lane = token of the m-block
+    const int cg = (warp - kProducerWarps) >> 2;      // which 128 of the 256 columns
+    const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
+    constexpr int NC = kWideCols / 2;                 // columns per thread
+    int t = 0, li = 0;
+    bool dead = false;
+    for (int item = next_valid(blockIdx.x); item < total_items && !dead;
+         item = next_valid(item + gridDim.x), ++li) {
+      const int mb = item / p.n_tiles, nt = item - mb * p.n_tiles;
+      const int expert = s_expert[mb];
+      const int buf = li % MB;
+      const bool meta_ok = mbar_wait(&meta_full_bar[buf], (li / MB) & 1);
+      if (__any_sync(0xffffffffu, !meta_ok) || s_abort) {
+        dead = true;
+        break;
+      }
+      const float* sa_item = s_sa + buf * L::kSaFloats + tok;
+      const float* sw_item = s_sw + buf * L::kSwFloats;
+      float acc[NC];
+#pragma unroll
+      for (int j = 0; j < NC; ++j) acc[j] = 0.f;
+      for (int kb = 0; kb < nkb && !dead; ++kb, ++t) {
+        const int s = t % S, b = t % NB;
+        const bool ok = mbar_wait(&done_bar[s], (t / S) & 1);
+        if (__any_sync(0xffffffffu, !ok)) {
+          dead = true;
+          break;
+        }
+        tc_fence_after_sync();
+        const float sa = sa_item[kb * kWideTok];
+        // gate: even columns are gate rows, odd ones up rows; else one block per column group
+        float f_even = sa, f_odd = sa;
+        if (p.scale_kind == 2) {
+          f_even *= gate ? sw_item[2 * kb] : sw_item[2 * kb + cg];
+          f_odd *= gate ? sw_item[2 * kb + 1] : sw_item[2 * kb + cg];
+        }
+        const uint32_t src = tmem + lane_base + b * kWideCols + cg * NC;
+        uint32_t r[2][32];
+        tmem_ld_32x32(src, r[0]);
+#pragma unroll
+        for (int ch = 0; ch < NC / 32; ++ch) {
+          tmem_ld_wait();
+          if (ch + 1 < NC / 32) tmem_ld_32x32(src + (ch + 1) * 32, r[(ch + 1) & 1]);
+          if (ch + 1 == NC / 32) {       // everything read: hand the accumulator back
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty_bar[b]);
+          }
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            acc[ch * 32 + j] = fmaf(__uint_as_float(r[ch & 1][j]), f_even, acc[ch * 32 + j]);
+            acc[ch * 32 + j + 1] = fmaf(__uint_as_float(r[ch & 1][j + 1]), f_odd, acc[ch * 32 + j + 1]);
+          }
+        }
+      }
+      if (dead) break;
+
+      // ---- epilogue: this thread's token row, its 128 columns
+      const int sid = s_sid[buf * kWideTok + tok];
+      const int crow = p.c_sorted ? mb * kWideTok + tok : sid;
+      __nv_bfloat16* cptr = static_cast<__nv_bfloat16*>(p.c) + int64_t(crow < 0 ? 0 : crow) * p.c_stride;
+      if (gate) {
+        // columns 2i, 2i + 1 of the tile = gate row, up row  nt * 128 + cg * 64 + i
+        const int out0 = nt * tile_rows + cg * (NC / 2);
+        const float* chp = p.scales + int64_t(expert) * p.s_se;
+#pragma unroll
+        for (int i = 0; i < NC / 2; i += 8) {
+          uint32_t o[4];
+#pragma unroll
+          for (int u = 0; u < 8; u += 2) {
+            float v[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              float gv = acc[2 * (i + u + e)], uv = acc[2 * (i + u + e) + 1];
+              if (p.scale_kind == 1) gv *= __ldg(chp + out0 + i + u + e), uv *= __ldg(chp + half_n + out0 + i + u + e);
+              v[e] = gate_fn(gv, p.gate_act) * uv;
+            }
+            o[u >> 1] = pack_bf16x2(v[0], v[1]);
+          }
+          if (crow >= 0) *reinterpret_cast<uint4*>(cptr + out0 + i) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      } else {
+        const int out0 = nt * tile_rows + cg * NC;
+        const float tw = s_tw[buf * kWideTok + tok];
+        const float* chp = p.scales + int64_t(expert) * p.s_se + out0;
+#pragma unroll
+        for (int i = 0; i < NC; i += 8) {
+          uint32_t o[4];
+#pragma unroll
+          for (int u = 0; u < 8; u += 2) {
+            float v0 = acc[i + u] * tw, v1 = acc[i + u + 1] * tw;
+            if (p.scale_kind == 1) v0 *= __ldg(chp + i + u), v1 *= __ldg(chp + i + u + 1);
+            o[u >> 1] = pack_bf16x2(v0, v1);
+          }
+          if (crow >= 0) *reinterpret_cast<uint4*>(cptr + out0 + i) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&meta_empty_bar[buf]);
+    }
+    if (dead) atomicExch(p.status, 1), s_abort = 1;
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == kIssuerWarp) tmem_dealloc(tmem, 512);
+}
+
 // Status word the kernels raise when a bounded wait runs out (0 = healthy).
 __device__ int32_t g_umma_status = 0;
 // Cycle counters of CTA 0, filled only while STRIX_UMMA_PROF is set: [0] issuer
@@ -503,6 +779,23 @@ int launch_umma(const UmmaMoeArgs& p, const CUtensorMap& map_w, const CUtensorMa
   }
   kernel<<<sms[dev], umma_threads(NTOK), L::kSmem, st>>>(p, map_w, map_a);
   return launch_status("moe_gemm_umma");
+}
+
+int launch_umma_wide(const UmmaMoeArgs& p, const CUtensorMap& map_w, const CUtensorMap& map_a,
+                     cudaStream_t st) {
+  static bool done[64] = {};
+  static int sms[64] = {};
+  int dev = 0;
+  STRIX_CUDA(cudaGetDevice(&dev));
+  STRIX_CHECK(dev >= 0 && dev < 64, "device index %d out of range", dev);
+  if (!done[dev]) {
+    STRIX_CUDA(cudaFuncSetAttribute(moe_gemm_umma_wide_kernel,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, WideLayout::kSmem));
+    STRIX_CUDA(cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev));
+    done[dev] = true;
+  }
+  moe_gemm_umma_wide_kernel<<<sms[dev], kWideThreads, WideLayout::kSmem, st>>>(p, map_w, map_a);
+  return launch_status("moe_gemm_umma_wide");
 }
 
 }  // namespace
@@ -553,7 +846,13 @@ extern "C" int strix_moe_gemm_fp8_sorted(
   STRIX_CHECK(sa_stride >= k / kKBlock, "act_scales must be [sorted_len, K / 128]");
   if (sorted_len == 0 || num_valid == 0) return STRIX_OK;
   const int64_t out_rows = gate_act ? n / 2 : n;
-  const int tile_out = gate_act ? kTileM / 2 : kTileM;
+  // m-blocks of 128 tokens take the wide-tile kernel (tokens as the MMA's M, 256
+  // weight rows as its N) where its tile divides the problem
+  static const bool no_wide = getenv("STRIX_MOE_NO_WIDE") != nullptr;
+  const int wide_out = gate_act ? kWideCols / 2 : kWideCols;
+  const bool wide = !no_wide && block_m == kWideTok && k <= kWideKbMax * kKBlock &&
+                    out_rows % wide_out == 0;
+  const int tile_out = wide ? wide_out : gate_act ? kTileM / 2 : kTileM;
   UmmaMoeArgs p;
   p.c = c, p.scales = scales, p.sa = act_scales;
   p.sorted_ids = sorted_ids, p.expert_ids = expert_ids, p.num_post = num_post_padded;
@@ -590,6 +889,7 @@ extern "C" int strix_moe_gemm_fp8_sorted(
                                    uint32_t(block_m)),
               "tensor map encoding failed");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (wide) return launch_umma_wide(p, map_w, map_a, st);
   const bool short_k = k <= 16 * kKBlock;
   if (block_m == 16) return short_k ? launch_umma<16, 16>(p, map_w, map_a, st) : launch_umma<16, 64>(p, map_w, map_a, st);
   if (block_m == 32) return short_k ? launch_umma<32, 16>(p, map_w, map_a, st) : launch_umma<32, 64>(p, map_w, map_a, st);
