@@ -309,6 +309,25 @@ int strix_moe_act_quant_fp8_sorted(const void* x, void* q, float* sa, const int3
                                    int64_t q_stride, int64_t sa_stride, int x_is_f16,
                                    strix_stream_t stream);
 
+/* strix_moe_align that also writes the inverse permutation: slot_pos[i] = the
+ * sorted position of slot i (int32 [numel]; -1 for an id outside 0..experts-1).
+ * slot_pos may be NULL. */
+int strix_moe_align_pos(const int32_t* topk_ids, int32_t* sorted_ids, int32_t* expert_ids,
+                        int32_t* num_post_padded, int32_t* slot_pos, int64_t numel,
+                        int64_t experts, int64_t block_m, int64_t sorted_capacity,
+                        int64_t expert_capacity, strix_stream_t stream);
+
+/* The sorted-layout e4m3 quantiser by scatter: token row t of x [tokens, k] is
+ * quantised once and stored at the sorted positions slot_pos[t * top_k + j] of
+ * its top_k slots; padding slots below *num_post_padded get zeros with scale 1.
+ * Same result as strix_moe_act_quant_fp8_sorted with sorted_ids, top_k times
+ * less reading and arithmetic. q e4m3 [rows, k], sa fp32 [rows, k / 128]. */
+int strix_moe_act_quant_fp8_scatter(const void* x, void* q, float* sa, const int32_t* slot_pos,
+                                    const int32_t* sorted_ids, const int32_t* num_post_padded,
+                                    int64_t tokens, int64_t rows, int64_t k, int64_t top_k,
+                                    int64_t x_stride, int64_t q_stride, int64_t sa_stride,
+                                    int x_is_f16, strix_stream_t stream);
+
 /* FP8 W8A8 grouped expert GEMM on tcgen05 over activations in sorted order
  * (row p of a / act_scales = sorted position p; see above). Arithmetic and
  * epilogues are those of strix_moe_gemm with weight_format 0, act_format 2,

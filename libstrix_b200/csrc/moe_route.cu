@@ -91,7 +91,7 @@ constexpr int kAlignThreads = 256;
 __global__ void __launch_bounds__(kAlignThreads) moe_align_kernel(
     const int32_t* __restrict__ topk_ids, int32_t* __restrict__ sorted_ids,
     int32_t* __restrict__ expert_ids, int32_t* __restrict__ num_post, int numel, int experts,
-    int block_m, int cap, int cap_blocks) {
+    int block_m, int cap, int cap_blocks, int32_t* __restrict__ slot_pos) {
   extern __shared__ int s_count[];            // [experts]
   __shared__ int s_warp[kAlignThreads / 32];
   __shared__ int s_base;
@@ -151,6 +151,7 @@ __global__ void __launch_bounds__(kAlignThreads) moe_align_kernel(
     if (hit) {
       const int pos = base + placed + before + __popc(bal & ((1u << (tid & 31)) - 1u));
       if (pos < cap) sorted_ids[pos] = i;
+      if (slot_pos != nullptr) slot_pos[i] = pos < cap ? pos : -1;   // the inverse permutation
     }
     placed += total;
   }
@@ -237,6 +238,72 @@ __global__ void __launch_bounds__(256) act_quant_kernel(
   if (sub == 0) sa[r * sa_stride + gi] = s;
 }
 
+// e4m3 quantiser that writes the sorted layout by SCATTER: a 16-lane team
+// quantises one (token, 128 group) once and stores it at the sorted positions of
+// the token's top_k slots (slot_pos = the inverse permutation from moe_align), so
+// a token is read and quantised once instead of top_k times. Teams past the
+// tokens cover the sorted positions: a padding slot inside the padded range gets
+// a row of zeros with scale 1.
+template <bool IN_F16>
+__global__ void __launch_bounds__(256) act_quant_scatter_kernel(
+    const uint16_t* __restrict__ x, int64_t x_stride, uint8_t* __restrict__ q, int64_t q_stride,
+    float* __restrict__ sa, int64_t sa_stride, int64_t tokens, int groups, int top_k,
+    const int32_t* __restrict__ slot_pos, const int32_t* __restrict__ sorted_ids,
+    const int32_t* __restrict__ num_post, int64_t rows_cap, int64_t num_valid) {
+  const int64_t team = (int64_t(blockIdx.x) * 256 + threadIdx.x) >> 4;
+  const int sub = threadIdx.x & 15;
+  const int64_t token_teams = tokens * groups;
+  if (team >= token_teams) {
+    // ---- padding rows (a whole 16-lane team takes this branch together)
+    const int64_t pt = team - token_teams;
+    const int64_t r = pt / groups;
+    const int gi = int(pt % groups);
+    if (r >= rows_cap || r >= *num_post) return;
+    const int64_t sid = sorted_ids[r];
+    if (sid >= 0 && sid < num_valid) return;
+    *reinterpret_cast<uint2*>(q + r * q_stride + gi * 128 + sub * 8) = make_uint2(0u, 0u);
+    if (sub == 0) sa[r * sa_stride + gi] = 1.f;
+    return;
+  }
+  const int64_t r = team / groups;
+  const int gi = int(team % groups);
+  const uint4 w = *reinterpret_cast<const uint4*>(x + r * x_stride + gi * 128 + sub * 8);
+  const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+  float v[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (IN_F16) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&ws[i]));
+      v[2 * i] = f.x, v[2 * i + 1] = f.y;
+    } else {
+      v[2 * i] = bf16_lo(ws[i]), v[2 * i + 1] = bf16_hi(ws[i]);
+    }
+  }
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+  // only this team's 16 lanes take part: the other half of the warp may be a padding team
+  const unsigned team_mask = 0xffffu << (threadIdx.x & 16);
+  for (int o = 8; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(team_mask, amax, o, 16));
+  const float s = amax > 0.f ? __fdiv_rn(amax, 448.f) : 1.f;
+  uint32_t h[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float a = __fdiv_rn(v[2 * i], s), b = __fdiv_rn(v[2 * i + 1], s);
+    uint16_t o;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(o) : "f"(b), "f"(a));
+    h[i] = o;
+  }
+  const uint2 packed = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+  for (int j = 0; j < top_k; ++j) {
+    const int pos = slot_pos[r * top_k + j];
+    if (pos < 0 || pos >= rows_cap) continue;
+    *reinterpret_cast<uint2*>(q + int64_t(pos) * q_stride + gi * 128 + sub * 8) = packed;
+    if (sub == 0) sa[int64_t(pos) * sa_stride + gi] = s;
+  }
+}
+
 // -------------------------------------------------------------------- combine
 // out[t, h] = sum_j in[t, j, h] in fp32 (j ascending), one bf16 rounding.
 __global__ void __launch_bounds__(256) moe_sum_kernel(
@@ -300,10 +367,11 @@ extern "C" int64_t strix_moe_align_capacity(int64_t numel, int64_t experts, int6
   return (cap + block_m - 1) / block_m * block_m;
 }
 
-extern "C" int strix_moe_align(const int32_t* topk_ids, int32_t* sorted_ids, int32_t* expert_ids,
-                               int32_t* num_post_padded, int64_t numel, int64_t experts,
-                               int64_t block_m, int64_t sorted_capacity, int64_t expert_capacity,
-                               strix_stream_t stream) {
+extern "C" int strix_moe_align_pos(const int32_t* topk_ids, int32_t* sorted_ids,
+                                   int32_t* expert_ids, int32_t* num_post_padded,
+                                   int32_t* slot_pos, int64_t numel, int64_t experts,
+                                   int64_t block_m, int64_t sorted_capacity,
+                                   int64_t expert_capacity, strix_stream_t stream) {
   STRIX_CHECK(numel >= 0 && numel < (int64_t(1) << 30), "too many routed slots");
   STRIX_CHECK(experts >= 1 && experts <= 8192, "experts must be in 1..8192");
   STRIX_CHECK(block_m >= 1 && block_m <= 1024, "block_m must be in 1..1024");
@@ -314,8 +382,45 @@ extern "C" int strix_moe_align(const int32_t* topk_ids, int32_t* sorted_ids, int
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   moe_align_kernel<<<unsigned(experts + 1), kAlignThreads, size_t(experts) * sizeof(int), st>>>(
       topk_ids, sorted_ids, expert_ids, num_post_padded, int(numel), int(experts), int(block_m),
-      int(sorted_capacity), int(expert_capacity));
+      int(sorted_capacity), int(expert_capacity), slot_pos);
   return launch_status("moe_align");
+}
+
+extern "C" int strix_moe_align(const int32_t* topk_ids, int32_t* sorted_ids, int32_t* expert_ids,
+                               int32_t* num_post_padded, int64_t numel, int64_t experts,
+                               int64_t block_m, int64_t sorted_capacity, int64_t expert_capacity,
+                               strix_stream_t stream) {
+  return strix_moe_align_pos(topk_ids, sorted_ids, expert_ids, num_post_padded, nullptr, numel,
+                             experts, block_m, sorted_capacity, expert_capacity, stream);
+}
+
+extern "C" int strix_moe_act_quant_fp8_scatter(const void* x, void* q, float* sa,
+                                               const int32_t* slot_pos, const int32_t* sorted_ids,
+                                               const int32_t* num_post_padded, int64_t tokens,
+                                               int64_t rows, int64_t k, int64_t top_k,
+                                               int64_t x_stride, int64_t q_stride,
+                                               int64_t sa_stride, int x_is_f16,
+                                               strix_stream_t stream) {
+  STRIX_CHECK(slot_pos != nullptr && sorted_ids != nullptr && num_post_padded != nullptr,
+              "slot_pos, sorted_ids and num_post_padded must not be NULL");
+  STRIX_CHECK(tokens >= 0 && rows >= 0 && k > 0 && k % 128 == 0 && top_k >= 1,
+              "K must be a multiple of 128");
+  STRIX_CHECK(x_stride % 8 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && q_stride % 8 == 0 &&
+                  reinterpret_cast<uintptr_t>(q) % 8 == 0 && sa_stride >= k / 128,
+              "16-byte aligned rows required");
+  if (tokens == 0 && rows == 0) return STRIX_OK;
+  const int groups = int(k / 128);
+  const int64_t teams = (tokens + rows) * groups;
+  const unsigned grid = unsigned((teams * 16 + 255) / 256);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  auto xp = static_cast<const uint16_t*>(x);
+  auto qp = static_cast<uint8_t*>(q);
+  const int64_t num_valid = tokens * top_k;
+  if (x_is_f16)
+    act_quant_scatter_kernel<true><<<grid, 256, 0, st>>>(xp, x_stride, qp, q_stride, sa, sa_stride, tokens, groups, int(top_k), slot_pos, sorted_ids, num_post_padded, rows, num_valid);
+  else
+    act_quant_scatter_kernel<false><<<grid, 256, 0, st>>>(xp, x_stride, qp, q_stride, sa, sa_stride, tokens, groups, int(top_k), slot_pos, sorted_ids, num_post_padded, rows, num_valid);
+  return launch_status("moe_act_quant_scatter");
 }
 
 static int act_quant_common(const void* x, void* q, float* sa, int64_t rows, int64_t k,

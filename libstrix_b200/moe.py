@@ -15,14 +15,17 @@ from . import _lib
 
 
 def pick_block_m(tokens: int, top_k: int, experts: int) -> int:
-    """Rows per m-block: the smallest of 16/32/64 that holds an average expert's
-    share twice over, so most experts stream their weights exactly once; 64
-    (the widest token chunk of the streaming kernel) beyond that."""
+    """Rows per m-block. Up to 16 rows per expert on average: the smaller of 16 /
+    32 that holds an expert's share twice over, so most experts stream their
+    weights exactly once (tokens as the MMA's N, 128 weight rows as its M).
+    Beyond that 128, the tile of the wide tcgen05 kernel (tokens as the MMA's
+    M, 256 weight rows as its N): measured faster from 32 rows per expert on
+    (0.225 vs 0.234 ms at 512 tokens, 0.51 vs 0.99 ms at 4096)."""
     per_expert = tokens * top_k / max(experts, 1)
     for bm in (16, 32):
         if per_expert * 2 <= bm:
             return bm
-    return 64
+    return 128
 
 
 def route(logits: torch.Tensor, top_k: int, renormalize: bool = True):
@@ -44,6 +47,20 @@ def align(topk_ids: torch.Tensor, block_m: int, num_experts: int):
     torch.ops.strix.moe_align_block_size(topk_ids, num_experts, block_m, sorted_ids, expert_ids,
                                          num_post)
     return sorted_ids, expert_ids, num_post
+
+
+def align_with_positions(topk_ids: torch.Tensor, block_m: int, num_experts: int):
+    """align() plus slot_pos int32 [numel]: the sorted position of every slot."""
+    lib = _lib.load()
+    cap = lib.strix_moe_align_capacity(topk_ids.numel(), num_experts, block_m)
+    dev = topk_ids.device
+    sorted_ids = torch.empty(cap, dtype=torch.int32, device=dev)
+    expert_ids = torch.empty(cap // block_m, dtype=torch.int32, device=dev)
+    num_post = torch.empty(1, dtype=torch.int32, device=dev)
+    slot_pos = torch.empty(topk_ids.numel(), dtype=torch.int32, device=dev)
+    torch.ops.strix.moe_align_block_size_pos(topk_ids, num_experts, block_m, sorted_ids, expert_ids,
+                                             num_post, slot_pos)
+    return sorted_ids, expert_ids, num_post, slot_pos
 
 
 def act_quant_fp8(x: torch.Tensor):
@@ -114,14 +131,17 @@ def fused_moe_fp8_w8a8(x, logits, w13, w13_scale, w2, w2_scale, top_k, block_m=N
     if layout == "auto":
         layout = "sorted" if sorted_path_covers(w13, w13_scale, w2, w2_scale, bm) else "gather"
     weights, ids = route(logits, top_k)
-    sorted_ids, expert_ids, num_post = align(ids, bm, e)
     ops = torch.ops.strix
+    if layout == "sorted":
+        sorted_ids, expert_ids, num_post, slot_pos = align_with_positions(ids, bm, e)
+    else:
+        sorted_ids, expert_ids, num_post = align(ids, bm, e)
     if layout == "sorted":
         cap = sorted_ids.numel()
         if ws is None or ws.sorted_rows != cap:
             ws = Fp8MoeWorkspace(t, top_k, h, inter, x.device, sorted_rows=cap)
         slots = t * top_k
-        ops.moe_act_quant_fp8_sorted(x, ws.xq, ws.xs, sorted_ids, num_post, top_k, slots)
+        ops.moe_act_quant_fp8_scatter(x, ws.xq, ws.xs, slot_pos, sorted_ids, num_post, top_k)
         ops.moe_gemm_fp8_sorted(ws.act, ws.xq, ws.xs, w13, w13_scale, sorted_ids, expert_ids,
                                 num_post, None, slots, bm, True, "silu", True)
         ops.moe_act_quant_fp8_sorted(ws.act, ws.aq, ws.as_, None, num_post, 1, slots)

@@ -152,6 +152,14 @@ _MOE_ROWS = [
            "sorted_ids[p] / top_k, zeros for padding), the input layout of moe_gemm_fp8_sorted",
            {"dtype": ("bf16", "fp16"), "activation_dtype": "fp8_e4m3", "group_size": 128,
             "layout": "sorted"}),
+    Kernel("moe_act_quant_fp8_scatter", "moe_act_quant_fp8",
+           "the sorted-layout e4m3 quantiser by scatter: a token is quantised once and stored "
+           "at the sorted positions of its top_k slots (inverse permutation from the align kernel)",
+           {"dtype": ("bf16", "fp16"), "activation_dtype": "fp8_e4m3", "group_size": 128,
+            "layout": "sorted", "scatter": True}),
+    Kernel("moe_align_block_size_pos", "moe_align",
+           "moe_align_block_size that also writes the inverse permutation (slot -> sorted position)",
+           {"experts": Range(1, 8192), "block_m": Range(1, 1024), "positions": True}),
     _moe_row(
         "moe_gemm_fp8_w8a8", "moe_gemm_fp8",
         "e4m3 experts x e4m3 activations (one fp32 scale per token and 128-wide K "

@@ -349,6 +349,48 @@ def moe_act_quant_fp8_sorted(x, q, sa, sorted_ids, num_post_padded, top_k, num_v
                   x.stride(0), q.stride(0), sa.stride(0), int(x.dtype == torch.float16), _stream())
 
 
+@_define("moe_align_block_size_pos(Tensor topk_ids, int num_experts, int block_size, "
+         "Tensor(a!) sorted_token_ids, Tensor(b!) experts_ids, Tensor(c!) num_tokens_post_pad, "
+         "Tensor(d!) slot_pos) -> ()")
+def moe_align_block_size_pos(topk_ids, num_experts, block_size, sorted_token_ids, experts_ids,
+                             num_tokens_post_pad, slot_pos):
+    """moe_align_block_size plus the inverse permutation slot_pos [numel] int32."""
+    _check(all(t.dtype == torch.int32 and t.is_contiguous()
+               for t in (topk_ids, sorted_token_ids, experts_ids, num_tokens_post_pad, slot_pos)),
+           "routing tensors must be contiguous int32")
+    _check(slot_pos.numel() >= topk_ids.numel(), "slot_pos must have an entry per slot")
+    with torch.cuda.device(topk_ids.device):
+        _lib.call("strix_moe_align_pos", topk_ids.data_ptr(), sorted_token_ids.data_ptr(),
+                  experts_ids.data_ptr(), num_tokens_post_pad.data_ptr(), slot_pos.data_ptr(),
+                  topk_ids.numel(), num_experts, block_size, sorted_token_ids.numel(),
+                  experts_ids.numel(), _stream())
+
+
+@_define("moe_act_quant_fp8_scatter(Tensor x, Tensor(a!) q, Tensor(b!) sa, Tensor slot_pos, "
+         "Tensor sorted_ids, Tensor num_post_padded, int top_k) -> ()")
+def moe_act_quant_fp8_scatter(x, q, sa, slot_pos, sorted_ids, num_post_padded, top_k):
+    """Sorted-layout quantiser by scatter: x[t] is quantised once and stored at
+    the sorted positions slot_pos[t * top_k + j]; padding rows become zeros."""
+    _check(x.dim() == 2 and x.dtype in (torch.bfloat16, torch.float16) and x.stride(1) == 1,
+           "x must be bf16 or fp16 [tokens, K]")
+    k = x.size(1)
+    _check(k % 128 == 0, "K must be a multiple of 128")
+    rows = q.size(0)
+    _check(q.dtype == torch.float8_e4m3fn and q.dim() == 2 and q.size(1) == k and q.stride(1) == 1,
+           "q must be float8_e4m3fn [sorted rows, K]")
+    _check(sa.dtype == torch.float32 and tuple(sa.shape) == (rows, k // 128) and sa.stride(1) == 1,
+           "sa must be fp32 [sorted rows, K / 128]")
+    _check(all(t.dtype == torch.int32 and t.is_contiguous()
+               for t in (slot_pos, sorted_ids, num_post_padded)), "routing tensors must be int32")
+    _check(slot_pos.numel() >= x.size(0) * top_k and sorted_ids.numel() >= rows,
+           "slot_pos / sorted_ids too short")
+    with torch.cuda.device(x.device):
+        _lib.call("strix_moe_act_quant_fp8_scatter", x.data_ptr(), q.data_ptr(), sa.data_ptr(),
+                  slot_pos.data_ptr(), sorted_ids.data_ptr(), num_post_padded.data_ptr(), x.size(0),
+                  rows, k, top_k, x.stride(0), q.stride(0), sa.stride(0),
+                  int(x.dtype == torch.float16), _stream())
+
+
 @_define("moe_gemm_fp8_sorted(Tensor(a!) c, Tensor qa, Tensor sa, Tensor b, Tensor scales, "
          "Tensor sorted_ids, Tensor expert_ids, Tensor num_post_padded, Tensor? topk_weights, "
          "int num_valid, int block_m, bool silu_mul=False, str activation='silu', "

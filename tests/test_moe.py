@@ -416,3 +416,30 @@ def test_fp8_layer_benchmark_geometry(tokens, layout):
     w, ids = strix.moe.route(layer.logits, layer.top_k)
     assert torch.equal(ids.cpu(), ids_ref)
     rms_check(out, ref, 2e-2)
+
+
+@pytest.mark.parametrize("tokens,top_k,experts,block_m", [(1, 8, 128, 16), (37, 8, 128, 32),
+                                                          (300, 4, 16, 64), (256, 8, 128, 128)])
+def test_scatter_quantiser_equals_gather_quantiser(tokens, top_k, experts, block_m):
+    """Same bytes and scales in every row below num_post_padded, and slot_pos is
+    the inverse of sorted_ids."""
+    g = torch.Generator().manual_seed(tokens)
+    ids = torch.stack([torch.randperm(experts, generator=g)[:top_k] for _ in range(tokens)]).int()
+    x = (torch.randn(tokens, 256, generator=g) * 3).bfloat16().to(DEV)
+    x[0, 128:] = 0
+    sorted_ids, expert_ids, num_post, slot_pos = strix.moe.align_with_positions(ids.to(DEV), block_m,
+                                                                                experts)
+    ref_sorted, _, ref_post = M.align(ids, block_m, experts)
+    n_post = int(num_post.item())
+    assert n_post == int(ref_post.item())
+    assert torch.equal(sorted_ids.cpu()[:n_post], ref_sorted[:n_post])
+    pos = slot_pos.cpu().long()
+    assert torch.equal(sorted_ids.cpu()[pos].long(), torch.arange(tokens * top_k))
+    cap, slots = sorted_ids.numel(), tokens * top_k
+    qa = torch.full((cap, 256), 0x7F, dtype=torch.uint8, device=DEV).view(torch.float8_e4m3fn)
+    sa = torch.full((cap, 2), -1.0, device=DEV)
+    qb, sb = qa.clone(), sa.clone()
+    torch.ops.strix.moe_act_quant_fp8_sorted(x, qa, sa, sorted_ids, num_post, top_k, slots)
+    torch.ops.strix.moe_act_quant_fp8_scatter(x, qb, sb, slot_pos, sorted_ids, num_post, top_k)
+    assert torch.equal(qa.view(torch.uint8)[:n_post], qb.view(torch.uint8)[:n_post])
+    assert torch.equal(sa[:n_post], sb[:n_post])
