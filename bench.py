@@ -530,12 +530,57 @@ def bench_ep_moe(args, dev, rank: int, world: int) -> dict:
     ok = bool(torch.isfinite(out.float()).all())
     flops = 2.0 * tokens_total * top_k * (2 * inter * hid + hid * inter)
     ms = ms.item()
-    return {"config": "MXFP4 MoE, H=2880 E=128 top-4 I=2880, 8192 tokens, EP over ranks, Zipf(1.1) bias",
+    fp8 = _bench_ep_fp8(dev, rank, world, steps)
+    return {"fp8": fp8,
+            "config": "MXFP4 MoE, H=2880 E=128 top-4 I=2880, 8192 tokens, EP over ranks, Zipf(1.1) bias",
             "n_gpus": world, "scaling": "strong", "ms_per_layer": ms,
             "tflops": flops / (ms * 1e-3) / 1e12, "tokens_per_s": tokens_total / (ms * 1e-3),
             "weight_bytes_per_rank": int(w13.numel() + s13.numel() + w2.numel() + s2.numel()),
             "finite": ok, "gpu_launches": 5 * steps,
             "exchange": "NCCL all_to_all_single x4 per layer (counts, rows, ids+weights, results)"}
+
+
+def _bench_ep_fp8(dev, rank: int, world: int, steps: int) -> dict:
+    """The FP8 W8A8 layer of config 1 (H=2048, E=128, top-8, I=768) expert-parallel:
+    4096 tokens in total, 4096 / N per rank, 128 / N experts per rank; local
+    experts on the sorted-layout tcgen05 kernels. Strong scaling."""
+    import torch.distributed as dist
+
+    from libstrix_b200 import ep
+    from libstrix_b200.workloads import moe_fp8_layer
+
+    tokens_total, experts = 4096, 128
+    layer = moe_fp8_layer(tokens=tokens_total // world, seed=10 + rank, device=dev)
+    e_local = experts // world
+    lo = rank * e_local
+    w13, s13 = layer.w13[lo:lo + e_local].contiguous(), layer.w13_scale[lo:lo + e_local].contiguous()
+    w2, s2 = layer.w2[lo:lo + e_local].contiguous(), layer.w2_scale[lo:lo + e_local].contiguous()
+    x, logits, top_k = layer.x, layer.logits, layer.top_k
+    flops_total = layer.flops * world
+    del layer
+    torch.cuda.empty_cache()
+
+    def step():
+        return ep.ep_moe_fp8(x, logits, w13, s13, w2, s2, top_k)
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        out = step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = ms.item()
+    return {"config": "FP8 W8A8 MoE, H=2048 E=128 top-8 I=768, 4096 tokens, EP over ranks",
+            "n_gpus": world, "scaling": "strong", "ms_per_layer": ms,
+            "tflops": flops_total / (ms * 1e-3) / 1e12, "tokens_per_s": tokens_total / (ms * 1e-3),
+            "finite": bool(torch.isfinite(out.float()).all())}
 
 
 def bench_attn_prefill(args, dev, with_cpu: bool) -> dict:

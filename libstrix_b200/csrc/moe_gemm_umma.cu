@@ -480,11 +480,6 @@ __global__ void __launch_bounds__(umma_threads(NTOK), 1) moe_gemm_umma_kernel(co
   if (warp == kIssuerWarp) tmem_dealloc(tmem, L::kTmemCols);
 }
 
-__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
 // ===================================================================== wide tiles
 // The same GEMM for m-blocks of 128 tokens, where the tensor core, not the weight
 // stream, sets the pace: the operands keep their natural roles - the m-block's
@@ -643,12 +638,10 @@ __global__ void __launch_bounds__(kWideThreads, 1) moe_gemm_umma_wide_kernel(
           tc_fence_after_sync();
           const uint32_t a_lo = a_lo0 + s * (L::kStageBytes >> 4), b_lo = a_lo + (L::kABytes >> 4);
           const uint32_t d = tmem + b * kWideCols;
-          if (!(p.debug & 8)) {
-            mma_ss_lo<KIND_F8F6F4, false>(d, a_lo, b_lo, idesc);
-            mma_ss_lo<KIND_F8F6F4, true>(d, a_lo + 2, b_lo + 2, idesc);
-            mma_ss_lo<KIND_F8F6F4, true>(d, a_lo + 4, b_lo + 4, idesc);
-            mma_ss_lo<KIND_F8F6F4, true>(d, a_lo + 6, b_lo + 6, idesc);
-          }
+          mma_ss_lo<KIND_F8F6F4, false>(d, a_lo, b_lo, idesc);
+          mma_ss_lo<KIND_F8F6F4, true>(d, a_lo + 2, b_lo + 2, idesc);
+          mma_ss_lo<KIND_F8F6F4, true>(d, a_lo + 4, b_lo + 4, idesc);
+          mma_ss_lo<KIND_F8F6F4, true>(d, a_lo + 6, b_lo + 6, idesc);
           mma_commit(&done_bar[s]);   // the stage may be refilled, the sums are ready
         }
       }
@@ -674,11 +667,9 @@ __global__ void __launch_bounds__(kWideThreads, 1) moe_gemm_umma_wide_kernel(
       }
       const float* sa_item = s_sa + buf * L::kSaFloats + tok;
       const float* sw_item = s_sw + buf * L::kSwFloats;
-      // the sums live as (even, odd) column pairs, one 64-bit register pair each,
-      // so that a K block folds with packed fp32 FMAs (two columns per instruction)
-      uint64_t acc2[NC / 2];
+      float acc[NC];
 #pragma unroll
-      for (int j = 0; j < NC / 2; ++j) acc2[j] = 0ull;
+      for (int j = 0; j < NC; ++j) acc[j] = 0.f;
       for (int kb = 0; kb < nkb && !dead; ++kb, ++t) {
         const int s = t % S, b = t % NB;
         const bool ok = mbar_wait(&done_bar[s], (t / S) & 1);
@@ -694,42 +685,35 @@ __global__ void __launch_bounds__(kWideThreads, 1) moe_gemm_umma_wide_kernel(
           f_even *= gate ? sw_item[2 * kb] : sw_item[2 * kb + cg];
           f_odd *= gate ? sw_item[2 * kb + 1] : sw_item[2 * kb + cg];
         }
-        const uint64_t f_pair = pack_f32x2(f_even, f_odd);
         const uint32_t src = tmem + lane_base + b * kWideCols + cg * NC;
-        constexpr int CHW = 16, NCHW = NC / CHW;     // columns per TMEM load
-        uint32_t r[2][CHW];
-        tmem_ld_32x16(src, r[0]);
+        // (measured on the 4096-token gate-up GEMM: 32-column loads with scalar FMAs,
+        // 198 us, beat 16-column loads with packed fma.f32x2, 224 us; with neither
+        // folds nor epilogue the launch takes 147 us, without MMAs as well 118 us)
+        uint32_t r[2][32];
+        tmem_ld_32x32(src, r[0]);
 #pragma unroll
-        for (int ch = 0; ch < NCHW; ++ch) {
+        for (int ch = 0; ch < NC / 32; ++ch) {
           tmem_ld_wait();
-          if (ch + 1 < NCHW) tmem_ld_32x16(src + (ch + 1) * CHW, r[(ch + 1) & 1]);
-          if (ch + 1 == NCHW) {          // everything read: hand the accumulator back
+          if (ch + 1 < NC / 32) tmem_ld_32x32(src + (ch + 1) * 32, r[(ch + 1) & 1]);
+          if (ch + 1 == NC / 32) {       // everything read: hand the accumulator back
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&tempty_bar[b]);
           }
-          if (!(p.debug & 1)) {
 #pragma unroll
-            for (int j = 0; j < CHW; j += 2) {
-              uint64_t a2;
-              asm("mov.b64 %0, {%1, %2};" : "=l"(a2) : "r"(r[ch & 1][j]), "r"(r[ch & 1][j + 1]));
-              asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc2[(ch * CHW + j) / 2]) : "l"(a2), "l"(f_pair));
-            }
+          for (int j = 0; j < 32; j += 2) {
+            acc[ch * 32 + j] = fmaf(__uint_as_float(r[ch & 1][j]), f_even, acc[ch * 32 + j]);
+            acc[ch * 32 + j + 1] = fmaf(__uint_as_float(r[ch & 1][j + 1]), f_odd, acc[ch * 32 + j + 1]);
           }
         }
       }
-      // column c of this thread: the low or high half of pair c / 2
-      auto col = [&](int c) {
-        return __uint_as_float(uint32_t(c & 1 ? acc2[c >> 1] >> 32 : acc2[c >> 1]));
-      };
       if (dead) break;
 
       // ---- epilogue: this thread's token row, its 128 columns
       const int sid = s_sid[buf * kWideTok + tok];
       const int crow = p.c_sorted ? mb * kWideTok + tok : sid;
       __nv_bfloat16* cptr = static_cast<__nv_bfloat16*>(p.c) + int64_t(crow < 0 ? 0 : crow) * p.c_stride;
-      if (p.debug & 2) {
-      } else if (gate) {
+      if (gate) {
         // columns 2i, 2i + 1 of the tile = gate row, up row  nt * 128 + cg * 64 + i
         const int out0 = nt * tile_rows + cg * (NC / 2);
         const float* chp = p.scales + int64_t(expert) * p.s_se;
@@ -741,7 +725,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) moe_gemm_umma_wide_kernel(
             float v[2];
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-              float gv = col(2 * (i + u + e)), uv = col(2 * (i + u + e) + 1);
+              float gv = acc[2 * (i + u + e)], uv = acc[2 * (i + u + e) + 1];
               if (p.scale_kind == 1) gv *= __ldg(chp + out0 + i + u + e), uv *= __ldg(chp + half_n + out0 + i + u + e);
               v[e] = gate_fn(gv, p.gate_act) * uv;
             }
@@ -758,7 +742,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) moe_gemm_umma_wide_kernel(
           uint32_t o[4];
 #pragma unroll
           for (int u = 0; u < 8; u += 2) {
-            float v0 = col(i + u) * tw, v1 = col(i + u + 1) * tw;
+            float v0 = acc[i + u] * tw, v1 = acc[i + u + 1] * tw;
             if (p.scale_kind == 1) v0 *= __ldg(chp + i + u), v1 *= __ldg(chp + i + u + 1);
             o[u >> 1] = pack_bf16x2(v0, v1);
           }

@@ -105,6 +105,65 @@ def local_experts_mxfp4(w13, w13_scale, w2, w2_scale, block_m: int = 64):
     return run
 
 
+def local_experts_fp8(w13, w13_scale, w2, w2_scale, block_m: int | None = None):
+    """local_fn over this rank's FP8 W8A8 block-scaled experts (w13 e4m3 [E, 2I, H]
+    with fp32 scales [E, 2I/128, H/128], w2 e4m3 [E, H, I] with [E, H/128, I/128]):
+    the sorted-layout tcgen05 path of moe.fused_moe_fp8_w8a8, the received rows
+    being tokens with one expert each."""
+    from . import moe as _moe
+
+    e = w13.size(0)
+    inter = w13.size(1) // 2
+    hidden = w2.size(1)
+    ops = torch.ops.strix
+    f8 = torch.float8_e4m3fn
+
+    def run(rows, local_ids, weights):
+        r = rows.size(0)
+        dev = rows.device
+        y = torch.empty(r, hidden, dtype=torch.bfloat16, device=dev)
+        if r == 0:
+            return y
+        bm = block_m or _moe.pick_block_m(r, 1, e)
+        if not _moe.sorted_path_covers(w13, w13_scale, w2, w2_scale, bm):
+            raise RuntimeError("local_experts_fp8: geometry not covered by the sorted-layout kernel")
+        sorted_ids, expert_ids, num_post, slot_pos = _moe.align_with_positions(
+            local_ids.view(r, 1).contiguous(), bm, e)
+        cap = sorted_ids.numel()
+        xq = torch.empty(cap, rows.size(1), dtype=f8, device=dev)
+        xs = torch.empty(cap, rows.size(1) // 128, dtype=torch.float32, device=dev)
+        act = torch.empty(cap, inter, dtype=torch.bfloat16, device=dev)
+        aq = torch.empty(cap, inter, dtype=f8, device=dev)
+        as_ = torch.empty(cap, inter // 128, dtype=torch.float32, device=dev)
+        ops.moe_act_quant_fp8_scatter(rows, xq, xs, slot_pos, sorted_ids, num_post, 1)
+        ops.moe_gemm_fp8_sorted(act, xq, xs, w13, w13_scale, sorted_ids, expert_ids, num_post, None,
+                                r, bm, True, "silu", True)
+        ops.moe_act_quant_fp8_sorted(act, aq, as_, None, num_post, 1, r)
+        ops.moe_gemm_fp8_sorted(y, aq, as_, w2, w2_scale, sorted_ids, expert_ids, num_post, weights,
+                                r, bm, False, "silu", False)
+        return y
+
+    return run
+
+
+def ep_moe_fp8(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, block_m=None):
+    """One expert-parallel FP8 W8A8 block-scaled MoE layer; arguments as
+    ep_moe_mxfp4 with the FP8 weight tensors of this rank's experts."""
+    from . import moe as _moe
+
+    weights, ids = _moe.route(logits, top_k)
+    t, h = x.shape
+
+    def combine(slots):
+        out = torch.empty(t, h, dtype=torch.bfloat16, device=x.device)
+        torch.ops.strix.moe_sum(slots, out)
+        return out
+
+    return ep_dispatch_combine(x, weights, ids, w13.size(0),
+                               local_experts_fp8(w13, w13_scale, w2, w2_scale, block_m), group,
+                               combine)
+
+
 def ep_moe_mxfp4(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, block_m: int = 64):
     """One expert-parallel MXFP4 MoE layer. x bf16 [T_local, H]; logits fp32
     [T_local, E_global]; the weight tensors hold this rank's E_global / world

@@ -287,6 +287,12 @@ KERNELS: list[Kernel] = [
     _decode_row(256, 8, "head 256 GQA 8, four warps per CTA (255 registers)"),
     _decode_row(256, 6, "head 256 GQA 6 (two MMA columns idle)"),
     _decode_row(256, 2, "head 256 GQA 2 (sliding layers)"),
+    *[Kernel("attn_decode_bf16", "attn_decode",
+             "bf16 KV cache: one query per sequence through the prefill kernel (q_len = 1)",
+             {"head_dim": hd, "gqa": Range(1, 64), "queries": 1, "dtype": "bf16",
+              "kv_dtype": ("bf16",), "window": (True, False), "sinks": (True, False)},
+             {"bound": "hbm", "note": "functional path; the int8 rows are the tuned ones"})
+      for hd in (128, 64)],
     *[Kernel(
         "attn_prefill_bf16", "attn_prefill",
         "causal paged flash attention over ragged sequences: 64 queries x one head per CTA, "

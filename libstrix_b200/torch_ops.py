@@ -94,6 +94,14 @@ def attn_decode_bf16(
         _check(sinks.dtype == torch.float32 and sinks.dim() == 1 and sinks.size(0) == q.size(1)
                and sinks.is_contiguous(), "sinks must be contiguous fp32 [Hq]")
     _check(0 <= num_splits <= 64, "num_splits in [1, 64]")
+    if not q8:
+        # bf16 caches: one query per sequence is the prefill kernel with q_len = 1
+        # (head 64 / 128); the int8 kernel below is the tuned decode path
+        nseq = q.size(0)
+        cu = torch.arange(nseq + 1, dtype=torch.int32, device=q.device)
+        attn_prefill_bf16(out, q, key_cache, value_cache, None, None, cu, seq_lens, block_table, cu,
+                          0, scale, 1, window_left, sinks)
+        return
     nseq, hq = q.size(0), q.size(1)
     bs, hkv = key_cache.size(1), key_cache.size(2)
     max_blocks = block_table.size(1)

@@ -166,3 +166,17 @@ def test_long_sequence_properties():
     ones = torch.full_like(vs, 1 / 64)
     flat = run(q, kq, vconst, cu, seq_lens, table, scale, 1, -1, ks, ones)
     torch.testing.assert_close(flat, torch.ones_like(flat), rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("hq,hkv,hd", [(32, 4, 128), (32, 8, 64)])
+@pytest.mark.parametrize("ctx_lens", [[0], [70, 200, 3], [500, 31, 1000, 64]])
+@pytest.mark.parametrize("window_left", [-1, 31])
+def test_decode_with_bf16_cache(hq, hkv, hd, ctx_lens, window_left):
+    """strix.attn_decode on a bf16 cache (tests/test_attn_prefill.py:146-163)."""
+    q_lens = [1] * len(ctx_lens)
+    q, kc, vc, cu, seq_lens, table = A.build_paged_kv(q_lens, ctx_lens, hq, hkv, 16, hd=hd)
+    scale = hd ** -0.5
+    out = torch.full_like(q, float("nan"), device=DEV)
+    strix.attn_decode(out, q.to(DEV), kc.to(DEV), vc.to(DEV), seq_lens.to(DEV), table.to(DEV), scale,
+                      1, window_left)
+    check(out.float().cpu(), A.attention_reference(q, kc, vc, cu, seq_lens, table, scale, window_left))

@@ -119,3 +119,31 @@ def test_ep_moe_mxfp4_matches_oracle_on_visible_gpus():
         assert bool((err <= 2e-2 * rms + ref.abs() * 2.0 ** -8).all()), f"{err.max()} vs rms {rms}"
     finally:
         dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+def test_ep_moe_fp8_equals_the_single_rank_layer():
+    """World size 1: the EP path with FP8 local experts against the fused layer
+    and the CPU oracle (same kernels, different permutation bookkeeping)."""
+    import libstrix_b200 as strix
+    from libstrix_b200 import ep
+    from libstrix_b200.workloads import moe_fp8_layer
+    from oracle import moe as M
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT="29712", RANK="0", WORLD_SIZE="1")
+    dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+    try:
+        layer = moe_fp8_layer(tokens=70, seed=2, device="cuda")
+        out = ep.ep_moe_fp8(layer.x, layer.logits, layer.w13, layer.w13_scale, layer.w2,
+                            layer.w2_scale, layer.top_k)
+        cpu = layer.to("cpu")
+        ref, _, _ = M.moe_fp8_layer(cpu.x, cpu.logits, cpu.w13, cpu.w13_scale, cpu.w2, cpu.w2_scale,
+                                    cpu.top_k)
+        err = (out.float().cpu() - ref.float()).abs()
+        rms = ref.float().pow(2).mean().sqrt()
+        assert bool((err <= 2e-2 * rms + ref.float().abs() * 2.0 ** -8).all()), f"{err.max()} vs {rms}"
+        fused = strix.moe.fused_moe_fp8_w8a8(layer.x, layer.logits, layer.w13, layer.w13_scale,
+                                             layer.w2, layer.w2_scale, layer.top_k)
+        torch.testing.assert_close(out.float(), fused.float(), rtol=2e-2, atol=2e-2)
+    finally:
+        dist.destroy_process_group()
