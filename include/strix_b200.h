@@ -257,6 +257,33 @@ int strix_dense_gemm_w8a16(void* c, const void* x, const void* w, const void* sc
                            int64_t bias_stride, int64_t block_m, int weight_format,
                            int act_format, int scale_kind, int scale_dtype, strix_stream_t stream);
 
+/* bf16 rows into sorted order by scatter: row t of x [tokens, k] is copied to
+ * the sorted positions slot_pos[t * top_k + j]; padding slots below
+ * *num_post_padded get zeros. y bf16 [rows, k]. The input layout of
+ * strix_moe_gemm_mxfp4_sorted. No counterpart in the reference (its kernels
+ * gather token rows inside the GEMM). */
+int strix_moe_permute_bf16(const void* x, void* y, const int32_t* slot_pos,
+                           const int32_t* sorted_ids, const int32_t* num_post_padded,
+                           int64_t tokens, int64_t rows, int64_t k, int64_t top_k,
+                           int64_t x_stride, int64_t y_stride, strix_stream_t stream);
+
+/* MXFP4 grouped expert GEMM on tcgen05 (bf16 x bf16 -> f32 MMAs over weights
+ * decoded to bf16 on the way, exact) for m-blocks of 128 tokens, over bf16
+ * activations in sorted order (row p of a = sorted position p). w uint8 [E, N,
+ * K/2], scales e8m0 [E, N, K/32] as in strix_gemm_w4a16; epilogues, gate_act and
+ * c_sorted as in strix_moe_gemm_fp8_sorted. K a multiple of 64, output width a
+ * multiple of 32 (tiles of 256 weight rows, 128 + 128 under the gate; a ragged
+ * last tile is zero-filled and masked); ..._covers() tells (1/0). The
+ * tensor-bound form of the new moe_gemm_mxfp4 op. */
+int strix_moe_gemm_mxfp4_sorted(void* c, const void* a, const void* w, const void* scales,
+                                const int32_t* sorted_ids, const int32_t* expert_ids,
+                                const int32_t* num_post_padded, const float* topk_weights,
+                                int64_t num_valid, int64_t n, int64_t k, int64_t a_stride,
+                                int64_t c_stride, int64_t w_stride_e, int64_t w_stride_n,
+                                int64_t s_stride_e, int64_t s_stride_n, int64_t sorted_len,
+                                int64_t block_m, int gate_act, int c_sorted, strix_stream_t stream);
+int strix_moe_gemm_mxfp4_sorted_covers(int64_t n, int64_t k, int64_t block_m, int gate_act);
+
 /* Grouped or dense GEMM with int8 activations (qa int8 [rows, k], sa fp32 [rows,
  * k/128], the output of strix_moe_act_quant_i8): s8 x s8 MMAs, sums exact in
  * int32 per 128-wide K group, folded in fp32 with sa * weight scale. Replaces

@@ -52,9 +52,10 @@ inline bool make_map_u8(CUtensorMap* map, const void* base, uint64_t rows, uint6
 
 // Map over bytes with up to 4 dimensions: dims[0] = bytes per row (stride 1),
 // dims[i] with byte strides[i - 1] for i >= 1 (multiples of 16, in any order of
-// magnitude, which lets a box interleave rows of two regions), box[0] = 128.
+// magnitude, which lets a box interleave rows of two regions); box[0] = 128 with
+// the 128-byte swizzle, or any multiple of 16 bytes without swizzle.
 inline bool make_map_u8_nd(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
-                           const uint64_t* strides, const uint32_t* box) {
+                           const uint64_t* strides, const uint32_t* box, bool swizzle128 = true) {
   EncodeTiledFn fn = encode_fn();
   if (!fn || rank < 2 || rank > 4) return false;
   cuuint64_t d[4], st[3];
@@ -62,7 +63,8 @@ inline bool make_map_u8_nd(CUtensorMap* map, const void* base, int rank, const u
   for (int i = 0; i < rank; ++i) d[i] = dims[i], b[i] = box[i], estr[i] = 1;
   for (int i = 0; i + 1 < rank; ++i) st[i] = strides[i];
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, cuuint32_t(rank), const_cast<void*>(base), d, st, b,
-            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 

@@ -77,29 +77,49 @@ def ep_dispatch_combine(
     return slots.float().sum(1).to(x.dtype)
 
 
-def local_experts_mxfp4(w13, w13_scale, w2, w2_scale, block_m: int = 64):
+def local_experts_mxfp4(w13, w13_scale, w2, w2_scale, block_m: int | None = None):
     """local_fn over this rank's MXFP4 experts: w13 uint8 [E, 2I, H/2] with e8m0
     scales [E, 2I, H/32], w2 uint8 [E, H, I/2] with scales [E, H, I/32]. Gate-up
-    GEMM with SiLU-mul, down GEMM times the routing weight, both on the grouped
-    MXFP4 kernel; the received rows are tokens with one expert each."""
+    GEMM with SiLU-mul, down GEMM times the routing weight; the received rows
+    are tokens with one expert each. From 32 rows per expert on (and where its
+    tiles divide the shapes) the tensor-core kernel over the sorted layout runs,
+    below that the weight-streaming kernel."""
+    from . import _lib
     from . import moe as _moe
 
     e = w13.size(0)
     inter = w13.size(1) // 2
     hidden = w2.size(1)
     ops = torch.ops.strix
+    lib = _lib.load()
+    wide_ok = bool(lib.strix_moe_gemm_mxfp4_sorted_covers(w13.size(1), w13.size(2) * 2, 128, 1)
+                   and lib.strix_moe_gemm_mxfp4_sorted_covers(w2.size(1), w2.size(2) * 2, 128, 0))
 
     def run(rows, local_ids, weights):
         r = rows.size(0)
-        y = torch.empty(r, hidden, dtype=torch.bfloat16, device=rows.device)
+        dev = rows.device
+        y = torch.empty(r, hidden, dtype=torch.bfloat16, device=dev)
         if r == 0:
             return y
-        sorted_ids, expert_ids, num_post = _moe.align(local_ids.view(r, 1), block_m, e)
-        act = torch.empty(r, inter, dtype=torch.bfloat16, device=rows.device)
+        bm = block_m or (128 if wide_ok and r >= 32 * e else 64)
+        if bm == 128 and wide_ok:
+            sorted_ids, expert_ids, num_post, slot_pos = _moe.align_with_positions(
+                local_ids.view(r, 1).contiguous(), 128, e)
+            cap = sorted_ids.numel()
+            xs = torch.empty(cap, rows.size(1), dtype=torch.bfloat16, device=dev)
+            act = torch.empty(cap, inter, dtype=torch.bfloat16, device=dev)
+            ops.moe_permute_bf16(rows, xs, slot_pos, sorted_ids, num_post, 1)
+            ops.moe_gemm_mxfp4_sorted(act, xs, w13, w13_scale, sorted_ids, expert_ids, num_post, None,
+                                      r, 128, True, "silu", True)
+            ops.moe_gemm_mxfp4_sorted(y, act, w2, w2_scale, sorted_ids, expert_ids, num_post, weights,
+                                      r, 128, False, "silu", False)
+            return y
+        sorted_ids, expert_ids, num_post = _moe.align(local_ids.view(r, 1), bm, e)
+        act = torch.empty(r, inter, dtype=torch.bfloat16, device=dev)
         ops.moe_gemm_mxfp4(act, rows, w13, w13_scale, sorted_ids, expert_ids, num_post, None, 1,
-                           block_m, 64, True, "silu")
+                           bm, 64, True, "silu")
         ops.moe_gemm_mxfp4(y, act, w2, w2_scale, sorted_ids, expert_ids, num_post, weights, 1,
-                           block_m, 64, False, "silu")
+                           bm, 64, False, "silu")
         return y
 
     return run
@@ -164,7 +184,7 @@ def ep_moe_fp8(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, block
                                combine)
 
 
-def ep_moe_mxfp4(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, block_m: int = 64):
+def ep_moe_mxfp4(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, block_m=None):
     """One expert-parallel MXFP4 MoE layer. x bf16 [T_local, H]; logits fp32
     [T_local, E_global]; the weight tensors hold this rank's E_global / world
     experts. Router and combine run on this rank's tokens, the experts where

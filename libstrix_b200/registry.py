@@ -223,6 +223,19 @@ KERNELS: list[Kernel] = [
            {"silu_mul": (True, False), "dtype": "bf16", "weight_dtype": "uint8", "weight_bits": 4,
             "quant": "mxfp4", "group_size": 32, "scale_dtype": "e8m0", "activation": _GATES},
            dict(_STREAM_SPEC)),
+    Kernel("moe_gemm_mxfp4_sorted", "moe_gemm_mxfp4",
+           "MXFP4 experts on tcgen05 for m-blocks of 128 tokens in sorted order: weights decoded "
+           "to bf16 operand tiles on the way (byte-permute table, exact), bf16 x bf16 -> f32 MMAs "
+           "of 128 x 256 x 16, the whole K accumulated in TMEM",
+           {"silu_mul": (True, False), "dtype": "bf16", "weight_dtype": "uint8", "weight_bits": 4,
+            "quant": "mxfp4", "group_size": 32, "scale_dtype": "e8m0", "activation": _GATES,
+            "layout": "sorted", "block_m": 128},
+           {"tile": "128 tokens x 256 weight rows, K blocks of 64",
+            "pipeline": "TMA producer, 8 transform warps, issuing thread, 4 epilogue warps",
+            "bound": "tensor"}),
+    Kernel("moe_permute_bf16", "moe_permute",
+           "bf16 rows into sorted order by scatter (inverse permutation from the align kernel)",
+           {"dtype": "bf16", "layout": "sorted"}),
     Kernel("mxfp4_gemv", "mxfp4_gemv", "MXFP4 W4A16 at 1-8 rows (the dense form of moe_gemm_mxfp4)",
            {"weight_bits": 4, "group_size": 32, "dtype": "bf16", "m_max": 8}, dict(_STREAM_SPEC)),
     Kernel("mxfp4_wmma_gemm", "mxfp4", "MXFP4 W4A16 dense GEMM, optional bias [N] or [M, N]",

@@ -565,6 +565,53 @@ def moe_gemm_mxfp4(c, a, b, scales, sorted_ids, expert_ids, num_post_padded, top
              block_m, _W_MXFP4, 32, _ACTS[activation] if silu_mul else 0)
 
 
+@_define("moe_permute_bf16(Tensor x, Tensor(a!) y, Tensor slot_pos, Tensor sorted_ids, "
+         "Tensor num_post_padded, int top_k) -> ()")
+def moe_permute_bf16(x, y, slot_pos, sorted_ids, num_post_padded, top_k):
+    """y[slot_pos[t * top_k + j]] = x[t]; padding rows below num_post_padded = 0."""
+    _check(x.dtype == torch.bfloat16 and y.dtype == torch.bfloat16 and x.dim() == 2 and y.dim() == 2
+           and x.size(1) == y.size(1) and x.stride(1) == 1 and y.stride(1) == 1,
+           "x, y bf16 [rows, K] with contiguous rows")
+    _check(all(t.dtype == torch.int32 and t.is_contiguous()
+               for t in (slot_pos, sorted_ids, num_post_padded)), "routing tensors must be int32")
+    _check(slot_pos.numel() >= x.size(0) * top_k and sorted_ids.numel() >= y.size(0),
+           "slot_pos / sorted_ids too short")
+    with torch.cuda.device(x.device):
+        _lib.call("strix_moe_permute_bf16", x.data_ptr(), y.data_ptr(), slot_pos.data_ptr(),
+                  sorted_ids.data_ptr(), num_post_padded.data_ptr(), x.size(0), y.size(0), x.size(1),
+                  top_k, x.stride(0), y.stride(0), _stream())
+
+
+@_define("moe_gemm_mxfp4_sorted(Tensor(a!) c, Tensor a, Tensor b, Tensor scales, Tensor sorted_ids, "
+         "Tensor expert_ids, Tensor num_post_padded, Tensor? topk_weights, int num_valid, "
+         "int block_m, bool silu_mul=False, str activation='silu', bool c_sorted=False) -> ()")
+def moe_gemm_mxfp4_sorted(c, a, b, scales, sorted_ids, expert_ids, num_post_padded, topk_weights,
+                          num_valid, block_m, silu_mul=False, activation="silu", c_sorted=False):
+    _check(a.dtype == torch.bfloat16 and c.dtype == torch.bfloat16 and b.dtype == torch.uint8
+           and scales.dtype == torch.uint8, "a, c bf16; b uint8; scale must be uint8 (e8m0)")
+    _check(a.dim() == 2 and b.dim() == 3 and c.dim() == 2, "bad ranks")
+    e, n, kh = b.shape
+    k = kh * 2
+    _check(a.size(1) == k and c.size(1) == (n // 2 if silu_mul else n)
+           and tuple(scales.shape) == (e, n, k // 32), "shape mismatch")
+    _check(a.stride(1) == 1 and b.stride(2) == 1 and c.stride(1) == 1 and scales.stride(2) == 1,
+           "last dims must be contiguous")
+    _check(activation in _ACTS, f"activation must be silu or gelu_tanh, got {activation}")
+    sorted_len = sorted_ids.numel() // block_m * block_m
+    _check(a.size(0) >= sorted_len and c.size(0) >= (sorted_len if c_sorted else num_valid),
+           "a / c have too few rows")
+    _check(expert_ids.numel() * block_m >= sorted_len, f"expert_ids too short for block_m {block_m}")
+    if topk_weights is not None:
+        _check(topk_weights.dtype == torch.float32 and topk_weights.is_contiguous()
+               and topk_weights.numel() >= num_valid, "topk_weights must be contiguous fp32 [num_valid]")
+    with torch.cuda.device(c.device):
+        _lib.call("strix_moe_gemm_mxfp4_sorted", c.data_ptr(), a.data_ptr(), b.data_ptr(),
+                  scales.data_ptr(), sorted_ids.data_ptr(), expert_ids.data_ptr(),
+                  num_post_padded.data_ptr(), _ptr(topk_weights), num_valid, n, k, a.stride(0),
+                  c.stride(0), b.stride(0), b.stride(1), scales.stride(0), scales.stride(1),
+                  sorted_len, block_m, _ACTS[activation] if silu_mul else 0, int(c_sorted), _stream())
+
+
 def _dense_fake(rows_from, w_from):
     def fake(*args, **kw):
         x, w = args[rows_from], args[w_from]

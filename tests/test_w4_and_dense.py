@@ -310,3 +310,62 @@ def test_w8a8_wmma_gemm_reference_schema(n, k, m, scale_form):
     close_to_peak(out, exact, 1e-2)
     # and the reference's looser statement against unquantised activations
     close_to_peak(out, x.float() @ (w_i8.float() * full).t(), 6e-2)
+
+
+# ------------------------------------------------- MXFP4 on tcgen05 (sorted layout)
+
+@pytest.mark.parametrize("tokens", [1, 40, 300])
+@pytest.mark.parametrize("gemm,activation,n,k", [("w13", "silu", 5760, 2880), ("w13", "gelu_tanh", 512, 256),
+                                                 ("w2", "silu", 2880, 2880), ("w2", "silu", 256, 128)])
+def test_moe_gemm_mxfp4_sorted(tokens, gemm, activation, n, k):
+    """The tensor-core kernel (m-blocks of 128 tokens, activations in sorted order)
+    against the gathered oracle; the permute kernel bit for bit."""
+    import libstrix_b200 as strix
+    from libstrix_b200 import _lib
+
+    g = torch.Generator().manual_seed(0)
+    w = torch.randint(0, 256, (E, n, k // 2), generator=g, dtype=torch.uint8)
+    s = torch.randint(118, 126, (E, n, k // 32), generator=g, dtype=torch.uint8)
+    s[0, :4, :2] = 0
+    b = G.mxfp4_dequant(w, s)
+    ids = routing(tokens)
+    slots = tokens * TOP_K
+    sorted_ids, expert_ids, num_post, slot_pos = strix.moe.align_with_positions(ids.to(DEV), 128, E)
+    cap = sorted_ids.numel()
+    pos = sorted_ids.cpu().long()
+    live = pos < slots
+    n_post = int(num_post.item())
+    if gemm == "w13":
+        a = torch.randn(tokens, k, generator=g).bfloat16()
+        a_sorted = torch.full((cap, k), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.moe_permute_bf16(a.to(DEV), a_sorted, slot_pos, sorted_ids, num_post, TOP_K)
+        got = a_sorted.cpu()
+        assert torch.equal(got[live].view(torch.int16), a[pos[live] // TOP_K].view(torch.int16))
+        pad = (~live) & (torch.arange(cap) < n_post)
+        assert not got[pad].view(torch.int16).any()
+        a_topk, weights = TOP_K, None
+    else:
+        a = torch.randn(slots, k, generator=g).bfloat16()
+        a_sorted = torch.zeros(cap, k, dtype=torch.bfloat16)
+        a_sorted[live] = a[pos[live]]
+        a_sorted = a_sorted.to(DEV)
+        a_topk, weights = 1, torch.rand(tokens, TOP_K, generator=g)
+    c_sorted = gemm == "w13"
+    out_cols = n // 2 if gemm == "w13" else n
+    c = torch.full((cap if c_sorted else slots, out_cols), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.moe_gemm_mxfp4_sorted(c, a_sorted, w.to(DEV), s.to(DEV), sorted_ids, expert_ids, num_post,
+                              None if weights is None else weights.flatten().to(DEV), slots, 128,
+                              gemm == "w13", activation, c_sorted)
+    torch.cuda.synchronize()
+    import ctypes
+    flag = ctypes.c_int32(-1)
+    assert _lib.load().strix_umma_status(ctypes.byref(flag)) == 0 and flag.value == 0
+    ref = M.grouped_reference(a, b, ids, a_topk, weights)
+    if gemm == "w13":
+        ref = M.gate_mul(ref, activation)
+    out = c.float().cpu()
+    if c_sorted:
+        by_slot = torch.full((slots, out_cols), float("nan"))
+        by_slot[pos[live]] = out[live]
+        out = by_slot
+    rms_check(out, ref, 2e-2)
