@@ -16,8 +16,15 @@
 //                         256-column TMEM buffers;
 //   epilogue (4 warps)    one token row per thread: act(gate) * up on adjacent
 //                         columns, or x routing weight; contiguous output rows.
-// One ring position holds the token tile, the packed weights and the decoded
-// tile; its single commit frees all three. Every mbarrier wait is bounded.
+// The decode is the expensive part (about 300 instructions per weight row and K
+// block), so a decoded tile serves TWO m-blocks where it can: consecutive
+// m-blocks of one expert form a unit of 256 tokens, whose halves accumulate in
+// the two 256-column TMEM buffers from the same decoded tile (a lone m-block is a
+// unit of one). Two rings: three stages of (two token tiles + packed weights),
+// 40 KB each, and two decoded operand tiles of 32 KB that alternate between the
+// transform warps and the MMAs. A K block's single tcgen05.commit frees its stage
+// for the producer and, two K blocks later, its decoded tile for the transform
+// warps. Every mbarrier wait is bounded.
 #include <cstdlib>
 
 #include "tma.cuh"
@@ -33,15 +40,15 @@ using namespace umma;
 constexpr int kMxTok = 128, kMxCols = 256, kMxKB = 64;       // tile: tokens x weight rows x K
 constexpr int kMxTransformWarps = 8, kMxEpilogueWarps = 4;
 constexpr int kMxThreads = (4 + kMxTransformWarps + kMxEpilogueWarps) * 32;
-constexpr int kMxStages = 3;
+constexpr int kMxStages = 3, kMxDecoded = 2;
 constexpr int kMxMaxMBlocks = 2048;
 
 struct MxLayout {
   static constexpr int kABytes = kMxTok * kMxKB * 2;          // 16 KB of bf16 token rows
   static constexpr int kRawBytes = kMxCols * kMxKB / 2;       // 8 KB of packed weights
   static constexpr int kBBytes = kMxCols * kMxKB * 2;         // 32 KB of decoded weights
-  static constexpr int kStageBytes = kABytes + kRawBytes + kBBytes;
-  static constexpr int kSmem = 1024 + kMxStages * kStageBytes + 256;
+  static constexpr int kStageBytes = 2 * kABytes + kRawBytes; // what the TMA fills: two token tiles + weights
+  static constexpr int kSmem = 1024 + kMxStages * kStageBytes + kMxDecoded * kBBytes + 256;
 };
 
 struct MxArgs {
@@ -94,7 +101,9 @@ __global__ void __launch_bounds__(kMxThreads, 1) moe_gemm_mxfp4_umma_kernel(
   extern __shared__ uint8_t raw_smem[];
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
                                              ~uintptr_t(1023));
-  __shared__ __align__(8) uint64_t full_bar[S], bready_bar[S], done_bar[S], tfull_bar[2], tempty_bar[2];
+  __shared__ __align__(8) uint64_t full_bar[S], bready_bar[S], done_bar[S], tfull_bar, tempty_bar[2];
+  __shared__ int s_unit[kMxMaxMBlocks];   // first m-block | (m-blocks in the unit << 16)
+  __shared__ int s_units;
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int s_abort;
   __shared__ int s_expert[kMxMaxMBlocks];
@@ -104,16 +113,29 @@ __global__ void __launch_bounds__(kMxThreads, 1) moe_gemm_mxfp4_umma_kernel(
   const int half_n = p.N / 2;
   const int nkb = p.K / kMxKB;
   const int m_blocks = *p.num_post / kMxTok;
-  const int total_items = m_blocks * p.n_tiles;
   const int tile_rows = gate ? kMxCols / 2 : kMxCols;
   for (int i = tid; i < m_blocks && i < kMxMaxMBlocks; i += kMxThreads) s_expert[i] = p.expert_ids[i];
+  __syncthreads();
+  if (tid == 0) {
+    // units: pairs of consecutive m-blocks of one expert, else single m-blocks
+    int n = 0;
+    for (int i = 0; i < m_blocks;) {
+      const int e = s_expert[i];
+      if (e < 0) { ++i; continue; }
+      const int cnt = (i + 1 < m_blocks && s_expert[i + 1] == e) ? 2 : 1;
+      s_unit[n++] = i | (cnt << 16);
+      i += cnt;
+    }
+    s_units = n;
+  }
   if (tid == 0) {
     for (int i = 0; i < S; ++i) {
       mbar_init(&full_bar[i], 1);
       mbar_init(&bready_bar[i], kMxTransformWarps);
       mbar_init(&done_bar[i], 1);
     }
-    for (int i = 0; i < 2; ++i) mbar_init(&tfull_bar[i], 1), mbar_init(&tempty_bar[i], kMxEpilogueWarps);
+    mbar_init(&tfull_bar, 1);
+    for (int i = 0; i < 2; ++i) mbar_init(&tempty_bar[i], kMxEpilogueWarps);
     s_abort = 0;
     fence_mbar_init();
   }
@@ -123,10 +145,7 @@ __global__ void __launch_bounds__(kMxThreads, 1) moe_gemm_mxfp4_umma_kernel(
   tc_fence_after_sync();
   const uint32_t tmem = tmem_slot;
   const uint32_t ring_s = smem_u32(ring);
-  auto next_valid = [&](int item) {
-    while (item < total_items && s_expert[item / p.n_tiles] < 0) item += gridDim.x;
-    return item;
-  };
+  const int total_items = s_units * p.n_tiles;
 
   if (warp == 0) {
     // ------------------------------------------------------------- producer
@@ -135,9 +154,9 @@ __global__ void __launch_bounds__(kMxThreads, 1) moe_gemm_mxfp4_umma_kernel(
       tma::prefetch_map(&map_w);
       int t = 0;
       bool dead = false;
-      for (int item = next_valid(blockIdx.x); item < total_items && !dead;
-           item = next_valid(item + gridDim.x)) {
-        const int mb = item / p.n_tiles, nt = item - mb * p.n_tiles;
+      for (int item = blockIdx.x; item < total_items && !dead; item += gridDim.x) {
+        const int unit = s_unit[item / p.n_tiles], nt = item % p.n_tiles;
+        const int mb = unit & 0xffff, cnt = unit >> 16;
         const int expert = s_expert[mb];
         for (int kb = 0; kb < nkb; ++kb, ++t) {
           const int s = t % S;
@@ -146,9 +165,11 @@ __global__ void __launch_bounds__(kMxThreads, 1) moe_gemm_mxfp4_umma_kernel(
             break;
           }
           const uint32_t st = ring_s + s * L::kStageBytes;
-          tma::mbar_expect_tx(&full_bar[s], L::kABytes + L::kRawBytes);
+          tma::mbar_expect_tx(&full_bar[s], cnt * L::kABytes + L::kRawBytes);
           tma::load_2d(st, &map_a, kb * kMxKB * 2, mb * kMxTok, &full_bar[s]);
-          tma::load_4d(st + L::kABytes, &map_w, kb * (kMxKB / 2), 0, nt * tile_rows, expert,
+          if (cnt == 2)
+            tma::load_2d(st + L::kABytes, &map_a, kb * kMxKB * 2, (mb + 1) * kMxTok, &full_bar[s]);
+          tma::load_4d(st + 2 * L::kABytes, &map_w, kb * (kMxKB / 2), 0, nt * tile_rows, expert,
                        &full_bar[s]);
         }
       }
@@ -161,14 +182,13 @@ __global__ void __launch_bounds__(kMxThreads, 1) moe_gemm_mxfp4_umma_kernel(
       const uint32_t lo0 = smem_desc_lo(ring_s);
       int t = 0, li = 0;
       bool dead = false;
-      for (int item = next_valid(blockIdx.x); item < total_items && !dead;
-           item = next_valid(item + gridDim.x), ++li) {
-        const int buf = li & 1;
-        if (!mbar_wait(&tempty_bar[buf], ((li >> 1) & 1) ^ 1)) {   // the epilogue drained it
+      for (int item = blockIdx.x; item < total_items && !dead; item += gridDim.x, ++li) {
+        const int cnt = s_unit[item / p.n_tiles] >> 16;
+        // both accumulators belong to this item: the epilogue must have drained them
+        if (!mbar_wait(&tempty_bar[0], (li & 1) ^ 1) || !mbar_wait(&tempty_bar[1], (li & 1) ^ 1)) {
           dead = true;
           break;
         }
-        const uint32_t d = tmem + buf * kMxCols;
         for (int kb = 0; kb < nkb; ++kb, ++t) {
           const int s = t % S;
           if (!mbar_wait(&bready_bar[s], (t / S) & 1) || s_abort) {   // tokens landed, weights decoded
@@ -176,16 +196,19 @@ __global__ void __launch_bounds__(kMxThreads, 1) moe_gemm_mxfp4_umma_kernel(
             break;
           }
           tc_fence_after_sync();
-          const uint32_t a_lo = lo0 + s * (L::kStageBytes >> 4);
-          const uint32_t b_lo = a_lo + ((L::kABytes + L::kRawBytes) >> 4);
-          if (kb == 0) mma_ss_lo<KIND_F16, false>(d, a_lo, b_lo, idesc);
-          else mma_ss_lo<KIND_F16, true>(d, a_lo, b_lo, idesc);
-          mma_ss_lo<KIND_F16, true>(d, a_lo + 2, b_lo + 2, idesc);
-          mma_ss_lo<KIND_F16, true>(d, a_lo + 4, b_lo + 4, idesc);
-          mma_ss_lo<KIND_F16, true>(d, a_lo + 6, b_lo + 6, idesc);
+          const uint32_t b_lo = lo0 + ((S * L::kStageBytes + (t % kMxDecoded) * L::kBBytes) >> 4);
+          for (int h = 0; h < cnt; ++h) {             // the unit's m-blocks share the decoded tile
+            const uint32_t a_lo = lo0 + ((s * L::kStageBytes + h * L::kABytes) >> 4);
+            const uint32_t d = tmem + h * kMxCols;
+            if (kb == 0) mma_ss_lo<KIND_F16, false>(d, a_lo, b_lo, idesc);
+            else mma_ss_lo<KIND_F16, true>(d, a_lo, b_lo, idesc);
+            mma_ss_lo<KIND_F16, true>(d, a_lo + 2, b_lo + 2, idesc);
+            mma_ss_lo<KIND_F16, true>(d, a_lo + 4, b_lo + 4, idesc);
+            mma_ss_lo<KIND_F16, true>(d, a_lo + 6, b_lo + 6, idesc);
+          }
           mma_commit(&done_bar[s]);
         }
-        if (!dead) mma_commit(&tfull_bar[buf]);
+        if (!dead) mma_commit(&tfull_bar);
       }
       if (dead) atomicExch(p.status, 1), s_abort = 1;
     }
@@ -194,10 +217,9 @@ __global__ void __launch_bounds__(kMxThreads, 1) moe_gemm_mxfp4_umma_kernel(
     const int r = tid - 128;                          // row of the tile, 0..255
     int t = 0;
     bool dead = false;
-    for (int item = next_valid(blockIdx.x); item < total_items && !dead;
-         item = next_valid(item + gridDim.x)) {
-      const int mb = item / p.n_tiles, nt = item - mb * p.n_tiles;
-      const int expert = s_expert[mb];
+    for (int item = blockIdx.x; item < total_items && !dead; item += gridDim.x) {
+      const int nt = item % p.n_tiles;
+      const int expert = s_expert[s_unit[item / p.n_tiles] & 0xffff];
       // a ragged last tile: rows past the matrix arrive as zeros (TMA) and take scale 0
       const int orow = nt * tile_rows + (gate ? (r >> 1) : r);
       const bool row_ok = orow < (gate ? half_n : p.N);
@@ -208,14 +230,19 @@ __global__ void __launch_bounds__(kMxThreads, 1) moe_gemm_mxfp4_umma_kernel(
         const int s = t % S;
         const uint32_t scb = sc_next;               // the two scale bytes of this K block
         if (kb + 1 < nkb && row_ok) sc_next = uint32_t(sc[2 * kb + 2]) | (uint32_t(sc[2 * kb + 3]) << 8);
-        const bool ok = mbar_wait(&full_bar[s], (t / S) & 1);
+        bool ok = mbar_wait(&full_bar[s], (t / S) & 1);
+        // the decoded tile t % 2 was last read by the MMAs of K block t - 2
+        if (t >= kMxDecoded) {
+          const int u = t - kMxDecoded;
+          ok = mbar_wait(&done_bar[u % S], (u / S) & 1) && ok;
+        }
         if (__any_sync(0xffffffffu, !ok || s_abort != 0)) {
           dead = true;
           break;
         }
         const uint8_t* st = ring + s * L::kStageBytes;
-        const uint4* src = reinterpret_cast<const uint4*>(st + L::kABytes + r * (kMxKB / 2));
-        uint8_t* dst = ring + s * L::kStageBytes + L::kABytes + L::kRawBytes;
+        const uint4* src = reinterpret_cast<const uint4*>(st + 2 * L::kABytes + r * (kMxKB / 2));
+        uint8_t* dst = ring + S * L::kStageBytes + (t % kMxDecoded) * L::kBBytes;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {               // 32 elements = one scale group each
           const uint4 x = src[h];
@@ -243,53 +270,65 @@ __global__ void __launch_bounds__(kMxThreads, 1) moe_gemm_mxfp4_umma_kernel(
     const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
     int li = 0;
     bool dead = false;
-    for (int item = next_valid(blockIdx.x); item < total_items && !dead;
-         item = next_valid(item + gridDim.x), ++li) {
-      const int mb = item / p.n_tiles, nt = item - mb * p.n_tiles;
-      const int buf = li & 1;
-      const int64_t sid_raw = p.sorted_ids[mb * kMxTok + tok];
-      const int sid = (sid_raw >= 0 && sid_raw < p.num_valid) ? int(sid_raw) : -1;
-      const float tw = (sid >= 0 && p.topk_w != nullptr) ? p.topk_w[sid] : 1.f;
-      const int crow = p.c_sorted ? mb * kMxTok + tok : sid;
-      __nv_bfloat16* cptr = p.c + int64_t(crow < 0 ? 0 : crow) * p.c_stride + nt * tile_rows;
-      const bool ok = mbar_wait(&tfull_bar[buf], (li >> 1) & 1);
+    for (int item = blockIdx.x; item < total_items && !dead; item += gridDim.x, ++li) {
+      const int unit = s_unit[item / p.n_tiles], nt = item % p.n_tiles;
+      const int mb0 = unit & 0xffff, cnt = unit >> 16;
+      int sid[2], crow[2];
+      float tw[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int64_t raw = h < cnt ? p.sorted_ids[(mb0 + h) * kMxTok + tok] : -1;
+        sid[h] = (raw >= 0 && raw < p.num_valid) ? int(raw) : -1;
+        tw[h] = (sid[h] >= 0 && p.topk_w != nullptr) ? p.topk_w[sid[h]] : 1.f;
+        crow[h] = h < cnt ? (p.c_sorted ? (mb0 + h) * kMxTok + tok : sid[h]) : -1;
+      }
+      const bool ok = mbar_wait(&tfull_bar, li & 1);
       if (__any_sync(0xffffffffu, !ok || s_abort != 0)) {
         dead = true;
         break;
       }
       tc_fence_after_sync();
 #pragma unroll 1
-      for (int c0 = 0; c0 < kMxCols; c0 += 32) {
-        uint32_t rr[32];
-        tmem_ld_32x32(tmem + lane_base + buf * kMxCols + c0, rr);
-        tmem_ld_wait();
-        if (c0 + 32 == kMxCols) {
-          tc_fence_before_sync();
+      for (int h = 0; h < 2; ++h) {
+        __nv_bfloat16* cptr = p.c + int64_t(crow[h] < 0 ? 0 : crow[h]) * p.c_stride + nt * tile_rows;
+        if (h >= cnt) {            // a unit of one: the second accumulator was not used
           __syncwarp();
-          if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+          if (lane == 0) mbar_arrive(&tempty_bar[h]);
+          continue;
         }
-        // output columns of this chunk: 16 under the gate, else 32; past the matrix: nothing
-        const int out_col = nt * tile_rows + (gate ? c0 / 2 : c0);
-        if (crow < 0 || out_col >= (gate ? half_n : p.N)) continue;
-        if (gate) {
-          uint32_t o[8];
-#pragma unroll
-          for (int i = 0; i < 16; i += 2) {
-            const float v0 = mx_gate(__uint_as_float(rr[2 * i]), p.gate_act) * __uint_as_float(rr[2 * i + 1]);
-            const float v1 = mx_gate(__uint_as_float(rr[2 * i + 2]), p.gate_act) * __uint_as_float(rr[2 * i + 3]);
-            o[i >> 1] = pack_bf16x2(v0, v1);
+#pragma unroll 1
+        for (int c0 = 0; c0 < kMxCols; c0 += 32) {
+          uint32_t rr[32];
+          tmem_ld_32x32(tmem + lane_base + h * kMxCols + c0, rr);
+          tmem_ld_wait();
+          if (c0 + 32 == kMxCols) {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty_bar[h]);
           }
-          uint4* dstp = reinterpret_cast<uint4*>(cptr + c0 / 2);
-          dstp[0] = make_uint4(o[0], o[1], o[2], o[3]);
-          dstp[1] = make_uint4(o[4], o[5], o[6], o[7]);
-        } else {
-          uint32_t o[16];
+          // output columns of this chunk: 16 under the gate, else 32; past the matrix: nothing
+          const int out_col = nt * tile_rows + (gate ? c0 / 2 : c0);
+          if (crow[h] < 0 || out_col >= (gate ? half_n : p.N)) continue;
+          if (gate) {
+            uint32_t o[8];
 #pragma unroll
-          for (int i = 0; i < 32; i += 2)
-            o[i >> 1] = pack_bf16x2(__uint_as_float(rr[i]) * tw, __uint_as_float(rr[i + 1]) * tw);
-          uint4* dstp = reinterpret_cast<uint4*>(cptr + c0);
+            for (int i = 0; i < 16; i += 2) {
+              const float v0 = mx_gate(__uint_as_float(rr[2 * i]), p.gate_act) * __uint_as_float(rr[2 * i + 1]);
+              const float v1 = mx_gate(__uint_as_float(rr[2 * i + 2]), p.gate_act) * __uint_as_float(rr[2 * i + 3]);
+              o[i >> 1] = pack_bf16x2(v0, v1);
+            }
+            uint4* dstp = reinterpret_cast<uint4*>(cptr + c0 / 2);
+            dstp[0] = make_uint4(o[0], o[1], o[2], o[3]);
+            dstp[1] = make_uint4(o[4], o[5], o[6], o[7]);
+          } else {
+            uint32_t o[16];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) dstp[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+            for (int i = 0; i < 32; i += 2)
+              o[i >> 1] = pack_bf16x2(__uint_as_float(rr[i]) * tw[h], __uint_as_float(rr[i + 1]) * tw[h]);
+            uint4* dstp = reinterpret_cast<uint4*>(cptr + c0);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dstp[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+          }
         }
       }
     }

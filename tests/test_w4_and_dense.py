@@ -318,6 +318,18 @@ def test_w8a8_wmma_gemm_reference_schema(n, k, m, scale_form):
 @pytest.mark.parametrize("gemm,activation,n,k", [("w13", "silu", 5760, 2880), ("w13", "gelu_tanh", 512, 256),
                                                  ("w2", "silu", 2880, 2880), ("w2", "silu", 256, 128)])
 def test_moe_gemm_mxfp4_sorted(tokens, gemm, activation, n, k):
+    _mxfp4_sorted_case(tokens, gemm, activation, n, k)
+
+
+@pytest.mark.parametrize("gemm,activation,n,k", [("w13", "silu", 512, 256), ("w2", "silu", 256, 128),
+                                                 ("w13", "silu", 5760, 2880)])
+def test_moe_gemm_mxfp4_sorted_units_of_two_m_blocks(gemm, activation, n, k):
+    """1200 tokens over 16 experts: about 300 rows per expert = a pair of
+    m-blocks sharing each decoded weight tile plus a single one."""
+    _mxfp4_sorted_case(1200, gemm, activation, n, k)
+
+
+def _mxfp4_sorted_case(tokens, gemm, activation, n, k):
     """The tensor-core kernel (m-blocks of 128 tokens, activations in sorted order)
     against the gathered oracle; the permute kernel bit for bit."""
     import libstrix_b200 as strix
