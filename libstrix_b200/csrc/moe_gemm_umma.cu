@@ -7,9 +7,11 @@
 // that are already laid out in sorted order: row p of `a` (and of its scales)
 // belongs to sorted position p, so an m-block's tokens are block_m consecutive
 // rows and one TMA box fetches them. The quantiser writes that layout
-// (strix_moe_act_quant_fp8_sorted), the gate-up GEMM can write its output in it
-// too, and the down GEMM scatters to slot order for the combine. What differs
-// from moe_gemm.cu is the machine mapping:
+// (strix_moe_act_quant_fp8_scatter / _sorted), the gate-up GEMM can write its
+// output in it too, and the down GEMM scatters to slot order for the combine.
+// Two kernels: this one for m-blocks of 16..64 tokens (the weight stream sets the
+// pace), and the wide-tile kernel further down for m-blocks of 128 tokens. What
+// differs from moe_gemm.cu is the machine mapping:
 //
 //   * operands swap roles: a tile of 128 expert-weight rows is the MMA's A (M =
 //     128) and the m-block's tokens are B (N = block_m, 16..128), so a ragged
@@ -20,17 +22,19 @@
 //     in a fixed stride; three roles run decoupled through mbarriers:
 //       producer (1 thread)  two TMA boxes per K block - 128 weight rows (a 4-d
 //                            box, which also interleaves the gate and up rows)
-//                            and the m-block's token rows - into an 8..5-stage
-//                            ring in the 128-byte-swizzled K-major layout the
-//                            MMA descriptors expect; they complete the stage's
+//                            and the m-block's token rows - into a ring of up to
+//                            12 stages (what shared memory and TMEM leave) in
+//                            the 128-byte-swizzled K-major layout the MMA
+//                            descriptors expect; they complete the stage's
 //                            barrier by byte count;
 //       metadata (1 warp)    a few items ahead: the tokens' slot ids, routing
 //                            weights and activation scales and the tile's weight
 //                            block scales, into shared memory;
-//       issuer (1 thread)    four K=32 MMAs per 128-wide K block into one of the
-//                            TMEM accumulator buffers, then tcgen05.commit to
-//                            free the ring stage and to publish the buffer;
-//       consumers (4 warps)  tcgen05.ld the K block's partial sums and fold them
+//       issuer (1 thread)    four K=32 MMAs per 128-wide K block into the ring
+//                            position's TMEM accumulator, then ONE tcgen05.commit
+//                            that frees the stage and publishes the sums;
+//       consumers (8-16 warps, 2-4 per TMEM lane quadrant, each a share of the
+//                            tokens) tcgen05.ld the K block's partial sums and fold them
 //                            into fp32 registers with the block's weight scale
 //                            times the token's activation scale (the scales are
 //                            not powers of two, so they cannot ride the MMA);

@@ -142,10 +142,11 @@ _MOE_ROWS = [
         {"dtype": "bf16", "activation_dtype": "fp8_e4m3", "weight_dtype": "fp8_e4m3",
          "weight_bits": 8, "quant": "fp8", "group_size": (0, 128), "layout": "sorted",
          "block_m": (16, 32, 64, 128), "silu_mul": (True, False), "activation": _GATES},
-        {"tile": "128 weight rows x block_m tokens, K blocks of 128",
-         "pipeline": "TMA producer thread, issuing thread, metadata warp, 4 folding warps; "
-                     "8..5-stage ring, up to 8 TMEM accumulators, persistent grid",
-         "bound": "hbm (weight stream) at small token counts"},
+        {"tile": "128 weight rows x block_m tokens (block_m <= 64); 128 tokens x 256 weight rows "
+                 "(block_m 128); K blocks of 128",
+         "pipeline": "TMA producer thread, issuing thread, metadata warp, 8-16 folding warps; "
+                     "one commit per K block, persistent grid",
+         "bound": "hbm (weight stream) at small token counts, L2 -> shared memory at 4k tokens"},
     ),
     Kernel("moe_act_quant_fp8_sorted", "moe_act_quant_fp8",
            "e4m3 activations per (row, 128 group) written in sorted order (row p = token "
