@@ -344,6 +344,28 @@ int strix_moe_align_pos(const int32_t* topk_ids, int32_t* sorted_ids, int32_t* e
                         int64_t experts, int64_t block_m, int64_t sorted_capacity,
                         int64_t expert_capacity, strix_stream_t stream);
 
+/* strix_moe_align_pos that also writes counts[e] = slots routed to expert e
+ * (int32 [experts]; NULL to skip). With the destination rank as the "expert" and
+ * block_m = 1 this is the dispatch plan of the expert-parallel path. */
+int strix_moe_align_counts(const int32_t* topk_ids, int32_t* sorted_ids, int32_t* expert_ids,
+                           int32_t* num_post_padded, int32_t* slot_pos, int32_t* counts,
+                           int64_t numel, int64_t experts, int64_t block_m,
+                           int64_t sorted_capacity, int64_t expert_capacity,
+                           strix_stream_t stream);
+
+/* Expert-parallel helpers (no counterpart in the reference, which has no EP).
+ * strix_ep_pack: send[i] = x[order[i] / top_k] (bf16 rows of `hidden`), meta[i] =
+ * (topk_ids[order[i]] % experts_per_rank as float, topk_weights[order[i]]).
+ * strix_moe_sum_gather: out[t] = sum_j rows[pos[t * top_k + j]] in fp32, one bf16
+ * rounding (negative positions are skipped). */
+int strix_ep_pack(const void* x, void* send, float* meta, const int32_t* order,
+                  const int32_t* topk_ids, const float* topk_weights, int64_t slots,
+                  int64_t hidden, int64_t top_k, int64_t experts_per_rank, int64_t x_stride,
+                  int64_t send_stride, strix_stream_t stream);
+int strix_moe_sum_gather(const void* rows, const int32_t* pos, void* out, int64_t tokens,
+                         int64_t top_k, int64_t hidden, int64_t row_st, int64_t out_st,
+                         strix_stream_t stream);
+
 /* The sorted-layout e4m3 quantiser by scatter: token row t of x [tokens, k] is
  * quantised once and stored at the sorted positions slot_pos[t * top_k + j] of
  * its top_k slots; padding slots below *num_post_padded get zeros with scale 1.

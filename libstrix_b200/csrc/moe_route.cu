@@ -91,7 +91,8 @@ constexpr int kAlignThreads = 256;
 __global__ void __launch_bounds__(kAlignThreads) moe_align_kernel(
     const int32_t* __restrict__ topk_ids, int32_t* __restrict__ sorted_ids,
     int32_t* __restrict__ expert_ids, int32_t* __restrict__ num_post, int numel, int experts,
-    int block_m, int cap, int cap_blocks, int32_t* __restrict__ slot_pos) {
+    int block_m, int cap, int cap_blocks, int32_t* __restrict__ slot_pos,
+    int32_t* __restrict__ counts) {
   extern __shared__ int s_count[];            // [experts]
   __shared__ int s_warp[kAlignThreads / 32];
   __shared__ int s_base;
@@ -126,6 +127,7 @@ __global__ void __launch_bounds__(kAlignThreads) moe_align_kernel(
     return;
   }
   const int count = s_count[e];
+  if (counts != nullptr && tid == 0) counts[e] = count;
   const int padded = (count + block_m - 1) / block_m * block_m;
   for (int i = tid; i < padded / block_m; i += kAlignThreads)
     if (base / block_m + i < cap_blocks) expert_ids[base / block_m + i] = e;
@@ -331,10 +333,90 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(
   *reinterpret_cast<uint4*>(out + t * out_st + h) = o;
 }
 
+// out[t, h] = sum_j rows[pos[t * top_k + j], h]: the combine over rows that lie in
+// another order (expert-parallel: the order the result rows came back in).
+__global__ void __launch_bounds__(256) moe_sum_gather_kernel(
+    const uint16_t* __restrict__ rows, int64_t row_st, const int32_t* __restrict__ pos,
+    uint16_t* __restrict__ out, int64_t out_st, int tokens, int top_k, int hidden8) {
+  const int64_t idx = int64_t(blockIdx.x) * 256 + threadIdx.x;
+  if (idx >= int64_t(tokens) * hidden8) return;
+  const int64_t t = idx / hidden8;
+  const int h = int(idx % hidden8) * 8;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int j = 0; j < top_k; ++j) {
+    const int64_t r = pos[t * top_k + j];
+    if (r < 0) continue;
+    const uint4 w = *reinterpret_cast<const uint4*>(rows + r * row_st + h);
+    const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      acc[2 * i] += bf16_lo(ws[i]);
+      acc[2 * i + 1] += bf16_hi(ws[i]);
+    }
+  }
+  uint4 o;
+  o.x = pack_bf16x2(acc[0], acc[1]);
+  o.y = pack_bf16x2(acc[2], acc[3]);
+  o.z = pack_bf16x2(acc[4], acc[5]);
+  o.w = pack_bf16x2(acc[6], acc[7]);
+  *reinterpret_cast<uint4*>(out + t * out_st + h) = o;
+}
+
+// Expert-parallel dispatch buffers: row i of the send buffer is the token row of
+// slot order[i]; meta[i] = (expert id modulo experts_per_rank, routing weight).
+__global__ void __launch_bounds__(256) ep_pack_kernel(
+    const uint4* __restrict__ x, int64_t x_st16, uint4* __restrict__ send, int64_t send_st16,
+    float2* __restrict__ meta, const int32_t* __restrict__ order, const int32_t* __restrict__ topk_ids,
+    const float* __restrict__ topk_w, int64_t slots, int chunks, int top_k, int experts_per_rank) {
+  const int64_t idx = int64_t(blockIdx.x) * 256 + threadIdx.x;
+  const int64_t i = idx / chunks;
+  if (i >= slots) return;
+  const int ch = int(idx % chunks);
+  const int slot = order[i];
+  send[i * send_st16 + ch] = x[int64_t(slot / top_k) * x_st16 + ch];
+  if (ch == 0) meta[i] = make_float2(float(topk_ids[slot] % experts_per_rank), topk_w[slot]);
+}
+
 }  // namespace
 }  // namespace strix
 
 using namespace strix;
+
+extern "C" int strix_moe_sum_gather(const void* rows, const int32_t* pos, void* out, int64_t tokens,
+                                    int64_t top_k, int64_t hidden, int64_t row_st, int64_t out_st,
+                                    strix_stream_t stream) {
+  STRIX_CHECK(tokens >= 0 && top_k >= 1 && hidden > 0 && hidden % 8 == 0,
+              "hidden must be a multiple of 8");
+  STRIX_CHECK(row_st % 8 == 0 && out_st % 8 == 0 && reinterpret_cast<uintptr_t>(rows) % 16 == 0 &&
+                  reinterpret_cast<uintptr_t>(out) % 16 == 0 && pos != nullptr,
+              "16-byte aligned rows required");
+  if (tokens == 0) return STRIX_OK;
+  const int64_t work = tokens * (hidden / 8);
+  moe_sum_gather_kernel<<<unsigned((work + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint16_t*>(rows), row_st, pos, static_cast<uint16_t*>(out), out_st,
+      int(tokens), int(top_k), int(hidden / 8));
+  return launch_status("moe_sum_gather");
+}
+
+extern "C" int strix_ep_pack(const void* x, void* send, float* meta, const int32_t* order,
+                             const int32_t* topk_ids, const float* topk_weights, int64_t slots,
+                             int64_t hidden, int64_t top_k, int64_t experts_per_rank,
+                             int64_t x_stride, int64_t send_stride, strix_stream_t stream) {
+  STRIX_CHECK(slots >= 0 && hidden > 0 && hidden % 8 == 0 && top_k >= 1 && experts_per_rank >= 1,
+              "hidden must be a multiple of 8");
+  STRIX_CHECK(x_stride % 8 == 0 && send_stride % 8 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 &&
+                  reinterpret_cast<uintptr_t>(send) % 16 == 0 &&
+                  reinterpret_cast<uintptr_t>(meta) % 8 == 0,
+              "16-byte aligned rows required");
+  if (slots == 0) return STRIX_OK;
+  const int chunks = int(hidden / 8);
+  const int64_t work = slots * chunks;
+  ep_pack_kernel<<<unsigned((work + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), x_stride / 8, static_cast<uint4*>(send), send_stride / 8,
+      reinterpret_cast<float2*>(meta), order, topk_ids, topk_weights, slots, chunks, int(top_k),
+      int(experts_per_rank));
+  return launch_status("ep_pack");
+}
 
 extern "C" int strix_moe_topk_softmax(const float* logits, int32_t* topk_ids, float* topk_weights,
                                       int64_t tokens, int64_t experts, int64_t top_k,
@@ -372,6 +454,15 @@ extern "C" int strix_moe_align_pos(const int32_t* topk_ids, int32_t* sorted_ids,
                                    int32_t* slot_pos, int64_t numel, int64_t experts,
                                    int64_t block_m, int64_t sorted_capacity,
                                    int64_t expert_capacity, strix_stream_t stream) {
+  return strix_moe_align_counts(topk_ids, sorted_ids, expert_ids, num_post_padded, slot_pos, nullptr,
+                                numel, experts, block_m, sorted_capacity, expert_capacity, stream);
+}
+
+extern "C" int strix_moe_align_counts(const int32_t* topk_ids, int32_t* sorted_ids,
+                                      int32_t* expert_ids, int32_t* num_post_padded,
+                                      int32_t* slot_pos, int32_t* counts, int64_t numel,
+                                      int64_t experts, int64_t block_m, int64_t sorted_capacity,
+                                      int64_t expert_capacity, strix_stream_t stream) {
   STRIX_CHECK(numel >= 0 && numel < (int64_t(1) << 30), "too many routed slots");
   STRIX_CHECK(experts >= 1 && experts <= 8192, "experts must be in 1..8192");
   STRIX_CHECK(block_m >= 1 && block_m <= 1024, "block_m must be in 1..1024");
@@ -382,7 +473,7 @@ extern "C" int strix_moe_align_pos(const int32_t* topk_ids, int32_t* sorted_ids,
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   moe_align_kernel<<<unsigned(experts + 1), kAlignThreads, size_t(experts) * sizeof(int), st>>>(
       topk_ids, sorted_ids, expert_ids, num_post_padded, int(numel), int(experts), int(block_m),
-      int(sorted_capacity), int(expert_capacity), slot_pos);
+      int(sorted_capacity), int(expert_capacity), slot_pos, counts);
   return launch_status("moe_align");
 }
 

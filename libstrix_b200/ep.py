@@ -48,6 +48,8 @@ def ep_dispatch_combine(
     world = dist.get_world_size(group)
     t, k = topk_ids.shape
     h = x.size(1)
+    if x.is_cuda and x.dtype == torch.bfloat16 and h % 8 == 0:
+        return _dispatch_combine_cuda(x, topk_weights, topk_ids, experts_per_rank, local_fn, group)
     order, send_counts = dispatch_plan(topk_ids, experts_per_rank, world)
     recv_counts = torch.empty_like(send_counts)
     dist.all_to_all_single(recv_counts, send_counts, group=group)
@@ -75,6 +77,61 @@ def ep_dispatch_combine(
     if combine is not None:
         return combine(slots)
     return slots.float().sum(1).to(x.dtype)
+
+
+def _dispatch_combine_cuda(x, topk_weights, topk_ids, experts_per_rank, local_fn, group):
+    """ep_dispatch_combine on the GPU with this library's kernels around the four
+    collectives: the plan (slots grouped by destination rank, its inverse and the
+    per-rank counts) is one launch of the align kernel with ranks as "experts" and
+    block_m = 1; one launch packs the send rows and the (local expert, weight)
+    pairs; the combine reads the returned rows through the inverse permutation."""
+    from . import _lib
+
+    world = dist.get_world_size(group)
+    t, k = topk_ids.shape
+    h = x.size(1)
+    n = t * k
+    dev = x.device
+    i32 = dict(dtype=torch.int32, device=dev)
+    ids = topk_ids.reshape(-1).to(torch.int32).contiguous()
+    wts = topk_weights.reshape(-1).to(torch.float32).contiguous()
+    dest = torch.div(ids, experts_per_rank, rounding_mode="floor").to(torch.int32)
+    order = torch.empty(max(n, 1), **i32)
+    blocks = torch.empty(max(n, 1), **i32)
+    n_post = torch.empty(1, **i32)
+    slot_pos = torch.empty(max(n, 1), **i32)
+    counts = torch.empty(world, **i32)
+    stream = torch.cuda.current_stream().cuda_stream
+    with torch.cuda.device(dev):
+        _lib.call("strix_moe_align_counts", dest.data_ptr(), order.data_ptr(), blocks.data_ptr(),
+                  n_post.data_ptr(), slot_pos.data_ptr(), counts.data_ptr(), n, world, 1,
+                  order.numel(), blocks.numel(), stream)
+    send_counts = counts.to(torch.int64)
+    recv_counts = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv_counts, send_counts, group=group)
+    send_splits, recv_splits = send_counts.tolist(), recv_counts.tolist()   # the one host sync
+    n_recv = sum(recv_splits)
+
+    send_x = torch.empty(n, h, dtype=torch.bfloat16, device=dev)
+    meta = torch.empty(n, 2, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.call("strix_ep_pack", x.data_ptr(), send_x.data_ptr(), meta.data_ptr(), order.data_ptr(),
+                  ids.data_ptr(), wts.data_ptr(), n, h, k, experts_per_rank, x.stride(0),
+                  send_x.stride(0), stream)
+    recv_x = torch.empty(n_recv, h, dtype=torch.bfloat16, device=dev)
+    recv_meta = torch.empty(n_recv, 2, dtype=torch.float32, device=dev)
+    dist.all_to_all_single(recv_x, send_x, recv_splits, send_splits, group=group)
+    dist.all_to_all_single(recv_meta, meta, recv_splits, send_splits, group=group)
+
+    y = local_fn(recv_x, recv_meta[:, 0].to(torch.int32), recv_meta[:, 1].contiguous())
+
+    back = torch.empty(n, h, dtype=torch.bfloat16, device=dev)
+    dist.all_to_all_single(back, y.contiguous(), send_splits, recv_splits, group=group)
+    out = torch.empty(t, h, dtype=torch.bfloat16, device=dev)
+    with torch.cuda.device(dev):
+        _lib.call("strix_moe_sum_gather", back.data_ptr(), slot_pos.data_ptr(), out.data_ptr(), t, k, h,
+                  back.stride(0) if n else h, out.stride(0), stream)
+    return out
 
 
 def local_experts_mxfp4(w13, w13_scale, w2, w2_scale, block_m: int | None = None):
