@@ -236,19 +236,37 @@ __global__ void __launch_bounds__(kPfThreads) attn_prefill_kernel(const PrefillA
     const float* sks = reinterpret_cast<const float*>(smem + raw_base(buf) + 2 * L::kRawKV);
     const float* svs = sks + kBN;
     float mx_lo = m_lo, mx_hi = m_hi;
+    // a tile strictly inside every row's visible range needs no mask (most tiles do not):
+    // all 64 keys at or before the warp's first query, and inside the window of its last
+    const bool interior = k0 + kBN - 1 <= pos0 + row0 &&
+                          (p.window_left < 0 || pos0 + row0 + 15 - k0 <= p.window_left);
+    if (interior) {
 #pragma unroll
-    for (int j = 0; j < kBN / 8; ++j) {
+      for (int j = 0; j < kBN / 8; ++j) {
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int key = k0 + 8 * j + 2 * c + e;
-        const float f = Q8 ? sks[8 * j + 2 * c + e] * sl2 : sl2;
-        const bool in = key < k_end;
-        const bool v_lo = in && key <= qpos_lo && (p.window_left < 0 || qpos_lo - key <= p.window_left);
-        const bool v_hi = in && key <= qpos_hi && (p.window_left < 0 || qpos_hi - key <= p.window_left);
-        s[j][e] = v_lo ? s[j][e] * f : -INFINITY;
-        s[j][2 + e] = v_hi ? s[j][2 + e] * f : -INFINITY;
-        mx_lo = fmaxf(mx_lo, s[j][e]);
-        mx_hi = fmaxf(mx_hi, s[j][2 + e]);
+        for (int e = 0; e < 2; ++e) {
+          const float f = Q8 ? sks[8 * j + 2 * c + e] * sl2 : sl2;
+          s[j][e] *= f;
+          s[j][2 + e] *= f;
+          mx_lo = fmaxf(mx_lo, s[j][e]);
+          mx_hi = fmaxf(mx_hi, s[j][2 + e]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < kBN / 8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int key = k0 + 8 * j + 2 * c + e;
+          const float f = Q8 ? sks[8 * j + 2 * c + e] * sl2 : sl2;
+          const bool in = key < k_end;
+          const bool v_lo = in && key <= qpos_lo && (p.window_left < 0 || qpos_lo - key <= p.window_left);
+          const bool v_hi = in && key <= qpos_hi && (p.window_left < 0 || qpos_hi - key <= p.window_left);
+          s[j][e] = v_lo ? s[j][e] * f : -INFINITY;
+          s[j][2 + e] = v_hi ? s[j][2 + e] * f : -INFINITY;
+          mx_lo = fmaxf(mx_lo, s[j][e]);
+          mx_hi = fmaxf(mx_hi, s[j][2 + e]);
+        }
       }
     }
     mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
@@ -258,10 +276,15 @@ __global__ void __launch_bounds__(kPfThreads) attn_prefill_kernel(const PrefillA
     // a row that has seen no key yet keeps m = -inf; its exponent base is 0 then
     const float b_lo = mx_lo == -INFINITY ? 0.f : mx_lo, b_hi = mx_hi == -INFINITY ? 0.f : mx_hi;
     const float r_lo = fast_exp2(m_lo - b_lo), r_hi = fast_exp2(m_hi - b_hi);
+    // the accumulators are rescaled only when some row's maximum moved (a warp-wide
+    // decision: after the first tiles it rarely does)
+    const bool moved = __any_sync(0xffffffffu, mx_lo != m_lo || mx_hi != m_hi);
     m_lo = mx_lo, m_hi = mx_hi;
-    l_lo *= r_lo, l_hi *= r_hi;
+    if (moved) {
+      l_lo *= r_lo, l_hi *= r_hi;
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i) o[i][0] *= r_lo, o[i][1] *= r_lo, o[i][2] *= r_hi, o[i][3] *= r_hi;
+      for (int i = 0; i < D / 8; ++i) o[i][0] *= r_lo, o[i][1] *= r_lo, o[i][2] *= r_hi, o[i][3] *= r_hi;
+    }
 
     uint32_t pf[kBN / 16][4];   // P as the A operand of P V
 #pragma unroll
