@@ -73,7 +73,7 @@ struct PfLayout {
 };
 
 template <int D, bool Q8>
-__global__ void __launch_bounds__(kPfThreads) attn_prefill_kernel(const PrefillArgs p) {
+__global__ void __launch_bounds__(kPfThreads, 3) attn_prefill_kernel(const PrefillArgs p) {
   using L = PfLayout<D, Q8>;
   extern __shared__ __align__(128) uint8_t smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
