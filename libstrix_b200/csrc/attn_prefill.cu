@@ -207,6 +207,11 @@ __global__ void __launch_bounds__(kPfThreads, 3) attn_prefill_kernel(const Prefi
           *reinterpret_cast<uint4*>(dst + tile_off<D>(row, chunk + 1)) = make_uint4(h[4], h[5], h[6], h[7]);
         }
       }
+      // the tile's scales, once: K scale x softmax scale x log2(e), V scale x lift
+      if (tid < 2 * kBN) {
+        float* sc = reinterpret_cast<float*>(smem + raw_base(buf) + 2 * L::kRawKV) + tid;
+        *sc *= tid < kBN ? sl2 : kLift;
+      }
       __syncthreads();
     }
     const uint32_t kt = smem_s + k16_base(buf), vt = smem_s + v16_base(buf);
@@ -245,7 +250,7 @@ __global__ void __launch_bounds__(kPfThreads, 3) attn_prefill_kernel(const Prefi
       for (int j = 0; j < kBN / 8; ++j) {
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          const float f = Q8 ? sks[8 * j + 2 * c + e] * sl2 : sl2;
+          const float f = Q8 ? sks[8 * j + 2 * c + e] : sl2;
           s[j][e] *= f;
           s[j][2 + e] *= f;
           mx_lo = fmaxf(mx_lo, s[j][e]);
@@ -258,7 +263,7 @@ __global__ void __launch_bounds__(kPfThreads, 3) attn_prefill_kernel(const Prefi
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int key = k0 + 8 * j + 2 * c + e;
-          const float f = Q8 ? sks[8 * j + 2 * c + e] * sl2 : sl2;
+          const float f = Q8 ? sks[8 * j + 2 * c + e] : sl2;
           const bool in = key < k_end;
           const bool v_lo = in && key <= qpos_lo && (p.window_left < 0 || qpos_lo - key <= p.window_left);
           const bool v_hi = in && key <= qpos_hi && (p.window_left < 0 || qpos_hi - key <= p.window_left);
@@ -294,7 +299,7 @@ __global__ void __launch_bounds__(kPfThreads, 3) attn_prefill_kernel(const Prefi
       for (int e = 0; e < 2; ++e) {
         const float p_lo = fast_exp2(s[j][e] - b_lo), p_hi = fast_exp2(s[j][2 + e] - b_hi);
         l_lo += p_lo, l_hi += p_hi;
-        const float w = Q8 ? svs[8 * j + 2 * c + e] * kLift : 1.f;
+        const float w = Q8 ? svs[8 * j + 2 * c + e] : 1.f;
         pv[e] = p_lo * w, pv[2 + e] = p_hi * w;
       }
       const int tt = j >> 1, h = (j & 1) * 2;
