@@ -289,9 +289,15 @@ __global__ void __launch_bounds__(umma_threads(NTOK), 1) moe_gemm_umma_kernel(co
       ++li;
     }
     if (dead && lane == 0) atomicExch(p.status, 1), s_abort = 1;
-  } else if (warp == kIssuerWarp) {
-    // --------------------------------------------------------------- issuer
-    if (lane == 0) {
+  } else if (warp == kIssuerWarp || warp == kIssuerWarp + 1) {
+    // -------------------------------------------------------------- issuers
+    // Two issuing threads take the K blocks alternately (each block has its own
+    // stage and accumulator, so they are independent): a block costs one thread
+    // two waits, four MMAs and a commit in program order, which at full weight
+    // bandwidth is most of a block's time. Off unless STRIX_UMMA_DEBUG has bit 32.
+    const bool solo = (p.debug & 32) == 0;
+    const int parity = warp - kIssuerWarp;
+    if (lane == 0 && !(solo && parity == 1)) {
       const uint32_t idesc = instr_desc(D_F32, 0, 0, kTileM, NTOK);
       const uint32_t a_lo0 = smem_desc_lo(ring_s);
       int t = 0;
@@ -300,6 +306,7 @@ __global__ void __launch_bounds__(umma_threads(NTOK), 1) moe_gemm_umma_kernel(co
         const int mb = item / p.n_tiles;
         if (s_expert[mb] < 0) continue;
         for (int kb = 0; kb < nkb; ++kb, ++t) {
+          if (!solo && (t & 1) != parity) continue;
           const int s = t % S, b = t % NB;
           const bool prof = p.prof != nullptr && blockIdx.x == 0;
           const long long c0 = prof ? clock64() : 0;
