@@ -630,9 +630,13 @@ __global__ void __launch_bounds__(kWideThreads, 1) moe_gemm_umma_wide_kernel(
       if (lane == 0) mbar_arrive(&meta_full_bar[buf]);
     }
     if (dead && lane == 0) atomicExch(p.status, 1), s_abort = 1;
-  } else if (warp == kIssuerWarp) {
-    // --------------------------------------------------------------- issuer
-    if (lane == 0) {
+  } else if (warp == kIssuerWarp || warp == kIssuerWarp + 1) {
+    // -------------------------------------------------------------- issuers
+    // optionally two threads on alternate K blocks (= alternate accumulators):
+    // bit 64 of STRIX_UMMA_DEBUG
+    const bool solo = (p.debug & 64) == 0;
+    const int parity = warp - kIssuerWarp;
+    if (lane == 0 && !(solo && parity == 1)) {
       const uint32_t idesc = instr_desc(D_F32, 0, 0, kWideTok, kWideCols);
       const uint32_t a_lo0 = smem_desc_lo(ring_s);
       int t = 0;
@@ -640,6 +644,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) moe_gemm_umma_wide_kernel(
       for (int item = next_valid(blockIdx.x); item < total_items && !dead;
            item = next_valid(item + gridDim.x)) {
         for (int kb = 0; kb < nkb; ++kb, ++t) {
+          if (!solo && (t & 1) != parity) continue;
           const int s = t % S, b = t % NB;
           const bool ok_full = mbar_wait(&full_bar[s], (t / S) & 1);
           const bool ok_acc = mbar_wait(&tempty_bar[b], ((t / NB) & 1) ^ 1);
