@@ -395,8 +395,31 @@ def bench_moe_fp8(args, dev, with_cpu: bool) -> dict:
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / args.steps
+        # the same seven launches replayed from a CUDA graph (how a serving loop runs
+        # decode steps): an empty kernel costs 5 us per eager launch on this system
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            step()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                step()
+        torch.cuda.synchronize()
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms_graph = e0.elapsed_time(e1) / args.steps
+        del graph
         gbs = layer.weight_bytes / (ms * 1e-3) / 1e9
         run = {"tokens": tokens, "ms_per_layer": ms, "tflops": layer.flops / (ms * 1e-3) / 1e12,
+               "ms_per_layer_cuda_graph": ms_graph,
+               "tflops_cuda_graph": layer.flops / (ms_graph * 1e-3) / 1e12,
+               "weight_gbs_cuda_graph": layer.weight_bytes / (ms_graph * 1e-3) / 1e9,
                "weight_gbs": gbs, "weight_bytes": layer.weight_bytes,
                "block_m": pick_block_m(tokens, layer.top_k, 128),
                "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s",
