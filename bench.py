@@ -226,7 +226,9 @@ def main() -> None:
             dist.destroy_process_group()
         return
 
-    batch = decode_batch(batch=args.batch, ctx_hi=args.ctx_hi, seed=rank, device=dev)
+    # weak scaling: every rank holds a batch with the SAME context lengths (seed 0), so
+    # the per-GPU work is fixed as N grows; the tensors are each rank's own
+    batch = decode_batch(batch=args.batch, ctx_hi=args.ctx_hi, seed=0, device=dev)
     kv_bytes = batch.kv_bytes
     out = torch.empty_like(batch.q)
     nseg = strix._lib.load().strix_attn_decode_segments(
