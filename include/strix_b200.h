@@ -354,14 +354,17 @@ int strix_moe_align_counts(const int32_t* topk_ids, int32_t* sorted_ids, int32_t
                            strix_stream_t stream);
 
 /* Expert-parallel helpers (no counterpart in the reference, which has no EP).
- * strix_ep_pack: send[i] = x[order[i] / top_k] (bf16 rows of `hidden`), meta[i] =
- * (topk_ids[order[i]] % experts_per_rank as float, topk_weights[order[i]]).
+ * strix_ep_pack: send[i] = x[order[i] / top_k] (bf16 rows of `hidden`), meta[i *
+ * meta_stride] = (topk_ids[order[i]] % experts_per_rank as float,
+ * topk_weights[order[i]]); meta_stride counts floats (2 for a dense [slots, 2]
+ * array; pointing meta at the padded tail of the send rows lets one collective
+ * carry both).
  * strix_moe_sum_gather: out[t] = sum_j rows[pos[t * top_k + j]] in fp32, one bf16
  * rounding (negative positions are skipped). */
 int strix_ep_pack(const void* x, void* send, float* meta, const int32_t* order,
                   const int32_t* topk_ids, const float* topk_weights, int64_t slots,
                   int64_t hidden, int64_t top_k, int64_t experts_per_rank, int64_t x_stride,
-                  int64_t send_stride, strix_stream_t stream);
+                  int64_t send_stride, int64_t meta_stride, strix_stream_t stream);
 int strix_moe_sum_gather(const void* rows, const int32_t* pos, void* out, int64_t tokens,
                          int64_t top_k, int64_t hidden, int64_t row_st, int64_t out_st,
                          strix_stream_t stream);

@@ -367,14 +367,15 @@ __global__ void __launch_bounds__(256) moe_sum_gather_kernel(
 __global__ void __launch_bounds__(256) ep_pack_kernel(
     const uint4* __restrict__ x, int64_t x_st16, uint4* __restrict__ send, int64_t send_st16,
     float2* __restrict__ meta, const int32_t* __restrict__ order, const int32_t* __restrict__ topk_ids,
-    const float* __restrict__ topk_w, int64_t slots, int chunks, int top_k, int experts_per_rank) {
+    const float* __restrict__ topk_w, int64_t slots, int chunks, int top_k, int experts_per_rank,
+    int64_t meta_st2) {
   const int64_t idx = int64_t(blockIdx.x) * 256 + threadIdx.x;
   const int64_t i = idx / chunks;
   if (i >= slots) return;
   const int ch = int(idx % chunks);
   const int slot = order[i];
   send[i * send_st16 + ch] = x[int64_t(slot / top_k) * x_st16 + ch];
-  if (ch == 0) meta[i] = make_float2(float(topk_ids[slot] % experts_per_rank), topk_w[slot]);
+  if (ch == 0) meta[i * meta_st2] = make_float2(float(topk_ids[slot] % experts_per_rank), topk_w[slot]);
 }
 
 }  // namespace
@@ -401,7 +402,9 @@ extern "C" int strix_moe_sum_gather(const void* rows, const int32_t* pos, void* 
 extern "C" int strix_ep_pack(const void* x, void* send, float* meta, const int32_t* order,
                              const int32_t* topk_ids, const float* topk_weights, int64_t slots,
                              int64_t hidden, int64_t top_k, int64_t experts_per_rank,
-                             int64_t x_stride, int64_t send_stride, strix_stream_t stream) {
+                             int64_t x_stride, int64_t send_stride, int64_t meta_stride,
+                             strix_stream_t stream) {
+  STRIX_CHECK(meta_stride >= 2 && meta_stride % 2 == 0, "meta_stride counts floats, even, >= 2");
   STRIX_CHECK(slots >= 0 && hidden > 0 && hidden % 8 == 0 && top_k >= 1 && experts_per_rank >= 1,
               "hidden must be a multiple of 8");
   STRIX_CHECK(x_stride % 8 == 0 && send_stride % 8 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 &&
@@ -414,7 +417,7 @@ extern "C" int strix_ep_pack(const void* x, void* send, float* meta, const int32
   ep_pack_kernel<<<unsigned((work + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(x), x_stride / 8, static_cast<uint4*>(send), send_stride / 8,
       reinterpret_cast<float2*>(meta), order, topk_ids, topk_weights, slots, chunks, int(top_k),
-      int(experts_per_rank));
+      int(experts_per_rank), meta_stride / 2);
   return launch_status("ep_pack");
 }
 

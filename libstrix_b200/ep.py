@@ -112,18 +112,19 @@ def _dispatch_combine_cuda(x, topk_weights, topk_ids, experts_per_rank, local_fn
     send_splits, recv_splits = send_counts.tolist(), recv_counts.tolist()   # the one host sync
     n_recv = sum(recv_splits)
 
-    send_x = torch.empty(n, h, dtype=torch.bfloat16, device=dev)
-    meta = torch.empty(n, 2, dtype=torch.float32, device=dev)
+    # a send row = the token's `h` bf16 values + 16 bytes holding (local expert id,
+    # routing weight) as two floats, so one collective carries both
+    hp = h + 8
+    send = torch.empty(n, hp, dtype=torch.bfloat16, device=dev)
     with torch.cuda.device(dev):
-        _lib.call("strix_ep_pack", x.data_ptr(), send_x.data_ptr(), meta.data_ptr(), order.data_ptr(),
-                  ids.data_ptr(), wts.data_ptr(), n, h, k, experts_per_rank, x.stride(0),
-                  send_x.stride(0), stream)
-    recv_x = torch.empty(n_recv, h, dtype=torch.bfloat16, device=dev)
-    recv_meta = torch.empty(n_recv, 2, dtype=torch.float32, device=dev)
-    dist.all_to_all_single(recv_x, send_x, recv_splits, send_splits, group=group)
-    dist.all_to_all_single(recv_meta, meta, recv_splits, send_splits, group=group)
+        _lib.call("strix_ep_pack", x.data_ptr(), send.data_ptr(), send.data_ptr() + 2 * h,
+                  order.data_ptr(), ids.data_ptr(), wts.data_ptr(), n, h, k, experts_per_rank,
+                  x.stride(0), hp, hp // 2, stream)
+    recv = torch.empty(n_recv, hp, dtype=torch.bfloat16, device=dev)
+    dist.all_to_all_single(recv, send, recv_splits, send_splits, group=group)
+    recv_meta = recv[:, h:h + 4].view(torch.float32)
 
-    y = local_fn(recv_x, recv_meta[:, 0].to(torch.int32), recv_meta[:, 1].contiguous())
+    y = local_fn(recv[:, :h], recv_meta[:, 0].to(torch.int32), recv_meta[:, 1].contiguous())
 
     back = torch.empty(n, h, dtype=torch.bfloat16, device=dev)
     dist.all_to_all_single(back, y.contiguous(), send_splits, recv_splits, group=group)
