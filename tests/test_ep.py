@@ -147,3 +147,54 @@ def test_ep_moe_fp8_equals_the_single_rank_layer():
         torch.testing.assert_close(out.float(), fused.float(), rtol=2e-2, atol=2e-2)
     finally:
         dist.destroy_process_group()
+
+
+def _gpu_worker(rank, world, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
+                      WORLD_SIZE=str(world))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from libstrix_b200 import ep
+        from libstrix_b200 import moe as smoe
+
+        e, k, hid, inter = 8, 2, 256, 128
+        per = e // world
+        g = torch.Generator().manual_seed(0)          # the same experts on every rank
+        w13 = torch.randint(0, 256, (e, 2 * inter, hid // 2), generator=g, dtype=torch.uint8).to(dev)
+        s13 = torch.randint(118, 124, (e, 2 * inter, hid // 32), generator=g, dtype=torch.uint8).to(dev)
+        w2 = torch.randint(0, 256, (e, hid, inter // 2), generator=g, dtype=torch.uint8).to(dev)
+        s2 = torch.randint(118, 124, (e, hid, inter // 32), generator=g, dtype=torch.uint8).to(dev)
+        gr = torch.Generator().manual_seed(100 + rank)  # each rank's own tokens
+        t = 50 + 30 * rank
+        x = torch.randn(t, hid, generator=gr).bfloat16().to(dev)
+        logits = torch.randn(t, e, generator=gr).to(dev)
+        lo = rank * per
+        out = ep.ep_moe_mxfp4(x, logits, w13[lo:lo + per].contiguous(), s13[lo:lo + per].contiguous(),
+                              w2[lo:lo + per].contiguous(), s2[lo:lo + per].contiguous(), k)
+        # the same layer without parallelism: all experts here, this rank's tokens
+        weights, ids = smoe.route(logits, k)
+        run = ep.local_experts_mxfp4(w13, s13, w2, s2)
+        rows = x.repeat_interleave(k, 0)
+        y = run(rows, ids.reshape(-1).to(torch.int32), weights.reshape(-1).contiguous())
+        ref = torch.empty(t, hid, dtype=torch.bfloat16, device=dev)
+        torch.ops.strix.moe_sum(y.view(t, k, hid), ref)
+        torch.cuda.synchronize()
+        results[rank] = float((out.float() - ref.float()).abs().max()), float(ref.float().abs().max())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_ep_moe_mxfp4_two_gpus_equals_unsharded_layer():
+    """Two NCCL ranks, each with its own tokens and half of the experts, against
+    the same layer computed on one rank with all experts: a row's result does not
+    depend on where or in which m-block it was computed."""
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_gpu_worker, args=(2, 29741, results), nprocs=2, join=True)
+    for rank in (0, 1):
+        err, peak = results[rank]
+        assert err <= 1e-2 * peak, f"rank {rank}: max error {err} vs peak {peak}"
