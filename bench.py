@@ -40,6 +40,9 @@ sys.path.insert(0, str(ROOT))
 
 METRIC = "int8-KV paged decode attention, algorithmic KV bytes read per second"
 UNIT = "GB/s"
+# (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of the decode kernel,
+# from the ncu capture summarised in profiles/attn_decode_q8_decode_batch64.md
+DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = (1_183_573_248 + 16_128_000) / 1_182_370_464
 WORKLOAD = ("decode_attn_int8kv B=64/gpu Hq=32 Hkv=4 D=128 block=16 ctx~U[1024,65536] "
             "shuffled block table")
 
@@ -325,7 +328,12 @@ def main() -> None:
                        "segments": int(nseg), "l2": "inputs (2.2 GB) larger than the 126 MB L2",
                        "timing": "cuda events, max over ranks"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                         "frac": achieved / peak,
+                         # DRAM read + write bytes per launch: measured with ncu on the 32-sequence
+                         # case (1,183.6 + 16.1 MB for 1,182.4 MB algorithmic) and scaled by the keys
+                         "traffic": kv_bytes * DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE,
+                         "traffic_note": "ncu capture at batch 32 scaled to this launch by its keys",
+                         "peak_kind": peak_kind,
                          "frac_of_8TBps": achieved / 8000.0},
             "e2e": {"value": e2e_value, "unit": UNIT,
                     "h2d_bytes_per_step": int(q_h.nbytes + sl_h.nbytes + bt_h.nbytes),
