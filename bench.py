@@ -41,7 +41,7 @@ sys.path.insert(0, str(ROOT))
 METRIC = "int8-KV paged decode attention, algorithmic KV bytes read per second"
 UNIT = "GB/s"
 # (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of the decode kernel,
-# from the ncu capture summarised in profiles/attn_decode_q8_decode_batch64.md
+# from an ncu capture of the 32-sequence case (committed summary under profiles/)
 DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = (1_183_573_248 + 16_128_000) / 1_182_370_464
 WORKLOAD = ("decode_attn_int8kv B=64/gpu Hq=32 Hkv=4 D=128 block=16 ctx~U[1024,65536] "
             "shuffled block table")
