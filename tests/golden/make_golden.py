@@ -1,9 +1,9 @@
 """Generates the golden vectors under tests/golden/ from the reference's own tests.
 
-Run once, in a container that has the asf0/libstrix tree (default
-/root/reference, or $STRIX_REFERENCE):
+Run once, in a container that has the asf0/libstrix tree, with its location in
+$STRIX_REFERENCE:
 
-    python tests/golden/make_golden.py
+    STRIX_REFERENCE=<path to the asf0/libstrix checkout> python tests/golden/make_golden.py
 
 The reference's kernel tests carry their torch reference implementations
 in-file (tests/test_attn_prefill.py: build/quantize/reference, ...). Those test
@@ -24,7 +24,9 @@ from pathlib import Path
 
 import torch
 
-REF = Path(os.environ.get("STRIX_REFERENCE", "/root/reference"))
+if "STRIX_REFERENCE" not in os.environ:
+    raise SystemExit("set STRIX_REFERENCE to the asf0/libstrix checkout")
+REF = Path(os.environ["STRIX_REFERENCE"])
 OUT = Path(__file__).resolve().parent
 
 
