@@ -278,10 +278,11 @@ int strix_moe_permute_bf16(const void* x, void* y, const int32_t* slot_pos,
 int strix_moe_gemm_mxfp4_sorted(void* c, const void* a, const void* w, const void* scales,
                                 const int32_t* sorted_ids, const int32_t* expert_ids,
                                 const int32_t* num_post_padded, const float* topk_weights,
-                                int64_t num_valid, int64_t n, int64_t k, int64_t a_stride,
-                                int64_t c_stride, int64_t w_stride_e, int64_t w_stride_n,
-                                int64_t s_stride_e, int64_t s_stride_n, int64_t sorted_len,
-                                int64_t block_m, int gate_act, int c_sorted, strix_stream_t stream);
+                                int64_t num_valid, int64_t num_experts, int64_t n, int64_t k,
+                                int64_t a_stride, int64_t c_stride, int64_t w_stride_e,
+                                int64_t w_stride_n, int64_t s_stride_e, int64_t s_stride_n,
+                                int64_t sorted_len, int64_t block_m, int gate_act, int c_sorted,
+                                strix_stream_t stream);
 int strix_moe_gemm_mxfp4_sorted_covers(int64_t n, int64_t k, int64_t block_m, int gate_act);
 
 /* Grouped or dense GEMM with int8 activations (qa int8 [rows, k], sa fp32 [rows,
@@ -389,26 +390,20 @@ int strix_moe_act_quant_fp8_scatter(const void* x, void* q, float* sa, const int
  * sorted position of the processed m-blocks (padding rows included), else row
  * sorted_ids[p] for valid slots only - the contract of the reference's
  * moe_gemm_fp8 (csrc/moe/moe_gemm_w8a16.hip:581-623). sorted_len counts whole
- * m-blocks. strix_moe_gemm_fp8_sorted_covers() tells (1/0) whether a geometry
- * is covered; uncovered ones are rejected. */
+ * m-blocks; num_experts is the first extent of w (m-blocks whose expert id is
+ * negative or >= num_experts are skipped). strix_moe_gemm_fp8_sorted_covers()
+ * tells (1/0) whether a geometry is covered; uncovered ones are rejected. */
 int strix_moe_gemm_fp8_sorted(void* c, const void* a, const float* act_scales, const void* w,
                               const float* scales, const int32_t* sorted_ids,
                               const int32_t* expert_ids, const int32_t* num_post_padded,
-                              const float* topk_weights, int64_t num_valid, int64_t n, int64_t k,
+                              const float* topk_weights, int64_t num_valid, int64_t num_experts,
+                              int64_t n, int64_t k,
                               int64_t a_stride, int64_t c_stride, int64_t w_stride_e,
                               int64_t w_stride_n, int64_t s_stride_e, int64_t s_stride_n,
                               int64_t sa_stride, int64_t sorted_len, int64_t block_m,
                               int scale_kind, int gate_act, int c_sorted, strix_stream_t stream);
 int strix_moe_gemm_fp8_sorted_covers(int64_t n, int64_t k, int64_t block_m, int gate_act,
                                      int scale_kind);
-
-/* Tuning aid: cycle counters of CTA 0 of the tcgen05 MoE kernel, accumulated only
- * while the environment variable STRIX_UMMA_PROF is set: [0] issuer waiting for
- * data, [1] issuer waiting for an accumulator, [2] steps, [3] consumer waiting
- * for MMAs, [4] consumer waiting for TMEM loads, [5] consumer epilogues, [6]
- * consumer waiting for metadata, [7] kernel cycles. Synchronises the device;
- * reset != 0 zeroes the counters afterwards. No reference counterpart. */
-int strix_umma_prof(int64_t* host_out8, int reset);
 
 /* strix_attn_decode_bf16 without a workspace argument, for callers that cannot
  * allocate device memory: a host loop that owns nothing but the input and

@@ -65,11 +65,12 @@ __global__ void __launch_bounds__(kGThreads, 1) gemm_w8a8_umma_kernel(const Gemm
   extern __shared__ uint8_t raw_smem[];
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
                                              ~uintptr_t(1023));
-  __shared__ __align__(8) uint64_t full_bar[S], empty_bar[S], tfull_bar[2], tempty_bar[2];
+  __shared__ __align__(8) uint64_t full_bar[S], empty_bar[S], tfull_bar[2], tempty_bar[2], drain_bar;
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int s_abort;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int armed = 0;   // producer thread: stages it handed to the TMA (read at teardown)
   const int nkb = p.K / kGKBlock;
   const int total_items = p.a_tiles * p.b_tiles;
 
@@ -82,6 +83,7 @@ __global__ void __launch_bounds__(kGThreads, 1) gemm_w8a8_umma_kernel(const Gemm
       mbar_init(&tfull_bar[i], 1);
       mbar_init(&tempty_bar[i], kGEpilogueWarps);
     }
+    mbar_init(&drain_bar, 1);
     s_abort = 0;
     fence_mbar_init();
   }
@@ -113,6 +115,7 @@ __global__ void __launch_bounds__(kGThreads, 1) gemm_w8a8_umma_kernel(const Gemm
           tma::load_2d(st + L::kABytes, &map_b, kb * kGKBlock, bt * NB, &full_bar[s]);
         }
       }
+      armed = t;
       if (dead) atomicExch(p.status, 1), s_abort = 1;
     }
   } else if (warp == 1) {
@@ -229,6 +232,12 @@ __global__ void __launch_bounds__(kGThreads, 1) gemm_w8a8_umma_kernel(const Gemm
 
   tc_fence_before_sync();
   __syncthreads();
+  if (s_abort) {   // wait for the copies and MMAs still in flight before TMEM goes
+    if (tid == 0) drain_armed_loads(full_bar, S, armed);
+    if (warp == 1 && lane == 0) drain_issued_mmas(&drain_bar);
+    tc_fence_before_sync();
+    __syncthreads();
+  }
   if (warp == 1) tmem_dealloc(tmem, L::kTmemCols);
 }
 

@@ -60,7 +60,7 @@ struct MxArgs {
   const float* topk_w;
   int32_t* status;
   int64_t num_valid, c_stride, s_se, s_sn;
-  int K, N, n_tiles, gate_act, c_sorted;
+  int K, N, n_tiles, gate_act, c_sorted, experts;
 };
 
 __device__ __forceinline__ uint32_t mx_mul_bf16x2(uint32_t a, uint32_t b) {
@@ -101,7 +101,7 @@ __global__ void __launch_bounds__(kMxThreads, 1) moe_gemm_mxfp4_umma_kernel(
   extern __shared__ uint8_t raw_smem[];
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
                                              ~uintptr_t(1023));
-  __shared__ __align__(8) uint64_t full_bar[S], bready_bar[S], done_bar[S], tfull_bar, tempty_bar[2];
+  __shared__ __align__(8) uint64_t full_bar[S], bready_bar[S], done_bar[S], tfull_bar, tempty_bar[2], drain_bar;
   __shared__ int s_unit[kMxMaxMBlocks];   // first m-block | (m-blocks in the unit << 16)
   __shared__ int s_units;
   __shared__ uint32_t tmem_slot;
@@ -109,12 +109,16 @@ __global__ void __launch_bounds__(kMxThreads, 1) moe_gemm_mxfp4_umma_kernel(
   __shared__ int s_expert[kMxMaxMBlocks];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int armed = 0;   // producer thread: stages it handed to the TMA (read at teardown)
   const bool gate = p.gate_act != 0;
   const int half_n = p.N / 2;
   const int nkb = p.K / kMxKB;
   const int m_blocks = *p.num_post / kMxTok;
   const int tile_rows = gate ? kMxCols / 2 : kMxCols;
-  for (int i = tid; i < m_blocks && i < kMxMaxMBlocks; i += kMxThreads) s_expert[i] = p.expert_ids[i];
+  for (int i = tid; i < m_blocks && i < kMxMaxMBlocks; i += kMxThreads) {
+    const int e = p.expert_ids[i];
+    s_expert[i] = e < p.experts ? e : -1;   // ids past the weight tensor skip their m-block
+  }
   __syncthreads();
   if (tid == 0) {
     // units: pairs of consecutive m-blocks of one expert, else single m-blocks
@@ -135,6 +139,7 @@ __global__ void __launch_bounds__(kMxThreads, 1) moe_gemm_mxfp4_umma_kernel(
       mbar_init(&done_bar[i], 1);
     }
     mbar_init(&tfull_bar, 1);
+    mbar_init(&drain_bar, 1);
     for (int i = 0; i < 2; ++i) mbar_init(&tempty_bar[i], kMxEpilogueWarps);
     s_abort = 0;
     fence_mbar_init();
@@ -173,6 +178,7 @@ __global__ void __launch_bounds__(kMxThreads, 1) moe_gemm_mxfp4_umma_kernel(
                        &full_bar[s]);
         }
       }
+      armed = t;
       if (dead) atomicExch(p.status, 1), s_abort = 1;
     }
   } else if (warp == 1) {
@@ -337,6 +343,12 @@ __global__ void __launch_bounds__(kMxThreads, 1) moe_gemm_mxfp4_umma_kernel(
 
   tc_fence_before_sync();
   __syncthreads();
+  if (s_abort) {   // wait for the copies and MMAs still in flight before TMEM goes
+    if (tid == 0) drain_armed_loads(full_bar, S, armed);
+    if (warp == 1 && lane == 0) drain_issued_mmas(&drain_bar);
+    tc_fence_before_sync();
+    __syncthreads();
+  }
   if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
@@ -398,10 +410,11 @@ extern "C" int strix_moe_gemm_mxfp4_sorted_covers(int64_t n, int64_t k, int64_t 
 extern "C" int strix_moe_gemm_mxfp4_sorted(
     void* c, const void* a, const void* w, const void* scales, const int32_t* sorted_ids,
     const int32_t* expert_ids, const int32_t* num_post_padded, const float* topk_weights,
-    int64_t num_valid, int64_t n, int64_t k, int64_t a_stride, int64_t c_stride, int64_t w_stride_e,
-    int64_t w_stride_n, int64_t s_stride_e, int64_t s_stride_n, int64_t sorted_len, int64_t block_m,
-    int gate_act, int c_sorted, strix_stream_t stream) {
+    int64_t num_valid, int64_t num_experts, int64_t n, int64_t k, int64_t a_stride, int64_t c_stride,
+    int64_t w_stride_e, int64_t w_stride_n, int64_t s_stride_e, int64_t s_stride_n, int64_t sorted_len,
+    int64_t block_m, int gate_act, int c_sorted, strix_stream_t stream) {
   STRIX_CHECK(gate_act >= 0 && gate_act <= 2, "activation must be none, silu or gelu_tanh");
+  STRIX_CHECK(num_experts >= 1 && num_experts <= (int64_t(1) << 24), "num_experts out of range");
   STRIX_CHECK(strix_moe_gemm_mxfp4_sorted_covers(n, k, block_m, gate_act),
               "geometry not covered: block_m 128, K %% 64, output width %% 32");
   STRIX_CHECK(sorted_len % block_m == 0 && sorted_len / block_m <= kMxMaxMBlocks,
@@ -421,14 +434,14 @@ extern "C" int strix_moe_gemm_mxfp4_sorted(
   STRIX_CHECK(p.status != nullptr, "status word unavailable");
   p.num_valid = num_valid, p.c_stride = c_stride, p.s_se = s_stride_e, p.s_sn = s_stride_n;
   p.K = int(k), p.N = int(n), p.n_tiles = int((out_rows + tile - 1) / tile), p.gate_act = gate_act;
-  p.c_sorted = c_sorted;
+  p.c_sorted = c_sorted, p.experts = int(num_experts);
   // activations: bytes [sorted rows, 2K], boxes of 128 rows x 128 bytes, swizzled
   CUtensorMap map_a, map_w;
   STRIX_CHECK(tma::make_map_u8(&map_a, a, uint64_t(sorted_len), uint64_t(2 * k), uint64_t(2 * a_stride), kMxTok),
               "tensor map encoding failed (activations)");
   // packed weights: bytes (k / 2, half, row, expert), boxes of 32 bytes x halves x rows, not swizzled
   const uint64_t halves = gate_act ? 2 : 1, rows = uint64_t(out_rows);
-  const uint64_t dims[4] = {uint64_t(k / 2), halves, rows, uint64_t(1) << 16};
+  const uint64_t dims[4] = {uint64_t(k / 2), halves, rows, uint64_t(num_experts)};
   const uint64_t strides[3] = {uint64_t(w_stride_n) * rows, uint64_t(w_stride_n), uint64_t(w_stride_e)};
   const uint32_t box[4] = {kMxKB / 2, uint32_t(halves), uint32_t(tile), 1};
   STRIX_CHECK(tma::make_map_u8_nd(&map_w, w, 4, dims, strides, box, /*swizzle128=*/false),

@@ -41,7 +41,8 @@
 //   * under the fused gate the tile's rows alternate gate row i / up row i, so
 //     act(gate) * up is one lane shuffle in the epilogue;
 //   * every mbarrier wait is bounded; on a timeout the CTA sets *status, stops
-//     issuing, drains its copies, frees TMEM and returns.
+//     issuing, waits (bounded) for the copies and MMAs it has in flight, frees
+//     TMEM and returns.
 #include <cstdlib>
 #include <type_traits>
 
@@ -73,16 +74,15 @@ struct UmmaMoeArgs {
   const int32_t* num_post;
   const float* topk_w;
   int32_t* status;
-  long long* prof;         // optional cycle counters of CTA 0 (tuning aid), or NULL
   int64_t num_valid;
   int64_t c_stride, s_se, s_sn, sa_stride;
   int K, N, block_m;
+  int experts;     // expert ids outside [0, experts) skip their m-block
   int scale_kind;  // 1 channel, 2 block
   int gate_act;    // 0 none, 1 silu, 2 gelu_tanh
   int n_tiles;     // weight tiles per m-block
   int c_sorted;    // 1: c rows are sorted positions, 0: slot ids (padding skipped)
   int prefetch;    // K blocks of weights requested into L2 ahead of the ring
-  int debug;       // measurement switches (STRIX_UMMA_DEBUG): 1 skip the folds, 2 skip the epilogue
 };
 
 // KBMAX bounds the K blocks of an item (16: K <= 2048, 64: K <= 8192); it sizes
@@ -147,12 +147,12 @@ __global__ void __launch_bounds__(umma_threads(NTOK), 1) moe_gemm_umma_kernel(co
   float* s_tw = s_sw + MB * L::kSwFloats;                                 // [MB][NTOK] routing weights
   int* s_sid = reinterpret_cast<int*>(s_tw + MB * NTOK);                  // [MB][NTOK]
   __shared__ __align__(8) uint64_t full_bar[S], empty_bar[S], tempty_bar[NB];
-  __shared__ __align__(8) uint64_t meta_empty_bar[MB], meta_full_bar[MB];
+  __shared__ __align__(8) uint64_t meta_empty_bar[MB], meta_full_bar[MB], drain_bar[2];
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int s_abort;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const long long kernel_t0 = clock64();
+  int armed = 0;   // producer thread: stages it handed to the TMA (read at teardown)
   const bool gate = p.gate_act != 0;
   const int half_n = p.N / 2;
   const int nkb = p.K / kKBlock;
@@ -161,7 +161,10 @@ __global__ void __launch_bounds__(umma_threads(NTOK), 1) moe_gemm_umma_kernel(co
   // expert of every m-block, once, so that no role pays a global-memory round
   // trip per work item for it
   __shared__ int s_expert[kMaxMBlocks];
-  for (int i = tid; i < m_blocks && i < kMaxMBlocks; i += kThreadsU) s_expert[i] = p.expert_ids[i];
+  for (int i = tid; i < m_blocks && i < kMaxMBlocks; i += kThreadsU) {
+    const int e = p.expert_ids[i];
+    s_expert[i] = e < p.experts ? e : -1;
+  }
 
   if (tid == 0) {
     for (int i = 0; i < S; ++i) {
@@ -175,6 +178,7 @@ __global__ void __launch_bounds__(umma_threads(NTOK), 1) moe_gemm_umma_kernel(co
       mbar_init(&meta_empty_bar[i], kConsumerWarps);
       mbar_init(&meta_full_bar[i], 1);
     }
+    mbar_init(&drain_bar[0], 1), mbar_init(&drain_bar[1], 1);
     s_abort = 0;
     fence_mbar_init();
   }
@@ -228,6 +232,7 @@ __global__ void __launch_bounds__(umma_threads(NTOK), 1) moe_gemm_umma_kernel(co
           tma::load_2d(st + L::kABytes, &map_a, kb * kKBlock, mb * NTOK, &full_bar[s]);
         }
       }
+      armed = t;
       if (dead) atomicExch(p.status, 1), s_abort = 1;
     }
   } else if (warp == 1) {
@@ -295,10 +300,9 @@ __global__ void __launch_bounds__(umma_threads(NTOK), 1) moe_gemm_umma_kernel(co
     // stage and accumulator, so they are independent): a block costs one thread
     // two waits, four MMAs and a commit in program order, which at full weight
     // bandwidth is most of a block's time (measured: 0.205 -> 0.188 ms per 256-token
-    // layer, 0.186 -> 0.154 ms at 64 tokens). STRIX_UMMA_DEBUG bit 32: one issuer.
-    const bool solo = (p.debug & 32) != 0;
+    // layer, 0.186 -> 0.154 ms at 64 tokens).
     const int parity = warp - kIssuerWarp;
-    if (lane == 0 && !(solo && parity == 1)) {
+    if (lane == 0) {
       const uint32_t idesc = instr_desc(D_F32, 0, 0, kTileM, NTOK);
       const uint32_t a_lo0 = smem_desc_lo(ring_s);
       int t = 0;
@@ -307,19 +311,10 @@ __global__ void __launch_bounds__(umma_threads(NTOK), 1) moe_gemm_umma_kernel(co
         const int mb = item / p.n_tiles;
         if (s_expert[mb] < 0) continue;
         for (int kb = 0; kb < nkb; ++kb, ++t) {
-          if (!solo && (t & 1) != parity) continue;
+          if ((t & 1) != parity) continue;
           const int s = t % S, b = t % NB;
-          const bool prof = p.prof != nullptr && blockIdx.x == 0;
-          const long long c0 = prof ? clock64() : 0;
           const bool ok_full = mbar_wait(&full_bar[s], (t / S) & 1);
-          const long long c1 = prof ? clock64() : 0;
           const bool ok_acc = mbar_wait(&tempty_bar[b], ((t / NB) & 1) ^ 1);
-          if (prof) {
-            const long long c2 = clock64();
-            p.prof[0] += c1 - c0;   // cycles waiting for data
-            p.prof[1] += c2 - c1;   // cycles waiting for a free accumulator
-            p.prof[2] += 1;         // steps
-          }
           if (!ok_full || !ok_acc || s_abort) {
             dead = true;
             break;
@@ -328,12 +323,10 @@ __global__ void __launch_bounds__(umma_threads(NTOK), 1) moe_gemm_umma_kernel(co
           // one add per operand and MMA: the issuing thread runs in order
           const uint32_t a_lo = a_lo0 + s * (L::kStageBytes >> 4), b_lo = a_lo + (L::kABytes >> 4);
           const uint32_t d = tmem + b * NTOK;
-          if (!(p.debug & 8)) {
-            mma_ss_lo<KIND_F8F6F4, false>(d, a_lo, b_lo, idesc);
-            mma_ss_lo<KIND_F8F6F4, true>(d, a_lo + 2, b_lo + 2, idesc);
-            mma_ss_lo<KIND_F8F6F4, true>(d, a_lo + 4, b_lo + 4, idesc);
-            mma_ss_lo<KIND_F8F6F4, true>(d, a_lo + 6, b_lo + 6, idesc);
-          }
+          mma_ss_lo<KIND_F8F6F4, false>(d, a_lo, b_lo, idesc);
+          mma_ss_lo<KIND_F8F6F4, true>(d, a_lo + 2, b_lo + 2, idesc);
+          mma_ss_lo<KIND_F8F6F4, true>(d, a_lo + 4, b_lo + 4, idesc);
+          mma_ss_lo<KIND_F8F6F4, true>(d, a_lo + 6, b_lo + 6, idesc);
           mma_commit(&empty_bar[s]);   // the stage may be refilled, the partial sums are ready
         }
       }
@@ -357,10 +350,7 @@ __global__ void __launch_bounds__(umma_threads(NTOK), 1) moe_gemm_umma_kernel(co
       const float chs = p.scale_kind == 1 ? p.scales[int64_t(expert) * p.s_se + row] : 1.f;
       // the producers wrote this item's token ids and activation scales
       const int buf = li % MB;
-      const bool cprof = p.prof != nullptr && blockIdx.x == 0 && ctid == 0;
-      const long long m0 = cprof ? clock64() : 0;
       const bool meta_ok = mbar_wait(&meta_full_bar[buf], (li / MB) & 1);
-      if (cprof) p.prof[6] += clock64() - m0;
       if (__any_sync(0xffffffffu, !meta_ok) || s_abort) {
         dead = true;
         break;
@@ -383,16 +373,13 @@ __global__ void __launch_bounds__(umma_threads(NTOK), 1) moe_gemm_umma_kernel(co
       auto issue_ld = [&](int kb, int c, uint32_t (&r)[CH]) {
         const int ts = t0 + kb, b = ts % NB;
         if (c == 0) {
-          const long long w0 = cprof ? clock64() : 0;
           const bool ok = mbar_wait(&empty_bar[b], (ts / NB) & 1);
-          if (cprof) p.prof[3] += clock64() - w0;
           if (__any_sync(0xffffffffu, !ok)) {   // warp-uniform: the epilogue shuffles
             dead = true;
             return;
           }
           tc_fence_after_sync();
         }
-        if (p.debug & 16) return;
         const uint32_t src = tmem + lane_base + b * NTOK + cg * NT2 + c * CH;
         if constexpr (CH == 32) tmem_ld_32x32(src, r);
         else if constexpr (CH == 16) tmem_ld_32x16(src, r);
@@ -425,20 +412,16 @@ __global__ void __launch_bounds__(umma_threads(NTOK), 1) moe_gemm_umma_kernel(co
             const int nkb_ = last ? kb + 1 : kb, nc = last ? 0 : C + 1;
             const bool more = nkb_ < nkb;
             if (more) issue_ld(nkb_, nc, R[BUF ^ 1]);
-            if (!(p.debug & 1)) {
 #pragma unroll
-              for (int j = 0; j < CH; j += 4) {
-                const float4 s4 = *reinterpret_cast<const float4*>(sak + C * CH + j);
-                acc[C * CH + j] = fmaf(__uint_as_float(R[BUF][j]), sw * s4.x, acc[C * CH + j]);
-                acc[C * CH + j + 1] = fmaf(__uint_as_float(R[BUF][j + 1]), sw * s4.y, acc[C * CH + j + 1]);
-                acc[C * CH + j + 2] = fmaf(__uint_as_float(R[BUF][j + 2]), sw * s4.z, acc[C * CH + j + 2]);
-                acc[C * CH + j + 3] = fmaf(__uint_as_float(R[BUF][j + 3]), sw * s4.w, acc[C * CH + j + 3]);
-              }
+            for (int j = 0; j < CH; j += 4) {
+              const float4 s4 = *reinterpret_cast<const float4*>(sak + C * CH + j);
+              acc[C * CH + j] = fmaf(__uint_as_float(R[BUF][j]), sw * s4.x, acc[C * CH + j]);
+              acc[C * CH + j + 1] = fmaf(__uint_as_float(R[BUF][j + 1]), sw * s4.y, acc[C * CH + j + 1]);
+              acc[C * CH + j + 2] = fmaf(__uint_as_float(R[BUF][j + 2]), sw * s4.z, acc[C * CH + j + 2]);
+              acc[C * CH + j + 3] = fmaf(__uint_as_float(R[BUF][j + 3]), sw * s4.w, acc[C * CH + j + 3]);
             }
             if (more && !dead) {
-              const long long w0 = cprof ? clock64() : 0;
               tmem_ld_wait();
-              if (cprof) p.prof[4] += clock64() - w0;
               landed(nkb_, nc);
             }
           };
@@ -456,9 +439,7 @@ __global__ void __launch_bounds__(umma_threads(NTOK), 1) moe_gemm_umma_kernel(co
       if (dead) break;
 
       // ---- epilogue of the item: this thread owns weight row `row`, all tokens
-      const long long ep0 = cprof ? clock64() : 0;
-      if (p.debug & 2) {
-      } else if (gate) {
+      if (gate) {
         __nv_bfloat16* cbase = static_cast<__nv_bfloat16*>(p.c) + nt * (kTileM / 2) + (ctid >> 1);
 #pragma unroll
         for (int j = 0; j < NT2; ++j) {
@@ -479,16 +460,22 @@ __global__ void __launch_bounds__(umma_threads(NTOK), 1) moe_gemm_umma_kernel(co
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&meta_empty_bar[buf]);   // the producers may reuse this buffer
-      if (cprof) p.prof[5] += clock64() - ep0;
       ++li;
     }
     if (dead) atomicExch(p.status, 1), s_abort = 1;
   }
 
-  if (p.prof != nullptr && blockIdx.x == 0 && tid == 0) p.prof[7] += clock64() - kernel_t0;
-  // ---- teardown: all roles meet, then the allocating warp frees TMEM
+  // ---- teardown: all roles meet; after an abort the copies and MMAs still in
+  // flight are waited for; then the allocating warp frees TMEM
   tc_fence_before_sync();
   __syncthreads();
+  if (s_abort) {
+    if (tid == 0) drain_armed_loads(full_bar, S, armed);
+    if ((warp == kIssuerWarp || warp == kIssuerWarp + 1) && lane == 0)
+      drain_issued_mmas(&drain_bar[warp - kIssuerWarp]);
+    tc_fence_before_sync();
+    __syncthreads();
+  }
   if (warp == kIssuerWarp) tmem_dealloc(tmem, L::kTmemCols);
 }
 
@@ -530,23 +517,28 @@ __global__ void __launch_bounds__(kWideThreads, 1) moe_gemm_umma_wide_kernel(
   float* s_tw = s_sw + MB * L::kSwFloats;                                 // [MB][token]
   int* s_sid = reinterpret_cast<int*>(s_tw + MB * kWideTok);              // [MB][token]
   __shared__ __align__(8) uint64_t full_bar[S], done_bar[S], tempty_bar[NB];
-  __shared__ __align__(8) uint64_t meta_empty_bar[MB], meta_full_bar[MB];
+  __shared__ __align__(8) uint64_t meta_empty_bar[MB], meta_full_bar[MB], drain_bar[2];
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int s_abort;
   __shared__ int s_expert[kMaxMBlocks];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int armed = 0;   // producer thread: stages it handed to the TMA (read at teardown)
   const bool gate = p.gate_act != 0;
   const int half_n = p.N / 2;
   const int nkb = p.K / kKBlock;
   const int m_blocks = *p.num_post / kWideTok;
   const int total_items = m_blocks * p.n_tiles;
   const int tile_rows = gate ? kWideCols / 2 : kWideCols;   // output rows (per half) of a tile
-  for (int i = tid; i < m_blocks && i < kMaxMBlocks; i += kWideThreads) s_expert[i] = p.expert_ids[i];
+  for (int i = tid; i < m_blocks && i < kMaxMBlocks; i += kWideThreads) {
+    const int e = p.expert_ids[i];
+    s_expert[i] = e < p.experts ? e : -1;
+  }
   if (tid == 0) {
     for (int i = 0; i < S; ++i) mbar_init(&full_bar[i], 1), mbar_init(&done_bar[i], 1);
     for (int i = 0; i < NB; ++i) mbar_init(&tempty_bar[i], kWideConsumerWarps);
     for (int i = 0; i < MB; ++i) mbar_init(&meta_empty_bar[i], kWideConsumerWarps), mbar_init(&meta_full_bar[i], 1);
+    mbar_init(&drain_bar[0], 1), mbar_init(&drain_bar[1], 1);
     s_abort = 0;
     fence_mbar_init();
   }
@@ -585,6 +577,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) moe_gemm_umma_wide_kernel(
           tma::load_4d(st + L::kABytes, &map_w, kb * kKBlock, 0, nt * tile_rows, expert, &full_bar[s]);
         }
       }
+      armed = t;
       if (dead) atomicExch(p.status, 1), s_abort = 1;
     }
   } else if (warp == 1) {
@@ -633,10 +626,9 @@ __global__ void __launch_bounds__(kWideThreads, 1) moe_gemm_umma_wide_kernel(
   } else if (warp == kIssuerWarp || warp == kIssuerWarp + 1) {
     // -------------------------------------------------------------- issuers
     // two threads on alternate K blocks (= alternate accumulators; measured 0.539 ->
-    // 0.528 ms per 4096-token layer); bit 32 of STRIX_UMMA_DEBUG leaves one
-    const bool solo = (p.debug & 32) != 0;
+    // 0.528 ms per 4096-token layer)
     const int parity = warp - kIssuerWarp;
-    if (lane == 0 && !(solo && parity == 1)) {
+    if (lane == 0) {
       const uint32_t idesc = instr_desc(D_F32, 0, 0, kWideTok, kWideCols);
       const uint32_t a_lo0 = smem_desc_lo(ring_s);
       int t = 0;
@@ -644,7 +636,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) moe_gemm_umma_wide_kernel(
       for (int item = next_valid(blockIdx.x); item < total_items && !dead;
            item = next_valid(item + gridDim.x)) {
         for (int kb = 0; kb < nkb; ++kb, ++t) {
-          if (!solo && (t & 1) != parity) continue;
+          if ((t & 1) != parity) continue;
           const int s = t % S, b = t % NB;
           const bool ok_full = mbar_wait(&full_bar[s], (t / S) & 1);
           const bool ok_acc = mbar_wait(&tempty_bar[b], ((t / NB) & 1) ^ 1);
@@ -774,16 +766,18 @@ __global__ void __launch_bounds__(kWideThreads, 1) moe_gemm_umma_wide_kernel(
 
   tc_fence_before_sync();
   __syncthreads();
+  if (s_abort) {
+    if (tid == 0) drain_armed_loads(full_bar, S, armed);
+    if ((warp == kIssuerWarp || warp == kIssuerWarp + 1) && lane == 0)
+      drain_issued_mmas(&drain_bar[warp - kIssuerWarp]);
+    tc_fence_before_sync();
+    __syncthreads();
+  }
   if (warp == kIssuerWarp) tmem_dealloc(tmem, 512);
 }
 
 // Status word the kernels raise when a bounded wait runs out (0 = healthy).
 __device__ int32_t g_umma_status = 0;
-// Cycle counters of CTA 0, filled only while STRIX_UMMA_PROF is set: [0] issuer
-// waiting for data, [1] issuer waiting for an accumulator, [2] steps, [3]
-// consumer waiting for MMAs, [4] consumer waiting for TMEM loads, [5] consumer
-// epilogues, [6] consumer waiting for metadata, [7] kernel cycles.
-__device__ long long g_umma_prof[8] = {};
 
 template <int NTOK, int KBMAX>
 int launch_umma(const UmmaMoeArgs& p, const CUtensorMap& map_w, const CUtensorMap& map_a,
@@ -852,11 +846,12 @@ extern "C" int strix_moe_gemm_fp8_sorted_covers(int64_t n, int64_t k, int64_t bl
 extern "C" int strix_moe_gemm_fp8_sorted(
     void* c, const void* a, const float* act_scales, const void* w, const float* scales,
     const int32_t* sorted_ids, const int32_t* expert_ids, const int32_t* num_post_padded,
-    const float* topk_weights, int64_t num_valid, int64_t n, int64_t k, int64_t a_stride,
-    int64_t c_stride, int64_t w_stride_e, int64_t w_stride_n, int64_t s_stride_e,
+    const float* topk_weights, int64_t num_valid, int64_t num_experts, int64_t n, int64_t k,
+    int64_t a_stride, int64_t c_stride, int64_t w_stride_e, int64_t w_stride_n, int64_t s_stride_e,
     int64_t s_stride_n, int64_t sa_stride, int64_t sorted_len, int64_t block_m, int scale_kind,
     int gate_act, int c_sorted, strix_stream_t stream) {
   STRIX_CHECK(gate_act >= 0 && gate_act <= 2, "activation must be none, silu or gelu_tanh");
+  STRIX_CHECK(num_experts >= 1 && num_experts <= (int64_t(1) << 24), "num_experts out of range");
   STRIX_CHECK(sorted_covers(n, k, block_m, gate_act, scale_kind),
               "geometry not covered: block_m in 16/32/64/128, K %% 128, K <= 8192 (4096 at 128 "
               "tokens), whole 128-row weight tiles, channel or 128x128 block scales");
@@ -882,28 +877,18 @@ extern "C" int strix_moe_gemm_fp8_sorted(
   p.topk_w = topk_weights;
   p.status = umma_status_ptr();
   STRIX_CHECK(p.status != nullptr, "status word unavailable");
-  static const bool profiling = getenv("STRIX_UMMA_PROF") != nullptr;
-  p.prof = nullptr;
-  if (profiling) {
-    void* prof_addr = nullptr;
-    STRIX_CUDA(cudaGetSymbolAddress(&prof_addr, g_umma_prof));
-    p.prof = static_cast<long long*>(prof_addr);
-  }
   p.num_valid = num_valid;
   p.c_stride = c_stride, p.s_se = s_stride_e, p.s_sn = s_stride_n, p.sa_stride = sa_stride;
-  p.K = int(k), p.N = int(n), p.block_m = int(block_m);
+  p.K = int(k), p.N = int(n), p.block_m = int(block_m), p.experts = int(num_experts);
   p.scale_kind = scale_kind, p.gate_act = gate_act, p.c_sorted = c_sorted;
   p.n_tiles = int(out_rows / tile_out);
-  static const int debug = [] { const char* e = getenv("STRIX_UMMA_DEBUG"); return e ? atoi(e) : 0; }();
-  p.debug = debug;
   static const int prefetch = [] { const char* e = getenv("STRIX_UMMA_PREFETCH"); return e ? atoi(e) : 0; }();
   p.prefetch = prefetch < 0 ? 0 : prefetch > 256 ? 256 : prefetch;
   // Weights as a 4-d byte tensor (k, half, row, expert): under the fused gate
   // `half` steps from the gate rows to the up rows, so a box of 2 x 64 rows lands
-  // as gate row i / up row i alternating; otherwise it has extent 1. The expert
-  // extent is an upper bound (expert ids index it).
+  // as gate row i / up row i alternating; otherwise it has extent 1.
   const uint64_t halves = gate_act ? 2 : 1, rows = uint64_t(out_rows);
-  const uint64_t dims[4] = {uint64_t(k), halves, rows, uint64_t(1) << 16};
+  const uint64_t dims[4] = {uint64_t(k), halves, rows, uint64_t(num_experts)};
   const uint64_t strides[3] = {uint64_t(w_stride_n) * rows, uint64_t(w_stride_n), uint64_t(w_stride_e)};
   const uint32_t box[4] = {128, uint32_t(halves), uint32_t(tile_out), 1};
   CUtensorMap map_w, map_a;
@@ -918,16 +903,6 @@ extern "C" int strix_moe_gemm_fp8_sorted(
   if (block_m == 32) return short_k ? launch_umma<32, 16>(p, map_w, map_a, st) : launch_umma<32, 64>(p, map_w, map_a, st);
   if (block_m == 64) return short_k ? launch_umma<64, 16>(p, map_w, map_a, st) : launch_umma<64, 64>(p, map_w, map_a, st);
   return short_k ? launch_umma<128, 16>(p, map_w, map_a, st) : launch_umma<128, 32>(p, map_w, map_a, st);
-}
-
-extern "C" int strix_umma_prof(int64_t* host_out8, int reset) {
-  STRIX_CHECK(host_out8 != nullptr, "host_out8 must not be NULL");
-  STRIX_CUDA(cudaMemcpyFromSymbol(host_out8, strix::g_umma_prof, 8 * sizeof(long long)));
-  if (reset) {
-    const long long zeros[8] = {};
-    STRIX_CUDA(cudaMemcpyToSymbol(strix::g_umma_prof, zeros, sizeof(zeros)));
-  }
-  return STRIX_OK;
 }
 
 extern "C" int strix_umma_status(int32_t* host_out) {

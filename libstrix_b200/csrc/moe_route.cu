@@ -122,6 +122,12 @@ __global__ void __launch_bounds__(kAlignThreads) moe_align_kernel(
   const int base = s_base;
   if (e == experts) {
     if (tid == 0) num_post[0] = base;
+    // slots whose id names no expert (masked, -1) have no position
+    if (slot_pos != nullptr)
+      for (int i = tid; i < numel; i += kAlignThreads) {
+        const int id = topk_ids[i];
+        if (id < 0 || id >= experts) slot_pos[i] = -1;
+      }
     for (int i = base + tid; i < cap; i += kAlignThreads) sorted_ids[i] = numel;
     for (int i = base / block_m + tid; i < cap_blocks; i += kAlignThreads) expert_ids[i] = -1;
     return;
@@ -284,9 +290,9 @@ __global__ void __launch_bounds__(256) act_quant_scatter_kernel(
   float amax = 0.f;
 #pragma unroll
   for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-#pragma unroll
   // only this team's 16 lanes take part: the other half of the warp may be a padding team
   const unsigned team_mask = 0xffffu << (threadIdx.x & 16);
+#pragma unroll
   for (int o = 8; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(team_mask, amax, o, 16));
   const float s = amax > 0.f ? __fdiv_rn(amax, 448.f) : 1.f;
   uint32_t h[4];
@@ -374,6 +380,7 @@ __global__ void __launch_bounds__(256) ep_pack_kernel(
   if (i >= slots) return;
   const int ch = int(idx % chunks);
   const int slot = order[i];
+  if (slot < 0 || slot >= slots) return;   // a position no valid slot was sorted into
   send[i * send_st16 + ch] = x[int64_t(slot / top_k) * x_st16 + ch];
   if (ch == 0) meta[i * meta_st2] = make_float2(float(topk_ids[slot] % experts_per_rank), topk_w[slot]);
 }

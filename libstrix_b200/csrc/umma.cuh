@@ -9,8 +9,10 @@
 //     boundaries. This is the layout a TMA copy with 128-byte swizzle writes,
 //     and the kernels that gather rows write the same layout with cp.async;
 //   * every wait on an mbarrier is bounded: after kSpinLimit polls the waiter
-//     gives up, records a status word and the kernel drains and returns, so a
-//     protocol bug can never hang the device.
+//     gives up, records a status word and raises the CTA's abort flag; every role
+//     then leaves its loop, the producer waits for the copies it armed and the
+//     issuers for the MMAs they issued (drain_armed_loads / drain_issued_mmas),
+//     and only then is TMEM freed, so a protocol bug can never hang the device.
 #pragma once
 
 #include "common.cuh"
@@ -242,6 +244,24 @@ __device__ __forceinline__ void mma_ss_lo(uint32_t tmem_d, uint32_t a_lo, uint32
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "n"(ACC ? 1 : 0)
         : "memory");
   }
+}
+
+// Teardown after a bounded wait gave up (a role set the CTA's abort flag). A CTA
+// must not free TMEM or exit while bulk copies it armed can still write its
+// shared memory or MMAs it issued can still write TMEM, so before the final
+// barrier the producing thread waits (bounded again) for the last `stages`
+// stages it armed, and every issuing thread commits to a barrier of its own and
+// waits for it: tcgen05.commit arrives once all MMAs that thread issued retired.
+__device__ __forceinline__ void drain_armed_loads(uint64_t* full_bar, int stages, int armed) {
+  const int n = armed < stages ? armed : stages;
+  for (int i = 0; i < n; ++i) {
+    const int t = armed - 1 - i;
+    mbar_wait(&full_bar[t % stages], (t / stages) & 1);
+  }
+}
+__device__ __forceinline__ void drain_issued_mmas(uint64_t* drain_bar) {
+  mma_commit(drain_bar);
+  mbar_wait(drain_bar, 0);
 }
 
 // Byte offset of 16-byte chunk `chunk` of row `row` inside a swizzled tile.

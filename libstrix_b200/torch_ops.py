@@ -436,7 +436,7 @@ def moe_gemm_fp8_sorted(c, qa, sa, b, scales, sorted_ids, expert_ids, num_post_p
     with torch.cuda.device(c.device):
         _lib.call("strix_moe_gemm_fp8_sorted", c.data_ptr(), qa.data_ptr(), sa.data_ptr(),
                   b.data_ptr(), scales.data_ptr(), sorted_ids.data_ptr(), expert_ids.data_ptr(),
-                  num_post_padded.data_ptr(), _ptr(topk_weights), num_valid, n, k, qa.stride(0),
+                  num_post_padded.data_ptr(), _ptr(topk_weights), num_valid, e, n, k, qa.stride(0),
                   c.stride(0), b.stride(0), b.stride(1), scales.stride(0), s_sn, sa.stride(0),
                   sorted_len, block_m, scale_kind, _ACTS[activation] if silu_mul else 0,
                   int(c_sorted), _stream())
@@ -607,7 +607,7 @@ def moe_gemm_mxfp4_sorted(c, a, b, scales, sorted_ids, expert_ids, num_post_padd
     with torch.cuda.device(c.device):
         _lib.call("strix_moe_gemm_mxfp4_sorted", c.data_ptr(), a.data_ptr(), b.data_ptr(),
                   scales.data_ptr(), sorted_ids.data_ptr(), expert_ids.data_ptr(),
-                  num_post_padded.data_ptr(), _ptr(topk_weights), num_valid, n, k, a.stride(0),
+                  num_post_padded.data_ptr(), _ptr(topk_weights), num_valid, e, n, k, a.stride(0),
                   c.stride(0), b.stride(0), b.stride(1), scales.stride(0), scales.stride(1),
                   sorted_len, block_m, _ACTS[activation] if silu_mul else 0, int(c_sorted), _stream())
 

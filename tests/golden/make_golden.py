@@ -118,7 +118,80 @@ def golden_moe() -> None:
     torch.save(out, OUT / "moe.pt")
 
 
-GENERATORS = {"attn_decode": golden_attn_decode, "moe": golden_moe}
+def golden_gemm() -> None:
+    """The in-test reference functions of the dense and 4-bit ops evaluated on
+    seeded inputs: torch_dequant() of tests/test_mxfp4.py:28-45, pack() and
+    dequant() of tests/test_moe_wna16.py:44-62, reference() of
+    tests/test_w8a16.py:9-17 and of tests/test_w8a8_int8.py:50-57, ref_weight()
+    of tests/test_fp8.py:17-20. The activation quantiser of
+    tests/test_moe_w4a8.py:24-36 has its expectation inline in a test function;
+    that function is run here with torch.ops.strix.moe_act_quant_i8 served by the
+    oracle, so the stored vector is one the reference's own test accepted."""
+    root = Path(__file__).resolve().parents[2]
+    if str(root) not in sys.path:
+        sys.path.insert(0, str(root))
+    from oracle import moe as M
+
+    mx = load_reference_test("test_mxfp4")
+    wna = load_reference_test("test_moe_wna16")
+    sys.modules["test_moe_wna16"] = wna
+    w8a16 = load_reference_test("test_w8a16")
+    w8a8 = load_reference_test("test_w8a8_int8")
+    fp8 = load_reference_test("test_fp8")
+    w4a8 = load_reference_test("test_moe_w4a8")
+    g = torch.Generator().manual_seed(0)
+    out = {}
+
+    w = torch.randint(0, 256, (48, 80), generator=g, dtype=torch.uint8)        # K = 160
+    s = torch.randint(118, 134, (48, 5), generator=g, dtype=torch.uint8)
+    out["mxfp4"] = {"w": w, "s": s, "deq": mx.torch_dequant(w, s),
+                    "lut": torch.tensor(mx.MX_VALUES)}
+
+    out["int4"] = []
+    for group, sdt in ((32, torch.bfloat16), (64, torch.float16), (128, torch.bfloat16)):
+        q = torch.randint(0, 16, (3, 24, 256), generator=g, dtype=torch.uint8)
+        sc = (torch.rand(3, 24, 256 // group, generator=g) * 0.05 + 0.01).to(sdt)
+        packed = wna.pack(q)
+        out["int4"].append({"q": q, "packed": packed, "scales": sc, "group": group,
+                            "deq": wna.dequant(packed, sc, group)})
+
+    out["w8a16"] = []
+    for group in (0, 128):
+        x = torch.randn(5, 384, generator=g).bfloat16()
+        wu = torch.randint(0, 256, (40, 384), generator=g, dtype=torch.uint8)
+        sc = (torch.rand(40, 384 // group if group else 1, generator=g) * 0.01).bfloat16()
+        if group == 0:
+            sc = sc.reshape(40)
+        out["w8a16"].append({"x": x, "w": wu, "scales": sc, "group": group,
+                             "out": w8a16.reference(x, wu, sc, group)})
+
+    x = torch.randn(7, 512, generator=g).bfloat16()
+    x[2, 128:256] = 0
+    wi = torch.randint(-127, 128, (24, 512), generator=g, dtype=torch.int8)
+    sw = (torch.rand(24, 1, generator=g) * 0.01 + 1e-4).float()
+    out["w8a8_group"] = {"x": x, "w": wi, "scale": sw, "out": w8a8.reference(x, wi, sw)}
+
+    wq = (torch.randn(200, 256, generator=g) * 40).clamp(-448, 448).to(torch.float8_e4m3fn)
+    bs = torch.rand(2, 2, generator=g) * 0.02 + 0.005
+    out["fp8_block"] = {"w": wq.view(torch.uint8), "scales": bs, "deq": fp8.ref_weight(wq, bs)}
+
+    # the reference's own acceptance test of the activation quantiser, over the oracle
+    seen = {}
+    lib = torch.library.Library("strix", "DEF")
+    lib.define("moe_act_quant_i8(Tensor x, Tensor(a!) q, Tensor(b!) sa) -> ()")
+
+    def impl(x, q, sa):
+        qq, ss = M.act_quant_i8(x)
+        q.copy_(qq), sa.copy_(ss)
+        seen.update(x=x.clone(), q=qq.clone(), sa=ss.clone())
+
+    lib.impl("moe_act_quant_i8", impl, "CPU")
+    w4a8.test_act_quant_matches_reference()          # raises if the oracle breaks the reference's rule
+    out["act_quant_i8"] = dict(seen, accepted_by="tests/test_moe_w4a8.py:24-36")
+    torch.save(out, OUT / "gemm.pt")
+
+
+GENERATORS = {"attn_decode": golden_attn_decode, "moe": golden_moe, "gemm": golden_gemm}
 
 if __name__ == "__main__":
     wanted = sys.argv[1:] or list(GENERATORS)

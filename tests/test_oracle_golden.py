@@ -89,3 +89,36 @@ def test_router_oracle_properties():
     # the chosen experts are the 8 largest logits of each row, in descending order
     want = torch.sort(logits, dim=-1, descending=True).indices[:, :8]
     assert torch.equal(ids.long(), want)
+
+
+def test_gemm_oracle_matches_reference_outputs():
+    """oracle/gemm.py and the activation quantiser against vectors produced by the
+    reference's own in-test functions (tests/golden/make_golden.py::golden_gemm)."""
+    from oracle import gemm as G
+    from oracle import moe as M
+
+    gold = torch.load(GOLDEN / "gemm.pt")
+    c = gold["mxfp4"]
+    assert tuple(c["lut"].tolist()) == G.MX_VALUES
+    assert torch.equal(G.mxfp4_dequant(c["w"], c["s"]), c["deq"])
+    for c in gold["int4"]:
+        assert torch.equal(G.int4_pack(c["q"]), c["packed"])
+        # groups that are a multiple of 64 are judged against the exact fp32 weights
+        # (tests/test_moe_wna16.py:52-62), the others against their bf16 rounding
+        deq = G.int4_dequant(c["packed"], c["scales"], c["group"], exact=c["group"] % 64 == 0)
+        assert deq.dtype == c["deq"].dtype and torch.equal(deq, c["deq"])
+    for c in gold["w8a16"]:
+        out = G.w8a16_reference(c["x"], c["w"], c["scales"], c["group"])
+        torch.testing.assert_close(out, c["out"], rtol=0, atol=0)
+    c = gold["w8a8_group"]
+    torch.testing.assert_close(G.w8a8_group_reference(c["x"], c["w"], c["scale"]), c["out"],
+                               rtol=0, atol=0)
+    c = gold["fp8_block"]
+    w = c["w"].view(torch.float8_e4m3fn)
+    assert torch.equal(G.fp8_dequant(w, c["scales"]), c["deq"])
+    c = gold["act_quant_i8"]
+    q, s = M.act_quant_i8(c["x"])
+    assert torch.equal(q, c["q"]) and torch.equal(s, c["sa"])
+    # the dense op's in-kernel quantiser follows the same rule
+    q2, s2 = G.act_quant_group_i8(c["x"])
+    assert torch.equal(s2, c["sa"]) and int((q2.int() - c["q"].int()).abs().max()) <= 1
