@@ -405,6 +405,30 @@ int strix_moe_gemm_fp8_sorted(void* c, const void* a, const float* act_scales, c
 int strix_moe_gemm_fp8_sorted_covers(int64_t n, int64_t k, int64_t block_m, int gate_act,
                                      int scale_kind);
 
+/* Writes new keys and values into the int8 paged KV cache with one fp32
+ * dequant scale per (token, KV head) - the step before every attention call.
+ * The reference leaves it to vLLM; its semantics are pinned by quantize() of
+ * the reference's tests/test_attn_prefill.py:202-206 and the consumer views by
+ * python/strix_vllm/attn.py:185-203. key / value: bf16 (fp16 if in_f16)
+ * [tokens, hkv, head_dim] with element strides over tokens and heads;
+ * slot_mapping int64 [tokens]: cache slot (block * block_size + offset) of each
+ * token, negative = skip. Caches are bytes [blocks, block_size, hkv, >= head_dim]
+ * with BYTE strides (multiples of 4), scales fp32 [blocks, block_size, hkv] with
+ * element strides - contiguous tensors, or views into a packed cache whose head
+ * rows carry the scale inline after the bytes.
+ * rule 0: scale = max(absmax, 1e-8) / 127, q = clamp(rint(x / scale), +-127);
+ * rule 1 (vLLM 0.22's writer): scale = max(absmax / 127, 1e-6),
+ * q = trunc(clamp(x * (1 / scale), -128, 127)). */
+int strix_kv_write_i8(const void* key, const void* value, void* key_cache, void* value_cache,
+                      float* k_scale, float* v_scale, const int64_t* slot_mapping,
+                      int64_t tokens, int64_t hkv, int64_t head_dim, int64_t block_size,
+                      int64_t key_stride_t, int64_t key_stride_h, int64_t value_stride_t,
+                      int64_t value_stride_h, int64_t k_stride_b, int64_t k_stride_s,
+                      int64_t k_stride_h, int64_t v_stride_b, int64_t v_stride_s,
+                      int64_t v_stride_h, int64_t ks_stride_b, int64_t ks_stride_s,
+                      int64_t ks_stride_h, int64_t vs_stride_b, int64_t vs_stride_s,
+                      int64_t vs_stride_h, int in_f16, int rule, strix_stream_t stream);
+
 /* strix_attn_decode_bf16 without a workspace argument, for callers that cannot
  * allocate device memory: a host loop that owns nothing but the input and
  * output buffers it was given, or a process whose device memory was budgeted

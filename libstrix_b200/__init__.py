@@ -94,6 +94,40 @@ def attn_prefill(
     return out
 
 
+def kv_write_int8(key, value, key_cache, value_cache, k_scale, v_scale, slot_mapping,
+                  rule: str = "reference") -> None:
+    """Quantises new K/V rows ([tokens, Hkv, D] bf16/fp16) per (token, head) into
+    the int8 paged cache ([blocks, block_size, Hkv, >= D] views) and writes their
+    fp32 scales ([blocks, block_size, Hkv] views); slot_mapping int64 [tokens]
+    gives each token's slot, negative = skip. The reference leaves this step to
+    vLLM; rule "reference" is quantize() of its tests/test_attn_prefill.py:202-206,
+    "vllm" the rule of vLLM 0.22's int8_per_token_head writer."""
+    torch.ops.strix.kv_write_i8(key, value, key_cache, value_cache, k_scale, v_scale,
+                                slot_mapping.to(torch.int64), rule)
+
+
+def packed_int8_kv_views(kv_cache: torch.Tensor):
+    """(key_cache, value_cache, k_scale, v_scale) views of vLLM 0.22's packed
+    int8_per_token_head cache [blocks, 2, block_size, Hkv, D + 4] (int8; the last
+    four bytes of every head row hold its fp32 scale): byte views [blocks,
+    block_size, Hkv, D] and strided fp32 views [blocks, block_size, Hkv]. The
+    reference's plugin carves the same views (python/strix_vllm/attn.py:185-203)."""
+    assert kv_cache.dtype == torch.int8 and kv_cache.dim() == 5 and kv_cache.size(1) == 2
+    blocks, _, bs, hkv, padded = kv_cache.shape
+    d = padded - 4
+    key_cache, value_cache = kv_cache[:, 0, :, :, :d], kv_cache[:, 1, :, :, :d]
+    f32 = torch.empty(0, dtype=torch.float32, device=kv_cache.device).set_(kv_cache.untyped_storage())
+    st = kv_cache.stride()
+    base = kv_cache.storage_offset()
+    assert all(x % 4 == 0 for x in (st[0], st[1], st[2], st[3], base, d)), "cache not 4-byte aligned"
+
+    def scales(half):
+        return torch.as_strided(f32, (blocks, bs, hkv), (st[0] // 4, st[2] // 4, st[3] // 4),
+                                (base + half * st[1] + d) // 4)
+
+    return key_cache, value_cache, scales(0), scales(1)
+
+
 __all__ = [
     "attn_prefill",
     "Range",
@@ -103,8 +137,10 @@ __all__ = [
     "geometries",
     "is_supported_device",
     "kernels",
+    "kv_write_int8",
     "moe",
     "ops",
+    "packed_int8_kv_views",
     "select",
     "selections",
 ]

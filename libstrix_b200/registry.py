@@ -288,6 +288,13 @@ KERNELS: list[Kernel] = [
             "pipeline": "4 producer warps (cp.async ring, 128B swizzle), 1 issuing thread, "
                         "4 epilogue warps, 2 TMEM accumulators, persistent grid"}),
     # ------------------------------------------------------------ attention
+    Kernel("kv_write_i8", "kv_write",
+           "new K/V rows quantised per (token, KV head) into the int8 paged cache with their "
+           "fp32 scales; separate scale tensors or the packed layout with the scale inline "
+           "after each head's bytes (through strides)",
+           {"dtype": ("bf16", "fp16"), "kv_dtype": "int8", "head_dim": Range(8, 512),
+            "rule": ("reference", "vllm")},
+           {"unit": "one warp per (token, head, K or V)", "bound": "hbm"}),
     _decode_row(
         128, 8,
         "one query per sequence over an int8_per_token_head paged cache: 16-key "

@@ -125,6 +125,36 @@ def attn_decode_bf16(
         )
 
 
+# Not in the reference (vLLM's reshape_and_cache does it there): quantise new K/V
+# rows per (token, head) into the int8 paged cache; rule "reference" is quantize()
+# of tests/test_attn_prefill.py:202-206, "vllm" the rule of vLLM 0.22's writer.
+@_define("kv_write_i8(Tensor key, Tensor value, Tensor(a!) key_cache, Tensor(b!) value_cache, "
+         "Tensor(c!) k_scale, Tensor(d!) v_scale, Tensor slot_mapping, str rule='reference') -> ()")
+def kv_write_i8(key, value, key_cache, value_cache, k_scale, v_scale, slot_mapping,
+                rule="reference"):
+    _check(key.dim() == 3 and value.dim() == 3 and key.shape == value.shape,
+           "key / value must be [tokens, Hkv, D]")
+    _check(key.dtype in (torch.bfloat16, torch.float16) and value.dtype == key.dtype
+           and key.stride(-1) == 1 and value.stride(-1) == 1, "key / value bf16 or fp16, contiguous D")
+    t, hkv, d = key.shape
+    for c in (key_cache, value_cache):
+        _check(c.dim() == 4 and c.dtype == torch.int8 and c.size(2) == hkv and c.size(3) >= d
+               and c.stride(3) == 1, "caches must be int8 [blocks, block_size, Hkv, >= D]")
+    for sc in (k_scale, v_scale):
+        _check(sc.dtype == torch.float32 and tuple(sc.shape) == tuple(key_cache.shape[:3]),
+               "scales must be fp32 [blocks, block_size, Hkv]")
+    _check(slot_mapping.dtype == torch.int64 and slot_mapping.is_contiguous()
+           and slot_mapping.numel() >= t, "slot_mapping must be contiguous int64 [tokens]")
+    _check(rule in ("reference", "vllm"), "rule must be 'reference' or 'vllm'")
+    with torch.cuda.device(key.device):
+        _lib.call("strix_kv_write_i8", key.data_ptr(), value.data_ptr(), key_cache.data_ptr(),
+                  value_cache.data_ptr(), k_scale.data_ptr(), v_scale.data_ptr(),
+                  slot_mapping.data_ptr(), t, hkv, d, key_cache.size(1), key.stride(0),
+                  key.stride(1), value.stride(0), value.stride(1), *key_cache.stride()[:3],
+                  *value_cache.stride()[:3], *k_scale.stride(), *v_scale.stride(),
+                  int(key.dtype == torch.float16), 0 if rule == "reference" else 1, _stream())
+
+
 @_define(
     "attn_prefill_bf16(Tensor(a!) out, Tensor q, Tensor key_cache, "
     "Tensor value_cache, Tensor? k_scale, Tensor? v_scale, "

@@ -45,6 +45,18 @@ def quantize_kv(cache: torch.Tensor):
     return q, s.contiguous()
 
 
+def quantize_kv_vllm(cache: torch.Tensor):
+    """The rule of vLLM 0.22's int8_per_token_head cache writer
+    (vllm/v1/attention/ops/triton_reshape_and_cache_flash.py, the third-party
+    dependency that writes the cache in a deployment): scale = max(absmax / 127,
+    1e-6), q = x * (1 / scale) clamped to [-128, 127] and converted to int8 by
+    truncation. Parity unpinned: that Triton kernel cannot run without a GPU,
+    so this restates its source."""
+    s = (cache.abs().amax(-1).float() / 127.0).clamp_min(1e-6)
+    q = (cache.float() * (1.0 / s)[..., None]).clamp(-128, 127).trunc().to(torch.int8)
+    return q, s.contiguous()
+
+
 def attention_reference(q, key_cache, value_cache, cu, seq_lens, table, scale,
                         window_left=-1, sinks=None):
     """Dense causal softmax attention over the gathered pages, fp32.
