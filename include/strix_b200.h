@@ -405,6 +405,32 @@ int strix_moe_gemm_fp8_sorted(void* c, const void* a, const float* act_scales, c
 int strix_moe_gemm_fp8_sorted_covers(int64_t n, int64_t k, int64_t block_m, int gate_act,
                                      int scale_kind);
 
+/* strix_attn_prefill_bf16 on the tcgen05 tensor cores (S and O in tensor memory,
+ * TMA-fed operands): same contract and arguments (attn_prefill_bf16 of the
+ * reference, csrc/attn/attn_prefill_bf16.hip:508-662), for head_dim 64 / 128 with
+ * 16-byte aligned q / out rows (strix_attn_prefill_umma_covers() tells, 1/0). A
+ * first kernel gathers the batch's keys and values from the pages into a
+ * contiguous 16-bit workspace (int8 caches dequantised with their scales, each
+ * sequence padded to 128 keys); the caller provides it: `workspace` 1024-byte
+ * aligned, at least strix_attn_prefill_workspace(nseq, max_blocks, block_size,
+ * hkv, head_dim) bytes, where max_blocks is the block table's row length. The
+ * dequantised values must fit fp16. num_splits does not apply. */
+int64_t strix_attn_prefill_workspace(int64_t nseq, int64_t max_blocks, int64_t block_size,
+                                     int64_t hkv, int64_t head_dim);
+int strix_attn_prefill_umma_covers(int64_t head_dim, int64_t q_stride_t, int64_t q_stride_h,
+                                   int64_t out_stride_t, int64_t out_stride_h, int kv_int8);
+int strix_attn_prefill_umma(
+    void* out, const void* q, const void* key_cache, const void* value_cache, const float* k_scale,
+    const float* v_scale, const int32_t* cu_seqlens_q, const int32_t* seq_lens,
+    const int32_t* block_table, const float* sinks, void* workspace, int64_t workspace_bytes,
+    int64_t total_q, int64_t nseq, int64_t hq, int64_t hkv, int64_t head_dim, int64_t block_size,
+    int64_t max_blocks, int64_t bt_stride, int64_t q_stride_t, int64_t q_stride_h,
+    int64_t out_stride_t, int64_t out_stride_h, int64_t k_stride_b, int64_t k_stride_s,
+    int64_t k_stride_h, int64_t v_stride_b, int64_t v_stride_s, int64_t v_stride_h,
+    int64_t ks_stride_b, int64_t ks_stride_s, int64_t ks_stride_h, int64_t vs_stride_b,
+    int64_t vs_stride_s, int64_t vs_stride_h, double scale, int64_t window_left, int kv_int8,
+    strix_stream_t stream);
+
 /* Writes new keys and values into the int8 paged KV cache with one fp32
  * dequant scale per (token, KV head) - the step before every attention call.
  * The reference leaves it to vLLM; its semantics are pinned by quantize() of

@@ -11,9 +11,15 @@ NotImplementedError from the dispatcher.
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _lib
+
+# Which prefill-attention kernel attn_prefill_bf16 runs: "auto" = the tcgen05 kernel
+# where it covers the geometry, else the mma.sync kernel; "umma" / "mma" force one.
+PREFILL_IMPL = os.environ.get("STRIX_PREFILL_IMPL", "auto")
 
 _LIBRARY = torch.library.Library("strix", "DEF")
 _registered: list[str] = []
@@ -196,6 +202,32 @@ def attn_prefill_bf16(out, q, key_cache, value_cache, k_scale, v_scale, cu_seqle
                and sinks.is_contiguous(), "sinks must be contiguous fp32 [Hq]")
     ks = k_scale if q8 else None
     vs = v_scale if q8 else None
+    nseq, hkv, bs, max_blocks = cu_seqlens_q.numel() - 1, key_cache.size(2), key_cache.size(1), \
+        block_table.size(1)
+    lib = _lib.load()
+    umma = PREFILL_IMPL != "mma" and bool(lib.strix_attn_prefill_umma_covers(
+        d, q.stride(0), q.stride(1), out.stride(0), out.stride(1), int(q8))) \
+        and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0
+    _check(umma or PREFILL_IMPL != "umma", "the tcgen05 prefill kernel does not cover this geometry")
+    if umma and nseq > 0 and q.size(0) > 0:
+        # tensor-core path: the batch's keys and values are gathered (int8: dequantised) once
+        # into a contiguous 16-bit workspace, which the attention kernel reads by TMA
+        ws_bytes = lib.strix_attn_prefill_workspace(nseq, max_blocks, bs, hkv, d)
+        with torch.cuda.device(q.device):
+            ws = torch.empty(ws_bytes + 1024, dtype=torch.uint8, device=q.device)
+            ws_ptr = (ws.data_ptr() + 1023) // 1024 * 1024
+            _lib.call(
+                "strix_attn_prefill_umma",
+                out.data_ptr(), q.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(), _ptr(ks),
+                _ptr(vs), cu_seqlens_q.data_ptr(), seq_lens.data_ptr(), block_table.data_ptr(),
+                _ptr(sinks), ws_ptr, ws_bytes, q.size(0), nseq, q.size(1), hkv, d, bs, max_blocks,
+                block_table.stride(0), q.stride(0), q.stride(1), out.stride(0), out.stride(1),
+                key_cache.stride(0), key_cache.stride(1), key_cache.stride(2),
+                value_cache.stride(0), value_cache.stride(1), value_cache.stride(2),
+                *(ks.stride() if q8 else (0, 0, 0)), *(vs.stride() if q8 else (0, 0, 0)),
+                float(scale), window_left, int(q8), _stream(),
+            )
+        return
     with torch.cuda.device(q.device):
         _lib.call(
             "strix_attn_prefill_bf16",

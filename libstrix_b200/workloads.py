@@ -156,3 +156,93 @@ def moe_fp8_layer(tokens=256, hidden=2048, experts=128, top_k=8, inter=768, seed
     w13, s13 = weights(2 * inter, hidden)
     w2, s2 = weights(hidden, inter)
     return MoeFp8Layer(x, logits, w13, s13, w2, s2, top_k)
+
+
+# ------------------------------------------------------------------ MXFP4 (config 5)
+def quantize_mxfp4(w: torch.Tensor):
+    """fp32 [..., K] (K % 32 == 0) -> (uint8 [..., K/2], uint8 e8m0 scales [..., K/32]).
+
+    Per 32 elements the scale is the power of two 2^ceil(log2(amax / 6)) (byte =
+    exponent + 127; an all-zero group takes byte 0, the zero block), the elements
+    are x / scale rounded to nearest-even onto the e2m1 grid {0, .5, 1, 1.5, 2, 3,
+    4, 6} with a sign bit, and byte j holds element 2j in its low nibble - the
+    layout csrc/gemm/mxfp4_wmma_gemm.hip:14-23,38-57 of the reference decodes."""
+    k = w.size(-1)
+    g = w.float().reshape(*w.shape[:-1], k // 32, 32)
+    amax = g.abs().amax(-1)
+    m, ex = torch.frexp(amax / 6.0)                 # amax / 6 = m * 2^ex, m in [0.5, 1)
+    e = torch.where(m > 0.5, ex, ex - 1)            # ceil(log2(.))
+    byte = torch.where(amax > 0, (e + 127).clamp(1, 254), torch.zeros_like(e))
+    scale = torch.ldexp(torch.ones_like(amax), byte - 127)
+    x = (g / scale[..., None]).abs()
+    # thresholds are the midpoints of the grid; a tie goes to the even mantissa
+    code = ((x > 0.25).to(torch.uint8) + (x >= 0.75) + (x > 1.25) + (x >= 1.75) + (x > 2.5)
+            + (x >= 3.5) + (x > 5.0)).to(torch.uint8)
+    code = code | ((g < 0).to(torch.uint8) << 3)
+    code = torch.where((byte == 0)[..., None], torch.zeros_like(code), code).reshape(*w.shape[:-1], k)
+    packed = code[..., 0::2] | (code[..., 1::2] << 4)
+    return packed.contiguous(), byte.to(torch.uint8).contiguous()
+
+
+def zipf_bias(experts: int, alpha: float = 1.1, seed: int = 7, device="cpu") -> torch.Tensor:
+    """log of Zipf(alpha) weights over the experts, randomly permuted: the
+    per-expert router bias that skews the load of config 5."""
+    ranks = torch.arange(1, experts + 1, dtype=torch.float32)
+    wts = ranks.pow(-alpha)
+    bias = torch.log(wts / wts.sum())
+    perm = torch.randperm(experts, generator=torch.Generator().manual_seed(seed))
+    return bias[perm].to(device)
+
+
+@dataclass
+class MoeMxfp4Layer:
+    """One MXFP4 MoE layer (benchmark config 5), or a rank's expert shard of it."""
+
+    x: torch.Tensor          # bf16 [T, H]
+    logits: torch.Tensor     # fp32 [T, E_global]
+    w13: torch.Tensor        # uint8 [E, 2I, H/2]   rows [gate; up], e2m1 nibbles
+    w13_scale: torch.Tensor  # uint8 [E, 2I, H/32]  e8m0
+    w2: torch.Tensor         # uint8 [E, H, I/2]
+    w2_scale: torch.Tensor   # uint8 [E, H, I/32]
+    top_k: int
+
+    def to(self, device) -> "MoeMxfp4Layer":
+        return MoeMxfp4Layer(*[
+            v.to(device) if isinstance(v, torch.Tensor) else v for v in self.__dict__.values()
+        ])
+
+    @property
+    def flops(self) -> int:
+        t, h = self.x.shape
+        n13 = self.w13_scale.size(1)
+        return 2 * t * self.top_k * (n13 * h + h * (n13 // 2))
+
+
+def moe_mxfp4_layer(tokens=8192, hidden=2880, experts=128, top_k=4, inter=2880, seed=0,
+                    device="cpu", expert_lo=0, expert_hi=None, token_lo=0, token_hi=None,
+                    zipf_alpha: float | None = 1.1) -> MoeMxfp4Layer:
+    """Config 5: x bf16 ~ N(0,1); router logits N(0,1) plus a Zipf(1.1) per-expert
+    bias; weights N(0, 0.02) quantised to MXFP4 (quantize_mxfp4). Every expert
+    and every token block has its own generator seed, so a rank can build only
+    its experts [expert_lo, expert_hi) and tokens [token_lo, token_hi) and still
+    hold exactly the slices of the one global layer (token blocks of 256)."""
+    expert_hi = experts if expert_hi is None else expert_hi
+    token_hi = tokens if token_hi is None else token_hi
+    assert token_lo % 256 == 0 and (token_hi % 256 == 0 or token_hi == tokens)
+    xs, ls = [], []
+    bias = zipf_bias(experts, zipf_alpha, device=device) if zipf_alpha is not None else 0.0
+    for t0 in range(token_lo, token_hi, 256):
+        g = torch.Generator(device=device).manual_seed(seed * 1_000_003 + 17 + t0)
+        n = min(256, tokens - t0)
+        xs.append(torch.randn(n, hidden, generator=g, device=device).bfloat16())
+        ls.append(torch.randn(n, experts, generator=g, device=device) + bias)
+    e_n = expert_hi - expert_lo
+    w13 = torch.empty(e_n, 2 * inter, hidden // 2, dtype=torch.uint8, device=device)
+    s13 = torch.empty(e_n, 2 * inter, hidden // 32, dtype=torch.uint8, device=device)
+    w2 = torch.empty(e_n, hidden, inter // 2, dtype=torch.uint8, device=device)
+    s2 = torch.empty(e_n, hidden, inter // 32, dtype=torch.uint8, device=device)
+    for i, e in enumerate(range(expert_lo, expert_hi)):
+        g = torch.Generator(device=device).manual_seed(seed * 1_000_003 + 1_000 + e)
+        w13[i], s13[i] = quantize_mxfp4(torch.randn(2 * inter, hidden, generator=g, device=device) * 0.02)
+        w2[i], s2[i] = quantize_mxfp4(torch.randn(hidden, inter, generator=g, device=device) * 0.02)
+    return MoeMxfp4Layer(torch.cat(xs), torch.cat(ls), w13, s13, w2, s2, top_k)

@@ -78,6 +78,35 @@ def mxfp4_dequant(w_u8: torch.Tensor, s_u8: torch.Tensor) -> torch.Tensor:
     return out * scale.repeat_interleave(32, dim=-1)
 
 
+def mxfp4_quantize(w: torch.Tensor):
+    """fp32 [..., K] -> (uint8 [..., K/2] e2m1 nibbles, uint8 [..., K/32] e8m0), the
+    quantiser benchmark config 5 states: per 32 elements scale = 2^ceil(log2(amax
+    / 6)), elements rounded to the nearest e2m1 value (ties to the even mantissa),
+    low nibble = even k. Written as a nearest-neighbour search over the decode
+    table, so that it shares no arithmetic with the threshold form the workload
+    generator uses. The MX format has no counterpart quantiser in the reference
+    (its checkpoints come quantised); the decode it must invert is
+    tests/test_mxfp4.py:28-45."""
+    k = w.size(-1)
+    g = w.float().reshape(*w.shape[:-1], k // 32, 32)
+    amax = g.abs().amax(-1)
+    e = torch.ceil(torch.log2(amax.double() / 6.0))
+    byte = torch.where(amax > 0, (e + 127).clamp(1, 254), torch.zeros_like(e)).to(torch.int64)
+    scale = torch.pow(2.0, (byte - 127).double())
+    x = (g.double() / scale[..., None]).abs()
+    lut = torch.tensor(MX_VALUES, dtype=torch.float64)
+    dist = (x[..., None] - lut).abs()                       # [..., 32, 8]
+    best = dist.min(-1, keepdim=True).values
+    cand = dist == best                                     # one or (on a tie) two codes
+    even = torch.tensor([c % 2 == 0 for c in range(8)])
+    pick_even = (cand & even).any(-1)
+    code = torch.where(pick_even, (cand & even).to(torch.uint8).argmax(-1),
+                       cand.to(torch.uint8).argmax(-1)).to(torch.uint8)
+    code = code | ((g < 0).to(torch.uint8) << 3)
+    code = torch.where((byte == 0)[..., None], torch.zeros_like(code), code).reshape(*w.shape[:-1], k)
+    return (code[..., 0::2] | (code[..., 1::2] << 4)).contiguous(), byte.to(torch.uint8)
+
+
 def int4_pack(q: torch.Tensor) -> torch.Tensor:
     """[..., K] values 0..15 -> [..., K/2] bytes, low nibble = even k
     (tests/test_moe_wna16.py:44-46)."""

@@ -149,3 +149,30 @@ def moe_fp8_layer(x, logits, w13_q, w13_s, w2_q, w2_s, top_k):
     y = grouped_reference(dequant_act(aq, as_), dequant_fp8_block(w2_q, w2_s), ids, 1, wts)
     y = y.to(torch.bfloat16)
     return moe_sum(y.view(x.size(0), top_k, -1)), ids, wts
+
+
+def moe_mxfp4_layer(x, logits, w13, w13_scale, w2, w2_scale, top_k, token_ids=None,
+                    expert_offset=0):
+    """Benchmark config 5 (MXFP4 experts, bf16 activations, W4A16 reading): router
+    -> gate-up GEMM over the exactly dequantised weights -> SiLU-mul rounded to
+    bf16 -> down GEMM x routing weight rounded to bf16 -> fp32 sum over top-k, one
+    bf16 rounding. `token_ids` restricts the evaluation to a sample of tokens (the
+    router still sees every row it is given); the weights are dequantised one
+    expert at a time inside the loop. Weight tensors may hold a contiguous slice
+    of the experts starting at `expert_offset` (slots routed elsewhere must not
+    occur in the sample then). Returns (out bf16 [len(token_ids), H], ids, weights)."""
+    from . import gemm as G
+
+    ids, wts = router(logits, top_k)
+    sel = torch.arange(x.size(0)) if token_ids is None else torch.as_tensor(token_ids)
+    xs, ids_s, wts_s = x[sel].float(), ids[sel].long(), wts[sel]
+    hidden = w2.size(1)
+    y = torch.zeros(sel.numel(), top_k, hidden)
+    for e in ids_s.unique().tolist():
+        tok, slot = (ids_s == e).nonzero(as_tuple=True)
+        le = e - expert_offset
+        h = xs[tok] @ G.mxfp4_dequant(w13[le], w13_scale[le]).t()
+        act = gate_mul(h).to(torch.bfloat16).float()
+        out = act @ G.mxfp4_dequant(w2[le], w2_scale[le]).t()
+        y[tok, slot] = (out * wts_s[tok, slot, None]).to(torch.bfloat16).float()
+    return y.sum(1).to(torch.bfloat16), ids, wts

@@ -15,13 +15,41 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
+LONG = ("test_long_sequence", "test_config4", "test_decode_with_bf16", "test_unbuilt", "test_sinks_refuse")
+
+
+@pytest.fixture(params=["auto", "mma"], autouse=True)
+def prefill_impl(request, monkeypatch):
+    """Every case runs on the tcgen05 kernel ("auto": it covers head 64 / 128 with
+    16-byte aligned rows) and, the short ones, on the mma.sync kernel that serves
+    the remaining layouts."""
+    from libstrix_b200 import torch_ops
+
+    if request.param == "mma" and request.node.name.startswith(LONG):
+        pytest.skip("long cases run once, on the default kernel")
+    monkeypatch.setattr(torch_ops, "PREFILL_IMPL", request.param)
+    return request.param
+
+
+def umma_status():
+    import ctypes
+
+    from libstrix_b200 import _lib
+
+    flag = ctypes.c_int32(-1)
+    assert _lib.load().strix_umma_status(ctypes.byref(flag)) == 0
+    return flag.value
+
+
 def run(q, kc, vc, cu, seq_lens, table, scale, num_splits=1, window_left=-1, ks=None, vs=None,
         sinks=None):
     out = torch.full_like(q, float("nan"), device=DEV)
     d = lambda t: None if t is None else t.to(DEV)  # noqa: E731
     strix.attn_prefill(out, d(q), d(kc), d(vc), d(cu), d(seq_lens), d(table), scale, num_splits,
                        window_left, d(ks), d(vs), d(sinks))
-    return out.float().cpu()
+    res = out.float().cpu()
+    assert umma_status() == 0, "a bounded wait of a tcgen05 kernel gave up"
+    return res
 
 
 def check(out, ref):
@@ -180,3 +208,67 @@ def test_decode_with_bf16_cache(hq, hkv, hd, ctx_lens, window_left):
     strix.attn_decode(out, q.to(DEV), kc.to(DEV), vc.to(DEV), seq_lens.to(DEV), table.to(DEV), scale,
                       1, window_left)
     check(out.float().cpu(), A.attention_reference(q, kc, vc, cu, seq_lens, table, scale, window_left))
+
+
+def test_tcgen05_kernel_is_the_default_for_config4():
+    """head 128 with contiguous rows is covered by the tensor-core kernel."""
+    from libstrix_b200 import _lib
+
+    assert _lib.load().strix_attn_prefill_umma_covers(128, 40 * 128, 128, 40 * 128, 128, 1) == 1
+    assert _lib.load().strix_attn_prefill_umma_covers(256, 8 * 256, 256, 8 * 256, 256, 1) == 0
+    assert _lib.load().strix_attn_prefill_umma_covers(128, 40 * 128 + 2, 128, 40 * 128, 128, 1) == 0
+
+
+@pytest.mark.parametrize("q_lens,ctx_lens", [([300, 1, 257], [0, 511, 130]), ([129], [1000]),
+                                             ([256, 256], [0, 256]), ([513], [0])])
+@pytest.mark.parametrize("int8", [False, True])
+def test_tile_boundaries(q_lens, ctx_lens, int8):
+    """Query counts and contexts around the 128 / 256 tile sizes of the tensor-core
+    kernel (second Q tile empty or ragged, keys ending inside a tile)."""
+    q, kc, vc, cu, seq_lens, table = A.build_paged_kv(q_lens, ctx_lens, 16, 4, 16, hd=128)
+    scale = 128 ** -0.5
+    if int8:
+        kq, ks = A.quantize_kv(kc)
+        vq, vs = A.quantize_kv(vc)
+        out = run(q, kq, vq, cu, seq_lens, table, scale, 1, -1, ks, vs)
+        check(out, dequant_refs(q, kq, ks, vq, vs, cu, seq_lens, table, scale)[0])
+    else:
+        check(run(q, kc, vc, cu, seq_lens, table, scale),
+              A.attention_reference(q, kc, vc, cu, seq_lens, table, scale))
+
+
+def test_lazy_rescale_with_growing_scores():
+    """Scores that keep growing along the keys force the accumulator rescale of the
+    tensor-core kernel (the row maximum moves by far more than 2^8 between tiles)."""
+    t, hq, hkv, hd = 700, 4, 2, 128
+    q, kc, vc, cu, seq_lens, table = A.build_paged_kv([t], [0], hq, hkv, 16, hd=hd)
+    ramp = torch.linspace(0.05, 3.0, t)                  # key j is ~ ramp[j] x a common direction
+    direction = torch.randn(hd, generator=torch.Generator().manual_seed(3))
+    pos = torch.arange(t)
+    blocks = table[0, pos // 16].long()
+    kc[blocks, pos % 16] = (ramp[:, None, None] * direction[None, None, :] * 4).bfloat16().expand(t, hkv, hd)
+    q[:] = (direction * 2).bfloat16()
+    scale = hd ** -0.5
+    check(run(q, kc, vc, cu, seq_lens, table, scale),
+          A.attention_reference(q, kc, vc, cu, seq_lens, table, scale))
+
+
+def test_config4_geometry_65536_tokens_on_a_tile_sample():
+    """Config 4 at full length: one sequence of 65,536 tokens, 40 q / 8 kv heads,
+    head 128, int8 KV. The oracle evaluates every 128th 64-query tile plus the
+    first and the last (a tile = the last 64 queries of a context that ends
+    with it, the chunked-prefill reading of tests/test_attn_prefill.py:31-59)."""
+    t, hq, hkv, hd = 65536, 40, 8, 128
+    q, kc, vc, cu, seq_lens, table = A.build_paged_kv([t], [0], hq, hkv, 16, hd=hd)
+    kq, ks = A.quantize_kv(kc)
+    vq, vs = A.quantize_kv(vc)
+    del kc, vc
+    scale = hd ** -0.5
+    out = run(q, kq, vq, cu, seq_lens, table, scale, 1, -1, ks, vs)
+    kx, vx = kq.float() * ks[..., None], vq.float() * vs[..., None]
+    tiles = sorted(set(range(0, t // 64, 128)) | {t // 64 - 1})
+    for tile in tiles:
+        a, b = tile * 64, tile * 64 + 64
+        ref = A.attention_reference(q[a:b], kx, vx, torch.tensor([0, 64], dtype=torch.int32),
+                                    torch.tensor([b], dtype=torch.int32), table, scale)
+        check(out[a:b], ref)
