@@ -405,6 +405,64 @@ int strix_moe_gemm_fp8_sorted(void* c, const void* a, const float* act_scales, c
 int strix_moe_gemm_fp8_sorted_covers(int64_t n, int64_t k, int64_t block_m, int gate_act,
                                      int scale_kind);
 
+/* ---- Expert-parallel exchange over peer memory (no counterpart in the
+ * reference, whose experts refuse an expert_map: python/strix_vllm/moe.py:193-210).
+ * Buffers are plain device allocations that peers map through CUDA IPC:
+ * strix_peer_alloc (zero-filled cudaMalloc) / _free, _export (64-byte handle) /
+ * _import / _unimport. Per rank: recv [world][cap][row_bytes], meta
+ * [world][cap][1 + 2 top_k] int32, counts [world], flags [world], ret
+ * [world][cap][hidden] bf16, rflags [world]; `peer_*` arguments are host arrays of
+ * `world` device pointers, entry d = rank d's buffer as addressable from this
+ * rank. `epoch` must grow by one per layer on every rank; `ticket` is one zeroed
+ * int32 of this rank. spin_limit bounds the waits (0 = about two seconds); a wait
+ * that runs out raises strix_ep_status (1 dispatch, 2 return) and the kernel goes
+ * on with empty input instead of hanging.
+ *   strix_ep_plan      tok_pos [world][tokens] (index of token t among this rank's
+ *                      tokens with a slot on rank d, or -1), counts [world]
+ *   strix_ep_dispatch  payload row (row_bytes, a multiple of 16) and metadata of
+ *                      every token to each rank it has a slot on, then counts and
+ *                      flags (release, system scope)
+ *   strix_ep_prepare   receiver: waits for all sources, writes ids int32 / weights
+ *                      fp32 [world * cap, top_k] (-1 / 0 where nothing arrived) and
+ *                      optionally rows_per_source [world]
+ *   strix_ep_return    expert rank: y bf16 [world * cap * top_k, hidden] in slot
+ *                      order -> one fp32-summed bf16 row per received token into
+ *                      the source's ret region, then rflags
+ *   strix_ep_combine   source: waits for all returns, out[t] = sum of the partial
+ *                      rows of the ranks token t was sent to
+ *   strix_moe_permute_rows  byte twin of strix_moe_permute_bf16 (rows of any
+ *                      16-byte multiple, e.g. e4m3 activations followed by their
+ *                      fp32 group scales) */
+int strix_peer_alloc(void** ptr, int64_t bytes);
+int strix_peer_free(void* ptr);
+int strix_peer_export(const void* ptr, void* handle64);
+int strix_peer_import(const void* handle64, void** ptr);
+int strix_peer_unimport(void* ptr);
+int strix_ep_status(int32_t* host_out, int reset);
+int strix_ep_plan(const int32_t* topk_ids, int32_t* tok_pos, int32_t* counts, int64_t tokens,
+                  int64_t top_k, int64_t experts_per_rank, int64_t world, strix_stream_t stream);
+int strix_ep_dispatch(const void* x, const int32_t* topk_ids, const float* topk_weights,
+                      const int32_t* tok_pos, const int32_t* counts, void* const* peer_recv,
+                      void* const* peer_meta, void* const* peer_counts, void* const* peer_flags,
+                      int32_t* ticket, int64_t tokens, int64_t row_bytes, int64_t x_stride_bytes,
+                      int64_t top_k, int64_t experts_per_rank, int64_t world, int64_t rank,
+                      int64_t cap, int64_t epoch, strix_stream_t stream);
+int strix_ep_prepare(const int32_t* meta, const int32_t* counts, const int32_t* flags,
+                     int32_t* ids, float* weights, int32_t* rows_per_source, int64_t world,
+                     int64_t cap, int64_t top_k, int64_t epoch, int64_t spin_limit,
+                     strix_stream_t stream);
+int strix_ep_return(const void* y, const int32_t* ids, const int32_t* meta, const int32_t* counts,
+                    void* const* peer_ret, void* const* peer_rflags, int32_t* ticket,
+                    int64_t world, int64_t rank, int64_t cap, int64_t top_k, int64_t hidden,
+                    int64_t y_stride, int64_t epoch, strix_stream_t stream);
+int strix_ep_combine(const void* ret, const int32_t* rflags, const int32_t* tok_pos, void* out,
+                     int64_t tokens, int64_t hidden, int64_t out_stride, int64_t world,
+                     int64_t cap, int64_t epoch, int64_t spin_limit, strix_stream_t stream);
+int strix_moe_permute_rows(const void* x, void* y, const int32_t* slot_pos,
+                           const int32_t* sorted_ids, const int32_t* num_post_padded,
+                           int64_t rows, int64_t sorted_rows, int64_t row_bytes, int64_t top_k,
+                           int64_t x_stride_bytes, int64_t y_stride_bytes, strix_stream_t stream);
+
 /* strix_attn_prefill_bf16 on the tcgen05 tensor cores (S and O in tensor memory,
  * TMA-fed operands): same contract and arguments (attn_prefill_bf16 of the
  * reference, csrc/attn/attn_prefill_bf16.hip:508-662), for head_dim 64 / 128 with

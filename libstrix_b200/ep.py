@@ -1,21 +1,31 @@
 """Expert-parallel MoE: token dispatch -> local experts -> combine.
 
 Every rank holds `experts_per_rank` consecutive experts and its own tokens. A
-routed slot (token, k) travels to the rank that owns its expert, is computed
-there with the grouped GEMMs of this library, and its result row travels back;
-the source rank then sums a token's top-k rows. The exchange is two
-`all_to_all_single` calls over the process group (NCCL over NVLink on GPUs,
-gloo in the CPU tests): activation rows one way, result rows the other, plus one
-small call for (local expert id, routing weight) pairs and one for the counts.
+token travels to every rank that owns one of its top-k experts, is computed
+there with the grouped GEMMs of this library, and one partial row per (token,
+rank) travels back; the source rank sums them.
+
+Two exchanges are implemented:
+
+  * peer memory (the GPU path, `EpContext`): this library's own kernels write
+    payload rows, metadata, counts and epoch flags straight into the peers'
+    buffers over NVLink (csrc/ep_exchange.cu). No host synchronisation, no
+    collective call per layer; a token is sent once per destination rank; the
+    FP8 layer quantises before dispatch (e4m3 bytes + per-128 scales travel, a
+    quarter of the bf16 payload is saved twice over); received rows are scattered
+    straight into the expert-sorted layout of the tcgen05 GEMMs.
+  * collectives (`ep_dispatch_combine`): `all_to_all_single` over the process
+    group with split sizes on the host - the portable form, which the CPU tests
+    run over gloo and which serves as fallback where peer mappings are refused.
 
 The reference has no expert parallelism (its experts refuse an `expert_map`,
 python/strix_vllm/moe.py:193-210); this is the path the 8-GPU configuration
-needs. The split sizes of an uneven all-to-all live on the host, so a layer call
-synchronises once (the counts); everything else stays on the stream.
+needs.
 """
 
 from __future__ import annotations
 
+import ctypes
 from typing import Callable
 
 import torch
@@ -224,39 +234,338 @@ def local_experts_fp8(w13, w13_scale, w2, w2_scale, block_m: int | None = None):
     return run
 
 
-def ep_moe_fp8(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, block_m=None):
-    """One expert-parallel FP8 W8A8 block-scaled MoE layer; arguments as
-    ep_moe_mxfp4 with the FP8 weight tensors of this rank's experts."""
-    from . import moe as _moe
+# --------------------------------------------------------------- peer memory
+class _RawCuda:
+    """A cudaMalloc allocation presented through __cuda_array_interface__."""
 
-    weights, ids = _moe.route(logits, top_k)
-    t, h = x.shape
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1",
+                                         "data": (ptr, False), "version": 2}
 
-    def combine(slots):
-        out = torch.empty(t, h, dtype=torch.bfloat16, device=x.device)
-        torch.ops.strix.moe_sum(slots, out)
+
+_BUFFERS = ("recv", "meta", "counts", "flags", "ret", "rflags")
+
+
+class EpContext:
+    """One rank's buffers for the peer-memory exchange, plus the addresses of
+    every peer's buffers as this rank sees them.
+
+    cap: tokens a source rank may send (its token count at most); row_bytes: the
+    payload row (a multiple of 16); hidden: width of the result rows (bf16).
+    Build with `EpContext.create(group, ...)` (one per process, CUDA IPC between
+    the ranks of one node) or `EpContext.emulate(world, ...)` (all ranks in this
+    process on one device, for tests: the phases of the ranks then run in
+    lockstep, never concurrently)."""
+
+    def __init__(self, world, rank, cap, top_k, row_bytes, hidden, device):
+        from . import _lib
+
+        self.world, self.rank, self.cap, self.top_k = world, rank, cap, top_k
+        self.row_bytes, self.hidden, self.device = row_bytes, hidden, torch.device(device)
+        self.epoch = 0
+        self._lib = _lib
+        self._imported: list[int] = []
+        meta_ints = 1 + 2 * top_k
+        sizes = {"recv": world * cap * row_bytes, "meta": world * cap * meta_ints * 4,
+                 "counts": 256, "flags": 256, "ret": world * cap * hidden * 2, "rflags": 256}
+        self.ptr: dict[str, int] = {}
+        self.t: dict[str, torch.Tensor] = {}
+        with torch.cuda.device(self.device):
+            for name, nbytes in sizes.items():
+                p = ctypes.c_void_p()
+                _lib.call("strix_peer_alloc", ctypes.byref(p), nbytes)
+                self.ptr[name] = p.value
+                self.t[name] = torch.as_tensor(_RawCuda(p.value, nbytes), device=self.device)
+        self.peer: dict[str, list[int]] = {}
+        i32 = dict(dtype=torch.int32, device=self.device)
+        self.ticket = torch.zeros(2, **i32)
+        self.ids = torch.empty(world * cap, top_k, **i32)
+        self.weights = torch.empty(world * cap, top_k, dtype=torch.float32, device=self.device)
+        self.rows_per_source = torch.zeros(world, **i32)
+        self.y = torch.empty(world * cap * top_k, hidden, dtype=torch.bfloat16, device=self.device)
+        self.tok_pos = None
+        self.counts = torch.empty(world, **i32)
+
+    # ---- construction
+    @classmethod
+    def create(cls, group, cap, top_k, row_bytes, hidden, device):
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        ctx = cls(world, rank, cap, top_k, row_bytes, hidden, device)
+        handles = {}
+        for name in _BUFFERS:
+            h = (ctypes.c_uint8 * 64)()
+            ctx._lib.call("strix_peer_export", ctx.ptr[name], h)
+            handles[name] = bytes(h)
+        gathered = [None] * world
+        dist.all_gather_object(gathered, handles, group=group)
+        with torch.cuda.device(ctx.device):
+            for name in _BUFFERS:
+                ptrs = []
+                for r in range(world):
+                    if r == rank:
+                        ptrs.append(ctx.ptr[name])
+                        continue
+                    p = ctypes.c_void_p()
+                    ctx._lib.call("strix_peer_import", gathered[r][name], ctypes.byref(p))
+                    ctx._imported.append(p.value)
+                    ptrs.append(p.value)
+                ctx.peer[name] = ptrs
+        dist.barrier(group=group)
+        return ctx
+
+    @classmethod
+    def emulate(cls, world, cap, top_k, row_bytes, hidden, device):
+        ctxs = [cls(world, r, cap, top_k, row_bytes, hidden, device) for r in range(world)]
+        for c in ctxs:
+            for name in _BUFFERS:
+                c.peer[name] = [o.ptr[name] for o in ctxs]
+        return ctxs
+
+    def close(self):
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize()
+            for p in self._imported:
+                self._lib.call("strix_peer_unimport", p)
+            self._imported = []
+            self.t = {}
+            for name, p in self.ptr.items():
+                self._lib.call("strix_peer_free", p)
+            self.ptr = {}
+
+    def _ptrs(self, name):
+        return (ctypes.c_void_p * self.world)(*self.peer[name])
+
+    # ---- the exchange phases (each enqueues kernels on the current stream)
+    def dispatch(self, payload: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
+                 experts_per_rank: int):
+        """payload [T, row_bytes worth of elements] (last dim contiguous) goes to every
+        rank that owns one of the token's experts."""
+        t, k = topk_ids.shape
+        assert k == self.top_k and t <= self.cap
+        assert payload.size(1) * payload.element_size() == self.row_bytes and payload.stride(1) == 1
+        self.epoch += 1
+        self.tokens = t
+        ids = topk_ids.to(torch.int32).contiguous()
+        wts = topk_weights.to(torch.float32).contiguous()
+        if self.tok_pos is None or self.tok_pos.numel() != self.world * max(t, 1):
+            self.tok_pos = torch.empty(self.world, max(t, 1), dtype=torch.int32, device=self.device)
+        stream = torch.cuda.current_stream().cuda_stream
+        call = self._lib.call
+        with torch.cuda.device(self.device):
+            call("strix_ep_plan", ids.data_ptr(), self.tok_pos.data_ptr(), self.counts.data_ptr(), t, k,
+                 experts_per_rank, self.world, stream)
+            call("strix_ep_dispatch", payload.data_ptr(), ids.data_ptr(), wts.data_ptr(),
+                 self.tok_pos.data_ptr(), self.counts.data_ptr(), self._ptrs("recv"), self._ptrs("meta"),
+                 self._ptrs("counts"), self._ptrs("flags"), self.ticket.data_ptr(), t, self.row_bytes,
+                 payload.stride(0) * payload.element_size(), k, experts_per_rank, self.world, self.rank,
+                 self.cap, self.epoch, stream)
+
+    def receive(self, spin_limit: int = 0):
+        """Waits (on the device) for every source; returns (rows uint8 [world * cap,
+        row_bytes], ids int32 [world * cap, top_k] with -1 where nothing arrived,
+        weights fp32 of the same shape)."""
+        stream = torch.cuda.current_stream().cuda_stream
+        with torch.cuda.device(self.device):
+            self._lib.call("strix_ep_prepare", self.ptr["meta"], self.ptr["counts"], self.ptr["flags"],
+                           self.ids.data_ptr(), self.weights.data_ptr(), self.rows_per_source.data_ptr(),
+                           self.world, self.cap, self.top_k, self.epoch, spin_limit, stream)
+        rows = self.t["recv"][: self.world * self.cap * self.row_bytes].view(self.world * self.cap,
+                                                                             self.row_bytes)
+        return rows, self.ids, self.weights
+
+    def send_back(self, y: torch.Tensor):
+        """y bf16 [world * cap * top_k, hidden], slot order, weighted: one summed row
+        per received token goes back to its source."""
+        stream = torch.cuda.current_stream().cuda_stream
+        with torch.cuda.device(self.device):
+            self._lib.call("strix_ep_return", y.data_ptr(), self.ids.data_ptr(), self.ptr["meta"],
+                           self.ptr["counts"], self._ptrs("ret"), self._ptrs("rflags"),
+                           self.ticket.data_ptr() + 4, self.world, self.rank, self.cap, self.top_k,
+                           self.hidden, y.stride(0), self.epoch, stream)
+
+    def combine(self, out: torch.Tensor | None = None, spin_limit: int = 0) -> torch.Tensor:
+        """Waits for every rank's return; out[t] = sum of token t's partial rows."""
+        t = self.tokens
+        if out is None:
+            out = torch.empty(t, self.hidden, dtype=torch.bfloat16, device=self.device)
+        stream = torch.cuda.current_stream().cuda_stream
+        with torch.cuda.device(self.device):
+            self._lib.call("strix_ep_combine", self.ptr["ret"], self.ptr["rflags"], self.tok_pos.data_ptr(),
+                           out.data_ptr(), t, self.hidden, out.stride(0) if t else self.hidden, self.world,
+                           self.cap, self.epoch, spin_limit, stream)
         return out
 
-    return ep_dispatch_combine(x, weights, ids, w13.size(0),
-                               local_experts_fp8(w13, w13_scale, w2, w2_scale, block_m), group,
-                               combine)
+    def status(self, reset: bool = False) -> int:
+        flag = ctypes.c_int32(-1)
+        with torch.cuda.device(self.device):
+            self._lib.call("strix_ep_status", ctypes.byref(flag), int(reset))
+        return flag.value
 
 
-def ep_moe_mxfp4(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, block_m=None):
+def _experts_mxfp4_on_received(ctx: EpContext, w13, w13_scale, w2, w2_scale):
+    """The received tokens through this rank's MXFP4 experts; returns y in slot order."""
+    from . import moe as _moe
+
+    rows, ids, weights = ctx.receive()
+    e = w13.size(0)
+    inter = w13.size(1) // 2
+    ops = torch.ops.strix
+    sorted_ids, expert_ids, num_post, slot_pos = _moe.align_with_positions(ids, 128, e)
+    cap_s = sorted_ids.numel()
+    dev = ctx.device
+    xs = torch.empty(cap_s, ctx.row_bytes // 2, dtype=torch.bfloat16, device=dev)
+    act = torch.empty(cap_s, inter, dtype=torch.bfloat16, device=dev)
+    ops.moe_permute_rows(rows, xs.view(torch.uint8), slot_pos, sorted_ids, num_post, ctx.top_k)
+    n_slots = ids.numel()
+    ops.moe_gemm_mxfp4_sorted(act, xs, w13, w13_scale, sorted_ids, expert_ids, num_post, None, n_slots,
+                              128, True, "silu", True)
+    ops.moe_gemm_mxfp4_sorted(ctx.y, act, w2, w2_scale, sorted_ids, expert_ids, num_post,
+                              weights.view(-1), n_slots, 128, False, "silu", False)
+    return ctx.y
+
+
+def _experts_fp8_on_received(ctx: EpContext, w13, w13_scale, w2, w2_scale, block_m):
+    """The received (already quantised) tokens through this rank's FP8 experts."""
+    from . import moe as _moe
+
+    rows, ids, weights = ctx.receive()
+    e, n13, h = w13.shape
+    inter = n13 // 2
+    ops = torch.ops.strix
+    f8 = torch.float8_e4m3fn
+    sorted_ids, expert_ids, num_post, slot_pos = _moe.align_with_positions(ids, block_m, e)
+    cap_s = sorted_ids.numel()
+    dev = ctx.device
+    srt = torch.empty(cap_s, ctx.row_bytes, dtype=torch.uint8, device=dev)
+    ops.moe_permute_rows(rows, srt, slot_pos, sorted_ids, num_post, ctx.top_k)
+    xq, xs = srt[:, :h].view(f8), srt[:, h:].view(torch.float32)
+    act = torch.empty(cap_s, inter, dtype=torch.bfloat16, device=dev)
+    aq = torch.empty(cap_s, inter, dtype=f8, device=dev)
+    as_ = torch.empty(cap_s, inter // 128, dtype=torch.float32, device=dev)
+    n_slots = ids.numel()
+    ops.moe_gemm_fp8_sorted(act, xq, xs, w13, w13_scale, sorted_ids, expert_ids, num_post, None, n_slots,
+                            block_m, True, "silu", True)
+    ops.moe_act_quant_fp8_sorted(act, aq, as_, None, num_post, 1, n_slots)
+    ops.moe_gemm_fp8_sorted(ctx.y, aq, as_, w2, w2_scale, sorted_ids, expert_ids, num_post,
+                            weights.view(-1), n_slots, block_m, False, "silu", False)
+    return ctx.y
+
+
+_CONTEXTS: dict[tuple, EpContext] = {}
+
+
+def context_for(group, tokens, top_k, row_bytes, hidden, device) -> EpContext:
+    """The cached EpContext of this (group, payload shape). It is built on first use
+    - a collective: every rank must reach it together - with a capacity of the
+    largest token count over the ranks at that moment; later calls may bring
+    fewer tokens, never more (build an EpContext of your own for a larger batch)."""
+    key = (id(group), top_k, row_bytes, hidden, str(device))
+    ctx = _CONTEXTS.get(key)
+    if ctx is None:
+        ctx = _CONTEXTS[key] = EpContext.create(group, _capacity(tokens, group), top_k, row_bytes,
+                                                hidden, device)
+    if tokens > ctx.cap:
+        raise RuntimeError(f"{tokens} tokens exceed the exchange capacity {ctx.cap} set at first use")
+    return ctx
+
+
+def close_contexts() -> None:
+    for ctx in _CONTEXTS.values():
+        ctx.close()
+    _CONTEXTS.clear()
+
+
+def fp8_payload(x: torch.Tensor, buf: torch.Tensor | None = None):
+    """(payload uint8 [T, H + H / 32], q view, scale view): x quantised to e4m3 per
+    (token, 128 group) with the fp32 scales behind each row's bytes - what the FP8
+    layer sends instead of bf16 rows."""
+    t, h = x.shape
+    row = h + h // 32
+    if buf is None or buf.size(0) < t or buf.size(1) != row:
+        buf = torch.empty(max(t, 1), row, dtype=torch.uint8, device=x.device)
+    q, s = buf[:t, :h].view(torch.float8_e4m3fn), buf[:t, h:].view(torch.float32)
+    torch.ops.strix.moe_act_quant_fp8(x, q, s)
+    return buf[:t], q, s
+
+
+def ep_moe_fp8(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, block_m=None,
+               exchange="auto", ctx=None):
+    """One expert-parallel FP8 W8A8 block-scaled MoE layer. x bf16 [T_local, H];
+    logits fp32 [T_local, E_global]; the weight tensors hold this rank's E_global /
+    world experts. Returns bf16 [T_local, H]. exchange: "peer" (this library's
+    kernels over peer memory), "nccl" (all_to_all_single) or "auto" (peer on CUDA;
+    a single rank runs the fused single-GPU layer, which is the same computation
+    without an exchange)."""
+    from . import moe as _moe
+
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    t, h = x.shape
+    if world == 1 and exchange == "auto" and ctx is None:
+        return _moe.fused_moe_fp8_w8a8(x, logits, w13, w13_scale, w2, w2_scale, top_k, block_m=block_m)
+    weights, ids = _moe.route(logits, top_k)
+    if exchange == "nccl" or not x.is_cuda:
+        def combine(slots):
+            out = torch.empty(t, h, dtype=torch.bfloat16, device=x.device)
+            torch.ops.strix.moe_sum(slots, out)
+            return out
+
+        return ep_dispatch_combine(x, weights, ids, w13.size(0),
+                                   local_experts_fp8(w13, w13_scale, w2, w2_scale, block_m), group,
+                                   combine)
+    e_local = w13.size(0)
+    row_bytes = h + h // 32
+    if ctx is None:
+        ctx = context_for(group, t, top_k, row_bytes, h, x.device)
+    bm = block_m or _moe.pick_block_m(t * ctx.world, top_k, e_local * ctx.world)
+    if not _moe.sorted_path_covers(w13, w13_scale, w2, w2_scale, bm):
+        raise RuntimeError("ep_moe_fp8: geometry not covered by the sorted-layout kernel")
+    payload, _, _ = fp8_payload(x)
+    ctx.dispatch(payload, weights, ids, e_local)
+    y = _experts_fp8_on_received(ctx, w13, w13_scale, w2, w2_scale, bm)
+    ctx.send_back(y)
+    return ctx.combine()
+
+
+def ep_moe_mxfp4(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, block_m=None,
+                 exchange="auto", ctx=None):
     """One expert-parallel MXFP4 MoE layer. x bf16 [T_local, H]; logits fp32
     [T_local, E_global]; the weight tensors hold this rank's E_global / world
     experts. Router and combine run on this rank's tokens, the experts where
-    they live. Returns bf16 [T_local, H]."""
+    they live. Returns bf16 [T_local, H]. `exchange` as in ep_moe_fp8."""
+    from . import _lib
     from . import moe as _moe
 
-    weights, ids = _moe.route(logits, top_k)
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
     t, h = x.shape
+    lib = _lib.load()
+    wide_ok = bool(lib.strix_moe_gemm_mxfp4_sorted_covers(w13.size(1), w13.size(2) * 2, 128, 1)
+                   and lib.strix_moe_gemm_mxfp4_sorted_covers(w2.size(1), w2.size(2) * 2, 128, 0))
+    if world == 1 and exchange == "auto" and ctx is None and x.is_cuda:
+        return _moe.fused_moe_mxfp4(x, logits, w13, w13_scale, w2, w2_scale, top_k, block_m=block_m)
+    weights, ids = _moe.route(logits, top_k)
+    if exchange == "nccl" or not x.is_cuda or not wide_ok or (h * 2) % 16:
+        def combine(slots):
+            out = torch.empty(t, h, dtype=torch.bfloat16, device=x.device)
+            torch.ops.strix.moe_sum(slots, out)
+            return out
 
-    def combine(slots):
-        out = torch.empty(t, h, dtype=torch.bfloat16, device=x.device)
-        torch.ops.strix.moe_sum(slots, out)
-        return out
+        return ep_dispatch_combine(x, weights, ids, w13.size(0),
+                                   local_experts_mxfp4(w13, w13_scale, w2, w2_scale, block_m),
+                                   group, combine)
+    if ctx is None:
+        ctx = context_for(group, t, top_k, h * 2, h, x.device)
+    ctx.dispatch(x, weights, ids, w13.size(0))
+    y = _experts_mxfp4_on_received(ctx, w13, w13_scale, w2, w2_scale)
+    ctx.send_back(y)
+    return ctx.combine()
 
-    return ep_dispatch_combine(x, weights, ids, w13.size(0),
-                               local_experts_mxfp4(w13, w13_scale, w2, w2_scale, block_m),
-                               group, combine)
+
+def _capacity(tokens: int, group) -> int:
+    """Rows a source may send: the largest token count over the ranks (one small
+    collective with a host read, at context creation only)."""
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return max(tokens, 1)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    n = torch.tensor([tokens], dtype=torch.int64, device=dev)
+    dist.all_reduce(n, op=dist.ReduceOp.MAX, group=group)
+    return max(int(n.item()), 1)

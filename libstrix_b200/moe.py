@@ -158,3 +158,43 @@ def fused_moe_fp8_w8a8(x, logits, w13, w13_scale, w2, w2_scale, top_k, block_m=N
                               weights.view(-1), 1, bm, 64, False, "silu")
     ops.moe_sum(ws.y.view(t, top_k, h), ws.out)
     return ws.out
+
+
+def fused_moe_mxfp4(x, logits, w13, w13_scale, w2, w2_scale, top_k, block_m=None):
+    """One MoE layer over MXFP4 experts (e2m1 nibbles, e8m0 scale per 32) and bf16
+    activations: w13 uint8 [E, 2I, H/2] + scales [E, 2I, H/32], w2 uint8 [E, H, I/2]
+    + scales [E, H, I/32]. route -> align -> permute into sorted order -> gate-up
+    GEMM with SiLU-mul -> down GEMM x routing weight -> sum over top-k. From 32 rows
+    per expert on (and where its tiles divide the shapes) the tcgen05 kernel over
+    the sorted layout runs, below that the weight-streaming kernel. Six launches,
+    no host synchronisation. Returns bf16 [T, H]."""
+    t, h = x.shape
+    e = w13.size(0)
+    inter = w13.size(1) // 2
+    lib = _lib.load()
+    ops = torch.ops.strix
+    weights, ids = route(logits, top_k)
+    out = torch.empty(t, h, dtype=torch.bfloat16, device=x.device)
+    y = torch.empty(t * top_k, h, dtype=torch.bfloat16, device=x.device)
+    wide_ok = bool(lib.strix_moe_gemm_mxfp4_sorted_covers(w13.size(1), w13.size(2) * 2, 128, 1)
+                   and lib.strix_moe_gemm_mxfp4_sorted_covers(w2.size(1), w2.size(2) * 2, 128, 0))
+    bm = block_m or (128 if wide_ok and t * top_k >= 32 * e else 64)
+    if bm == 128 and wide_ok:
+        sorted_ids, expert_ids, num_post, slot_pos = align_with_positions(ids, 128, e)
+        cap = sorted_ids.numel()
+        xs = torch.empty(cap, h, dtype=torch.bfloat16, device=x.device)
+        act = torch.empty(cap, inter, dtype=torch.bfloat16, device=x.device)
+        ops.moe_permute_bf16(x, xs, slot_pos, sorted_ids, num_post, top_k)
+        ops.moe_gemm_mxfp4_sorted(act, xs, w13, w13_scale, sorted_ids, expert_ids, num_post, None,
+                                  t * top_k, 128, True, "silu", True)
+        ops.moe_gemm_mxfp4_sorted(y, act, w2, w2_scale, sorted_ids, expert_ids, num_post,
+                                  weights.view(-1), t * top_k, 128, False, "silu", False)
+    else:
+        sorted_ids, expert_ids, num_post = align(ids, bm, e)
+        act = torch.empty(t * top_k, inter, dtype=torch.bfloat16, device=x.device)
+        ops.moe_gemm_mxfp4(act, x, w13, w13_scale, sorted_ids, expert_ids, num_post, None, top_k,
+                           bm, 64, True, "silu")
+        ops.moe_gemm_mxfp4(y, act, w2, w2_scale, sorted_ids, expert_ids, num_post, weights.view(-1),
+                           1, bm, 64, False, "silu")
+    ops.moe_sum(y.view(t, top_k, h), out)
+    return out

@@ -237,6 +237,10 @@ KERNELS: list[Kernel] = [
     Kernel("moe_permute_bf16", "moe_permute",
            "bf16 rows into sorted order by scatter (inverse permutation from the align kernel)",
            {"dtype": "bf16", "layout": "sorted"}),
+    Kernel("moe_permute_rows", "moe_permute",
+           "rows of any element type (whole 16-byte chunks, e.g. e4m3 bytes followed by their "
+           "fp32 group scales) into sorted order by scatter; rows without a position are skipped",
+           {"dtype": ("uint8", "bf16", "fp8_e4m3"), "layout": "sorted", "bytes": True}),
     Kernel("mxfp4_gemv", "mxfp4_gemv", "MXFP4 W4A16 at 1-8 rows (the dense form of moe_gemm_mxfp4)",
            {"weight_bits": 4, "group_size": 32, "dtype": "bf16", "m_max": 8}, dict(_STREAM_SPEC)),
     Kernel("mxfp4_wmma_gemm", "mxfp4", "MXFP4 W4A16 dense GEMM, optional bias [N] or [M, N]",

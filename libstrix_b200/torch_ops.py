@@ -644,6 +644,25 @@ def moe_permute_bf16(x, y, slot_pos, sorted_ids, num_post_padded, top_k):
                   top_k, x.stride(0), y.stride(0), _stream())
 
 
+@_define("moe_permute_rows(Tensor x, Tensor(a!) y, Tensor slot_pos, Tensor sorted_ids, "
+         "Tensor num_post_padded, int top_k) -> ()")
+def moe_permute_rows(x, y, slot_pos, sorted_ids, num_post_padded, top_k):
+    """moe_permute_bf16 for rows of any element type (whole 16-byte chunks), e.g.
+    e4m3 activations followed by their fp32 group scales: y[slot_pos[r * top_k + j]]
+    = x[r]; rows none of whose slots has a position are not read."""
+    _check(x.dim() == 2 and y.dim() == 2 and x.dtype == y.dtype and x.size(1) == y.size(1)
+           and x.stride(1) == 1 and y.stride(1) == 1, "x, y [rows, K] of one dtype, contiguous rows")
+    _check(all(t.dtype == torch.int32 and t.is_contiguous()
+               for t in (slot_pos, sorted_ids, num_post_padded)), "routing tensors must be int32")
+    _check(slot_pos.numel() >= x.size(0) * top_k and sorted_ids.numel() >= y.size(0),
+           "slot_pos / sorted_ids too short")
+    eb = x.element_size()
+    with torch.cuda.device(x.device):
+        _lib.call("strix_moe_permute_rows", x.data_ptr(), y.data_ptr(), slot_pos.data_ptr(),
+                  sorted_ids.data_ptr(), num_post_padded.data_ptr(), x.size(0), y.size(0),
+                  x.size(1) * eb, top_k, x.stride(0) * eb, y.stride(0) * eb, _stream())
+
+
 @_define("moe_gemm_mxfp4_sorted(Tensor(a!) c, Tensor a, Tensor b, Tensor scales, Tensor sorted_ids, "
          "Tensor expert_ids, Tensor num_post_padded, Tensor? topk_weights, int num_valid, "
          "int block_m, bool silu_mul=False, str activation='silu', bool c_sorted=False) -> ()")

@@ -198,3 +198,114 @@ def test_ep_moe_mxfp4_two_gpus_equals_unsharded_layer():
     for rank in (0, 1):
         err, peak = results[rank]
         assert err <= 1e-2 * peak, f"rank {rank}: max error {err} vs peak {peak}"
+
+
+# ------------------------------------------------- peer-memory exchange (GPU kernels)
+def _bound_ok(out, ref):
+    err = (out.float().cpu() - ref.float()).abs()
+    rms = ref.float().pow(2).mean().sqrt()
+    return bool((err <= 2e-2 * rms + ref.float().abs() * 2.0 ** -8).all()), float(err.max()), float(rms)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kind", ["mxfp4", "fp8"])
+@pytest.mark.parametrize("tokens_per_rank", [[70, 0, 33, 128], [1, 1, 1, 1]])
+def test_peer_exchange_with_emulated_ranks(kind, tokens_per_rank):
+    """Four ranks emulated in one process on one GPU (the phases of all ranks run in
+    lockstep, so no kernel ever waits for one that has not been launched): plan,
+    dispatch, receive, local experts, return and combine against the CPU oracle of
+    the unsharded layer."""
+    from libstrix_b200 import ep
+    from libstrix_b200 import moe as smoe
+    from libstrix_b200.workloads import moe_fp8_layer, moe_mxfp4_layer
+    from oracle import moe as M
+
+    dev = torch.device("cuda", 0)
+    world, e_global, k, hid, inter = 4, 8, 2, 256, 128
+    per = e_global // world
+    total = sum(tokens_per_rank)
+    if kind == "mxfp4":
+        layer = moe_mxfp4_layer(tokens=256, hidden=hid, experts=e_global, top_k=k, inter=inter, seed=3)
+        ref, _, _ = M.moe_mxfp4_layer(layer.x[:total], layer.logits[:total], layer.w13, layer.w13_scale,
+                                      layer.w2, layer.w2_scale, k)
+        row_bytes = hid * 2
+    else:
+        layer = moe_fp8_layer(tokens=256, hidden=hid, experts=e_global, top_k=k, inter=inter, seed=3)
+        ref, _, _ = M.moe_fp8_layer(layer.x[:total], layer.logits[:total], layer.w13, layer.w13_scale,
+                                    layer.w2, layer.w2_scale, k)
+        row_bytes = hid + hid // 32
+    g = layer.to(dev)
+    ctxs = ep.EpContext.emulate(world, max(tokens_per_rank), k, row_bytes, hid, dev)
+    try:
+        offs = [sum(tokens_per_rank[:r]) for r in range(world + 1)]
+        for rounds in range(2):                       # twice: the epoch stamps must carry over
+            for r, ctx in enumerate(ctxs):
+                x, logits = g.x[offs[r]:offs[r + 1]], g.logits[offs[r]:offs[r + 1]]
+                weights, ids = smoe.route(logits, k)
+                payload = x if kind == "mxfp4" else ep.fp8_payload(x)[0]
+                ctx.dispatch(payload, weights, ids, per)
+            for r, ctx in enumerate(ctxs):
+                sl = slice(r * per, (r + 1) * per)
+                if kind == "mxfp4":
+                    y = ep._experts_mxfp4_on_received(ctx, g.w13[sl], g.w13_scale[sl], g.w2[sl], g.w2_scale[sl])
+                else:
+                    y = ep._experts_fp8_on_received(ctx, g.w13[sl].contiguous(), g.w13_scale[sl].contiguous(),
+                                                    g.w2[sl].contiguous(), g.w2_scale[sl].contiguous(), 128)
+                ctx.send_back(y)
+            outs = [ctx.combine() for ctx in ctxs]
+            torch.cuda.synchronize()
+            assert ctxs[0].status() == 0
+            # every token reached each rank that owns one of its experts exactly once
+            got = torch.stack([c.rows_per_source for c in ctxs]).cpu()       # [dest, src]
+            ids_all, _ = M.router(layer.logits[:total], k)
+            for r in range(world):
+                mine = ids_all[offs[r]:offs[r + 1]] // per
+                for d in range(world):
+                    assert int(got[d, r]) == int((mine == d).any(-1).sum())
+            for r in range(world):
+                ok, err, rms = _bound_ok(outs[r], ref[offs[r]:offs[r + 1]])
+                assert ok, f"round {rounds} rank {r}: max err {err} vs rms {rms}"
+    finally:
+        for c in ctxs:
+            c.close()
+
+
+@pytest.mark.gpu
+def test_peer_exchange_waits_are_bounded():
+    """A flag that nothing sets: the receive and combine kernels give up after the
+    given number of polls, raise the status word and deliver empty input."""
+    from libstrix_b200 import ep
+
+    dev = torch.device("cuda", 0)
+    ctx = ep.EpContext.emulate(2, 8, 2, 64, 32, dev)[0]     # its "peer" never dispatches
+    try:
+        ctx.epoch, ctx.tokens = 5, 4
+        ctx.tok_pos = torch.zeros(2, 4, dtype=torch.int32, device=dev)
+        _, ids, _ = ctx.receive(spin_limit=50)
+        torch.cuda.synchronize()
+        assert ctx.status(reset=True) == 1 and bool((ids == -1).all())
+        out = ctx.combine(spin_limit=50)
+        torch.cuda.synchronize()
+        assert ctx.status(reset=True) == 2 and bool((out == 0).all())
+        assert ctx.status() == 0
+    finally:
+        ctx.close()
+
+
+@pytest.mark.gpu
+def test_masked_expert_ids_have_no_position():
+    """Slots whose expert id is -1 (masked) or out of range get slot_pos -1 and are
+    skipped by the scatter kernels."""
+    from libstrix_b200 import moe as smoe
+
+    ids = torch.tensor([[0, -1], [3, 1], [-1, -1], [2, 9]], dtype=torch.int32, device="cuda")
+    sorted_ids, expert_ids, num_post, slot_pos = smoe.align_with_positions(ids, 4, 4)
+    pos = slot_pos.cpu().tolist()
+    assert [p >= 0 for p in pos] == [True, False, True, True, False, False, True, False]
+    assert int(num_post) == 16
+    srt = sorted_ids.cpu()[:16].view(4, 4)
+    assert srt[:, 0].tolist() == [0, 3, 6, 2] and bool((srt[:, 1:] == 8).all())
+    x = torch.arange(4 * 8, dtype=torch.float32, device="cuda").view(4, 8).bfloat16()
+    y = torch.full((sorted_ids.numel(), 8), -1.0, dtype=torch.bfloat16, device="cuda")
+    torch.ops.strix.moe_permute_bf16(x, y, slot_pos, sorted_ids, num_post, 2)
+    assert torch.equal(y[pos[0]], x[0]) and torch.equal(y[pos[2]], x[1]) and torch.equal(y[pos[6]], x[3])
