@@ -677,20 +677,27 @@ def _timed(fn, steps: int, warmup: int = 3) -> float:
     return e0.elapsed_time(e1) / steps
 
 
-def _phase_times(stages, reps: int = 5) -> dict:
-    """Mean CUDA-event time of each named stage of a layer, the stages run back to
-    back `reps` times (stages = [(name, fn)])."""
-    acc = {name: 0.0 for name, _ in stages}
+def _phase_times(layer_fn, reps: int = 5) -> dict:
+    """Mean CUDA-event time between the marks a layer sets (layer_fn(mark) runs one
+    layer and calls mark(name) after each phase is enqueued)."""
+    acc: dict[str, float] = {}
     for it in range(reps + 1):
-        evs = [torch.cuda.Event(enable_timing=True) for _ in range(len(stages) + 1)]
-        evs[0].record()
-        for i, (_, fn) in enumerate(stages):
-            fn()
-            evs[i + 1].record()
+        marks = []
+        start = torch.cuda.Event(enable_timing=True)
+        start.record()
+
+        def mark(name):
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            marks.append((name, ev))
+
+        layer_fn(mark)
         torch.cuda.synchronize()
         if it:
-            for i, (name, _) in enumerate(stages):
-                acc[name] += evs[i].elapsed_time(evs[i + 1]) / reps
+            prev = start
+            for name, ev in marks:
+                acc[name] = acc.get(name, 0.0) + prev.elapsed_time(ev) / reps
+                prev = ev
     return {k: round(v, 4) for k, v in acc.items()}
 
 
@@ -711,10 +718,6 @@ def bench_ep_moe(args, dev, rank: int, world: int, with_cpu: bool) -> dict:
     from libstrix_b200.workloads import moe_mxfp4_layer
     from oracle import moe as M
 
-    if not dist.is_initialized():
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ.setdefault("MASTER_PORT", "29517")
-        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     tokens_total, hid, inter, experts, top_k = 8192, 2880, 2880, 128, 4
     t_local, e_local = tokens_total // world, experts // world
     layer = moe_mxfp4_layer(tokens=tokens_total, hidden=hid, experts=experts, top_k=top_k, inter=inter,
@@ -730,7 +733,8 @@ def bench_ep_moe(args, dev, rank: int, world: int, with_cpu: bool) -> dict:
     for _ in range(3):
         step()
     torch.cuda.synchronize()
-    dist.barrier()
+    if world > 1:
+        dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -739,7 +743,8 @@ def bench_ep_moe(args, dev, rank: int, world: int, with_cpu: bool) -> dict:
     e1.record()
     torch.cuda.synchronize()
     ms_t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
-    dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
+    if world > 1:
+        dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
     ms = ms_t.item()
     flops = 2.0 * tokens_total * top_k * (2 * inter * hid + hid * inter)
 
@@ -748,7 +753,8 @@ def bench_ep_moe(args, dev, rank: int, world: int, with_cpu: bool) -> dict:
 
     _, ids = smoe.route(layer.logits, top_k)
     per_rank = torch.bincount((ids.reshape(-1) // e_local).long(), minlength=world).to(torch.float64)
-    dist.all_reduce(per_rank, op=dist.ReduceOp.SUM)
+    if world > 1:
+        dist.all_reduce(per_rank, op=dist.ReduceOp.SUM)
     res = {"config": "MXFP4 MoE, H=2880 E=128 top-4 I=2880, 8192 tokens, EP over ranks, Zipf(1.1) bias, "
                      "weights N(0,0.02) -> e2m1 / e8m0 per 32",
            "n_gpus": world, "scaling": "strong", "ms_per_layer": ms,
@@ -763,20 +769,11 @@ def bench_ep_moe(args, dev, rank: int, world: int, with_cpu: bool) -> dict:
                         else "peer-memory kernels over NVLink (CUDA IPC), no host synchronisation"),
            "gpu_launches": (6 if world == 1 else 11) * steps}
     if world > 1 and exchange != "nccl":
-        ctx = next(iter(ep._CONTEXTS.values()))
-        w, i = smoe.route(layer.logits, top_k)
-        state = {}
-        stages = [
-            ("route", lambda: state.update(r=smoe.route(layer.logits, top_k))),
-            ("plan_dispatch", lambda: ctx.dispatch(layer.x, state["r"][0], state["r"][1], e_local)),
-            ("wait_experts", lambda: state.update(y=ep._experts_mxfp4_on_received(
-                ctx, layer.w13, layer.w13_scale, layer.w2, layer.w2_scale))),
-            ("return", lambda: ctx.send_back(state["y"])),
-            ("wait_combine", lambda: ctx.combine()),
-        ]
         dist.barrier()
-        res["phases_ms_rank0"] = _phase_times(stages)
-        res["ep_status"] = ctx.status()
+        res["phases_ms_rank0"] = _phase_times(lambda mark: ep.ep_moe_mxfp4(
+            layer.x, layer.logits, layer.w13, layer.w13_scale, layer.w2, layer.w2_scale, top_k,
+            exchange=exchange, mark=mark))
+        res["ep_status"] = next(iter(ep._CONTEXTS.values())).status()
     # parity on rank 0: a sample of its tokens against the oracle over regenerated experts
     if with_cpu and rank == 0:
         sample = torch.arange(0, t_local, max(1, t_local // 8))[:8]
@@ -829,7 +826,8 @@ def _bench_ep_fp8(args, dev, rank: int, world: int, steps: int, with_cpu: bool) 
     for _ in range(3):
         step()
     torch.cuda.synchronize()
-    dist.barrier()
+    if world > 1:
+        dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -838,11 +836,16 @@ def _bench_ep_fp8(args, dev, rank: int, world: int, steps: int, with_cpu: bool) 
     e1.record()
     torch.cuda.synchronize()
     ms_t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
-    dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
+    if world > 1:
+        dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
     ms = ms_t.item()
     res = {"config": "FP8 W8A8 MoE, H=2048 E=128 top-8 I=768, 4096 tokens, EP over ranks",
            "n_gpus": world, "scaling": "strong", "ms_per_layer": ms,
            "tflops": flops_total / (ms * 1e-3) / 1e12, "tokens_per_s": tokens_total / (ms * 1e-3)}
+    if world > 1 and args.ep_exchange != "nccl":
+        dist.barrier()
+        res["phases_ms_rank0"] = _phase_times(lambda mark: ep.ep_moe_fp8(
+            x, logits, w13, s13, w2, s2, top_k, exchange=args.ep_exchange, mark=mark))
     if with_cpu and rank == 0:
         cpu = layer.to("cpu")
         sample = torch.arange(0, t_local, max(1, t_local // 16))[:16]

@@ -110,29 +110,53 @@ __global__ void __launch_bounds__(256) ep_plan_kernel(const int32_t* __restrict_
   (void)world;
 }
 
-// A thread = one 16-byte chunk of one token's payload row, copied to every
-// destination the token has a slot on; chunk 0 also writes the row's metadata.
-__global__ void __launch_bounds__(256) ep_dispatch_kernel(
+// Raises this grid's flags once every CTA has passed: a CTA's stores are ordered
+// before its ticket by a barrier and ONE system-scope fence of thread 0 (fences are
+// cumulative over what the barrier made visible to that thread), and the CTA that
+// draws the last ticket publishes.
+template <class Publish>
+__device__ __forceinline__ void publish_when_last(int32_t* ticket, Publish publish) {
+  __shared__ int s_last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    s_last = atomicAdd(ticket, 1) == int(gridDim.x) - 1;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  if (threadIdx.x == 0) __threadfence_system();
+  __syncthreads();
+  publish();
+  if (threadIdx.x == 0) *ticket = 0;
+}
+
+constexpr int kEpWarps = 8;   // warps per CTA of the row-copy kernels (a warp = one row at a time)
+
+// A warp = one token at a time: its payload row goes to every destination the token
+// has a slot on (16-byte chunks, lane-strided); lane 0 also writes the row's metadata.
+__global__ void __launch_bounds__(kEpWarps * 32) ep_dispatch_kernel(
     const uint4* __restrict__ x, int64_t x_st16, const int32_t* __restrict__ topk_ids,
     const float* __restrict__ topk_w, const int32_t* __restrict__ tok_pos,
     const int32_t* __restrict__ counts, const EpPeers peers, int32_t* __restrict__ ticket,
     int tokens, int chunks, int top_k, int experts_per_rank, int world, int rank, int64_t cap,
     int32_t epoch) {
-  const int64_t idx = int64_t(blockIdx.x) * 256 + threadIdx.x;
-  const int64_t t = idx / chunks;
-  const int ch = int(idx % chunks);
-  if (t < tokens) {
-    const uint4 v = x[t * x_st16 + ch];
-    const int meta_st = 1 + 2 * top_k;
+  const int lane = threadIdx.x & 31;
+  const int warps = gridDim.x * kEpWarps;
+  const int meta_st = 1 + 2 * top_k;
+  for (int t = blockIdx.x * kEpWarps + (threadIdx.x >> 5); t < tokens; t += warps) {
     for (int d = 0; d < world; ++d) {
       const int pos = tok_pos[int64_t(d) * tokens + t];
       if (pos < 0 || pos >= cap) continue;
       const int64_t row = int64_t(rank) * cap + pos;
-      reinterpret_cast<uint4*>(peers.recv[d])[row * chunks + ch] = v;
-      if (ch == 0) {
+      uint4* dst = reinterpret_cast<uint4*>(peers.recv[d]) + row * chunks;
+      const uint4* src = x + int64_t(t) * x_st16;
+      for (int ch = lane; ch < chunks; ch += 32) dst[ch] = src[ch];
+      if (lane <= top_k) {
         int32_t* m = peers.meta[d] + row * meta_st;
-        m[0] = int32_t(t);
-        for (int j = 0; j < top_k; ++j) {
+        if (lane == 0) {
+          m[0] = t;
+        } else {
+          const int j = lane - 1;
           const int e = topk_ids[t * top_k + j];
           const bool here = e >= 0 && e / experts_per_rank == d;
           m[1 + 2 * j] = here ? e % experts_per_rank : -1;
@@ -141,21 +165,14 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(
       }
     }
   }
-  // publish: every thread's stores first, then the grid's last CTA raises the flags
-  __threadfence_system();
-  __syncthreads();
-  __shared__ int s_last;
-  if (threadIdx.x == 0) s_last = atomicAdd(ticket, 1) == int(gridDim.x) - 1;
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence_system();
-  if (threadIdx.x < world) {
-    const int d = threadIdx.x;
-    peers.counts[d][rank] = min(counts[d], int(cap));
-    __threadfence_system();
-    st_release_sys(peers.flags[d] + rank, epoch);
-  }
-  if (threadIdx.x == 0) *ticket = 0;
+  publish_when_last(ticket, [&] {
+    if (threadIdx.x < world) {
+      const int d = threadIdx.x;
+      peers.counts[d][rank] = min(counts[d], int(cap));
+      __threadfence_system();
+      st_release_sys(peers.flags[d] + rank, epoch);
+    }
+  });
 }
 
 // Receiver: ids / weights per (row, slot) for the rows that arrived, -1 elsewhere.
@@ -192,50 +209,47 @@ __global__ void __launch_bounds__(256) ep_prepare_kernel(
 
 // Expert rank: one bf16 row per received token = the fp32 sum of its result rows
 // here, written into the source rank's ret region at the source's token index.
-__global__ void __launch_bounds__(256) ep_return_kernel(
+// A warp = one received row at a time (rows nothing arrived in cost one compare).
+__global__ void __launch_bounds__(kEpWarps * 32) ep_return_kernel(
     const uint16_t* __restrict__ y, int64_t y_st, const int32_t* __restrict__ ids,
     const int32_t* __restrict__ meta, const int32_t* __restrict__ counts, const EpPeers peers,
     int32_t* __restrict__ ticket, int world, int rank, int64_t cap, int top_k, int hidden8,
     int32_t epoch) {
-  const int64_t idx = int64_t(blockIdx.x) * 256 + threadIdx.x;
-  const int64_t row = idx / hidden8;
-  const int h = int(idx % hidden8) * 8;
-  if (row < int64_t(world) * cap) {
+  const int lane = threadIdx.x & 31;
+  const int warps = gridDim.x * kEpWarps;
+  const int64_t rows = int64_t(world) * cap;
+  for (int64_t row = blockIdx.x * kEpWarps + (threadIdx.x >> 5); row < rows; row += warps) {
     const int src = int(row / cap), pos = int(row % cap);
-    if (pos < counts[src]) {
+    if (pos >= counts[src]) continue;
+    const int tok = meta[row * (1 + 2 * top_k)];
+    uint16_t* dst = reinterpret_cast<uint16_t*>(peers.ret[src]) + (int64_t(rank) * cap + tok) * (int64_t(hidden8) * 8);
+    for (int c = lane; c < hidden8; c += 32) {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
       for (int j = 0; j < top_k; ++j) {
         if (ids[row * top_k + j] < 0) continue;
-        const uint4 w = *reinterpret_cast<const uint4*>(y + (row * top_k + j) * y_st + h);
+        const uint4 w = *reinterpret_cast<const uint4*>(y + (row * top_k + j) * y_st + c * 8);
         const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[2 * i] += bf16_lo(ws[i]), acc[2 * i + 1] += bf16_hi(ws[i]);
       }
-      const int tok = meta[row * (1 + 2 * top_k)];
       uint4 o;
       o.x = pack_bf16x2(acc[0], acc[1]), o.y = pack_bf16x2(acc[2], acc[3]);
       o.z = pack_bf16x2(acc[4], acc[5]), o.w = pack_bf16x2(acc[6], acc[7]);
-      uint16_t* dst = reinterpret_cast<uint16_t*>(peers.ret[src]) +
-                      (int64_t(rank) * cap + tok) * (int64_t(hidden8) * 8) + h;
-      *reinterpret_cast<uint4*>(dst) = o;
+      *reinterpret_cast<uint4*>(dst + c * 8) = o;
     }
   }
-  __threadfence_system();
-  __syncthreads();
-  __shared__ int s_last;
-  if (threadIdx.x == 0) s_last = atomicAdd(ticket, 1) == int(gridDim.x) - 1;
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence_system();
-  if (threadIdx.x < world) st_release_sys(peers.rflags[threadIdx.x] + rank, epoch);
-  if (threadIdx.x == 0) *ticket = 0;
+  publish_when_last(ticket, [&] {
+    if (threadIdx.x < world) st_release_sys(peers.rflags[threadIdx.x] + rank, epoch);
+  });
 }
 
 // Source rank: out[t] = sum over the ranks token t was sent to of their partial rows.
-__global__ void __launch_bounds__(256) ep_combine_kernel(
-    const uint16_t* ret, const int32_t* rflags,
-    const int32_t* __restrict__ tok_pos, uint16_t* __restrict__ out, int64_t out_st, int tokens,
-    int hidden8, int world, int64_t cap, int32_t epoch, uint32_t spin_limit) {
+// A warp = one token at a time. (ret is written by the peers while this kernel waits:
+// it is read with ld.global.cg after the flags, never through the non-coherent path.)
+__global__ void __launch_bounds__(kEpWarps * 32) ep_combine_kernel(
+    const uint16_t* ret, const int32_t* rflags, const int32_t* __restrict__ tok_pos,
+    uint16_t* __restrict__ out, int64_t out_st, int tokens, int hidden8, int world, int64_t cap,
+    int32_t epoch, uint32_t spin_limit) {
   __shared__ int s_ok;
   if (threadIdx.x == 0) {
     bool ok = true;
@@ -244,23 +258,27 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(
     s_ok = ok;
   }
   __syncthreads();
-  const int64_t idx = int64_t(blockIdx.x) * 256 + threadIdx.x;
-  if (idx >= int64_t(tokens) * hidden8) return;
-  const int64_t t = idx / hidden8;
-  const int h = int(idx % hidden8) * 8;
-  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  if (s_ok)
-    for (int d = 0; d < world; ++d) {
-      if (tok_pos[int64_t(d) * tokens + t] < 0) continue;
-      const uint4 w = __ldcg(reinterpret_cast<const uint4*>(ret + (int64_t(d) * cap + t) * (int64_t(hidden8) * 8) + h));
-      const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+  const int lane = threadIdx.x & 31;
+  const int warps = gridDim.x * kEpWarps;
+  for (int t = blockIdx.x * kEpWarps + (threadIdx.x >> 5); t < tokens; t += warps) {
+    unsigned from = 0;
+    if (s_ok)
+      for (int d = 0; d < world; ++d) from |= tok_pos[int64_t(d) * tokens + t] >= 0 ? 1u << d : 0u;
+    for (int c = lane; c < hidden8; c += 32) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int d = 0; d < world; ++d) {
+        if (!(from >> d & 1)) continue;
+        const uint4 w = __ldcg(reinterpret_cast<const uint4*>(ret + (int64_t(d) * cap + t) * (int64_t(hidden8) * 8) + c * 8));
+        const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-      for (int i = 0; i < 4; ++i) acc[2 * i] += bf16_lo(ws[i]), acc[2 * i + 1] += bf16_hi(ws[i]);
+        for (int i = 0; i < 4; ++i) acc[2 * i] += bf16_lo(ws[i]), acc[2 * i + 1] += bf16_hi(ws[i]);
+      }
+      uint4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]), o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]), o.w = pack_bf16x2(acc[6], acc[7]);
+      *reinterpret_cast<uint4*>(out + int64_t(t) * out_st + c * 8) = o;
     }
-  uint4 o;
-  o.x = pack_bf16x2(acc[0], acc[1]), o.y = pack_bf16x2(acc[2], acc[3]);
-  o.z = pack_bf16x2(acc[4], acc[5]), o.w = pack_bf16x2(acc[6], acc[7]);
-  *reinterpret_cast<uint4*>(out + t * out_st + h) = o;
+  }
 }
 
 // Byte rows into sorted order by scatter (the byte twin of moe_permute_bf16):
@@ -289,6 +307,19 @@ __global__ void __launch_bounds__(256) permute_byte_rows_kernel(
   const int64_t sid = sorted_ids[r];
   if (sid >= 0 && sid < num_valid) return;
   y[r * y_st16 + ch] = make_uint4(0u, 0u, 0u, 0u);
+}
+
+// CTAs of a row-copy kernel: enough warps for the rows, at most eight CTAs per SM
+unsigned row_grid(int64_t rows) {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      sms = 148;
+  }
+  const int64_t want = (rows + kEpWarps - 1) / kEpWarps;
+  return unsigned(want < 1 ? 1 : want > int64_t(sms) * 8 ? int64_t(sms) * 8 : want);
 }
 
 int fill_peers(EpPeers* p, void* const* recv, void* const* meta, void* const* counts, void* const* flags,
@@ -361,7 +392,8 @@ extern "C" int strix_ep_status(int32_t* host_out, int reset) {
 // ------------------------------------------------------------------ kernels
 extern "C" int strix_ep_plan(const int32_t* topk_ids, int32_t* tok_pos, int32_t* counts, int64_t tokens,
                              int64_t top_k, int64_t experts_per_rank, int64_t world, strix_stream_t stream) {
-  STRIX_CHECK(topk_ids != nullptr && tok_pos != nullptr && counts != nullptr, "pointers must not be NULL");
+  STRIX_CHECK(counts != nullptr && (tokens == 0 || (topk_ids != nullptr && tok_pos != nullptr)),
+              "pointers must not be NULL");
   STRIX_CHECK(tokens >= 0 && top_k >= 1 && experts_per_rank >= 1 && world >= 1 && world <= kEpMaxWorld,
               "bad sizes");
   ep_plan_kernel<<<unsigned(world), 256, 0, static_cast<cudaStream_t>(stream)>>>(
@@ -375,18 +407,19 @@ extern "C" int strix_ep_dispatch(const void* x, const int32_t* topk_ids, const f
                                  int32_t* ticket, int64_t tokens, int64_t row_bytes, int64_t x_stride_bytes,
                                  int64_t top_k, int64_t experts_per_rank, int64_t world, int64_t rank,
                                  int64_t cap, int64_t epoch, strix_stream_t stream) {
-  STRIX_CHECK(x != nullptr && topk_ids != nullptr && topk_weights != nullptr && tok_pos != nullptr &&
-                  counts != nullptr && ticket != nullptr, "pointers must not be NULL");
+  STRIX_CHECK(counts != nullptr && ticket != nullptr &&
+                  (tokens == 0 || (x != nullptr && topk_ids != nullptr && topk_weights != nullptr &&
+                                   tok_pos != nullptr)), "pointers must not be NULL");
   STRIX_CHECK(row_bytes > 0 && row_bytes % 16 == 0 && x_stride_bytes % 16 == 0 &&
                   reinterpret_cast<uintptr_t>(x) % 16 == 0, "payload rows must be whole 16-byte chunks");
-  STRIX_CHECK(tokens >= 0 && tokens <= cap && rank >= 0 && rank < world && top_k >= 1 && top_k <= 32,
+  STRIX_CHECK(tokens >= 0 && tokens <= cap && rank >= 0 && rank < world && top_k >= 1 && top_k <= 31,
               "tokens must fit the buffer capacity");
   EpPeers peers;
   if (int rc = fill_peers(&peers, peer_recv, peer_meta, peer_counts, peer_flags, nullptr, nullptr, world)) return rc;
   const int chunks = int(row_bytes / 16);
-  const int64_t work = tokens * chunks;
-  const unsigned grid = unsigned(work > 0 ? (work + 255) / 256 : 1);   // an empty rank still raises its flags
-  ep_dispatch_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  // an empty rank still raises its flags
+  const unsigned grid = row_grid(tokens);
+  ep_dispatch_kernel<<<grid, kEpWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(x), x_stride_bytes / 16, topk_ids, topk_weights, tok_pos, counts, peers,
       ticket, int(tokens), chunks, int(top_k), int(experts_per_rank), int(world), int(rank), cap,
       int32_t(epoch));
@@ -418,8 +451,7 @@ extern "C" int strix_ep_return(const void* y, const int32_t* ids, const int32_t*
   EpPeers peers;
   if (int rc = fill_peers(&peers, nullptr, nullptr, nullptr, nullptr, peer_ret, peer_rflags, world)) return rc;
   STRIX_CHECK(rank >= 0 && rank < world && cap >= 1, "bad rank");
-  const int64_t work = world * cap * (hidden / 8);
-  ep_return_kernel<<<unsigned((work + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  ep_return_kernel<<<row_grid(world * cap), kEpWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint16_t*>(y), y_stride, ids, meta, counts, peers, ticket, int(world), int(rank),
       cap, int(top_k), int(hidden / 8), int32_t(epoch));
   return launch_status("ep_return");
@@ -428,14 +460,12 @@ extern "C" int strix_ep_return(const void* y, const int32_t* ids, const int32_t*
 extern "C" int strix_ep_combine(const void* ret, const int32_t* rflags, const int32_t* tok_pos, void* out,
                                 int64_t tokens, int64_t hidden, int64_t out_stride, int64_t world,
                                 int64_t cap, int64_t epoch, int64_t spin_limit, strix_stream_t stream) {
-  STRIX_CHECK(ret != nullptr && rflags != nullptr && tok_pos != nullptr && out != nullptr,
+  STRIX_CHECK(ret != nullptr && rflags != nullptr && (tokens == 0 || (tok_pos != nullptr && out != nullptr)),
               "pointers must not be NULL");
   STRIX_CHECK(hidden > 0 && hidden % 8 == 0 && out_stride % 8 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0,
               "hidden must be a multiple of 8");
   STRIX_CHECK(tokens >= 0 && tokens <= cap && world >= 1 && world <= kEpMaxWorld, "bad sizes");
-  const int64_t work = tokens * (hidden / 8);
-  const unsigned grid = unsigned(work > 0 ? (work + 255) / 256 : 1);
-  ep_combine_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  ep_combine_kernel<<<row_grid(tokens), kEpWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint16_t*>(ret), rflags, tok_pos, static_cast<uint16_t*>(out), out_stride, int(tokens),
       int(hidden / 8), int(world), cap, int32_t(epoch), spin_limit > 0 ? uint32_t(spin_limit) : kEpSpinDefault);
   return launch_status("ep_combine");

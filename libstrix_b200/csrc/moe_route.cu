@@ -85,8 +85,11 @@ __global__ void __launch_bounds__(128) topk_softmax_kernel(
 // itself (one pass over the ids, served by L2), so there is no inter-CTA
 // dependency and a single launch suffices. Order inside an expert is ascending
 // slot id (a stable partition), which makes the result unique and comparable
-// bit for bit.
-constexpr int kAlignThreads = 256;
+// bit for bit. Every warp owns one contiguous eighth of the slots: the histogram
+// pass also counts the warp's hits for expert e, one barrier turns the counts
+// into offsets, and the placement pass runs on warp ballots alone - no barrier
+// inside either pass, whatever the number of slots.
+constexpr int kAlignThreads = 256, kAlignWarps = kAlignThreads / 32;
 
 __global__ void __launch_bounds__(kAlignThreads) moe_align_kernel(
     const int32_t* __restrict__ topk_ids, int32_t* __restrict__ sorted_ids,
@@ -94,15 +97,21 @@ __global__ void __launch_bounds__(kAlignThreads) moe_align_kernel(
     int block_m, int cap, int cap_blocks, int32_t* __restrict__ slot_pos,
     int32_t* __restrict__ counts) {
   extern __shared__ int s_count[];            // [experts]
-  __shared__ int s_warp[kAlignThreads / 32];
+  __shared__ int s_warp[kAlignWarps];
   __shared__ int s_base;
-  const int e = blockIdx.x, tid = threadIdx.x;
+  const int e = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   for (int i = tid; i < experts; i += kAlignThreads) s_count[i] = 0;
   __syncthreads();
-  for (int i = tid; i < numel; i += kAlignThreads) {
-    const int id = topk_ids[i];
+  // this warp's slots: [lo, hi), a multiple of 32 long except at the end
+  const int per_warp = ((numel + kAlignWarps - 1) / kAlignWarps + 31) / 32 * 32;
+  const int lo = min(warp * per_warp, numel), hi = min(lo + per_warp, numel);
+  int mine = 0;                                // hits for expert e in this warp's slots
+  for (int i = lo + lane; i - lane < hi; i += 32) {
+    const int id = i < hi ? topk_ids[i] : -1;
     if (id >= 0 && id < experts) atomicAdd(&s_count[id], 1);
+    mine += __popc(__ballot_sync(0xffffffffu, id == e));
   }
+  if (lane == 0) s_warp[warp] = mine;
   __syncthreads();
   // padded slots before expert e (or the grand total for the last CTA)
   int part = 0;
@@ -111,12 +120,16 @@ __global__ void __launch_bounds__(kAlignThreads) moe_align_kernel(
     part += (s_count[i] + block_m - 1) / block_m * block_m;
 #pragma unroll
   for (int o = 16; o; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-  if ((tid & 31) == 0) s_warp[tid >> 5] = part;
+  int before = 0;                              // hits of the warps in front of this one
+#pragma unroll
+  for (int w = 0; w < kAlignWarps; ++w) before += w < warp ? s_warp[w] : 0;
+  __syncthreads();                             // s_warp is reused for the partial sums
+  if (lane == 0) s_warp[warp] = part;
   __syncthreads();
   if (tid == 0) {
-    int s = 0;
-    for (int i = 0; i < kAlignThreads / 32; ++i) s += s_warp[i];
-    s_base = s;
+    int t = 0;
+    for (int i = 0; i < kAlignWarps; ++i) t += s_warp[i];
+    s_base = t;
   }
   __syncthreads();
   const int base = s_base;
@@ -141,27 +154,16 @@ __global__ void __launch_bounds__(kAlignThreads) moe_align_kernel(
     if (base + i < cap) sorted_ids[base + i] = numel;
   if (count == 0) return;
   // ordered compaction of the slots whose id == e
-  int placed = 0;
-  for (int start = 0; start < numel; start += kAlignThreads) {
-    const int i = start + tid;
-    const bool hit = i < numel && topk_ids[i] == e;
+  int placed = base + before;
+  for (int i = lo + lane; i - lane < hi; i += 32) {
+    const bool hit = i < hi && topk_ids[i] == e;
     const unsigned bal = __ballot_sync(0xffffffffu, hit);
-    __syncthreads();  // s_warp reuse
-    if ((tid & 31) == 0) s_warp[tid >> 5] = __popc(bal);
-    __syncthreads();
-    int before = 0, total = 0;
-#pragma unroll
-    for (int w = 0; w < kAlignThreads / 32; ++w) {
-      const int c = s_warp[w];
-      before += w < (tid >> 5) ? c : 0;
-      total += c;
-    }
     if (hit) {
-      const int pos = base + placed + before + __popc(bal & ((1u << (tid & 31)) - 1u));
+      const int pos = placed + __popc(bal & ((1u << lane) - 1u));
       if (pos < cap) sorted_ids[pos] = i;
       if (slot_pos != nullptr) slot_pos[i] = pos < cap ? pos : -1;   // the inverse permutation
     }
-    placed += total;
+    placed += __popc(bal);
   }
 }
 

@@ -235,6 +235,10 @@ def local_experts_fp8(w13, w13_scale, w2, w2_scale, block_m: int | None = None):
 
 
 # --------------------------------------------------------------- peer memory
+def _no_mark(name: str) -> None:
+    pass
+
+
 class _RawCuda:
     """A cudaMalloc allocation presented through __cuda_array_interface__."""
 
@@ -337,9 +341,10 @@ class EpContext:
 
     # ---- the exchange phases (each enqueues kernels on the current stream)
     def dispatch(self, payload: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
-                 experts_per_rank: int):
+                 experts_per_rank: int, mark=_no_mark):
         """payload [T, row_bytes worth of elements] (last dim contiguous) goes to every
-        rank that owns one of the token's experts."""
+        rank that owns one of the token's experts. `mark(name)` is called after each
+        kernel is enqueued (a hook for per-phase timing)."""
         t, k = topk_ids.shape
         assert k == self.top_k and t <= self.cap
         assert payload.size(1) * payload.element_size() == self.row_bytes and payload.stride(1) == 1
@@ -354,11 +359,13 @@ class EpContext:
         with torch.cuda.device(self.device):
             call("strix_ep_plan", ids.data_ptr(), self.tok_pos.data_ptr(), self.counts.data_ptr(), t, k,
                  experts_per_rank, self.world, stream)
+            mark("plan")
             call("strix_ep_dispatch", payload.data_ptr(), ids.data_ptr(), wts.data_ptr(),
                  self.tok_pos.data_ptr(), self.counts.data_ptr(), self._ptrs("recv"), self._ptrs("meta"),
                  self._ptrs("counts"), self._ptrs("flags"), self.ticket.data_ptr(), t, self.row_bytes,
                  payload.stride(0) * payload.element_size(), k, experts_per_rank, self.world, self.rank,
                  self.cap, self.epoch, stream)
+            mark("dispatch")
 
     def receive(self, spin_limit: int = 0):
         """Waits (on the device) for every source; returns (rows uint8 [world * cap,
@@ -402,52 +409,63 @@ class EpContext:
         return flag.value
 
 
-def _experts_mxfp4_on_received(ctx: EpContext, w13, w13_scale, w2, w2_scale):
+def _experts_mxfp4_on_received(ctx: EpContext, w13, w13_scale, w2, w2_scale, mark=_no_mark):
     """The received tokens through this rank's MXFP4 experts; returns y in slot order."""
     from . import moe as _moe
 
     rows, ids, weights = ctx.receive()
+    mark("receive_wait")
     e = w13.size(0)
     inter = w13.size(1) // 2
     ops = torch.ops.strix
     sorted_ids, expert_ids, num_post, slot_pos = _moe.align_with_positions(ids, 128, e)
+    mark("align")
     cap_s = sorted_ids.numel()
     dev = ctx.device
     xs = torch.empty(cap_s, ctx.row_bytes // 2, dtype=torch.bfloat16, device=dev)
     act = torch.empty(cap_s, inter, dtype=torch.bfloat16, device=dev)
     ops.moe_permute_rows(rows, xs.view(torch.uint8), slot_pos, sorted_ids, num_post, ctx.top_k)
+    mark("permute")
     n_slots = ids.numel()
     ops.moe_gemm_mxfp4_sorted(act, xs, w13, w13_scale, sorted_ids, expert_ids, num_post, None, n_slots,
                               128, True, "silu", True)
+    mark("gemm_gate_up")
     ops.moe_gemm_mxfp4_sorted(ctx.y, act, w2, w2_scale, sorted_ids, expert_ids, num_post,
                               weights.view(-1), n_slots, 128, False, "silu", False)
+    mark("gemm_down")
     return ctx.y
 
 
-def _experts_fp8_on_received(ctx: EpContext, w13, w13_scale, w2, w2_scale, block_m):
+def _experts_fp8_on_received(ctx: EpContext, w13, w13_scale, w2, w2_scale, block_m, mark=_no_mark):
     """The received (already quantised) tokens through this rank's FP8 experts."""
     from . import moe as _moe
 
     rows, ids, weights = ctx.receive()
+    mark("receive_wait")
     e, n13, h = w13.shape
     inter = n13 // 2
     ops = torch.ops.strix
     f8 = torch.float8_e4m3fn
     sorted_ids, expert_ids, num_post, slot_pos = _moe.align_with_positions(ids, block_m, e)
+    mark("align")
     cap_s = sorted_ids.numel()
     dev = ctx.device
     srt = torch.empty(cap_s, ctx.row_bytes, dtype=torch.uint8, device=dev)
     ops.moe_permute_rows(rows, srt, slot_pos, sorted_ids, num_post, ctx.top_k)
-    xq, xs = srt[:, :h].view(f8), srt[:, h:].view(torch.float32)
+    mark("permute")
+    xq, xs = srt[:, :h].view(f8), srt[:, h:h + h // 32].view(torch.float32)
     act = torch.empty(cap_s, inter, dtype=torch.bfloat16, device=dev)
     aq = torch.empty(cap_s, inter, dtype=f8, device=dev)
     as_ = torch.empty(cap_s, inter // 128, dtype=torch.float32, device=dev)
     n_slots = ids.numel()
     ops.moe_gemm_fp8_sorted(act, xq, xs, w13, w13_scale, sorted_ids, expert_ids, num_post, None, n_slots,
                             block_m, True, "silu", True)
+    mark("gemm_gate_up")
     ops.moe_act_quant_fp8_sorted(act, aq, as_, None, num_post, 1, n_slots)
+    mark("act_quant")
     ops.moe_gemm_fp8_sorted(ctx.y, aq, as_, w2, w2_scale, sorted_ids, expert_ids, num_post,
                             weights.view(-1), n_slots, block_m, False, "silu", False)
+    mark("gemm_down")
     return ctx.y
 
 
@@ -475,21 +493,27 @@ def close_contexts() -> None:
     _CONTEXTS.clear()
 
 
+def fp8_row_bytes(hidden: int) -> int:
+    """Bytes of an FP8 payload row: `hidden` e4m3 bytes, hidden / 128 fp32 scales,
+    padded to whole 16-byte chunks."""
+    return (hidden + hidden // 32 + 15) // 16 * 16
+
+
 def fp8_payload(x: torch.Tensor, buf: torch.Tensor | None = None):
-    """(payload uint8 [T, H + H / 32], q view, scale view): x quantised to e4m3 per
-    (token, 128 group) with the fp32 scales behind each row's bytes - what the FP8
-    layer sends instead of bf16 rows."""
+    """(payload uint8 [T, fp8_row_bytes(H)], q view, scale view): x quantised to e4m3
+    per (token, 128 group) with the fp32 scales behind each row's bytes - what the
+    FP8 layer sends instead of bf16 rows."""
     t, h = x.shape
-    row = h + h // 32
+    row = fp8_row_bytes(h)
     if buf is None or buf.size(0) < t or buf.size(1) != row:
-        buf = torch.empty(max(t, 1), row, dtype=torch.uint8, device=x.device)
-    q, s = buf[:t, :h].view(torch.float8_e4m3fn), buf[:t, h:].view(torch.float32)
+        buf = torch.zeros(max(t, 1), row, dtype=torch.uint8, device=x.device)
+    q, s = buf[:t, :h].view(torch.float8_e4m3fn), buf[:t, h:h + h // 32].view(torch.float32)
     torch.ops.strix.moe_act_quant_fp8(x, q, s)
     return buf[:t], q, s
 
 
 def ep_moe_fp8(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, block_m=None,
-               exchange="auto", ctx=None):
+               exchange="auto", ctx=None, mark=_no_mark):
     """One expert-parallel FP8 W8A8 block-scaled MoE layer. x bf16 [T_local, H];
     logits fp32 [T_local, E_global]; the weight tensors hold this rank's E_global /
     world experts. Returns bf16 [T_local, H]. exchange: "peer" (this library's
@@ -513,21 +537,26 @@ def ep_moe_fp8(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, block
                                    local_experts_fp8(w13, w13_scale, w2, w2_scale, block_m), group,
                                    combine)
     e_local = w13.size(0)
-    row_bytes = h + h // 32
+    row_bytes = fp8_row_bytes(h)
     if ctx is None:
         ctx = context_for(group, t, top_k, row_bytes, h, x.device)
     bm = block_m or _moe.pick_block_m(t * ctx.world, top_k, e_local * ctx.world)
     if not _moe.sorted_path_covers(w13, w13_scale, w2, w2_scale, bm):
         raise RuntimeError("ep_moe_fp8: geometry not covered by the sorted-layout kernel")
+    mark("route")
     payload, _, _ = fp8_payload(x)
-    ctx.dispatch(payload, weights, ids, e_local)
-    y = _experts_fp8_on_received(ctx, w13, w13_scale, w2, w2_scale, bm)
+    mark("quantise")
+    ctx.dispatch(payload, weights, ids, e_local, mark)
+    y = _experts_fp8_on_received(ctx, w13, w13_scale, w2, w2_scale, bm, mark)
     ctx.send_back(y)
-    return ctx.combine()
+    mark("return")
+    out = ctx.combine()
+    mark("combine_wait")
+    return out
 
 
 def ep_moe_mxfp4(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, block_m=None,
-                 exchange="auto", ctx=None):
+                 exchange="auto", ctx=None, mark=_no_mark):
     """One expert-parallel MXFP4 MoE layer. x bf16 [T_local, H]; logits fp32
     [T_local, E_global]; the weight tensors hold this rank's E_global / world
     experts. Router and combine run on this rank's tokens, the experts where
@@ -554,10 +583,14 @@ def ep_moe_mxfp4(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, blo
                                    group, combine)
     if ctx is None:
         ctx = context_for(group, t, top_k, h * 2, h, x.device)
-    ctx.dispatch(x, weights, ids, w13.size(0))
-    y = _experts_mxfp4_on_received(ctx, w13, w13_scale, w2, w2_scale)
+    mark("route")
+    ctx.dispatch(x, weights, ids, w13.size(0), mark)
+    y = _experts_mxfp4_on_received(ctx, w13, w13_scale, w2, w2_scale, mark)
     ctx.send_back(y)
-    return ctx.combine()
+    mark("return")
+    out = ctx.combine()
+    mark("combine_wait")
+    return out
 
 
 def _capacity(tokens: int, group) -> int:

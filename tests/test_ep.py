@@ -263,6 +263,9 @@ def test_peer_exchange_with_emulated_ranks(kind, tokens_per_rank):
                 for d in range(world):
                     assert int(got[d, r]) == int((mine == d).any(-1).sum())
             for r in range(world):
+                if tokens_per_rank[r] == 0:
+                    assert outs[r].shape == (0, hid)
+                    continue
                 ok, err, rms = _bound_ok(outs[r], ref[offs[r]:offs[r + 1]])
                 assert ok, f"round {rounds} rank {r}: max err {err} vs rms {rms}"
     finally:
