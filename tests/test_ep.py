@@ -233,7 +233,7 @@ def test_peer_exchange_with_emulated_ranks(kind, tokens_per_rank):
         layer = moe_fp8_layer(tokens=256, hidden=hid, experts=e_global, top_k=k, inter=inter, seed=3)
         ref, _, _ = M.moe_fp8_layer(layer.x[:total], layer.logits[:total], layer.w13, layer.w13_scale,
                                     layer.w2, layer.w2_scale, k)
-        row_bytes = hid + hid // 32
+        row_bytes = ep.fp8_row_bytes(hid)
     g = layer.to(dev)
     ctxs = ep.EpContext.emulate(world, max(tokens_per_rank), k, row_bytes, hid, dev)
     try:
