@@ -318,6 +318,16 @@ int strix_dequant_bf16(void* out, const void* w, const void* scales, int64_t n, 
                        int format, int group, int scale_kind, int scale_dtype,
                        strix_stream_t stream);
 
+/* Dynamic per-token int8 quantisation of activations, the input form of
+ * strix_w8a8_int8_gemm: x bf16 (fp16 if in_f16) [rows, k] -> q int8 [rows, k],
+ * scales fp32 [rows] with scale = absmax / 127 (1 for an all-zero row), q =
+ * rint(x / scale). The reference's w8a8_wmma_gemm quantises per 128 group inside
+ * its GEMM (csrc/gemm/w8a8_wmma_gemm.hip:508-529); this is the per-token rule of
+ * benchmark config 2 and of vLLM's int8 scaled-MM contract. Strides in elements. */
+int strix_act_quant_token_i8(const void* x, void* q, float* scales, int64_t rows, int64_t k,
+                             int64_t x_stride, int64_t q_stride, int in_f16,
+                             strix_stream_t stream);
+
 /* Health of the tcgen05 kernels: *host_out = 0 while every launch so far met its
  * bounded waits, 1 after one of them gave up (its output is then incomplete).
  * Synchronises the device; for tests and debugging. No reference counterpart. */

@@ -241,6 +241,57 @@ __global__ void __launch_bounds__(kGThreads, 1) gemm_w8a8_umma_kernel(const Gemm
   if (warp == 1) tmem_dealloc(tmem, L::kTmemCols);
 }
 
+// Dynamic per-token int8 quantisation of the activations (the input form of the
+// GEMM above; vLLM's scaled_int8_quant rule for symmetric dynamic activations):
+// scale = absmax / 127 (1 for an all-zero row), q = rint(x / scale). One CTA per
+// row: a pass for the maximum, a pass to write (the row is served by L1 / L2).
+__global__ void __launch_bounds__(256) act_quant_token_i8_kernel(
+    const uint16_t* __restrict__ x, int64_t x_st, int8_t* __restrict__ q, int64_t q_st,
+    float* __restrict__ scales, int k8, int in_f16) {
+  __shared__ float s_red[8];
+  const int64_t row = blockIdx.x;
+  const uint4* src = reinterpret_cast<const uint4*>(x + row * x_st);
+  auto unpack = [&](const uint4& w, float* v) {
+    const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (in_f16) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&ws[i]));
+        v[2 * i] = f.x, v[2 * i + 1] = f.y;
+      } else {
+        v[2 * i] = bf16_lo(ws[i]), v[2 * i + 1] = bf16_hi(ws[i]);
+      }
+    }
+  };
+  float amax = 0.f;
+  for (int c = threadIdx.x; c < k8; c += 256) {
+    float v[8];
+    unpack(src[c], v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = s_red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) amax = fmaxf(amax, s_red[i]);
+  const float s = amax > 0.f ? __fdiv_rn(amax, 127.f) : 1.f;
+  if (threadIdx.x == 0) scales[row] = s;
+  uint2* dst = reinterpret_cast<uint2*>(q + row * q_st);
+  for (int c = threadIdx.x; c < k8; c += 256) {
+    float v[8];
+    unpack(src[c], v);
+    int b[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      b[i] = __float2int_rn(fminf(fmaxf(rintf(__fdiv_rn(v[i], s)), -127.f), 127.f)) & 255;
+    dst[c] = make_uint2(b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24),
+                        b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24));
+  }
+}
+
 template <int NB>
 int launch_gemm(const GemmArgs& p, const void* a_mat, int64_t a_stride, const void* b_mat,
                 int64_t b_stride, cudaStream_t st) {
@@ -308,4 +359,18 @@ extern "C" int strix_w8a8_int8_gemm(void* out, int32_t* acc_out, const void* a_q
   p.a_rows = int(m), p.b_rows = int(n);
   p.a_tiles = int((m + 127) / 128), p.b_tiles = int((n + 255) / 256);
   return launch_gemm<256>(p, a_q, a_stride, w, w_stride, st);
+}
+
+extern "C" int strix_act_quant_token_i8(const void* x, void* q, float* scales, int64_t rows, int64_t k,
+                                        int64_t x_stride, int64_t q_stride, int in_f16,
+                                        strix_stream_t stream) {
+  STRIX_CHECK(x != nullptr && q != nullptr && scales != nullptr, "pointers must not be NULL");
+  STRIX_CHECK(rows >= 0 && k > 0 && k % 8 == 0 && x_stride % 8 == 0 && q_stride % 8 == 0 &&
+                  reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(q) % 8 == 0,
+              "K must be a multiple of 8 with 16-byte aligned rows");
+  if (rows == 0) return STRIX_OK;
+  act_quant_token_i8_kernel<<<unsigned(rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint16_t*>(x), x_stride, static_cast<int8_t*>(q), q_stride, scales, int(k / 8),
+      in_f16);
+  return launch_status("act_quant_token_i8");
 }

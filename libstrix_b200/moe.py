@@ -14,6 +14,11 @@ import torch
 from . import _lib
 
 
+# m-blocks the sorted-layout tcgen05 kernels index in one launch (kMaxMBlocks in
+# csrc/moe_gemm_umma.cu); larger batches take the gather layout
+MAX_SORTED_M_BLOCKS = 2048
+
+
 def pick_block_m(tokens: int, top_k: int, experts: int) -> int:
     """Rows per m-block. Up to 16 rows per expert on average: the smaller of 16 /
     32 that holds an expert's share twice over, so most experts stream their
@@ -117,7 +122,20 @@ def fused_moe_fp8_w8a8(x, logits, w13, w13_scale, w2, w2_scale, top_k, block_m=N
     """One MoE layer, FP8 W8A8 block-scaled. x bf16 [T, H]; logits fp32 [T, E];
     w13 e4m3 [E, 2I, H] + fp32 scales [E, 2I/128, H/128]; w2 e4m3 [E, H, I] +
     scales [E, H/128, I/128]. Returns bf16 [T, H]. Seven kernel launches, no
-    host synchronisation.
+    host synchronisation: the router, then experts_fp8_w8a8."""
+    weights, ids = route(logits, top_k)
+    return experts_fp8_w8a8(x, weights, ids, w13, w13_scale, w2, w2_scale, block_m=block_m, ws=ws,
+                            layout=layout)
+
+
+def experts_fp8_w8a8(x, topk_weights, topk_ids, w13, w13_scale, w2, w2_scale, out=None,
+                     block_m=None, ws=None, layout="auto", activation="silu"):
+    """The experts of an FP8 W8A8 MoE layer for routing that is already decided
+    (topk_weights fp32 / topk_ids int32 [T, k], e.g. by the serving framework's
+    router): permute -> quantise -> gate-up GEMM with the fused gate -> quantise
+    -> down GEMM x routing weight -> sum over top-k into `out` (bf16 [T, H]).
+    The sequence is the reference's StrixFp8Experts.apply
+    (python/strix_vllm/moe.py:905-1014) with e4m3 activations per (token, 128).
 
     layout "sorted" (the default where covered): the quantiser permutes the
     tokens into sorted order, both GEMMs run on tcgen05 with TMA-fed operands,
@@ -126,11 +144,16 @@ def fused_moe_fp8_w8a8(x, logits, w13, w13_scale, w2, w2_scale, top_k, block_m=N
     id themselves (the reference's op contract, mma.sync streaming kernels)."""
     t, h = x.shape
     e, n13, _ = w13.shape
+    top_k = topk_ids.size(1)
     inter = n13 // 2
     bm = block_m or pick_block_m(t, top_k, e)
+    lib = _lib.load()
     if layout == "auto":
-        layout = "sorted" if sorted_path_covers(w13, w13_scale, w2, w2_scale, bm) else "gather"
-    weights, ids = route(logits, top_k)
+        cap_blocks = lib.strix_moe_align_capacity(t * top_k, e, bm) // bm
+        layout = "sorted" if sorted_path_covers(w13, w13_scale, w2, w2_scale, bm) \
+            and cap_blocks <= MAX_SORTED_M_BLOCKS else "gather"
+    weights = topk_weights.to(torch.float32)
+    ids = topk_ids.to(torch.int32).contiguous()
     ops = torch.ops.strix
     if layout == "sorted":
         sorted_ids, expert_ids, num_post, slot_pos = align_with_positions(ids, bm, e)
@@ -143,21 +166,22 @@ def fused_moe_fp8_w8a8(x, logits, w13, w13_scale, w2, w2_scale, top_k, block_m=N
         slots = t * top_k
         ops.moe_act_quant_fp8_scatter(x, ws.xq, ws.xs, slot_pos, sorted_ids, num_post, top_k)
         ops.moe_gemm_fp8_sorted(ws.act, ws.xq, ws.xs, w13, w13_scale, sorted_ids, expert_ids,
-                                num_post, None, slots, bm, True, "silu", True)
+                                num_post, None, slots, bm, True, activation, True)
         ops.moe_act_quant_fp8_sorted(ws.act, ws.aq, ws.as_, None, num_post, 1, slots)
         ops.moe_gemm_fp8_sorted(ws.y, ws.aq, ws.as_, w2, w2_scale, sorted_ids, expert_ids,
-                                num_post, weights.view(-1), slots, bm, False, "silu", False)
+                                num_post, weights.reshape(-1), slots, bm, False, "silu", False)
     else:
         if ws is None or ws.sorted_rows is not None:
             ws = Fp8MoeWorkspace(t, top_k, h, inter, x.device)
         ops.moe_act_quant_fp8(x, ws.xq, ws.xs)
         ops.moe_gemm_fp8_w8a8(ws.act, ws.xq, ws.xs, w13, w13_scale, sorted_ids, expert_ids,
-                              num_post, None, top_k, bm, 64, True, "silu")
+                              num_post, None, top_k, bm, 64, True, activation)
         ops.moe_act_quant_fp8(ws.act, ws.aq, ws.as_)
         ops.moe_gemm_fp8_w8a8(ws.y, ws.aq, ws.as_, w2, w2_scale, sorted_ids, expert_ids, num_post,
-                              weights.view(-1), 1, bm, 64, False, "silu")
-    ops.moe_sum(ws.y.view(t, top_k, h), ws.out)
-    return ws.out
+                              weights.reshape(-1), 1, bm, 64, False, "silu")
+    out = ws.out if out is None else out
+    ops.moe_sum(ws.y.view(t, top_k, h), out)
+    return out
 
 
 def fused_moe_mxfp4(x, logits, w13, w13_scale, w2, w2_scale, top_k, block_m=None):

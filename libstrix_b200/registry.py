@@ -291,6 +291,10 @@ KERNELS: list[Kernel] = [
            {"tile": "128 weights x 16/32/64 tokens (rows <= 64), 128 tokens x 256 weights",
             "pipeline": "4 producer warps (cp.async ring, 128B swizzle), 1 issuing thread, "
                         "4 epilogue warps, 2 TMEM accumulators, persistent grid"}),
+    Kernel("act_quant_token_i8", "act_quant_token",
+           "dynamic symmetric per-token int8 activations (scale = absmax / 127), the input "
+           "form of w8a8_int8_gemm",
+           {"dtype": ("bf16", "fp16"), "activation_dtype": "int8", "group_size": 0}),
     # ------------------------------------------------------------ attention
     Kernel("kv_write_i8", "kv_write",
            "new K/V rows quantised per (token, KV head) into the int8 paged cache with their "

@@ -960,6 +960,25 @@ def w8a8_int8_gemm(a_q, a_scale, w, w_scale, acc_out=None):
     return out
 
 
+def _act_quant_token_fake(x):
+    return (x.new_empty(x.shape, dtype=torch.int8),
+            x.new_empty((x.size(0),), dtype=torch.float32))
+
+
+@_define("act_quant_token_i8(Tensor x) -> (Tensor, Tensor)", fake=_act_quant_token_fake)
+def act_quant_token_i8(x):
+    """(q int8 [M, K], scale fp32 [M]): dynamic symmetric per-token quantisation, the
+    activation form w8a8_int8_gemm takes."""
+    _check(x.dim() == 2 and x.dtype in (torch.bfloat16, torch.float16) and x.stride(1) == 1
+           and x.size(1) % 8 == 0, "x must be bf16 or fp16 [M, K], K a multiple of 8")
+    q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    s = torch.empty(x.size(0), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.call("strix_act_quant_token_i8", x.data_ptr(), q.data_ptr(), s.data_ptr(), x.size(0),
+                  x.size(1), x.stride(0), q.stride(0), int(x.dtype == torch.float16), _stream())
+    return q, s
+
+
 # ----------------------------------------------------------- tcgen05 layout probe
 
 def _umma_tile_fake(a, b):
