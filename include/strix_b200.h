@@ -249,13 +249,15 @@ int strix_gemm_w4a16(void* c, const void* a, const void* w, const void* scales, 
  *   weight_format 0 e4m3, 1 int8, 5 excess-128 bytes (value = byte - 128)
  *   act_format    0 bf16, 1 fp16 (e4m3 weights only; exact weights, scaled sums)
  *   scale_kind    1 per channel [N]; 2 fp32 blocks [ceil(N/128), K/128] (e4m3);
- *                 3 per row and 128-wide K group [N, K/128]; s_stride_n = row stride
+ *                 3 per row and K group [N, K/group]; s_stride_n = row stride
+ *   group         K elements per scale for scale_kind 3: 128 (or 0), and 32 / 64 with
+ *                 bf16 activations (csrc/gemm/w8a16_skinny_gemm.hip:420-426)
  * c bf16 [m, n]; K a multiple of 128, N of 16. */
 int strix_dense_gemm_w8a16(void* c, const void* x, const void* w, const void* scales,
                            const void* bias, int64_t m, int64_t n, int64_t k, int64_t x_stride,
                            int64_t c_stride, int64_t w_stride, int64_t s_stride_n,
                            int64_t bias_stride, int64_t block_m, int weight_format,
-                           int act_format, int scale_kind, int scale_dtype, strix_stream_t stream);
+                           int act_format, int scale_kind, int scale_dtype, int group, strix_stream_t stream);
 
 /* bf16 rows into sorted order by scatter: row t of x [tokens, k] is copied to
  * the sorted positions slot_pos[t * top_k + j]; padding slots below

@@ -13,7 +13,9 @@
 namespace strix {
 namespace {
 
-enum DqFmt { DQ_MXFP4 = 0, DQ_INT4 = 1, DQ_E4M3 = 2 };
+// DQ_INT4X = int4 whose 32-bit words hold their nibbles in vLLM's ExLlama order
+// (k = 0 2 4 6 1 3 5 7), the dense layout of w4a16_dequant in the reference
+enum DqFmt { DQ_MXFP4 = 0, DQ_INT4 = 1, DQ_E4M3 = 2, DQ_INT4X = 3 };
 
 __device__ __forceinline__ float e2m1(uint32_t n) {
   const uint32_t e = (n >> 1) & 3u, m = n & 1u;
@@ -63,7 +65,11 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict_
       const uint16_t h = static_cast<const uint16_t*>(scales)[si];
       s = scale_dtype == 1 ? __uint_as_float(uint32_t(h) << 16) : __half2float(__ushort_as_half(h));
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = float(int((x >> (4 * i)) & 15u) - 8);
+      for (int i = 0; i < 8; ++i) {
+        // element i sits in nibble i, or (shuffled words) evens in the low half, odds in the high
+        const int nib = FMT == DQ_INT4X ? (i >> 1) + 4 * (i & 1) : i;
+        v[i] = float(int((x >> (4 * nib)) & 15u) - 8);
+      }
     }
   }
   uint4 o;
@@ -83,14 +89,14 @@ extern "C" int strix_dequant_bf16(void* out, const void* w, const void* scales, 
                                   int64_t w_stride, int64_t out_stride, int64_t s_stride_n,
                                   int64_t s_stride_g, int format, int group, int scale_kind,
                                   int scale_dtype, strix_stream_t stream) {
-  STRIX_CHECK(format >= DQ_MXFP4 && format <= DQ_E4M3, "format 0 mxfp4, 1 int4, 2 e4m3");
+  STRIX_CHECK(format >= DQ_MXFP4 && format <= DQ_INT4X, "format 0 mxfp4, 1 int4, 2 e4m3, 3 int4 (ExLlama order)");
   STRIX_CHECK(n >= 0 && k > 0 && k % 8 == 0, "K must be a multiple of 8");
   STRIX_CHECK(out_stride % 8 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0 &&
                   reinterpret_cast<uintptr_t>(w) % 8 == 0 &&
                   w_stride % (format == DQ_E4M3 ? 8 : 4) == 0,
               "aligned rows required");
   if (format == DQ_MXFP4) STRIX_CHECK(group == 32 && k % 32 == 0, "mxfp4 scales cover 32 elements");
-  if (format == DQ_INT4)
+  if (format == DQ_INT4 || format == DQ_INT4X)
     STRIX_CHECK((group == 32 || group == 64 || group == 128) && k % group == 0 &&
                     (scale_dtype == 1 || scale_dtype == 2),
                 "int4 scales are bf16 or fp16 per 32, 64 or 128 elements");
@@ -109,6 +115,9 @@ extern "C" int strix_dequant_bf16(void* out, const void* w, const void* scales, 
   else if (format == DQ_INT4)
     dequant_kernel<DQ_INT4><<<grid, 256, 0, st>>>(wp, w_stride, scales, s_stride_n, s_stride_g, op,
                                                   out_stride, n, k, group, scale_kind, scale_dtype);
+  else if (format == DQ_INT4X)
+    dequant_kernel<DQ_INT4X><<<grid, 256, 0, st>>>(wp, w_stride, scales, s_stride_n, s_stride_g, op,
+                                                   out_stride, n, k, group, scale_kind, scale_dtype);
   else
     dequant_kernel<DQ_E4M3><<<grid, 256, 0, st>>>(wp, w_stride, scales, s_stride_n, s_stride_g, op,
                                                   out_stride, n, k, group, scale_kind, scale_dtype);

@@ -35,7 +35,10 @@ constexpr int kThreads = kWarps * 32;
 constexpr int kStages = 4;
 constexpr int kKB = 128;  // K elements per pipeline step (= the scale block)
 
-enum WFmt { W_E4M3 = 0, W_INT8 = 1, W_BF16 = 2, W_MXFP4 = 3, W_INT4 = 4, W_U8B128 = 5 };
+// W_INT4X (host-side only) = W_INT4 whose 32-bit words hold their eight nibbles in
+// vLLM's ExLlama order (k = 0 2 4 6 1 3 5 7), the dense int4 layout of the reference
+// (csrc/gemm/w8a8_wmma_gemm.hip:128-132): same kernels, words unshuffled on load
+enum WFmt { W_E4M3 = 0, W_INT8 = 1, W_BF16 = 2, W_MXFP4 = 3, W_INT4 = 4, W_U8B128 = 5, W_INT4X = 6 };
 constexpr bool is_w4(int wf) { return wf == W_MXFP4 || wf == W_INT4; }
 enum AFmt { A_BF16 = 0, A_F16 = 1, A_E4M3 = 2, A_INT8 = 3 };
 constexpr bool is_a8(int af) { return af == A_E4M3 || af == A_INT8; }
@@ -62,7 +65,8 @@ struct MoeArgs {
   int scale_kind, scale_dtype;  // dtype: 0 fp32, 1 bf16, 2 fp16
   int c_f16;
   int tiles_per_cta;  // consecutive n-tiles one CTA streams
-  int group;          // K elements per weight scale (4-bit formats: 32, 64 or 128)
+  int group;          // K elements per weight scale (32, 64 or 128)
+  int w4_shuffled;    // int4 words in ExLlama nibble order
 };
 
 __device__ __forceinline__ float load_scale(const void* p, int64_t idx, int dtype) {
@@ -127,6 +131,15 @@ __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
   uint32_t r;
   asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
   return r;
+}
+
+// An int4 word whose nibbles 0..7 hold k = 0 2 4 6 1 3 5 7 -> nibble k holds k:
+// the low half carries the even elements, the high half the odd ones; interleave.
+__device__ __forceinline__ uint32_t unshuffle_int4(uint32_t w) {
+  uint32_t e = w & 0xffffu, o = w >> 16;
+  e = (e | (e << 8)) & 0x00ff00ffu, e = (e | (e << 4)) & 0x0f0f0f0fu;
+  o = (o | (o << 8)) & 0x00ff00ffu, o = (o | (o << 4)) & 0x0f0f0f0fu;
+  return e | (o << 4);
 }
 
 // MXFP4 by table: the low three bits of a nibble index an 8-entry table of bf16
@@ -423,8 +436,11 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs
 
       float sw0 = 1.f, sw1 = 1.f;
       if (p.scale_kind >= S_BLOCK) {
-        sw0 = load_scale(p.scales, sc0 + kb_now * p.s_sg, p.scale_dtype);
-        sw1 = load_scale(p.scales, sc1 + kb_now * p.s_sg, p.scale_dtype);
+        // this lane's 32 elements of the K block lie in one scale group; groups finer
+        // than the block (8-bit weights scaled before the MMA only) differ per lane
+        const int gi = p.scale_kind == S_GROUP && p.group < kKB ? (kb_now * kKB + 32 * c) / p.group : kb_now;
+        sw0 = load_scale(p.scales, sc0 + gi * p.s_sg, p.scale_dtype);
+        sw1 = load_scale(p.scales, sc1 + gi * p.s_sg, p.scale_dtype);
       }
 
       if constexpr (is_a8(AF)) {
@@ -436,7 +452,11 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs
           if constexpr (WF == W_INT4) {
             // 8 nibbles -> 8 signed bytes (nibble - 8), in element order
             const uint4 x = *reinterpret_cast<const uint4*>(st + w_off[r][0]);
-            const uint32_t ws[4] = {x.x, x.y, x.z, x.w};
+            uint32_t ws[4] = {x.x, x.y, x.z, x.w};
+            if (p.w4_shuffled) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) ws[i] = unshuffle_int4(ws[i]);
+            }
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               const uint32_t lo = ws[i] & 0x0F0F0F0Fu, hi = (ws[i] >> 4) & 0x0F0F0F0Fu;
@@ -500,7 +520,9 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_stream_kernel(const MoeArgs
               wf[r][4 * i] = x.x, wf[r][4 * i + 1] = x.y, wf[r][4 * i + 2] = x.z, wf[r][4 * i + 3] = x.w;
             }
           } else if constexpr (is_w4(WF)) {
-            const uint4 x = *reinterpret_cast<const uint4*>(st + w_off[r][0]);
+            uint4 x = *reinterpret_cast<const uint4*>(st + w_off[r][0]);
+            if (WF == W_INT4 && p.w4_shuffled)
+              x.x = unshuffle_int4(x.x), x.y = unshuffle_int4(x.y), x.z = unshuffle_int4(x.z), x.w = unshuffle_int4(x.w);
             // a scale that covers the whole K block goes onto the fp32 sums and the
             // weights stay exact (the reference's deferred-scale path and its oracle,
             // tests/test_moe_wna16.py:50-62); finer groups scale the weights
@@ -625,8 +647,15 @@ static int moe_gemm_impl(
     int64_t expert_len, int64_t top_k, int64_t block_m, int weight_format, int act_format,
     int scale_kind, int scale_dtype, int gate_act, int c_is_f16, strix_stream_t stream,
     const void* bias, int64_t bias_stride, int group, int64_t s_stride_g = 1) {
-  STRIX_CHECK(weight_format >= W_E4M3 && weight_format <= W_U8B128, "unknown weight format");
+  STRIX_CHECK(weight_format >= W_E4M3 && weight_format <= W_INT4X, "unknown weight format");
+  const int w4_shuffled = weight_format == W_INT4X;
+  if (w4_shuffled) weight_format = W_INT4;
   const bool w4 = is_w4(weight_format);
+  // scale groups finer than the 128-wide K block on 8-bit weights: only where the
+  // weights are scaled before the MMA (bf16 activations), each lane with its own scale
+  STRIX_CHECK(w4 || scale_kind != S_GROUP || group == 0 || group == 128 ||
+                  ((group == 32 || group == 64) && act_format == A_BF16),
+              "8-bit weights take scale groups of 128 (32 and 64 with bf16 activations)");
   STRIX_CHECK(act_format >= A_BF16 && act_format <= A_INT8, "unknown activation format");
   STRIX_CHECK(gate_act >= ACT_NONE && gate_act <= ACT_GELU_TANH,
               "activation must be silu or gelu_tanh");
@@ -679,6 +708,7 @@ static int moe_gemm_impl(
   p.s_sg = s_stride_g > 0 ? s_stride_g : 1;
   p.top_k = int(top_k), p.K = int(k), p.N = int(n), p.block_m = int(block_m);
   p.scale_kind = scale_kind, p.scale_dtype = scale_dtype, p.c_f16 = c_is_f16;
+  p.w4_shuffled = w4_shuffled;
 
   const int rows_per_cta = kWarps * (gate_act != ACT_NONE ? 8 : 16);
   const int64_t out_rows = gate_act != ACT_NONE ? n / 2 : n;
@@ -737,7 +767,8 @@ extern "C" int strix_gemm_w4a16(
     int64_t s_stride_e, int64_t s_stride_n, int64_t bias_stride, int64_t sorted_len,
     int64_t expert_len, int64_t top_k, int64_t block_m, int weight_format, int group,
     int scale_dtype, int gate_act, strix_stream_t stream) {
-  STRIX_CHECK(weight_format == W_MXFP4 || weight_format == W_INT4, "weight_format 3 (mxfp4) or 4 (int4)");
+  STRIX_CHECK(weight_format == W_MXFP4 || weight_format == W_INT4 || weight_format == W_INT4X,
+              "weight_format 3 (mxfp4), 4 (int4) or 6 (int4, ExLlama word order)");
   return moe_gemm_impl(c, a, w, scales, nullptr, sorted_ids, expert_ids, num_post_padded,
                        topk_weights, num_valid, a_rows, experts, n, k, a_stride, c_stride,
                        w_stride_e, w_stride_n, s_stride_e, s_stride_n, 0, sorted_len, expert_len,
@@ -750,7 +781,7 @@ extern "C" int strix_dense_gemm_w8a16(void* c, const void* x, const void* w, con
                                       int64_t x_stride, int64_t c_stride, int64_t w_stride,
                                       int64_t s_stride_n, int64_t bias_stride, int64_t block_m,
                                       int weight_format, int act_format, int scale_kind,
-                                      int scale_dtype, strix_stream_t stream) {
+                                      int scale_dtype, int group, strix_stream_t stream) {
   STRIX_CHECK(weight_format == W_E4M3 || weight_format == W_INT8 || weight_format == W_U8B128,
               "weight_format 0 (e4m3), 1 (int8) or 5 (excess-128 bytes)");
   STRIX_CHECK(m >= 0 && block_m >= 1, "bad M / block_m");
@@ -758,7 +789,7 @@ extern "C" int strix_dense_gemm_w8a16(void* c, const void* x, const void* w, con
   return moe_gemm_impl(c, x, w, scales, nullptr, nullptr, nullptr, nullptr, nullptr, m, m, 1, n, k,
                        x_stride, c_stride, 0, w_stride, 0, s_stride_n, 0, sorted_len, 0, 1, block_m,
                        weight_format, act_format, scale_kind, scale_dtype, ACT_NONE, 0, stream, bias,
-                       bias_stride, 0);
+                       bias_stride, group);
 }
 
 extern "C" int strix_gemm_w8a8_group(
@@ -769,8 +800,8 @@ extern "C" int strix_gemm_w8a8_group(
     int64_t s_stride_e, int64_t s_stride_n, int64_t s_stride_g, int64_t sa_stride,
     int64_t sorted_len, int64_t expert_len, int64_t top_k, int64_t block_m, int weight_format,
     int scale_kind, int scale_dtype, int gate_act, strix_stream_t stream) {
-  STRIX_CHECK(weight_format == W_INT4 || weight_format == W_U8B128,
-              "weight_format 4 (int4) or 5 (excess-128 bytes)");
+  STRIX_CHECK(weight_format == W_INT4 || weight_format == W_U8B128 || weight_format == W_INT4X,
+              "weight_format 4 (int4), 5 (excess-128 bytes) or 6 (int4, ExLlama word order)");
   return moe_gemm_impl(c, qa, w, scales, sa, sorted_ids, expert_ids, num_post_padded, topk_weights,
                        num_valid, a_rows, experts, n, k, a_stride, c_stride, w_stride_e, w_stride_n,
                        s_stride_e, s_stride_n, sa_stride, sorted_len, expert_len, top_k, block_m,

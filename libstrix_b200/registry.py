@@ -246,19 +246,27 @@ KERNELS: list[Kernel] = [
     Kernel("mxfp4_wmma_gemm", "mxfp4", "MXFP4 W4A16 dense GEMM, optional bias [N] or [M, N]",
            {"weight_bits": 4, "group_size": 32, "dtype": "bf16", "scale_dtype": "e8m0"},
            dict(_STREAM_SPEC)),
-    Kernel("w4a16_wmma_gemm", "w4a16", "int4 W4A16 dense GEMM, optional bias",
+    Kernel("w4a8_wmma_gemm", "w4a16",
+           "int4 weights (ExLlama word order) x activations quantised to int8 per (row, 128 "
+           "group) inside the op: s8 MMAs, int32-exact per group, fp32 fold; the dense twin of "
+           "moe_gemm_w4a8 on the weight-streaming kernel",
+           {"weight_bits": 4, "group_size": (0, 128), "dtype": "bf16", "rows": Range(hi=128),
+            "act_quant": "int8"}, dict(_STREAM_SPEC)),
+    Kernel("w4a16_wmma_gemm", "w4a16",
+           "int4 W4A16 dense GEMM (ExLlama word order), optional bias; the dense form of "
+           "moe_gemm_w4a16 on the weight-streaming kernel",
            {"weight_bits": 4, "group_size": (32, 64, 128), "dtype": "bf16",
             "scale_dtype": ("bf16", "fp16")}, dict(_STREAM_SPEC)),
     Kernel("mxfp4_dequant", "mxfp4_dequant", "MXFP4 -> bf16 [N, K], byte-exact",
            {"weight_bits": 4, "group_size": 32, "dtype": "bf16"}),
-    Kernel("w4a16_dequant", "w4a16_dequant", "int4 -> bf16 [N, K]",
+    Kernel("w4a16_dequant", "w4a16_dequant", "int4 (ExLlama word order) -> bf16 [N, K]",
            {"weight_bits": 4, "group_size": (32, 64, 128), "dtype": "bf16"}),
     Kernel("fp8_dequant", "fp8_dequant", "e4m3 x fp32 block or channel scales -> bf16 [N, K]",
            {"weight_bits": 8, "weight_dtype": "fp8_e4m3", "group_size": (0, 128), "dtype": "bf16"}),
     Kernel("w8a16_skinny_gemm", "w8a16",
            "excess-128 byte weights x bf16 activations at 1-8 rows, scales per channel or per "
-           "(row, 128 group)",
-           {"weight_bits": 8, "group_size": (0, 128), "rows": Range(hi=8), "dtype": "bf16"},
+           "(row, 32 / 64 / 128 group); the dense form of the grouped weight-streaming kernel",
+           {"weight_bits": 8, "group_size": (0, 32, 64, 128), "rows": Range(hi=8), "dtype": "bf16"},
            dict(_STREAM_SPEC)),
     Kernel("fp8_skinny_gemm", "fp8", "e4m3 weights x bf16 activations at 1-8 rows",
            {"weight_bits": 8, "weight_dtype": "fp8_e4m3", "group_size": (0, 128),

@@ -245,6 +245,7 @@ def attn_prefill_bf16(out, q, key_cache, value_cache, k_scale, v_scale, cu_seqle
 # ----------------------------------------------------------------------- MoE
 
 _W_E4M3, _W_INT8, _W_BF16 = 0, 1, 2
+_W_INT4X = 6       # int4, 32-bit words in ExLlama nibble order (the dense int4 ops)
 _A_BF16, _A_F16, _A_E4M3 = 0, 1, 2
 _S_NONE, _S_CHANNEL, _S_BLOCK = 0, 1, 2
 _SCALE_DTYPES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
@@ -720,12 +721,19 @@ def mxfp4_gemv(x, w, scales):
 @_define("w4a16_wmma_gemm(Tensor x, Tensor w, Tensor scales, Tensor? bias, int group_size) -> Tensor",
          fake=_dense_fake(0, 1))
 def w4a16_wmma_gemm(x, w, scales, bias, group_size):
+    """int4 weights in vLLM's ExLlama word order (each 32-bit word holds k = 0 2 4 6 1
+    3 5 7 in its nibbles; uint8 or int8 view [N, K / 2]), as the reference's dense op
+    (csrc/gemm/w8a8_wmma_gemm.hip:128-132); the MoE ops keep the sequential order."""
     _check(group_size in (32, 64, 128), "group_size must be 32, 64 or 128")
     out = torch.empty(x.size(0), w.size(0), dtype=torch.bfloat16, device=x.device)
     if x.size(0):
-        _gemm_w4(out, x, w, scales, bias, None, None, 1, _dense_block_m(x.size(0)), _W_INT4,
-                 group_size, 0)
+        _gemm_w4(out, x, _as_u8(w), scales, bias, None, None, 1, _dense_block_m(x.size(0)),
+                 _W_INT4X, group_size, 0)
     return out
+
+
+def _as_u8(w):
+    return w.view(torch.uint8) if w.dtype == torch.int8 else w
 
 
 def _dequant(w, scales, fmt, group, scale_kind, k):
@@ -756,12 +764,13 @@ def mxfp4_dequant(w, scales):
 
 @_define("w4a16_dequant(Tensor w, Tensor scales, int group_size) -> Tensor", fake=_dq_fake)
 def w4a16_dequant(w, scales, group_size):
+    w = _as_u8(w)
     k = w.size(1) * 2
     _check(w.dtype == torch.uint8 and scales.dtype in (torch.bfloat16, torch.float16),
            "w uint8, scales bf16 or fp16")
     _check(group_size in (32, 64, 128) and tuple(scales.shape) == (w.size(0), k // group_size),
            "scales must be [N, K / group_size]")
-    return _dequant(w, scales, 1, group_size, 0, k)
+    return _dequant(w, scales, 3, group_size, 0, k)     # 3: int4 in ExLlama word order
 
 
 @_define("fp8_dequant(Tensor w, Tensor scales) -> Tensor", fake=_dq_fake)
@@ -776,7 +785,7 @@ def fp8_dequant(w, scales):
     return _dequant(w, scales.reshape(n), 2, 128, 1, k)
 
 
-def _dense_w8(x, w, scales, bias, wfmt, afmt, scale_kind):
+def _dense_w8(x, w, scales, bias, wfmt, afmt, scale_kind, group=0):
     m, k = x.shape
     n = w.size(0)
     _check(w.dim() == 2 and w.size(1) == k and x.stride(1) == 1 and w.stride(1) == 1,
@@ -795,7 +804,7 @@ def _dense_w8(x, w, scales, bias, wfmt, afmt, scale_kind):
                       scales.data_ptr(), _ptr(bias), m, n, k, x.stride(0), out.stride(0), w.stride(0),
                       scales.stride(0) if scale_kind != _S_CHANNEL else 0, bias_stride,
                       _dense_block_m(m), wfmt, afmt, scale_kind, _SCALE_DTYPES[scales.dtype],
-                      _stream())
+                      group, _stream())
     return out
 
 
@@ -803,16 +812,16 @@ def _dense_w8(x, w, scales, bias, wfmt, afmt, scale_kind):
          "int group_size) -> Tensor", fake=_dense_fake(1, 0))
 def w8a16_skinny_gemm(in_a, in_b, in_scale, in_bias, CuCount, group_size):
     """in_a: excess-128 weights uint8 [N, K]; in_b: activations bf16 [M <= 8, K];
-    in_scale: 16-bit [N] (group_size 0) or [N, K / 128] (group_size 128)."""
+    in_scale: 16-bit [N] (group_size 0) or [N, K / group_size] (32, 64 or 128)."""
     _check(1 <= in_b.size(0) <= 8, "w8a16_skinny_gemm takes 1-8 rows")
     _check(in_a.dtype == torch.uint8 and in_b.dtype == torch.bfloat16
            and in_scale.dtype in _SCALE_DTYPES, "in_a uint8, in_b bf16")
-    _check(group_size in (0, 128), "group_size must be 0 or 128")
+    _check(group_size in (0, 32, 64, 128), "group_size must be 0, 32, 64 or 128")
     n, k = in_a.shape
     if group_size:
-        _check(tuple(in_scale.shape) == (n, k // 128) and in_scale.stride(1) == 1,
-               "scales must be [N, K / 128]")
-        return _dense_w8(in_b, in_a, in_scale, in_bias, _W_U8B128, _A_BF16, _S_GROUP)
+        _check(tuple(in_scale.shape) == (n, k // group_size) and in_scale.stride(1) == 1,
+               f"scales must be [N, K / {group_size}]")
+        return _dense_w8(in_b, in_a, in_scale, in_bias, _W_U8B128, _A_BF16, _S_GROUP, group_size)
     _check(in_scale.numel() == n, "scales must be [N]")
     return _dense_w8(in_b, in_a, in_scale.reshape(n), in_bias, _W_U8B128, _A_BF16, _S_CHANNEL)
 
@@ -925,6 +934,39 @@ def w8a8_wmma_gemm(in_w8, in_act, in_scale):
     sa = torch.empty(m, g, dtype=torch.float32, device=in_act.device)
     moe_act_quant_i8(in_act, qa, sa)
     _gemm_a8(out, qa, sa, in_w8, sc, None, None, 1, _dense_block_m(m), _W_U8B128, 0, s_sn, s_sg, kind)
+    return out
+
+
+@_define("w4a8_wmma_gemm(Tensor in_w4, Tensor in_act, Tensor in_scale) -> Tensor",
+         fake=_dense_fake(1, 0))
+def w4a8_wmma_gemm(in_w4, in_act, in_scale):
+    """int4 weights (nibble - 8, ExLlama word order, uint8 or int8 view [N, K / 2]) x
+    bf16 activations quantised to int8 per (row, 128 group) inside the op; int32-exact
+    sums per group, fp32 fold (csrc/torch_ops.cpp:283,
+    csrc/gemm/w8a8_wmma_gemm.hip:128-132,278-291 of the reference). in_scale fp32 [N]
+    or [K/128, N] (group-major); the reference's [K/32, N] form is not built."""
+    w = _as_u8(in_w4)
+    n, k = w.size(0), w.size(1) * 2
+    m = in_act.size(0)
+    _check(w.dtype == torch.uint8 and w.dim() == 2 and w.stride(1) == 1, "in_w4 must be 8-bit [N, K / 2]")
+    _check(in_act.dtype == torch.bfloat16 and in_act.dim() == 2 and in_act.size(1) == k,
+           "in_act must be bf16 [M, K]")
+    _check(k % 128 == 0, "K must be a multiple of 128")
+    _check(in_scale.dtype == torch.float32, "in_scale must be fp32")
+    g = k // 128
+    if in_scale.numel() == n:
+        kind, s_sn, s_sg, sc = _S_CHANNEL, 0, 1, in_scale.reshape(n)
+    else:
+        _check(tuple(in_scale.shape) == (g, n),
+               "in_scale must be [N] or [K/128, N] (scales per 32 elements are not built)")
+        kind, s_sn, s_sg, sc = _S_GROUP, in_scale.stride(1), in_scale.stride(0), in_scale
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=in_act.device)
+    if m == 0:
+        return out
+    qa = torch.empty(m, k, dtype=torch.int8, device=in_act.device)
+    sa = torch.empty(m, g, dtype=torch.float32, device=in_act.device)
+    moe_act_quant_i8(in_act, qa, sa)
+    _gemm_a8(out, qa, sa, w, sc, None, None, 1, _dense_block_m(m), _W_INT4X, 0, s_sn, s_sg, kind)
     return out
 
 

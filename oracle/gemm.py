@@ -113,6 +113,20 @@ def int4_pack(q: torch.Tensor) -> torch.Tensor:
     return (q[..., 0::2] | (q[..., 1::2] << 4)).contiguous()
 
 
+def int4_pack_exllama(q: torch.Tensor) -> torch.Tensor:
+    """[..., K] values 0..15 -> [..., K/2] bytes in vLLM's ExLlama word order: every
+    32-bit word holds eight consecutive elements, nibble i = element (0 2 4 6 1 3 5
+    7)[i] - the layout the reference's dense int4 ops decode
+    (csrc/gemm/w8a8_wmma_gemm.hip:128-132,278-291; its tests pack with vLLM's
+    pack_skinny_int4, tests/test_w8a16.py:74-98, which is not available here, so this
+    packer is pinned only by the format statement in the kernel source: parity
+    unpinned)."""
+    order = torch.tensor([0, 2, 4, 6, 1, 3, 5, 7])
+    k = q.size(-1)
+    words = q.reshape(*q.shape[:-1], k // 8, 8)[..., order].to(torch.uint8)     # nibble i of each word
+    return (words[..., 0::2] | (words[..., 1::2] << 4)).reshape(*q.shape[:-1], k // 2).contiguous()
+
+
 def int4_dequant(w_u8: torch.Tensor, scales: torch.Tensor, group: int, exact: bool = False):
     """(nibble - 8) * scale per group, rounded to bf16 unless `exact`
     (tests/test_moe_wna16.py:48-62)."""

@@ -179,23 +179,57 @@ def test_moe_gemm_mxfp4(tokens, block_m, gemm, activation):
     rms_check(c, ref, 2e-2)
 
 
-def test_w4a16_dense_and_dequant():
-    n, k, group = 512, 1024, 64
-    g = torch.Generator().manual_seed(0)
-    w_u8 = G.int4_pack(torch.randint(0, 16, (n, k), generator=g, dtype=torch.uint8))
+@pytest.mark.parametrize("group", [32, 64, 128])
+def test_w4a16_dense_and_dequant(group):
+    """The dense int4 ops read vLLM's ExLlama word order (tests/test_w8a16.py:100-135
+    of the reference): the decode is judged against the values before packing."""
+    n, k = 512, 1024
+    g = torch.Generator().manual_seed(group)
+    q4 = torch.randint(0, 16, (n, k), generator=g, dtype=torch.uint8)
+    w_x = G.int4_pack_exllama(q4)
+    seq = G.int4_pack(q4)                                   # the same values, sequential order
     scales = (torch.rand(n, k // group, generator=g) * 0.02 + 0.001).bfloat16()
     x = torch.randn(40, k, generator=g).bfloat16()
-    dq = ops.w4a16_dequant(w_u8.to(DEV), scales.to(DEV), group)
-    assert torch.equal(dq.cpu(), G.int4_dequant(w_u8, scales, group))
-    out = ops.w4a16_wmma_gemm(x.to(DEV), w_u8.to(DEV), scales.to(DEV), None, group)
-    close_to_peak(out, x.float() @ G.int4_dequant(w_u8, scales, group).float().t(), 1e-2)
+    dq = ops.w4a16_dequant(w_x.to(DEV), scales.to(DEV), group)
+    assert torch.equal(dq.cpu(), G.int4_dequant(seq, scales, group))
+    out = ops.w4a16_wmma_gemm(x.to(DEV), w_x.view(torch.int8).to(DEV), scales.to(DEV), None, group)
+    close_to_peak(out, x.float() @ G.int4_dequant(seq, scales, group, exact=True).t(), 1e-2)
+
+
+def test_exllama_packing_is_a_nibble_permutation():
+    q4 = torch.arange(16, dtype=torch.uint8).repeat(2).view(1, 32)
+    w = G.int4_pack_exllama(q4).view(-1)
+    word = int.from_bytes(bytes(w[:4].tolist()), "little")
+    assert [(word >> (4 * i)) & 15 for i in range(8)] == [0, 2, 4, 6, 1, 3, 5, 7]
+
+
+@pytest.mark.parametrize("n,k", [(16384, 5120), (256, 1024)])
+@pytest.mark.parametrize("m", [6, 64, 300])
+@pytest.mark.parametrize("group_size", [0, 128])
+def test_w4a8_wmma_gemm(n, k, m, group_size):
+    """tests/test_w8a16.py:74-98 of the reference: int4 (ExLlama order) x activations
+    quantised to int8 per 128 group inside the op."""
+    g = torch.Generator().manual_seed(m)
+    x = torch.randn(m, k, generator=g).bfloat16()
+    q4 = torch.randint(0, 16, (n, k), generator=g, dtype=torch.uint8)
+    s = (torch.rand(n, k // group_size if group_size else 1, generator=g) * 0.05 + 0.01).bfloat16()
+    full = s.float().repeat_interleave(group_size, 1) if group_size else s.float()
+    w = (q4.float() - 8.0) * full
+    sf = s.float().reshape(n) if group_size == 0 else s.float().t().contiguous()
+    out = ops.w4a8_wmma_gemm(G.int4_pack_exllama(q4).to(DEV), x.to(DEV), sf.to(DEV))
+    qa, sa = G.act_quant_group_i8(x)
+    close_to_peak(out, (qa.float() * sa.repeat_interleave(128, 1)) @ w.t(), 1e-2)
+    close_to_peak(out, x.float() @ w.t(), 6e-2)             # the reference's statement
+    with pytest.raises(RuntimeError, match="not built"):
+        ops.w4a8_wmma_gemm(G.int4_pack_exllama(q4).to(DEV), x.to(DEV),
+                           torch.ones(k // 32, n, device=DEV))
 
 
 # ------------------------------------------------------------------ dense 8-bit
 
 @pytest.mark.parametrize("n,k", [(16384, 5120), (5120, 17408), (256, 1024)])
 @pytest.mark.parametrize("m", [1, 3, 8])
-@pytest.mark.parametrize("group_size", [0, 128])
+@pytest.mark.parametrize("group_size", [0, 32, 64, 128])
 def test_w8a16_skinny(n, k, m, group_size):
     g = torch.Generator().manual_seed(0)
     x = torch.randn(m, k, generator=g).bfloat16()
