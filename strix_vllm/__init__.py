@@ -11,6 +11,7 @@ to CUDA compute capability 10.x and its hook points those of vLLM 0.22:
     moe     FP8 block-scaled experts                 -> fused_moe.oracle.fp8 selector
     attn    int8_per_token_head / bf16 paged attention, KV-cache write
                                                      -> a registered attention backend
+    dense_w8  int8 decode copies of bf16 linears (opt-in: STRIX_ENABLE=dense_w8)
 
 `register()` is the `vllm.general_plugins` entry point: it runs in every vLLM
 process, possibly more than once, and does nothing off a B200. STRIX_DISABLE=all
@@ -62,10 +63,11 @@ def register() -> None:
         return
     import libstrix_b200  # noqa: F401  (loads torch.ops.strix in this process)
 
-    from strix_vllm import attn, fp8, int8, moe
+    from strix_vllm import attn, dense_w8, fp8, int8, moe
 
     int8.register()
     fp8.register()
     moe.register()
     attn.register()
+    dense_w8.register()          # opt-in: STRIX_ENABLE=dense_w8
     logger.info("libstrix_b200: plugin registered")

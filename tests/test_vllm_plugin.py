@@ -136,7 +136,42 @@ def test_fp8_linear_gates():
     assert chan.__name__ == "StrixFp8ChannelMMKernel"
 
 
+def test_dense_w8_quantiser_and_switches(monkeypatch):
+    from strix_vllm import dense_w8
+
+    g = torch.Generator().manual_seed(0)
+    w = (torch.randn(64, 256, generator=g) * 0.05).bfloat16()
+    q, s, group = dense_w8.quantize(w)
+    assert q.dtype == torch.uint8 and q.shape == w.shape and group == 128 and s.shape == (64, 2)
+    deq = (q.float() - 128) * s.float().repeat_interleave(128, 1)
+    assert float((deq - w.float()).abs().max()) <= float(s.float().max()) * 0.51 + 1e-6
+    q2, s2, g2 = dense_w8.quantize(w[:, :200].contiguous())      # K % 128 != 0: per channel
+    assert g2 == 0 and s2.shape == (64,)
+    assert not dense_w8.enabled()
+    monkeypatch.setenv("STRIX_ENABLE", "dense_w8")
+    assert dense_w8.enabled()
+    monkeypatch.setenv("STRIX_DISABLE", "dense_w8")
+    assert not dense_w8.enabled()
+    x = torch.randn(3, 256).bfloat16()                            # no copy registered: plain bf16
+    torch.testing.assert_close(dense_w8.apply(x, w), torch.nn.functional.linear(x, w))
+
+
 # ------------------------------------------------------------------ on the GPU
+@pytest.mark.gpu
+def test_dense_w8_copy_serves_small_batches():
+    from strix_vllm import dense_w8
+
+    w = (torch.randn(512, 1024, generator=torch.Generator().manual_seed(1)) * 0.05).bfloat16().cuda()
+    assert dense_w8.add_copy(w) and dense_w8.lookup(w) is not None
+    bias = torch.randn(512, device="cuda").bfloat16()
+    for m in (1, 8, 9):
+        x = torch.randn(2, m, 1024, device="cuda").bfloat16()[0]
+        out = dense_w8.apply(x, w, bias).float()
+        ref = torch.nn.functional.linear(x, w, bias).float()
+        torch.testing.assert_close(out / ref.abs().amax(), ref / ref.abs().amax(), rtol=0, atol=3e-2)
+        assert m > 8 or not torch.equal(out, ref)                # the int8 copy really ran
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("m", [6, 64, 300])
 def test_int8_kernel_matches_the_oracle(m):
