@@ -36,9 +36,10 @@ def quantize(w: torch.Tensor):
     group = _GROUP if k % _GROUP == 0 else 0
     wf = w.float()
     g = wf.view(n, k // group, group) if group else wf.view(n, 1, k)
-    s = (g.abs().amax(-1) / 127.0).clamp_min(1e-12)
-    q = torch.round(g / s[..., None]).clamp(-127, 127).view(n, k) + 128
-    s = s.to(w.dtype).contiguous()
+    # the scale is rounded to the 16-bit type it is stored in BEFORE the weights are
+    # divided by it, so that the kernel multiplies by exactly the divisor used here
+    s = (g.abs().amax(-1) / 127.0).clamp_min(1e-12).to(w.dtype).contiguous()
+    q = torch.round(g / s.float()[..., None]).clamp(-127, 127).view(n, k) + 128
     return q.to(torch.uint8).contiguous(), (s if group else s.reshape(n)), group
 
 
