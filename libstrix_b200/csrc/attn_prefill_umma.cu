@@ -45,7 +45,7 @@ namespace {
 using namespace umma;
 
 constexpr int kPuQ = 128, kPuKeys = 128;           // Q tile rows, key tile
-constexpr int kPuThreads = 12 * 32;                // producer, issuer, 2 idle, 2 x 4 softmax warps
+constexpr int kPuThreads = 10 * 32;                // producer, issuer, 2 x 4 softmax warps
 constexpr int kPuStages = 2;
 constexpr float kPuRescale = 8.f;                  // log2 of the growth of the maximum that forces a rescale
 
@@ -331,9 +331,9 @@ __global__ void __launch_bounds__(kPuThreads, 1) attn_prefill_umma_kernel(
       if (!dead) mma_commit(&o_full);
       if (dead) atomicExch(p.status, 1), s_abort = 1;
     }
-  } else if (warp >= 4) {
+  } else if (warp >= 2) {
     // -------------------------------------------------------------- softmax
-    const int q = (warp - 4) >> 2;
+    const int q = (warp - 2) >> 2;
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
     const uint32_t t_s = tmem + lane_base + L::kTmemS + q * kPuKeys;
@@ -346,7 +346,7 @@ __global__ void __launch_bounds__(kPuThreads, 1) attn_prefill_umma_kernel(
       if (__any_sync(0xffffffffu, !ok)) dead = true;
       if (!dead) {
         uint4* qv = reinterpret_cast<uint4*>(smem);
-        for (int i = tid - 128; i < 2 * L::kQTile / 16; i += 256) {
+        for (int i = tid - 64; i < 2 * L::kQTile / 16; i += 256) {
           uint4 x = qv[i];
           x.x = pack_f16x2(bf16_lo(x.x), bf16_hi(x.x)), x.y = pack_f16x2(bf16_lo(x.y), bf16_hi(x.y));
           x.z = pack_f16x2(bf16_lo(x.z), bf16_hi(x.z)), x.w = pack_f16x2(bf16_lo(x.w), bf16_hi(x.w));
@@ -378,58 +378,75 @@ __global__ void __launch_bounds__(kPuThreads, 1) attn_prefill_umma_kernel(
         const bool vis = key < k_end && key <= qpos && (p.window_left < 0 || qpos - key <= p.window_left);
         return vis ? v : -INFINITY;
       };
-      // ---- pass 1: the row maximum of the raw scores
-      float mx = -INFINITY;
+      // One pass over the scores in the common case: P = 2^(s - m_ref) against the
+      // maximum carried over from the earlier tiles, the tile's own maximum taken on
+      // the way. Only if that maximum exceeds m_ref by more than 2^kPuRescale (or no
+      // key was seen yet) the accumulator is rescaled and the pass repeated - S is
+      // still intact, because P (which overwrites its first 64 columns) is held in
+      // registers until the decision. The TMEM load of the next 16 columns is in
+      // flight while the current ones are processed; maxima and sums run in four
+      // independent chains each (two warps per scheduler cannot hide a serial one).
+      uint32_t pk[kPuKeys / 2];
+      float lt = 0.f;
+      const bool seen = __all_sync(0xffffffffu, m_ref != -INFINITY);
 #pragma unroll 1
-      for (int c = 0; c < kPuKeys / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_s + c * 32, r);
-        tmem_ld_wait();
-        if (interior) {
+      for (int attempt = 0; attempt < 2; ++attempt) {
+        const bool want_p = attempt == 1 || seen;   // rows without a key yet only take the maximum first
+        const float base = m_ref == -INFINITY ? 0.f : m_ref;
+        float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY}, lta[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t r[2][16];
+        tmem_ld_32x16(t_s, r[0]);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-        } else {
+        for (int c = 0; c < kPuKeys / 16; ++c) {
+          tmem_ld_wait();
+          if (c + 1 < kPuKeys / 16) tmem_ld_32x16(t_s + (c + 1) * 16, r[(c + 1) & 1]);
+          float v[16];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, masked(__uint_as_float(r[i]), k0 + c * 32 + i));
-        }
-      }
-      const float m_new = fmaxf(m_ref, mx * sl2);
-      // lazy rescale: only when the maximum grew by more than 2^kPuRescale (or is the first)
-      const bool need = m_new > m_ref + kPuRescale || (m_ref == -INFINITY && m_new > -INFINITY);
-      if (__any_sync(0xffffffffu, need)) {
-        const float f = need ? (m_ref == -INFINITY ? 0.f : fast_exp2(m_ref - m_new)) : 1.f;
-        if (j > 0) {
-#pragma unroll 1
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32(t_o + c * 32, r);
-            tmem_ld_wait();
+          for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[c & 1][i]);
+          if (!interior) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * f);
-            tmem_st_32x32(t_o + c * 32, r);
+            for (int i = 0; i < 16; ++i) v[i] = masked(v[i], k0 + c * 16 + i);
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) mxa[i & 3] = fmaxf(mxa[i & 3], v[i]);
+          if (want_p) {
+#pragma unroll
+            for (int i = 0; i < 16; i += 2) {
+              const float p0 = fast_exp2(fmaf(v[i], sl2, -base)), p1 = fast_exp2(fmaf(v[i + 1], sl2, -base));
+              lta[(i >> 1) & 3] += p0 + p1;
+              pk[c * 8 + (i >> 1)] = Q8 ? pack_f16x2(p0, p1) : pack_bf16x2(p0, p1);
+            }
           }
         }
-        l *= f;
-        if (need) m_ref = m_new;
-      }
-      const float base = m_ref == -INFINITY ? 0.f : m_ref;
-      // ---- pass 2: P = 2^(s - m), 16-bit, over the first 64 columns of S
+        lt = (lta[0] + lta[1]) + (lta[2] + lta[3]);
+        const float mx = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3]));
+        if (attempt == 1) break;
+        const float m_new = fmaxf(m_ref, mx * sl2);
+        // lazy rescale: only when the maximum grew by more than 2^kPuRescale (or is the first)
+        const bool need = m_new > m_ref + kPuRescale || (m_ref == -INFINITY && m_new > -INFINITY);
+        const bool any_need = __any_sync(0xffffffffu, need);
+        if (!any_need && seen) break;
+        if (any_need) {
+          const float f = need ? (m_ref == -INFINITY ? 0.f : fast_exp2(m_ref - m_new)) : 1.f;
+          if (j > 0) {
 #pragma unroll 1
-      for (int c = 0; c < kPuKeys / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_s + c * 32, r);
-        tmem_ld_wait();
-        uint32_t pk[16];
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t ro[32];
+              tmem_ld_32x32(t_o + c * 32, ro);
+              tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float v0 = __uint_as_float(r[i]), v1 = __uint_as_float(r[i + 1]);
-          if (!interior) v0 = masked(v0, k0 + c * 32 + i), v1 = masked(v1, k0 + c * 32 + i + 1);
-          const float p0 = fast_exp2(fmaf(v0, sl2, -base)), p1 = fast_exp2(fmaf(v1, sl2, -base));
-          l += p0 + p1;
-          pk[i >> 1] = Q8 ? pack_f16x2(p0, p1) : pack_bf16x2(p0, p1);
+              for (int i = 0; i < 32; ++i) ro[i] = __float_as_uint(__uint_as_float(ro[i]) * f);
+              tmem_st_32x32(t_o + c * 32, ro);
+            }
+          }
+          l *= f;
+          if (need) m_ref = m_new;
         }
-        tmem_st_32x16(t_s + c * 16, pk);
       }
+      l += lt;
+#pragma unroll
+      for (int c = 0; c < kPuKeys / 32; ++c)
+        tmem_st_32x16(t_s + c * 16, *reinterpret_cast<uint32_t(*)[16]>(&pk[c * 16]));
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
