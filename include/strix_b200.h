@@ -331,8 +331,12 @@ int strix_act_quant_token_i8(const void* x, void* q, float* scales, int64_t rows
                              strix_stream_t stream);
 
 /* Health of the tcgen05 kernels: *host_out = 0 while every launch so far met its
- * bounded waits, 1 after one of them gave up (its output is then incomplete).
- * Synchronises the device; for tests and debugging. No reference counterpart. */
+ * bounded waits, 1 after one of them gave up (its output is then incomplete: the
+ * CTA stopped, waited for its own copies and MMAs in flight, freed tensor memory
+ * and returned). Synchronises the device. The launches themselves never report
+ * it - a caller polls this word at a point where it synchronises anyway (the
+ * Python ops do so after every call when STRIX_CHECK_STATUS=1). No reference
+ * counterpart. */
 int strix_umma_status(int32_t* host_out);
 
 /* The FP8 activation quantiser writing the SORTED layout the tcgen05 grouped

@@ -8,6 +8,7 @@ missing or lacks a declared symbol, importing fails with the build command.
 from __future__ import annotations
 
 import ctypes
+import os
 import re
 from pathlib import Path
 
@@ -105,3 +106,23 @@ def call(name: str, *args) -> None:
     if rc != STRIX_OK:
         msg = lib.strix_last_error().decode("utf-8", "replace")
         raise StrixError(msg or f"{name} failed with status {rc}")
+
+
+def umma_status() -> int:
+    """The health word of the tcgen05 kernels on the current device (synchronises it):
+    0 while every launch met its bounded waits, 1 after one gave up."""
+    flag = ctypes.c_int32(-1)
+    call("strix_umma_status", ctypes.byref(flag))
+    return flag.value
+
+
+# STRIX_CHECK_STATUS=1: every op that runs a tcgen05 kernel synchronises afterwards
+# and raises if a bounded wait gave up (its output is then incomplete). Off by
+# default - the check costs a device synchronisation per call; a serving loop polls
+# umma_status() at a point where it synchronises anyway.
+CHECK_STATUS = os.environ.get("STRIX_CHECK_STATUS", "") not in ("", "0")
+
+
+def after_tcgen05(op: str) -> None:
+    if CHECK_STATUS and umma_status() != 0:
+        raise StrixError(f"{op}: a bounded wait of a tcgen05 kernel gave up; the output is incomplete")

@@ -227,6 +227,7 @@ def attn_prefill_bf16(out, q, key_cache, value_cache, k_scale, v_scale, cu_seqle
                 *(ks.stride() if q8 else (0, 0, 0)), *(vs.stride() if q8 else (0, 0, 0)),
                 float(scale), window_left, int(q8), _stream(),
             )
+            _lib.after_tcgen05("attn_prefill_bf16")
         return
     with torch.cuda.device(q.device):
         _lib.call(
@@ -503,6 +504,7 @@ def moe_gemm_fp8_sorted(c, qa, sa, b, scales, sorted_ids, expert_ids, num_post_p
                   c.stride(0), b.stride(0), b.stride(1), scales.stride(0), s_sn, sa.stride(0),
                   sorted_len, block_m, scale_kind, _ACTS[activation] if silu_mul else 0,
                   int(c_sorted), _stream())
+        _lib.after_tcgen05("moe_gemm_fp8_sorted")
 
 
 @_define("moe_topk_softmax(Tensor(a!) topk_weights, Tensor(b!) topk_ids, Tensor gating_output, "
@@ -692,6 +694,7 @@ def moe_gemm_mxfp4_sorted(c, a, b, scales, sorted_ids, expert_ids, num_post_padd
                   num_post_padded.data_ptr(), _ptr(topk_weights), num_valid, e, n, k, a.stride(0),
                   c.stride(0), b.stride(0), b.stride(1), scales.stride(0), scales.stride(1),
                   sorted_len, block_m, _ACTS[activation] if silu_mul else 0, int(c_sorted), _stream())
+        _lib.after_tcgen05("moe_gemm_mxfp4_sorted")
 
 
 def _dense_fake(rows_from, w_from):
@@ -999,6 +1002,7 @@ def w8a8_int8_gemm(a_q, a_scale, w, w_scale, acc_out=None):
         _lib.call("strix_w8a8_int8_gemm", out.data_ptr(), _ptr(acc_out), a_q.data_ptr(),
                   a_scale.data_ptr(), w.data_ptr(), w_scale.data_ptr(), m, n, k, a_q.stride(0),
                   w.stride(0), out.stride(0), _stream())
+        _lib.after_tcgen05("w8a8_int8_gemm")
     return out
 
 

@@ -12,10 +12,22 @@ well as after the other tests.
 import pytest
 import torch
 
-from libstrix_b200 import _lib
-from libstrix_b200.workloads import decode_batch
+pytest.importorskip("libstrix_b200", reason="libstrix_b200.so is not built")   # noqa: E402
+from libstrix_b200 import _lib  # noqa: E402
+from libstrix_b200.workloads import decode_batch  # noqa: E402
+from oracle import attention as A  # noqa: E402
 
 DEV = "cuda"
+
+
+def oracle_ok(out, b):
+    """The output against the CPU oracle, at the bound the decode tests use."""
+    c = b.to("cpu")
+    ref = A.decode_reference(c.q, c.key_cache, c.value_cache, c.k_scale, c.v_scale, c.seq_lens,
+                             c.block_table, c.scale)
+    err = (out.float().cpu() - ref).abs()
+    rms = ref.pow(2).mean().sqrt().item()
+    return bool((err <= 2e-2 * rms + ref.abs() * 2.0 ** -8).all())
 
 
 def _args(b, out, workspace, num_splits):
@@ -50,6 +62,7 @@ def test_static_scratch_matches_the_workspace_entry_point_twice_in_a_row():
         # same kernels, same partition: the tests' tolerance (2e-2) is far from tight here
         torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
         assert torch.equal(got, want), f"call {call}"
+        assert oracle_ok(got, b), f"call {call}: the static entry point against the oracle"
     # a shorter batch afterwards sees the previous call's leftovers in the array
     b2 = decode_batch(ctx_lens=[40, 700], seed=12).to(DEV)
     ws = torch.empty(lib.strix_attn_decode_workspace(2, 32, 128, 4, b2.block_table.size(1), 16) // 4,
@@ -59,6 +72,30 @@ def test_static_scratch_matches_the_workspace_entry_point_twice_in_a_row():
     _lib.call("strix_attn_decode_bf16_static", *_args(b2, got, False, 4))
     torch.cuda.synchronize()
     torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
+    assert oracle_ok(got, b2)
+
+
+@pytest.mark.gpu
+def test_static_scratch_single_segment_and_exact_capacity():
+    """num_splits = 1 needs no scratch at all (no partials, no array lookup); a launch
+    whose partials fill the 16 MiB array exactly is still accepted."""
+    lib = _lib.load()
+    b = decode_batch(ctx_lens=[500, 31], seed=13).to(DEV)
+    assert lib.strix_attn_decode_workspace(2, 32, 128, 1, b.block_table.size(1), 16) == 0
+    got = torch.full_like(b.q, float("nan"))
+    _lib.call("strix_attn_decode_bf16_static", *_args(b, got, False, 1))
+    torch.cuda.synchronize()
+    assert oracle_ok(got, b)
+    # 16 sequences x 32 heads x 63 segments x 130 floats x 4 bytes = 16,773,120 <= 16 MiB;
+    # one more segment would not fit
+    big = decode_batch(ctx_lens=[300 + 64 * i for i in range(16)], seed=14).to(DEV)
+    need = lib.strix_attn_decode_workspace(16, 32, 128, 63, big.block_table.size(1), 16)
+    assert need == 16 * 32 * 63 * 130 * 4 <= 16 * 1024 * 1024
+    assert lib.strix_attn_decode_workspace(16, 32, 128, 64, big.block_table.size(1), 16) > 16 * 1024 * 1024
+    got = torch.full_like(big.q, float("nan"))
+    _lib.call("strix_attn_decode_bf16_static", *_args(big, got, False, 63))
+    torch.cuda.synchronize()
+    assert oracle_ok(got, big)
 
 
 def test_static_scratch_rejects_oversized_launches():
