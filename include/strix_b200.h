@@ -421,6 +421,30 @@ int strix_moe_gemm_fp8_sorted(void* c, const void* a, const float* act_scales, c
 int strix_moe_gemm_fp8_sorted_covers(int64_t n, int64_t k, int64_t block_m, int gate_act,
                                      int scale_kind);
 
+/* One call for a whole FP8 W8A8 MoE layer over the sorted-layout tcgen05 kernels:
+ * [router ->] permute + quantise -> gate-up GEMM with the fused gate -> quantise ->
+ * down GEMM x routing weight -> sum over top-k, the sequence of the reference's
+ * StrixFp8Experts.apply (python/strix_vllm/moe.py:905-1014), enqueued on `stream`
+ * without allocation or synchronisation. Pass either `logits` (fp32 [tokens,
+ * experts], row stride logits_stride: softmax -> top-k -> renormalise runs first)
+ * or the routing itself (topk_weights fp32 / topk_ids int32, contiguous [tokens,
+ * top_k]). x bf16 [tokens, hidden]; w13 e4m3 [experts, 2 inter, hidden], w2 e4m3
+ * [experts, hidden, inter] with fp32 scales (scale_kind 1 channel [E, N], 2 block
+ * [E, N/128, K/128]; strides in elements); out bf16 [tokens, hidden]. gate_act 1
+ * silu, 2 gelu_tanh. workspace: 256-byte aligned, at least
+ * strix_moe_fp8_layer_workspace(...) bytes. */
+int64_t strix_moe_fp8_layer_workspace(int64_t tokens, int64_t top_k, int64_t hidden,
+                                      int64_t inter, int64_t experts, int64_t block_m);
+int strix_moe_fp8_layer(void* out, const void* x, const float* logits, const float* topk_weights,
+                        const int32_t* topk_ids, const void* w13, const float* w13_scale,
+                        const void* w2, const float* w2_scale, void* workspace,
+                        int64_t workspace_bytes, int64_t tokens, int64_t hidden, int64_t inter,
+                        int64_t experts, int64_t top_k, int64_t block_m, int64_t x_stride,
+                        int64_t logits_stride, int64_t out_stride, int64_t w13_stride_e,
+                        int64_t w13_stride_n, int64_t s13_stride_e, int64_t s13_stride_n,
+                        int64_t w2_stride_e, int64_t w2_stride_n, int64_t s2_stride_e,
+                        int64_t s2_stride_n, int scale_kind, int gate_act, strix_stream_t stream);
+
 /* ---- Expert-parallel exchange over peer memory (no counterpart in the
  * reference, whose experts refuse an expert_map: python/strix_vllm/moe.py:193-210).
  * Buffers are plain device allocations that peers map through CUDA IPC:

@@ -117,6 +117,7 @@ template <int D>
 struct WarpState {
   float m[2], l[2];
   float acc[D / 16][4];
+  float wsum[4];   // sum of the fp16 weights per head (computed by the MMA): see compute_tile
 };
 
 // Query fragments for the score MMAs. The bf16 query of a head is turned into
@@ -190,18 +191,33 @@ __device__ __forceinline__ void compute_tile(const TileQ8<D>& t, WarpState<D>& s
       st.acc[i][2] *= al0;
       st.acc[i][3] *= al1;
     }
+    st.wsum[0] *= al0, st.wsum[1] *= al1, st.wsum[2] *= al0, st.wsum[3] *= al1;
+  }
+  // The V bytes enter the MMA as fp16 1024 + (b + 128) - one byte permute per
+  // register, no subtraction: V^T P^T then carries the offset 1152 x (sum of the
+  // weights), and that sum comes out of one more MMA with an all-ones A operand
+  // (exactly the fp16-rounded weights the other MMAs see), so the offset is
+  // removed once per launch, in fp32, when the accumulators are merged.
+  uint32_t vx[4][D / 32];
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int w = 0; w < D / 32; ++w) vx[r][w] = t.v[r][w] ^ 0x80808080u;
+  {
+    const uint32_t ones[4] = {0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u};
+    mma_f16_16816(st.wsum, ones, b0, b1);
   }
 #pragma unroll
   for (int i = 0; i < D / 16; ++i) {
     const int w = i / 2;
     const uint32_t sel = (i & 1) ? 0x7362u : 0x5140u;
-    const uint32_t x01 = prmt(t.v[0][w] ^ 0x80808080u, t.v[1][w] ^ 0x80808080u, sel);
-    const uint32_t x23 = prmt(t.v[2][w] ^ 0x80808080u, t.v[3][w] ^ 0x80808080u, sel);
+    const uint32_t x01 = prmt(vx[0][w], vx[1][w], sel);
+    const uint32_t x23 = prmt(vx[2][w], vx[3][w], sel);
     uint32_t a[4];
-    a[0] = sub_f16x2(prmt(x01, kMagic, 0x4140), kBias);
-    a[1] = sub_f16x2(prmt(x01, kMagic, 0x4342), kBias);
-    a[2] = sub_f16x2(prmt(x23, kMagic, 0x4140), kBias);
-    a[3] = sub_f16x2(prmt(x23, kMagic, 0x4342), kBias);
+    a[0] = prmt(x01, kMagic, 0x4140);
+    a[1] = prmt(x01, kMagic, 0x4342);
+    a[2] = prmt(x23, kMagic, 0x4140);
+    a[3] = prmt(x23, kMagic, 0x4342);
     mma_f16_16816(st.acc[i], a, b0, b1);
   }
 }
@@ -303,6 +319,7 @@ attn_decode_q8_kernel(const DecodeArgs a) {
   WarpState<D> st;
   st.m[0] = st.m[1] = -INFINITY;
   st.l[0] = st.l[1] = 0.f;
+  st.wsum[0] = st.wsum[1] = st.wsum[2] = st.wsum[3] = 0.f;
 #pragma unroll
   for (int i = 0; i < D / 16; ++i)
     st.acc[i][0] = st.acc[i][1] = st.acc[i][2] = st.acc[i][3] = 0.f;
@@ -452,12 +469,14 @@ attn_decode_q8_kernel(const DecodeArgs a) {
   {
     const float f0 = st.m[0] == -INFINITY ? 0.f : fast_exp2(st.m[0] - M[0]) * kPScaleInv;
     const float f1 = st.m[1] == -INFINITY ? 0.f : fast_exp2(st.m[1] - M[1]) * kPScaleInv;
+    // the offset the unsubtracted V operand left behind: 1152 x the weights' sum
+    const float off0 = 1152.f * st.wsum[0], off1 = 1152.f * st.wsum[1];
 #pragma unroll
     for (int i = 0; i < D / 16; ++i) {
-      st.acc[i][0] *= f0;
-      st.acc[i][1] *= f1;
-      st.acc[i][2] *= f0;
-      st.acc[i][3] *= f1;
+      st.acc[i][0] = (st.acc[i][0] - off0) * f0;
+      st.acc[i][1] = (st.acc[i][1] - off1) * f1;
+      st.acc[i][2] = (st.acc[i][2] - off0) * f0;
+      st.acc[i][3] = (st.acc[i][3] - off1) * f1;
     }
   }
   // s_o[slot][head][d]: lane owns dims g * D/8 + 2i, + 2i + 1 of heads 2c, 2c + 1.

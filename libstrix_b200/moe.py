@@ -95,13 +95,24 @@ class Fp8MoeWorkspace:
         self.out = torch.empty(tokens, hidden, dtype=bf16, device=device)
 
 
+class Fp8LayerWorkspace:
+    """Scratch of the one-call layer launcher (strix_moe_fp8_layer) for one shape,
+    plus the output rows."""
+
+    def __init__(self, tokens, top_k, hidden, inter, experts, block_m, device):
+        self.key = (tokens, top_k, hidden, inter, experts, block_m)
+        self.nbytes = _lib.load().strix_moe_fp8_layer_workspace(*self.key)
+        self.buf = torch.empty(self.nbytes + 256, dtype=torch.uint8, device=device)
+        self.ptr = (self.buf.data_ptr() + 255) // 256 * 256
+        self.out = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=device)
+
+
 def workspace_for(tokens, top_k, hidden, inter, experts, block_m, device, layout="sorted"):
     """The workspace fused_moe_fp8_w8a8 wants for this shape, so that a caller
     can allocate it once."""
     if layout != "sorted":
         return Fp8MoeWorkspace(tokens, top_k, hidden, inter, device)
-    cap = _lib.load().strix_moe_align_capacity(tokens * top_k, experts, block_m)
-    return Fp8MoeWorkspace(tokens, top_k, hidden, inter, device, sorted_rows=cap)
+    return Fp8LayerWorkspace(tokens, top_k, hidden, inter, experts, block_m, device)
 
 
 def sorted_path_covers(w13, w13_scale, w2, w2_scale, block_m: int) -> bool:
@@ -122,10 +133,59 @@ def fused_moe_fp8_w8a8(x, logits, w13, w13_scale, w2, w2_scale, top_k, block_m=N
     """One MoE layer, FP8 W8A8 block-scaled. x bf16 [T, H]; logits fp32 [T, E];
     w13 e4m3 [E, 2I, H] + fp32 scales [E, 2I/128, H/128]; w2 e4m3 [E, H, I] +
     scales [E, H/128, I/128]. Returns bf16 [T, H]. Seven kernel launches, no
-    host synchronisation: the router, then experts_fp8_w8a8."""
+    host synchronisation. Where the sorted-layout tcgen05 kernels cover the shape the
+    whole layer is ONE call into the library (strix_moe_fp8_layer); otherwise the
+    router op, then experts_fp8_w8a8."""
+    out = _layer_call(x, logits, None, None, w13, w13_scale, w2, w2_scale, top_k, block_m, ws, layout,
+                      None, "silu")
+    if out is not None:
+        return out
     weights, ids = route(logits, top_k)
     return experts_fp8_w8a8(x, weights, ids, w13, w13_scale, w2, w2_scale, block_m=block_m, ws=ws,
-                            layout=layout)
+                            layout="gather" if layout == "auto" else layout)
+
+
+def _layer_call(x, logits, topk_weights, topk_ids, w13, w13_scale, w2, w2_scale, top_k, block_m, ws,
+                layout, out, activation):
+    """The layer through strix_moe_fp8_layer, or None where it does not apply."""
+    t, h = x.shape
+    e, n13, _ = w13.shape
+    inter = n13 // 2
+    bm = block_m or pick_block_m(t, top_k, e)
+    lib = _lib.load()
+    if layout not in ("auto", "sorted") or x.dtype != torch.bfloat16 or x.stride(1) != 1 or t == 0:
+        return None
+    f8 = torch.float8_e4m3fn
+    if w13.dtype != f8 or w2.dtype != f8 or w13_scale.dtype != torch.float32 \
+            or w2_scale.dtype != torch.float32 or w13.stride(2) != 1 or w2.stride(2) != 1 \
+            or w13_scale.stride(-1) != 1 or w2_scale.stride(-1) != 1 \
+            or (logits is not None and (logits.dtype != torch.float32 or logits.stride(1) != 1)):
+        return None
+    if not sorted_path_covers(w13, w13_scale, w2, w2_scale, bm) \
+            or lib.strix_moe_align_capacity(t * top_k, e, bm) // bm > MAX_SORTED_M_BLOCKS:
+        if layout == "sorted":
+            raise RuntimeError("fused_moe_fp8_w8a8: geometry not covered by the sorted-layout kernels")
+        return None
+    if not isinstance(ws, Fp8LayerWorkspace) or ws.key != (t, top_k, h, inter, e, bm):
+        ws = Fp8LayerWorkspace(t, top_k, h, inter, e, bm, x.device)
+    out = ws.out if out is None else out
+    block = w13_scale.dim() == 3 and w13_scale.size(1) != n13
+    if topk_ids is not None:
+        topk_ids = topk_ids.to(torch.int32).contiguous()
+        topk_weights = topk_weights.to(torch.float32).contiguous()
+    with torch.cuda.device(x.device):
+        _lib.call("strix_moe_fp8_layer", out.data_ptr(), x.data_ptr(),
+                  None if logits is None else logits.data_ptr(),
+                  None if topk_weights is None else topk_weights.data_ptr(),
+                  None if topk_ids is None else topk_ids.data_ptr(),
+                  w13.data_ptr(), w13_scale.data_ptr(), w2.data_ptr(), w2_scale.data_ptr(), ws.ptr,
+                  ws.nbytes, t, h, inter, e, top_k, bm, x.stride(0),
+                  0 if logits is None else logits.stride(0), out.stride(0), w13.stride(0), w13.stride(1),
+                  w13_scale.stride(0), w13_scale.stride(1) if block else 0, w2.stride(0), w2.stride(1),
+                  w2_scale.stride(0), w2_scale.stride(1) if block else 0, 2 if block else 1,
+                  2 if activation == "gelu_tanh" else 1, torch.cuda.current_stream().cuda_stream)
+        _lib.after_tcgen05("fused_moe_fp8_w8a8")
+    return out
 
 
 def experts_fp8_w8a8(x, topk_weights, topk_ids, w13, w13_scale, w2, w2_scale, out=None,
@@ -146,6 +206,11 @@ def experts_fp8_w8a8(x, topk_weights, topk_ids, w13, w13_scale, w2, w2_scale, ou
     e, n13, _ = w13.shape
     top_k = topk_ids.size(1)
     inter = n13 // 2
+    if layout in ("auto", "sorted") and not isinstance(ws, Fp8MoeWorkspace):
+        done = _layer_call(x, None, topk_weights, topk_ids, w13, w13_scale, w2, w2_scale, top_k,
+                           block_m, ws, layout, out, activation)
+        if done is not None:
+            return done
     bm = block_m or pick_block_m(t, top_k, e)
     lib = _lib.load()
     if layout == "auto":
