@@ -445,6 +445,25 @@ int strix_moe_fp8_layer(void* out, const void* x, const float* logits, const flo
                         int64_t w2_stride_e, int64_t w2_stride_n, int64_t s2_stride_e,
                         int64_t s2_stride_n, int scale_kind, int gate_act, strix_stream_t stream);
 
+/* The experts of that layer over rows that ARRIVE quantised, with slots that may be
+ * masked (expert id < 0 or >= experts): the receiving side of the expert-parallel
+ * exchange below, in one call (align -> permute payload rows -> gate-up GEMM ->
+ * quantise -> down GEMM x routing weight). rows_payload [rows, row_stride_bytes]:
+ * hidden e4m3 bytes, then hidden / 128 fp32 scales, rows padded to 16 bytes;
+ * topk_ids / topk_weights contiguous [rows, top_k]; y bf16 [rows * top_k, hidden]
+ * receives the weighted rows in slot order (rows of masked slots are not written).
+ * Same workspace as strix_moe_fp8_layer for tokens = rows. */
+int strix_moe_fp8_experts_on_rows(void* y, const void* rows_payload, const float* topk_weights,
+                                  const int32_t* topk_ids, const void* w13, const float* w13_scale,
+                                  const void* w2, const float* w2_scale, void* workspace,
+                                  int64_t workspace_bytes, int64_t rows, int64_t hidden,
+                                  int64_t inter, int64_t experts, int64_t top_k, int64_t block_m,
+                                  int64_t row_stride_bytes, int64_t y_stride, int64_t w13_stride_e,
+                                  int64_t w13_stride_n, int64_t s13_stride_e, int64_t s13_stride_n,
+                                  int64_t w2_stride_e, int64_t w2_stride_n, int64_t s2_stride_e,
+                                  int64_t s2_stride_n, int scale_kind, int gate_act,
+                                  strix_stream_t stream);
+
 /* ---- Expert-parallel exchange over peer memory (no counterpart in the
  * reference, whose experts refuse an expert_map: python/strix_vllm/moe.py:193-210).
  * Buffers are plain device allocations that peers map through CUDA IPC:
@@ -502,6 +521,49 @@ int strix_moe_permute_rows(const void* x, void* y, const int32_t* slot_pos,
                            const int32_t* sorted_ids, const int32_t* num_post_padded,
                            int64_t rows, int64_t sorted_rows, int64_t row_bytes, int64_t top_k,
                            int64_t x_stride_bytes, int64_t y_stride_bytes, strix_stream_t stream);
+
+/* One call for a whole expert-parallel MoE layer over the exchange above: router ->
+ * (FP8: quantise the payload) -> plan -> dispatch -> wait for the sources -> this
+ * rank's experts over the received rows (sorted-layout tcgen05 kernels) -> partial
+ * sums back -> wait and combine into out (bf16 [tokens, hidden]). Enqueues about
+ * ten kernels on `stream`, allocates nothing, never synchronises the host. The two
+ * structs carry what does not change from call to call; `epoch` must be one more
+ * than at the previous call over these buffers (1 at the first). */
+typedef struct strix_expert_weights {
+  const void* w13;        /* MXFP4: uint8 [E, 2I, H/2]; FP8: e4m3 [E, 2I, H] */
+  const void* w13_scale;  /* MXFP4: e8m0 [E, 2I, H/32]; FP8: fp32 channel [E, 2I] or block */
+  const void* w2;         /* [E, H, I/2] or [E, H, I] */
+  const void* w2_scale;
+  int64_t w13_stride_e, w13_stride_n, s13_stride_e, s13_stride_n;   /* in elements */
+  int64_t w2_stride_e, w2_stride_n, s2_stride_e, s2_stride_n;
+  int64_t experts, hidden, inter;   /* experts on THIS rank */
+  int32_t kind;                     /* 0 MXFP4 x bf16, 1 FP8 W8A8 channel scales, 2 block scales */
+  int32_t gate_act;                 /* 1 silu, 2 gelu_tanh */
+} strix_expert_weights;
+
+typedef struct strix_ep_exchange {
+  int64_t world, rank, cap, top_k, row_bytes, hidden, epoch;
+  void* const* peer_recv;     /* host arrays of `world` device addresses, own rank included */
+  void* const* peer_meta;
+  void* const* peer_counts;
+  void* const* peer_flags;
+  void* const* peer_ret;
+  void* const* peer_rflags;
+  int32_t* ticket;            /* 2 ints, zeroed once */
+  int32_t* ids;               /* [world * cap, top_k] received routing */
+  float* weights;             /* [world * cap, top_k] */
+  int32_t* rows_per_source;   /* [world] */
+  void* y;                    /* bf16 [world * cap * top_k, hidden] */
+  int32_t* tok_pos;           /* [world, cap] */
+  int32_t* counts;            /* [world] */
+} strix_ep_exchange;
+
+int64_t strix_ep_moe_layer_workspace(const strix_expert_weights* w, const strix_ep_exchange* ep,
+                                     int64_t block_m);
+int strix_ep_moe_layer(void* out, const void* x, const float* logits, const strix_expert_weights* w,
+                       const strix_ep_exchange* ep, void* workspace, int64_t workspace_bytes,
+                       int64_t tokens, int64_t x_stride, int64_t logits_stride, int64_t out_stride,
+                       int64_t block_m, int64_t spin_limit, strix_stream_t stream);
 
 /* strix_attn_prefill_bf16 on the tcgen05 tensor cores (S and O in tensor memory,
  * TMA-fed operands): same contract and arguments (attn_prefill_bf16 of the

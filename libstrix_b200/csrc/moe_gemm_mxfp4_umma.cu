@@ -16,7 +16,7 @@
 //                         256-column TMEM buffers;
 //   epilogue (4 warps)    one token row per thread: act(gate) * up on adjacent
 //                         columns, or x routing weight; contiguous output rows.
-// The decode is the expensive part (about 300 instructions per weight row and K
+// The decode is the expensive part (about 200 instructions per weight row and K
 // block), so a decoded tile serves TWO m-blocks where it can: consecutive
 // m-blocks of one expert form a unit of 256 tokens, whose halves accumulate in
 // the two 256-column TMEM buffers from the same decoded tile (a lone m-block is a
@@ -72,18 +72,20 @@ __device__ __forceinline__ uint32_t mx_mul_bf16x2(uint32_t a, uint32_t b) {
 // Eight nibbles (element i in bits [4i, 4i + 4)) -> four bf16 pairs times scale2
 // (2^(s - 127) twice, bf16 pattern s << 7; s = 0 is the zero block). The low three
 // bits of a nibble index an 8-entry table of bf16 patterns (0, .5, 1, 1.5, 2, 3,
-// 4, 6) looked up by byte permutes, bit 3 is the sign.
+// 4, 6) looked up by byte permutes. Bit 3 is the sign: a permute whose selector
+// nibble has bit 3 set replicates the source byte's top bit, so the raw nibbles
+// as selectors over bytes of 0x80 give 0xFF for a negative element and 0x80 for a
+// positive one - the four sign bits of a half word cost three instructions.
 __device__ __forceinline__ void mx_decode8(uint32_t w, uint32_t scale2, uint32_t* out) {
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const uint32_t x = h == 0 ? w : w >> 16;
     const uint32_t sel = x & 0x7777u;
-    const uint32_t hi = prmt(0x3F3F3F00u, 0x40404040u, sel);
+    const uint32_t neg = prmt(0x80808080u, 0x80808080u, x) << 7;        // bit 7 of a byte: negative
+    const uint32_t hi = prmt(0x3F3F3F00u, 0x40404040u, sel) | (neg & 0x80808080u);
     const uint32_t lo = prmt(0xC0800000u, 0xC0804000u, sel);
-    const uint32_t p01 = prmt(lo, hi, 0x5140) | ((x & 0x8u) << 12) | ((x & 0x80u) << 24);
-    const uint32_t p23 = prmt(lo, hi, 0x7362) | ((x & 0x800u) << 4) | ((x & 0x8000u) << 16);
-    out[2 * h] = mx_mul_bf16x2(p01, scale2);
-    out[2 * h + 1] = mx_mul_bf16x2(p23, scale2);
+    out[2 * h] = mx_mul_bf16x2(prmt(lo, hi, 0x5140), scale2);
+    out[2 * h + 1] = mx_mul_bf16x2(prmt(lo, hi, 0x7362), scale2);
   }
 }
 

@@ -250,6 +250,37 @@ class _RawCuda:
 _BUFFERS = ("recv", "meta", "counts", "flags", "ret", "rflags")
 
 
+class _ExpertWeights(ctypes.Structure):
+    """strix_expert_weights of the header."""
+    _fields_ = [("w13", ctypes.c_void_p), ("w13_scale", ctypes.c_void_p), ("w2", ctypes.c_void_p),
+                ("w2_scale", ctypes.c_void_p)] + \
+               [(n, ctypes.c_int64) for n in ("w13_stride_e", "w13_stride_n", "s13_stride_e", "s13_stride_n",
+                                              "w2_stride_e", "w2_stride_n", "s2_stride_e", "s2_stride_n",
+                                              "experts", "hidden", "inter")] + \
+               [("kind", ctypes.c_int32), ("gate_act", ctypes.c_int32)]
+
+
+class _Exchange(ctypes.Structure):
+    """strix_ep_exchange of the header."""
+    _fields_ = [(n, ctypes.c_int64) for n in ("world", "rank", "cap", "top_k", "row_bytes", "hidden",
+                                              "epoch")] + \
+               [("peer_" + n, ctypes.POINTER(ctypes.c_void_p)) for n in _BUFFERS] + \
+               [(n, ctypes.c_void_p) for n in ("ticket", "ids", "weights", "rows_per_source", "y", "tok_pos",
+                                               "counts")]
+
+
+def _expert_weights(w13, w13_scale, w2, w2_scale, kind: int) -> _ExpertWeights:
+    e, n13 = w13.size(0), w13.size(1)
+    hidden, inter = w2.size(1), n13 // 2
+    block = kind == 2
+    per_row = kind == 0 or block     # scale tensors with a row stride ([E, N, K/32] or [E, N/128, K/128])
+    return _ExpertWeights(
+        w13.data_ptr(), w13_scale.data_ptr(), w2.data_ptr(), w2_scale.data_ptr(),
+        w13.stride(0), w13.stride(1), w13_scale.stride(0), w13_scale.stride(1) if per_row else 0,
+        w2.stride(0), w2.stride(1), w2_scale.stride(0), w2_scale.stride(1) if per_row else 0,
+        e, hidden, inter, kind, 1)
+
+
 class EpContext:
     """One rank's buffers for the peer-memory exchange, plus the addresses of
     every peer's buffers as this rank sees them.
@@ -287,7 +318,7 @@ class EpContext:
         self.weights = torch.empty(world * cap, top_k, dtype=torch.float32, device=self.device)
         self.rows_per_source = torch.zeros(world, **i32)
         self.y = torch.empty(world * cap * top_k, hidden, dtype=torch.bfloat16, device=self.device)
-        self.tok_pos = None
+        self.tok_pos = torch.empty(world, cap, **i32)    # used as [world, tokens] of the call
         self.counts = torch.empty(world, **i32)
 
     # ---- construction
@@ -352,8 +383,6 @@ class EpContext:
         self.tokens = t
         ids = topk_ids.to(torch.int32).contiguous()
         wts = topk_weights.to(torch.float32).contiguous()
-        if self.tok_pos is None or self.tok_pos.numel() != self.world * max(t, 1):
-            self.tok_pos = torch.empty(self.world, max(t, 1), dtype=torch.int32, device=self.device)
         stream = torch.cuda.current_stream().cuda_stream
         call = self._lib.call
         with torch.cuda.device(self.device):
@@ -402,6 +431,41 @@ class EpContext:
                            self.cap, self.epoch, spin_limit, stream)
         return out
 
+    def layer(self, x, logits, w13, w13_scale, w2, w2_scale, kind: int, block_m: int,
+              out: torch.Tensor | None = None, spin_limit: int = 0) -> torch.Tensor:
+        """One expert-parallel layer as ONE call into the library (strix_ep_moe_layer):
+        router, payload, dispatch, this rank's experts over what it receives, return
+        and combine. kind 0 MXFP4 experts over bf16 rows, 1 / 2 FP8 W8A8 experts
+        (channel / block scales) over e4m3 rows."""
+        t, h = x.shape
+        assert t <= self.cap and h == self.hidden and x.stride(1) == 1 and logits.stride(1) == 1
+        assert x.dtype == torch.bfloat16 and logits.dtype == torch.float32
+        self.epoch += 1
+        self.tokens = t
+        if out is None:
+            out = torch.empty(t, h, dtype=torch.bfloat16, device=self.device)
+        keep = {n: self._ptrs(n) for n in _BUFFERS}        # host arrays the struct points into
+        ex = _Exchange(self.world, self.rank, self.cap, self.top_k, self.row_bytes, self.hidden, self.epoch,
+                       *[ctypes.cast(keep[n], ctypes.POINTER(ctypes.c_void_p)) for n in _BUFFERS],
+                       self.ticket.data_ptr(), self.ids.data_ptr(), self.weights.data_ptr(),
+                       self.rows_per_source.data_ptr(), self.y.data_ptr(), self.tok_pos.data_ptr(),
+                       self.counts.data_ptr())
+        wt = _expert_weights(w13, w13_scale, w2, w2_scale, kind)
+        lib = self._lib.load()
+        need = lib.strix_ep_moe_layer_workspace(ctypes.byref(wt), ctypes.byref(ex), block_m)
+        if need < 0:
+            raise RuntimeError(lib.strix_last_error().decode())
+        ws = getattr(self, "_layer_ws", None)
+        if ws is None or ws.numel() < need + 256:
+            ws = self._layer_ws = torch.empty(need + 256, dtype=torch.uint8, device=self.device)
+        with torch.cuda.device(self.device):
+            self._lib.call("strix_ep_moe_layer", out.data_ptr(), x.data_ptr(), logits.data_ptr(),
+                           ctypes.byref(wt), ctypes.byref(ex), (ws.data_ptr() + 255) // 256 * 256, need, t,
+                           x.stride(0), logits.stride(0), out.stride(0) if t else h, block_m, spin_limit,
+                           torch.cuda.current_stream().cuda_stream)
+            self._lib.after_tcgen05("ep_moe_layer")
+        return out
+
     def status(self, reset: bool = False) -> int:
         flag = ctypes.c_int32(-1)
         with torch.cuda.device(self.device):
@@ -444,6 +508,24 @@ def _experts_fp8_on_received(ctx: EpContext, w13, w13_scale, w2, w2_scale, block
     mark("receive_wait")
     e, n13, h = w13.shape
     inter = n13 // 2
+    if mark is _no_mark and w13_scale.stride(-1) == 1 and w2_scale.stride(-1) == 1:
+        # no phase timing wanted: the five launches as ONE call into the library
+        from . import _lib
+        n_rows, key = ids.size(0), (ids.size(0), ctx.top_k, h, inter, e, block_m)
+        ws = getattr(ctx, "_fp8_ws", None)
+        if ws is None or ws.key != key:
+            ws = ctx._fp8_ws = _moe.Fp8LayerWorkspace(n_rows, ctx.top_k, h, inter, e, block_m, ctx.device,
+                                                      with_out=False)
+        block = w13_scale.dim() == 3 and w13_scale.size(1) != n13
+        _lib.call("strix_moe_fp8_experts_on_rows", ctx.y.data_ptr(), rows.data_ptr(), weights.data_ptr(),
+                  ids.data_ptr(), w13.data_ptr(), w13_scale.data_ptr(), w2.data_ptr(), w2_scale.data_ptr(),
+                  ws.ptr, ws.nbytes, n_rows, h, inter, e, ctx.top_k, block_m, rows.stride(0),
+                  ctx.y.stride(0), w13.stride(0), w13.stride(1), w13_scale.stride(0),
+                  w13_scale.stride(1) if block else 0, w2.stride(0), w2.stride(1), w2_scale.stride(0),
+                  w2_scale.stride(1) if block else 0, 2 if block else 1, 1,
+                  torch.cuda.current_stream().cuda_stream)
+        _lib.after_tcgen05("ep_moe_fp8")
+        return ctx.y
     ops = torch.ops.strix
     f8 = torch.float8_e4m3fn
     sorted_ids, expert_ids, num_post, slot_pos = _moe.align_with_positions(ids, block_m, e)
@@ -505,8 +587,8 @@ def fp8_payload(x: torch.Tensor, buf: torch.Tensor | None = None):
     FP8 layer sends instead of bf16 rows."""
     t, h = x.shape
     row = fp8_row_bytes(h)
-    if buf is None or buf.size(0) < t or buf.size(1) != row:
-        buf = torch.zeros(max(t, 1), row, dtype=torch.uint8, device=x.device)
+    if buf is None or buf.size(0) != t or buf.size(1) != row or buf.device != x.device:
+        buf = torch.zeros(t, row, dtype=torch.uint8, device=x.device)
     q, s = buf[:t, :h].view(torch.float8_e4m3fn), buf[:t, h:h + h // 32].view(torch.float32)
     torch.ops.strix.moe_act_quant_fp8(x, q, s)
     return buf[:t], q, s
@@ -526,8 +608,9 @@ def ep_moe_fp8(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, block
     t, h = x.shape
     if world == 1 and exchange == "auto" and ctx is None:
         return _moe.fused_moe_fp8_w8a8(x, logits, w13, w13_scale, w2, w2_scale, top_k, block_m=block_m)
-    weights, ids = _moe.route(logits, top_k)
     if exchange == "nccl" or not x.is_cuda:
+        weights, ids = _moe.route(logits, top_k)
+
         def combine(slots):
             out = torch.empty(t, h, dtype=torch.bfloat16, device=x.device)
             torch.ops.strix.moe_sum(slots, out)
@@ -543,8 +626,13 @@ def ep_moe_fp8(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, block
     bm = block_m or _moe.pick_block_m(t * ctx.world, top_k, e_local * ctx.world)
     if not _moe.sorted_path_covers(w13, w13_scale, w2, w2_scale, bm):
         raise RuntimeError("ep_moe_fp8: geometry not covered by the sorted-layout kernel")
+    if mark is _no_mark and _one_call_ok(x, logits, w13_scale, w2_scale):
+        block = w13_scale.dim() == 3 and w13_scale.size(1) != w13.size(1)
+        return ctx.layer(x, logits, w13, w13_scale, w2, w2_scale, 2 if block else 1, bm)
+    weights, ids = _moe.route(logits, top_k)
     mark("route")
-    payload, _, _ = fp8_payload(x)
+    payload, _, _ = fp8_payload(x, getattr(ctx, "_payload", None))
+    ctx._payload = payload          # the padding bytes were zeroed once, at allocation
     mark("quantise")
     ctx.dispatch(payload, weights, ids, e_local, mark)
     y = _experts_fp8_on_received(ctx, w13, w13_scale, w2, w2_scale, bm, mark)
@@ -571,8 +659,13 @@ def ep_moe_mxfp4(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, blo
                    and lib.strix_moe_gemm_mxfp4_sorted_covers(w2.size(1), w2.size(2) * 2, 128, 0))
     if world == 1 and exchange == "auto" and ctx is None and x.is_cuda:
         return _moe.fused_moe_mxfp4(x, logits, w13, w13_scale, w2, w2_scale, top_k, block_m=block_m)
+    peer = exchange != "nccl" and x.is_cuda and wide_ok and (h * 2) % 16 == 0
+    if peer and mark is _no_mark and _one_call_ok(x, logits, w13_scale, w2_scale):
+        if ctx is None:
+            ctx = context_for(group, t, top_k, h * 2, h, x.device)
+        return ctx.layer(x, logits, w13, w13_scale, w2, w2_scale, 0, 128)
     weights, ids = _moe.route(logits, top_k)
-    if exchange == "nccl" or not x.is_cuda or not wide_ok or (h * 2) % 16:
+    if not peer:
         def combine(slots):
             out = torch.empty(t, h, dtype=torch.bfloat16, device=x.device)
             torch.ops.strix.moe_sum(slots, out)
@@ -591,6 +684,12 @@ def ep_moe_mxfp4(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, blo
     out = ctx.combine()
     mark("combine_wait")
     return out
+
+
+def _one_call_ok(x, logits, w13_scale, w2_scale) -> bool:
+    """Layouts strix_ep_moe_layer takes as they are."""
+    return x.dtype == torch.bfloat16 and x.stride(1) == 1 and logits.dtype == torch.float32 \
+        and logits.stride(1) == 1 and w13_scale.stride(-1) == 1 and w2_scale.stride(-1) == 1
 
 
 def _capacity(tokens: int, group) -> int:

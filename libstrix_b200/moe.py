@@ -99,12 +99,12 @@ class Fp8LayerWorkspace:
     """Scratch of the one-call layer launcher (strix_moe_fp8_layer) for one shape,
     plus the output rows."""
 
-    def __init__(self, tokens, top_k, hidden, inter, experts, block_m, device):
+    def __init__(self, tokens, top_k, hidden, inter, experts, block_m, device, with_out=True):
         self.key = (tokens, top_k, hidden, inter, experts, block_m)
         self.nbytes = _lib.load().strix_moe_fp8_layer_workspace(*self.key)
         self.buf = torch.empty(self.nbytes + 256, dtype=torch.uint8, device=device)
         self.ptr = (self.buf.data_ptr() + 255) // 256 * 256
-        self.out = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=device)
+        self.out = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=device) if with_out else None
 
 
 def workspace_for(tokens, top_k, hidden, inter, experts, block_m, device, layout="sorted"):
@@ -113,6 +113,13 @@ def workspace_for(tokens, top_k, hidden, inter, experts, block_m, device, layout
     if layout != "sorted":
         return Fp8MoeWorkspace(tokens, top_k, hidden, inter, device)
     return Fp8LayerWorkspace(tokens, top_k, hidden, inter, experts, block_m, device)
+
+
+def fits_sorted_grid(slots: int, experts: int, block_m: int) -> bool:
+    """Whether the padded id list of `slots` routed rows stays within the m-blocks
+    one launch of the sorted-layout kernels may walk (MAX_SORTED_M_BLOCKS); above
+    it the layer takes the gather layout. Host arithmetic only."""
+    return _lib.load().strix_moe_align_capacity(slots, experts, block_m) // block_m <= MAX_SORTED_M_BLOCKS
 
 
 def sorted_path_covers(w13, w13_scale, w2, w2_scale, block_m: int) -> bool:
@@ -162,7 +169,7 @@ def _layer_call(x, logits, topk_weights, topk_ids, w13, w13_scale, w2, w2_scale,
             or (logits is not None and (logits.dtype != torch.float32 or logits.stride(1) != 1)):
         return None
     if not sorted_path_covers(w13, w13_scale, w2, w2_scale, bm) \
-            or lib.strix_moe_align_capacity(t * top_k, e, bm) // bm > MAX_SORTED_M_BLOCKS:
+            or not fits_sorted_grid(t * top_k, e, bm):
         if layout == "sorted":
             raise RuntimeError("fused_moe_fp8_w8a8: geometry not covered by the sorted-layout kernels")
         return None
@@ -214,9 +221,8 @@ def experts_fp8_w8a8(x, topk_weights, topk_ids, w13, w13_scale, w2, w2_scale, ou
     bm = block_m or pick_block_m(t, top_k, e)
     lib = _lib.load()
     if layout == "auto":
-        cap_blocks = lib.strix_moe_align_capacity(t * top_k, e, bm) // bm
         layout = "sorted" if sorted_path_covers(w13, w13_scale, w2, w2_scale, bm) \
-            and cap_blocks <= MAX_SORTED_M_BLOCKS else "gather"
+            and fits_sorted_grid(t * top_k, e, bm) else "gather"
     weights = topk_weights.to(torch.float32)
     ids = topk_ids.to(torch.int32).contiguous()
     ops = torch.ops.strix

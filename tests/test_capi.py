@@ -59,3 +59,23 @@ def _decode_args(**over):
 def test_decode_rejects_bad_arguments_without_a_gpu(over, fragment):
     with pytest.raises(_lib.StrixError, match=fragment.replace("[", r"\[").replace("]", r"\]")):
         _lib.call("strix_attn_decode_bf16", *_decode_args(**over))
+
+
+def test_sorted_layout_gives_way_to_gather_above_the_m_block_limit():
+    """Needs no GPU: the padded list's capacity is host arithmetic. 2048 m-blocks of
+    128 rows hold the benchmark layer's 4096 x 8 slots with room to spare; a batch
+    whose padded list needs more blocks than one launch walks takes the gather
+    layout instead of failing."""
+    from libstrix_b200 import moe
+
+    lib = _lib.load()
+    assert moe.fits_sorted_grid(4096 * 8, 128, 128)
+    assert moe.fits_sorted_grid(1, 128, 16)
+    # capacity = slots + experts * (block_m - 1) rounded up to whole blocks
+    cap = lib.strix_moe_align_capacity(4096 * 8, 128, 128)
+    assert cap % 128 == 0 and cap >= 4096 * 8 + 128 * 127
+    limit = moe.MAX_SORTED_M_BLOCKS * 128
+    slots_at_limit = limit - 128 * 127
+    assert moe.fits_sorted_grid(slots_at_limit, 128, 128)
+    assert not moe.fits_sorted_grid(slots_at_limit + 1, 128, 128)
+    assert not moe.fits_sorted_grid(1 << 20, 128, 16)

@@ -274,6 +274,41 @@ def test_peer_exchange_with_emulated_ranks(kind, tokens_per_rank):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("kind", ["mxfp4", "fp8"])
+@pytest.mark.parametrize("tokens", [70, 1])
+def test_one_call_layer_on_a_single_rank(kind, tokens):
+    """strix_ep_moe_layer (router, payload, dispatch, experts, return, combine in one
+    call) on a world of one - the rank sends to itself, so every wait is for a kernel
+    launched earlier on the same stream - against the CPU oracle, twice in a row
+    (the epoch stamps carry over) and with fewer tokens than the capacity."""
+    from libstrix_b200 import ep
+    from libstrix_b200.workloads import moe_fp8_layer, moe_mxfp4_layer
+    from oracle import moe as M
+
+    dev = torch.device("cuda", 0)
+    e, k, hid, inter = 8, 2, 256, 128
+    if kind == "mxfp4":
+        layer = moe_mxfp4_layer(tokens=128, hidden=hid, experts=e, top_k=k, inter=inter, seed=5)
+        oracle, row_bytes, code, bm = M.moe_mxfp4_layer, hid * 2, 0, 128
+    else:
+        layer = moe_fp8_layer(tokens=128, hidden=hid, experts=e, top_k=k, inter=inter, seed=5)
+        oracle, row_bytes, code, bm = M.moe_fp8_layer, ep.fp8_row_bytes(hid), 2, 128
+    g = layer.to(dev)
+    ctx = ep.EpContext.emulate(1, 100, k, row_bytes, hid, dev)[0]
+    try:
+        for n in (tokens, min(tokens + 20, 100)):
+            ref, _, _ = oracle(layer.x[:n], layer.logits[:n], layer.w13, layer.w13_scale, layer.w2,
+                               layer.w2_scale, k)
+            out = ctx.layer(g.x[:n], g.logits[:n], g.w13, g.w13_scale, g.w2, g.w2_scale, code, bm)
+            torch.cuda.synchronize()
+            assert ctx.status() == 0
+            ok, err, rms = _bound_ok(out, ref)
+            assert ok, f"{n} tokens: max err {err} vs rms {rms}"
+    finally:
+        ctx.close()
+
+
+@pytest.mark.gpu
 def test_peer_exchange_waits_are_bounded():
     """A flag that nothing sets: the receive and combine kernels give up after the
     given number of polls, raise the status word and deliver empty input."""
