@@ -25,12 +25,23 @@
 //                           stored it over S), interleaved between the two tiles
 //                           so the tensor pipe works on one tile while the softmax
 //                           of the other runs;
-//      softmax (2 x 4 warps) one query row per thread: tcgen05.ld of the scores,
-//                           online softmax in the exp2 domain, P packed to 16 bits
-//                           and written back with tcgen05.st, the running sum kept
-//                           in a register; O is rescaled in TMEM only when the
-//                           row maximum grew by more than 2^8 (the stale maximum
-//                           keeps P below 256, well inside 16-bit range).
+//      softmax (2 x 8 warps) TWO threads per query row, 64 of a key tile's 128
+//                           columns each (the two warps that share a TMEM lane
+//                           quadrant): tcgen05.ld of the scores, online softmax
+//                           in the exp2 domain, P packed to 16 bits and written
+//                           back with tcgen05.st, the running sum kept per half;
+//                           the halves exchange their maxima through shared
+//                           memory and an mbarrier once per key tile, which also
+//                           orders one half's P store after the other's S reads.
+//                           O is rescaled in TMEM only when the row maximum grew
+//                           by more than 2^8 (the stale maximum keeps P below
+//                           256, well inside 16-bit range). Four softmax warps
+//                           per scheduler instead of two hide the latencies of
+//                           the dependent max / exp2 / sum chains. (One issuing
+//                           thread for both tiles is deliberate: with a thread per
+//                           tile the two tiles' MMAs interleave in the tensor
+//                           pipe and each tile waits for both - measured 850
+//                           against 1,015 TFLOP/s.)
 //    TMEM: S0, S1 (128 columns each, P aliases their first 64), O0, O1 (D each).
 //    Every mbarrier wait is bounded; a timeout raises the status word and the CTA
 //    drains its copies and MMAs before it frees TMEM.
@@ -45,7 +56,10 @@ namespace {
 using namespace umma;
 
 constexpr int kPuQ = 128, kPuKeys = 128;           // Q tile rows, key tile
-constexpr int kPuThreads = 10 * 32;                // producer, issuer, 2 x 4 softmax warps
+constexpr int kPuHalves = 2;                       // threads per query row
+constexpr int kPuCols = kPuKeys / kPuHalves;       // columns of a key tile per softmax thread
+constexpr int kPuSoftmaxWarps = 2 * 4 * kPuHalves;
+constexpr int kPuThreads = (2 + kPuSoftmaxWarps) * 32;   // producer, issuer, softmax warps
 constexpr int kPuStages = 2;
 constexpr float kPuRescale = 8.f;                  // log2 of the growth of the maximum that forces a rescale
 
@@ -170,6 +184,12 @@ __global__ void __launch_bounds__(256) prefill_gather_kernel(const GatherArgs p)
   }
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 // ------------------------------------------------------------------ attention
 template <int D, bool Q8>
 __global__ void __launch_bounds__(kPuThreads, 1) attn_prefill_umma_kernel(
@@ -182,6 +202,8 @@ __global__ void __launch_bounds__(kPuThreads, 1) attn_prefill_umma_kernel(
   extern __shared__ uint8_t raw_smem[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
   __shared__ __align__(8) uint64_t q_full, q_ready, full_bar[S], empty_bar[S], s_full[2], p_full[2], o_full, drain_bar;
+  __shared__ __align__(8) uint64_t pair_bar[8];      // the two warps that share (Q tile, lane quadrant)
+  __shared__ float s_xmax[2][kPuHalves][kPuQ], s_xl[2][kPuHalves][kPuQ];   // what the halves of a row exchange
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int s_abort;
 
@@ -226,9 +248,10 @@ __global__ void __launch_bounds__(kPuThreads, 1) attn_prefill_umma_kernel(
 
   if (tid == 0) {
     mbar_init(&q_full, 1);
-    mbar_init(&q_ready, 8);
+    mbar_init(&q_ready, kPuSoftmaxWarps);
     for (int i = 0; i < S; ++i) mbar_init(&full_bar[i], 1), mbar_init(&empty_bar[i], 1);
-    for (int i = 0; i < 2; ++i) mbar_init(&s_full[i], 1), mbar_init(&p_full[i], 4);
+    for (int i = 0; i < 2; ++i) mbar_init(&s_full[i], 1), mbar_init(&p_full[i], 4 * kPuHalves);
+    for (int i = 0; i < 8; ++i) mbar_init(&pair_bar[i], kPuHalves);
     mbar_init(&o_full, 1);
     mbar_init(&drain_bar, 1);
     s_abort = 0;
@@ -333,12 +356,28 @@ __global__ void __launch_bounds__(kPuThreads, 1) attn_prefill_umma_kernel(
     }
   } else if (warp >= 2) {
     // -------------------------------------------------------------- softmax
-    const int q = (warp - 2) >> 2;
-    const int row = (warp & 3) * 32 + lane;
-    const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
-    const uint32_t t_s = tmem + lane_base + L::kTmemS + q * kPuKeys;
+    const int sw = warp - 2;
+    const int q = sw >> 3;                             // Q tile
+    const int half = (sw >> 2) & 1;                    // which 64 of a key tile's columns
+    const int quad = warp & 3;                         // the TMEM lane quadrant this warp may touch
+    const int row = quad * 32 + lane;
+    uint64_t* const pbar = &pair_bar[q * 4 + quad];
+    const uint32_t lane_base = uint32_t(quad * 32) << 16;
+    const uint32_t t_s = tmem + lane_base + L::kTmemS + q * kPuKeys + half * kPuCols;   // this thread's scores
+    const uint32_t t_p = tmem + lane_base + L::kTmemS + q * kPuKeys + half * (kPuCols / 2);   // its share of P
     const uint32_t t_o = tmem + lane_base + L::kTmemO + q * D;
     bool dead = false;
+    int px = 0;                                        // uses of the pair's barrier so far
+    // Both warps of a row have passed this point and see each other's shared-memory
+    // writes from before it. A bounded mbarrier wait, not bar.sync: if one warp gave
+    // up on a wait and left, the other must time out too instead of hanging.
+    auto pair_sync = [&]() {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pbar);
+      const bool ok = mbar_wait(pbar, px & 1);
+      ++px;
+      return !__any_sync(0xffffffffu, !ok);
+    };
 
     if constexpr (Q8) {
       // the bf16 queries become fp16 in place (element-wise, so the swizzle is untouched)
@@ -346,7 +385,7 @@ __global__ void __launch_bounds__(kPuThreads, 1) attn_prefill_umma_kernel(
       if (__any_sync(0xffffffffu, !ok)) dead = true;
       if (!dead) {
         uint4* qv = reinterpret_cast<uint4*>(smem);
-        for (int i = tid - 64; i < 2 * L::kQTile / 16; i += 256) {
+        for (int i = tid - 64; i < 2 * L::kQTile / 16; i += kPuSoftmaxWarps * 32) {
           uint4 x = qv[i];
           x.x = pack_f16x2(bf16_lo(x.x), bf16_hi(x.x)), x.y = pack_f16x2(bf16_lo(x.y), bf16_hi(x.y));
           x.z = pack_f16x2(bf16_lo(x.z), bf16_hi(x.z)), x.w = pack_f16x2(bf16_lo(x.w), bf16_hi(x.w));
@@ -360,19 +399,20 @@ __global__ void __launch_bounds__(kPuThreads, 1) attn_prefill_umma_kernel(
 
     const int qi = cta_q0 + q * kPuQ + row;            // local query index of this thread's row
     const int qpos = pos0 + qi;
-    const int warp_q0 = pos0 + cta_q0 + q * kPuQ + (warp & 3) * 32;   // position of the warp's first row
+    const int warp_q0 = pos0 + cta_q0 + q * kPuQ + quad * 32;   // position of the warp's first row
     const float sl2 = p.scale * kLog2e;
-    float m_ref = -INFINITY, l = 0.f;
+    const float2 sl2x2 = make_float2(sl2, sl2);
+    float m_ref = -INFINITY, l = 0.f;                  // l: this half's share of the row sum
     for (int j = 0; j < n_tiles && !dead; ++j) {
-      const int k0 = k_begin + j * kPuKeys;
+      const int k0 = k_begin + j * kPuKeys + half * kPuCols;   // first key of this thread's columns
       const bool ok = mbar_wait(&s_full[q], j & 1);
       if (__any_sync(0xffffffffu, !ok) || s_abort) {
         dead = true;
         break;
       }
       tc_fence_after_sync();
-      // a tile every row of the warp sees completely needs no mask
-      const bool interior = k0 + kPuKeys <= k_end && k0 + kPuKeys - 1 <= warp_q0 &&
+      // columns every row of the warp sees completely need no mask
+      const bool interior = k0 + kPuCols <= k_end && k0 + kPuCols - 1 <= warp_q0 &&
                             (p.window_left < 0 || warp_q0 + 31 - k0 <= p.window_left);
       auto masked = [&](float v, int key) {
         const bool vis = key < k_end && key <= qpos && (p.window_left < 0 || qpos - key <= p.window_left);
@@ -380,47 +420,62 @@ __global__ void __launch_bounds__(kPuThreads, 1) attn_prefill_umma_kernel(
       };
       // One pass over the scores in the common case: P = 2^(s - m_ref) against the
       // maximum carried over from the earlier tiles, the tile's own maximum taken on
-      // the way. Only if that maximum exceeds m_ref by more than 2^kPuRescale (or no
-      // key was seen yet) the accumulator is rescaled and the pass repeated - S is
-      // still intact, because P (which overwrites its first 64 columns) is held in
-      // registers until the decision. The TMEM load of the next 16 columns is in
-      // flight while the current ones are processed; maxima and sums run in four
-      // independent chains each (two warps per scheduler cannot hide a serial one).
-      uint32_t pk[kPuKeys / 2];
+      // the way (three-input max, packed two-wide multiply-add and add: about three
+      // instructions per score). Only if the row's maximum exceeds m_ref by more than
+      // 2^kPuRescale (or no key was seen yet) the accumulator is rescaled and the pass
+      // repeated - S is still intact, because P (which overwrites its first 64
+      // columns) is held in registers until both halves have decided. The scores come
+      // 16 columns at a time and are not prefetched: with four softmax warps per
+      // scheduler another warp covers the TMEM load, and the registers a second buffer
+      // would take are what keeps the loop free of spills at the 96 registers a CTA of
+      // 18 warps allows (measured at 65,536 tokens: 8-column double buffering 950
+      // TFLOP/s, 16-column double buffering with spills 825, this form 1,015). Maxima
+      // and sums run in four independent chains each.
+      uint32_t pk[kPuCols / 2];
       float lt = 0.f;
       const bool seen = __all_sync(0xffffffffu, m_ref != -INFINITY);
 #pragma unroll 1
-      for (int attempt = 0; attempt < 2; ++attempt) {
+      for (int attempt = 0; attempt < 2 && !dead; ++attempt) {
         const bool want_p = attempt == 1 || seen;   // rows without a key yet only take the maximum first
-        const float base = m_ref == -INFINITY ? 0.f : m_ref;
-        float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY}, lta[4] = {0.f, 0.f, 0.f, 0.f};
-        uint32_t r[2][16];
-        tmem_ld_32x16(t_s, r[0]);
+        const float nb = m_ref == -INFINITY ? 0.f : -m_ref;
+        const float2 nbx2 = make_float2(nb, nb);
+        float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        float2 lta[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+        uint32_t r[16];
 #pragma unroll
-        for (int c = 0; c < kPuKeys / 16; ++c) {
+        for (int c = 0; c < kPuCols / 16; ++c) {
+          tmem_ld_32x16(t_s + c * 16, r);
           tmem_ld_wait();
-          if (c + 1 < kPuKeys / 16) tmem_ld_32x16(t_s + (c + 1) * 16, r[(c + 1) & 1]);
           float v[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[c & 1][i]);
+          for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
           if (!interior) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) v[i] = masked(v[i], k0 + c * 16 + i);
           }
 #pragma unroll
-          for (int i = 0; i < 16; ++i) mxa[i & 3] = fmaxf(mxa[i & 3], v[i]);
+          for (int i = 0; i < 16; i += 2) mxa[(i >> 1) & 3] = max3(mxa[(i >> 1) & 3], v[i], v[i + 1]);
           if (want_p) {
 #pragma unroll
             for (int i = 0; i < 16; i += 2) {
-              const float p0 = fast_exp2(fmaf(v[i], sl2, -base)), p1 = fast_exp2(fmaf(v[i + 1], sl2, -base));
-              lta[(i >> 1) & 3] += p0 + p1;
-              pk[c * 8 + (i >> 1)] = Q8 ? pack_f16x2(p0, p1) : pack_bf16x2(p0, p1);
+              const float2 e = __ffma2_rn(make_float2(v[i], v[i + 1]), sl2x2, nbx2);
+              const float2 pp = make_float2(fast_exp2(e.x), fast_exp2(e.y));
+              lta[(i >> 1) & 1] = __fadd2_rn(lta[(i >> 1) & 1], pp);
+              pk[c * 8 + (i >> 1)] = Q8 ? pack_f16x2(pp.x, pp.y) : pack_bf16x2(pp.x, pp.y);
             }
           }
         }
-        lt = (lta[0] + lta[1]) + (lta[2] + lta[3]);
-        const float mx = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3]));
-        if (attempt == 1) break;
+        lt = (lta[0].x + lta[0].y) + (lta[1].x + lta[1].y);
+        if (attempt == 1) {
+          if (!pair_sync()) dead = true;     // the other half has finished re-reading S
+          break;
+        }
+        s_xmax[q][half][row] = fmaxf(max3(mxa[0], mxa[1], mxa[2]), mxa[3]);
+        if (!pair_sync()) {                  // both halves have read S; the maxima are visible
+          dead = true;
+          break;
+        }
+        const float mx = fmaxf(s_xmax[q][0][row], s_xmax[q][1][row]);
         const float m_new = fmaxf(m_ref, mx * sl2);
         // lazy rescale: only when the maximum grew by more than 2^kPuRescale (or is the first)
         const bool need = m_new > m_ref + kPuRescale || (m_ref == -INFINITY && m_new > -INFINITY);
@@ -428,32 +483,38 @@ __global__ void __launch_bounds__(kPuThreads, 1) attn_prefill_umma_kernel(
         if (!any_need && seen) break;
         if (any_need) {
           const float f = need ? (m_ref == -INFINITY ? 0.f : fast_exp2(m_ref - m_new)) : 1.f;
-          if (j > 0) {
+          if (j > 0) {                       // each half rescales its half of O's columns
 #pragma unroll 1
-            for (int c = 0; c < D / 32; ++c) {
-              uint32_t ro[32];
-              tmem_ld_32x32(t_o + c * 32, ro);
+            for (int c = half * (D / 32); c < (half + 1) * (D / 32); ++c) {
+              uint32_t ro[16];
+              tmem_ld_32x16(t_o + c * 16, ro);
               tmem_ld_wait();
 #pragma unroll
-              for (int i = 0; i < 32; ++i) ro[i] = __float_as_uint(__uint_as_float(ro[i]) * f);
-              tmem_st_32x32(t_o + c * 32, ro);
+              for (int i = 0; i < 16; ++i) ro[i] = __float_as_uint(__uint_as_float(ro[i]) * f);
+              tmem_st_32x16(t_o + c * 16, ro);
             }
           }
           l *= f;
           if (need) m_ref = m_new;
         }
       }
+      if (dead) break;
       l += lt;
 #pragma unroll
-      for (int c = 0; c < kPuKeys / 32; ++c)
-        tmem_st_32x16(t_s + c * 16, *reinterpret_cast<uint32_t(*)[16]>(&pk[c * 16]));
+      for (int c = 0; c < kPuCols / 32; ++c)
+        tmem_st_32x16(t_p + c * 16, *reinterpret_cast<uint32_t(*)[16]>(&pk[c * 16]));
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[q]);
     }
 
-    // ---- epilogue: sinks, normalise, store this thread's row
+    // ---- epilogue: the row's sum from both halves, sinks, normalise, store this half's columns
+    if (!dead) {
+      s_xl[q][half][row] = l;
+      if (!pair_sync()) dead = true;
+      l = s_xl[q][0][row] + s_xl[q][1][row];
+    }
     if (!dead) {
       const bool ok = mbar_wait(&o_full, 0);
       if (__any_sync(0xffffffffu, !ok) || s_abort) dead = true;
@@ -467,19 +528,19 @@ __global__ void __launch_bounds__(kPuThreads, 1) attn_prefill_umma_kernel(
       const float inv = l > 0.f ? 1.f / l : 0.f;
       __nv_bfloat16* orow = p.out + int64_t(q_begin + min(qi, q_len - 1)) * p.o_st + head * p.o_sh;
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_o + c * 32, r);
+      for (int c = half * (D / 32); c < (half + 1) * (D / 32); ++c) {
+        uint32_t r[16];
+        tmem_ld_32x16(t_o + c * 16, r);
         tmem_ld_wait();
         if (qi < q_len) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
+          for (int i = 0; i < 16; i += 8) {
             uint4 o;
             o.x = pack_bf16x2(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
             o.y = pack_bf16x2(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
             o.z = pack_bf16x2(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
             o.w = pack_bf16x2(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + c * 32 + i) = o;
+            *reinterpret_cast<uint4*>(orow + c * 16 + i) = o;
           }
         }
       }

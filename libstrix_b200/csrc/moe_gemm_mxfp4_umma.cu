@@ -8,9 +8,11 @@
 //                         (bf16, 128-byte-swizzled) and the tile's 256 weight
 //                         rows of the same K block as packed bytes (32 per row;
 //                         a 4-d box interleaves gate and up rows);
-//   transform (8 warps)   one weight row per thread: 64 nibbles -> 64 bf16 by a
-//                         byte-permute table, times the two e8m0 scales (exact),
-//                         stored as the 128-byte-swizzled B operand tile;
+//   transform (16 warps)  half a weight row per thread - one scale group: 32 nibbles
+//                         -> 32 bf16 by a byte-permute table, times the group's e8m0
+//                         scale (exact), stored as the 128-byte-swizzled B operand
+//                         tile (four warps per scheduler, so that the latencies of
+//                         the shared-memory round trip are covered);
 //   issuer (1 thread)     four tcgen05.mma kind::f16 (bf16 x bf16 -> f32, 128 x 256
 //                         x 16) per K block; the whole K accumulates in one of two
 //                         256-column TMEM buffers;
@@ -38,7 +40,7 @@ namespace {
 using namespace umma;
 
 constexpr int kMxTok = 128, kMxCols = 256, kMxKB = 64;       // tile: tokens x weight rows x K
-constexpr int kMxTransformWarps = 8, kMxEpilogueWarps = 4;
+constexpr int kMxTransformWarps = 16, kMxEpilogueWarps = 4;
 constexpr int kMxThreads = (4 + kMxTransformWarps + kMxEpilogueWarps) * 32;
 constexpr int kMxStages = 3, kMxDecoded = 2;
 constexpr int kMxMaxMBlocks = 2048;
@@ -222,7 +224,8 @@ __global__ void __launch_bounds__(kMxThreads, 1) moe_gemm_mxfp4_umma_kernel(
     }
   } else if (warp >= 4 && warp < 4 + kMxTransformWarps) {
     // ------------------------------------------------------------ transform
-    const int r = tid - 128;                          // row of the tile, 0..255
+    const int r = (tid - 128) >> 1;                   // row of the tile, 0..255
+    const int th = (tid - 128) & 1;                   // which 32 of the K block's 64 elements
     int t = 0;
     bool dead = false;
     for (int item = blockIdx.x; item < total_items && !dead; item += gridDim.x) {
@@ -232,12 +235,12 @@ __global__ void __launch_bounds__(kMxThreads, 1) moe_gemm_mxfp4_umma_kernel(
       const int orow = nt * tile_rows + (gate ? (r >> 1) : r);
       const bool row_ok = orow < (gate ? half_n : p.N);
       const int wrow = gate && (r & 1) ? half_n + orow : orow;
-      const uint8_t* sc = p.scales + int64_t(expert) * p.s_se + int64_t(row_ok ? wrow : 0) * p.s_sn;
-      uint32_t sc_next = row_ok ? uint32_t(sc[0]) | (uint32_t(sc[1]) << 8) : 0u;
+      const uint8_t* sc = p.scales + int64_t(expert) * p.s_se + int64_t(row_ok ? wrow : 0) * p.s_sn + th;
+      uint32_t sc_next = row_ok ? uint32_t(sc[0]) : 0u;
       for (int kb = 0; kb < nkb && !dead; ++kb, ++t) {
         const int s = t % S;
-        const uint32_t scb = sc_next;               // the two scale bytes of this K block
-        if (kb + 1 < nkb && row_ok) sc_next = uint32_t(sc[2 * kb + 2]) | (uint32_t(sc[2 * kb + 3]) << 8);
+        const uint32_t scb = sc_next;               // the scale byte of this thread's group
+        if (kb + 1 < nkb && row_ok) sc_next = uint32_t(sc[2 * kb + 2]);
         bool ok = mbar_wait(&full_bar[s], (t / S) & 1);
         // the decoded tile t % 2 was last read by the MMAs of K block t - 2
         if (t >= kMxDecoded) {
@@ -249,22 +252,18 @@ __global__ void __launch_bounds__(kMxThreads, 1) moe_gemm_mxfp4_umma_kernel(
           break;
         }
         const uint8_t* st = ring + s * L::kStageBytes;
-        const uint4* src = reinterpret_cast<const uint4*>(st + 2 * L::kABytes + r * (kMxKB / 2));
+        const uint4 x = *reinterpret_cast<const uint4*>(st + 2 * L::kABytes + r * (kMxKB / 2) + th * 16);
         uint8_t* dst = ring + S * L::kStageBytes + (t % kMxDecoded) * L::kBBytes;
+        const uint32_t sb = scb << 7;
+        const uint32_t s2 = sb | (sb << 16);
+        const uint32_t ws[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {               // 32 elements = one scale group each
-          const uint4 x = src[h];
-          const uint32_t sb = ((scb >> (8 * h)) & 0xffu) << 7;
-          const uint32_t s2 = sb | (sb << 16);
-          const uint32_t ws[4] = {x.x, x.y, x.z, x.w};
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint32_t o[4];
-            mx_decode8(ws[i], s2, o);
-            const int chunk = 4 * h + i;             // 8 elements = 16 bytes
-            *reinterpret_cast<uint4*>(dst + r * 128 + ((chunk ^ (r & 7)) << 4)) =
-                make_uint4(o[0], o[1], o[2], o[3]);
-          }
+        for (int i = 0; i < 4; ++i) {
+          uint32_t o[4];
+          mx_decode8(ws[i], s2, o);
+          const int chunk = 4 * th + i;              // 8 elements = 16 bytes
+          *reinterpret_cast<uint4*>(dst + r * 128 + ((chunk ^ (r & 7)) << 4)) =
+              make_uint4(o[0], o[1], o[2], o[3]);
         }
         fence_proxy_async();                          // generic-proxy stores -> the MMA's async proxy
         __syncwarp();
