@@ -32,8 +32,12 @@ namespace {
 
 constexpr uint32_t kMagic = 0x64646464u;   // high byte of fp16 1024 + x
 constexpr uint32_t kBias = 0x64806480u;    // f16x2 (1152, 1152)
-constexpr float kPScale = 32768.f;         // fp16 headroom for the V-scaled weights
-constexpr float kPScaleInv = 1.f / 32768.f;
+// The softmax reference of a warp is renewed only when a score exceeds it by more
+// than 2^kLazy: the weights then stay below 2^kLazy, and kPScale = 2^(15 - kLazy)
+// keeps the V-scaled fp16 weights in range.
+constexpr float kLazy = 4.f;
+constexpr float kPScale = 2048.f;
+constexpr float kPScaleInv = 1.f / 2048.f;
 
 // Bytes of one ring stage: 16 K rows, 16 V rows, 16 + 16 fp32 scales.
 constexpr int stage_bytes(int d) { return 2 * 16 * d + 128; }
@@ -156,34 +160,32 @@ __device__ __forceinline__ void compute_tile(const TileQ8<D>& t, WarpState<D>& s
   const float x0 = va ? s[0] * ksa : -INFINITY, x1 = va ? s[1] * ksa : -INFINITY;
   const float x2 = vb ? s[2] * ksb : -INFINITY, x3 = vb ? s[3] * ksb : -INFINITY;
   // The running reference is max(x + log2|v_scale|), not max(x): then the
-  // V-scaled weights p * |v_scale| are <= 1 whatever the scale's magnitude, and
+  // V-scaled weights p * |v_scale| are bounded whatever the scale's magnitude, and
   // kPScale lifts them into fp16's normal range (tiny weights of a 65k-key
   // softmax would otherwise land in fp16 subnormals). m, l and O all use the
   // same reference, so the split-KV merge formulas are unchanged. A stale scale
   // of a masked key may be anything (NaN included): it is replaced.
   const float lva = va ? fmaxf(fast_log2(fabsf(t.vs[0])), -100.f) : 0.f;
   const float lvb = vb ? fmaxf(fast_log2(fabsf(t.vs[1])), -100.f) : 0.f;
-  float mx0 = fmaxf(x0 + lva, x2 + lvb), mx1 = fmaxf(x1 + lva, x3 + lvb);
+  const float c0 = fmaxf(x0 + lva, x2 + lvb), c1 = fmaxf(x1 + lva, x3 + lvb);
+  // The reference is any upper bound minus at most kLazy, the same in the eight
+  // lanes that share a head: it is renewed (warp-wide maximum, accumulators
+  // rescaled) only when some score outgrew it by more than 2^kLazy - after the
+  // first tiles almost never, which saves the shuffles and the rescale test.
+  if (__any_sync(0xffffffffu, c0 > st.m[0] + kLazy || c1 > st.m[1] + kLazy)) {
+    float mx0 = c0, mx1 = c1;
 #pragma unroll
-  for (int o = 4; o < 32; o <<= 1) {
-    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
-    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
-  }
-  const float mn0 = fmaxf(st.m[0], mx0), mn1 = fmaxf(st.m[1], mx1);
-  const float r0 = mn0 == -INFINITY ? 0.f : mn0, r1 = mn1 == -INFINITY ? 0.f : mn1;
-  const float al0 = fast_exp2(st.m[0] - r0), al1 = fast_exp2(st.m[1] - r1);
-  st.m[0] = mn0;
-  st.m[1] = mn1;
-  const float p0 = fast_exp2(x0 - r0), p1 = fast_exp2(x1 - r1);
-  const float p2 = fast_exp2(x2 - r0), p3 = fast_exp2(x3 - r1);
-  st.l[0] = st.l[0] * al0 + (p0 + p2);
-  st.l[1] = st.l[1] * al1 + (p1 + p3);
-  const float vsa = va ? t.vs[0] * kPScale : 0.f, vsb = vb ? t.vs[1] * kPScale : 0.f;
-  const uint32_t b0 = movmatrix_trans(pack_f16x2(p0 * vsa, p1 * vsa));
-  const uint32_t b1 = movmatrix_trans(pack_f16x2(p2 * vsb, p3 * vsb));
-  // O^T[D, 8 heads] = alpha O^T + V^T P^T; the rescale is skipped while no lane's
-  // running reference moved (the common case after the first tiles).
-  if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {
+    for (int o = 4; o < 32; o <<= 1) {
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+    }
+    const float mn0 = fmaxf(st.m[0], mx0), mn1 = fmaxf(st.m[1], mx1);
+    const float al0 = mn0 == -INFINITY ? 1.f : fast_exp2(st.m[0] - mn0);
+    const float al1 = mn1 == -INFINITY ? 1.f : fast_exp2(st.m[1] - mn1);
+    st.m[0] = mn0;
+    st.m[1] = mn1;
+    st.l[0] *= al0;
+    st.l[1] *= al1;
 #pragma unroll
     for (int i = 0; i < D / 16; ++i) {
       st.acc[i][0] *= al0;
@@ -193,6 +195,14 @@ __device__ __forceinline__ void compute_tile(const TileQ8<D>& t, WarpState<D>& s
     }
     st.wsum[0] *= al0, st.wsum[1] *= al1, st.wsum[2] *= al0, st.wsum[3] *= al1;
   }
+  const float r0 = st.m[0] == -INFINITY ? 0.f : st.m[0], r1 = st.m[1] == -INFINITY ? 0.f : st.m[1];
+  const float p0 = fast_exp2(x0 - r0), p1 = fast_exp2(x1 - r1);
+  const float p2 = fast_exp2(x2 - r0), p3 = fast_exp2(x3 - r1);
+  st.l[0] += p0 + p2;
+  st.l[1] += p1 + p3;
+  const float vsa = va ? t.vs[0] * kPScale : 0.f, vsb = vb ? t.vs[1] * kPScale : 0.f;
+  const uint32_t b0 = movmatrix_trans(pack_f16x2(p0 * vsa, p1 * vsa));
+  const uint32_t b1 = movmatrix_trans(pack_f16x2(p2 * vsb, p3 * vsb));
   // The V bytes enter the MMA as fp16 1024 + (b + 128) - one byte permute per
   // register, no subtraction: V^T P^T then carries the offset 1152 x (sum of the
   // weights), and that sum comes out of one more MMA with an all-ones A operand
@@ -330,6 +340,10 @@ attn_decode_q8_kernel(const DecodeArgs a) {
   const int32_t* bt = a.bt + int64_t(n) * a.bt_stride;
   const int bs = a.block_size;
 
+  auto run_tile = [&](const TileQ8<D>& tile, int key0) {
+    compute_tile<D>(tile, st, qf, key0, k_begin, k_end, g);
+  };
+
   int my_blk = 0, nload = 0;
   // Returns the block id of this warp's nload-th tile; every 32 tiles each lane
   // fetches one entry ahead of use.
@@ -355,14 +369,14 @@ attn_decode_q8_kernel(const DecodeArgs a) {
         const int blk = next_block(t + wph);
         load_tile<D, ALIGNED>(tb, a, blk, ((t + wph) * 16) % bs, kvh, g, c);
       }
-      compute_tile<D>(ta, st, qf, t * 16, k_begin, k_end, g);
+      run_tile(ta, t * 16);
       t += wph;
       if (t >= t_end) break;
       if (t + wph < t_end) {
         const int blk = next_block(t + wph);
         load_tile<D, ALIGNED>(ta, a, blk, ((t + wph) * 16) % bs, kvh, g, c);
       }
-      compute_tile<D>(tb, st, qf, t * 16, k_begin, k_end, g);
+      run_tile(tb, t * 16);
       t += wph;
     }
   } else {
@@ -436,7 +450,7 @@ attn_decode_q8_kernel(const DecodeArgs a) {
       const float* scp = reinterpret_cast<const float*>(sp + 32 * D);
       tile.ks[0] = scp[g], tile.ks[1] = scp[g + 8];
       tile.vs[0] = scp[16 + g], tile.vs[1] = scp[24 + g];
-      compute_tile<D>(tile, st, qf, t * 16, k_begin, k_end, g);
+      run_tile(tile, t * 16);
       __syncwarp();
       stage = stage + 1 == STAGES ? 0 : stage + 1;
     }

@@ -698,21 +698,22 @@ __global__ void __launch_bounds__(kWideThreads, 1) moe_gemm_umma_wide_kernel(
         // (measured on the 4096-token gate-up GEMM: 32-column loads with scalar FMAs,
         // 198 us, beat 16-column loads with packed fma.f32x2, 224 us; with neither
         // folds nor epilogue the launch takes 147 us, without MMAs as well 118 us)
-        uint32_t r[2][32];
-        tmem_ld_32x32(src, r[0]);
+        uint32_t r[16];
 #pragma unroll
-        for (int ch = 0; ch < NC / 32; ++ch) {
+        for (int ch = 0; ch < NC / 16; ++ch) {
+          tmem_ld_32x16(src + ch * 16, r);
           tmem_ld_wait();
-          if (ch + 1 < NC / 32) tmem_ld_32x32(src + (ch + 1) * 32, r[(ch + 1) & 1]);
-          if (ch + 1 == NC / 32) {       // everything read: hand the accumulator back
+          if (ch + 1 == NC / 16) {       // everything read: hand the accumulator back
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&tempty_bar[b]);
           }
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            acc[ch * 32 + j] = fmaf(__uint_as_float(r[ch & 1][j]), f_even, acc[ch * 32 + j]);
-            acc[ch * 32 + j + 1] = fmaf(__uint_as_float(r[ch & 1][j + 1]), f_odd, acc[ch * 32 + j + 1]);
+          for (int j = 0; j < 16; j += 2) {
+            const float2 a2 = __ffma2_rn(make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])),
+                                         make_float2(f_even, f_odd),
+                                         make_float2(acc[ch * 16 + j], acc[ch * 16 + j + 1]));
+            acc[ch * 16 + j] = a2.x, acc[ch * 16 + j + 1] = a2.y;
           }
         }
       }
