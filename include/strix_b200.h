@@ -361,6 +361,18 @@ int strix_moe_align_pos(const int32_t* topk_ids, int32_t* sorted_ids, int32_t* e
                         int64_t experts, int64_t block_m, int64_t sorted_capacity,
                         int64_t expert_capacity, strix_stream_t stream);
 
+/* strix_moe_align_counts for large batches: with a scratch of
+ * strix_moe_align_scratch_bytes(numel, experts) bytes (4-byte aligned, contents
+ * irrelevant) the slots are walked once per pass by one CTA per 1024 slots instead
+ * of once per expert - two launches, the same output bit for bit. Falls back to the
+ * one-kernel form for up to 4096 slots, more than 1024 experts or scratch == NULL. */
+int64_t strix_moe_align_scratch_bytes(int64_t numel, int64_t experts);
+int strix_moe_align_scratch(const int32_t* topk_ids, int32_t* sorted_ids, int32_t* expert_ids,
+                            int32_t* num_post_padded, int32_t* slot_pos, int32_t* counts,
+                            void* scratch, int64_t scratch_bytes, int64_t numel, int64_t experts,
+                            int64_t block_m, int64_t sorted_capacity, int64_t expert_capacity,
+                            strix_stream_t stream);
+
 /* strix_moe_align_pos that also writes counts[e] = slots routed to expert e
  * (int32 [experts]; NULL to skip). With the destination rank as the "expert" and
  * block_m = 1 this is the dispatch plan of the expert-parallel path. */

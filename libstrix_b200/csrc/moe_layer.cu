@@ -14,7 +14,7 @@ namespace {
 struct Fp8LayerPlan {
   int64_t cap;                 // sorted rows (capacity of the padded id list)
   int64_t off_ids, off_wts, off_sorted, off_expert, off_post, off_pos;
-  int64_t off_xq, off_xs, off_act, off_aq, off_as, off_y, bytes;
+  int64_t off_xq, off_xs, off_act, off_aq, off_as, off_y, off_hist, hist_bytes, bytes;
 };
 
 int64_t up(int64_t x) { return (x + 255) / 256 * 256; }
@@ -35,6 +35,8 @@ Fp8LayerPlan plan_fp8(int64_t tokens, int64_t top_k, int64_t hidden, int64_t int
   p.off_act = take(p.cap * inter * 2);
   p.off_aq = take(p.cap * inter), p.off_as = take(p.cap * (inter / 128) * 4);
   p.off_y = take(slots * hidden * 2);
+  p.hist_bytes = strix_moe_align_scratch_bytes(slots, experts);
+  p.off_hist = take(p.hist_bytes);
   p.bytes = o;
   return p;
 }
@@ -90,8 +92,9 @@ static int fp8_layer_impl(
       return rc;
     ids = i32(p.off_ids), wts = f32(p.off_wts);
   }
-  if ((rc = strix_moe_align_pos(ids, i32(p.off_sorted), i32(p.off_expert), i32(p.off_post),
-                                i32(p.off_pos), slots, experts, block_m, p.cap, p.cap / block_m, stream)))
+  if ((rc = strix_moe_align_scratch(ids, i32(p.off_sorted), i32(p.off_expert), i32(p.off_post),
+                                    i32(p.off_pos), nullptr, ws + p.off_hist, p.hist_bytes, slots, experts,
+                                    block_m, p.cap, p.cap / block_m, stream)))
     return rc;
   // sorted activations: e4m3 rows [cap, hidden] + scales [cap, hidden / 128], or - for
   // a payload that arrives quantised - whole payload rows, scales behind the bytes
@@ -178,7 +181,7 @@ namespace {
 struct EpLayerPlan {
   int64_t rows, slots, cap;       // received rows (world * exchange capacity), their slots, sorted rows
   int64_t off_ids, off_wts, off_payload;                       // this rank's routing, FP8 payload
-  int64_t off_sorted, off_expert, off_post, off_pos, off_xs, off_act;   // MXFP4 receiving side
+  int64_t off_sorted, off_expert, off_post, off_pos, off_xs, off_act, off_hist, hist_bytes;   // MXFP4 receiving side
   int64_t off_inner, inner_bytes;                              // FP8 receiving side (plan_fp8)
   int64_t bytes;
 };
@@ -196,6 +199,8 @@ EpLayerPlan plan_ep(const strix_expert_weights& w, const strix_ep_exchange& ep, 
     p.off_sorted = take(p.cap * 4), p.off_expert = take((p.cap / block_m) * 4), p.off_post = take(4);
     p.off_pos = take(p.slots * 4);
     p.off_xs = take(p.cap * w.hidden * 2), p.off_act = take(p.cap * w.inter * 2);
+    p.hist_bytes = strix_moe_align_scratch_bytes(p.slots, w.experts);
+    p.off_hist = take(p.hist_bytes);
   } else {
     p.off_payload = take(ep.cap * ep.row_bytes);
     p.inner_bytes = plan_fp8(p.rows, ep.top_k, w.hidden, w.inter, w.experts, block_m).bytes;
@@ -279,9 +284,9 @@ extern "C" int strix_ep_moe_layer(void* out, const void* x, const float* logits,
                              ep->rows_per_source, ep->world, ep->cap, k, ep->epoch, spin_limit, stream)))
     return rc;
   if (w->kind == 0) {
-    if ((rc = strix_moe_align_pos(ep->ids, i32(p.off_sorted), i32(p.off_expert), i32(p.off_post),
-                                  i32(p.off_pos), p.slots, w->experts, block_m, p.cap, p.cap / block_m,
-                                  stream)))
+    if ((rc = strix_moe_align_scratch(ep->ids, i32(p.off_sorted), i32(p.off_expert), i32(p.off_post),
+                                      i32(p.off_pos), nullptr, ws + p.off_hist, p.hist_bytes, p.slots,
+                                      w->experts, block_m, p.cap, p.cap / block_m, stream)))
       return rc;
     if ((rc = strix_moe_permute_rows(recv, ws + p.off_xs, i32(p.off_pos), i32(p.off_sorted),
                                      i32(p.off_post), p.rows, p.cap, h * 2, k, ep->row_bytes, h * 2, stream)))

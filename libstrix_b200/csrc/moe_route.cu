@@ -167,6 +167,149 @@ __global__ void __launch_bounds__(kAlignThreads) moe_align_kernel(
   }
 }
 
+// ------------------------------------------------ the same, for many slots
+// moe_align_kernel lets every expert's CTA walk all the slots: fine up to a few
+// thousand, 67 us at 32,768. The two-level form walks them once per pass:
+//   hist   one CTA per chunk of 1024 consecutive slots counts its slots per expert
+//          into hist[chunk][expert] (global scratch from the caller);
+//   place  the same CTAs sum the columns of hist (the expert's total, and the slots
+//          of earlier chunks - which, in slot order, come first), scan the padded
+//          totals, rank their own slots (a warp owns 128 consecutive slots; ranks
+//          inside a warp from match masks, warps ordered through shared memory) and
+//          write sorted_ids / slot_pos; paddings, expert_ids and the tail are split
+//          over the CTAs.
+// Same output, bit for bit, as moe_align_kernel.
+constexpr int kChunkSlots = 1024, kPlaceThreads = 256, kPlaceWarps = 8, kPlaceMaxExperts = 1024;
+
+__global__ void __launch_bounds__(kPlaceThreads) moe_align_hist_kernel(
+    const int32_t* __restrict__ topk_ids, int32_t* __restrict__ hist, int numel, int experts) {
+  extern __shared__ int s_cnt[];
+  for (int i = threadIdx.x; i < experts; i += kPlaceThreads) s_cnt[i] = 0;
+  __syncthreads();
+  const int base = blockIdx.x * kChunkSlots;
+#pragma unroll
+  for (int j = 0; j < kChunkSlots / kPlaceThreads; ++j) {
+    const int i = base + j * kPlaceThreads + threadIdx.x;
+    const int id = i < numel ? topk_ids[i] : -1;
+    if (id >= 0 && id < experts) atomicAdd(&s_cnt[id], 1);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < experts; i += kPlaceThreads) hist[blockIdx.x * experts + i] = s_cnt[i];
+}
+
+__global__ void __launch_bounds__(kPlaceThreads) moe_align_place_kernel(
+    const int32_t* __restrict__ topk_ids, const int32_t* __restrict__ hist,
+    int32_t* __restrict__ sorted_ids, int32_t* __restrict__ expert_ids, int32_t* __restrict__ num_post,
+    int numel, int experts, int block_m, int cap, int cap_blocks, int chunks,
+    int32_t* __restrict__ slot_pos, int32_t* __restrict__ counts) {
+  extern __shared__ int s_dyn[];
+  int* s_tot = s_dyn;                       // [experts] slots of the expert
+  int* s_base = s_tot + experts;            // [experts] first sorted position of the expert
+  int* s_off = s_base + experts;            // [experts] its slots in earlier chunks
+  int* s_w = s_off + experts;               // [warps][experts] running rank within this chunk
+  __shared__ int s_scan[kPlaceWarps];
+  __shared__ int s_total;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, chunk = blockIdx.x;
+  for (int e = tid; e < experts; e += kPlaceThreads) {
+    int tot = 0, off = 0;
+    for (int c = 0; c < chunks; ++c) {
+      const int h = hist[c * experts + e];
+      tot += h;
+      off += c < chunk ? h : 0;
+    }
+    s_tot[e] = tot, s_off[e] = off;
+  }
+  for (int i = tid; i < kPlaceWarps * experts; i += kPlaceThreads) s_w[i] = 0;
+  __syncthreads();
+  // exclusive scan of the padded totals: thread t owns experts [t * per, t * per + per)
+  const int per = (experts + kPlaceThreads - 1) / kPlaceThreads;
+  int mine = 0;
+  for (int j = 0; j < per; ++j) {
+    const int e = tid * per + j;
+    if (e < experts) mine += (s_tot[e] + block_m - 1) / block_m * block_m;
+  }
+  int incl = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
+  }
+  if (lane == 31) s_scan[warp] = incl;
+  __syncthreads();
+  int before = 0;
+#pragma unroll
+  for (int w = 0; w < kPlaceWarps; ++w) before += w < warp ? s_scan[w] : 0;
+  if (tid == kPlaceThreads - 1) s_total = before + incl;
+  int run = before + incl - mine;
+  for (int j = 0; j < per; ++j) {
+    const int e = tid * per + j;
+    if (e < experts) {
+      s_base[e] = run;
+      run += (s_tot[e] + block_m - 1) / block_m * block_m;
+    }
+  }
+  // this warp's 128 slots: counts per expert, then the warps in slot order
+  const int w0 = chunk * kChunkSlots + warp * (kChunkSlots / kPlaceWarps);
+  int ids[kChunkSlots / kPlaceWarps / 32];
+#pragma unroll
+  for (int j = 0; j < kChunkSlots / kPlaceWarps / 32; ++j) {
+    const int i = w0 + j * 32 + lane;
+    const int id = i < numel ? topk_ids[i] : -1;
+    ids[j] = (id >= 0 && id < experts) ? id : -1;
+    if (ids[j] >= 0) atomicAdd(&s_w[warp * experts + ids[j]], 1);
+  }
+  __syncthreads();
+  for (int e = tid; e < experts; e += kPlaceThreads) {
+    int acc = 0;
+#pragma unroll
+    for (int w = 0; w < kPlaceWarps; ++w) {
+      const int t = s_w[w * experts + e];
+      s_w[w * experts + e] = acc;
+      acc += t;
+    }
+  }
+  __syncthreads();
+  const int total = s_total;
+  if (chunk < chunks) {
+#pragma unroll
+    for (int j = 0; j < kChunkSlots / kPlaceWarps / 32; ++j) {
+      const int i = w0 + j * 32 + lane;
+      const int id = ids[j];
+      // lanes without an expert get keys of their own, so that they match nobody
+      const unsigned peers = __match_any_sync(0xffffffffu, id >= 0 ? id : experts + lane);
+      if (id >= 0) {
+        const int rank = __popc(peers & ((1u << lane) - 1u));
+        const int pos = s_base[id] + s_off[id] + s_w[warp * experts + id] + rank;
+        if (pos < cap) sorted_ids[pos] = i;
+        if (slot_pos != nullptr) slot_pos[i] = pos < cap ? pos : -1;
+      } else if (slot_pos != nullptr && i < numel) {
+        slot_pos[i] = -1;
+      }
+      __syncwarp();
+      if (id >= 0 && (peers & ((1u << lane) - 1u)) == 0) s_w[warp * experts + id] += __popc(peers);
+      __syncwarp();
+    }
+  }
+  // paddings and block ids of the experts e = blockIdx.x, + gridDim.x, ...; the tail in slices
+  for (int e = blockIdx.x; e < experts; e += gridDim.x) {
+    const int count = s_tot[e], padded = (count + block_m - 1) / block_m * block_m, base = s_base[e];
+    if (counts != nullptr && tid == 0) counts[e] = count;
+    for (int i = tid; i < padded / block_m; i += kPlaceThreads)
+      if (base / block_m + i < cap_blocks) expert_ids[base / block_m + i] = e;
+    for (int i = count + tid; i < padded; i += kPlaceThreads)
+      if (base + i < cap) sorted_ids[base + i] = numel;
+  }
+  if (blockIdx.x == 0 && tid == 0) num_post[0] = total;
+  {
+    const int tail = cap - total, slice = (tail + int(gridDim.x) - 1) / int(gridDim.x);
+    const int lo = total + blockIdx.x * slice, hi = min(lo + slice, cap);
+    for (int i = lo + tid; i < hi; i += kPlaceThreads) sorted_ids[i] = numel;
+    const int b0 = total / block_m, btail = cap_blocks - b0, bslice = (btail + int(gridDim.x) - 1) / int(gridDim.x);
+    const int blo = b0 + blockIdx.x * bslice, bhi = min(blo + bslice, cap_blocks);
+    for (int i = blo + tid; i < bhi; i += kPlaceThreads) expert_ids[i] = -1;
+  }
+}
+
 // ------------------------------------------------------- activation quantisers
 // 16 lanes share one 128-element group (8 elements = 16 bytes each).
 // With `row_map` (the sorted ids of moe_align_block_size) output row r is the
@@ -487,6 +630,42 @@ extern "C" int strix_moe_align_counts(const int32_t* topk_ids, int32_t* sorted_i
       topk_ids, sorted_ids, expert_ids, num_post_padded, int(numel), int(experts), int(block_m),
       int(sorted_capacity), int(expert_capacity), slot_pos, counts);
   return launch_status("moe_align");
+}
+
+extern "C" int64_t strix_moe_align_scratch_bytes(int64_t numel, int64_t experts) {
+  if (numel < 0 || experts < 1) return -1;
+  return ((numel + kChunkSlots - 1) / kChunkSlots) * experts * int64_t(sizeof(int32_t));
+}
+
+extern "C" int strix_moe_align_scratch(const int32_t* topk_ids, int32_t* sorted_ids,
+                                       int32_t* expert_ids, int32_t* num_post_padded,
+                                       int32_t* slot_pos, int32_t* counts, void* scratch,
+                                       int64_t scratch_bytes, int64_t numel, int64_t experts,
+                                       int64_t block_m, int64_t sorted_capacity,
+                                       int64_t expert_capacity, strix_stream_t stream) {
+  // few slots, or more experts than the ranking tables hold: the one-kernel form
+  if (numel <= 4 * kChunkSlots || experts > kPlaceMaxExperts || scratch == nullptr)
+    return strix_moe_align_counts(topk_ids, sorted_ids, expert_ids, num_post_padded, slot_pos, counts,
+                                  numel, experts, block_m, sorted_capacity, expert_capacity, stream);
+  STRIX_CHECK(numel < (int64_t(1) << 30), "too many routed slots");
+  STRIX_CHECK(block_m >= 1 && block_m <= 1024, "block_m must be in 1..1024");
+  STRIX_CHECK(sorted_capacity >= strix_moe_align_capacity(numel, experts, block_m),
+              "sorted_ids too short: needs strix_moe_align_capacity() entries");
+  STRIX_CHECK(expert_capacity * block_m >= sorted_capacity,
+              "expert_ids too short for block_m %lld", (long long)block_m);
+  STRIX_CHECK(scratch_bytes >= strix_moe_align_scratch_bytes(numel, experts) &&
+                  reinterpret_cast<uintptr_t>(scratch) % 4 == 0, "scratch too small");
+  const int chunks = int((numel + kChunkSlots - 1) / kChunkSlots);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int32_t* hist = static_cast<int32_t*>(scratch);
+  moe_align_hist_kernel<<<unsigned(chunks), kPlaceThreads, size_t(experts) * sizeof(int), st>>>(
+      topk_ids, hist, int(numel), int(experts));
+  if (int rc = launch_status("moe_align_hist")) return rc;
+  const size_t smem = size_t(3 + kPlaceWarps) * size_t(experts) * sizeof(int);
+  moe_align_place_kernel<<<unsigned(chunks), kPlaceThreads, smem, st>>>(
+      topk_ids, hist, sorted_ids, expert_ids, num_post_padded, int(numel), int(experts), int(block_m),
+      int(sorted_capacity), int(expert_capacity), chunks, slot_pos, counts);
+  return launch_status("moe_align_place");
 }
 
 extern "C" int strix_moe_align(const int32_t* topk_ids, int32_t* sorted_ids, int32_t* expert_ids,

@@ -431,11 +431,21 @@ def moe_align_block_size_pos(topk_ids, num_experts, block_size, sorted_token_ids
                for t in (topk_ids, sorted_token_ids, experts_ids, num_tokens_post_pad, slot_pos)),
            "routing tensors must be contiguous int32")
     _check(slot_pos.numel() >= topk_ids.numel(), "slot_pos must have an entry per slot")
+    _align(topk_ids, num_experts, block_size, sorted_token_ids, experts_ids, num_tokens_post_pad, slot_pos)
+
+
+def _align(topk_ids, num_experts, block_size, sorted_token_ids, experts_ids, num_tokens_post_pad, slot_pos):
+    """The permutation, through the two-level kernels (and a scratch from torch's
+    caching allocator) where the batch is large enough for them to pay."""
+    n = topk_ids.numel()
+    nbytes = _lib.load().strix_moe_align_scratch_bytes(n, num_experts) if n > 4096 else 0
+    scratch = torch.empty(nbytes // 4, dtype=torch.int32, device=topk_ids.device) if nbytes > 0 else None
     with torch.cuda.device(topk_ids.device):
-        _lib.call("strix_moe_align_pos", topk_ids.data_ptr(), sorted_token_ids.data_ptr(),
-                  experts_ids.data_ptr(), num_tokens_post_pad.data_ptr(), slot_pos.data_ptr(),
-                  topk_ids.numel(), num_experts, block_size, sorted_token_ids.numel(),
-                  experts_ids.numel(), _stream())
+        _lib.call("strix_moe_align_scratch", topk_ids.data_ptr(), sorted_token_ids.data_ptr(),
+                  experts_ids.data_ptr(), num_tokens_post_pad.data_ptr(),
+                  None if slot_pos is None else slot_pos.data_ptr(), None,
+                  None if scratch is None else scratch.data_ptr(), nbytes, n, num_experts, block_size,
+                  sorted_token_ids.numel(), experts_ids.numel(), _stream())
 
 
 @_define("moe_act_quant_fp8_scatter(Tensor x, Tensor(a!) q, Tensor(b!) sa, Tensor slot_pos, "
@@ -531,10 +541,7 @@ def moe_align_block_size(topk_ids, num_experts, block_size, sorted_token_ids, ex
            and sorted_token_ids.dtype == torch.int32 and sorted_token_ids.is_contiguous()
            and experts_ids.dtype == torch.int32 and experts_ids.is_contiguous()
            and num_tokens_post_pad.dtype == torch.int32, "routing tensors must be int32")
-    with torch.cuda.device(topk_ids.device):
-        _lib.call("strix_moe_align", topk_ids.data_ptr(), sorted_token_ids.data_ptr(),
-                  experts_ids.data_ptr(), num_tokens_post_pad.data_ptr(), topk_ids.numel(),
-                  num_experts, block_size, sorted_token_ids.numel(), experts_ids.numel(), _stream())
+    _align(topk_ids, num_experts, block_size, sorted_token_ids, experts_ids, num_tokens_post_pad, None)
 
 
 @_define("moe_sum(Tensor input, Tensor(a!) output) -> ()")

@@ -89,6 +89,56 @@ def test_align_is_bit_exact(tokens, experts, top_k, block_m):
     assert bool((s.cpu()[total:] == ids.numel()).all()) and bool((e.cpu()[total // block_m:] == -1).all())
 
 
+@pytest.mark.parametrize("numel,experts,block_m", [(4097, 8, 16), (5000, 128, 128), (32768, 128, 128),
+                                                   (20001, 1000, 32), (9000, 3, 1), (6000, 2000, 16)])
+def test_two_level_align_equals_the_one_kernel_form(numel, experts, block_m):
+    """Above 4096 slots the permutation is built by two launches over a scratch
+    (one CTA per 1024 slots): every output - sorted ids, block experts, padded total,
+    inverse positions, counts - equals the one-kernel form and the oracle, with ids
+    that name no local expert (-1, >= experts) sprinkled in. More than 1024 experts
+    fall back to the one-kernel form inside the same call."""
+    from libstrix_b200 import _lib
+    lib = _lib.load()
+    g = torch.Generator().manual_seed(numel)
+    ids = torch.randint(0, experts, (numel,), generator=g, dtype=torch.int32)
+    ids[torch.rand(numel, generator=g) < 0.1] = -1
+    ids[torch.rand(numel, generator=g) < 0.05] = experts + 3
+    cap = lib.strix_moe_align_capacity(numel, experts, block_m)
+    d = ids.to(DEV)
+
+    def run(two_level):
+        out = dict(s=torch.full((cap,), -7, dtype=torch.int32, device=DEV),
+                   e=torch.full((cap // block_m,), -7, dtype=torch.int32, device=DEV),
+                   n=torch.full((1,), -7, dtype=torch.int32, device=DEV),
+                   pos=torch.full((numel,), -7, dtype=torch.int32, device=DEV),
+                   cnt=torch.full((experts,), -7, dtype=torch.int32, device=DEV))
+        nbytes = lib.strix_moe_align_scratch_bytes(numel, experts)
+        scratch = torch.full((nbytes // 4,), 0x7f7f7f7f, dtype=torch.int32, device=DEV)
+        if two_level:
+            _lib.call("strix_moe_align_scratch", d.data_ptr(), out["s"].data_ptr(), out["e"].data_ptr(),
+                      out["n"].data_ptr(), out["pos"].data_ptr(), out["cnt"].data_ptr(), scratch.data_ptr(),
+                      nbytes, numel, experts, block_m, cap, cap // block_m,
+                      torch.cuda.current_stream().cuda_stream)
+        else:
+            _lib.call("strix_moe_align_counts", d.data_ptr(), out["s"].data_ptr(), out["e"].data_ptr(),
+                      out["n"].data_ptr(), out["pos"].data_ptr(), out["cnt"].data_ptr(), numel, experts,
+                      block_m, cap, cap // block_m, torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        return {k: v.cpu() for k, v in out.items()}
+
+    a, b = run(True), run(False)
+    for k in a:
+        assert torch.equal(a[k], b[k]), k
+    s_ref, e_ref, n_ref = M.align(ids.view(-1, 1), block_m, experts)
+    total = int(n_ref)
+    assert int(a["n"]) == total and torch.equal(a["s"][:total], s_ref[:total])
+    assert torch.equal(a["e"][: total // block_m], e_ref[: total // block_m])
+    valid = (ids >= 0) & (ids < experts)
+    assert bool((a["pos"][~valid] == -1).all())
+    assert torch.equal(a["s"][a["pos"][valid].long()].long(), torch.arange(numel)[valid])
+    assert torch.equal(a["cnt"].long(), torch.bincount(ids[valid].long(), minlength=experts))
+
+
 def test_align_golden_and_foreign_ids():
     for c in torch.load(GOLDEN / "moe.pt")["align"]:
         s, e, n = strix.moe.align(c["topk_ids"].int().to(DEV), c["block_m"], c["experts"])
