@@ -364,6 +364,8 @@ def main() -> None:
     ap.add_argument("--gemm-m", type=int, nargs="*", default=[1, 16, 4096])
     ap.add_argument("--prefill-tokens", type=int, nargs="*", default=[2048, 65536])
     ap.add_argument("--ep-exchange", default="auto", choices=["auto", "peer", "nccl"])
+    ap.add_argument("--ep-placement", default="round_robin", choices=["round_robin", "contiguous"],
+                    help="which rank owns which expert in the expert-parallel sections")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -707,7 +709,10 @@ def bench_ep_moe(args, dev, rank: int, world: int, with_cpu: bool) -> dict:
     rank holds 8192 / N tokens and 128 / N experts. Weights N(0, 0.02) quantised to
     e2m1 with e8m0 scales per 32; router logits N(0,1) plus a Zipf(1.1) per-expert
     bias. Tokens move through this library's peer-memory exchange (or NCCL
-    all-to-all with --ep-exchange nccl). Strong scaling: the total work is fixed.
+    all-to-all with --ep-exchange nccl). Experts are placed round-robin (rank r
+    holds r, r + N, ...; --ep-placement contiguous for blocks): the Zipf bias falls
+    along the expert index, so blocks would give rank 0 all the hot experts - both
+    load ratios are reported. Strong scaling: the total work is fixed.
     Time = max over ranks of the CUDA-event time; TFLOP/s counts 2 x slots x
     (2I x H + H x I). Rank 0 checks a sample of its tokens against the CPU oracle
     (the experts they need are regenerated from their seeds). A second entry runs
@@ -720,14 +725,17 @@ def bench_ep_moe(args, dev, rank: int, world: int, with_cpu: bool) -> dict:
 
     tokens_total, hid, inter, experts, top_k = 8192, 2880, 2880, 128, 4
     t_local, e_local = tokens_total // world, experts // world
-    layer = moe_mxfp4_layer(tokens=tokens_total, hidden=hid, experts=experts, top_k=top_k, inter=inter,
-                            seed=0, device=dev, expert_lo=rank * e_local, expert_hi=(rank + 1) * e_local,
-                            token_lo=rank * t_local, token_hi=(rank + 1) * t_local)
     exchange = args.ep_exchange
+    placement = "contiguous" if world == 1 or exchange == "nccl" else args.ep_placement
+    mine = list(range(rank, experts, world)) if placement == "round_robin" else \
+        list(range(rank * e_local, (rank + 1) * e_local))
+    layer = moe_mxfp4_layer(tokens=tokens_total, hidden=hid, experts=experts, top_k=top_k, inter=inter,
+                            seed=0, device=dev, expert_list=mine,
+                            token_lo=rank * t_local, token_hi=(rank + 1) * t_local)
 
     def step():
         return ep.ep_moe_mxfp4(layer.x, layer.logits, layer.w13, layer.w13_scale, layer.w2,
-                               layer.w2_scale, top_k, exchange=exchange)
+                               layer.w2_scale, top_k, exchange=exchange, placement=placement)
 
     steps = max(2, min(args.steps, 10))
     for _ in range(3):
@@ -752,9 +760,13 @@ def bench_ep_moe(args, dev, rank: int, world: int, with_cpu: bool) -> dict:
     from libstrix_b200 import moe as smoe
 
     _, ids = smoe.route(layer.logits, top_k)
-    per_rank = torch.bincount((ids.reshape(-1) // e_local).long(), minlength=world).to(torch.float64)
+    flat = ids.reshape(-1).long()
+    per_rank_blocks = torch.bincount(flat // e_local, minlength=world).to(torch.float64)
+    per_rank_rr = torch.bincount(flat % world, minlength=world).to(torch.float64)
     if world > 1:
-        dist.all_reduce(per_rank, op=dist.ReduceOp.SUM)
+        dist.all_reduce(per_rank_blocks, op=dist.ReduceOp.SUM)
+        dist.all_reduce(per_rank_rr, op=dist.ReduceOp.SUM)
+    per_rank = per_rank_rr if placement == "round_robin" else per_rank_blocks
     res = {"config": "MXFP4 MoE, H=2880 E=128 top-4 I=2880, 8192 tokens, EP over ranks, Zipf(1.1) bias, "
                      "weights N(0,0.02) -> e2m1 / e8m0 per 32",
            "n_gpus": world, "scaling": "strong", "ms_per_layer": ms,
@@ -764,6 +776,8 @@ def bench_ep_moe(args, dev, rank: int, world: int, with_cpu: bool) -> dict:
                         "frac": flops / (ms * 1e-3) / 1e12 / world / measured_peaks()["bf16"],
                         "peak_kind": "measured bf16 (the kernel runs kind::f16 on decoded weights)"},
            "slots_per_rank_max_over_mean": (per_rank.max() / per_rank.mean()).item(),
+           "expert_placement": placement,
+           "slots_per_rank_max_over_mean_if_contiguous": (per_rank_blocks.max() / per_rank_blocks.mean()).item(),
            "exchange": ("none (one rank: the fused single-GPU layer)" if world == 1 and exchange == "auto"
                         else "NCCL all_to_all_single" if exchange == "nccl"
                         else "peer-memory kernels over NVLink (CUDA IPC), no host synchronisation"),
@@ -772,7 +786,7 @@ def bench_ep_moe(args, dev, rank: int, world: int, with_cpu: bool) -> dict:
         dist.barrier()
         res["phases_ms_rank0"] = _phase_times(lambda mark: ep.ep_moe_mxfp4(
             layer.x, layer.logits, layer.w13, layer.w13_scale, layer.w2, layer.w2_scale, top_k,
-            exchange=exchange, mark=mark))
+            exchange=exchange, mark=mark, placement=placement))
         res["ep_status"] = next(iter(ep._CONTEXTS.values())).status()
     # parity on rank 0: a sample of its tokens against the oracle over regenerated experts
     if with_cpu and rank == 0:
@@ -815,13 +829,16 @@ def _bench_ep_fp8(args, dev, rank: int, world: int, steps: int, with_cpu: bool) 
     layer = moe_fp8_layer(tokens=tokens_total, seed=10, device=dev)     # the same layer on every rank
     t_local, e_local = tokens_total // world, experts // world
     lo, t0 = rank * e_local, rank * t_local
-    w13, s13 = layer.w13[lo:lo + e_local].contiguous(), layer.w13_scale[lo:lo + e_local].contiguous()
-    w2, s2 = layer.w2[lo:lo + e_local].contiguous(), layer.w2_scale[lo:lo + e_local].contiguous()
+    placement = "contiguous" if world == 1 or args.ep_exchange == "nccl" else args.ep_placement
+    own = slice(rank, None, world) if placement == "round_robin" else slice(lo, lo + e_local)
+    w13, s13 = layer.w13[own].contiguous(), layer.w13_scale[own].contiguous()
+    w2, s2 = layer.w2[own].contiguous(), layer.w2_scale[own].contiguous()
     x, logits, top_k = layer.x[t0:t0 + t_local].contiguous(), layer.logits[t0:t0 + t_local].contiguous(), layer.top_k
     flops_total = layer.flops
 
     def step():
-        return ep.ep_moe_fp8(x, logits, w13, s13, w2, s2, top_k, exchange=args.ep_exchange)
+        return ep.ep_moe_fp8(x, logits, w13, s13, w2, s2, top_k, exchange=args.ep_exchange,
+                             placement=placement)
 
     for _ in range(3):
         step()
@@ -841,11 +858,12 @@ def _bench_ep_fp8(args, dev, rank: int, world: int, steps: int, with_cpu: bool) 
     ms = ms_t.item()
     res = {"config": "FP8 W8A8 MoE, H=2048 E=128 top-8 I=768, 4096 tokens, EP over ranks",
            "n_gpus": world, "scaling": "strong", "ms_per_layer": ms,
-           "tflops": flops_total / (ms * 1e-3) / 1e12, "tokens_per_s": tokens_total / (ms * 1e-3)}
+           "tflops": flops_total / (ms * 1e-3) / 1e12, "tokens_per_s": tokens_total / (ms * 1e-3),
+           "expert_placement": placement}
     if world > 1 and args.ep_exchange != "nccl":
         dist.barrier()
         res["phases_ms_rank0"] = _phase_times(lambda mark: ep.ep_moe_fp8(
-            x, logits, w13, s13, w2, s2, top_k, exchange=args.ep_exchange, mark=mark))
+            x, logits, w13, s13, w2, s2, top_k, exchange=args.ep_exchange, mark=mark, placement=placement))
     if with_cpu and rank == 0:
         cpu = layer.to("cpu")
         sample = torch.arange(0, t_local, max(1, t_local // 16))[:16]

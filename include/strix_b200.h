@@ -509,6 +509,9 @@ int strix_peer_free(void* ptr);
 int strix_peer_export(const void* ptr, void* handle64);
 int strix_peer_import(const void* handle64, void** ptr);
 int strix_peer_unimport(void* ptr);
+/* experts_per_rank > 0: rank r owns the experts [r * epr, (r + 1) * epr); < 0: round-robin
+ * placement, expert e lives on rank e mod world as local expert e / world (-epr experts per
+ * rank) - a load skewed along the expert index then spreads evenly over the ranks. */
 int strix_ep_status(int32_t* host_out, int reset);
 int strix_ep_plan(const int32_t* topk_ids, int32_t* tok_pos, int32_t* counts, int64_t tokens,
                   int64_t top_k, int64_t experts_per_rank, int64_t world, strix_stream_t stream);
@@ -555,6 +558,7 @@ typedef struct strix_expert_weights {
 
 typedef struct strix_ep_exchange {
   int64_t world, rank, cap, top_k, row_bytes, hidden, epoch;
+  int64_t round_robin;        /* 0: contiguous expert blocks per rank, 1: expert e on rank e mod world */
   void* const* peer_recv;     /* host arrays of `world` device addresses, own rank included */
   void* const* peer_meta;
   void* const* peer_counts;

@@ -74,6 +74,16 @@ __device__ __forceinline__ bool wait_epoch(const int32_t* flag, int32_t epoch, u
   return false;
 }
 
+// Which rank owns global expert e, and under which local index. experts_per_rank > 0:
+// contiguous blocks (rank r owns [r * epr, (r + 1) * epr)); < 0: round-robin (expert e
+// lives on rank e mod world as local expert e / world, -epr experts per rank), which
+// spreads a load that is skewed along the expert index evenly over the ranks.
+__device__ __forceinline__ int ep_owner(int e, int epr, int world) {
+  if (epr > 0) return e >= 0 ? e / epr : -1;
+  return (e >= 0 && e < -epr * world) ? e % world : -1;
+}
+__device__ __forceinline__ int ep_local(int e, int epr, int world) { return epr > 0 ? e % epr : e / world; }
+
 // One CTA per destination rank: tok_pos[d][t] = index of token t among this
 // rank's tokens with a slot on rank d (token order), or -1; counts[d].
 __global__ void __launch_bounds__(256) ep_plan_kernel(const int32_t* __restrict__ topk_ids,
@@ -89,7 +99,7 @@ __global__ void __launch_bounds__(256) ep_plan_kernel(const int32_t* __restrict_
     if (t < tokens)
       for (int j = 0; j < top_k; ++j) {
         const int e = topk_ids[t * top_k + j];
-        hit = hit || (e >= 0 && e / experts_per_rank == d);
+        hit = hit || ep_owner(e, experts_per_rank, world) == d;
       }
     const unsigned bal = __ballot_sync(0xffffffffu, hit);
     __syncthreads();
@@ -107,7 +117,6 @@ __global__ void __launch_bounds__(256) ep_plan_kernel(const int32_t* __restrict_
     placed += total;
   }
   if (tid == 0) counts[d] = placed;
-  (void)world;
 }
 
 // Raises this grid's flags once every CTA has passed: a CTA's stores are ordered
@@ -158,8 +167,8 @@ __global__ void __launch_bounds__(kEpWarps * 32) ep_dispatch_kernel(
         } else {
           const int j = lane - 1;
           const int e = topk_ids[t * top_k + j];
-          const bool here = e >= 0 && e / experts_per_rank == d;
-          m[1 + 2 * j] = here ? e % experts_per_rank : -1;
+          const bool here = ep_owner(e, experts_per_rank, world) == d;
+          m[1 + 2 * j] = here ? ep_local(e, experts_per_rank, world) : -1;
           m[2 + 2 * j] = __float_as_int(topk_w[t * top_k + j]);
         }
       }
@@ -394,7 +403,7 @@ extern "C" int strix_ep_plan(const int32_t* topk_ids, int32_t* tok_pos, int32_t*
                              int64_t top_k, int64_t experts_per_rank, int64_t world, strix_stream_t stream) {
   STRIX_CHECK(counts != nullptr && (tokens == 0 || (topk_ids != nullptr && tok_pos != nullptr)),
               "pointers must not be NULL");
-  STRIX_CHECK(tokens >= 0 && top_k >= 1 && experts_per_rank >= 1 && world >= 1 && world <= kEpMaxWorld,
+  STRIX_CHECK(tokens >= 0 && top_k >= 1 && experts_per_rank != 0 && world >= 1 && world <= kEpMaxWorld,
               "bad sizes");
   ep_plan_kernel<<<unsigned(world), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       topk_ids, tok_pos, counts, int(tokens), int(top_k), int(experts_per_rank), int(world));

@@ -253,6 +253,7 @@ extern "C" int strix_ep_moe_layer(void* out, const void* x, const float* logits,
   auto i32 = [&](int64_t off) { return reinterpret_cast<int32_t*>(ws + off); };
   auto f32 = [&](int64_t off) { return reinterpret_cast<float*>(ws + off); };
   const int64_t k = ep->top_k, h = w->hidden, inter = w->inter;
+  const int64_t epr = ep->round_robin ? -w->experts : w->experts;   // how experts map to ranks
   int rc;
   // ---- this rank's tokens: route, (quantise,) send
   const void* payload = x;
@@ -269,11 +270,11 @@ extern "C" int strix_ep_moe_layer(void* out, const void* x, const float* logits,
       payload = q, payload_stride = ep->row_bytes;
     }
   }
-  if ((rc = strix_ep_plan(i32(p.off_ids), ep->tok_pos, ep->counts, tokens, k, w->experts, ep->world, stream)))
+  if ((rc = strix_ep_plan(i32(p.off_ids), ep->tok_pos, ep->counts, tokens, k, epr, ep->world, stream)))
     return rc;
   if ((rc = strix_ep_dispatch(payload, i32(p.off_ids), f32(p.off_wts), ep->tok_pos, ep->counts,
                               ep->peer_recv, ep->peer_meta, ep->peer_counts, ep->peer_flags, ep->ticket,
-                              tokens, ep->row_bytes, payload_stride, k, w->experts, ep->world, ep->rank,
+                              tokens, ep->row_bytes, payload_stride, k, epr, ep->world, ep->rank,
                               ep->cap, ep->epoch, stream)))
     return rc;
   // ---- the rows other ranks sent here: through this rank's experts

@@ -263,7 +263,7 @@ class _ExpertWeights(ctypes.Structure):
 class _Exchange(ctypes.Structure):
     """strix_ep_exchange of the header."""
     _fields_ = [(n, ctypes.c_int64) for n in ("world", "rank", "cap", "top_k", "row_bytes", "hidden",
-                                              "epoch")] + \
+                                              "epoch", "round_robin")] + \
                [("peer_" + n, ctypes.POINTER(ctypes.c_void_p)) for n in _BUFFERS] + \
                [(n, ctypes.c_void_p) for n in ("ticket", "ids", "weights", "rows_per_source", "y", "tok_pos",
                                                "counts")]
@@ -374,7 +374,8 @@ class EpContext:
     def dispatch(self, payload: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
                  experts_per_rank: int, mark=_no_mark):
         """payload [T, row_bytes worth of elements] (last dim contiguous) goes to every
-        rank that owns one of the token's experts. `mark(name)` is called after each
+        rank that owns one of the token's experts (experts_per_rank < 0: round-robin
+        placement, expert e on rank e mod world). `mark(name)` is called after each
         kernel is enqueued (a hook for per-phase timing)."""
         t, k = topk_ids.shape
         assert k == self.top_k and t <= self.cap
@@ -432,7 +433,7 @@ class EpContext:
         return out
 
     def layer(self, x, logits, w13, w13_scale, w2, w2_scale, kind: int, block_m: int,
-              out: torch.Tensor | None = None, spin_limit: int = 0) -> torch.Tensor:
+              out: torch.Tensor | None = None, spin_limit: int = 0, round_robin: bool = False) -> torch.Tensor:
         """One expert-parallel layer as ONE call into the library (strix_ep_moe_layer):
         router, payload, dispatch, this rank's experts over what it receives, return
         and combine. kind 0 MXFP4 experts over bf16 rows, 1 / 2 FP8 W8A8 experts
@@ -446,7 +447,7 @@ class EpContext:
             out = torch.empty(t, h, dtype=torch.bfloat16, device=self.device)
         keep = {n: self._ptrs(n) for n in _BUFFERS}        # host arrays the struct points into
         ex = _Exchange(self.world, self.rank, self.cap, self.top_k, self.row_bytes, self.hidden, self.epoch,
-                       *[ctypes.cast(keep[n], ctypes.POINTER(ctypes.c_void_p)) for n in _BUFFERS],
+                       int(round_robin), *[ctypes.cast(keep[n], ctypes.POINTER(ctypes.c_void_p)) for n in _BUFFERS],
                        self.ticket.data_ptr(), self.ids.data_ptr(), self.weights.data_ptr(),
                        self.rows_per_source.data_ptr(), self.y.data_ptr(), self.tok_pos.data_ptr(),
                        self.counts.data_ptr())
@@ -595,16 +596,20 @@ def fp8_payload(x: torch.Tensor, buf: torch.Tensor | None = None):
 
 
 def ep_moe_fp8(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, block_m=None,
-               exchange="auto", ctx=None, mark=_no_mark):
+               exchange="auto", ctx=None, mark=_no_mark, placement="contiguous"):
     """One expert-parallel FP8 W8A8 block-scaled MoE layer. x bf16 [T_local, H];
     logits fp32 [T_local, E_global]; the weight tensors hold this rank's E_global /
     world experts. Returns bf16 [T_local, H]. exchange: "peer" (this library's
     kernels over peer memory), "nccl" (all_to_all_single) or "auto" (peer on CUDA;
     a single rank runs the fused single-GPU layer, which is the same computation
-    without an exchange)."""
+    without an exchange). placement: which rank owns which expert - "contiguous"
+    (rank r holds the experts [r E/N, (r + 1) E/N)) or "round_robin" (rank r holds r,
+    r + N, r + 2N, ...: its local expert i is global expert i N + r), which balances
+    a load that is skewed along the expert index; peer exchange only."""
     from . import moe as _moe
 
     world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rr = _round_robin(placement, exchange, x)
     t, h = x.shape
     if world == 1 and exchange == "auto" and ctx is None:
         return _moe.fused_moe_fp8_w8a8(x, logits, w13, w13_scale, w2, w2_scale, top_k, block_m=block_m)
@@ -628,13 +633,13 @@ def ep_moe_fp8(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, block
         raise RuntimeError("ep_moe_fp8: geometry not covered by the sorted-layout kernel")
     if mark is _no_mark and _one_call_ok(x, logits, w13_scale, w2_scale):
         block = w13_scale.dim() == 3 and w13_scale.size(1) != w13.size(1)
-        return ctx.layer(x, logits, w13, w13_scale, w2, w2_scale, 2 if block else 1, bm)
+        return ctx.layer(x, logits, w13, w13_scale, w2, w2_scale, 2 if block else 1, bm, round_robin=rr)
     weights, ids = _moe.route(logits, top_k)
     mark("route")
     payload, _, _ = fp8_payload(x, getattr(ctx, "_payload", None))
     ctx._payload = payload          # the padding bytes were zeroed once, at allocation
     mark("quantise")
-    ctx.dispatch(payload, weights, ids, e_local, mark)
+    ctx.dispatch(payload, weights, ids, -e_local if rr else e_local, mark)
     y = _experts_fp8_on_received(ctx, w13, w13_scale, w2, w2_scale, bm, mark)
     ctx.send_back(y)
     mark("return")
@@ -644,15 +649,17 @@ def ep_moe_fp8(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, block
 
 
 def ep_moe_mxfp4(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, block_m=None,
-                 exchange="auto", ctx=None, mark=_no_mark):
+                 exchange="auto", ctx=None, mark=_no_mark, placement="contiguous"):
     """One expert-parallel MXFP4 MoE layer. x bf16 [T_local, H]; logits fp32
     [T_local, E_global]; the weight tensors hold this rank's E_global / world
     experts. Router and combine run on this rank's tokens, the experts where
-    they live. Returns bf16 [T_local, H]. `exchange` as in ep_moe_fp8."""
+    they live. Returns bf16 [T_local, H]. `exchange` and `placement` as in
+    ep_moe_fp8."""
     from . import _lib
     from . import moe as _moe
 
     world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rr = _round_robin(placement, exchange, x)
     t, h = x.shape
     lib = _lib.load()
     wide_ok = bool(lib.strix_moe_gemm_mxfp4_sorted_covers(w13.size(1), w13.size(2) * 2, 128, 1)
@@ -663,7 +670,7 @@ def ep_moe_mxfp4(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, blo
     if peer and mark is _no_mark and _one_call_ok(x, logits, w13_scale, w2_scale):
         if ctx is None:
             ctx = context_for(group, t, top_k, h * 2, h, x.device)
-        return ctx.layer(x, logits, w13, w13_scale, w2, w2_scale, 0, 128)
+        return ctx.layer(x, logits, w13, w13_scale, w2, w2_scale, 0, 128, round_robin=rr)
     weights, ids = _moe.route(logits, top_k)
     if not peer:
         def combine(slots):
@@ -677,13 +684,21 @@ def ep_moe_mxfp4(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, blo
     if ctx is None:
         ctx = context_for(group, t, top_k, h * 2, h, x.device)
     mark("route")
-    ctx.dispatch(x, weights, ids, w13.size(0), mark)
+    ctx.dispatch(x, weights, ids, -w13.size(0) if rr else w13.size(0), mark)
     y = _experts_mxfp4_on_received(ctx, w13, w13_scale, w2, w2_scale, mark)
     ctx.send_back(y)
     mark("return")
     out = ctx.combine()
     mark("combine_wait")
     return out
+
+
+def _round_robin(placement: str, exchange: str, x) -> bool:
+    if placement not in ("contiguous", "round_robin"):
+        raise ValueError(f"placement must be 'contiguous' or 'round_robin', got {placement!r}")
+    if placement == "round_robin" and (exchange == "nccl" or not x.is_cuda):
+        raise ValueError("round_robin placement needs the peer-memory exchange")
+    return placement == "round_robin"
 
 
 def _one_call_ok(x, logits, w13_scale, w2_scale) -> bool:

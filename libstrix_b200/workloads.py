@@ -220,12 +220,14 @@ class MoeMxfp4Layer:
 
 def moe_mxfp4_layer(tokens=8192, hidden=2880, experts=128, top_k=4, inter=2880, seed=0,
                     device="cpu", expert_lo=0, expert_hi=None, token_lo=0, token_hi=None,
-                    zipf_alpha: float | None = 1.1) -> MoeMxfp4Layer:
+                    zipf_alpha: float | None = 1.1, expert_list=None) -> MoeMxfp4Layer:
     """Config 5: x bf16 ~ N(0,1); router logits N(0,1) plus a Zipf(1.1) per-expert
     bias; weights N(0, 0.02) quantised to MXFP4 (quantize_mxfp4). Every expert
     and every token block has its own generator seed, so a rank can build only
     its experts [expert_lo, expert_hi) and tokens [token_lo, token_hi) and still
-    hold exactly the slices of the one global layer (token blocks of 256)."""
+    hold exactly the slices of the one global layer (token blocks of 256).
+    `expert_list` names the global experts to build instead of a range (a rank of a
+    round-robin placement holds rank, rank + N, ...)."""
     expert_hi = experts if expert_hi is None else expert_hi
     token_hi = tokens if token_hi is None else token_hi
     assert token_lo % 256 == 0 and (token_hi % 256 == 0 or token_hi == tokens)
@@ -236,12 +238,13 @@ def moe_mxfp4_layer(tokens=8192, hidden=2880, experts=128, top_k=4, inter=2880, 
         n = min(256, tokens - t0)
         xs.append(torch.randn(n, hidden, generator=g, device=device).bfloat16())
         ls.append(torch.randn(n, experts, generator=g, device=device) + bias)
-    e_n = expert_hi - expert_lo
+    which = list(range(expert_lo, expert_hi)) if expert_list is None else list(expert_list)
+    e_n = len(which)
     w13 = torch.empty(e_n, 2 * inter, hidden // 2, dtype=torch.uint8, device=device)
     s13 = torch.empty(e_n, 2 * inter, hidden // 32, dtype=torch.uint8, device=device)
     w2 = torch.empty(e_n, hidden, inter // 2, dtype=torch.uint8, device=device)
     s2 = torch.empty(e_n, hidden, inter // 32, dtype=torch.uint8, device=device)
-    for i, e in enumerate(range(expert_lo, expert_hi)):
+    for i, e in enumerate(which):
         g = torch.Generator(device=device).manual_seed(seed * 1_000_003 + 1_000 + e)
         w13[i], s13[i] = quantize_mxfp4(torch.randn(2 * inter, hidden, generator=g, device=device) * 0.02)
         w2[i], s2[i] = quantize_mxfp4(torch.randn(hidden, inter, generator=g, device=device) * 0.02)

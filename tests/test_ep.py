@@ -208,13 +208,15 @@ def _bound_ok(out, ref):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("placement", ["contiguous", "round_robin"])
 @pytest.mark.parametrize("kind", ["mxfp4", "fp8"])
 @pytest.mark.parametrize("tokens_per_rank", [[70, 0, 33, 128], [1, 1, 1, 1]])
-def test_peer_exchange_with_emulated_ranks(kind, tokens_per_rank):
+def test_peer_exchange_with_emulated_ranks(kind, tokens_per_rank, placement):
     """Four ranks emulated in one process on one GPU (the phases of all ranks run in
     lockstep, so no kernel ever waits for one that has not been launched): plan,
     dispatch, receive, local experts, return and combine against the CPU oracle of
-    the unsharded layer."""
+    the unsharded layer, with the experts in contiguous blocks per rank or placed
+    round-robin (expert e on rank e mod 4)."""
     from libstrix_b200 import ep
     from libstrix_b200 import moe as smoe
     from libstrix_b200.workloads import moe_fp8_layer, moe_mxfp4_layer
@@ -223,6 +225,7 @@ def test_peer_exchange_with_emulated_ranks(kind, tokens_per_rank):
     dev = torch.device("cuda", 0)
     world, e_global, k, hid, inter = 4, 8, 2, 256, 128
     per = e_global // world
+    rr = placement == "round_robin"
     total = sum(tokens_per_rank)
     if kind == "mxfp4":
         layer = moe_mxfp4_layer(tokens=256, hidden=hid, experts=e_global, top_k=k, inter=inter, seed=3)
@@ -243,11 +246,12 @@ def test_peer_exchange_with_emulated_ranks(kind, tokens_per_rank):
                 x, logits = g.x[offs[r]:offs[r + 1]], g.logits[offs[r]:offs[r + 1]]
                 weights, ids = smoe.route(logits, k)
                 payload = x if kind == "mxfp4" else ep.fp8_payload(x)[0]
-                ctx.dispatch(payload, weights, ids, per)
+                ctx.dispatch(payload, weights, ids, -per if rr else per)
             for r, ctx in enumerate(ctxs):
-                sl = slice(r * per, (r + 1) * per)
+                sl = slice(r, None, world) if rr else slice(r * per, (r + 1) * per)
                 if kind == "mxfp4":
-                    y = ep._experts_mxfp4_on_received(ctx, g.w13[sl], g.w13_scale[sl], g.w2[sl], g.w2_scale[sl])
+                    y = ep._experts_mxfp4_on_received(ctx, g.w13[sl].contiguous(), g.w13_scale[sl].contiguous(),
+                                                      g.w2[sl].contiguous(), g.w2_scale[sl].contiguous())
                 else:
                     y = ep._experts_fp8_on_received(ctx, g.w13[sl].contiguous(), g.w13_scale[sl].contiguous(),
                                                     g.w2[sl].contiguous(), g.w2_scale[sl].contiguous(), 128)
@@ -259,7 +263,7 @@ def test_peer_exchange_with_emulated_ranks(kind, tokens_per_rank):
             got = torch.stack([c.rows_per_source for c in ctxs]).cpu()       # [dest, src]
             ids_all, _ = M.router(layer.logits[:total], k)
             for r in range(world):
-                mine = ids_all[offs[r]:offs[r + 1]] // per
+                mine = ids_all[offs[r]:offs[r + 1]] % world if rr else ids_all[offs[r]:offs[r + 1]] // per
                 for d in range(world):
                     assert int(got[d, r]) == int((mine == d).any(-1).sum())
             for r in range(world):
