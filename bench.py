@@ -364,7 +364,7 @@ def main() -> None:
     ap.add_argument("--gemm-m", type=int, nargs="*", default=[1, 16, 4096])
     ap.add_argument("--prefill-tokens", type=int, nargs="*", default=[2048, 65536])
     ap.add_argument("--ep-exchange", default="auto", choices=["auto", "peer", "nccl"])
-    ap.add_argument("--ep-placement", default="round_robin", choices=["round_robin", "contiguous"],
+    ap.add_argument("--ep-placement", default="balanced", choices=["balanced", "round_robin", "contiguous"],
                     help="which rank owns which expert in the expert-parallel sections")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -709,10 +709,14 @@ def bench_ep_moe(args, dev, rank: int, world: int, with_cpu: bool) -> dict:
     rank holds 8192 / N tokens and 128 / N experts. Weights N(0, 0.02) quantised to
     e2m1 with e8m0 scales per 32; router logits N(0,1) plus a Zipf(1.1) per-expert
     bias. Tokens move through this library's peer-memory exchange (or NCCL
-    all-to-all with --ep-exchange nccl). Experts are placed round-robin (rank r
-    holds r, r + N, ...; --ep-placement contiguous for blocks): the Zipf bias falls
-    along the expert index, so blocks would give rank 0 all the hot experts - both
-    load ratios are reported. Strong scaling: the total work is fixed.
+    all-to-all with --ep-exchange nccl). Expert placement (--ep-placement): the Zipf
+    bias makes one expert draw 22 % of all slots, more than a rank's share from 8
+    ranks on, so the default is `balanced`: a placement table computed from the
+    router's load on a seeded calibration batch (not the timed tokens), one spare
+    expert slot per rank, the spare slots holding copies of the hottest experts whose
+    tokens are spread over the copies. `contiguous` (blocks) and `round_robin` have
+    no copies; the load ratios of all three are reported. Strong scaling: the total
+    work is fixed.
     Time = max over ranks of the CUDA-event time; TFLOP/s counts 2 x slots x
     (2I x H + H x I). Rank 0 checks a sample of its tokens against the CPU oracle
     (the experts they need are regenerated from their seeds). A second entry runs
@@ -727,15 +731,26 @@ def bench_ep_moe(args, dev, rank: int, world: int, with_cpu: bool) -> dict:
     t_local, e_local = tokens_total // world, experts // world
     exchange = args.ep_exchange
     placement = "contiguous" if world == 1 or exchange == "nccl" else args.ep_placement
-    mine = list(range(rank, experts, world)) if placement == "round_robin" else \
-        list(range(rank * e_local, (rank + 1) * e_local))
+    place = placement
+    if placement == "balanced":
+        # expected load per expert: the router over a calibration batch of the same distribution
+        from libstrix_b200.workloads import zipf_bias
+        g = torch.Generator().manual_seed(4242)
+        cal = (torch.randn(8192, experts, generator=g) + zipf_bias(experts, 1.1)).to(dev)
+        from libstrix_b200 import moe as smoe_cal
+        loads = torch.bincount(smoe_cal.route(cal, top_k)[1].flatten().long(), minlength=experts).tolist()
+        place = ep.Placement.balanced(loads, world, slots_per_rank=e_local + 1)
+        mine = place.ranks[rank]
+    else:
+        mine = list(range(rank, experts, world)) if placement == "round_robin" else \
+            list(range(rank * e_local, (rank + 1) * e_local))
     layer = moe_mxfp4_layer(tokens=tokens_total, hidden=hid, experts=experts, top_k=top_k, inter=inter,
                             seed=0, device=dev, expert_list=mine,
                             token_lo=rank * t_local, token_hi=(rank + 1) * t_local)
 
     def step():
         return ep.ep_moe_mxfp4(layer.x, layer.logits, layer.w13, layer.w13_scale, layer.w2,
-                               layer.w2_scale, top_k, exchange=exchange, placement=placement)
+                               layer.w2_scale, top_k, exchange=exchange, placement=place)
 
     steps = max(2, min(args.steps, 10))
     for _ in range(3):
@@ -767,6 +782,10 @@ def bench_ep_moe(args, dev, rank: int, world: int, with_cpu: bool) -> dict:
         dist.all_reduce(per_rank_blocks, op=dist.ReduceOp.SUM)
         dist.all_reduce(per_rank_rr, op=dist.ReduceOp.SUM)
     per_rank = per_rank_rr if placement == "round_robin" else per_rank_blocks
+    if placement == "balanced":
+        per_rank = torch.bincount(place.rank_of(ids).reshape(-1).long(), minlength=world).to(torch.float64)
+        if world > 1:
+            dist.all_reduce(per_rank, op=dist.ReduceOp.SUM)
     res = {"config": "MXFP4 MoE, H=2880 E=128 top-4 I=2880, 8192 tokens, EP over ranks, Zipf(1.1) bias, "
                      "weights N(0,0.02) -> e2m1 / e8m0 per 32",
            "n_gpus": world, "scaling": "strong", "ms_per_layer": ms,
@@ -778,6 +797,8 @@ def bench_ep_moe(args, dev, rank: int, world: int, with_cpu: bool) -> dict:
            "slots_per_rank_max_over_mean": (per_rank.max() / per_rank.mean()).item(),
            "expert_placement": placement,
            "slots_per_rank_max_over_mean_if_contiguous": (per_rank_blocks.max() / per_rank_blocks.mean()).item(),
+           "slots_per_rank_max_over_mean_if_round_robin": (per_rank_rr.max() / per_rank_rr.mean()).item(),
+           "experts_held_per_rank": len(mine),
            "exchange": ("none (one rank: the fused single-GPU layer)" if world == 1 and exchange == "auto"
                         else "NCCL all_to_all_single" if exchange == "nccl"
                         else "peer-memory kernels over NVLink (CUDA IPC), no host synchronisation"),
@@ -786,7 +807,7 @@ def bench_ep_moe(args, dev, rank: int, world: int, with_cpu: bool) -> dict:
         dist.barrier()
         res["phases_ms_rank0"] = _phase_times(lambda mark: ep.ep_moe_mxfp4(
             layer.x, layer.logits, layer.w13, layer.w13_scale, layer.w2, layer.w2_scale, top_k,
-            exchange=exchange, mark=mark, placement=placement))
+            exchange=exchange, mark=mark, placement=place))
         res["ep_status"] = next(iter(ep._CONTEXTS.values())).status()
     # parity on rank 0: a sample of its tokens against the oracle over regenerated experts
     if with_cpu and rank == 0:
@@ -830,6 +851,7 @@ def _bench_ep_fp8(args, dev, rank: int, world: int, steps: int, with_cpu: bool) 
     t_local, e_local = tokens_total // world, experts // world
     lo, t0 = rank * e_local, rank * t_local
     placement = "contiguous" if world == 1 or args.ep_exchange == "nccl" else args.ep_placement
+    placement = "contiguous" if placement == "balanced" else placement   # this router has no bias
     own = slice(rank, None, world) if placement == "round_robin" else slice(lo, lo + e_local)
     w13, s13 = layer.w13[own].contiguous(), layer.w13_scale[own].contiguous()
     w2, s2 = layer.w2[own].contiguous(), layer.w2_scale[own].contiguous()

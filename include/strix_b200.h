@@ -511,16 +511,20 @@ int strix_peer_import(const void* handle64, void** ptr);
 int strix_peer_unimport(void* ptr);
 /* experts_per_rank > 0: rank r owns the experts [r * epr, (r + 1) * epr); < 0: round-robin
  * placement, expert e lives on rank e mod world as local expert e / world (-epr experts per
- * rank) - a load skewed along the expert index then spreads evenly over the ranks. */
+ * rank). `placement` (device memory, NULL for the two arithmetic forms) is a table
+ * instead: int32 {global experts, row stride, then per expert a row {copies, rank << 16 |
+ * local id, ... (copies entries)}}; an expert with several copies - a hot expert replicated
+ * so that the ranks' loads balance - serves token t from copy t mod copies. */
 int strix_ep_status(int32_t* host_out, int reset);
 int strix_ep_plan(const int32_t* topk_ids, int32_t* tok_pos, int32_t* counts, int64_t tokens,
-                  int64_t top_k, int64_t experts_per_rank, int64_t world, strix_stream_t stream);
+                  int64_t top_k, int64_t experts_per_rank, int64_t world, const int32_t* placement,
+                  strix_stream_t stream);
 int strix_ep_dispatch(const void* x, const int32_t* topk_ids, const float* topk_weights,
                       const int32_t* tok_pos, const int32_t* counts, void* const* peer_recv,
                       void* const* peer_meta, void* const* peer_counts, void* const* peer_flags,
                       int32_t* ticket, int64_t tokens, int64_t row_bytes, int64_t x_stride_bytes,
                       int64_t top_k, int64_t experts_per_rank, int64_t world, int64_t rank,
-                      int64_t cap, int64_t epoch, strix_stream_t stream);
+                      int64_t cap, int64_t epoch, const int32_t* placement, strix_stream_t stream);
 int strix_ep_prepare(const int32_t* meta, const int32_t* counts, const int32_t* flags,
                      int32_t* ids, float* weights, int32_t* rows_per_source, int64_t world,
                      int64_t cap, int64_t top_k, int64_t epoch, int64_t spin_limit,
@@ -559,6 +563,8 @@ typedef struct strix_expert_weights {
 typedef struct strix_ep_exchange {
   int64_t world, rank, cap, top_k, row_bytes, hidden, epoch;
   int64_t round_robin;        /* 0: contiguous expert blocks per rank, 1: expert e on rank e mod world */
+  const int32_t* placement;   /* placement table (device memory) or NULL; overrides round_robin */
+  int64_t experts_global;     /* router width; 0 = experts on this rank x world */
   void* const* peer_recv;     /* host arrays of `world` device addresses, own rank included */
   void* const* peer_meta;
   void* const* peer_counts;

@@ -78,18 +78,29 @@ __device__ __forceinline__ bool wait_epoch(const int32_t* flag, int32_t epoch, u
 // contiguous blocks (rank r owns [r * epr, (r + 1) * epr)); < 0: round-robin (expert e
 // lives on rank e mod world as local expert e / world, -epr experts per rank), which
 // spreads a load that is skewed along the expert index evenly over the ranks.
-__device__ __forceinline__ int ep_owner(int e, int epr, int world) {
-  if (epr > 0) return e >= 0 ? e / epr : -1;
-  return (e >= 0 && e < -epr * world) ? e % world : -1;
+// With a placement table (device memory: [0] = global experts, [1] = row stride, then
+// per expert a row {copies, rank << 16 | local id, ...}) the owner is looked up, and an
+// expert that has several copies (a hot expert replicated to balance the ranks) serves
+// token t from copy t mod copies. Returns rank << 16 | local id, or -1.
+__device__ __forceinline__ int ep_where(int e, int t, int epr, int world, const int32_t* __restrict__ table) {
+  if (e < 0) return -1;
+  if (table != nullptr) {
+    if (e >= table[0]) return -1;
+    const int32_t* row = table + 2 + int64_t(e) * table[1];
+    const int copies = row[0];
+    return copies > 0 ? row[1 + t % copies] : -1;
+  }
+  if (epr > 0) return e / epr < world ? ((e / epr) << 16) | (e % epr) : -1;
+  return e < -epr * world ? ((e % world) << 16) | (e / world) : -1;
 }
-__device__ __forceinline__ int ep_local(int e, int epr, int world) { return epr > 0 ? e % epr : e / world; }
 
 // One CTA per destination rank: tok_pos[d][t] = index of token t among this
 // rank's tokens with a slot on rank d (token order), or -1; counts[d].
 __global__ void __launch_bounds__(256) ep_plan_kernel(const int32_t* __restrict__ topk_ids,
                                                       int32_t* __restrict__ tok_pos,
                                                       int32_t* __restrict__ counts, int tokens,
-                                                      int top_k, int experts_per_rank, int world) {
+                                                      int top_k, int experts_per_rank, int world,
+                                                      const int32_t* __restrict__ placement) {
   __shared__ int s_warp[8];
   const int d = blockIdx.x, tid = threadIdx.x;
   int placed = 0;
@@ -99,7 +110,8 @@ __global__ void __launch_bounds__(256) ep_plan_kernel(const int32_t* __restrict_
     if (t < tokens)
       for (int j = 0; j < top_k; ++j) {
         const int e = topk_ids[t * top_k + j];
-        hit = hit || ep_owner(e, experts_per_rank, world) == d;
+        const int w = ep_where(e, t, experts_per_rank, world, placement);
+        hit = hit || (w >= 0 && (w >> 16) == d);
       }
     const unsigned bal = __ballot_sync(0xffffffffu, hit);
     __syncthreads();
@@ -148,6 +160,7 @@ __global__ void __launch_bounds__(kEpWarps * 32) ep_dispatch_kernel(
     const float* __restrict__ topk_w, const int32_t* __restrict__ tok_pos,
     const int32_t* __restrict__ counts, const EpPeers peers, int32_t* __restrict__ ticket,
     int tokens, int chunks, int top_k, int experts_per_rank, int world, int rank, int64_t cap,
+    const int32_t* __restrict__ placement,
     int32_t epoch) {
   const int lane = threadIdx.x & 31;
   const int warps = gridDim.x * kEpWarps;
@@ -167,8 +180,8 @@ __global__ void __launch_bounds__(kEpWarps * 32) ep_dispatch_kernel(
         } else {
           const int j = lane - 1;
           const int e = topk_ids[t * top_k + j];
-          const bool here = ep_owner(e, experts_per_rank, world) == d;
-          m[1 + 2 * j] = here ? ep_local(e, experts_per_rank, world) : -1;
+          const int w = ep_where(e, t, experts_per_rank, world, placement);
+          m[1 + 2 * j] = (w >= 0 && (w >> 16) == d) ? (w & 0xffff) : -1;
           m[2 + 2 * j] = __float_as_int(topk_w[t * top_k + j]);
         }
       }
@@ -400,13 +413,14 @@ extern "C" int strix_ep_status(int32_t* host_out, int reset) {
 
 // ------------------------------------------------------------------ kernels
 extern "C" int strix_ep_plan(const int32_t* topk_ids, int32_t* tok_pos, int32_t* counts, int64_t tokens,
-                             int64_t top_k, int64_t experts_per_rank, int64_t world, strix_stream_t stream) {
+                             int64_t top_k, int64_t experts_per_rank, int64_t world,
+                             const int32_t* placement, strix_stream_t stream) {
   STRIX_CHECK(counts != nullptr && (tokens == 0 || (topk_ids != nullptr && tok_pos != nullptr)),
               "pointers must not be NULL");
   STRIX_CHECK(tokens >= 0 && top_k >= 1 && experts_per_rank != 0 && world >= 1 && world <= kEpMaxWorld,
               "bad sizes");
   ep_plan_kernel<<<unsigned(world), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      topk_ids, tok_pos, counts, int(tokens), int(top_k), int(experts_per_rank), int(world));
+      topk_ids, tok_pos, counts, int(tokens), int(top_k), int(experts_per_rank), int(world), placement);
   return launch_status("ep_plan");
 }
 
@@ -415,7 +429,8 @@ extern "C" int strix_ep_dispatch(const void* x, const int32_t* topk_ids, const f
                                  void* const* peer_meta, void* const* peer_counts, void* const* peer_flags,
                                  int32_t* ticket, int64_t tokens, int64_t row_bytes, int64_t x_stride_bytes,
                                  int64_t top_k, int64_t experts_per_rank, int64_t world, int64_t rank,
-                                 int64_t cap, int64_t epoch, strix_stream_t stream) {
+                                 int64_t cap, int64_t epoch, const int32_t* placement,
+                                 strix_stream_t stream) {
   STRIX_CHECK(counts != nullptr && ticket != nullptr &&
                   (tokens == 0 || (x != nullptr && topk_ids != nullptr && topk_weights != nullptr &&
                                    tok_pos != nullptr)), "pointers must not be NULL");
@@ -431,7 +446,7 @@ extern "C" int strix_ep_dispatch(const void* x, const int32_t* topk_ids, const f
   ep_dispatch_kernel<<<grid, kEpWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(x), x_stride_bytes / 16, topk_ids, topk_weights, tok_pos, counts, peers,
       ticket, int(tokens), chunks, int(top_k), int(experts_per_rank), int(world), int(rank), cap,
-      int32_t(epoch));
+      placement, int32_t(epoch));
   return launch_status("ep_dispatch");
 }
 

@@ -259,8 +259,9 @@ extern "C" int strix_ep_moe_layer(void* out, const void* x, const float* logits,
   const void* payload = x;
   int64_t payload_stride = x_stride * 2;
   if (tokens > 0) {
-    if ((rc = strix_moe_topk_softmax(logits, i32(p.off_ids), f32(p.off_wts), tokens, w->experts * ep->world,
-                                     k, logits_stride, 1, stream)))
+    const int64_t e_global = ep->experts_global > 0 ? ep->experts_global : w->experts * ep->world;
+    if ((rc = strix_moe_topk_softmax(logits, i32(p.off_ids), f32(p.off_wts), tokens, e_global, k,
+                                     logits_stride, 1, stream)))
       return rc;
     if (w->kind != 0) {
       uint8_t* q = ws + p.off_payload;
@@ -270,12 +271,13 @@ extern "C" int strix_ep_moe_layer(void* out, const void* x, const float* logits,
       payload = q, payload_stride = ep->row_bytes;
     }
   }
-  if ((rc = strix_ep_plan(i32(p.off_ids), ep->tok_pos, ep->counts, tokens, k, epr, ep->world, stream)))
+  if ((rc = strix_ep_plan(i32(p.off_ids), ep->tok_pos, ep->counts, tokens, k, epr, ep->world, ep->placement,
+                          stream)))
     return rc;
   if ((rc = strix_ep_dispatch(payload, i32(p.off_ids), f32(p.off_wts), ep->tok_pos, ep->counts,
                               ep->peer_recv, ep->peer_meta, ep->peer_counts, ep->peer_flags, ep->ticket,
                               tokens, ep->row_bytes, payload_stride, k, epr, ep->world, ep->rank,
-                              ep->cap, ep->epoch, stream)))
+                              ep->cap, ep->epoch, ep->placement, stream)))
     return rc;
   // ---- the rows other ranks sent here: through this rank's experts
   const void* recv = ep->peer_recv[ep->rank];

@@ -264,6 +264,7 @@ class _Exchange(ctypes.Structure):
     """strix_ep_exchange of the header."""
     _fields_ = [(n, ctypes.c_int64) for n in ("world", "rank", "cap", "top_k", "row_bytes", "hidden",
                                               "epoch", "round_robin")] + \
+               [("placement", ctypes.c_void_p), ("experts_global", ctypes.c_int64)] + \
                [("peer_" + n, ctypes.POINTER(ctypes.c_void_p)) for n in _BUFFERS] + \
                [(n, ctypes.c_void_p) for n in ("ticket", "ids", "weights", "rows_per_source", "y", "tok_pos",
                                                "counts")]
@@ -372,11 +373,12 @@ class EpContext:
 
     # ---- the exchange phases (each enqueues kernels on the current stream)
     def dispatch(self, payload: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
-                 experts_per_rank: int, mark=_no_mark):
+                 experts_per_rank: int, mark=_no_mark, placement: torch.Tensor | None = None):
         """payload [T, row_bytes worth of elements] (last dim contiguous) goes to every
         rank that owns one of the token's experts (experts_per_rank < 0: round-robin
-        placement, expert e on rank e mod world). `mark(name)` is called after each
-        kernel is enqueued (a hook for per-phase timing)."""
+        placement, expert e on rank e mod world; `placement`: a table from
+        placement_table() instead). `mark(name)` is called after each kernel is
+        enqueued (a hook for per-phase timing)."""
         t, k = topk_ids.shape
         assert k == self.top_k and t <= self.cap
         assert payload.size(1) * payload.element_size() == self.row_bytes and payload.stride(1) == 1
@@ -387,14 +389,15 @@ class EpContext:
         stream = torch.cuda.current_stream().cuda_stream
         call = self._lib.call
         with torch.cuda.device(self.device):
+            table = None if placement is None else placement.data_ptr()
             call("strix_ep_plan", ids.data_ptr(), self.tok_pos.data_ptr(), self.counts.data_ptr(), t, k,
-                 experts_per_rank, self.world, stream)
+                 experts_per_rank, self.world, table, stream)
             mark("plan")
             call("strix_ep_dispatch", payload.data_ptr(), ids.data_ptr(), wts.data_ptr(),
                  self.tok_pos.data_ptr(), self.counts.data_ptr(), self._ptrs("recv"), self._ptrs("meta"),
                  self._ptrs("counts"), self._ptrs("flags"), self.ticket.data_ptr(), t, self.row_bytes,
                  payload.stride(0) * payload.element_size(), k, experts_per_rank, self.world, self.rank,
-                 self.cap, self.epoch, stream)
+                 self.cap, self.epoch, table, stream)
             mark("dispatch")
 
     def receive(self, spin_limit: int = 0):
@@ -433,7 +436,8 @@ class EpContext:
         return out
 
     def layer(self, x, logits, w13, w13_scale, w2, w2_scale, kind: int, block_m: int,
-              out: torch.Tensor | None = None, spin_limit: int = 0, round_robin: bool = False) -> torch.Tensor:
+              out: torch.Tensor | None = None, spin_limit: int = 0, round_robin: bool = False,
+              placement: torch.Tensor | None = None) -> torch.Tensor:
         """One expert-parallel layer as ONE call into the library (strix_ep_moe_layer):
         router, payload, dispatch, this rank's experts over what it receives, return
         and combine. kind 0 MXFP4 experts over bf16 rows, 1 / 2 FP8 W8A8 experts
@@ -447,7 +451,8 @@ class EpContext:
             out = torch.empty(t, h, dtype=torch.bfloat16, device=self.device)
         keep = {n: self._ptrs(n) for n in _BUFFERS}        # host arrays the struct points into
         ex = _Exchange(self.world, self.rank, self.cap, self.top_k, self.row_bytes, self.hidden, self.epoch,
-                       int(round_robin), *[ctypes.cast(keep[n], ctypes.POINTER(ctypes.c_void_p)) for n in _BUFFERS],
+                       int(round_robin), None if placement is None else placement.data_ptr(),
+                       logits.size(1), *[ctypes.cast(keep[n], ctypes.POINTER(ctypes.c_void_p)) for n in _BUFFERS],
                        self.ticket.data_ptr(), self.ids.data_ptr(), self.weights.data_ptr(),
                        self.rows_per_source.data_ptr(), self.y.data_ptr(), self.tok_pos.data_ptr(),
                        self.counts.data_ptr())
@@ -605,11 +610,14 @@ def ep_moe_fp8(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, block
     without an exchange). placement: which rank owns which expert - "contiguous"
     (rank r holds the experts [r E/N, (r + 1) E/N)) or "round_robin" (rank r holds r,
     r + N, r + 2N, ...: its local expert i is global expert i N + r), which balances
-    a load that is skewed along the expert index; peer exchange only."""
+    a load that is skewed along the expert index, or a `Placement` (any assignment,
+    hot experts replicated: `Placement.balanced(loads, world, slots_per_rank)`); the
+    weight tensors then hold placement.ranks[rank] in that order. Peer exchange only."""
     from . import moe as _moe
 
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     rr = _round_robin(placement, exchange, x)
+    table = placement.table(x.device) if isinstance(placement, Placement) else None
     t, h = x.shape
     if world == 1 and exchange == "auto" and ctx is None:
         return _moe.fused_moe_fp8_w8a8(x, logits, w13, w13_scale, w2, w2_scale, top_k, block_m=block_m)
@@ -633,13 +641,14 @@ def ep_moe_fp8(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, block
         raise RuntimeError("ep_moe_fp8: geometry not covered by the sorted-layout kernel")
     if mark is _no_mark and _one_call_ok(x, logits, w13_scale, w2_scale):
         block = w13_scale.dim() == 3 and w13_scale.size(1) != w13.size(1)
-        return ctx.layer(x, logits, w13, w13_scale, w2, w2_scale, 2 if block else 1, bm, round_robin=rr)
+        return ctx.layer(x, logits, w13, w13_scale, w2, w2_scale, 2 if block else 1, bm, round_robin=rr,
+                         placement=table)
     weights, ids = _moe.route(logits, top_k)
     mark("route")
     payload, _, _ = fp8_payload(x, getattr(ctx, "_payload", None))
     ctx._payload = payload          # the padding bytes were zeroed once, at allocation
     mark("quantise")
-    ctx.dispatch(payload, weights, ids, -e_local if rr else e_local, mark)
+    ctx.dispatch(payload, weights, ids, -e_local if rr else e_local, mark, placement=table)
     y = _experts_fp8_on_received(ctx, w13, w13_scale, w2, w2_scale, bm, mark)
     ctx.send_back(y)
     mark("return")
@@ -660,6 +669,7 @@ def ep_moe_mxfp4(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, blo
 
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     rr = _round_robin(placement, exchange, x)
+    table = placement.table(x.device) if isinstance(placement, Placement) else None
     t, h = x.shape
     lib = _lib.load()
     wide_ok = bool(lib.strix_moe_gemm_mxfp4_sorted_covers(w13.size(1), w13.size(2) * 2, 128, 1)
@@ -670,7 +680,7 @@ def ep_moe_mxfp4(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, blo
     if peer and mark is _no_mark and _one_call_ok(x, logits, w13_scale, w2_scale):
         if ctx is None:
             ctx = context_for(group, t, top_k, h * 2, h, x.device)
-        return ctx.layer(x, logits, w13, w13_scale, w2, w2_scale, 0, 128, round_robin=rr)
+        return ctx.layer(x, logits, w13, w13_scale, w2, w2_scale, 0, 128, round_robin=rr, placement=table)
     weights, ids = _moe.route(logits, top_k)
     if not peer:
         def combine(slots):
@@ -684,7 +694,7 @@ def ep_moe_mxfp4(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, blo
     if ctx is None:
         ctx = context_for(group, t, top_k, h * 2, h, x.device)
     mark("route")
-    ctx.dispatch(x, weights, ids, -w13.size(0) if rr else w13.size(0), mark)
+    ctx.dispatch(x, weights, ids, -w13.size(0) if rr else w13.size(0), mark, placement=table)
     y = _experts_mxfp4_on_received(ctx, w13, w13_scale, w2, w2_scale, mark)
     ctx.send_back(y)
     mark("return")
@@ -693,9 +703,80 @@ def ep_moe_mxfp4(x, logits, w13, w13_scale, w2, w2_scale, top_k, group=None, blo
     return out
 
 
-def _round_robin(placement: str, exchange: str, x) -> bool:
+class Placement:
+    """Which rank holds which expert, as a table: `ranks[r]` lists the global experts
+    rank r holds, in the order of its weight tensors (its local expert i is global
+    expert ranks[r][i]). An expert may appear on several ranks: a replicated hot
+    expert, whose tokens are spread over the copies (token t goes to copy t mod
+    copies). `table(device)` is the int32 tensor the exchange kernels read."""
+
+    def __init__(self, ranks: list[list[int]], experts: int):
+        self.ranks, self.experts, self.world = [list(r) for r in ranks], experts, len(ranks)
+        where: list[list[int]] = [[] for _ in range(experts)]
+        for r, held in enumerate(self.ranks):
+            for i, e in enumerate(held):
+                where[e].append((r << 16) | i)
+        if any(not w for w in where):
+            raise ValueError("every expert needs a rank")
+        self.max_copies = max(len(w) for w in where)
+        self.where = where
+        self._tables: dict[str, torch.Tensor] = {}
+
+    def table(self, device) -> torch.Tensor:
+        key = str(device)
+        if key not in self._tables:
+            stride = 1 + self.max_copies
+            rows = [[len(w)] + w + [-1] * (self.max_copies - len(w)) for w in self.where]
+            flat = [self.experts, stride] + [v for row in rows for v in row]
+            self._tables[key] = torch.tensor(flat, dtype=torch.int32, device=device)
+        return self._tables[key]
+
+    def rank_of(self, topk_ids: torch.Tensor) -> torch.Tensor:
+        """The rank that serves each slot of topk_ids [T, k] (token t = row t): the
+        table's rule, on whatever device the ids are."""
+        dev = topk_ids.device
+        tab = self.table(dev)[2:].view(self.experts, 1 + self.max_copies)
+        e = topk_ids.long()
+        t = torch.arange(e.size(0), device=dev).view(-1, 1).expand_as(e)
+        copy = t % tab[e, 0].long()
+        return tab[e, 1 + copy] >> 16
+
+    @classmethod
+    def balanced(cls, loads, world: int, slots_per_rank: int | None = None) -> "Placement":
+        """Longest-processing-time placement of `loads` (expected routed slots per
+        expert) with at most `slots_per_rank` experts per rank (default: experts /
+        world, no copies). Spare slots are spent on copies of whichever expert has the
+        largest load per copy; copies of one expert go to different ranks."""
+        loads = [float(v) for v in loads]
+        experts = len(loads)
+        per = slots_per_rank or -(-experts // world)
+        if per * world < experts:
+            raise ValueError("not enough expert slots")
+        copies = [1] * experts
+        for _ in range(per * world - experts):
+            e = max(range(experts), key=lambda i: loads[i] / copies[i])
+            if copies[e] >= world or loads[e] / copies[e] <= sum(loads) / (world * per):
+                break
+            copies[e] += 1
+        items = sorted(((loads[e] / copies[e], e) for e in range(experts) for _ in range(copies[e])),
+                       reverse=True)
+        ranks: list[list[int]] = [[] for _ in range(world)]
+        total = [0.0] * world
+        for w, e in items:
+            free = [r for r in range(world) if len(ranks[r]) < per and e not in ranks[r]]
+            r = min(free, key=lambda i: total[i])
+            ranks[r].append(e)
+            total[r] += w
+        return cls(ranks, experts)
+
+
+def _round_robin(placement, exchange: str, x) -> bool:
+    if isinstance(placement, Placement):
+        if exchange == "nccl" or not x.is_cuda:
+            raise ValueError("a placement table needs the peer-memory exchange")
+        return False
     if placement not in ("contiguous", "round_robin"):
-        raise ValueError(f"placement must be 'contiguous' or 'round_robin', got {placement!r}")
+        raise ValueError(f"placement must be 'contiguous', 'round_robin' or a Placement, got {placement!r}")
     if placement == "round_robin" and (exchange == "nccl" or not x.is_cuda):
         raise ValueError("round_robin placement needs the peer-memory exchange")
     return placement == "round_robin"

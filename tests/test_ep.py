@@ -89,6 +89,38 @@ def test_dispatch_plan_is_stable_and_counts():
     assert order.tolist() == [1, 2, 5, 0, 3, 4]              # rank 0's slots first, in slot order
 
 
+def test_placement_table_and_balancing():
+    """Host logic of expert placement: the table the kernels read, the rank each slot
+    goes to, and the balanced placement with copies of hot experts."""
+    from libstrix_b200 import ep
+
+    pl = ep.Placement([[0, 1, 2], [3, 4, 0], [5, 6], [7, 0]], 8)
+    tab = pl.table("cpu")
+    assert tab[:2].tolist() == [8, 4]                              # experts, row stride (1 + 3 copies)
+    rows = tab[2:].view(8, 4)
+    assert rows[0].tolist() == [3, (0 << 16) | 0, (1 << 16) | 2, (3 << 16) | 1]
+    assert rows[5].tolist() == [1, (2 << 16) | 0, -1, -1]
+    ids = torch.tensor([[0, 5], [0, 3], [0, 7], [0, 1]], dtype=torch.int32)
+    assert pl.rank_of(ids).tolist() == [[0, 2], [1, 1], [3, 3], [0, 0]]   # token t -> copy t mod 3
+    with pytest.raises(ValueError, match="every expert needs a rank"):
+        ep.Placement([[0], [1]], 3)
+    # one expert with 40 % of the load: no placement without copies can balance 4 ranks
+    loads = [400.0] + [600.0 / 15] * 15
+    plain = ep.Placement.balanced(loads, 4)
+    spare = ep.Placement.balanced(loads, 4, slots_per_rank=5)
+
+    def ratio(p):
+        per = [0.0] * p.world
+        for e, where in enumerate(p.where):
+            for w in where:
+                per[w >> 16] += loads[e] / len(where)
+        return max(per) / (sum(per) / p.world)
+
+    assert all(len(r) == 4 for r in plain.ranks) and ratio(plain) > 1.5
+    assert all(len(r) <= 5 for r in spare.ranks) and ratio(spare) < 1.1
+    assert len(spare.where[0]) >= 2 and len({w >> 16 for w in spare.where[0]}) == len(spare.where[0])
+
+
 @pytest.mark.gpu
 def test_ep_moe_mxfp4_matches_oracle_on_visible_gpus():
     """World size 1 on one GPU (the all-to-alls degenerate to copies): the
@@ -208,15 +240,16 @@ def _bound_ok(out, ref):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("placement", ["contiguous", "round_robin"])
+@pytest.mark.parametrize("placement", ["contiguous", "round_robin", "table"])
 @pytest.mark.parametrize("kind", ["mxfp4", "fp8"])
 @pytest.mark.parametrize("tokens_per_rank", [[70, 0, 33, 128], [1, 1, 1, 1]])
 def test_peer_exchange_with_emulated_ranks(kind, tokens_per_rank, placement):
     """Four ranks emulated in one process on one GPU (the phases of all ranks run in
     lockstep, so no kernel ever waits for one that has not been launched): plan,
     dispatch, receive, local experts, return and combine against the CPU oracle of
-    the unsharded layer, with the experts in contiguous blocks per rank or placed
-    round-robin (expert e on rank e mod 4)."""
+    the unsharded layer, with the experts in contiguous blocks per rank, placed
+    round-robin (expert e on rank e mod 4), or by a table in which expert 0 has three
+    copies (its tokens are spread over them) and the ranks hold 3, 3, 2 and 2 experts."""
     from libstrix_b200 import ep
     from libstrix_b200 import moe as smoe
     from libstrix_b200.workloads import moe_fp8_layer, moe_mxfp4_layer
@@ -226,6 +259,8 @@ def test_peer_exchange_with_emulated_ranks(kind, tokens_per_rank, placement):
     world, e_global, k, hid, inter = 4, 8, 2, 256, 128
     per = e_global // world
     rr = placement == "round_robin"
+    place = ep.Placement([[0, 1, 2], [3, 4, 0], [5, 6], [7, 0]], e_global) if placement == "table" else None
+    table = place.table(dev) if place else None
     total = sum(tokens_per_rank)
     if kind == "mxfp4":
         layer = moe_mxfp4_layer(tokens=256, hidden=hid, experts=e_global, top_k=k, inter=inter, seed=3)
@@ -246,9 +281,11 @@ def test_peer_exchange_with_emulated_ranks(kind, tokens_per_rank, placement):
                 x, logits = g.x[offs[r]:offs[r + 1]], g.logits[offs[r]:offs[r + 1]]
                 weights, ids = smoe.route(logits, k)
                 payload = x if kind == "mxfp4" else ep.fp8_payload(x)[0]
-                ctx.dispatch(payload, weights, ids, -per if rr else per)
+                ctx.dispatch(payload, weights, ids, -per if rr else per, placement=table)
             for r, ctx in enumerate(ctxs):
                 sl = slice(r, None, world) if rr else slice(r * per, (r + 1) * per)
+                if place:
+                    sl = torch.tensor(place.ranks[r], device=dev)
                 if kind == "mxfp4":
                     y = ep._experts_mxfp4_on_received(ctx, g.w13[sl].contiguous(), g.w13_scale[sl].contiguous(),
                                                       g.w2[sl].contiguous(), g.w2_scale[sl].contiguous())
@@ -264,6 +301,8 @@ def test_peer_exchange_with_emulated_ranks(kind, tokens_per_rank, placement):
             ids_all, _ = M.router(layer.logits[:total], k)
             for r in range(world):
                 mine = ids_all[offs[r]:offs[r + 1]] % world if rr else ids_all[offs[r]:offs[r + 1]] // per
+                if place:
+                    mine = place.rank_of(ids_all[offs[r]:offs[r + 1]])
                 for d in range(world):
                     assert int(got[d, r]) == int((mine == d).any(-1).sum())
             for r in range(world):
