@@ -125,15 +125,19 @@ __global__ void __launch_bounds__(kMxThreads, 1) moe_gemm_mxfp4_umma_kernel(
   }
   __syncthreads();
   if (tid == 0) {
-    // units: pairs of consecutive m-blocks of one expert, else single m-blocks
+    // units: pairs of consecutive m-blocks of one expert, else single m-blocks. The
+    // pairs come first in the list: items are dealt to the CTAs in a fixed stride, and
+    // a pair costs twice a single, so this order keeps the CTAs' sums within one single
+    // of each other instead of leaving the balance to chance.
     int n = 0;
-    for (int i = 0; i < m_blocks;) {
-      const int e = s_expert[i];
-      if (e < 0) { ++i; continue; }
-      const int cnt = (i + 1 < m_blocks && s_expert[i + 1] == e) ? 2 : 1;
-      s_unit[n++] = i | (cnt << 16);
-      i += cnt;
-    }
+    for (int want = 2; want >= 1; --want)
+      for (int i = 0; i < m_blocks;) {
+        const int e = s_expert[i];
+        if (e < 0) { ++i; continue; }
+        const int cnt = (i + 1 < m_blocks && s_expert[i + 1] == e) ? 2 : 1;
+        if (cnt == want) s_unit[n++] = i | (cnt << 16);
+        i += cnt;
+      }
     s_units = n;
   }
   if (tid == 0) {

@@ -568,8 +568,11 @@ def context_for(group, tokens, top_k, row_bytes, hidden, device) -> EpContext:
     key = (id(group), top_k, row_bytes, hidden, str(device))
     ctx = _CONTEXTS.get(key)
     if ctx is None:
-        ctx = _CONTEXTS[key] = EpContext.create(group, _capacity(tokens, group), top_k, row_bytes,
-                                                hidden, device)
+        if not dist.is_initialized():       # a single process: the rank exchanges with itself
+            ctx = _CONTEXTS[key] = EpContext.emulate(1, max(tokens, 1), top_k, row_bytes, hidden, device)[0]
+        else:
+            ctx = _CONTEXTS[key] = EpContext.create(group, _capacity(tokens, group), top_k, row_bytes,
+                                                    hidden, device)
     if tokens > ctx.cap:
         raise RuntimeError(f"{tokens} tokens exceed the exchange capacity {ctx.cap} set at first use")
     return ctx
