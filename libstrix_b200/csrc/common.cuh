@@ -12,6 +12,7 @@
 #include <stdint.h>
 
 #include <cstdarg>
+#include <cstdlib>
 #include <cstdio>
 
 #include "../../include/strix_b200.h"
@@ -42,7 +43,42 @@ inline int launch_status(const char* what) {
   return STRIX_OK;
 }
 
+// Programmatic dependent launch: the kernels of a layer are enqueued back to back
+// and each one begins with pdl_enter(), which lets the NEXT kernel of the stream be
+// launched right away (its CTAs become resident as resources allow) and then waits
+// until every kernel before it has completed and its writes are visible. A kernel
+// does nothing before that wait, so the order of all memory effects is that of
+// ordinary stream order; what is saved is the launch latency and scheduling gap
+// between kernels (a few microseconds each, a tenth of a 256-token MoE layer).
+// STRIX_PDL=0 launches the plain way.
+inline bool pdl_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("STRIX_PDL");
+    return v == nullptr || v[0] != '0';
+  }();
+  return on;
+}
+
+template <typename... P, typename... A>
+inline void launch_chain(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                         A&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = st;
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, P(static_cast<A&&>(args))...);
+}
+
 // ---------------------------------------------------------------- device side
+
+// First statement of a kernel launched with launch_chain (see there).
+__device__ __forceinline__ void pdl_enter() {
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 
 constexpr float kLog2e = 1.4426950408889634f;
 

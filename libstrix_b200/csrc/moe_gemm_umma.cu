@@ -131,6 +131,7 @@ template <int NTOK, int KBMAX>
 __global__ void __launch_bounds__(umma_threads(NTOK), 1) moe_gemm_umma_kernel(const UmmaMoeArgs p,
                                                                     const __grid_constant__ CUtensorMap map_w,
                                                                     const __grid_constant__ CUtensorMap map_a) {
+  pdl_enter();
   using L = UmmaLayout<NTOK, KBMAX>;
   constexpr int S = L::kStages, NB = L::kAccBufs;
   constexpr int kColumnGroups = column_groups(NTOK), kConsumerWarps = 4 * kColumnGroups;
@@ -507,6 +508,7 @@ struct WideLayout {
 __global__ void __launch_bounds__(kWideThreads, 1) moe_gemm_umma_wide_kernel(
     const UmmaMoeArgs p, const __grid_constant__ CUtensorMap map_w,
     const __grid_constant__ CUtensorMap map_a) {
+  pdl_enter();
   using L = WideLayout;
   constexpr int S = L::kStages, NB = L::kAccBufs, MB = L::kMetaBufs;
   extern __shared__ uint8_t raw_smem[];
@@ -795,7 +797,7 @@ int launch_umma(const UmmaMoeArgs& p, const CUtensorMap& map_w, const CUtensorMa
     STRIX_CUDA(cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev));
     done[dev] = true;
   }
-  kernel<<<sms[dev], umma_threads(NTOK), L::kSmem, st>>>(p, map_w, map_a);
+  launch_chain(kernel, sms[dev], umma_threads(NTOK), L::kSmem, st, p, map_w, map_a);
   return launch_status("moe_gemm_umma");
 }
 
@@ -812,7 +814,7 @@ int launch_umma_wide(const UmmaMoeArgs& p, const CUtensorMap& map_w, const CUten
     STRIX_CUDA(cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev));
     done[dev] = true;
   }
-  moe_gemm_umma_wide_kernel<<<sms[dev], kWideThreads, WideLayout::kSmem, st>>>(p, map_w, map_a);
+  launch_chain(moe_gemm_umma_wide_kernel, sms[dev], kWideThreads, WideLayout::kSmem, st, p, map_w, map_a);
   return launch_status("moe_gemm_umma_wide");
 }
 

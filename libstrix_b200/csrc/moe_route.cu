@@ -20,6 +20,7 @@ template <int VPL>  // values per lane: experts <= 32 * VPL
 __global__ void __launch_bounds__(128) topk_softmax_kernel(
     const float* __restrict__ logits, int64_t l_stride, int32_t* __restrict__ ids,
     float* __restrict__ weights, int tokens, int experts, int top_k, int renorm) {
+  pdl_enter();
   const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (t >= tokens) return;
   const float* row = logits + int64_t(t) * l_stride;
@@ -96,6 +97,7 @@ __global__ void __launch_bounds__(kAlignThreads) moe_align_kernel(
     int32_t* __restrict__ expert_ids, int32_t* __restrict__ num_post, int numel, int experts,
     int block_m, int cap, int cap_blocks, int32_t* __restrict__ slot_pos,
     int32_t* __restrict__ counts) {
+  pdl_enter();
   extern __shared__ int s_count[];            // [experts]
   __shared__ int s_warp[kAlignWarps];
   __shared__ int s_base;
@@ -183,6 +185,7 @@ constexpr int kChunkSlots = 1024, kPlaceThreads = 256, kPlaceWarps = 8, kPlaceMa
 
 __global__ void __launch_bounds__(kPlaceThreads) moe_align_hist_kernel(
     const int32_t* __restrict__ topk_ids, int32_t* __restrict__ hist, int numel, int experts) {
+  pdl_enter();
   extern __shared__ int s_cnt[];
   for (int i = threadIdx.x; i < experts; i += kPlaceThreads) s_cnt[i] = 0;
   __syncthreads();
@@ -202,6 +205,7 @@ __global__ void __launch_bounds__(kPlaceThreads) moe_align_place_kernel(
     int32_t* __restrict__ sorted_ids, int32_t* __restrict__ expert_ids, int32_t* __restrict__ num_post,
     int numel, int experts, int block_m, int cap, int cap_blocks, int chunks,
     int32_t* __restrict__ slot_pos, int32_t* __restrict__ counts) {
+  pdl_enter();
   extern __shared__ int s_dyn[];
   int* s_tot = s_dyn;                       // [experts] slots of the expert
   int* s_base = s_tot + experts;            // [experts] first sorted position of the expert
@@ -322,6 +326,7 @@ __global__ void __launch_bounds__(256) act_quant_kernel(
     float* __restrict__ sa, int64_t sa_stride, int64_t rows, int groups,
     const int32_t* __restrict__ row_map, const int32_t* __restrict__ row_limit, int top_k,
     int64_t num_valid) {
+  pdl_enter();
   int64_t team = (int64_t(blockIdx.x) * 256 + threadIdx.x) >> 4;
   const int sub = threadIdx.x & 15;
   // out-of-range teams redo the last group and skip the stores, so every lane
@@ -403,6 +408,7 @@ __global__ void __launch_bounds__(256) act_quant_scatter_kernel(
     float* __restrict__ sa, int64_t sa_stride, int64_t tokens, int groups, int top_k,
     const int32_t* __restrict__ slot_pos, const int32_t* __restrict__ sorted_ids,
     const int32_t* __restrict__ num_post, int64_t rows_cap, int64_t num_valid) {
+  pdl_enter();
   const int64_t team = (int64_t(blockIdx.x) * 256 + threadIdx.x) >> 4;
   const int sub = threadIdx.x & 15;
   const int64_t token_teams = tokens * groups;
@@ -462,6 +468,7 @@ __global__ void __launch_bounds__(256) act_quant_scatter_kernel(
 __global__ void __launch_bounds__(256) moe_sum_kernel(
     const uint16_t* __restrict__ in, int64_t in_st, int64_t in_sj, uint16_t* __restrict__ out,
     int64_t out_st, int tokens, int top_k, int hidden8) {
+  pdl_enter();
   const int64_t idx = int64_t(blockIdx.x) * 256 + threadIdx.x;
   if (idx >= int64_t(tokens) * hidden8) return;
   const int64_t t = idx / hidden8;
@@ -584,8 +591,8 @@ extern "C" int strix_moe_topk_softmax(const float* logits, int32_t* topk_ids, fl
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const unsigned grid = unsigned((tokens + 3) / 4);
 #define STRIX_TOPK(V)                                                                        \
-  topk_softmax_kernel<V><<<grid, 128, 0, st>>>(logits, logits_stride, topk_ids, topk_weights, \
-                                               int(tokens), int(experts), int(top_k), renormalize)
+  launch_chain(topk_softmax_kernel<V>, grid, 128, 0, st, logits, logits_stride, topk_ids, topk_weights, \
+               int(tokens), int(experts), int(top_k), renormalize)
   if (experts <= 32) STRIX_TOPK(1);
   else if (experts <= 64) STRIX_TOPK(2);
   else if (experts <= 128) STRIX_TOPK(4);
@@ -626,7 +633,7 @@ extern "C" int strix_moe_align_counts(const int32_t* topk_ids, int32_t* sorted_i
   STRIX_CHECK(expert_capacity * block_m >= sorted_capacity,
               "expert_ids too short for block_m %lld", (long long)block_m);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  moe_align_kernel<<<unsigned(experts + 1), kAlignThreads, size_t(experts) * sizeof(int), st>>>(
+  launch_chain(moe_align_kernel, unsigned(experts + 1), kAlignThreads, size_t(experts) * sizeof(int), st,
       topk_ids, sorted_ids, expert_ids, num_post_padded, int(numel), int(experts), int(block_m),
       int(sorted_capacity), int(expert_capacity), slot_pos, counts);
   return launch_status("moe_align");
@@ -658,11 +665,11 @@ extern "C" int strix_moe_align_scratch(const int32_t* topk_ids, int32_t* sorted_
   const int chunks = int((numel + kChunkSlots - 1) / kChunkSlots);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int32_t* hist = static_cast<int32_t*>(scratch);
-  moe_align_hist_kernel<<<unsigned(chunks), kPlaceThreads, size_t(experts) * sizeof(int), st>>>(
+  launch_chain(moe_align_hist_kernel, unsigned(chunks), kPlaceThreads, size_t(experts) * sizeof(int), st,
       topk_ids, hist, int(numel), int(experts));
   if (int rc = launch_status("moe_align_hist")) return rc;
   const size_t smem = size_t(3 + kPlaceWarps) * size_t(experts) * sizeof(int);
-  moe_align_place_kernel<<<unsigned(chunks), kPlaceThreads, smem, st>>>(
+  launch_chain(moe_align_place_kernel, unsigned(chunks), kPlaceThreads, smem, st,
       topk_ids, hist, sorted_ids, expert_ids, num_post_padded, int(numel), int(experts), int(block_m),
       int(sorted_capacity), int(expert_capacity), chunks, slot_pos, counts);
   return launch_status("moe_align_place");
@@ -699,9 +706,9 @@ extern "C" int strix_moe_act_quant_fp8_scatter(const void* x, void* q, float* sa
   auto qp = static_cast<uint8_t*>(q);
   const int64_t num_valid = tokens * top_k;
   if (x_is_f16)
-    act_quant_scatter_kernel<true><<<grid, 256, 0, st>>>(xp, x_stride, qp, q_stride, sa, sa_stride, tokens, groups, int(top_k), slot_pos, sorted_ids, num_post_padded, rows, num_valid);
+    launch_chain(act_quant_scatter_kernel<true>, grid, 256, 0, st, xp, x_stride, qp, q_stride, sa, sa_stride, tokens, groups, int(top_k), slot_pos, sorted_ids, num_post_padded, rows, num_valid);
   else
-    act_quant_scatter_kernel<false><<<grid, 256, 0, st>>>(xp, x_stride, qp, q_stride, sa, sa_stride, tokens, groups, int(top_k), slot_pos, sorted_ids, num_post_padded, rows, num_valid);
+    launch_chain(act_quant_scatter_kernel<false>, grid, 256, 0, st, xp, x_stride, qp, q_stride, sa, sa_stride, tokens, groups, int(top_k), slot_pos, sorted_ids, num_post_padded, rows, num_valid);
   return launch_status("moe_act_quant_scatter");
 }
 
@@ -723,11 +730,11 @@ static int act_quant_common(const void* x, void* q, float* sa, int64_t rows, int
   auto xp = static_cast<const uint16_t*>(x);
   auto qp = static_cast<uint8_t*>(q);
   if (fp8) {
-    if (x_is_f16) act_quant_kernel<true, true><<<grid, 256, 0, st>>>(xp, x_stride, qp, q_stride, sa, sa_stride, rows, groups, row_map, row_limit, top_k, num_valid);
-    else act_quant_kernel<true, false><<<grid, 256, 0, st>>>(xp, x_stride, qp, q_stride, sa, sa_stride, rows, groups, row_map, row_limit, top_k, num_valid);
+    if (x_is_f16) launch_chain(act_quant_kernel<true, true>, grid, 256, 0, st, xp, x_stride, qp, q_stride, sa, sa_stride, rows, groups, row_map, row_limit, top_k, num_valid);
+    else launch_chain(act_quant_kernel<true, false>, grid, 256, 0, st, xp, x_stride, qp, q_stride, sa, sa_stride, rows, groups, row_map, row_limit, top_k, num_valid);
   } else {
-    if (x_is_f16) act_quant_kernel<false, true><<<grid, 256, 0, st>>>(xp, x_stride, qp, q_stride, sa, sa_stride, rows, groups, row_map, row_limit, top_k, num_valid);
-    else act_quant_kernel<false, false><<<grid, 256, 0, st>>>(xp, x_stride, qp, q_stride, sa, sa_stride, rows, groups, row_map, row_limit, top_k, num_valid);
+    if (x_is_f16) launch_chain(act_quant_kernel<false, true>, grid, 256, 0, st, xp, x_stride, qp, q_stride, sa, sa_stride, rows, groups, row_map, row_limit, top_k, num_valid);
+    else launch_chain(act_quant_kernel<false, false>, grid, 256, 0, st, xp, x_stride, qp, q_stride, sa, sa_stride, rows, groups, row_map, row_limit, top_k, num_valid);
   }
   return launch_status("moe_act_quant");
 }
@@ -768,7 +775,7 @@ extern "C" int strix_moe_sum(const void* in, void* out, int64_t tokens, int64_t 
               "16-byte aligned rows required");
   if (tokens == 0) return STRIX_OK;
   const int64_t work = tokens * (hidden / 8);
-  moe_sum_kernel<<<unsigned((work + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_chain(moe_sum_kernel, unsigned((work + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream),
       static_cast<const uint16_t*>(in), in_st, in_sj, static_cast<uint16_t*>(out), out_st,
       int(tokens), int(top_k), int(hidden / 8));
   return launch_status("moe_sum");
