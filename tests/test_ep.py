@@ -244,6 +244,23 @@ def _bound_ok(out, ref):
 @pytest.mark.parametrize("kind", ["mxfp4", "fp8"])
 @pytest.mark.parametrize("tokens_per_rank", [[70, 0, 33, 128], [1, 1, 1, 1]])
 def test_peer_exchange_with_emulated_ranks(kind, tokens_per_rank, placement):
+    _emulated_exchange(kind, tokens_per_rank, placement)
+
+
+@pytest.mark.gpu
+def test_peer_exchange_eight_emulated_ranks_balanced_placement():
+    """Eight ranks, sixteen experts of which one draws a third of the load: the
+    balanced placement (three expert slots per rank) replicates it, and the layer
+    still matches the oracle of the unsharded layer."""
+    from libstrix_b200 import ep
+
+    loads = [40.0] + [80.0 / 15] * 15
+    place = ep.Placement.balanced(loads, 8, slots_per_rank=3)
+    assert len(place.where[0]) >= 2
+    _emulated_exchange("mxfp4", [5, 0, 9, 1, 33, 2, 7, 64], "table", world=8, e_global=16, place=place)
+
+
+def _emulated_exchange(kind, tokens_per_rank, placement, world=4, e_global=8, place=None):
     """Four ranks emulated in one process on one GPU (the phases of all ranks run in
     lockstep, so no kernel ever waits for one that has not been launched): plan,
     dispatch, receive, local experts, return and combine against the CPU oracle of
@@ -256,10 +273,11 @@ def test_peer_exchange_with_emulated_ranks(kind, tokens_per_rank, placement):
     from oracle import moe as M
 
     dev = torch.device("cuda", 0)
-    world, e_global, k, hid, inter = 4, 8, 2, 256, 128
+    k, hid, inter = 2, 256, 128
     per = e_global // world
     rr = placement == "round_robin"
-    place = ep.Placement([[0, 1, 2], [3, 4, 0], [5, 6], [7, 0]], e_global) if placement == "table" else None
+    if placement == "table" and place is None:
+        place = ep.Placement([[0, 1, 2], [3, 4, 0], [5, 6], [7, 0]], e_global)
     table = place.table(dev) if place else None
     total = sum(tokens_per_rank)
     if kind == "mxfp4":
