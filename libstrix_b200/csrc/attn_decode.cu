@@ -241,6 +241,7 @@ __device__ __forceinline__ void compute_tile(const TileQ8<D>& t, WarpState<D>& s
 template <int D, bool ALIGNED, int kWarps, int kMinCtas, int STAGES>
 __global__ void __launch_bounds__(kWarps * 32, kMinCtas)
 attn_decode_q8_kernel(const DecodeArgs a) {
+  pdl_enter();
   constexpr int kThreads = kWarps * 32;
   extern __shared__ __align__(16) uint8_t dyn_smem[];
   const int seg = blockIdx.x, hgrp = blockIdx.y, n = blockIdx.z;
@@ -555,27 +556,50 @@ attn_decode_q8_kernel(const DecodeArgs a) {
 
 // Combines the segments of one (sequence, head): w_s = 2^(m_s - m),
 // O = sum w_s O_s / sum w_s l_s; empty segments (m = -inf) weigh nothing.
-// Follows attn_decode_reduce_kernel (csrc/attn/attn_decode_bf16.hip:276-300).
+// Follows attn_decode_reduce_kernel (csrc/attn/attn_decode_bf16.hip:276-300). Four
+// groups of D / 2 threads take every fourth segment each (a 65,536-key row has 64
+// partials: one thread walking them all is 64 dependent round trips to L2) and
+// meet in shared memory.
+constexpr int kReduceParts = 4;
+
 template <int D>
-__global__ void __launch_bounds__(D / 2) attn_decode_reduce_kernel(
+__global__ void __launch_bounds__(kReduceParts * D / 2) attn_decode_reduce_kernel(
     __nv_bfloat16* __restrict__ out, const float* __restrict__ o_part,
     const float* __restrict__ ml_part, int nseg, int hq, int64_t o_st, int64_t o_sh,
     const float* __restrict__ sinks) {
+  pdl_enter();
+  __shared__ float s_m[kReduceParts], s_l[kReduceParts];
+  __shared__ float2 s_acc[kReduceParts][D / 2];
+  const int part = threadIdx.x / (D / 2), dp = threadIdx.x % (D / 2);
   const int64_t row = int64_t(blockIdx.y) * hq + blockIdx.x;
   const float* ml = ml_part + row * nseg * 2;
   float m = -INFINITY;
-  for (int s = 0; s < nseg; ++s) m = fmaxf(m, ml[2 * s]);
+  for (int s = part; s < nseg; s += kReduceParts) m = fmaxf(m, ml[2 * s]);
+  if (dp == 0) s_m[part] = m;
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < kReduceParts; ++i) m = fmaxf(m, s_m[i]);
   float l = 0.f;
   float2 acc = make_float2(0.f, 0.f);
-  for (int s = 0; s < nseg; ++s) {
+#pragma unroll 4
+  for (int s = part; s < nseg; s += kReduceParts) {
     const float ms = ml[2 * s];
     if (ms == -INFINITY) continue;
     const float w = exp2f(ms - m);
     l += w * ml[2 * s + 1];
-    const float2 o =
-        *reinterpret_cast<const float2*>(o_part + (row * nseg + s) * D + 2 * threadIdx.x);
+    const float2 o = *reinterpret_cast<const float2*>(o_part + (row * nseg + s) * D + 2 * dp);
     acc.x += w * o.x;
     acc.y += w * o.y;
+  }
+  s_acc[part][dp] = acc;
+  if (dp == 0) s_l[part] = l;
+  __syncthreads();
+  if (part != 0) return;
+#pragma unroll
+  for (int i = 1; i < kReduceParts; ++i) {
+    acc.x += s_acc[i][dp].x;
+    acc.y += s_acc[i][dp].y;
+    l += s_l[i];
   }
   if (sinks != nullptr) {
     const float s2 = sinks[blockIdx.x] * kLog2e;
@@ -586,8 +610,8 @@ __global__ void __launch_bounds__(D / 2) attn_decode_reduce_kernel(
     l = l * al + exp2f(s2 - mf);
   }
   const float inv = l > 0.f ? 1.f / l : 0.f;
-  *reinterpret_cast<uint32_t*>(out + int64_t(blockIdx.y) * o_st + int64_t(blockIdx.x) * o_sh +
-                               2 * threadIdx.x) = pack_bf16x2(acc.x * inv, acc.y * inv);
+  *reinterpret_cast<uint32_t*>(out + int64_t(blockIdx.y) * o_st + int64_t(blockIdx.x) * o_sh + 2 * dp) =
+      pack_bf16x2(acc.x * inv, acc.y * inv);
 }
 
 template <int D, bool AL, int W, int MINB, int S>
@@ -604,7 +628,7 @@ int launch_decode(dim3 grid, cudaStream_t st, const DecodeArgs& a, size_t smem) 
       if (dev >= 0 && dev < 64) done[dev] = true;
     }
   }
-  kernel<<<grid, W * 32, smem, st>>>(a);
+  launch_chain(kernel, grid, W * 32, smem, st, a);
   return launch_status("attn_decode");
 }
 
@@ -750,11 +774,11 @@ extern "C" int strix_attn_decode_bf16(
   if (nseg > 1) {
     const dim3 rgrid{unsigned(hq), unsigned(nseq), 1u};
     if (head_dim == 128)
-      attn_decode_reduce_kernel<128><<<rgrid, 64, 0, st>>>(a.out, a.o_part, a.ml_part, a.nseg,
-                                                           a.hq, o_st, o_sh, sinks);
+      launch_chain(attn_decode_reduce_kernel<128>, rgrid, kReduceParts * 64, 0, st, a.out, a.o_part,
+                   a.ml_part, a.nseg, a.hq, o_st, o_sh, sinks);
     else
-      attn_decode_reduce_kernel<256><<<rgrid, 128, 0, st>>>(a.out, a.o_part, a.ml_part, a.nseg,
-                                                            a.hq, o_st, o_sh, sinks);
+      launch_chain(attn_decode_reduce_kernel<256>, rgrid, kReduceParts * 128, 0, st, a.out, a.o_part,
+                   a.ml_part, a.nseg, a.hq, o_st, o_sh, sinks);
     rc = launch_status("attn_decode_reduce");
   }
   return rc;
