@@ -301,6 +301,26 @@ def time_decode(strix, batch, args, world, dist, local_rank, sample_clocks: bool
     for _ in range(args.warmup):
         step()
     barrier()
+    # The timed step is a replay of the captured call (the op neither synchronises nor
+    # allocates outside torch's pool, so it records as it is): a shard of 8 sequences
+    # runs for 0.1 ms, which the Python call path alone does not sustain.
+    if not args.no_graph:
+        eager_step = step
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            eager_step()
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            eager_step()
+
+        def step():
+            graph.replay()
+
+        for _ in range(3):
+            step()
+        barrier()
     sampler = ClockSampler(local_rank) if sample_clocks else None
     if sampler:
         sampler.start()
@@ -357,6 +377,8 @@ def main() -> None:
     ap.add_argument("--num-splits", type=int, default=0, help="0 = fixed 1024-key segments")
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="time eager calls of the decode op instead of replays of its CUDA graph")
     ap.add_argument("--no-moe", action="store_true", help="skip the MoE / GEMM / prefill / EP sections")
     ap.add_argument("--only", choices=["moe", "gemm", "prefill", "ep"], default=None,
                     help="run one secondary section alone (for profiling) and print its JSON")
@@ -443,7 +465,9 @@ def main() -> None:
                        "shard_balance_max_over_mean": max_bytes / (all_bytes / world),
                        "segments": nseg,
                        "l2": f"each rank's KV ({kv_bytes / 1e6:.0f} MB on rank 0) exceeds the 126 MB L2",
-                       "timing": "cuda events, max over ranks"},
+                       "timing": "cuda events, max over ranks",
+                       "launch": "eager op calls" if args.no_graph else
+                                 "replays of the op's CUDA graph (value); eager calls with host copies (e2e)"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm"],
                          # DRAM read + write bytes per launch: measured with ncu on the 32-sequence
