@@ -284,7 +284,8 @@ def time_decode(strix, batch, args, world, dist, local_rank, sample_clocks: bool
     """(total ms over K steps, per-step ms list, e2e total ms, clocks, out, launches per
     step, h2d bytes, d2h bytes) for one rank's batch."""
     out = torch.empty_like(batch.q)
-    nseg = strix._lib.load().strix_attn_decode_segments(args.num_splits, batch.block_table.size(1), 16)
+    nseg = strix._lib.load().strix_attn_decode_segments_n(batch.q.size(0), args.num_splits,
+                                                          batch.block_table.size(1), 16)
     launches = 2 if nseg > 1 else 1
 
     def step():

@@ -70,7 +70,13 @@ int strix_version(void);
  * ---------------------------------------------------------------------- */
 #define STRIX_DECODE_AUTO_KEYS 1024
 
-/* Number of key segments the call will use (>= 1), or -1 on bad arguments. */
+/* Number of key segments a call over nseq sequences will use (>= 1), or -1 on bad
+ * arguments. num_splits 0: segments of STRIX_DECODE_AUTO_KEYS keys, of half that for
+ * a batch so small (nseq x max_blocks x block_size below one wave of such segments)
+ * that the SMs would otherwise stay half empty - a shard of a batch spread over
+ * several GPUs. strix_attn_decode_segments is the count for a large batch. */
+int64_t strix_attn_decode_segments_n(int64_t nseq, int64_t num_splits, int64_t max_blocks,
+                                     int64_t block_size);
 int64_t strix_attn_decode_segments(int64_t num_splits, int64_t max_blocks,
                                    int64_t block_size);
 

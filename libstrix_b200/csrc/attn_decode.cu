@@ -637,31 +637,41 @@ int launch_decode(dim3 grid, cudaStream_t st, const DecodeArgs& a, size_t smem) 
 
 using namespace strix;
 
-// Keys per segment in automatic mode; STRIX_DECODE_SEG_KEYS (a multiple of 16)
-// overrides the default for tuning runs.
-static int auto_seg_keys() {
-  static const int keys = [] {
+// Keys per segment in automatic mode: STRIX_DECODE_AUTO_KEYS, halved for a batch so
+// small that 1,024-key segments would not even fill one wave of CTAs (a shard of 8
+// long sequences: 3,360 -> 3,780 GB/s; at 16 sequences the longer segments win
+// again). STRIX_DECODE_SEG_KEYS (a multiple of 16) fixes the length for tuning runs.
+static int auto_seg_keys(int64_t nseq, int64_t max_keys) {
+  static const int fixed = [] {
     const char* e = getenv("STRIX_DECODE_SEG_KEYS");
     const int v = e ? atoi(e) : 0;
-    return (v >= 64 && v % 16 == 0) ? v : STRIX_DECODE_AUTO_KEYS;
+    return (v >= 64 && v % 16 == 0) ? v : 0;
   }();
-  return keys;
+  if (fixed) return fixed;
+  constexpr int64_t kWaveKeys = int64_t(148) * 4 * STRIX_DECODE_AUTO_KEYS;   // one CTA slot per segment
+  return (nseq > 0 && nseq * max_keys < kWaveKeys) ? STRIX_DECODE_AUTO_KEYS / 2 : STRIX_DECODE_AUTO_KEYS;
 }
 
-extern "C" int64_t strix_attn_decode_segments(int64_t num_splits, int64_t max_blocks,
-                                              int64_t block_size) {
+extern "C" int64_t strix_attn_decode_segments_n(int64_t nseq, int64_t num_splits, int64_t max_blocks,
+                                                int64_t block_size) {
   if (num_splits < 0 || num_splits > 64) return -1;
   if (num_splits > 0) return num_splits;
   if (max_blocks < 0 || block_size <= 0) return -1;
   const int64_t keys = max_blocks * block_size;
-  const int64_t n = (keys + auto_seg_keys() - 1) / auto_seg_keys();
+  const int64_t seg = auto_seg_keys(nseq, keys);
+  const int64_t n = (keys + seg - 1) / seg;
   return n < 1 ? 1 : n;
+}
+
+extern "C" int64_t strix_attn_decode_segments(int64_t num_splits, int64_t max_blocks,
+                                              int64_t block_size) {
+  return strix_attn_decode_segments_n(0, num_splits, max_blocks, block_size);
 }
 
 extern "C" int64_t strix_attn_decode_workspace(int64_t nseq, int64_t hq, int64_t head_dim,
                                                int64_t num_splits, int64_t max_blocks,
                                                int64_t block_size) {
-  const int64_t nseg = strix_attn_decode_segments(num_splits, max_blocks, block_size);
+  const int64_t nseg = strix_attn_decode_segments_n(nseq, num_splits, max_blocks, block_size);
   if (nseg < 0) return -1;
   if (nseg == 1) return 0;
   return nseq * hq * nseg * (head_dim + 2) * int64_t(sizeof(float));
@@ -696,7 +706,7 @@ extern "C" int strix_attn_decode_bf16(
               "out must match q");
   STRIX_CHECK(num_splits >= 0 && num_splits <= 64, "num_splits in [1, 64]");
   STRIX_CHECK(window_left >= -1, "window_left >= -1");
-  const int64_t nseg = strix_attn_decode_segments(num_splits, max_blocks, block_size);
+  const int64_t nseg = strix_attn_decode_segments_n(nseq, num_splits, max_blocks, block_size);
   STRIX_CHECK(nseg >= 1 && nseg <= 65535, "segment count out of range");
   STRIX_CHECK(nseg == 1 || nseq == 0 || workspace != nullptr, "split-KV needs a workspace");
   STRIX_CHECK(nseq <= 65535, "at most 65535 sequences per call");
@@ -724,7 +734,7 @@ extern "C" int strix_attn_decode_bf16(
   a.hq = int(hq), a.hkv = int(hkv), a.g = int(g);
   a.hpc = hkv % 4 == 0 ? 4 : (hkv % 2 == 0 ? 2 : 1);
   a.nseg = int(nseg);
-  a.seg_keys = num_splits == 0 ? auto_seg_keys() : 0;
+  a.seg_keys = num_splits == 0 ? auto_seg_keys(nseq, max_blocks * block_size) : 0;
   a.win_left = int(window_left);
   a.scale_log2 = float(scale) * kLog2e;
 

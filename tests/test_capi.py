@@ -28,6 +28,12 @@ def test_decode_segments_and_workspace():
     assert lib.strix_attn_decode_segments(0, 4096, 16) == 64
     assert lib.strix_attn_decode_segments(0, 0, 16) == 1
     assert lib.strix_attn_decode_segments(65, 1, 16) == -1
+    # a batch below one wave of 1024-key segments gets 512-key segments
+    assert lib.strix_attn_decode_segments_n(64, 0, 4096, 16) == 64
+    assert lib.strix_attn_decode_segments_n(16, 0, 4096, 16) == 64
+    assert lib.strix_attn_decode_segments_n(8, 0, 4096, 16) == 128
+    assert lib.strix_attn_decode_segments_n(8, 4, 4096, 16) == 4
+    assert lib.strix_attn_decode_workspace(8, 32, 128, 0, 4096, 16) == 8 * 32 * 128 * 130 * 4
     assert lib.strix_attn_decode_workspace(3, 32, 128, 1, 10, 16) == 0
     assert lib.strix_attn_decode_workspace(3, 32, 128, 4, 10, 16) == 3 * 32 * 4 * 130 * 4
 
