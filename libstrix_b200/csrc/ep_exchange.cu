@@ -101,6 +101,7 @@ __global__ void __launch_bounds__(256) ep_plan_kernel(const int32_t* __restrict_
                                                       int32_t* __restrict__ counts, int tokens,
                                                       int top_k, int experts_per_rank, int world,
                                                       const int32_t* __restrict__ placement) {
+  pdl_enter();
   __shared__ int s_warp[8];
   const int d = blockIdx.x, tid = threadIdx.x;
   int placed = 0;
@@ -162,6 +163,7 @@ __global__ void __launch_bounds__(kEpWarps * 32) ep_dispatch_kernel(
     int tokens, int chunks, int top_k, int experts_per_rank, int world, int rank, int64_t cap,
     const int32_t* __restrict__ placement,
     int32_t epoch) {
+  pdl_enter();
   const int lane = threadIdx.x & 31;
   const int warps = gridDim.x * kEpWarps;
   const int meta_st = 1 + 2 * top_k;
@@ -205,6 +207,7 @@ __global__ void __launch_bounds__(256) ep_prepare_kernel(
     float* __restrict__ wts,
     int32_t* __restrict__ rows_out, int world, int64_t cap, int top_k, int32_t epoch,
     uint32_t spin_limit) {
+  pdl_enter();
   __shared__ int s_ok;
   const int64_t first = int64_t(blockIdx.x) * 256, total = int64_t(world) * cap * top_k;
   if (threadIdx.x == 0) {
@@ -237,6 +240,7 @@ __global__ void __launch_bounds__(kEpWarps * 32) ep_return_kernel(
     const int32_t* __restrict__ meta, const int32_t* __restrict__ counts, const EpPeers peers,
     int32_t* __restrict__ ticket, int world, int rank, int64_t cap, int top_k, int hidden8,
     int32_t epoch) {
+  pdl_enter();
   const int lane = threadIdx.x & 31;
   const int warps = gridDim.x * kEpWarps;
   const int64_t rows = int64_t(world) * cap;
@@ -272,6 +276,7 @@ __global__ void __launch_bounds__(kEpWarps * 32) ep_combine_kernel(
     const uint16_t* ret, const int32_t* rflags, const int32_t* __restrict__ tok_pos,
     uint16_t* __restrict__ out, int64_t out_st, int tokens, int hidden8, int world, int64_t cap,
     int32_t epoch, uint32_t spin_limit) {
+  pdl_enter();
   __shared__ int s_ok;
   if (threadIdx.x == 0) {
     bool ok = true;
@@ -310,6 +315,7 @@ __global__ void __launch_bounds__(256) permute_byte_rows_kernel(
     const uint4* __restrict__ x, int64_t x_st16, uint4* __restrict__ y, int64_t y_st16, int64_t rows,
     int chunks, int top_k, const int32_t* __restrict__ slot_pos, const int32_t* __restrict__ sorted_ids,
     const int32_t* __restrict__ num_post, int64_t rows_cap, int64_t num_valid) {
+  pdl_enter();
   const int64_t idx = int64_t(blockIdx.x) * 256 + threadIdx.x;
   const int64_t row = idx / chunks;
   const int ch = int(idx % chunks);
@@ -419,7 +425,7 @@ extern "C" int strix_ep_plan(const int32_t* topk_ids, int32_t* tok_pos, int32_t*
               "pointers must not be NULL");
   STRIX_CHECK(tokens >= 0 && top_k >= 1 && experts_per_rank != 0 && world >= 1 && world <= kEpMaxWorld,
               "bad sizes");
-  ep_plan_kernel<<<unsigned(world), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_chain(ep_plan_kernel, unsigned(world), 256, 0, static_cast<cudaStream_t>(stream), 
       topk_ids, tok_pos, counts, int(tokens), int(top_k), int(experts_per_rank), int(world), placement);
   return launch_status("ep_plan");
 }
@@ -443,7 +449,7 @@ extern "C" int strix_ep_dispatch(const void* x, const int32_t* topk_ids, const f
   const int chunks = int(row_bytes / 16);
   // an empty rank still raises its flags
   const unsigned grid = row_grid(tokens);
-  ep_dispatch_kernel<<<grid, kEpWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_chain(ep_dispatch_kernel, grid, kEpWarps * 32, 0, static_cast<cudaStream_t>(stream), 
       static_cast<const uint4*>(x), x_stride_bytes / 16, topk_ids, topk_weights, tok_pos, counts, peers,
       ticket, int(tokens), chunks, int(top_k), int(experts_per_rank), int(world), int(rank), cap,
       placement, int32_t(epoch));
@@ -458,7 +464,7 @@ extern "C" int strix_ep_prepare(const int32_t* meta, const int32_t* counts, cons
               "pointers must not be NULL");
   STRIX_CHECK(world >= 1 && world <= kEpMaxWorld && cap >= 1 && top_k >= 1, "bad sizes");
   const int64_t total = world * cap * top_k;
-  ep_prepare_kernel<<<unsigned((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_chain(ep_prepare_kernel, unsigned((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream), 
       meta, counts, flags, ids, weights, rows_per_source, int(world), cap, int(top_k), int32_t(epoch),
       spin_limit > 0 ? uint32_t(spin_limit) : kEpSpinDefault);
   return launch_status("ep_prepare");
@@ -475,7 +481,7 @@ extern "C" int strix_ep_return(const void* y, const int32_t* ids, const int32_t*
   EpPeers peers;
   if (int rc = fill_peers(&peers, nullptr, nullptr, nullptr, nullptr, peer_ret, peer_rflags, world)) return rc;
   STRIX_CHECK(rank >= 0 && rank < world && cap >= 1, "bad rank");
-  ep_return_kernel<<<row_grid(world * cap), kEpWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_chain(ep_return_kernel, row_grid(world * cap), kEpWarps * 32, 0, static_cast<cudaStream_t>(stream), 
       static_cast<const uint16_t*>(y), y_stride, ids, meta, counts, peers, ticket, int(world), int(rank),
       cap, int(top_k), int(hidden / 8), int32_t(epoch));
   return launch_status("ep_return");
@@ -489,7 +495,7 @@ extern "C" int strix_ep_combine(const void* ret, const int32_t* rflags, const in
   STRIX_CHECK(hidden > 0 && hidden % 8 == 0 && out_stride % 8 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0,
               "hidden must be a multiple of 8");
   STRIX_CHECK(tokens >= 0 && tokens <= cap && world >= 1 && world <= kEpMaxWorld, "bad sizes");
-  ep_combine_kernel<<<row_grid(tokens), kEpWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_chain(ep_combine_kernel, row_grid(tokens), kEpWarps * 32, 0, static_cast<cudaStream_t>(stream), 
       static_cast<const uint16_t*>(ret), rflags, tok_pos, static_cast<uint16_t*>(out), out_stride, int(tokens),
       int(hidden / 8), int(world), cap, int32_t(epoch), spin_limit > 0 ? uint32_t(spin_limit) : kEpSpinDefault);
   return launch_status("ep_combine");
@@ -508,7 +514,7 @@ extern "C" int strix_moe_permute_rows(const void* x, void* y, const int32_t* slo
   if (rows + sorted_rows == 0) return STRIX_OK;
   const int chunks = int(row_bytes / 16);
   const int64_t threads = (rows + sorted_rows) * chunks;
-  permute_byte_rows_kernel<<<unsigned((threads + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_chain(permute_byte_rows_kernel, unsigned((threads + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream), 
       static_cast<const uint4*>(x), x_stride_bytes / 16, static_cast<uint4*>(y), y_stride_bytes / 16, rows,
       chunks, int(top_k), slot_pos, sorted_ids, num_post_padded, sorted_rows, rows * top_k);
   return launch_status("moe_permute_rows");

@@ -100,6 +100,7 @@ __device__ __forceinline__ float mx_gate(float g, int act) {
 __global__ void __launch_bounds__(kMxThreads, 1) moe_gemm_mxfp4_umma_kernel(
     const MxArgs p, const __grid_constant__ CUtensorMap map_a,
     const __grid_constant__ CUtensorMap map_w) {
+  pdl_enter();
   using L = MxLayout;
   constexpr int S = kMxStages;
   extern __shared__ uint8_t raw_smem[];
@@ -364,6 +365,7 @@ __global__ void __launch_bounds__(256) permute_rows_kernel(
     int64_t tokens, int chunks, int top_k, const int32_t* __restrict__ slot_pos,
     const int32_t* __restrict__ sorted_ids, const int32_t* __restrict__ num_post, int64_t rows_cap,
     int64_t num_valid) {
+  pdl_enter();
   const int64_t idx = int64_t(blockIdx.x) * 256 + threadIdx.x;
   const int64_t row = idx / chunks;
   const int ch = int(idx % chunks);
@@ -399,7 +401,7 @@ extern "C" int strix_moe_permute_bf16(const void* x, void* y, const int32_t* slo
   if (tokens + rows == 0) return STRIX_OK;
   const int chunks = int(k / 8);
   const int64_t threads = (tokens + rows) * chunks;
-  permute_rows_kernel<<<unsigned((threads + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_chain(permute_rows_kernel, unsigned((threads + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream), 
       static_cast<const uint4*>(x), x_stride / 8, static_cast<uint4*>(y), y_stride / 8, tokens, chunks,
       int(top_k), slot_pos, sorted_ids, num_post_padded, rows, tokens * top_k);
   return launch_status("moe_permute_bf16");
@@ -462,7 +464,7 @@ extern "C" int strix_moe_gemm_mxfp4_sorted(
     STRIX_CUDA(cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev));
     done[dev] = true;
   }
-  moe_gemm_mxfp4_umma_kernel<<<sms[dev], kMxThreads, MxLayout::kSmem, static_cast<cudaStream_t>(stream)>>>(
+  launch_chain(moe_gemm_mxfp4_umma_kernel, sms[dev], kMxThreads, MxLayout::kSmem, static_cast<cudaStream_t>(stream), 
       p, map_a, map_w);
   return launch_status("moe_gemm_mxfp4_umma");
 }
