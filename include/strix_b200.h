@@ -45,11 +45,9 @@ int strix_version(void);
  *                 kv_int8 != 0: int8 bytes (strides multiples of 4) with fp32
  *                 dequant scales k_scale / v_scale [blocks, block_size, hkv]
  *                 (element strides ks_* / vs_*), one per (key, head).
- *                 kv_int8 == 0 (bf16 caches, the reference's native form) is NOT
- *                 built in this entry point: it returns STRIX_ERR_INVALID. The
- *                 torch op attn_decode_bf16 serves bf16 caches through
- *                 strix_attn_prefill_bf16 with one query per sequence - correct,
- *                 but without split-KV (one CTA per sequence and head).
+ *                 kv_int8 == 0: bf16 caches, the reference's native form (rows on
+ *                 16-byte boundaries: strides multiples of 8; scales NULL), head_dim
+ *                 64 or 128, with the same split-KV partials and reduce.
  *   seq_lens      int32 [nseq]; the query sits at position seq_lens[n] - 1.
  *   block_table   int32 [nseq, >= ceil(seq_len / block_size)], row stride bt_stride.
  *   sinks         optional fp32 [hq]: one extra unscaled natural-log logit per
@@ -65,8 +63,8 @@ int strix_version(void);
  *                 [nseq, hq, nseg, head_dim] followed by (m, l) pairs
  *                 [nseq, hq, nseg, 2].
  *
- * Built geometries: head_dim 128 or 256, hq / hkv in 1..8, block_size a
- * multiple of 16. Others return STRIX_ERR_INVALID.
+ * Built geometries: head_dim 128 or 256 (int8 caches), 64 or 128 (bf16 caches),
+ * hq / hkv in 1..8, block_size a multiple of 16. Others return STRIX_ERR_INVALID.
  * ---------------------------------------------------------------------- */
 #define STRIX_DECODE_AUTO_KEYS 1024
 

@@ -554,6 +554,230 @@ attn_decode_q8_kernel(const DecodeArgs a) {
   }
 }
 
+// ---------------------------------------------------------------------------
+// The same operation over a bf16 KV cache (the reference's native form). One warp
+// per KV head of the CTA's group, no cross-warp merge: a warp owns 16-key tiles of
+// 2 x 16 x D bf16 that arrive through a per-warp cp.async ring (3 stages, 16-byte
+// chunks XOR-swizzled by row); S^T = K Q^T and O^T = V^T P^T are bf16
+// mma.sync.m16n8k16 whose A fragments come from ldmatrix (transposing for V), so
+// neither K nor V is touched by an ordinary instruction. Softmax, split-KV
+// partials and the reduce are those of the int8 kernel.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                               uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+      "{%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+constexpr int kBfStages = 3;
+
+template <int D>
+__global__ void __launch_bounds__(128) attn_decode_bf16kv_kernel(const DecodeArgs a) {
+  pdl_enter();
+  constexpr int kRow = D * 2;                 // bytes of a cache row
+  constexpr int kChunks = kRow / 16;          // 16-byte chunks per row
+  constexpr int kTile = 16 * kRow;            // K (or V) rows of a tile
+  constexpr int kStage = 2 * kTile;
+  extern __shared__ __align__(128) uint8_t dyn_smem[];
+  const int seg = blockIdx.x, hgrp = blockIdx.y, n = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, c = lane & 3;
+  const int kvh = hgrp * a.hpc + warp;        // blockDim.x = 32 * hpc: one warp per KV head
+  const int G = a.g;
+  const int h0 = kvh * G;
+
+  const int kv_len = a.seq_lens[n];
+  const int pos = kv_len - 1;
+  const int k_lo = a.win_left >= 0 ? max(0, pos - a.win_left) : 0;
+  const int seg_len = a.seg_keys > 0 ? a.seg_keys
+                                     : ((kv_len - k_lo + a.nseg - 1) / a.nseg + 15) / 16 * 16;
+  const int k_begin = k_lo + seg * seg_len;
+  const int k_end = min(kv_len, k_begin + seg_len);
+  const bool single = a.nseg == 1;
+
+  if (k_begin >= k_end) {                     // empty segment (block-uniform)
+    for (int j = 0; j < 2; ++j) {
+      const int hl = 2 * c + j;
+      if (hl >= G) continue;
+      const int h = h0 + hl;
+      if (single) {
+        for (int d = g; d < D; d += 8)
+          a.out[int64_t(n) * a.o_st + int64_t(h) * a.o_sh + d] = __float2bfloat16(0.f);
+      } else if (g == 0) {
+        float* ml = a.ml_part + ((int64_t(n) * a.hq + h) * a.nseg + seg) * 2;
+        ml[0] = -INFINITY;
+        ml[1] = 0.f;
+      }
+    }
+    return;
+  }
+
+  // Q^T fragments: b0 / b1 of k-step ks = q[head g][16 ks + 2c, + 1] / [16 ks + 8 + 2c, + 1]
+  uint32_t qb[D / 16][2];
+  {
+    const __nv_bfloat16* qp = a.q + int64_t(n) * a.q_st + int64_t(h0 + g) * a.q_sh;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      qb[ks][0] = g < G ? *reinterpret_cast<const uint32_t*>(qp + 16 * ks + 2 * c) : 0u;
+      qb[ks][1] = g < G ? *reinterpret_cast<const uint32_t*>(qp + 16 * ks + 8 + 2 * c) : 0u;
+    }
+  }
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float acc[D / 16][4];
+#pragma unroll
+  for (int i = 0; i < D / 16; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+
+  const int t_begin = k_begin >> 4, t_end = (k_end + 15) >> 4;
+  const int32_t* bt = a.bt + int64_t(n) * a.bt_stride;
+  const int bs = a.block_size;
+  uint8_t* const ring = dyn_smem + warp * (kBfStages * kStage);
+  const uint32_t ring_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring));
+  const uint8_t* const kc = static_cast<const uint8_t*>(a.kc) + int64_t(kvh) * a.k_sh * 2;
+  const uint8_t* const vc = static_cast<const uint8_t*>(a.vc) + int64_t(kvh) * a.v_sh * 2;
+
+  int t_issue = t_begin, stage_issue = 0;
+  auto issue_next = [&]() {
+    if (t_issue < t_end) {
+      const int blk = bt[(t_issue * 16) / bs];
+      const int off = (t_issue * 16) % bs;
+      const uint8_t* kp = kc + (int64_t(blk) * a.k_sb + int64_t(off) * a.k_ss) * 2;
+      const uint8_t* vp = vc + (int64_t(blk) * a.v_sb + int64_t(off) * a.v_ss) * 2;
+      const uint32_t dst = ring_s + stage_issue * kStage;
+#pragma unroll
+      for (int j = 0; j < 16 * kChunks / 32; ++j) {
+        const int idx = j * 32 + lane, row = idx / kChunks, ch = idx % kChunks;
+        const uint32_t d = dst + row * kRow + ((ch ^ (row & 7)) << 4);
+        cp_async_16(d, kp + int64_t(row) * a.k_ss * 2 + ch * 16);
+        cp_async_16(d + kTile, vp + int64_t(row) * a.v_ss * 2 + ch * 16);
+      }
+    }
+    cp_async_commit();
+    ++t_issue;
+    stage_issue = stage_issue + 1 == kBfStages ? 0 : stage_issue + 1;
+  };
+#pragma unroll
+  for (int i = 0; i < kBfStages - 1; ++i) issue_next();
+  int stage = 0;
+  for (int t = t_begin; t < t_end; ++t) {
+    issue_next();
+    cp_async_wait<kBfStages - 1>();
+    __syncwarp();
+    const uint32_t ks_s = ring_s + stage * kStage, vs_s = ks_s + kTile;
+    const int key0 = t * 16;
+    // rows of keys outside [k_begin, k_end) may hold anything (NaN bit patterns too):
+    // their scores are masked below, their V rows are zeroed here
+    if (key0 < k_begin || key0 + 16 > k_end) {
+      for (int idx = lane; idx < 16 * kChunks; idx += 32) {
+        const int row = idx / kChunks;
+        const int key = key0 + row;
+        if (key < k_begin || key >= k_end)
+          *reinterpret_cast<uint4*>(ring + stage * kStage + kTile + idx * 16) = make_uint4(0u, 0u, 0u, 0u);
+      }
+      __syncwarp();
+    }
+    // S^T[16 keys, 8 heads] = K Q^T
+    float sc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      uint32_t af[4];
+      const int row = lane & 15, ch = 2 * ks + (lane >> 4);
+      ldmatrix_x4(af, ks_s + row * kRow + ((ch ^ (row & 7)) << 4));
+      mma_bf16_16816(sc, af, qb[ks][0], qb[ks][1]);
+    }
+    const int ka = key0 + g, kb = ka + 8;
+    const bool va = ka >= k_begin && ka < k_end, vb = kb >= k_begin && kb < k_end;
+    const float x0 = va ? sc[0] * a.scale_log2 : -INFINITY, x1 = va ? sc[1] * a.scale_log2 : -INFINITY;
+    const float x2 = vb ? sc[2] * a.scale_log2 : -INFINITY, x3 = vb ? sc[3] * a.scale_log2 : -INFINITY;
+    const float c0 = fmaxf(x0, x2), c1 = fmaxf(x1, x3);
+    if (__any_sync(0xffffffffu, c0 > m[0] + kLazy || c1 > m[1] + kLazy)) {
+      float mx0 = c0, mx1 = c1;
+#pragma unroll
+      for (int o = 4; o < 32; o <<= 1) {
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+      }
+      const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
+      const float al0 = mn0 == -INFINITY ? 1.f : fast_exp2(m[0] - mn0);
+      const float al1 = mn1 == -INFINITY ? 1.f : fast_exp2(m[1] - mn1);
+      m[0] = mn0, m[1] = mn1;
+      l[0] *= al0, l[1] *= al1;
+#pragma unroll
+      for (int i = 0; i < D / 16; ++i) {
+        acc[i][0] *= al0, acc[i][1] *= al1, acc[i][2] *= al0, acc[i][3] *= al1;
+      }
+    }
+    const float r0 = m[0] == -INFINITY ? 0.f : m[0], r1 = m[1] == -INFINITY ? 0.f : m[1];
+    const float p0 = fast_exp2(x0 - r0), p1 = fast_exp2(x1 - r1);
+    const float p2 = fast_exp2(x2 - r0), p3 = fast_exp2(x3 - r1);
+    l[0] += p0 + p2;
+    l[1] += p1 + p3;
+    const uint32_t b0 = movmatrix_trans(pack_bf16x2(p0, p1));
+    const uint32_t b1 = movmatrix_trans(pack_bf16x2(p2, p3));
+    // O^T[D, 8 heads] += V^T P^T
+#pragma unroll
+    for (int i = 0; i < D / 16; ++i) {
+      uint32_t af[4];
+      const int key = (lane & 7) + 8 * (lane >> 4), ch = 2 * i + ((lane >> 3) & 1);
+      ldmatrix_x4_trans(af, vs_s + key * kRow + ((ch ^ (key & 7)) << 4));
+      mma_bf16_16816(acc[i], af, b0, b1);
+    }
+    __syncwarp();
+    stage = stage + 1 == kBfStages ? 0 : stage + 1;
+  }
+  cp_async_wait<0>();
+
+  // l is a per-lane partial over this lane's keys: the eight lanes of a head pair add up
+#pragma unroll
+  for (int o = 4; o < 32; o <<= 1) {
+    l[0] += __shfl_xor_sync(0xffffffffu, l[0], o);
+    l[1] += __shfl_xor_sync(0xffffffffu, l[1], o);
+  }
+  // acc[i][j]: dim 16 i + g (j = 0, 1) or 16 i + g + 8 (j = 2, 3), head 2c + (j & 1)
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int hl = 2 * c + j;
+    if (hl >= G) continue;
+    const int h = h0 + hl;
+    if (single) {
+      float inv = l[j] > 0.f ? 1.f / l[j] : 0.f;
+      if (a.sinks != nullptr) {
+        const float s2 = a.sinks[h] * kLog2e;
+        const float mf = fmaxf(m[j], s2);
+        const float al = m[j] == -INFINITY ? 0.f : fast_exp2(m[j] - mf);
+        inv = al / (l[j] * al + fast_exp2(s2 - mf));
+      }
+      __nv_bfloat16* op = a.out + int64_t(n) * a.o_st + int64_t(h) * a.o_sh;
+#pragma unroll
+      for (int i = 0; i < D / 16; ++i) {
+        op[16 * i + g] = __float2bfloat16(acc[i][j] * inv);
+        op[16 * i + g + 8] = __float2bfloat16(acc[i][2 + j] * inv);
+      }
+    } else {
+      const int64_t row = (int64_t(n) * a.hq + h) * a.nseg + seg;
+      float* op = a.o_part + row * D;
+#pragma unroll
+      for (int i = 0; i < D / 16; ++i) {
+        op[16 * i + g] = acc[i][j];
+        op[16 * i + g + 8] = acc[i][2 + j];
+      }
+      if (g == 0) {
+        a.ml_part[2 * row] = m[j];
+        a.ml_part[2 * row + 1] = l[j];
+      }
+    }
+  }
+}
+
 // Combines the segments of one (sequence, head): w_s = 2^(m_s - m),
 // O = sum w_s O_s / sum w_s l_s; empty segments (m = -inf) weigh nothing.
 // Follows attn_decode_reduce_kernel (csrc/attn/attn_decode_bf16.hip:276-300). Four
@@ -689,17 +913,26 @@ extern "C" int strix_attn_decode_bf16(
   STRIX_CHECK(nseq >= 0 && hq > 0 && hkv > 0, "q [N, H, D], caches [blocks, block_size, Hkv, D]");
   STRIX_CHECK(hq % hkv == 0, "Hq %% Hkv");
   const int64_t g = hq / hkv;
-  STRIX_CHECK(kv_int8 != 0, "attn_decode_bf16: bf16 KV cache not built (int8 only)");
-  STRIX_CHECK((head_dim == 128 || head_dim == 256) && g <= 8,
-              "attn_decode_bf16 int8: head_dim %lld GQA %lld not built (128, 256: GQA 1-8)",
-              (long long)head_dim, (long long)g);
-  STRIX_CHECK(k_scale != nullptr && v_scale != nullptr, "int8 KV needs k_scale and v_scale");
+  if (kv_int8) {
+    STRIX_CHECK((head_dim == 128 || head_dim == 256) && g <= 8,
+                "attn_decode_bf16 int8: head_dim %lld GQA %lld not built (128, 256: GQA 1-8)",
+                (long long)head_dim, (long long)g);
+    STRIX_CHECK(k_scale != nullptr && v_scale != nullptr, "int8 KV needs k_scale and v_scale");
+    STRIX_CHECK(k_sb % 4 == 0 && k_ss % 4 == 0 && k_sh % 4 == 0 && v_sb % 4 == 0 &&
+                    v_ss % 4 == 0 && v_sh % 4 == 0,
+                "aligned cache rows");
+    STRIX_CHECK((reinterpret_cast<uintptr_t>(key_cache) | reinterpret_cast<uintptr_t>(value_cache)) % 4 == 0,
+                "aligned cache rows");
+  } else {
+    STRIX_CHECK((head_dim == 64 || head_dim == 128) && g <= 8,
+                "attn_decode_bf16 bf16 KV: head_dim %lld GQA %lld not built (64, 128: GQA 1-8)",
+                (long long)head_dim, (long long)g);
+    STRIX_CHECK(k_sb % 8 == 0 && k_ss % 8 == 0 && k_sh % 8 == 0 && v_sb % 8 == 0 &&
+                    v_ss % 8 == 0 && v_sh % 8 == 0 &&
+                    (reinterpret_cast<uintptr_t>(key_cache) | reinterpret_cast<uintptr_t>(value_cache)) % 16 == 0,
+                "bf16 cache rows must be 16-byte aligned");
+  }
   STRIX_CHECK(block_size > 0 && block_size % 16 == 0, "block_size must be a multiple of 16");
-  STRIX_CHECK(k_sb % 4 == 0 && k_ss % 4 == 0 && k_sh % 4 == 0 && v_sb % 4 == 0 &&
-                  v_ss % 4 == 0 && v_sh % 4 == 0,
-              "aligned cache rows");
-  STRIX_CHECK((reinterpret_cast<uintptr_t>(key_cache) | reinterpret_cast<uintptr_t>(value_cache)) % 4 == 0,
-              "aligned cache rows");
   STRIX_CHECK(q_st % 4 == 0 && q_sh % 4 == 0 && reinterpret_cast<uintptr_t>(q) % 8 == 0,
               "q must be bf16 with a contiguous head_dim");
   STRIX_CHECK(o_st % 2 == 0 && o_sh % 2 == 0 && reinterpret_cast<uintptr_t>(out) % 4 == 0,
@@ -738,6 +971,37 @@ extern "C" int strix_attn_decode_bf16(
   a.win_left = int(window_left);
   a.scale_log2 = float(scale) * kLog2e;
 
+  if (!kv_int8) {
+    // bf16 caches: one warp per KV head of the group, per-warp cp.async ring
+    const dim3 bgrid{unsigned(nseg), unsigned(hkv / a.hpc), unsigned(nseq)};
+    cudaStream_t bst = static_cast<cudaStream_t>(stream);
+    const size_t smem = size_t(a.hpc) * kBfStages * 2 * 16 * size_t(head_dim) * 2;
+    auto bkernel = head_dim == 128 ? attn_decode_bf16kv_kernel<128> : attn_decode_bf16kv_kernel<64>;
+    if (smem > 48 * 1024) {
+      static bool done[64] = {};
+      int dev = 0;
+      STRIX_CUDA(cudaGetDevice(&dev));
+      if (dev < 0 || dev >= 64 || !done[dev]) {
+        STRIX_CUDA(cudaFuncSetAttribute(attn_decode_bf16kv_kernel<128>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * kBfStages * 2 * 16 * 256));
+        if (dev >= 0 && dev < 64) done[dev] = true;
+      }
+    }
+    launch_chain(bkernel, bgrid, 32 * a.hpc, smem, bst, a);
+    int brc = launch_status("attn_decode_bf16kv");
+    if (brc != STRIX_OK) return brc;
+    if (nseg > 1) {
+      const dim3 rgrid{unsigned(hq), unsigned(nseq), 1u};
+      if (head_dim == 128)
+        launch_chain(attn_decode_reduce_kernel<128>, rgrid, kReduceParts * 64, 0, bst, a.out, a.o_part,
+                     a.ml_part, a.nseg, a.hq, o_st, o_sh, sinks);
+      else
+        launch_chain(attn_decode_reduce_kernel<64>, rgrid, kReduceParts * 32, 0, bst, a.out, a.o_part,
+                     a.ml_part, a.nseg, a.hq, o_st, o_sh, sinks);
+      brc = launch_status("attn_decode_reduce");
+    }
+    return brc;
+  }
   const bool aligned = (k_sb | k_ss | k_sh | v_sb | v_ss | v_sh) % 16 == 0 &&
                        (reinterpret_cast<uintptr_t>(key_cache) |
                         reinterpret_cast<uintptr_t>(value_cache)) % 16 == 0;

@@ -325,10 +325,13 @@ KERNELS: list[Kernel] = [
     _decode_row(256, 6, "head 256 GQA 6 (two MMA columns idle)"),
     _decode_row(256, 2, "head 256 GQA 2 (sliding layers)"),
     *[Kernel("attn_decode_bf16", "attn_decode",
-             "bf16 KV cache: one query per sequence through the prefill kernel (q_len = 1)",
+             "bf16 KV cache, split-KV: one warp per KV head, per-warp cp.async ring of 16-key "
+             "tiles, K and V^T fragments by ldmatrix, bf16 m16n8k16 MMAs (rows on 16-byte "
+             "boundaries, GQA 1-8; other layouts go through the prefill kernel with one query "
+             "per sequence)",
              {"head_dim": hd, "gqa": Range(1, 64), "queries": 1, "dtype": "bf16",
               "kv_dtype": ("bf16",), "window": (True, False), "sinks": (True, False)},
-             {"bound": "hbm", "note": "functional path; the int8 rows are the tuned ones"})
+             {"tile_keys": 16, "mma": "m16n8k16 bf16, keys as M", "bound": "hbm"})
       for hd in (128, 64)],
     *[Kernel(
         "attn_prefill_bf16", "attn_prefill",

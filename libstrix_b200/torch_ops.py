@@ -100,9 +100,12 @@ def attn_decode_bf16(
         _check(sinks.dtype == torch.float32 and sinks.dim() == 1 and sinks.size(0) == q.size(1)
                and sinks.is_contiguous(), "sinks must be contiguous fp32 [Hq]")
     _check(0 <= num_splits <= 64, "num_splits in [1, 64]")
-    if not q8:
-        # bf16 caches: one query per sequence is the prefill kernel with q_len = 1
-        # (head 64 / 128); the int8 kernel below is the tuned decode path
+    bf16_rows_ok = not q8 and d in (64, 128) and q.size(1) // key_cache.size(2) <= 8 and all(
+        st % 8 == 0 for t in (key_cache, value_cache) for st in t.stride()[:3]) and \
+        key_cache.data_ptr() % 16 == 0 and value_cache.data_ptr() % 16 == 0
+    if not q8 and not bf16_rows_ok:
+        # bf16 caches the split-KV decode kernel does not take (rows off 16-byte
+        # boundaries, other head sizes): the prefill kernel with one query per sequence
         nseq = q.size(0)
         cu = torch.arange(nseq + 1, dtype=torch.int32, device=q.device)
         attn_prefill_bf16(out, q, key_cache, value_cache, None, None, cu, seq_lens, block_table, cu,

@@ -223,6 +223,47 @@ def test_full_size_properties(strix):
     assert torch.equal(out2[:6], out_auto[:6])
 
 
+@pytest.mark.parametrize("hq,hkv,hd", [(32, 4, 128), (16, 2, 128), (8, 8, 64), (6, 1, 128)])
+@pytest.mark.parametrize("num_splits", [0, 1, 5])
+def test_bf16_kv_cache(strix, hq, hkv, hd, num_splits):
+    """The reference's native form: a bf16 cache, split-KV, window and sinks, ragged
+    lengths, stale NaN rows past the sequences - against the dense oracle."""
+    lens = [1, 17, 300, 1500, 16, 33]
+    bs = 16
+    g = torch.Generator().manual_seed(hq * 100 + hd + num_splits)
+    nblk = [(n + bs - 1) // bs for n in lens]
+    total = sum(nblk) + 2
+    kc = torch.randn(total, bs, hkv, hd, generator=g).bfloat16()
+    vc = torch.randn(total, bs, hkv, hd, generator=g).bfloat16()
+    perm = torch.randperm(total, generator=g)
+    table = torch.zeros(len(lens), max(nblk), dtype=torch.int32)
+    at = 0
+    for i, nb in enumerate(nblk):
+        table[i, :nb] = perm[at:at + nb].int()
+        at += nb
+    seq_lens = torch.tensor(lens, dtype=torch.int32)
+    q = torch.randn(len(lens), hq, hd, generator=g).bfloat16()
+    scale = hd ** -0.5
+    for window, use_sinks in ((-1, False), (200, True)):
+        if use_sinks and num_splits not in (0, 1):
+            continue
+        sinks = torch.randn(hq, generator=g) if use_sinks else None
+        cu = torch.arange(len(lens) + 1, dtype=torch.int32)
+        ref = A.attention_reference(q, kc.float(), vc.float(), cu, seq_lens, table, scale, window, sinks)
+        # slots past each sequence hold NaN: they must not reach the output
+        kd, vd = kc.clone(), vc.clone()
+        for i, n in enumerate(lens):
+            if n % bs:
+                blk = int(table[i, (n - 1) // bs])
+                kd[blk, n % bs:] = float("nan")
+                vd[blk, n % bs:] = float("nan")
+        out = torch.full_like(q, float("nan")).to(DEV)
+        strix.attn_decode(out, q.to(DEV), kd.to(DEV), vd.to(DEV), seq_lens.to(DEV), table.to(DEV), scale,
+                          num_splits, window, None, None, None if sinks is None else sinks.to(DEV))
+        torch.cuda.synchronize()
+        check(out, ref)
+
+
 def test_op_errors(strix):
     b = decode_batch(ctx_lens=[40]).to(DEV)
     out = torch.empty_like(b.q)
