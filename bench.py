@@ -388,7 +388,7 @@ def main() -> None:
     ap.add_argument("--no-graph", action="store_true",
                     help="time eager calls of the decode op instead of replays of its CUDA graph")
     ap.add_argument("--no-moe", action="store_true", help="skip the MoE / GEMM / prefill / EP sections")
-    ap.add_argument("--only", choices=["moe", "gemm", "prefill", "ep"], default=None,
+    ap.add_argument("--only", choices=["moe", "gemm", "prefill", "ep", "decode_bf16"], default=None,
                     help="run one secondary section alone (for profiling) and print its JSON")
     ap.add_argument("--moe-tokens", type=int, nargs="*", default=[256, 4096])
     ap.add_argument("--gemm-m", type=int, nargs="*", default=[1, 16, 4096])
@@ -428,7 +428,7 @@ def main() -> None:
     if args.only is not None:
         if rank == 0:
             section = {"moe": bench_moe_fp8, "gemm": bench_gemm_w8a8,
-                       "prefill": bench_attn_prefill}[args.only]
+                       "prefill": bench_attn_prefill, "decode_bf16": bench_decode_bf16kv}[args.only]
             print(json.dumps({args.only: section(args, dev, with_cpu)}), flush=True)
         if world > 1:
             dist.destroy_process_group()
@@ -519,9 +519,11 @@ def main() -> None:
         pre = bench_attn_prefill(args, dev, with_cpu)
         # the MoE half of the compound metric sits right behind the headline keys
         head = {k: line[k] for k in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step")}
+        dbf = bench_decode_bf16kv(args, dev, with_cpu)
         line = {**head, "moe_fp8": moe, **{k: v for k, v in line.items() if k not in head},
-                "gemm_w8a8_int8": gemm, "attn_prefill": pre}
-        line["gpu_launches"] += moe["gpu_launches"] + gemm["gpu_launches"] + pre["gpu_launches"]
+                "gemm_w8a8_int8": gemm, "attn_prefill": pre, "attn_decode_bf16kv": dbf}
+        line["gpu_launches"] += (moe["gpu_launches"] + gemm["gpu_launches"] + pre["gpu_launches"]
+                                 + dbf["gpu_launches"])
     # the expert-parallel layers run on every rank (they exchange tokens)
     ep_res = None if args.no_moe else bench_ep_moe(args, dev, rank, world, with_cpu)
     if rank == 0:
@@ -531,6 +533,46 @@ def main() -> None:
         print(json.dumps(line), flush=True)
     if dist.is_initialized():
         dist.destroy_process_group()
+
+
+def bench_decode_bf16kv(args, dev, with_cpu: bool) -> dict:
+    """Decode attention over bf16 caches (no scales): the first 32 sequences of the
+    headline batch, their int8 caches dequantised once outside the timed region. The
+    bytes are the K and V rows of every key (2 x 2 bytes x head x KV heads)."""
+    import libstrix_b200 as strix
+    from libstrix_b200.workloads import decode_batch
+
+    lens = batch_context_lengths()[:min(args.batch, 32)]
+    b = decode_batch(ctx_lens=lens, seed=7, device=dev)
+    kc = torch.empty(b.key_cache.shape, dtype=torch.bfloat16, device=dev)
+    vc = torch.empty_like(kc)
+    chunk = 4096                                   # blocks per pass: bounds the fp32 temporaries
+    for lo in range(0, kc.size(0), chunk):
+        sl = slice(lo, lo + chunk)
+        kc[sl] = (b.key_cache[sl].float() * b.k_scale[sl][..., None]).bfloat16()
+        vc[sl] = (b.value_cache[sl].float() * b.v_scale[sl][..., None]).bfloat16()
+    out = torch.empty_like(b.q)
+    out8 = torch.empty_like(b.q)
+    strix.attn_decode(out8, b.q, b.key_cache, b.value_cache, b.seq_lens, b.block_table, b.scale,
+                      0, -1, b.k_scale, b.v_scale)
+    nseg = strix._lib.load().strix_attn_decode_segments_n(b.q.size(0), 0, b.block_table.size(1), 16)
+    kv_heads, head = kc.size(-2), kc.size(-1)
+    nbytes = int(b.seq_lens.sum()) * kv_heads * head * 2 * 2
+
+    def step():
+        strix.attn_decode(out, b.q, kc, vc, b.seq_lens, b.block_table, b.scale, 0, -1)
+
+    ms = _timed(step, args.steps, max(args.warmup, 3))
+    peaks = measured_peaks()
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    diff = (out.float() - out8.float()).abs().max().item()
+    return {"workload": f"{len(lens)} sequences of the headline batch, bf16 K/V rows, block 16",
+            "ms_per_step": ms, "value": gbs, "unit": UNIT, "kv_bytes": nbytes, "segments": int(nseg),
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s",
+                         "frac": gbs / peaks["hbm"], "peak_kind": peaks["kind"]},
+            "max_abs_diff_vs_int8_kv_path": diff,
+            "l2": f"{nbytes / 1e6:.0f} MB of rows per step exceed the 126 MB L2",
+            "gpu_launches": (2 if nseg > 1 else 1) * args.steps}
 
 
 def bench_moe_fp8(args, dev, with_cpu: bool) -> dict:
