@@ -31,7 +31,6 @@ namespace strix {
 namespace {
 
 constexpr uint32_t kMagic = 0x64646464u;   // high byte of fp16 1024 + x
-constexpr uint32_t kBias = 0x64806480u;    // f16x2 (1152, 1152)
 // The softmax reference of a warp is renewed only when a score exceeds it by more
 // than 2^kLazy: the weights then stay below 2^kLazy, and kPScale = 2^(15 - kLazy)
 // keeps the V-scaled fp16 weights in range.
@@ -60,7 +59,17 @@ struct DecodeArgs {
   int block_size, hq, hkv, g, hpc;  // hpc: KV heads per CTA
   int nseg, seg_keys, win_left;
   float scale_log2;
+  int tpb_shift;  // log2(16-key tiles per page) when that is a power of two, else -1
 };
+
+// Page-table index and first row within the page of 16-key tile t: shifts for
+// power-of-two pages, a division only for the others.
+__device__ __forceinline__ int tile_page(const DecodeArgs& a, int t) {
+  return a.tpb_shift >= 0 ? t >> a.tpb_shift : (t * 16) / a.block_size;
+}
+__device__ __forceinline__ int tile_row(const DecodeArgs& a, int t) {
+  return a.tpb_shift >= 0 ? (t & ((1 << a.tpb_shift) - 1)) << 4 : (t * 16) % a.block_size;
+}
 
 template <int NW, bool ALIGNED>
 __device__ __forceinline__ void load_words(uint32_t (&dst)[NW], const uint8_t* p) {
@@ -135,6 +144,8 @@ struct QFrag {
   float qs[2];  // s * softmax_scale * log2(e) for heads 2c and 2c + 1
 };
 
+// (A second instantiation without the per-key tests for tiles wholly inside
+// [k_begin, k_end) was measured: it spills at the 128-register cap and is slower.)
 template <int D>
 __device__ __forceinline__ void compute_tile(const TileQ8<D>& t, WarpState<D>& st,
                                              const QFrag<D>& qf, int key0, int k_begin,
@@ -243,7 +254,7 @@ __global__ void __launch_bounds__(kWarps * 32, kMinCtas)
 attn_decode_q8_kernel(const DecodeArgs a) {
   pdl_enter();
   constexpr int kThreads = kWarps * 32;
-  extern __shared__ __align__(16) uint8_t dyn_smem[];
+  extern __shared__ __align__(128) uint8_t dyn_smem[];
   const int seg = blockIdx.x, hgrp = blockIdx.y, n = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
@@ -339,7 +350,6 @@ attn_decode_q8_kernel(const DecodeArgs a) {
   // page (block_size is a multiple of 16).
   const int t_begin = k_begin >> 4, t_end = (k_end + 15) >> 4;
   const int32_t* bt = a.bt + int64_t(n) * a.bt_stride;
-  const int bs = a.block_size;
 
   auto run_tile = [&](const TileQ8<D>& tile, int key0) {
     compute_tile<D>(tile, st, qf, key0, k_begin, k_end, g);
@@ -351,7 +361,7 @@ attn_decode_q8_kernel(const DecodeArgs a) {
   auto next_block = [&](int tile) {
     if ((nload & 31) == 0) {
       const int tl = tile + lane * wph;
-      my_blk = tl < t_end ? bt[(tl * 16) / bs] : 0;
+      my_blk = tl < t_end ? bt[tile_page(a, tl)] : 0;
     }
     const int blk = __shfl_sync(0xffffffffu, my_blk, nload & 31);
     ++nload;
@@ -363,19 +373,19 @@ attn_decode_q8_kernel(const DecodeArgs a) {
     int t = t_begin + sub;
     if (t < t_end) {
       const int blk = next_block(t);
-      load_tile<D, ALIGNED>(ta, a, blk, (t * 16) % bs, kvh, g, c);
+      load_tile<D, ALIGNED>(ta, a, blk, tile_row(a, t), kvh, g, c);
     }
     while (t < t_end) {
       if (t + wph < t_end) {
         const int blk = next_block(t + wph);
-        load_tile<D, ALIGNED>(tb, a, blk, ((t + wph) * 16) % bs, kvh, g, c);
+        load_tile<D, ALIGNED>(tb, a, blk, tile_row(a, t + wph), kvh, g, c);
       }
       run_tile(ta, t * 16);
       t += wph;
       if (t >= t_end) break;
       if (t + wph < t_end) {
         const int blk = next_block(t + wph);
-        load_tile<D, ALIGNED>(ta, a, blk, ((t + wph) * 16) % bs, kvh, g, c);
+        load_tile<D, ALIGNED>(ta, a, blk, tile_row(a, t + wph), kvh, g, c);
       }
       run_tile(tb, t * 16);
       t += wph;
@@ -398,7 +408,7 @@ attn_decode_q8_kernel(const DecodeArgs a) {
     auto issue_next = [&]() {
       if (t_issue < t_end) {
         const int blk = next_block(t_issue);
-        const int off = (t_issue * 16) % bs;
+        const int off = tile_row(a, t_issue);
         const uint8_t* kp = static_cast<const uint8_t*>(a.kc) + int64_t(blk) * a.k_sb +
                             int64_t(off) * a.k_ss + k_lane;
         const uint8_t* vp = static_cast<const uint8_t*>(a.vc) + int64_t(blk) * a.v_sb +
@@ -639,7 +649,6 @@ __global__ void __launch_bounds__(128) attn_decode_bf16kv_kernel(const DecodeArg
 
   const int t_begin = k_begin >> 4, t_end = (k_end + 15) >> 4;
   const int32_t* bt = a.bt + int64_t(n) * a.bt_stride;
-  const int bs = a.block_size;
   uint8_t* const ring = dyn_smem + warp * (kBfStages * kStage);
   const uint32_t ring_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring));
   const uint8_t* const kc = static_cast<const uint8_t*>(a.kc) + int64_t(kvh) * a.k_sh * 2;
@@ -648,8 +657,8 @@ __global__ void __launch_bounds__(128) attn_decode_bf16kv_kernel(const DecodeArg
   int t_issue = t_begin, stage_issue = 0;
   auto issue_next = [&]() {
     if (t_issue < t_end) {
-      const int blk = bt[(t_issue * 16) / bs];
-      const int off = (t_issue * 16) % bs;
+      const int blk = bt[tile_page(a, t_issue)];
+      const int off = tile_row(a, t_issue);
       const uint8_t* kp = kc + (int64_t(blk) * a.k_sb + int64_t(off) * a.k_ss) * 2;
       const uint8_t* vp = vc + (int64_t(blk) * a.v_sb + int64_t(off) * a.v_ss) * 2;
       const uint32_t dst = ring_s + stage_issue * kStage;
@@ -964,6 +973,13 @@ extern "C" int strix_attn_decode_bf16(
   a.ks_sb = ks_sb, a.ks_ss = ks_ss, a.ks_sh = ks_sh;
   a.vs_sb = vs_sb, a.vs_ss = vs_ss, a.vs_sh = vs_sh;
   a.block_size = int(block_size);
+  {
+    const int tpb = int(block_size / 16);
+    a.tpb_shift = -1;
+    if ((tpb & (tpb - 1)) == 0)
+      for (int sh = 0; sh < 31; ++sh)
+        if ((1 << sh) == tpb) a.tpb_shift = sh;
+  }
   a.hq = int(hq), a.hkv = int(hkv), a.g = int(g);
   a.hpc = hkv % 4 == 0 ? 4 : (hkv % 2 == 0 ? 2 : 1);
   a.nseg = int(nseg);
