@@ -47,7 +47,7 @@ int strix_version(void);
  *                 (element strides ks_* / vs_*), one per (key, head).
  *                 kv_int8 == 0: bf16 caches, the reference's native form (rows on
  *                 16-byte boundaries: strides multiples of 8; scales NULL), head_dim
- *                 64 or 128, with the same split-KV partials and reduce.
+ *                 64, 128 or 256, with the same split-KV partials and reduce.
  *   seq_lens      int32 [nseq]; the query sits at position seq_lens[n] - 1.
  *   block_table   int32 [nseq, >= ceil(seq_len / block_size)], row stride bt_stride.
  *   sinks         optional fp32 [hq]: one extra unscaled natural-log logit per
@@ -63,7 +63,7 @@ int strix_version(void);
  *                 [nseq, hq, nseg, head_dim] followed by (m, l) pairs
  *                 [nseq, hq, nseg, 2].
  *
- * Built geometries: head_dim 128 or 256 (int8 caches), 64 or 128 (bf16 caches),
+ * Built geometries: head_dim 128 or 256 (int8 caches), 64, 128 or 256 (bf16 caches),
  * hq / hkv in 1..8, block_size a multiple of 16. Others return STRIX_ERR_INVALID.
  * ---------------------------------------------------------------------- */
 #define STRIX_DECODE_AUTO_KEYS 1024
@@ -211,7 +211,7 @@ int strix_w8a8_int8_gemm(void* out, int32_t* acc_out, const void* a_q, const flo
  *                 does not depend on it and this kernel always runs one pass.
  *                 sinks need num_splits == 1 (the reference's rule and message).
  * The reference's tile_offsets / max_tiles arguments are not needed: the grid is
- * sized from total_q and nseq. Built: head_dim 64 and 128, any hq / hkv ratio.
+ * sized from total_q and nseq. Built: head_dim 64, 128 and 256, any hq / hkv ratio.
  * ---------------------------------------------------------------------- */
 int strix_attn_prefill_bf16(void* out, const void* q, const void* key_cache,
                             const void* value_cache, const float* k_scale, const float* v_scale,

@@ -865,6 +865,25 @@ int launch_decode(dim3 grid, cudaStream_t st, const DecodeArgs& a, size_t smem) 
   return launch_status("attn_decode");
 }
 
+template <int D>
+int launch_decode_bf16kv(dim3 grid, cudaStream_t st, const DecodeArgs& a) {
+  auto kernel = attn_decode_bf16kv_kernel<D>;
+  const size_t smem = size_t(a.hpc) * kBfStages * 2 * 16 * D * 2;
+  if (smem > 48 * 1024) {
+    // per device, once: opt in to the largest ring this head size can ask for
+    static bool done[64] = {};
+    int dev = 0;
+    STRIX_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !done[dev]) {
+      STRIX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (D == 256 ? 2 : 4) * kBfStages * 2 * 16 * D * 2));
+      if (dev >= 0 && dev < 64) done[dev] = true;
+    }
+  }
+  launch_chain(kernel, grid, 32 * a.hpc, smem, st, a);
+  return launch_status("attn_decode_bf16kv");
+}
+
 }  // namespace
 }  // namespace strix
 
@@ -933,8 +952,8 @@ extern "C" int strix_attn_decode_bf16(
     STRIX_CHECK((reinterpret_cast<uintptr_t>(key_cache) | reinterpret_cast<uintptr_t>(value_cache)) % 4 == 0,
                 "aligned cache rows");
   } else {
-    STRIX_CHECK((head_dim == 64 || head_dim == 128) && g <= 8,
-                "attn_decode_bf16 bf16 KV: head_dim %lld GQA %lld not built (64, 128: GQA 1-8)",
+    STRIX_CHECK((head_dim == 64 || head_dim == 128 || head_dim == 256) && g <= 8,
+                "attn_decode_bf16 bf16 KV: head_dim %lld GQA %lld not built (64, 128, 256: GQA 1-8)",
                 (long long)head_dim, (long long)g);
     STRIX_CHECK(k_sb % 8 == 0 && k_ss % 8 == 0 && k_sh % 8 == 0 && v_sb % 8 == 0 &&
                     v_ss % 8 == 0 && v_sh % 8 == 0 &&
@@ -989,26 +1008,20 @@ extern "C" int strix_attn_decode_bf16(
 
   if (!kv_int8) {
     // bf16 caches: one warp per KV head of the group, per-warp cp.async ring
+    // (head 256: two KV heads per CTA, so that two CTAs of 96 KB share an SM)
+    if (head_dim == 256 && a.hpc > 2) a.hpc = 2;
     const dim3 bgrid{unsigned(nseg), unsigned(hkv / a.hpc), unsigned(nseq)};
     cudaStream_t bst = static_cast<cudaStream_t>(stream);
-    const size_t smem = size_t(a.hpc) * kBfStages * 2 * 16 * size_t(head_dim) * 2;
-    auto bkernel = head_dim == 128 ? attn_decode_bf16kv_kernel<128> : attn_decode_bf16kv_kernel<64>;
-    if (smem > 48 * 1024) {
-      static bool done[64] = {};
-      int dev = 0;
-      STRIX_CUDA(cudaGetDevice(&dev));
-      if (dev < 0 || dev >= 64 || !done[dev]) {
-        STRIX_CUDA(cudaFuncSetAttribute(attn_decode_bf16kv_kernel<128>,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * kBfStages * 2 * 16 * 256));
-        if (dev >= 0 && dev < 64) done[dev] = true;
-      }
-    }
-    launch_chain(bkernel, bgrid, 32 * a.hpc, smem, bst, a);
-    int brc = launch_status("attn_decode_bf16kv");
+    int brc = head_dim == 256   ? launch_decode_bf16kv<256>(bgrid, bst, a)
+              : head_dim == 128 ? launch_decode_bf16kv<128>(bgrid, bst, a)
+                                : launch_decode_bf16kv<64>(bgrid, bst, a);
     if (brc != STRIX_OK) return brc;
     if (nseg > 1) {
       const dim3 rgrid{unsigned(hq), unsigned(nseq), 1u};
-      if (head_dim == 128)
+      if (head_dim == 256)
+        launch_chain(attn_decode_reduce_kernel<256>, rgrid, kReduceParts * 128, 0, bst, a.out, a.o_part,
+                     a.ml_part, a.nseg, a.hq, o_st, o_sh, sinks);
+      else if (head_dim == 128)
         launch_chain(attn_decode_reduce_kernel<128>, rgrid, kReduceParts * 64, 0, bst, a.out, a.o_part,
                      a.ml_part, a.nseg, a.hq, o_st, o_sh, sinks);
       else

@@ -69,12 +69,18 @@ struct PfLayout {
   static constexpr int kRawKV = Q8 ? kBN * D : 0;                // raw int8 rows of K (or V)
   static constexpr int kRaw = Q8 ? 2 * kRawKV + 2 * kBN * 4 : 0; // K, V, k scales, v scales
   // Q8: two raw buffers + one pair of operand tiles; bf16: two pairs of operand tiles
-  static constexpr int kSmem = Q8 ? 2 * kRaw + 2 * kTile : 4 * kTile;
+  static constexpr int kKV = Q8 ? 2 * kRaw + 2 * kTile : 4 * kTile;
+  // Head sizes above 128 keep the 64 x D query tile in shared memory as well (its
+  // fragments are re-read per key tile): 64 + 128 accumulator registers leave no room
+  // for D / 4 more of Q.
+  static constexpr bool kQInSmem = D > 128;
+  static constexpr int kSmem = kKV + (kQInSmem ? kBM * D * 2 : 0);
 };
 
 template <int D, bool Q8>
-__global__ void __launch_bounds__(kPfThreads, 3) attn_prefill_kernel(const PrefillArgs p) {
+__global__ void __launch_bounds__(kPfThreads, D > 128 ? 1 : 3) attn_prefill_kernel(const PrefillArgs p) {
   using L = PfLayout<D, Q8>;
+  constexpr bool QS = L::kQInSmem;
   extern __shared__ __align__(128) uint8_t smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, c = lane & 3;
@@ -103,7 +109,9 @@ __global__ void __launch_bounds__(kPfThreads, 3) attn_prefill_kernel(const Prefi
   const int n_tiles = (k_end - k_begin + kBN - 1) / kBN;
 
   // ---- Q fragments (A operand, m16k16 per 16 dims), rows g and g + 8 of the warp
-  uint32_t qf[D / 16][4];
+  // (QS: the same words go to this warp's 16 rows of the shared query tile instead)
+  uint32_t qf[QS ? 1 : D / 16][4];
+  const uint32_t q_tile = static_cast<uint32_t>(__cvta_generic_to_shared(smem)) + L::kKV;
   {
     const int r_lo = row0 + g, r_hi = row0 + g + 8;
     const __nv_bfloat16* q_lo = p.q + int64_t(q_begin + min(r_lo, q_len - 1)) * p.q_st + head * p.q_sh;
@@ -116,8 +124,18 @@ __global__ void __launch_bounds__(kPfThreads, 3) attn_prefill_kernel(const Prefi
       w[2] = *reinterpret_cast<const uint32_t*>(q_lo + 16 * s + 8 + 2 * c);
       w[3] = *reinterpret_cast<const uint32_t*>(q_hi + 16 * s + 8 + 2 * c);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) qf[s][i] = Q8 ? pack_f16x2(bf16_lo(w[i]), bf16_hi(w[i])) : w[i];
+      for (int i = 0; i < 4; ++i) w[i] = Q8 ? pack_f16x2(bf16_lo(w[i]), bf16_hi(w[i])) : w[i];
+      if constexpr (QS) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          *reinterpret_cast<uint32_t*>(smem + L::kKV + tile_off<D>(warp * 16 + g + 8 * (i & 1), 2 * s + (i >> 1)) +
+                                       4 * c) = w[i];
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) qf[s][i] = w[i];
+      }
     }
+    if constexpr (QS) __syncwarp();
   }
   const int qpos_lo = pos0 + row0 + g, qpos_hi = qpos_lo + 8;   // positions of the two rows
 
@@ -229,12 +247,17 @@ __global__ void __launch_bounds__(kPfThreads, 3) attn_prefill_kernel(const Prefi
       for (int j = 0; j < kBN / 8; ++j)
         ldmatrix_x4(b[j], kt + tile_off<D>(8 * j + (lane & 7), 4 * sp + (lane >> 3)));
 #pragma unroll
-      for (int h = 0; h < 2; ++h)
+      for (int h = 0; h < 2; ++h) {
+        if constexpr (QS)
+          ldmatrix_x4(qf[0], q_tile + tile_off<D>(warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1),
+                                                  2 * (2 * sp + h) + (lane >> 4)));
+        const uint32_t (&qa)[4] = qf[QS ? 0 : 2 * sp + h];
 #pragma unroll
         for (int j = 0; j < kBN / 8; ++j) {
-          if constexpr (Q8) mma_f16_16816(s[j], qf[2 * sp + h], b[j][2 * h], b[j][2 * h + 1]);
-          else mma_bf16_16816(s[j], qf[2 * sp + h], b[j][2 * h], b[j][2 * h + 1]);
+          if constexpr (Q8) mma_f16_16816(s[j], qa, b[j][2 * h], b[j][2 * h + 1]);
+          else mma_bf16_16816(s[j], qa, b[j][2 * h], b[j][2 * h + 1]);
         }
+      }
     }
 
     // ---- scale, mask, online softmax (rows g and g + 8; keys 8j + 2c, + 1)
@@ -381,7 +404,8 @@ extern "C" int strix_attn_prefill_bf16(
     int64_t v_stride_h, int64_t ks_stride_b, int64_t ks_stride_s, int64_t ks_stride_h,
     int64_t vs_stride_b, int64_t vs_stride_s, int64_t vs_stride_h, double scale,
     int64_t num_splits, int64_t window_left, int kv_int8, strix_stream_t stream) {
-  STRIX_CHECK(head_dim == 64 || head_dim == 128, "head_dim 64 or 128 (others are not built)");
+  STRIX_CHECK(head_dim == 64 || head_dim == 128 || head_dim == 256,
+              "head_dim 64, 128 or 256 (others are not built)");
   STRIX_CHECK(hq > 0 && hkv > 0 && hq % hkv == 0 && hq <= 65535, "hq must be a multiple of hkv");
   STRIX_CHECK(block_size >= 1 && nseq >= 0 && total_q >= 0, "bad sizes");
   STRIX_CHECK(num_splits >= 1 && num_splits <= 64, "num_splits in [1, 64]");
@@ -412,6 +436,7 @@ extern "C" int strix_attn_prefill_bf16(
   // an upper bound on the 64-query tiles without reading the lengths on the host
   const int64_t max_tiles = (total_q + kBM - 1) / kBM + nseq;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (head_dim == 256) return kv_int8 ? launch_prefill<256, true>(p, max_tiles, st) : launch_prefill<256, false>(p, max_tiles, st);
   if (head_dim == 128) return kv_int8 ? launch_prefill<128, true>(p, max_tiles, st) : launch_prefill<128, false>(p, max_tiles, st);
   return kv_int8 ? launch_prefill<64, true>(p, max_tiles, st) : launch_prefill<64, false>(p, max_tiles, st);
 }

@@ -333,6 +333,12 @@ KERNELS: list[Kernel] = [
               "kv_dtype": ("bf16",), "window": (True, False), "sinks": (True, False)},
              {"tile_keys": 16, "mma": "m16n8k16 bf16, keys as M", "bound": "hbm"})
       for hd in (128, 64)],
+    Kernel("attn_decode_bf16", "attn_decode",
+           "bf16 KV cache at head 256 (GQA 1-8 only: no prefill kernel behind it), two KV heads "
+           "per CTA so that two 96 KB rings share an SM",
+           {"head_dim": 256, "gqa": Range(1, 8), "queries": 1, "dtype": "bf16",
+            "kv_dtype": ("bf16",), "window": (True, False), "sinks": (True, False)},
+           {"tile_keys": 16, "mma": "m16n8k16 bf16, keys as M", "bound": "hbm"}),
     *[Kernel(
         "attn_prefill_bf16", "attn_prefill",
         "causal paged flash attention over ragged sequences: 64 queries x one head per CTA, "
@@ -343,6 +349,16 @@ KERNELS: list[Kernel] = [
          "sinks": (True, False)},
         {"tile": "64 queries x 64 keys", "mma": "m16n8k16 f16 (int8 KV) / bf16", "bound": "tensor"},
     ) for hd in (128, 64)],
+    Kernel(
+        "attn_prefill_bf16", "attn_prefill",
+        "head 256 (the reference's GQA 6 / 8 / 2 rows and any other ratio): the same 64 x 64 "
+        "mma.sync kernel, one CTA per SM, with the query tile in shared memory (its fragments "
+        "re-read by ldmatrix per key tile) because 128 accumulator registers leave no room for it",
+        {"head_dim": 256, "gqa": Range(1, 64), "dtype": "bf16", "kv_dtype": ("bf16", "int8"),
+         "split_kv": (True, False), "window": (True, False), "causal": True,
+         "sinks": (True, False)},
+        {"tile": "64 queries x 64 keys", "mma": "m16n8k16 f16 (int8 KV) / bf16", "bound": "tensor"},
+    ),
 ]
 
 _POINT_TYPES = (int, bool, str)
