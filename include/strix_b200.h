@@ -47,7 +47,7 @@ int strix_version(void);
  *                 (element strides ks_* / vs_*), one per (key, head).
  *                 kv_int8 == 0: bf16 caches, the reference's native form (rows on
  *                 16-byte boundaries: strides multiples of 8; scales NULL), head_dim
- *                 64, 128 or 256, with the same split-KV partials and reduce.
+ *                 64, 128, 256 or 512, with the same split-KV partials and reduce.
  *   seq_lens      int32 [nseq]; the query sits at position seq_lens[n] - 1.
  *   block_table   int32 [nseq, >= ceil(seq_len / block_size)], row stride bt_stride.
  *   sinks         optional fp32 [hq]: one extra unscaled natural-log logit per
@@ -63,7 +63,7 @@ int strix_version(void);
  *                 [nseq, hq, nseg, head_dim] followed by (m, l) pairs
  *                 [nseq, hq, nseg, 2].
  *
- * Built geometries: head_dim 128 or 256 (int8 caches), 64, 128 or 256 (bf16 caches),
+ * Built geometries: head_dim 128 or 256 (int8 caches), 64, 128, 256 or 512 (bf16 caches),
  * hq / hkv in 1..8, block_size a multiple of 16. Others return STRIX_ERR_INVALID.
  * ---------------------------------------------------------------------- */
 #define STRIX_DECODE_AUTO_KEYS 1024

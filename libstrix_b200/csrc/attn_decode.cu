@@ -591,10 +591,15 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
 
 constexpr int kBfStages = 3;
 
-template <int D>
+// SPLIT = 2 (head 512): two warps share a KV head, each owning D = 256 of its dims -
+// that half of every K and V row in its own ring, that half of Q and of O. Each
+// computes the score partials over its dims; the pair exchanges them through shared
+// memory (two buffers by tile parity, one 64-thread named barrier per tile) and then
+// holds the same scores, maxima and sums.
+template <int D, int SPLIT>
 __global__ void __launch_bounds__(128) attn_decode_bf16kv_kernel(const DecodeArgs a) {
   pdl_enter();
-  constexpr int kRow = D * 2;                 // bytes of a cache row
+  constexpr int kRow = D * 2;                 // bytes of this warp's part of a cache row
   constexpr int kChunks = kRow / 16;          // 16-byte chunks per row
   constexpr int kTile = 16 * kRow;            // K (or V) rows of a tile
   constexpr int kStage = 2 * kTile;
@@ -602,7 +607,9 @@ __global__ void __launch_bounds__(128) attn_decode_bf16kv_kernel(const DecodeArg
   const int seg = blockIdx.x, hgrp = blockIdx.y, n = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
-  const int kvh = hgrp * a.hpc + warp;        // blockDim.x = 32 * hpc: one warp per KV head
+  const int hslot = warp / SPLIT, half = warp % SPLIT;
+  const int kvh = hgrp * a.hpc + hslot;       // blockDim.x = 32 * hpc * SPLIT
+  const int d0 = half * D;                    // first head dim of this warp
   const int G = a.g;
   const int h0 = kvh * G;
 
@@ -622,8 +629,8 @@ __global__ void __launch_bounds__(128) attn_decode_bf16kv_kernel(const DecodeArg
       const int h = h0 + hl;
       if (single) {
         for (int d = g; d < D; d += 8)
-          a.out[int64_t(n) * a.o_st + int64_t(h) * a.o_sh + d] = __float2bfloat16(0.f);
-      } else if (g == 0) {
+          a.out[int64_t(n) * a.o_st + int64_t(h) * a.o_sh + d0 + d] = __float2bfloat16(0.f);
+      } else if (g == 0 && half == 0) {
         float* ml = a.ml_part + ((int64_t(n) * a.hq + h) * a.nseg + seg) * 2;
         ml[0] = -INFINITY;
         ml[1] = 0.f;
@@ -635,7 +642,7 @@ __global__ void __launch_bounds__(128) attn_decode_bf16kv_kernel(const DecodeArg
   // Q^T fragments: b0 / b1 of k-step ks = q[head g][16 ks + 2c, + 1] / [16 ks + 8 + 2c, + 1]
   uint32_t qb[D / 16][2];
   {
-    const __nv_bfloat16* qp = a.q + int64_t(n) * a.q_st + int64_t(h0 + g) * a.q_sh;
+    const __nv_bfloat16* qp = a.q + int64_t(n) * a.q_st + int64_t(h0 + g) * a.q_sh + d0;
 #pragma unroll
     for (int ks = 0; ks < D / 16; ++ks) {
       qb[ks][0] = g < G ? *reinterpret_cast<const uint32_t*>(qp + 16 * ks + 2 * c) : 0u;
@@ -651,8 +658,10 @@ __global__ void __launch_bounds__(128) attn_decode_bf16kv_kernel(const DecodeArg
   const int32_t* bt = a.bt + int64_t(n) * a.bt_stride;
   uint8_t* const ring = dyn_smem + warp * (kBfStages * kStage);
   const uint32_t ring_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring));
-  const uint8_t* const kc = static_cast<const uint8_t*>(a.kc) + int64_t(kvh) * a.k_sh * 2;
-  const uint8_t* const vc = static_cast<const uint8_t*>(a.vc) + int64_t(kvh) * a.v_sh * 2;
+  const uint8_t* const kc = static_cast<const uint8_t*>(a.kc) + (int64_t(kvh) * a.k_sh + d0) * 2;
+  const uint8_t* const vc = static_cast<const uint8_t*>(a.vc) + (int64_t(kvh) * a.v_sh + d0) * 2;
+  // score partials of the pair: [parity][hslot][half][lane] float4, behind the rings
+  float4* const xch = reinterpret_cast<float4*>(dyn_smem + a.hpc * SPLIT * (kBfStages * kStage));
 
   int t_issue = t_begin, stage_issue = 0;
   auto issue_next = [&]() {
@@ -702,6 +711,13 @@ __global__ void __launch_bounds__(128) attn_decode_bf16kv_kernel(const DecodeArg
       const int row = lane & 15, ch = 2 * ks + (lane >> 4);
       ldmatrix_x4(af, ks_s + row * kRow + ((ch ^ (row & 7)) << 4));
       mma_bf16_16816(sc, af, qb[ks][0], qb[ks][1]);
+    }
+    if constexpr (SPLIT == 2) {
+      float4* const mine = xch + (((t & 1) * a.hpc + hslot) * 2 + half) * 32 + lane;
+      *mine = make_float4(sc[0], sc[1], sc[2], sc[3]);
+      asm volatile("bar.sync %0, 64;" ::"r"(hslot + 1) : "memory");
+      const float4 other = half == 0 ? mine[32] : mine[-32];
+      sc[0] += other.x, sc[1] += other.y, sc[2] += other.z, sc[3] += other.w;
     }
     const int ka = key0 + g, kb = ka + 8;
     const bool va = ka >= k_begin && ka < k_end, vb = kb >= k_begin && kb < k_end;
@@ -765,7 +781,7 @@ __global__ void __launch_bounds__(128) attn_decode_bf16kv_kernel(const DecodeArg
         const float al = m[j] == -INFINITY ? 0.f : fast_exp2(m[j] - mf);
         inv = al / (l[j] * al + fast_exp2(s2 - mf));
       }
-      __nv_bfloat16* op = a.out + int64_t(n) * a.o_st + int64_t(h) * a.o_sh;
+      __nv_bfloat16* op = a.out + int64_t(n) * a.o_st + int64_t(h) * a.o_sh + d0;
 #pragma unroll
       for (int i = 0; i < D / 16; ++i) {
         op[16 * i + g] = __float2bfloat16(acc[i][j] * inv);
@@ -773,13 +789,13 @@ __global__ void __launch_bounds__(128) attn_decode_bf16kv_kernel(const DecodeArg
       }
     } else {
       const int64_t row = (int64_t(n) * a.hq + h) * a.nseg + seg;
-      float* op = a.o_part + row * D;
+      float* op = a.o_part + row * (D * SPLIT) + d0;
 #pragma unroll
       for (int i = 0; i < D / 16; ++i) {
         op[16 * i + g] = acc[i][j];
         op[16 * i + g + 8] = acc[i][2 + j];
       }
-      if (g == 0) {
+      if (g == 0 && half == 0) {
         a.ml_part[2 * row] = m[j];
         a.ml_part[2 * row + 1] = l[j];
       }
@@ -865,10 +881,12 @@ int launch_decode(dim3 grid, cudaStream_t st, const DecodeArgs& a, size_t smem) 
   return launch_status("attn_decode");
 }
 
-template <int D>
+template <int D, int SPLIT>
 int launch_decode_bf16kv(dim3 grid, cudaStream_t st, const DecodeArgs& a) {
-  auto kernel = attn_decode_bf16kv_kernel<D>;
-  const size_t smem = size_t(a.hpc) * kBfStages * 2 * 16 * D * 2;
+  auto kernel = attn_decode_bf16kv_kernel<D, SPLIT>;
+  // rings, then (SPLIT == 2) the pairs' score exchange: 2 parities x 2 halves x 32 float4
+  const size_t smem = size_t(a.hpc) * SPLIT * kBfStages * 2 * 16 * D * 2 +
+                      (SPLIT == 2 ? size_t(a.hpc) * 2 * 2 * 32 * 16 : 0);
   if (smem > 48 * 1024) {
     // per device, once: opt in to the largest ring this head size can ask for
     static bool done[64] = {};
@@ -876,11 +894,11 @@ int launch_decode_bf16kv(dim3 grid, cudaStream_t st, const DecodeArgs& a) {
     STRIX_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !done[dev]) {
       STRIX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (D == 256 ? 2 : 4) * kBfStages * 2 * 16 * D * 2));
+                                      (D == 256 ? 2 : 4) * kBfStages * 2 * 16 * D * 2 + 4096));
       if (dev >= 0 && dev < 64) done[dev] = true;
     }
   }
-  launch_chain(kernel, grid, 32 * a.hpc, smem, st, a);
+  launch_chain(kernel, grid, 32 * a.hpc * SPLIT, smem, st, a);
   return launch_status("attn_decode_bf16kv");
 }
 
@@ -952,8 +970,8 @@ extern "C" int strix_attn_decode_bf16(
     STRIX_CHECK((reinterpret_cast<uintptr_t>(key_cache) | reinterpret_cast<uintptr_t>(value_cache)) % 4 == 0,
                 "aligned cache rows");
   } else {
-    STRIX_CHECK((head_dim == 64 || head_dim == 128 || head_dim == 256) && g <= 8,
-                "attn_decode_bf16 bf16 KV: head_dim %lld GQA %lld not built (64, 128, 256: GQA 1-8)",
+    STRIX_CHECK((head_dim == 64 || head_dim == 128 || head_dim == 256 || head_dim == 512) && g <= 8,
+                "attn_decode_bf16 bf16 KV: head_dim %lld GQA %lld not built (64, 128, 256, 512: GQA 1-8)",
                 (long long)head_dim, (long long)g);
     STRIX_CHECK(k_sb % 8 == 0 && k_ss % 8 == 0 && k_sh % 8 == 0 && v_sb % 8 == 0 &&
                     v_ss % 8 == 0 && v_sh % 8 == 0 &&
@@ -1008,17 +1026,23 @@ extern "C" int strix_attn_decode_bf16(
 
   if (!kv_int8) {
     // bf16 caches: one warp per KV head of the group, per-warp cp.async ring
-    // (head 256: two KV heads per CTA, so that two CTAs of 96 KB share an SM)
+    // (head 256: two KV heads per CTA, so that two CTAs of 96 KB share an SM; head 512:
+    // one KV head per CTA, its dims split over a pair of warps)
     if (head_dim == 256 && a.hpc > 2) a.hpc = 2;
+    if (head_dim == 512) a.hpc = 1;
     const dim3 bgrid{unsigned(nseg), unsigned(hkv / a.hpc), unsigned(nseq)};
     cudaStream_t bst = static_cast<cudaStream_t>(stream);
-    int brc = head_dim == 256   ? launch_decode_bf16kv<256>(bgrid, bst, a)
-              : head_dim == 128 ? launch_decode_bf16kv<128>(bgrid, bst, a)
-                                : launch_decode_bf16kv<64>(bgrid, bst, a);
+    int brc = head_dim == 512   ? launch_decode_bf16kv<256, 2>(bgrid, bst, a)
+              : head_dim == 256 ? launch_decode_bf16kv<256, 1>(bgrid, bst, a)
+              : head_dim == 128 ? launch_decode_bf16kv<128, 1>(bgrid, bst, a)
+                                : launch_decode_bf16kv<64, 1>(bgrid, bst, a);
     if (brc != STRIX_OK) return brc;
     if (nseg > 1) {
       const dim3 rgrid{unsigned(hq), unsigned(nseq), 1u};
-      if (head_dim == 256)
+      if (head_dim == 512)
+        launch_chain(attn_decode_reduce_kernel<512>, rgrid, kReduceParts * 256, 0, bst, a.out, a.o_part,
+                     a.ml_part, a.nseg, a.hq, o_st, o_sh, sinks);
+      else if (head_dim == 256)
         launch_chain(attn_decode_reduce_kernel<256>, rgrid, kReduceParts * 128, 0, bst, a.out, a.o_part,
                      a.ml_part, a.nseg, a.hq, o_st, o_sh, sinks);
       else if (head_dim == 128)

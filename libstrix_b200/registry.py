@@ -339,6 +339,13 @@ KERNELS: list[Kernel] = [
            {"head_dim": 256, "gqa": Range(1, 8), "queries": 1, "dtype": "bf16",
             "kv_dtype": ("bf16",), "window": (True, False), "sinks": (True, False)},
            {"tile_keys": 16, "mma": "m16n8k16 bf16, keys as M", "bound": "hbm"}),
+    Kernel("attn_decode_bf16", "attn_decode",
+           "bf16 KV cache at head 512 (the reference's GQA 8 row; GQA 1-8): the head's dims split "
+           "over a pair of warps, each with its half of every K and V row in its own ring; the pair "
+           "adds its score partials through shared memory once per 16-key tile",
+           {"head_dim": 512, "gqa": Range(1, 8), "queries": 1, "dtype": "bf16",
+            "kv_dtype": ("bf16",), "window": (True, False), "sinks": (True, False)},
+           {"tile_keys": 16, "mma": "m16n8k16 bf16, keys as M", "bound": "hbm"}),
     *[Kernel(
         "attn_prefill_bf16", "attn_prefill",
         "causal paged flash attention over ragged sequences: 64 queries x one head per CTA, "

@@ -100,7 +100,7 @@ def attn_decode_bf16(
         _check(sinks.dtype == torch.float32 and sinks.dim() == 1 and sinks.size(0) == q.size(1)
                and sinks.is_contiguous(), "sinks must be contiguous fp32 [Hq]")
     _check(0 <= num_splits <= 64, "num_splits in [1, 64]")
-    bf16_rows_ok = not q8 and d in (64, 128, 256) and q.size(1) // key_cache.size(2) <= 8 and all(
+    bf16_rows_ok = not q8 and d in (64, 128, 256, 512) and q.size(1) // key_cache.size(2) <= 8 and all(
         st % 8 == 0 for t in (key_cache, value_cache) for st in t.stride()[:3]) and \
         key_cache.data_ptr() % 16 == 0 and value_cache.data_ptr() % 16 == 0
     if not q8 and not bf16_rows_ok:

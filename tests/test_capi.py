@@ -56,7 +56,7 @@ def _decode_args(**over):
         (dict(hq=30), "Hq % Hkv"),
         (dict(bs=24), "multiple of 16"),
         (dict(splits=65), "num_splits in [1, 64]"),
-        (dict(q8=0, d=512), "bf16 KV: head_dim 512 GQA 8 not built"),
+        (dict(q8=0, d=96), "bf16 KV: head_dim 96 GQA 8 not built"),
         (dict(q8=0, k_ss=516), "bf16 cache rows must be 16-byte aligned"),
         (dict(ks=None), "int8 KV needs k_scale and v_scale"),
         (dict(splits=4), "workspace"),
