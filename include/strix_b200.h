@@ -211,7 +211,7 @@ int strix_w8a8_int8_gemm(void* out, int32_t* acc_out, const void* a_q, const flo
  *                 does not depend on it and this kernel always runs one pass.
  *                 sinks need num_splits == 1 (the reference's rule and message).
  * The reference's tile_offsets / max_tiles arguments are not needed: the grid is
- * sized from total_q and nseq. Built: head_dim 64, 128 and 256, any hq / hkv ratio.
+ * sized from total_q and nseq. Built: head_dim 64, 128, 256 and 512, any hq / hkv ratio.
  * ---------------------------------------------------------------------- */
 int strix_attn_prefill_bf16(void* out, const void* q, const void* key_cache,
                             const void* value_cache, const float* k_scale, const float* v_scale,

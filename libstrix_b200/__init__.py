@@ -80,7 +80,7 @@ def attn_prefill(
     """Causal paged attention for prefill (no host sync); same arguments as the
     reference's strix.attn_prefill (python/strix/__init__.py:214-268).
 
-    q, out: [T, Hq, D] bf16, D = 64, 128 or 256; caches [blocks, block_size, Hkv, D]
+    q, out: [T, Hq, D] bf16, D = 64, 128, 256 or 512; caches [blocks, block_size, Hkv, D]
     views, bf16 or int8 with k_scale / v_scale fp32 [blocks, block_size, Hkv];
     the queries of sequence n are the last q_len of its seq_lens[n] positions.
     window_left >= 0: the query at position p sees keys p - window_left .. p.

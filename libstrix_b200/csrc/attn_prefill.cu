@@ -16,13 +16,18 @@
 // exactly); bf16 caches are copied straight into the operand tiles and use
 // bf16 MMAs. Operand tiles are read with ldmatrix (V transposed) through a
 // 16-byte-chunk XOR swizzle. Softmax is online, in the exp2 domain, fp32.
+//
+// Head 256 keeps the query tile in shared memory too (its fragments are re-read per
+// key tile). Head 512 (SPLIT = 2) gives each group of 16 queries to a PAIR of warps,
+// each owning 256 of the head's dims - that part of Q, of every K row (score
+// partials, added through shared memory behind a 64-thread named barrier) and of
+// every V row and O - over key tiles of 32.
 #include "common.cuh"
 
 namespace strix {
 namespace {
 
-constexpr int kPfWarps = 4, kPfThreads = kPfWarps * 32;
-constexpr int kBM = 64, kBN = 64;
+constexpr int kBM = 64;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLift = 64.f;   // P x v_scale is lifted into fp16's normal range
 
@@ -57,7 +62,7 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t add
                : "r"(addr));
 }
 
-// byte offset of 16-byte chunk `chunk` of key row `key` in a [64][D] 16-bit tile
+// byte offset of 16-byte chunk `chunk` of key row `key` in a [rows][D] 16-bit tile
 template <int D>
 __device__ __forceinline__ uint32_t tile_off(int key, int chunk) {
   return uint32_t(key * (D * 2) + ((chunk ^ (key & 7)) << 4));
@@ -65,6 +70,10 @@ __device__ __forceinline__ uint32_t tile_off(int key, int chunk) {
 
 template <int D, bool Q8>
 struct PfLayout {
+  static constexpr int kSplit = D > 256 ? 2 : 1;                 // warps sharing 16 queries
+  static constexpr int kDW = D / kSplit;                         // head dims per warp
+  static constexpr int kThreads = 128 * kSplit;
+  static constexpr int kBN = D > 256 ? 32 : 64;                  // keys per tile
   static constexpr int kTile = kBN * D * 2;                      // one 16-bit operand tile
   static constexpr int kRawKV = Q8 ? kBN * D : 0;                // raw int8 rows of K (or V)
   static constexpr int kRaw = Q8 ? 2 * kRawKV + 2 * kBN * 4 : 0; // K, V, k scales, v scales
@@ -74,15 +83,23 @@ struct PfLayout {
   // fragments are re-read per key tile): 64 + 128 accumulator registers leave no room
   // for D / 4 more of Q.
   static constexpr bool kQInSmem = D > 128;
-  static constexpr int kSmem = kKV + (kQInSmem ? kBM * D * 2 : 0);
+  static constexpr int kQ = kQInSmem ? kBM * D * 2 : 0;
+  // score partials of the warp pairs: [parity][4 query groups][2][kBN / 8][32 lanes] float4
+  static constexpr int kXch = kSplit == 2 ? 2 * 4 * 2 * (kBN / 8) * 32 * 16 : 0;
+  static constexpr int kSmem = kKV + kQ + kXch;
 };
 
 template <int D, bool Q8>
-__global__ void __launch_bounds__(kPfThreads, D > 128 ? 1 : 3) attn_prefill_kernel(const PrefillArgs p) {
+__global__ void __launch_bounds__(PfLayout<D, Q8>::kThreads, D > 128 ? 1 : 3)
+attn_prefill_kernel(const PrefillArgs p) {
   using L = PfLayout<D, Q8>;
   constexpr bool QS = L::kQInSmem;
+  constexpr int SPLIT = L::kSplit, DW = L::kDW, kBN = L::kBN;
   extern __shared__ __align__(128) uint8_t smem[];
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int warp = (tid >> 5) / SPLIT;          // group of 16 queries
+  const int half = (tid >> 5) % SPLIT;          // which DW dims of the head
+  constexpr int kC0 = DW / 8;                   // 16-byte chunks of a 16-bit row per warp
   const int g = lane >> 2, c = lane & 3;
   const int head = blockIdx.y, kvh = head / (p.hq / p.hkv);
 
@@ -110,14 +127,14 @@ __global__ void __launch_bounds__(kPfThreads, D > 128 ? 1 : 3) attn_prefill_kern
 
   // ---- Q fragments (A operand, m16k16 per 16 dims), rows g and g + 8 of the warp
   // (QS: the same words go to this warp's 16 rows of the shared query tile instead)
-  uint32_t qf[QS ? 1 : D / 16][4];
+  uint32_t qf[QS ? 1 : DW / 16][4];
   const uint32_t q_tile = static_cast<uint32_t>(__cvta_generic_to_shared(smem)) + L::kKV;
   {
     const int r_lo = row0 + g, r_hi = row0 + g + 8;
-    const __nv_bfloat16* q_lo = p.q + int64_t(q_begin + min(r_lo, q_len - 1)) * p.q_st + head * p.q_sh;
-    const __nv_bfloat16* q_hi = p.q + int64_t(q_begin + min(r_hi, q_len - 1)) * p.q_st + head * p.q_sh;
+    const __nv_bfloat16* q_lo = p.q + int64_t(q_begin + min(r_lo, q_len - 1)) * p.q_st + head * p.q_sh + half * DW;
+    const __nv_bfloat16* q_hi = p.q + int64_t(q_begin + min(r_hi, q_len - 1)) * p.q_st + head * p.q_sh + half * DW;
 #pragma unroll
-    for (int s = 0; s < D / 16; ++s) {
+    for (int s = 0; s < DW / 16; ++s) {
       uint32_t w[4];
       w[0] = *reinterpret_cast<const uint32_t*>(q_lo + 16 * s + 2 * c);
       w[1] = *reinterpret_cast<const uint32_t*>(q_hi + 16 * s + 2 * c);
@@ -128,7 +145,8 @@ __global__ void __launch_bounds__(kPfThreads, D > 128 ? 1 : 3) attn_prefill_kern
       if constexpr (QS) {
 #pragma unroll
         for (int i = 0; i < 4; ++i)
-          *reinterpret_cast<uint32_t*>(smem + L::kKV + tile_off<D>(warp * 16 + g + 8 * (i & 1), 2 * s + (i >> 1)) +
+          *reinterpret_cast<uint32_t*>(smem + L::kKV +
+                                       tile_off<D>(warp * 16 + g + 8 * (i & 1), half * kC0 + 2 * s + (i >> 1)) +
                                        4 * c) = w[i];
       } else {
 #pragma unroll
@@ -145,20 +163,22 @@ __global__ void __launch_bounds__(kPfThreads, D > 128 ? 1 : 3) attn_prefill_kern
   auto k16_base = [&](int buf) { return Q8 ? uint32_t(2 * L::kRaw) : uint32_t(buf * 2 * L::kTile); };
   auto v16_base = [&](int buf) { return k16_base(buf) + L::kTile; };
 
-  // ---- producer: key row tid / 2, half tid % 2 of the tile
+  // ---- producer: key row tid / kTPR, part tid % kTPR of the row
   constexpr int kRowBytes = Q8 ? D : 2 * D;      // cache bytes per key row and head
-  constexpr int kHalf = kRowBytes / 2;           // bytes this thread copies per matrix
+  constexpr int kTPR = L::kThreads / kBN;        // threads per key row
+  constexpr int kHalf = kRowBytes / kTPR;        // bytes this thread copies per matrix
+  const int prow = tid / kTPR, ppart = tid % kTPR;
   auto issue_tile = [&](int t, int buf) {
-    const int key = k_begin + t * kBN + (tid >> 1);
+    const int key = k_begin + t * kBN + prow;
     const bool ok = key < k_end;
     const int kk = ok ? key : k_end - 1;
     const int blk = p.block_table[int64_t(n) * p.bt_stride + kk / p.block_size];
     const int slot = kk % p.block_size;
-    const uint8_t* ksrc = p.kc + int64_t(blk) * p.k_sb + int64_t(slot) * p.k_ss + int64_t(kvh) * p.k_sh + (tid & 1) * kHalf;
-    const uint8_t* vsrc = p.vc + int64_t(blk) * p.v_sb + int64_t(slot) * p.v_ss + int64_t(kvh) * p.v_sh + (tid & 1) * kHalf;
-    const int row = tid >> 1;
+    const uint8_t* ksrc = p.kc + int64_t(blk) * p.k_sb + int64_t(slot) * p.k_ss + int64_t(kvh) * p.k_sh + ppart * kHalf;
+    const uint8_t* vsrc = p.vc + int64_t(blk) * p.v_sb + int64_t(slot) * p.v_ss + int64_t(kvh) * p.v_sh + ppart * kHalf;
+    const int row = prow;
     if constexpr (Q8) {
-      const uint32_t kd = smem_s + raw_base(buf) + row * D + (tid & 1) * kHalf;
+      const uint32_t kd = smem_s + raw_base(buf) + row * D + ppart * kHalf;
       const uint32_t vd = kd + L::kRawKV;
       if (p.aligned16) {
 #pragma unroll
@@ -173,7 +193,7 @@ __global__ void __launch_bounds__(kPfThreads, D > 128 ? 1 : 3) attn_prefill_kern
           cp_async_4_zfill(vd + 4 * i, vsrc + 4 * i, ok);
         }
       }
-      if ((tid & 1) == 0) {
+      if (ppart == 0) {
         const uint32_t sd = smem_s + raw_base(buf) + 2 * L::kRawKV + row * 4;
         cp_async_4_zfill(sd, p.ks + int64_t(blk) * p.ks_sb + int64_t(slot) * p.ks_ss + int64_t(kvh) * p.ks_sh, ok);
         cp_async_4_zfill(sd + kBN * 4, p.vs + int64_t(blk) * p.vs_sb + int64_t(slot) * p.vs_ss + int64_t(kvh) * p.vs_sh, ok);
@@ -182,7 +202,7 @@ __global__ void __launch_bounds__(kPfThreads, D > 128 ? 1 : 3) attn_prefill_kern
       // bf16: straight into the swizzled operand tiles (chunks of 8 elements)
 #pragma unroll
       for (int i = 0; i < kHalf / 16; ++i) {
-        const int chunk = (tid & 1) * (kHalf / 16) + i;
+        const int chunk = ppart * (kHalf / 16) + i;
         cp_async_16_zfill(smem_s + k16_base(buf) + tile_off<D>(row, chunk), ksrc + 16 * i, ok);
         cp_async_16_zfill(smem_s + v16_base(buf) + tile_off<D>(row, chunk), vsrc + 16 * i, ok);
       }
@@ -190,9 +210,9 @@ __global__ void __launch_bounds__(kPfThreads, D > 128 ? 1 : 3) attn_prefill_kern
     cp_async_commit();
   };
 
-  float o[D / 8][4];
+  float o[DW / 8][4];
 #pragma unroll
-  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  for (int i = 0; i < DW / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
   const float sl2 = p.scale * kLog2e;
 
@@ -204,8 +224,8 @@ __global__ void __launch_bounds__(kPfThreads, D > 128 ? 1 : 3) attn_prefill_kern
     if (t + 1 < n_tiles) issue_tile(t + 1, buf ^ 1);
     if constexpr (Q8) {
       // widen this thread's half rows: 0x6400 | (b ^ 0x80) is fp16 1024 + b + 128
-      const int row = tid >> 1;
-      const uint8_t* rk = smem + raw_base(buf) + row * D + (tid & 1) * kHalf;
+      const int row = prow;
+      const uint8_t* rk = smem + raw_base(buf) + row * D + ppart * kHalf;
 #pragma unroll
       for (int m = 0; m < 2; ++m) {
         const uint8_t* src = rk + m * L::kRawKV;
@@ -220,7 +240,7 @@ __global__ void __launch_bounds__(kPfThreads, D > 128 ? 1 : 3) attn_prefill_kern
             h[2 * j] = sub_f16x2(prmt(ws[j], 0x64646464u, 0x4140), 0x64806480u);
             h[2 * j + 1] = sub_f16x2(prmt(ws[j], 0x64646464u, 0x4342), 0x64806480u);
           }
-          const int chunk = ((tid & 1) * (kHalf / 16) + i) * 2;   // 16 bytes -> two 8-element chunks
+          const int chunk = (ppart * (kHalf / 16) + i) * 2;   // 16 bytes -> two 8-element chunks
           *reinterpret_cast<uint4*>(dst + tile_off<D>(row, chunk)) = make_uint4(h[0], h[1], h[2], h[3]);
           *reinterpret_cast<uint4*>(dst + tile_off<D>(row, chunk + 1)) = make_uint4(h[4], h[5], h[6], h[7]);
         }
@@ -235,28 +255,43 @@ __global__ void __launch_bounds__(kPfThreads, D > 128 ? 1 : 3) attn_prefill_kern
     const uint32_t kt = smem_s + k16_base(buf), vt = smem_s + v16_base(buf);
     const int k0 = k_begin + t * kBN;
 
-    // ---- S = Q K^T: 8 key tiles of 8 x D / 16 steps
+    // ---- S = Q K^T: kBN / 8 key tiles of 8 x DW / 16 steps
     // (d steps outermost: consecutive MMAs then feed eight independent accumulators)
     float s[kBN / 8][4];
 #pragma unroll
     for (int j = 0; j < kBN / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
 #pragma unroll
-    for (int sp = 0; sp < D / 32; ++sp) {
+    for (int sp = 0; sp < DW / 32; ++sp) {
       uint32_t b[kBN / 8][4];
 #pragma unroll
       for (int j = 0; j < kBN / 8; ++j)
-        ldmatrix_x4(b[j], kt + tile_off<D>(8 * j + (lane & 7), 4 * sp + (lane >> 3)));
+        ldmatrix_x4(b[j], kt + tile_off<D>(8 * j + (lane & 7), half * kC0 + 4 * sp + (lane >> 3)));
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         if constexpr (QS)
           ldmatrix_x4(qf[0], q_tile + tile_off<D>(warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1),
-                                                  2 * (2 * sp + h) + (lane >> 4)));
+                                                  half * kC0 + 2 * (2 * sp + h) + (lane >> 4)));
         const uint32_t (&qa)[4] = qf[QS ? 0 : 2 * sp + h];
 #pragma unroll
         for (int j = 0; j < kBN / 8; ++j) {
           if constexpr (Q8) mma_f16_16816(s[j], qa, b[j][2 * h], b[j][2 * h + 1]);
           else mma_bf16_16816(s[j], qa, b[j][2 * h], b[j][2 * h + 1]);
         }
+      }
+    }
+
+    if constexpr (SPLIT == 2) {
+      // the pair adds its score partials: both warps then hold the same scores
+      float4* const mine = reinterpret_cast<float4*>(smem + L::kKV + L::kQ) +
+                           ((((t & 1) * 4 + warp) * 2 + half) * (kBN / 8)) * 32 + lane;
+#pragma unroll
+      for (int j = 0; j < kBN / 8; ++j) mine[j * 32] = make_float4(s[j][0], s[j][1], s[j][2], s[j][3]);
+      asm volatile("bar.sync %0, 64;" ::"r"(warp + 1) : "memory");
+      const float4* const other = half == 0 ? mine + (kBN / 8) * 32 : mine - (kBN / 8) * 32;
+#pragma unroll
+      for (int j = 0; j < kBN / 8; ++j) {
+        const float4 x = other[j * 32];
+        s[j][0] += x.x, s[j][1] += x.y, s[j][2] += x.z, s[j][3] += x.w;
       }
     }
 
@@ -311,7 +346,7 @@ __global__ void __launch_bounds__(kPfThreads, D > 128 ? 1 : 3) attn_prefill_kern
     if (moved) {
       l_lo *= r_lo, l_hi *= r_hi;
 #pragma unroll
-      for (int i = 0; i < D / 8; ++i) o[i][0] *= r_lo, o[i][1] *= r_lo, o[i][2] *= r_hi, o[i][3] *= r_hi;
+      for (int i = 0; i < DW / 8; ++i) o[i][0] *= r_lo, o[i][1] *= r_lo, o[i][2] *= r_hi, o[i][3] *= r_hi;
     }
 
     uint32_t pf[kBN / 16][4];   // P as the A operand of P V
@@ -330,13 +365,14 @@ __global__ void __launch_bounds__(kPfThreads, D > 128 ? 1 : 3) attn_prefill_kern
       pf[tt][h + 1] = Q8 ? pack_f16x2(pv[2], pv[3]) : pack_bf16x2(pv[2], pv[3]);
     }
 
-    // ---- O += P V: D / 8 output tiles x 4 key steps of 16
+    // ---- O += P V: DW / 8 output tiles x kBN / 16 key steps of 16
 #pragma unroll
     for (int tt = 0; tt < kBN / 16; ++tt) {
 #pragma unroll
-      for (int i2 = 0; i2 < D / 16; ++i2) {
+      for (int i2 = 0; i2 < DW / 16; ++i2) {
         uint32_t b[4];
-        ldmatrix_x4_trans(b, vt + tile_off<D>(16 * tt + (lane & 7) + 8 * ((lane >> 3) & 1), 2 * i2 + (lane >> 4)));
+        ldmatrix_x4_trans(b, vt + tile_off<D>(16 * tt + (lane & 7) + 8 * ((lane >> 3) & 1),
+                                              half * kC0 + 2 * i2 + (lane >> 4)));
         if constexpr (Q8) {
           mma_f16_16816(o[2 * i2], pf[tt], b[0], b[1]);
           mma_f16_16816(o[2 * i2 + 1], pf[tt], b[2], b[3]);
@@ -363,12 +399,12 @@ __global__ void __launch_bounds__(kPfThreads, D > 128 ? 1 : 3) attn_prefill_kern
   const float inv_lo = l_lo > 0.f ? unlift / l_lo : 0.f, inv_hi = l_hi > 0.f ? unlift / l_hi : 0.f;
   const int r_lo = row0 + g, r_hi = row0 + g + 8;
 #pragma unroll
-  for (int i = 0; i < D / 8; ++i) {
+  for (int i = 0; i < DW / 8; ++i) {
     if (r_lo < q_len)
-      *reinterpret_cast<uint32_t*>(p.out + int64_t(q_begin + r_lo) * p.o_st + head * p.o_sh + 8 * i + 2 * c) =
+      *reinterpret_cast<uint32_t*>(p.out + int64_t(q_begin + r_lo) * p.o_st + head * p.o_sh + half * DW + 8 * i + 2 * c) =
           pack_bf16x2(o[i][0] * inv_lo, o[i][1] * inv_lo);
     if (r_hi < q_len)
-      *reinterpret_cast<uint32_t*>(p.out + int64_t(q_begin + r_hi) * p.o_st + head * p.o_sh + 8 * i + 2 * c) =
+      *reinterpret_cast<uint32_t*>(p.out + int64_t(q_begin + r_hi) * p.o_st + head * p.o_sh + half * DW + 8 * i + 2 * c) =
           pack_bf16x2(o[i][2] * inv_hi, o[i][3] * inv_hi);
   }
 }
@@ -385,7 +421,7 @@ int launch_prefill(const PrefillArgs& p, int64_t max_tiles, cudaStream_t st) {
     if (dev >= 0 && dev < 64) done[dev] = true;
   }
   const dim3 grid{unsigned(max_tiles), unsigned(p.hq), 1u};
-  kernel<<<grid, kPfThreads, L::kSmem, st>>>(p);
+  kernel<<<grid, L::kThreads, L::kSmem, st>>>(p);
   return launch_status("attn_prefill");
 }
 
@@ -404,8 +440,8 @@ extern "C" int strix_attn_prefill_bf16(
     int64_t v_stride_h, int64_t ks_stride_b, int64_t ks_stride_s, int64_t ks_stride_h,
     int64_t vs_stride_b, int64_t vs_stride_s, int64_t vs_stride_h, double scale,
     int64_t num_splits, int64_t window_left, int kv_int8, strix_stream_t stream) {
-  STRIX_CHECK(head_dim == 64 || head_dim == 128 || head_dim == 256,
-              "head_dim 64, 128 or 256 (others are not built)");
+  STRIX_CHECK(head_dim == 64 || head_dim == 128 || head_dim == 256 || head_dim == 512,
+              "head_dim 64, 128, 256 or 512 (others are not built)");
   STRIX_CHECK(hq > 0 && hkv > 0 && hq % hkv == 0 && hq <= 65535, "hq must be a multiple of hkv");
   STRIX_CHECK(block_size >= 1 && nseq >= 0 && total_q >= 0, "bad sizes");
   STRIX_CHECK(num_splits >= 1 && num_splits <= 64, "num_splits in [1, 64]");
@@ -436,6 +472,7 @@ extern "C" int strix_attn_prefill_bf16(
   // an upper bound on the 64-query tiles without reading the lengths on the host
   const int64_t max_tiles = (total_q + kBM - 1) / kBM + nseq;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (head_dim == 512) return kv_int8 ? launch_prefill<512, true>(p, max_tiles, st) : launch_prefill<512, false>(p, max_tiles, st);
   if (head_dim == 256) return kv_int8 ? launch_prefill<256, true>(p, max_tiles, st) : launch_prefill<256, false>(p, max_tiles, st);
   if (head_dim == 128) return kv_int8 ? launch_prefill<128, true>(p, max_tiles, st) : launch_prefill<128, false>(p, max_tiles, st);
   return kv_int8 ? launch_prefill<64, true>(p, max_tiles, st) : launch_prefill<64, false>(p, max_tiles, st);

@@ -366,6 +366,22 @@ KERNELS: list[Kernel] = [
          "sinks": (True, False)},
         {"tile": "64 queries x 64 keys", "mma": "m16n8k16 f16 (int8 KV) / bf16", "bound": "tensor"},
     ),
+    Kernel(
+        "attn_prefill_bf16", "attn_prefill",
+        "head 512 (the reference's GQA 8 row and any other ratio): 64 queries x 32 keys, eight "
+        "warps - each group of 16 queries belongs to a pair of warps that own 256 of the head's "
+        "dims each (their part of Q, K, V and O) and add their score partials through shared memory",
+        {"head_dim": 512, "gqa": Range(1, 64), "dtype": "bf16", "kv_dtype": ("bf16", "int8"),
+         "split_kv": (True, False), "window": (True, False), "causal": True,
+         "sinks": (True, False)},
+        {"tile": "64 queries x 32 keys", "mma": "m16n8k16 f16 (int8 KV) / bf16", "bound": "tensor"},
+    ),
+    Kernel("attn_decode_bf16", "attn_decode",
+           "int8 KV cache at head 512: no split-KV kernel of its own - the prefill kernel with one "
+           "query per sequence (correct, but it reads a KV head once per query head)",
+           {"head_dim": 512, "gqa": Range(1, 64), "queries": 1, "dtype": "bf16",
+            "kv_dtype": ("int8",), "window": (True, False), "sinks": (True, False)},
+           {"tile": "64 queries x 32 keys", "bound": "hbm"}),
 ]
 
 _POINT_TYPES = (int, bool, str)

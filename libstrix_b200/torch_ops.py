@@ -103,12 +103,14 @@ def attn_decode_bf16(
     bf16_rows_ok = not q8 and d in (64, 128, 256, 512) and q.size(1) // key_cache.size(2) <= 8 and all(
         st % 8 == 0 for t in (key_cache, value_cache) for st in t.stride()[:3]) and \
         key_cache.data_ptr() % 16 == 0 and value_cache.data_ptr() % 16 == 0
-    if not q8 and not bf16_rows_ok:
-        # bf16 caches the split-KV decode kernel does not take (rows off 16-byte
-        # boundaries, other head sizes): the prefill kernel with one query per sequence
+    if (not q8 and not bf16_rows_ok) or (q8 and d == 512):
+        # caches the split-KV decode kernels do not take (bf16 rows off 16-byte
+        # boundaries or at a GQA ratio above 8, int8 caches at head 512): the prefill
+        # kernel with one query per sequence
         nseq = q.size(0)
         cu = torch.arange(nseq + 1, dtype=torch.int32, device=q.device)
-        attn_prefill_bf16(out, q, key_cache, value_cache, None, None, cu, seq_lens, block_table, cu,
+        attn_prefill_bf16(out, q, key_cache, value_cache, k_scale if q8 else None,
+                          v_scale if q8 else None, cu, seq_lens, block_table, cu,
                           0, scale, 1, window_left, sinks)
         return
     nseq, hq = q.size(0), q.size(1)

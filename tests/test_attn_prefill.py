@@ -102,17 +102,17 @@ def test_int8_kv_matches_dequantized_reference(hq, hkv, hd, q_lens, ctx_lens, nu
     torch.testing.assert_close(out, rounded, rtol=2e-2, atol=2e-2)
 
 
-@pytest.mark.parametrize("hq,hkv", [(12, 2), (16, 2), (4, 2)])
+@pytest.mark.parametrize("hq,hkv,hd", [(12, 2, 256), (16, 2, 256), (4, 2, 256), (16, 2, 512), (3, 1, 512)])
 @pytest.mark.parametrize("q_lens,ctx_lens", [([64], [0]), ([100, 5, 17], [0, 40, 300]), ([1, 1], [70, 200]),
                                              ([130], [77])])
 @pytest.mark.parametrize("int8", [False, True])
 @pytest.mark.parametrize("window_left,use_sinks", [(-1, False), (40, True)])
-def test_head_256(hq, hkv, q_lens, ctx_lens, int8, window_left, use_sinks):
-    """Head 256 at GQA 6 / 8 / 2 (the reference's rows at
-    python/strix/registry.py:368-424): the mma.sync kernel with the query tile in
-    shared memory."""
-    q, kc, vc, cu, seq_lens, table = A.build_paged_kv(q_lens, ctx_lens, hq, hkv, 16, hd=256)
-    scale = 256 ** -0.5
+def test_head_256_and_512(hq, hkv, hd, q_lens, ctx_lens, int8, window_left, use_sinks):
+    """Head 256 at GQA 6 / 8 / 2 and head 512 at GQA 8 (the reference's rows at
+    python/strix/registry.py:368-441): the mma.sync kernel with the query tile in
+    shared memory, at head 512 with the head's dims split over pairs of warps."""
+    q, kc, vc, cu, seq_lens, table = A.build_paged_kv(q_lens, ctx_lens, hq, hkv, 16, hd=hd)
+    scale = hd ** -0.5
     sinks = torch.linspace(-1.0, 2.0, hq) if use_sinks else None
     if int8:
         kq, ks = A.quantize_kv(kc)
@@ -178,10 +178,10 @@ def test_sinks_refuse_split_kv():
 
 
 def test_unbuilt_head_dim_is_rejected():
-    q, kc, vc, cu, seq_lens, table = A.build_paged_kv([4], [0], 8, 2, 16, hd=512)
-    with pytest.raises(RuntimeError, match="head_dim 64, 128 or 256"):
+    q, kc, vc, cu, seq_lens, table = A.build_paged_kv([4], [0], 8, 2, 16, hd=96)
+    with pytest.raises(RuntimeError, match="head_dim 64, 128, 256 or 512"):
         run(q, kc, vc, cu, seq_lens, table, 0.1)
-    assert strix.select("attn_prefill", head_dim=512, gqa=4, dtype="bf16", kv_dtype="int8",
+    assert strix.select("attn_prefill", head_dim=96, gqa=4, dtype="bf16", kv_dtype="int8",
                         split_kv=False, window=False, causal=True, sinks=False) is None
 
 

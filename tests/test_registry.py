@@ -17,7 +17,8 @@ def test_every_registered_op_has_a_row_and_back():
 
 def test_select_hits_and_misses():
     assert strix.select("attn_decode", **DECODE) == "attn_decode_bf16"
-    assert strix.select("attn_decode", **{**DECODE, "head_dim": 512}) is None
+    assert strix.select("attn_decode", **{**DECODE, "head_dim": 512}) == "attn_decode_bf16"
+    assert strix.select("attn_decode", **{**DECODE, "head_dim": 96}) is None
     assert strix.select("attn_decode", **{**DECODE, "kv_dtype": "fp8_e4m3"}) is None
     assert strix.select("no_such_op", x=1) is None
 

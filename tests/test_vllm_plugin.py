@@ -121,9 +121,12 @@ def test_attention_gate_follows_the_kernel_table():
     assert attn.covers("decode", 128, 8, "int8", False, False)
     assert attn.covers("prefill", 128, 5, "int8", True, True)
     assert attn.covers("prefill", 64, 4, "bf16", False, False)
-    assert not attn.covers("decode", 512, 8, "int8", False, False)
+    assert attn.covers("decode", 512, 8, "int8", False, False)
+    assert attn.covers("decode", 512, 8, "bf16", True, False)
+    assert not attn.covers("decode", 96, 8, "int8", False, False)
     assert attn.covers("prefill", 256, 8, "int8", False, False)
-    assert not attn.covers("prefill", 512, 8, "int8", False, False)
+    assert attn.covers("prefill", 512, 8, "int8", False, False)
+    assert not attn.covers("prefill", 96, 8, "int8", False, False)
     impl = attn.impl_class()
     assert impl.__name__ == "StrixTritonAttentionImpl" and issubclass(attn.backend_class(), object)
 
