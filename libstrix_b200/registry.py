@@ -249,8 +249,9 @@ KERNELS: list[Kernel] = [
     Kernel("w4a8_wmma_gemm", "w4a16",
            "int4 weights (ExLlama word order) x activations quantised to int8 per (row, 128 "
            "group) inside the op: s8 MMAs, int32-exact per group, fp32 fold; the dense twin of "
-           "moe_gemm_w4a8 on the weight-streaming kernel",
-           {"weight_bits": 4, "group_size": (0, 128), "dtype": "bf16", "rows": Range(hi=128),
+           "moe_gemm_w4a8 on the weight-streaming kernel. Scales per 32 elements ([K/32, N]) "
+           "run with bf16 activations on the w4a16 kernel instead",
+           {"weight_bits": 4, "group_size": (0, 32, 128), "dtype": "bf16", "rows": Range(hi=128),
             "act_quant": "int8"}, dict(_STREAM_SPEC)),
     Kernel("w4a16_wmma_gemm", "w4a16",
            "int4 W4A16 dense GEMM (ExLlama word order), optional bias; the dense form of "
@@ -288,6 +289,19 @@ KERNELS: list[Kernel] = [
            "the op, int32-exact per group, fp32 group-scale fold. K % 128 == 0",
            {"weight_bits": 8, "group_size": (0, 128), "rows": Range(lo=9), "dtype": "bf16"},
            dict(_STREAM_SPEC)),
+    *[Kernel(name, op, f"bench-only: {name[:-4]} pinned to one token tile (cfg 0 / 1 / 2 = 16 / 32 / "
+             "64 tokens x 128 weight rows) instead of the choice by row count",
+             cons, {"cfg": "0..2"})
+      for name, op, cons in (
+          ("fp8_wmma_gemm_cfg", "fp8_tile_sweep",
+           {"weight_bits": 8, "weight_dtype": "fp8_e4m3", "group_size": (0, 128), "dtype": "bf16"}),
+          ("fp8_wmma_gemm_raw_cfg", "fp8_tile_sweep",
+           {"weight_bits": 8, "weight_dtype": "fp8_e4m3", "group_size": (0, 128), "dtype": "fp16"}),
+          ("mxfp4_wmma_gemm_cfg", "mxfp4_tile_sweep",
+           {"weight_bits": 4, "group_size": 32, "dtype": "bf16"}),
+          ("w8a8_wmma_gemm_cfg", "w8a8_tile_sweep",
+           {"weight_bits": 8, "group_size": (0, 128), "rows": Range(lo=1), "dtype": "bf16"}),
+      )],
     # ---------------------------------------------------------- dense GEMMs
     Kernel("w8a8_int8_gemm", "w8a8",
            "dense W8A8 INT8 GEMM on tcgen05 kind::i8 (int32 sums in TMEM, exact): int8 "

@@ -570,6 +570,16 @@ def _dense_block_m(m: int) -> int:
     return 16 if m <= 16 else 32 if m <= 32 else 64
 
 
+# Token-tile sizes of the weight-streaming GEMMs that the bench-only *_cfg ops pin
+# (the reference's *_cfg ops pin one of its own tile shapes the same way).
+TILE_CFGS = (16, 32, 64)
+
+
+def _cfg_block_m(cfg: int) -> int:
+    _check(0 <= cfg < len(TILE_CFGS), f"cfg must be in [0, {len(TILE_CFGS)})")
+    return TILE_CFGS[cfg]
+
+
 def _gemm_w4(c, a, w, scales, bias, routing, topk_weights, top_k, block_m, wfmt, group, gate):
     """Host side of strix_gemm_w4a16; routing = (sorted_ids, expert_ids, num_post) or None."""
     dense = routing is None
@@ -718,13 +728,26 @@ def _dense_fake(rows_from, w_from):
 
 @_define("mxfp4_wmma_gemm(Tensor w, Tensor x, Tensor scales, Tensor? bias) -> Tensor",
          fake=_dense_fake(1, 0))
-def mxfp4_wmma_gemm(w, x, scales, bias=None):
+def mxfp4_wmma_gemm(w, x, scales, bias=None, block_m=None):
     _check(w.dim() == 2 and x.dim() == 2, "bad ranks")
     _check(x.size(1) % 128 == 0, "K must be a multiple of 128")
     out = torch.empty(x.size(0), w.size(0), dtype=torch.bfloat16, device=x.device)
     if x.size(0):
-        _gemm_w4(out, x, w, scales, bias, None, None, 1, _dense_block_m(x.size(0)), _W_MXFP4, 32, 0)
+        _gemm_w4(out, x, w, scales, bias, None, None, 1, block_m or _dense_block_m(x.size(0)),
+                 _W_MXFP4, 32, 0)
     return out
+
+
+def _dense_cfg_fake(w, x, *a):
+    return x.new_empty((x.size(0), w.size(0)), dtype=torch.bfloat16)
+
+
+@_define("mxfp4_wmma_gemm_cfg(Tensor w, Tensor x, Tensor scales, Tensor? bias, int cfg) -> Tensor",
+         fake=_dense_cfg_fake)
+def mxfp4_wmma_gemm_cfg(w, x, scales, bias, cfg):
+    """mxfp4_wmma_gemm pinned to the token tile TILE_CFGS[cfg] instead of the choice
+    by row count (bench-only, as csrc/torch_ops.cpp:288-292 of the reference)."""
+    return mxfp4_wmma_gemm(w, x, scales, bias, _cfg_block_m(cfg))
 
 
 @_define("mxfp4_gemv(Tensor x, Tensor w, Tensor scales) -> Tensor", fake=_dense_fake(0, 1))
@@ -800,7 +823,7 @@ def fp8_dequant(w, scales):
     return _dequant(w, scales.reshape(n), 2, 128, 1, k)
 
 
-def _dense_w8(x, w, scales, bias, wfmt, afmt, scale_kind, group=0):
+def _dense_w8(x, w, scales, bias, wfmt, afmt, scale_kind, group=0, block_m=None):
     m, k = x.shape
     n = w.size(0)
     _check(w.dim() == 2 and w.size(1) == k and x.stride(1) == 1 and w.stride(1) == 1,
@@ -818,8 +841,8 @@ def _dense_w8(x, w, scales, bias, wfmt, afmt, scale_kind, group=0):
             _lib.call("strix_dense_gemm_w8a16", out.data_ptr(), x.data_ptr(), w.data_ptr(),
                       scales.data_ptr(), _ptr(bias), m, n, k, x.stride(0), out.stride(0), w.stride(0),
                       scales.stride(0) if scale_kind != _S_CHANNEL else 0, bias_stride,
-                      _dense_block_m(m), wfmt, afmt, scale_kind, _SCALE_DTYPES[scales.dtype],
-                      group, _stream())
+                      block_m or _dense_block_m(m), wfmt, afmt, scale_kind,
+                      _SCALE_DTYPES[scales.dtype], group, _stream())
     return out
 
 
@@ -841,15 +864,15 @@ def w8a16_skinny_gemm(in_a, in_b, in_scale, in_bias, CuCount, group_size):
     return _dense_w8(in_b, in_a, in_scale.reshape(n), in_bias, _W_U8B128, _A_BF16, _S_CHANNEL)
 
 
-def _fp8_dense(w, x, scales, bias, afmt):
+def _fp8_dense(w, x, scales, bias, afmt, block_m=None):
     _check(w.dtype == torch.float8_e4m3fn and scales.dtype == torch.float32, "w e4m3, scales fp32")
     n, k = w.shape
     if scales.dim() == 2 and scales.size(1) != 1:
         _check(tuple(scales.shape) == ((n + 127) // 128, k // 128) and scales.stride(1) == 1,
                "block scales must be [ceil(N/128), K/128]")
-        return _dense_w8(x, w, scales, bias, _W_E4M3, afmt, _S_BLOCK)
+        return _dense_w8(x, w, scales, bias, _W_E4M3, afmt, _S_BLOCK, block_m=block_m)
     _check(scales.numel() == n, "channel scales must be [N]")
-    return _dense_w8(x, w, scales.reshape(n), bias, _W_E4M3, afmt, _S_CHANNEL)
+    return _dense_w8(x, w, scales.reshape(n), bias, _W_E4M3, afmt, _S_CHANNEL, block_m=block_m)
 
 
 @_define("fp8_skinny_gemm(Tensor in_a, Tensor in_b, Tensor in_scale, Tensor? in_bias, int CuCount) "
@@ -870,6 +893,24 @@ def fp8_wmma_gemm(w, x, scales):
 def fp8_wmma_gemm_raw(w, x, scales):
     _check(x.dtype == torch.float16, "x must be fp16")
     return _fp8_dense(w, x, scales, None, _A_F16)
+
+
+@_define("fp8_wmma_gemm_cfg(Tensor w, Tensor x, Tensor scales, int cfg) -> Tensor",
+         fake=_dense_cfg_fake)
+def fp8_wmma_gemm_cfg(w, x, scales, cfg):
+    """fp8_wmma_gemm pinned to the token tile TILE_CFGS[cfg] (bench-only, as
+    csrc/torch_ops.cpp:258 of the reference)."""
+    _check(x.dtype == torch.bfloat16, "x must be bf16")
+    return _fp8_dense(w, x, scales, None, _A_BF16, _cfg_block_m(cfg))
+
+
+@_define("fp8_wmma_gemm_raw_cfg(Tensor w, Tensor x, Tensor scales, int cfg) -> Tensor",
+         fake=_dense_cfg_fake)
+def fp8_wmma_gemm_raw_cfg(w, x, scales, cfg):
+    """fp8_wmma_gemm_raw pinned to the token tile TILE_CFGS[cfg] (bench-only, as
+    csrc/torch_ops.cpp:260 of the reference)."""
+    _check(x.dtype == torch.float16, "x must be fp16")
+    return _fp8_dense(w, x, scales, None, _A_F16, _cfg_block_m(cfg))
 
 
 def _gemm_a8(c, qa, sa, w, scales, routing, topk_weights, top_k, block_m, wfmt, gate,
@@ -922,7 +963,7 @@ def moe_gemm_w4a8(c, qa, sa, b, scales, sorted_ids, expert_ids, num_post_padded,
 
 @_define("w8a8_wmma_gemm(Tensor in_w8, Tensor in_act, Tensor in_scale) -> Tensor",
          fake=_dense_fake(1, 0))
-def w8a8_wmma_gemm(in_w8, in_act, in_scale):
+def w8a8_wmma_gemm(in_w8, in_act, in_scale, block_m=None):
     """Excess-128 byte weights [N, K] x bf16 activations quantised to int8 per (row,
     128 group) inside the op; int32-exact sums per group, fp32 fold. in_scale fp32
     [N], [K/128, N] (group-major) or [N, K/128]."""
@@ -948,8 +989,18 @@ def w8a8_wmma_gemm(in_w8, in_act, in_scale):
     qa = torch.empty(m, k, dtype=torch.int8, device=in_act.device)
     sa = torch.empty(m, g, dtype=torch.float32, device=in_act.device)
     moe_act_quant_i8(in_act, qa, sa)
-    _gemm_a8(out, qa, sa, in_w8, sc, None, None, 1, _dense_block_m(m), _W_U8B128, 0, s_sn, s_sg, kind)
+    _gemm_a8(out, qa, sa, in_w8, sc, None, None, 1, block_m or _dense_block_m(m), _W_U8B128, 0,
+             s_sn, s_sg, kind)
     return out
+
+
+@_define("w8a8_wmma_gemm_cfg(Tensor in_w8, Tensor in_act, Tensor in_scale, int cfg) -> Tensor",
+         fake=_dense_cfg_fake)
+def w8a8_wmma_gemm_cfg(in_w8, in_act, in_scale, cfg):
+    """w8a8_wmma_gemm pinned to the token tile TILE_CFGS[cfg]: same arithmetic and the
+    same activation quantiser (bench-only, as csrc/torch_ops.cpp:280-282 of the
+    reference; any row count, where the reference wants a multiple of 128)."""
+    return w8a8_wmma_gemm(in_w8, in_act, in_scale, _cfg_block_m(cfg))
 
 
 @_define("w4a8_wmma_gemm(Tensor in_w4, Tensor in_act, Tensor in_scale) -> Tensor",
@@ -959,7 +1010,9 @@ def w4a8_wmma_gemm(in_w4, in_act, in_scale):
     bf16 activations quantised to int8 per (row, 128 group) inside the op; int32-exact
     sums per group, fp32 fold (csrc/torch_ops.cpp:283,
     csrc/gemm/w8a8_wmma_gemm.hip:128-132,278-291 of the reference). in_scale fp32 [N]
-    or [K/128, N] (group-major); the reference's [K/32, N] form is not built."""
+    or [K/128, N] (group-major). The [K/32, N] form (a weight scale per 32 elements
+    cannot ride a 128-wide integer sum) runs on the bf16-activation kernel instead:
+    the activations are not quantised there, the scales are rounded to bf16."""
     w = _as_u8(in_w4)
     n, k = w.size(0), w.size(1) * 2
     m = in_act.size(0)
@@ -969,11 +1022,12 @@ def w4a8_wmma_gemm(in_w4, in_act, in_scale):
     _check(k % 128 == 0, "K must be a multiple of 128")
     _check(in_scale.dtype == torch.float32, "in_scale must be fp32")
     g = k // 128
+    if in_scale.numel() != n and tuple(in_scale.shape) == (k // 32, n):
+        return w4a16_wmma_gemm(in_act, w, in_scale.t().to(torch.bfloat16).contiguous(), None, 32)
     if in_scale.numel() == n:
         kind, s_sn, s_sg, sc = _S_CHANNEL, 0, 1, in_scale.reshape(n)
     else:
-        _check(tuple(in_scale.shape) == (g, n),
-               "in_scale must be [N] or [K/128, N] (scales per 32 elements are not built)")
+        _check(tuple(in_scale.shape) == (g, n), "in_scale must be [N], [K/128, N] or [K/32, N]")
         kind, s_sn, s_sg, sc = _S_GROUP, in_scale.stride(1), in_scale.stride(0), in_scale
     out = torch.empty(m, n, dtype=torch.bfloat16, device=in_act.device)
     if m == 0:

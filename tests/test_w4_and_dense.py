@@ -220,9 +220,24 @@ def test_w4a8_wmma_gemm(n, k, m, group_size):
     qa, sa = G.act_quant_group_i8(x)
     close_to_peak(out, (qa.float() * sa.repeat_interleave(128, 1)) @ w.t(), 1e-2)
     close_to_peak(out, x.float() @ w.t(), 6e-2)             # the reference's statement
-    with pytest.raises(RuntimeError, match="not built"):
+    with pytest.raises(RuntimeError, match=r"\[K/32, N\]"):
         ops.w4a8_wmma_gemm(G.int4_pack_exllama(q4).to(DEV), x.to(DEV),
-                           torch.ones(k // 32, n, device=DEV))
+                           torch.ones(k // 64, n, device=DEV))
+
+
+@pytest.mark.parametrize("n,k", [(16384, 5120), (256, 1024)])
+@pytest.mark.parametrize("m", [6, 300])
+def test_w4a8_wmma_gemm_scales_per_32(n, k, m):
+    """group_size 32 of tests/test_w8a16.py:74-98: scales [K/32, N]. Served without
+    quantising the activations, so it meets the reference's bound against the
+    unquantised product with room to spare."""
+    g = torch.Generator().manual_seed(m)
+    x = torch.randn(m, k, generator=g).bfloat16()
+    q4 = torch.randint(0, 16, (n, k), generator=g, dtype=torch.uint8)
+    s = (torch.rand(n, k // 32, generator=g) * 0.05 + 0.01).bfloat16()
+    w = (q4.float() - 8.0) * s.float().repeat_interleave(32, 1)
+    out = ops.w4a8_wmma_gemm(G.int4_pack_exllama(q4).to(DEV), x.to(DEV), s.float().t().contiguous().to(DEV))
+    close_to_peak(out, x.float() @ w.t(), 1e-2)
 
 
 # ------------------------------------------------------------------ dense 8-bit
@@ -344,6 +359,40 @@ def test_w8a8_wmma_gemm_reference_schema(n, k, m, scale_form):
     close_to_peak(out, exact, 1e-2)
     # and the reference's looser statement against unquantised activations
     close_to_peak(out, x.float() @ (w_i8.float() * full).t(), 6e-2)
+
+
+# ------------------------------------------------------- bench-only *_cfg ops
+
+@pytest.mark.parametrize("cfg", [0, 1, 2])
+@pytest.mark.parametrize("m", [5, 130])
+def test_cfg_ops_match_the_production_ops(cfg, m):
+    """The four tile-sweep ops of the reference's schema (csrc/torch_ops.cpp:258-292):
+    the same GEMM pinned to one token tile, against the oracle and against the op that
+    picks the tile by row count."""
+    from libstrix_b200 import torch_ops
+
+    n, k = 1024, 1024
+    g = torch.Generator().manual_seed(cfg)
+    x = torch.randn(m, k, generator=g).bfloat16()
+    w, s = mx_case(n, k)
+    out = ops.mxfp4_wmma_gemm_cfg(w.to(DEV), x.to(DEV), s.to(DEV), None, cfg)
+    close_to_peak(out, x.float() @ G.mxfp4_dequant(w, s).t(), 1e-2)
+    close_to_peak(out, ops.mxfp4_wmma_gemm(w.to(DEV), x.to(DEV), s.to(DEV), None).float().cpu(), 1e-2)
+    for scheme in ("block", "channel"):
+        w8, sc = fp8_case(n, k, scheme)
+        ref_w = G.fp8_dequant(w8, sc)
+        out = ops.fp8_wmma_gemm_cfg(w8.to(DEV), x.to(DEV), sc.to(DEV), cfg)
+        close_to_peak(out, x.float() @ ref_w.to(torch.bfloat16).float().t(), 1e-2)
+        out = ops.fp8_wmma_gemm_raw_cfg(w8.to(DEV), x.half().to(DEV), sc.to(DEV), cfg)
+        close_to_peak(out, x.half().float() @ ref_w.t(), 1e-2)
+    w_i8 = torch.randint(-127, 128, (n, k), generator=g, dtype=torch.int8)
+    w_u8 = (w_i8.to(torch.int16) + 128).to(torch.uint8)
+    sw = torch.rand(n, generator=g) * 0.01 + 1e-4
+    out = ops.w8a8_wmma_gemm_cfg(w_u8.to(DEV), x.to(DEV), sw.to(DEV), cfg)
+    q, sg = G.act_quant_group_i8(x)
+    close_to_peak(out, (q.float() * sg.repeat_interleave(128, 1)) @ (w_i8.float() * sw[:, None]).t(), 1e-2)
+    with pytest.raises(RuntimeError, match="cfg must be in"):
+        ops.w8a8_wmma_gemm_cfg(w_u8.to(DEV), x.to(DEV), sw.to(DEV), len(torch_ops.TILE_CFGS))
 
 
 # ------------------------------------------------- MXFP4 on tcgen05 (sorted layout)
