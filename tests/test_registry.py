@@ -69,3 +69,33 @@ def test_selections_are_recorded():
     assert miss is None
     rec = [s for s in strix.selections() if s["query"].get("head_dim") == 96][0]
     assert rec["kernel"] is None and "head_dim=96" in rec["reason"]
+
+
+def test_every_head_size_of_the_reference_table_is_covered():
+    """(head_dim, gqa, kv_dtype) of the reference's attention rows
+    (python/strix/registry.py:368-560): each selects a kernel here."""
+    prefill = [(256, 6), (256, 8), (256, 2), (512, 8), (64, 4), (128, 8)]
+    decode = [(256, 2), (512, 8), (256, 8), (128, 8)]
+    for hd, gqa in prefill:
+        for kv in ("bf16", "int8"):
+            assert strix.select("attn_prefill", head_dim=hd, gqa=gqa, dtype="bf16", kv_dtype=kv,
+                                split_kv=False, window=True, causal=True, sinks=False) \
+                == "attn_prefill_bf16", (hd, gqa, kv)
+    for hd, gqa in decode:
+        for kv in ("bf16", "int8"):
+            assert strix.select("attn_decode", head_dim=hd, gqa=gqa, queries=1, dtype="bf16",
+                                kv_dtype=kv, window=False, sinks=False) == "attn_decode_bf16", (hd, gqa, kv)
+
+
+def test_tile_sweep_ops_take_a_bounded_cfg():
+    import pytest
+
+    assert [torch_ops._cfg_block_m(i) for i in range(len(torch_ops.TILE_CFGS))] == list(torch_ops.TILE_CFGS)
+    for bad in (-1, len(torch_ops.TILE_CFGS)):
+        with pytest.raises(RuntimeError, match="cfg must be in"):
+            torch_ops._cfg_block_m(bad)
+    sweeps = {"fp8_wmma_gemm_cfg": "fp8_tile_sweep", "fp8_wmma_gemm_raw_cfg": "fp8_tile_sweep",
+              "w8a8_wmma_gemm_cfg": "w8a8_tile_sweep", "mxfp4_wmma_gemm_cfg": "mxfp4_tile_sweep"}
+    rows = {k["name"]: k["op"] for k in strix.kernels()}
+    for name, op in sweeps.items():
+        assert name in torch_ops.registered_ops() and rows[name] == op
