@@ -8,7 +8,7 @@
 // joins only the denominator.
 //
 // Shape of the kernel: a CTA = 64 queries of one sequence x one query head, 4
-// warps of 16 queries. Key tiles of 64: the raw cache rows of the NEXT tile are
+// warps of 16 queries. Key tiles of 64 (32 above head 128): the raw cache rows of the NEXT tile are
 // in flight (cp.async, double buffer) while the current one is used. int8
 // caches are widened once per tile to fp16 in shared memory with byte permutes
 // (exact, the scales stay out: K scale on the score, V scale on P), and the two
@@ -18,7 +18,7 @@
 // 16-byte-chunk XOR swizzle. Softmax is online, in the exp2 domain, fp32.
 //
 // Head 256 keeps the query tile in shared memory too (its fragments are re-read per
-// key tile). Head 512 (SPLIT = 2) gives each group of 16 queries to a PAIR of warps,
+// key tile) and runs two CTAs of 97 KB per SM. Head 512 (SPLIT = 2) gives each group of 16 queries to a PAIR of warps,
 // each owning 256 of the head's dims - that part of Q, of every K row (score
 // partials, added through shared memory behind a 64-thread named barrier) and of
 // every V row and O - over key tiles of 32.
@@ -73,7 +73,7 @@ struct PfLayout {
   static constexpr int kSplit = D > 256 ? 2 : 1;                 // warps sharing 16 queries
   static constexpr int kDW = D / kSplit;                         // head dims per warp
   static constexpr int kThreads = 128 * kSplit;
-  static constexpr int kBN = D > 256 ? 32 : 64;                  // keys per tile
+  static constexpr int kBN = D > 128 ? 32 : 64;                  // keys per tile
   static constexpr int kTile = kBN * D * 2;                      // one 16-bit operand tile
   static constexpr int kRawKV = Q8 ? kBN * D : 0;                // raw int8 rows of K (or V)
   static constexpr int kRaw = Q8 ? 2 * kRawKV + 2 * kBN * 4 : 0; // K, V, k scales, v scales
@@ -90,7 +90,7 @@ struct PfLayout {
 };
 
 template <int D, bool Q8>
-__global__ void __launch_bounds__(PfLayout<D, Q8>::kThreads, D > 128 ? 1 : 3)
+__global__ void __launch_bounds__(PfLayout<D, Q8>::kThreads, D <= 128 ? 3 : D == 256 ? 2 : 1)
 attn_prefill_kernel(const PrefillArgs p) {
   using L = PfLayout<D, Q8>;
   constexpr bool QS = L::kQInSmem;
@@ -300,7 +300,7 @@ attn_prefill_kernel(const PrefillArgs p) {
     const float* svs = sks + kBN;
     float mx_lo = m_lo, mx_hi = m_hi;
     // a tile strictly inside every row's visible range needs no mask (most tiles do not):
-    // all 64 keys at or before the warp's first query, and inside the window of its last
+    // all its keys at or before the warp's first query, and inside the window of its last
     const bool interior = k0 + kBN - 1 <= pos0 + row0 &&
                           (p.window_left < 0 || pos0 + row0 + 15 - k0 <= p.window_left);
     if (interior) {

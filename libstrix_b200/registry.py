@@ -372,13 +372,14 @@ KERNELS: list[Kernel] = [
     ) for hd in (128, 64)],
     Kernel(
         "attn_prefill_bf16", "attn_prefill",
-        "head 256 (the reference's GQA 6 / 8 / 2 rows and any other ratio): the same 64 x 64 "
-        "mma.sync kernel, one CTA per SM, with the query tile in shared memory (its fragments "
-        "re-read by ldmatrix per key tile) because 128 accumulator registers leave no room for it",
+        "head 256 (the reference's GQA 6 / 8 / 2 rows and any other ratio): the same mma.sync "
+        "kernel over 64 x 32 tiles, two CTAs per SM, with the query tile in shared memory (its "
+        "fragments re-read by ldmatrix per key tile) because 128 accumulator registers leave no "
+        "room for it",
         {"head_dim": 256, "gqa": Range(1, 64), "dtype": "bf16", "kv_dtype": ("bf16", "int8"),
          "split_kv": (True, False), "window": (True, False), "causal": True,
          "sinks": (True, False)},
-        {"tile": "64 queries x 64 keys", "mma": "m16n8k16 f16 (int8 KV) / bf16", "bound": "tensor"},
+        {"tile": "64 queries x 32 keys", "mma": "m16n8k16 f16 (int8 KV) / bf16", "bound": "tensor"},
     ),
     Kernel(
         "attn_prefill_bf16", "attn_prefill",
