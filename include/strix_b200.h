@@ -227,6 +227,29 @@ int strix_attn_prefill_bf16(void* out, const void* q, const void* key_cache,
                             double scale, int64_t num_splits, int64_t window_left, int kv_int8,
                             strix_stream_t stream);
 
+/* Decode attention through the prefill kernel, for the geometries of
+ * strix_attn_decode_bf16 that have no split-KV kernel (int8 caches at head_dim 512,
+ * hq / hkv above 8): same arguments as strix_attn_prefill_bf16, but the rows
+ * cu_seqlens_q[n] .. cu_seqlens_q[n + 1] of sequence n are the G = hq_model / hkv query
+ * heads that share one KV head, ALL at position seq_lens[n] - 1 (no causal order among
+ * them). The caller regroups q and out to [nseq * G, hkv, head_dim] (row n * G + g,
+ * head h = query head h * G + g) and passes hq = hkv; a KV head is then read once per
+ * sequence. sinks stays fp32 [hkv * G] in query-head order. One pass, no split-KV. */
+int strix_attn_decode_grouped_bf16(void* out, const void* q, const void* key_cache,
+                                   const void* value_cache, const float* k_scale,
+                                   const float* v_scale, const int32_t* cu_seqlens_q,
+                                   const int32_t* seq_lens, const int32_t* block_table,
+                                   const float* sinks, int64_t total_q, int64_t nseq, int64_t hq,
+                                   int64_t hkv, int64_t head_dim, int64_t block_size,
+                                   int64_t bt_stride, int64_t q_stride_t, int64_t q_stride_h,
+                                   int64_t out_stride_t, int64_t out_stride_h, int64_t k_stride_b,
+                                   int64_t k_stride_s, int64_t k_stride_h, int64_t v_stride_b,
+                                   int64_t v_stride_s, int64_t v_stride_h, int64_t ks_stride_b,
+                                   int64_t ks_stride_s, int64_t ks_stride_h, int64_t vs_stride_b,
+                                   int64_t vs_stride_s, int64_t vs_stride_h, double scale,
+                                   int64_t num_splits, int64_t window_left, int kv_int8,
+                                   strix_stream_t stream);
+
 /* Grouped or dense GEMM with 4-bit weights and bf16 activations, on the
  * weight-streaming kernel. Replaces moe_gemm_w4a16 (csrc/moe/moe_gemm_w4a16.hip:374),
  * w4a16_wmma_gemm, mxfp4_wmma_gemm / mxfp4_gemv (csrc/gemm/mxfp4_wmma_gemm.hip:355-372,

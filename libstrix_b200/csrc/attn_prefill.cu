@@ -48,6 +48,7 @@ struct PrefillArgs {
   int64_t bt_stride;
   int nseq, hq, hkv, block_size, window_left;
   int aligned16;            // cache rows start on 16-byte boundaries
+  int same_pos;             // decode form: every query row of a sequence sits at its last position
   float scale;
 };
 
@@ -120,9 +121,13 @@ attn_prefill_kernel(const PrefillArgs p) {
   const int row0 = tile * kBM + warp * 16;             // this warp's first query (local index)
   const int pos0 = kv_len - q_len;                     // position of local query 0
   // keys this CTA needs: up to its last query's position, from the window of its first
+  // (decode form: the rows of a sequence are the query heads of one KV head, all at the
+  // last position - no causal order among them)
+  const bool grp = p.same_pos != 0;
   const int cta_last = min(tile * kBM + kBM, q_len) - 1;
-  const int k_end = pos0 + cta_last + 1;
-  const int k_begin = p.window_left >= 0 ? max(0, pos0 + tile * kBM - p.window_left) / kBN * kBN : 0;
+  const int k_end = grp ? kv_len : pos0 + cta_last + 1;
+  const int cta_first_pos = grp ? kv_len - 1 : pos0 + tile * kBM;
+  const int k_begin = p.window_left >= 0 ? max(0, cta_first_pos - p.window_left) / kBN * kBN : 0;
   const int n_tiles = (k_end - k_begin + kBN - 1) / kBN;
 
   // ---- Q fragments (A operand, m16k16 per 16 dims), rows g and g + 8 of the warp
@@ -155,7 +160,10 @@ attn_prefill_kernel(const PrefillArgs p) {
     }
     if constexpr (QS) __syncwarp();
   }
-  const int qpos_lo = pos0 + row0 + g, qpos_hi = qpos_lo + 8;   // positions of the two rows
+  const int qpos_lo = grp ? kv_len - 1 : pos0 + row0 + g;       // positions of the two rows
+  const int qpos_hi = grp ? kv_len - 1 : qpos_lo + 8;
+  const int wpos_first = grp ? kv_len - 1 : pos0 + row0;        // of the warp's first and last row
+  const int wpos_last = grp ? kv_len - 1 : pos0 + row0 + 15;
 
   const uint32_t smem_s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
   // Q8: [raw 0][raw 1][K16][V16]; bf16: [K16 0][V16 0][K16 1][V16 1]
@@ -301,8 +309,8 @@ attn_prefill_kernel(const PrefillArgs p) {
     float mx_lo = m_lo, mx_hi = m_hi;
     // a tile strictly inside every row's visible range needs no mask (most tiles do not):
     // all its keys at or before the warp's first query, and inside the window of its last
-    const bool interior = k0 + kBN - 1 <= pos0 + row0 &&
-                          (p.window_left < 0 || pos0 + row0 + 15 - k0 <= p.window_left);
+    const bool interior = k0 + kBN - 1 <= wpos_first &&
+                          (p.window_left < 0 || wpos_last - k0 <= p.window_left);
     if (interior) {
 #pragma unroll
       for (int j = 0; j < kBN / 8; ++j) {
@@ -390,14 +398,16 @@ attn_prefill_kernel(const PrefillArgs p) {
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  const int r_lo = row0 + g, r_hi = row0 + g + 8;
   if (p.sinks != nullptr) {
-    const float sk = p.sinks[head] * kLog2e;
-    if (m_lo == -INFINITY) l_lo = 1.f; else l_lo += fast_exp2(sk - m_lo);
-    if (m_hi == -INFINITY) l_hi = 1.f; else l_hi += fast_exp2(sk - m_hi);
+    // decode form: row r of the sequence is query head head * q_len + r
+    const float sk_lo = p.sinks[grp ? head * q_len + min(r_lo, q_len - 1) : head] * kLog2e;
+    const float sk_hi = p.sinks[grp ? head * q_len + min(r_hi, q_len - 1) : head] * kLog2e;
+    if (m_lo == -INFINITY) l_lo = 1.f; else l_lo += fast_exp2(sk_lo - m_lo);
+    if (m_hi == -INFINITY) l_hi = 1.f; else l_hi += fast_exp2(sk_hi - m_hi);
   }
   const float unlift = Q8 ? 1.f / kLift : 1.f;
   const float inv_lo = l_lo > 0.f ? unlift / l_lo : 0.f, inv_hi = l_hi > 0.f ? unlift / l_hi : 0.f;
-  const int r_lo = row0 + g, r_hi = row0 + g + 8;
 #pragma unroll
   for (int i = 0; i < DW / 8; ++i) {
     if (r_lo < q_len)
@@ -430,7 +440,8 @@ int launch_prefill(const PrefillArgs& p, int64_t max_tiles, cudaStream_t st) {
 
 using namespace strix;
 
-extern "C" int strix_attn_prefill_bf16(
+static int prefill_impl(
+    int same_pos,
     void* out, const void* q, const void* key_cache, const void* value_cache, const float* k_scale,
     const float* v_scale, const int32_t* cu_seqlens_q, const int32_t* seq_lens,
     const int32_t* block_table, const float* sinks, int64_t total_q, int64_t nseq, int64_t hq,
@@ -469,6 +480,7 @@ extern "C" int strix_attn_prefill_bf16(
   p.bt_stride = bt_stride;
   p.nseq = int(nseq), p.hq = int(hq), p.hkv = int(hkv), p.block_size = int(block_size);
   p.window_left = int(window_left), p.aligned16 = a16 ? 1 : 0, p.scale = float(scale);
+  p.same_pos = same_pos;
   // an upper bound on the 64-query tiles without reading the lengths on the host
   const int64_t max_tiles = (total_q + kBM - 1) / kBM + nseq;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -476,4 +488,33 @@ extern "C" int strix_attn_prefill_bf16(
   if (head_dim == 256) return kv_int8 ? launch_prefill<256, true>(p, max_tiles, st) : launch_prefill<256, false>(p, max_tiles, st);
   if (head_dim == 128) return kv_int8 ? launch_prefill<128, true>(p, max_tiles, st) : launch_prefill<128, false>(p, max_tiles, st);
   return kv_int8 ? launch_prefill<64, true>(p, max_tiles, st) : launch_prefill<64, false>(p, max_tiles, st);
+}
+
+#define STRIX_PREFILL_PARAMS                                                                       \
+  void *out, const void *q, const void *key_cache, const void *value_cache, const float *k_scale, \
+      const float *v_scale, const int32_t *cu_seqlens_q, const int32_t *seq_lens,                 \
+      const int32_t *block_table, const float *sinks, int64_t total_q, int64_t nseq, int64_t hq,  \
+      int64_t hkv, int64_t head_dim, int64_t block_size, int64_t bt_stride, int64_t q_stride_t,   \
+      int64_t q_stride_h, int64_t out_stride_t, int64_t out_stride_h, int64_t k_stride_b,         \
+      int64_t k_stride_s, int64_t k_stride_h, int64_t v_stride_b, int64_t v_stride_s,             \
+      int64_t v_stride_h, int64_t ks_stride_b, int64_t ks_stride_s, int64_t ks_stride_h,          \
+      int64_t vs_stride_b, int64_t vs_stride_s, int64_t vs_stride_h, double scale,                \
+      int64_t num_splits, int64_t window_left, int kv_int8, strix_stream_t stream
+#define STRIX_PREFILL_ARGS                                                                          \
+  out, q, key_cache, value_cache, k_scale, v_scale, cu_seqlens_q, seq_lens, block_table, sinks,    \
+      total_q, nseq, hq, hkv, head_dim, block_size, bt_stride, q_stride_t, q_stride_h,             \
+      out_stride_t, out_stride_h, k_stride_b, k_stride_s, k_stride_h, v_stride_b, v_stride_s,      \
+      v_stride_h, ks_stride_b, ks_stride_s, ks_stride_h, vs_stride_b, vs_stride_s, vs_stride_h,    \
+      scale, num_splits, window_left, kv_int8, stream
+
+extern "C" int strix_attn_prefill_bf16(STRIX_PREFILL_PARAMS) {
+  return prefill_impl(0, STRIX_PREFILL_ARGS);
+}
+
+// Decode through the same kernel, for geometries without a split-KV decode kernel: the
+// rows cu_seqlens_q[n] .. of sequence n are the hq / hkv query heads of one KV head (q
+// and out regrouped to [nseq * G, hkv, head_dim]), all at position seq_lens[n] - 1, so a
+// KV head is read once for its whole group; sinks stay [hkv * G] in query-head order.
+extern "C" int strix_attn_decode_grouped_bf16(STRIX_PREFILL_PARAMS) {
+  return prefill_impl(1, STRIX_PREFILL_ARGS);
 }

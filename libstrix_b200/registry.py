@@ -392,8 +392,9 @@ KERNELS: list[Kernel] = [
         {"tile": "64 queries x 32 keys", "mma": "m16n8k16 f16 (int8 KV) / bf16", "bound": "tensor"},
     ),
     Kernel("attn_decode_bf16", "attn_decode",
-           "int8 KV cache at head 512: no split-KV kernel of its own - the prefill kernel with one "
-           "query per sequence (correct, but it reads a KV head once per query head)",
+           "int8 KV cache at head 512: no split-KV kernel of its own - the prefill kernel in its "
+           "decode form (the query heads of a KV head as the rows of one sequence, all at the last "
+           "position: a KV head is read once, in one pass)",
            {"head_dim": 512, "gqa": Range(1, 64), "queries": 1, "dtype": "bf16",
             "kv_dtype": ("int8",), "window": (True, False), "sinks": (True, False)},
            {"tile": "64 queries x 32 keys", "bound": "hbm"}),

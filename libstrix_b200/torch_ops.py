@@ -104,14 +104,29 @@ def attn_decode_bf16(
         st % 8 == 0 for t in (key_cache, value_cache) for st in t.stride()[:3]) and \
         key_cache.data_ptr() % 16 == 0 and value_cache.data_ptr() % 16 == 0
     if (not q8 and not bf16_rows_ok) or (q8 and d == 512):
-        # caches the split-KV decode kernels do not take (bf16 rows off 16-byte
-        # boundaries or at a GQA ratio above 8, int8 caches at head 512): the prefill
-        # kernel with one query per sequence
-        nseq = q.size(0)
-        cu = torch.arange(nseq + 1, dtype=torch.int32, device=q.device)
-        attn_prefill_bf16(out, q, key_cache, value_cache, k_scale if q8 else None,
-                          v_scale if q8 else None, cu, seq_lens, block_table, cu,
-                          0, scale, 1, window_left, sinks)
+        # caches the split-KV decode kernels do not take (bf16 caches at a GQA ratio above
+        # 8 or another head size, int8 caches at head 512): the prefill kernel in its decode
+        # form - the query heads of a KV head become the rows of one sequence, all at the
+        # last position, so a KV head is read once
+        nseq, hq, hkv = q.size(0), q.size(1), key_cache.size(2)
+        _check(hkv > 0 and hq % hkv == 0, "Hq % Hkv")
+        g = hq // hkv
+        qg = q.view(nseq, hkv, g, d).transpose(1, 2).reshape(nseq * g, hkv, d).contiguous()
+        og = torch.empty_like(qg)
+        cu = torch.arange(0, (nseq + 1) * g, g, dtype=torch.int32, device=q.device)
+        ks, vs = (k_scale, v_scale) if q8 else (None, None)
+        with torch.cuda.device(q.device):
+            _lib.call(
+                "strix_attn_decode_grouped_bf16",
+                og.data_ptr(), qg.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(), _ptr(ks),
+                _ptr(vs), cu.data_ptr(), seq_lens.data_ptr(), block_table.data_ptr(), _ptr(sinks),
+                nseq * g, nseq, hkv, hkv, d, key_cache.size(1), block_table.stride(0), qg.stride(0),
+                qg.stride(1), og.stride(0), og.stride(1), key_cache.stride(0), key_cache.stride(1),
+                key_cache.stride(2), value_cache.stride(0), value_cache.stride(1),
+                value_cache.stride(2), *(ks.stride() if q8 else (0, 0, 0)),
+                *(vs.stride() if q8 else (0, 0, 0)), float(scale), 1, window_left, int(q8), _stream(),
+            )
+        out.copy_(og.view(nseq, g, hkv, d).transpose(1, 2).reshape(nseq, hq, d))
         return
     nseq, hq = q.size(0), q.size(1)
     bs, hkv = key_cache.size(1), key_cache.size(2)

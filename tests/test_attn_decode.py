@@ -231,7 +231,8 @@ def test_full_size_properties(strix):
 
 
 @pytest.mark.parametrize("hq,hkv,hd", [(32, 4, 128), (16, 2, 128), (8, 8, 64), (6, 1, 128),
-                                       (16, 2, 256), (8, 4, 256), (6, 1, 256), (16, 2, 512), (4, 4, 512)])
+                                       (16, 2, 256), (8, 4, 256), (6, 1, 256), (16, 2, 512), (4, 4, 512),
+                                       (32, 2, 128), (24, 2, 64)])
 @pytest.mark.parametrize("num_splits", [0, 1, 5])
 def test_bf16_kv_cache(strix, hq, hkv, hd, num_splits):
     """The reference's native form: a bf16 cache, split-KV, window and sinks, ragged
