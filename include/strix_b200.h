@@ -228,8 +228,8 @@ int strix_attn_prefill_bf16(void* out, const void* q, const void* key_cache,
                             strix_stream_t stream);
 
 /* Decode attention through the prefill kernel, for the geometries of
- * strix_attn_decode_bf16 that have no split-KV kernel (int8 caches at head_dim 512,
- * hq / hkv above 8): same arguments as strix_attn_prefill_bf16, but the rows
+ * strix_attn_decode_bf16 that have no split-KV kernel (int8 caches at head_dim 64 or
+ * 512, hq / hkv above 8): same arguments as strix_attn_prefill_bf16, but the rows
  * cu_seqlens_q[n] .. cu_seqlens_q[n + 1] of sequence n are the G = hq_model / hkv query
  * heads that share one KV head, ALL at position seq_lens[n] - 1 (no causal order among
  * them). The caller regroups q and out to [nseq * G, hkv, head_dim] (row n * G + g,

@@ -338,6 +338,14 @@ KERNELS: list[Kernel] = [
     _decode_row(256, 8, "head 256 GQA 8, four warps per CTA (255 registers)"),
     _decode_row(256, 6, "head 256 GQA 6 (two MMA columns idle)"),
     _decode_row(256, 2, "head 256 GQA 2 (sliding layers)"),
+    Kernel("attn_decode_bf16", "attn_decode",
+           "every other int8 geometry: GQA ratios 3, 5, 7 on the split-KV kernel; head 64 or 512 "
+           "and ratios above 8 have no split-KV kernel - the prefill kernel in its decode form (the "
+           "query heads of a KV head as the rows of one sequence, all at the last position: a KV "
+           "head is read once, in one pass)",
+           {"head_dim": (64, 128, 256, 512), "gqa": Range(1, 64), "queries": 1, "dtype": "bf16",
+            "kv_dtype": ("int8",), "window": (True, False), "sinks": (True, False)},
+           {"tile": "64 queries x 64 / 32 keys", "bound": "hbm"}),
     *[Kernel("attn_decode_bf16", "attn_decode",
              "bf16 KV cache, split-KV: one warp per KV head, per-warp cp.async ring of 16-key "
              "tiles, K and V^T fragments by ldmatrix, bf16 m16n8k16 MMAs (rows on 16-byte "
@@ -348,16 +356,17 @@ KERNELS: list[Kernel] = [
              {"tile_keys": 16, "mma": "m16n8k16 bf16, keys as M", "bound": "hbm"})
       for hd in (128, 64)],
     Kernel("attn_decode_bf16", "attn_decode",
-           "bf16 KV cache at head 256 (GQA 1-8 only: no prefill kernel behind it), two KV heads "
-           "per CTA so that two 96 KB rings share an SM",
-           {"head_dim": 256, "gqa": Range(1, 8), "queries": 1, "dtype": "bf16",
+           "bf16 KV cache at head 256, two KV heads per CTA so that two 96 KB rings share an SM "
+           "(GQA above 8: the prefill kernel's decode form)",
+           {"head_dim": 256, "gqa": Range(1, 64), "queries": 1, "dtype": "bf16",
             "kv_dtype": ("bf16",), "window": (True, False), "sinks": (True, False)},
            {"tile_keys": 16, "mma": "m16n8k16 bf16, keys as M", "bound": "hbm"}),
     Kernel("attn_decode_bf16", "attn_decode",
            "bf16 KV cache at head 512 (the reference's GQA 8 row; GQA 1-8): the head's dims split "
            "over a pair of warps, each with its half of every K and V row in its own ring; the pair "
-           "adds its score partials through shared memory once per 16-key tile",
-           {"head_dim": 512, "gqa": Range(1, 8), "queries": 1, "dtype": "bf16",
+           "adds its score partials through shared memory once per 16-key tile (GQA above 8: the "
+           "prefill kernel's decode form)",
+           {"head_dim": 512, "gqa": Range(1, 64), "queries": 1, "dtype": "bf16",
             "kv_dtype": ("bf16",), "window": (True, False), "sinks": (True, False)},
            {"tile_keys": 16, "mma": "m16n8k16 bf16, keys as M", "bound": "hbm"}),
     *[Kernel(
@@ -391,13 +400,6 @@ KERNELS: list[Kernel] = [
          "sinks": (True, False)},
         {"tile": "64 queries x 32 keys", "mma": "m16n8k16 f16 (int8 KV) / bf16", "bound": "tensor"},
     ),
-    Kernel("attn_decode_bf16", "attn_decode",
-           "int8 KV cache at head 512: no split-KV kernel of its own - the prefill kernel in its "
-           "decode form (the query heads of a KV head as the rows of one sequence, all at the last "
-           "position: a KV head is read once, in one pass)",
-           {"head_dim": 512, "gqa": Range(1, 64), "queries": 1, "dtype": "bf16",
-            "kv_dtype": ("int8",), "window": (True, False), "sinks": (True, False)},
-           {"tile": "64 queries x 32 keys", "bound": "hbm"}),
 ]
 
 _POINT_TYPES = (int, bool, str)

@@ -103,9 +103,10 @@ def attn_decode_bf16(
     bf16_rows_ok = not q8 and d in (64, 128, 256, 512) and q.size(1) // key_cache.size(2) <= 8 and all(
         st % 8 == 0 for t in (key_cache, value_cache) for st in t.stride()[:3]) and \
         key_cache.data_ptr() % 16 == 0 and value_cache.data_ptr() % 16 == 0
-    if (not q8 and not bf16_rows_ok) or (q8 and d == 512):
-        # caches the split-KV decode kernels do not take (bf16 caches at a GQA ratio above
-        # 8 or another head size, int8 caches at head 512): the prefill kernel in its decode
+    gqa = q.size(1) // max(key_cache.size(2), 1)
+    if (not q8 and not bf16_rows_ok) or (q8 and (d not in (128, 256) or gqa > 8)):
+        # caches the split-KV decode kernels do not take (a GQA ratio above 8, int8 caches
+        # at head 64 or 512, bf16 rows off 16-byte boundaries): the prefill kernel in its decode
         # form - the query heads of a KV head become the rows of one sequence, all at the
         # last position, so a KV head is read once
         nseq, hq, hkv = q.size(0), q.size(1), key_cache.size(2)

@@ -64,11 +64,13 @@ def test_other_geometries(strix, hq, hkv, hd, num_splits, block_size):
              False)
 
 
+@pytest.mark.parametrize("hq,hkv,hd", [(16, 2, 512), (32, 2, 128), (8, 2, 64), (24, 2, 256)])
 @pytest.mark.parametrize("window_left,use_sinks", [(-1, False), (40, True)])
-def test_head_512_int8_cache(strix, window_left, use_sinks):
+def test_int8_cache_through_the_grouped_form(strix, hq, hkv, hd, window_left, use_sinks):
     """Head 512 GQA 8 over an int8 cache (python/strix/registry.py:478-492 of the
-    reference): served by the prefill kernel with one query per sequence."""
-    run_case(strix, 16, 2, 512, [70, 200, 3, 0, 1000], 16, 1, window_left, use_sinks)
+    reference), head 64, and GQA ratios above 8: served by the prefill kernel in its
+    decode form (the query heads of a KV head as rows of one sequence)."""
+    run_case(strix, hq, hkv, hd, [70, 200, 3, 0, 1000], 16, 1, window_left, use_sinks)
 
 
 def test_golden_fixture_cases(strix):
