@@ -112,7 +112,7 @@ def attn_decode_bf16(
         nseq, hq, hkv = q.size(0), q.size(1), key_cache.size(2)
         _check(hkv > 0 and hq % hkv == 0, "Hq % Hkv")
         g = hq // hkv
-        qg = q.view(nseq, hkv, g, d).transpose(1, 2).reshape(nseq * g, hkv, d).contiguous()
+        qg = q.reshape(nseq, hkv, g, d).transpose(1, 2).reshape(nseq * g, hkv, d).contiguous()
         og = torch.empty_like(qg)
         cu = torch.arange(0, (nseq + 1) * g, g, dtype=torch.int32, device=q.device)
         ks, vs = (k_scale, v_scale) if q8 else (None, None)
