@@ -58,6 +58,21 @@ def registered_ops() -> list[str]:
 
 # ----------------------------------------------------------------- attention
 
+def group_queries(q: torch.Tensor, hkv: int) -> torch.Tensor:
+    """[nseq, hq, d] -> contiguous [nseq * G, hkv, d]: row n * G + j, head h holds query
+    head h * G + j (the layout strix_attn_decode_grouped_bf16 reads)."""
+    nseq, hq, d = q.shape
+    g = hq // hkv
+    return q.reshape(nseq, hkv, g, d).transpose(1, 2).reshape(nseq * g, hkv, d).contiguous()
+
+
+def ungroup_queries(og: torch.Tensor, nseq: int) -> torch.Tensor:
+    """Inverse of group_queries: [nseq * G, hkv, d] -> [nseq, hkv * G, d]."""
+    rows, hkv, d = og.shape
+    g = rows // max(nseq, 1)
+    return og.reshape(nseq, g, hkv, d).transpose(1, 2).reshape(nseq, hkv * g, d)
+
+
 
 @_define(
     "attn_decode_bf16(Tensor(a!) out, Tensor q, Tensor key_cache, "
@@ -112,7 +127,9 @@ def attn_decode_bf16(
         nseq, hq, hkv = q.size(0), q.size(1), key_cache.size(2)
         _check(hkv > 0 and hq % hkv == 0, "Hq % Hkv")
         g = hq // hkv
-        qg = q.reshape(nseq, hkv, g, d).transpose(1, 2).reshape(nseq * g, hkv, d).contiguous()
+        if nseq == 0:
+            return
+        qg = group_queries(q, hkv)
         og = torch.empty_like(qg)
         cu = torch.arange(0, (nseq + 1) * g, g, dtype=torch.int32, device=q.device)
         ks, vs = (k_scale, v_scale) if q8 else (None, None)
@@ -127,7 +144,7 @@ def attn_decode_bf16(
                 value_cache.stride(2), *(ks.stride() if q8 else (0, 0, 0)),
                 *(vs.stride() if q8 else (0, 0, 0)), float(scale), 1, window_left, int(q8), _stream(),
             )
-        out.copy_(og.view(nseq, g, hkv, d).transpose(1, 2).reshape(nseq, hq, d))
+        out.copy_(ungroup_queries(og, nseq))
         return
     nseq, hq = q.size(0), q.size(1)
     bs, hkv = key_cache.size(1), key_cache.size(2)

@@ -41,3 +41,21 @@ def test_fake_output_is_bf16_rows_by_channels(name):
     with FakeTensorMode():
         out = CASES[name]()
     assert tuple(out.shape) == (M, N) and out.dtype == torch.bfloat16
+
+
+def test_query_regrouping_of_the_grouped_decode_form():
+    """group_queries puts query head h * G + j of sequence n at row n * G + j, head h -
+    also for a q that is a strided slice of a fused qkv tensor - and ungroup_queries is
+    its inverse."""
+    from libstrix_b200 import torch_ops
+
+    nseq, hkv, g, d = 3, 2, 4, 8
+    qkv = torch.randn(nseq, (hkv * g + 2 * hkv) * d)
+    q = qkv[:, :hkv * g * d].view(nseq, hkv * g, d)
+    qg = torch_ops.group_queries(q, hkv)
+    assert qg.is_contiguous() and tuple(qg.shape) == (nseq * g, hkv, d)
+    for n in range(nseq):
+        for h in range(hkv):
+            for j in range(g):
+                assert torch.equal(qg[n * g + j, h], q[n, h * g + j])
+    assert torch.equal(torch_ops.ungroup_queries(qg, nseq), q)
